@@ -1,0 +1,140 @@
+"""ctypes bindings for the in-tree native libraries.
+
+``kernels()`` returns the CUDA kernel library (``_gk_kernels.so``) and ``runtime()`` the host C++ runtime
+(``_gk_runtime.so``).  On a machine with a GPU a missing kernel library is an error: the GPU code path never
+silently degrades to eager PyTorch.  ``GCORE_B200_FORCE_EAGER=1`` selects the PyTorch reference path on purpose
+(used for the ``nccl_eager`` baseline backend and for debugging).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+
+import torch
+
+_HERE = Path(__file__).resolve().parent
+_KERNELS = None
+_RUNTIME = None
+
+c_void_p = ctypes.c_void_p
+c_int = ctypes.c_int
+c_ll = ctypes.c_longlong
+c_float = ctypes.c_float
+
+
+def force_eager() -> bool:
+    return os.environ.get("GCORE_B200_FORCE_EAGER", "0") == "1"
+
+
+def kernels_available() -> bool:
+    return (_HERE / "_gk_kernels.so").exists()
+
+
+def use_native(t: torch.Tensor | None = None) -> bool:
+    """True when the op should run the hand-written sm_100a kernel."""
+    if force_eager():
+        return False
+    if t is not None and not t.is_cuda:
+        return False
+    if t is None and not torch.cuda.is_available():
+        return False
+    return True
+
+
+def kernels() -> ctypes.CDLL:
+    global _KERNELS
+    if _KERNELS is None:
+        path = _HERE / "_gk_kernels.so"
+        if not path.exists():
+            raise RuntimeError(
+                f"{path} is missing: run `python -m gcore_b200.build_native` (the GPU path does not fall back "
+                "to eager PyTorch)")
+        lib = ctypes.CDLL(str(path))
+        _declare_kernels(lib)
+        _KERNELS = lib
+    return _KERNELS
+
+
+def runtime() -> ctypes.CDLL:
+    global _RUNTIME
+    if _RUNTIME is None:
+        path = _HERE.parent / "runtime" / "_gk_runtime.so"
+        if not path.exists():
+            from .. import build_native
+            build_native.build_runtime()
+        lib = ctypes.CDLL(str(path))
+        _RUNTIME = lib
+    return _RUNTIME
+
+
+def ptr(t: torch.Tensor | None):
+    return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
+
+
+def stream_ptr():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def check(rc: int, what: str):
+    if rc != 0:
+        raise RuntimeError(f"gcore_b200 native call {what} failed with code {rc}")
+
+
+_ERR_FLAGS: dict[int, torch.Tensor] = {}
+
+
+def err_flag(device) -> torch.Tensor:
+    """Per-device int32 the kernels write a non-zero code into when a bounded wait expires."""
+    idx = torch.device(device).index
+    if idx is None:
+        idx = torch.cuda.current_device()
+    if idx not in _ERR_FLAGS:
+        _ERR_FLAGS[idx] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{idx}")
+    return _ERR_FLAGS[idx]
+
+
+def check_device_errors(device=None):
+    """Synchronising check of the kernel error word; raises if any kernel gave up on a wait."""
+    if not torch.cuda.is_available():
+        return
+    dev = device if device is not None else torch.cuda.current_device()
+    idx = torch.device(dev).index if not isinstance(dev, int) else dev
+    if idx in _ERR_FLAGS:
+        code = int(_ERR_FLAGS[idx].item())
+        if code != 0:
+            _ERR_FLAGS[idx].zero_()
+            raise RuntimeError(f"gcore_b200 kernel reported a timed-out wait (code {code})")
+
+
+def _declare_kernels(lib: ctypes.CDLL):
+    def d(name, argtypes, restype=c_int):
+        fn = getattr(lib, name, None)
+        if fn is not None:
+            fn.argtypes = argtypes
+            fn.restype = restype
+
+    P, I, L, F = c_void_p, c_int, c_ll, c_float
+    d("gk_gemm_bf16", [P, L, L, I, P, L, L, I, P, L, I, I, I, P, I, I, F, I, I, I, I, I, I, I, P, I, L, I, P, P, P, P])
+    d("gk_gemm_splitk_scratch", [I, I, I, I, ctypes.POINTER(L), ctypes.POINTER(L)], None)
+    d("gk_rmsnorm_fwd", [P, P, P, P, P, P, I, I, F, P])
+    d("gk_rmsnorm_bwd_parts", [I])
+    d("gk_rmsnorm_bwd", [P, P, P, P, P, P, P, P, I, I, I, P])
+    d("gk_rope", [P, P, I, I, I, I, L, F, I, I, P])
+    d("gk_swiglu_fwd", [P, P, L, I, P])
+    d("gk_swiglu_bwd", [P, P, P, L, I, P])
+    d("gk_adam", [P, P, P, P, I, P, L, F, F, F, F, F, I, P, F, P])
+    d("gk_sumsq", [P, I, L, P, P])
+    d("gk_axpy_cast", [P, I, P, I, L, F, I, P])
+    d("gk_logprob_entropy_fwd", [P, I, L, P, F, I, I, L, P, P, P, P, P])
+    d("gk_logprob_entropy_combine", [P, I, L, P, P, P, P])
+    d("gk_logprob_entropy_bwd", [P, I, L, P, P, P, P, P, F, I, I, L, P])
+    d("gk_sample", [P, I, L, I, I, F, I, P, P, P, P, P, I, P])
+    d("gk_sample_combine", [P, I, I, P, P, P])
+    d("gk_grpo_loss", [P, P, P, P, P, L, F, F, F, F, F, F, P, P, P, P])
+    d("gk_gae", [P, P, P, P, P, I, I, F, F, P])
+    d("gk_kv_append_rope", [P, P, P, P, P, I, I, I, I, I, I, F, I, P])
+    d("gk_paged_decode", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P])
+    d("gk_paged_decode_scratch", [I, I, I, I, ctypes.POINTER(L)], None)
+    d("gk_attn_fwd", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P])
+    d("gk_attn_bwd", [P, P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P])

@@ -1,0 +1,191 @@
+"""Attention front-ends.
+
+* ``flash_attn_varlen`` - training / prefill attention over packed (THD) sequences: causal or full, GQA, sliding
+  window, learned per-head sink logit, prefix-K offset.  Forward runs the tcgen05 kernel
+  (``csrc/attention_fwd.cu``); backward runs ``csrc/attention_bwd.cu`` when built, else a recompute through the
+  PyTorch reference.  Same call contract as ``myfa_varlen_sw_sinks`` (gfused/myfa_varlen_sw_sinks.py:704).
+* ``paged_decode`` / ``kv_append_rope`` - rollout decoder (``csrc/paged_attention.cu``).
+* ``attn_varlen_ref`` - the fp32 PyTorch oracle (mirrors tests/test_gfused/test_myfa_varlen_sw_sinks.py:33-98).
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import _lib
+
+LAUNCHES = {"attention": 0}
+
+
+def attn_varlen_ref(q, k, v, cu_q, cu_k, causal=True, window=0, sinks=None, scale=None, return_lse=False):
+    """fp32 reference.  q [Tq,Hq,D], k/v [Tk,Hk,D]; key j is visible to query i (indices inside a sequence) when
+    ``j <= i + (lk - lq)`` (causal) and ``j > i + (lk - lq) - window`` (window > 0)."""
+    Tq, Hq, D = q.shape
+    Hk = k.shape[1]
+    g = Hq // Hk
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    out = torch.zeros(Tq, Hq, v.shape[-1], dtype=torch.float32, device=q.device)
+    lse = torch.full((Hq, Tq), float("-inf"), dtype=torch.float32, device=q.device)
+    cq, ck = cu_q.tolist(), cu_k.tolist()
+    for b in range(len(cq) - 1):
+        qs, qe, ks, ke = cq[b], cq[b + 1], ck[b], ck[b + 1]
+        lq, lk = qe - qs, ke - ks
+        if lq == 0:
+            continue
+        qb = q[qs:qe].float().transpose(0, 1)  # [Hq, lq, D]
+        kb = k[ks:ke].float().transpose(0, 1).repeat_interleave(g, 0)
+        vb = v[ks:ke].float().transpose(0, 1).repeat_interleave(g, 0)
+        s = torch.einsum("hqd,hkd->hqk", qb, kb) * scale
+        qi = torch.arange(lq, device=q.device)[:, None] + (lk - lq)
+        kj = torch.arange(lk, device=q.device)[None, :]
+        mask = torch.ones(lq, lk, dtype=torch.bool, device=q.device)
+        if causal:
+            mask &= kj <= qi
+        if window and window > 0:
+            mask &= kj > qi - window
+        s = s.masked_fill(~mask[None], float("-inf"))
+        if sinks is not None:
+            s_aug = torch.cat([s, sinks.float()[:, None, None].expand(Hq, lq, 1)], dim=-1)
+            l = torch.logsumexp(s_aug, dim=-1)
+        else:
+            l = torch.logsumexp(s, dim=-1)
+        p = torch.exp(s - l[..., None])
+        p = torch.nan_to_num(p, nan=0.0)
+        out[qs:qe] = torch.einsum("hqk,hkd->hqd", p, vb).transpose(0, 1)
+        lse[:, qs:qe] = l
+    if return_lse:
+        return out.to(q.dtype), lse
+    return out.to(q.dtype)
+
+
+def _native_fwd(q, k, v, cu_q, cu_k, max_q, causal, window, sinks, scale):
+    Tq, Hq, D = q.shape
+    Tk, Hk, _ = k.shape
+    out = torch.empty(Tq, Hq, D, dtype=q.dtype, device=q.device)
+    lse = torch.empty(Hq, Tq, dtype=torch.float32, device=q.device)
+    B = cu_q.numel() - 1
+    strides = (ctypes.c_longlong * 4)(q.stride(0), k.stride(0), v.stride(0), out.stride(0))
+    se = (ctypes.c_void_p * 2)(torch.cuda.current_stream().cuda_stream, _lib.err_flag(q.device).data_ptr())
+    LAUNCHES["attention"] += 1
+    rc = _lib.kernels().gk_attn_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(lse),
+                                    _lib.ptr(cu_q), _lib.ptr(cu_k), _lib.ptr(sinks), B, Tq, Tk, Hq, Hk, D,
+                                    int(max_q), int(causal), float(scale), int(window or 0), 0,
+                                    ctypes.cast(strides, ctypes.c_void_p), ctypes.cast(se, ctypes.c_void_p))
+    _lib.check(rc, "gk_attn_fwd")
+    return out, lse
+
+
+def _native_ok(q, k, v):
+    D = q.shape[-1]
+    return (q.dtype == torch.bfloat16 and _lib.use_native(q) and D in (64, 128) and v.shape[-1] == D
+            and q.stride(2) == 1 and q.stride(1) == D and k.stride(2) == 1 and k.stride(1) == D
+            and v.stride(2) == 1 and v.stride(1) == D and q.stride(0) % 8 == 0 and k.stride(0) % 8 == 0
+            and v.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and k.data_ptr() % 16 == 0
+            and v.data_ptr() % 16 == 0)
+
+
+def _have_native_bwd():
+    return getattr(_lib.kernels(), "gk_attn_bwd", None) is not None
+
+
+class _FlashAttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, sinks, cu_q, cu_k, max_q, max_k, causal, window, scale):
+        out, lse = _native_fwd(q, k, v, cu_q, cu_k, max_q, causal, window, sinks, scale)
+        ctx.save_for_backward(q, k, v, out, lse, sinks if sinks is not None else torch.empty(0), cu_q, cu_k)
+        ctx.cfg = (max_q, max_k, causal, window, scale, sinks is not None)
+        return out
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, out, lse, sinks, cu_q, cu_k = ctx.saved_tensors
+        max_q, max_k, causal, window, scale, has_sinks = ctx.cfg
+        sinks = sinks if has_sinks else None
+        from .attention_bwd import attn_bwd
+        dq, dk, dv, dsinks = attn_bwd(do.contiguous(), q, k, v, out, lse, sinks, cu_q, cu_k, max_q, max_k, causal,
+                                      window, scale)
+        return dq, dk, dv, dsinks, None, None, None, None, None, None, None
+
+
+def flash_attn_varlen(q, k, v, cu_q, cu_k, max_q, max_k, causal=True, window=0, sinks=None, scale=None):
+    """Packed varlen attention; returns ``[Tq, Hq, D]``."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if _native_ok(q, k, v):
+        cu_q = cu_q if cu_q.dtype == torch.int32 else cu_q.to(torch.int32)
+        cu_k = cu_k if cu_k.dtype == torch.int32 else cu_k.to(torch.int32)
+        if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad or
+                                        (sinks is not None and sinks.requires_grad)):
+            return _FlashAttnFn.apply(q, k, v, sinks, cu_q, cu_k, max_q, max_k, causal, window, scale)
+        return _native_fwd(q, k, v, cu_q, cu_k, max_q, causal, window, sinks, scale)[0]
+    return attn_varlen_ref(q, k, v, cu_q, cu_k, causal, window, sinks, scale)
+
+
+# ---------------------------------------------------------------------------------------------- decoder side
+def kv_append_rope(qkv, pos, slots, k_cache, v_cache, Hq, Hk, D, theta, rot=None, do_rope=True):
+    """RoPE on the q and k parts of ``qkv`` [T, (Hq+2Hk)*D] in place, then k/v rows go to cache slot ``slots[t]``
+    (``k_cache``/``v_cache``: [num_blocks, block_size, Hk, D])."""
+    T = qkv.shape[0]
+    rot = rot or D
+    if _lib.use_native(qkv) and qkv.dtype == torch.bfloat16:
+        LAUNCHES["attention"] += 1
+        _lib.check(_lib.kernels().gk_kv_append_rope(_lib.ptr(qkv), _lib.ptr(pos), _lib.ptr(slots), _lib.ptr(k_cache),
+                                                    _lib.ptr(v_cache), T, Hq, Hk, D, rot, int(do_rope), float(theta),
+                                                    0, _lib.stream_ptr()), "kv_append_rope")
+        return
+    from .fused import rope_ref
+    x = qkv.view(T, Hq + 2 * Hk, D)
+    if do_rope:
+        x[:, :Hq + Hk] = rope_ref(x[:, :Hq + Hk], pos, theta, rot)
+    kc = k_cache.view(-1, Hk, D)
+    vc = v_cache.view(-1, Hk, D)
+    valid = slots >= 0
+    kc[slots[valid].long()] = x[valid, Hq:Hq + Hk]
+    vc[slots[valid].long()] = x[valid, Hq + Hk:]
+
+
+_PD_SCRATCH: dict = {}
+
+
+def paged_decode(q, k_cache, v_cache, block_table, ctx_len, max_ctx, scale=None, window=0, sinks=None, out=None):
+    """One-token-per-request attention over the paged cache.  q: [B, Hq, D] (row stride may be a packed QKV row);
+    block_table: [B, max_blocks] int32; ctx_len: [B] int32 (tokens in the cache, including the new one)."""
+    B, Hq, D = q.shape
+    nb, bs, Hk, _ = k_cache.shape
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if out is None:
+        out = torch.empty(B, Hq, D, dtype=q.dtype, device=q.device)
+    if _lib.use_native(q) and q.dtype == torch.bfloat16 and D == 128:
+        lib = _lib.kernels()
+        need = ctypes.c_longlong()
+        lib.gk_paged_decode_scratch(B, Hq, D, int(max_ctx), ctypes.byref(need))
+        key = q.device.index
+        sc = _PD_SCRATCH.get(key)
+        if sc is None or sc.numel() < need.value:
+            sc = torch.empty(max(need.value, 1), dtype=torch.float32, device=q.device)
+            _PD_SCRATCH[key] = sc
+        LAUNCHES["attention"] += 1
+        _lib.check(lib.gk_paged_decode(_lib.ptr(q), _lib.ptr(k_cache), _lib.ptr(v_cache), _lib.ptr(block_table),
+                                       _lib.ptr(ctx_len), _lib.ptr(sinks), _lib.ptr(out), _lib.ptr(sc), B, Hq, Hk, D,
+                                       bs, block_table.shape[1], int(max_ctx), float(scale), int(window or 0),
+                                       q.stride(0), _lib.stream_ptr()), "paged_decode")
+        return out
+    g = Hq // Hk
+    kc = k_cache.view(-1, Hk, D)
+    vc = v_cache.view(-1, Hk, D)
+    for b in range(B):
+        n = int(ctx_len[b])
+        start = max(0, n - window) if window and window > 0 else 0
+        toks = torch.arange(start, n, device=q.device)
+        slots = block_table[b, toks // bs].long() * bs + toks % bs
+        kk = kc[slots].float().repeat_interleave(g, 1)  # [n, Hq, D]
+        vv = vc[slots].float().repeat_interleave(g, 1)
+        s = torch.einsum("hd,nhd->hn", q[b].float(), kk) * scale
+        if sinks is not None:
+            l = torch.logsumexp(torch.cat([s, sinks.float()[:, None]], -1), -1)
+        else:
+            l = torch.logsumexp(s, -1)
+        p = torch.exp(s - l[:, None])
+        out[b] = torch.einsum("hn,nhd->hd", p, vv).to(out.dtype)
+    return out

@@ -1,0 +1,241 @@
+// Rollout-decoder attention: RoPE-fused KV-cache append and split-KV paged decode attention (GQA, optional
+// sliding window and per-head sink logit).  Both are HBM-bandwidth bound, so they run on CUDA cores with
+// 128-bit loads; a CTA serves one (request, kv-head, KV split) and all query heads of the group so every K/V
+// byte is read once.  Stands in for the vLLM / SGLang attention back ends the reference drives
+// (gpatch_v4/generation_backend/infer_engine.py:479-768).
+#include "host_utils.h"
+#include <cuda_bf16.h>
+#include <float.h>
+
+namespace gk {
+
+constexpr int PD_THREADS = 128;
+constexpr int PD_TILE = 32;     // tokens per shared-memory tile
+constexpr int PD_MAX_GROUP = 16;
+constexpr int PD_SPLIT = 256;   // tokens per KV split
+
+// qkv: [T, (Hq + 2*Hk) * D] as produced by the fused QKV projection ([q | k | v] per token).
+// Rotates q and k in place (rotate-half pairing) and writes k, v to cache slot `slots[t]`
+// (slot = block * block_size + offset; negative = skip the cache write).
+__global__ void kv_append_rope_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ pos,
+                                      const int* __restrict__ slots, __nv_bfloat16* __restrict__ kc,
+                                      __nv_bfloat16* __restrict__ vc, int T, int Hq, int Hk, int D, int rot,
+                                      float theta, int do_rope) {
+  const int t = blockIdx.x;
+  if (t >= T) return;
+  const int half = rot >> 1;
+  __nv_bfloat16* row = qkv + static_cast<long long>(t) * (Hq + 2 * Hk) * D;
+  const int p = pos[t];
+  if (do_rope) {
+    const int nrot = (Hq + Hk) * half;
+    for (int i = threadIdx.x; i < nrot; i += blockDim.x) {
+      const int h = i / half, j = i - h * half;
+      const float inv = __powf(theta, -2.f * j / rot);
+      float s, c;
+      sincosf(p * inv, &s, &c);
+      __nv_bfloat16* x = row + h * D;
+      const float a = __bfloat162float(x[j]), b = __bfloat162float(x[j + half]);
+      x[j] = __float2bfloat16(a * c - b * s);
+      x[j + half] = __float2bfloat16(b * c + a * s);
+    }
+    __syncthreads();
+  }
+  const long long slot = slots ? slots[t] : -1;
+  if (slot < 0) return;
+  const int nkv = Hk * D / 8;
+  const uint4* ks = reinterpret_cast<const uint4*>(row + Hq * D);
+  const uint4* vs = reinterpret_cast<const uint4*>(row + (Hq + Hk) * D);
+  uint4* kd = reinterpret_cast<uint4*>(kc + slot * Hk * D);
+  uint4* vd = reinterpret_cast<uint4*>(vc + slot * Hk * D);
+  for (int i = threadIdx.x; i < nkv; i += blockDim.x) {
+    kd[i] = ks[i];
+    vd[i] = vs[i];
+  }
+}
+
+// One CTA per (request b, kv head, split).  D == 128.  Writes either the final output (nsplit == 1) or
+// partial (o unnormalised, m, l) to the scratch buffer for the combine kernel.
+template <int D>
+__global__ void __launch_bounds__(PD_THREADS, 4) paged_decode_kernel(
+    const __nv_bfloat16* __restrict__ q, long long q_stride, const __nv_bfloat16* __restrict__ kc,
+    const __nv_bfloat16* __restrict__ vc, const int* __restrict__ block_table, int max_blocks,
+    const int* __restrict__ ctx_len, const float* __restrict__ sinks, __nv_bfloat16* __restrict__ out,
+    float* __restrict__ scratch, int Hq, int Hk, int block_size, int window, float scale, int nsplit) {
+  constexpr int DP = D + 8;  // padded row (bank-conflict free 16-byte accesses)
+  __shared__ __align__(16) __nv_bfloat16 sk[PD_TILE][DP];
+  __shared__ __align__(16) __nv_bfloat16 sv[PD_TILE][DP];
+  __shared__ float sq[PD_MAX_GROUP][D];
+  __shared__ float sp[PD_MAX_GROUP][PD_TILE];
+  __shared__ float s_m[PD_MAX_GROUP], s_l[PD_MAX_GROUP], s_scale[PD_MAX_GROUP];
+
+  const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  const int G = Hq / Hk;
+  const int len = ctx_len[b];
+  int start = 0;
+  if (window > 0 && len > window) start = len - window;
+  const int s0 = start + split * PD_SPLIT;
+  int s1 = s0 + PD_SPLIT;
+  if (s1 > len) s1 = len;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  for (int i = tid; i < G * D; i += PD_THREADS) {
+    const int g = i / D, d = i - g * D;
+    sq[g][d] = __bfloat162float(q[b * q_stride + static_cast<long long>(kvh * G + g) * D + d]) * scale;
+  }
+  if (tid < PD_MAX_GROUP) { s_m[tid] = -FLT_MAX; s_l[tid] = 0.f; }
+  float o[PD_MAX_GROUP];
+#pragma unroll
+  for (int g = 0; g < PD_MAX_GROUP; ++g) o[g] = 0.f;
+  __syncthreads();
+
+  for (int t0 = s0; t0 < s1; t0 += PD_TILE) {
+    const int nt = s1 - t0 < PD_TILE ? s1 - t0 : PD_TILE;
+    // ---- load K/V tile (16-byte coalesced)
+    for (int i = tid; i < PD_TILE * (D / 8); i += PD_THREADS) {
+      const int r = i / (D / 8), c = i - r * (D / 8);
+      uint4 kk = make_uint4(0, 0, 0, 0), vv = kk;
+      if (r < nt) {
+        const int tok = t0 + r;
+        const long long blk = block_table[static_cast<long long>(b) * max_blocks + tok / block_size];
+        const long long slot = blk * block_size + tok % block_size;
+        kk = reinterpret_cast<const uint4*>(kc + (slot * Hk + kvh) * D)[c];
+        vv = reinterpret_cast<const uint4*>(vc + (slot * Hk + kvh) * D)[c];
+      }
+      *reinterpret_cast<uint4*>(&sk[r][c * 8]) = kk;
+      *reinterpret_cast<uint4*>(&sv[r][c * 8]) = vv;
+    }
+    __syncthreads();
+    // ---- scores: thread = (slot = tid / 32, token = lane); heads g = slot, slot + 4, ...
+    for (int g = warp; g < G; g += PD_THREADS / 32) {
+      float acc = 0.f;
+#pragma unroll
+      for (int d8 = 0; d8 < D / 8; ++d8) {
+        const uint4 kk = *reinterpret_cast<const uint4*>(&sk[lane][d8 * 8]);
+        const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kk);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 kf = __bfloat1622float2(k2[j]);
+          acc += kf.x * sq[g][d8 * 8 + 2 * j] + kf.y * sq[g][d8 * 8 + 2 * j + 1];
+        }
+      }
+      const float s = lane < nt ? acc : -FLT_MAX;
+      float mx = s;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffff, mx, off));
+      const float m_old = s_m[g];
+      const float m_new = fmaxf(m_old, mx);
+      const float p = lane < nt ? __expf(s - m_new) : 0.f;
+      float ps = p;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) ps += __shfl_xor_sync(0xffffffff, ps, off);
+      sp[g][lane] = p;
+      if (lane == 0) {
+        const float sc = __expf(m_old - m_new);
+        s_scale[g] = sc;
+        s_l[g] = s_l[g] * sc + ps;
+        s_m[g] = m_new;
+      }
+    }
+    __syncthreads();
+    // ---- O += P V : thread owns output dim d = tid
+    if (tid < D) {
+#pragma unroll
+      for (int g = 0; g < PD_MAX_GROUP; ++g) {
+        if (g < G) {
+          float a = o[g] * s_scale[g];
+          for (int r = 0; r < nt; ++r) a += sp[g][r] * __bfloat162float(sv[r][tid]);
+          o[g] = a;
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  if (nsplit == 1) {
+    if (tid < D) {
+#pragma unroll
+      for (int g = 0; g < PD_MAX_GROUP; ++g) {
+        if (g < G) {
+          float l = s_l[g];
+          const int h = kvh * G + g;
+          if (sinks) l += __expf(sinks[h] - s_m[g]);
+          out[(static_cast<long long>(b) * Hq + h) * D + tid] = __float2bfloat16(l > 0.f ? o[g] / l : 0.f);
+        }
+      }
+    }
+  } else {
+    // scratch layout: [b, h, split, D + 2]
+#pragma unroll
+    for (int g = 0; g < PD_MAX_GROUP; ++g) {
+      if (g < G) {
+        const int h = kvh * G + g;
+        float* dst = scratch + ((static_cast<long long>(b) * Hq + h) * nsplit + split) * (D + 2);
+        if (tid < D) dst[tid] = o[g];
+        if (tid == 0) { dst[D] = s_m[g]; dst[D + 1] = s_l[g]; }
+      }
+    }
+  }
+}
+
+template <int D>
+__global__ void paged_decode_combine_kernel(const float* __restrict__ scratch, const float* __restrict__ sinks,
+                                            __nv_bfloat16* __restrict__ out, int Hq, int nsplit) {
+  const int b = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+  const float* base = scratch + (static_cast<long long>(b) * Hq + h) * nsplit * (D + 2);
+  float m = -FLT_MAX;
+  for (int s = 0; s < nsplit; ++s) m = fmaxf(m, base[s * (D + 2) + D]);
+  float l = 0.f, acc = 0.f;
+  for (int s = 0; s < nsplit; ++s) {
+    const float ms = base[s * (D + 2) + D];
+    const float w = ms == -FLT_MAX ? 0.f : __expf(ms - m);
+    l += base[s * (D + 2) + D + 1] * w;
+    acc += base[s * (D + 2) + d] * w;
+  }
+  if (sinks) l += __expf(sinks[h] - m);
+  out[(static_cast<long long>(b) * Hq + h) * D + d] = __float2bfloat16(l > 0.f ? acc / l : 0.f);
+}
+
+}  // namespace gk
+
+using namespace gk;
+
+GK_EXPORT int gk_kv_append_rope(void* qkv, const int* pos, const int* slots, void* kc, void* vc, int T, int Hq,
+                                int Hk, int D, int rot, int do_rope, float theta, int reserved, void* stream) {
+  (void)reserved;
+  if (T == 0) return 0;
+  if ((Hk * D) % 8) return -1;
+  kv_append_rope_kernel<<<T, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<__nv_bfloat16*>(qkv), pos, slots, reinterpret_cast<__nv_bfloat16*>(kc),
+      reinterpret_cast<__nv_bfloat16*>(vc), T, Hq, Hk, D, rot, theta, do_rope);
+  return launch_status();
+}
+
+GK_EXPORT void gk_paged_decode_scratch(int B, int Hq, int D, int max_ctx, long long* floats) {
+  const long long ns = (max_ctx + PD_SPLIT - 1) / PD_SPLIT;
+  *floats = static_cast<long long>(B) * Hq * ns * (D + 2);
+}
+
+// max_ctx bounds every ctx_len[b] (after windowing); it fixes the number of KV splits so the launch shape does
+// not depend on device data (CUDA-graph friendly).
+GK_EXPORT int gk_paged_decode(const void* q, const void* kc, const void* vc, const int* block_table,
+                              const int* ctx_len, const float* sinks, void* out, float* scratch, int B, int Hq,
+                              int Hk, int D, int block_size, int max_blocks, int max_ctx, float scale, int window,
+                              int q_stride, void* stream) {
+  if (D != 128 || Hq % Hk || Hq / Hk > PD_MAX_GROUP) return -1;
+  if (B == 0) return 0;
+  int span = max_ctx;
+  if (window > 0 && window < span) span = window;
+  const int nsplit = (span + PD_SPLIT - 1) / PD_SPLIT > 0 ? (span + PD_SPLIT - 1) / PD_SPLIT : 1;
+  if (nsplit > 1 && !scratch) return -2;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  dim3 grid(B, Hk, nsplit);
+  paged_decode_kernel<128><<<grid, PD_THREADS, 0, st>>>(
+      reinterpret_cast<const __nv_bfloat16*>(q), q_stride, reinterpret_cast<const __nv_bfloat16*>(kc),
+      reinterpret_cast<const __nv_bfloat16*>(vc), block_table, max_blocks, ctx_len, sinks,
+      reinterpret_cast<__nv_bfloat16*>(out), scratch, Hq, Hk, block_size, window, scale, nsplit);
+  if (nsplit > 1) {
+    paged_decode_combine_kernel<128><<<dim3(B, Hq), 128, 0, st>>>(scratch, sinks,
+                                                                  reinterpret_cast<__nv_bfloat16*>(out), Hq, nsplit);
+  }
+  return launch_status();
+}

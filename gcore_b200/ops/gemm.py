@@ -1,0 +1,239 @@
+"""bf16 GEMM front-end for the tcgen05 kernel (``csrc/gemm_tcgen05.cu``) and the autograd ``linear`` built on it.
+
+Layout vocabulary: the kernel computes ``C[M,N] = sum_k A[m,k] * B[n,k]``.  An operand is *K-major* when the
+contraction index is its contiguous (last) dimension and *MN-major* when it is its first dimension.  A linear
+layer ``y = x W^T`` therefore uses (K,K) in forward, (K,MN) for dgrad ``dy W`` and (MN,MN) for wgrad ``dy^T x``;
+no operand is ever transposed in memory.
+
+On CPU tensors, or with ``GCORE_B200_FORCE_EAGER=1``, the same functions run plain PyTorch matmuls: that path is
+the numerical oracle of the tests and the ``nccl_eager`` baseline backend.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+_SCRATCH: dict = {}
+LAUNCHES = {"gemm": 0}
+
+
+def _scratch(device, ws_floats: int, counters: int):
+    key = (device.index,)
+    ws, cnt = _SCRATCH.get(key, (None, None))
+    if ws is None or ws.numel() < ws_floats:
+        ws = torch.empty(max(ws_floats, 1 << 20), dtype=torch.float32, device=device)
+    if cnt is None or cnt.numel() < counters:
+        cnt = torch.zeros(max(counters, 4096), dtype=torch.int32, device=device)
+    _SCRATCH[key] = (ws, cnt)
+    return ws, cnt
+
+
+def _pick_bn(n: int) -> int:
+    if n >= 192:
+        return 256
+    if n > 64:
+        return 128
+    if n > 32:
+        return 64
+    return 32
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: torch.Tensor | None = None,
+         out_dtype: torch.dtype = torch.bfloat16, bias: torch.Tensor | None = None, bias_along_m: bool = False,
+         alpha: float = 1.0, accumulate: bool = False, transposed: bool = False, bn: int | None = None,
+         ksplit: int = 1) -> torch.Tensor:
+    """``C = alpha * A @ B^T (+ bias) (+ C)``; see the module docstring for the layout flags.
+
+    ``a`` is ``[M,K]`` (K-major) or ``[K,M]`` (``a_mn``); ``b`` is ``[N,K]`` or ``[K,N]`` (``b_mn``).  With
+    ``transposed`` the result is written as ``C^T`` (shape ``[N,M]``).
+    """
+    if a_mn:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    assert K == Kb, f"contraction mismatch {K} vs {Kb}"
+    if out is None:
+        assert not accumulate
+        out = torch.empty((N, M) if transposed else (M, N), dtype=out_dtype, device=a.device)
+    if not _lib.use_native(a):
+        af = (a.t() if a_mn else a).float()
+        bf = (b.t() if b_mn else b).float()
+        c = alpha * (af @ bf.t())
+        if bias is not None:
+            c = c + (bias.float()[:, None] if bias_along_m else bias.float()[None, :])
+        if transposed:
+            c = c.t()
+        if accumulate:
+            out.add_(c.to(out.dtype))
+        else:
+            out.copy_(c.to(out.dtype))
+        return out
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "native GEMM operands are bf16"
+    assert a.stride(-1) == 1 and b.stride(-1) == 1 and out.stride(-1) == 1
+    if K == 0:
+        if not accumulate:
+            out.zero_()
+        return out
+    if bn is None:
+        bn = _pick_bn(N)
+    if b_mn and bn < 64:
+        bn = 64
+    lib = _lib.kernels()
+    ws = cnt = None
+    if ksplit > 1:
+        wsf, cn = ctypes.c_longlong(), ctypes.c_longlong()
+        lib.gk_gemm_splitk_scratch(M, N, bn, ksplit, ctypes.byref(wsf), ctypes.byref(cn))
+        ws, cnt = _scratch(a.device, wsf.value, cn.value)
+    LAUNCHES["gemm"] += 1
+    rc = lib.gk_gemm_bf16(
+        _lib.ptr(a), a.stride(0), a.shape[0], int(a_mn), _lib.ptr(b), b.stride(0), b.shape[0], int(b_mn),
+        _lib.ptr(out), out.stride(0), int(out.dtype == torch.float32), int(transposed), int(accumulate),
+        _lib.ptr(bias), int(bias is not None and bias.dtype == torch.float32), int(bias_along_m), float(alpha),
+        M, N, K, bn, ksplit, 0, 0, None, 0, 0, 0, _lib.ptr(ws), _lib.ptr(cnt), _lib.ptr(_lib.err_flag(a.device)),
+        _lib.stream_ptr())
+    _lib.check(rc, "gk_gemm_bf16")
+    return out
+
+
+def grouped_gemm(a: torch.Tensor, b: torch.Tensor, offsets: torch.Tensor, *, b_mn: bool = False,
+                 out: torch.Tensor | None = None, out_dtype=torch.bfloat16, max_rows: int | None = None):
+    """Ragged-M grouped GEMM: rows ``offsets[g]:offsets[g+1]`` of ``a`` ([Mtot,K]) use weight ``b[g]``.
+
+    ``b`` is ``[G,N,K]`` (``b_mn=False``: ``y = x W_g^T``) or ``[G,K,N]`` (``b_mn=True``: ``y = x W_g``).
+    ``offsets`` (int32, on device) must be multiples of 128; rows between a segment's real end and its padded
+    end must be zero.  Mirrors the grouped expert GEMM the reference reaches through TransformerEngine
+    (gpatch_v4/models/deepseek_v4/fp8.py:181-394) without the 128-row buffer copies.
+    """
+    G = b.shape[0]
+    Mtot, K = a.shape
+    N = b.shape[2] if b_mn else b.shape[1]
+    if out is None:
+        out = torch.empty((Mtot, N), dtype=out_dtype, device=a.device)
+    if not _lib.use_native(a):
+        off = offsets.tolist()
+        out.zero_()
+        for g in range(G):
+            s, e = off[g], off[g + 1]
+            if e > s:
+                w = b[g].float()
+                out[s:e] = (a[s:e].float() @ (w if b_mn else w.t())).to(out.dtype)
+        return out
+    b2 = b.reshape(-1, b.shape[-1])
+    bn = _pick_bn(N)
+    if b_mn and bn < 64:
+        bn = 64
+    hint = (max_rows if max_rows is not None else Mtot) // 128 + 1
+    LAUNCHES["gemm"] += 1
+    rc = _lib.kernels().gk_gemm_bf16(
+        _lib.ptr(a), a.stride(0), Mtot, 0, _lib.ptr(b2), b2.stride(0), b2.shape[0], int(b_mn), _lib.ptr(out),
+        out.stride(0), int(out.dtype == torch.float32), 0, 0, None, 0, 0, 1.0, Mtot, N, K, bn, 1, 1, G,
+        _lib.ptr(offsets), b.shape[1], 0, hint, None, None, _lib.ptr(_lib.err_flag(a.device)), _lib.stream_ptr())
+    _lib.check(rc, "gk_gemm_bf16[grouped]")
+    return out
+
+
+def grouped_wgrad(dy: torch.Tensor, x: torch.Tensor, offsets: torch.Tensor, num_groups: int, *,
+                  out: torch.Tensor | None = None, accumulate: bool = False, out_dtype=torch.float32):
+    """Ragged-K grouped GEMM: ``dW[g] = dy[seg_g]^T @ x[seg_g]`` -> ``[G, N, K]``."""
+    Mtot, N = dy.shape
+    K = x.shape[1]
+    if out is None:
+        out = torch.empty((num_groups, N, K), dtype=out_dtype, device=dy.device)
+        accumulate = False
+    if not _lib.use_native(dy):
+        off = offsets.tolist()
+        for g in range(num_groups):
+            s, e = off[g], off[g + 1]
+            r = (dy[s:e].float().t() @ x[s:e].float()).to(out.dtype)
+            if accumulate:
+                out[g] += r
+            else:
+                out[g] = r
+        return out
+    bn = max(_pick_bn(K), 64)
+    LAUNCHES["gemm"] += 1
+    rc = _lib.kernels().gk_gemm_bf16(
+        _lib.ptr(dy), dy.stride(0), Mtot, 1, _lib.ptr(x), x.stride(0), Mtot, 1, _lib.ptr(out), out.stride(1),
+        int(out.dtype == torch.float32), 0, int(accumulate), None, 0, 0, 1.0, N, K, Mtot, bn, 1, 2, num_groups,
+        _lib.ptr(offsets), 0, out.stride(0), 0, None, None, _lib.ptr(_lib.err_flag(dy.device)), _lib.stream_ptr())
+    _lib.check(rc, "gk_gemm_bf16[wgrad-grouped]")
+    return out
+
+
+# ----------------------------------------------------------------------------------------------------------
+def linear_forward(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
+                   out: torch.Tensor | None = None, out_dtype=torch.bfloat16) -> torch.Tensor:
+    """``y[T,N] = x[T,K] @ w[N,K]^T + bias``.  Few tokens (decode) run swap-AB + split-K so the weight streams
+    from HBM exactly once with every SM busy."""
+    T, K = x.shape
+    N = w.shape[0]
+    if _lib.use_native(x) and T <= 128 and N >= 256:
+        bn = 32 if T <= 32 else (64 if T <= 64 else 128)
+        tiles = (N + 127) // 128
+        kb = (K + 63) // 64
+        ksplit = max(1, min(148 // tiles, kb // 4, 16)) if tiles < 120 else 1
+        return gemm(w, x, out=out, out_dtype=out_dtype, bias=bias, bias_along_m=True, transposed=True, bn=bn,
+                    ksplit=ksplit)
+    return gemm(x, w, out=out, out_dtype=out_dtype, bias=bias)
+
+
+def linear_dgrad(dy: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
+                 accumulate: bool = False) -> torch.Tensor:
+    """``dx[T,K] = dy[T,N] @ w[N,K]``."""
+    return gemm(dy, w, b_mn=True, out=out, accumulate=accumulate)
+
+
+def linear_wgrad(dy: torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool = False,
+                 out_dtype=torch.float32) -> torch.Tensor:
+    """``dw[N,K] = dy[T,N]^T @ x[T,K]`` (fp32 by default so micro-batches accumulate into the main grad)."""
+    return gemm(dy, x, a_mn=True, b_mn=True, out=out, out_dtype=out_dtype, accumulate=accumulate)
+
+
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias, main_grad):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1])
+        ctx.save_for_backward(x2, w)
+        ctx.has_bias = bias is not None
+        ctx.main_grad = main_grad
+        ctx.in_shape = shp
+        y = linear_forward(x2, w, bias)
+        return y.reshape(*shp[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = linear_dgrad(dy2, w).reshape(ctx.in_shape)
+        if ctx.needs_input_grad[1]:
+            mg = ctx.main_grad
+            if mg is not None:
+                # accumulate straight into the fp32 main-grad buffer (Megatron "gradient accumulation fusion")
+                linear_wgrad(dy2, x2, out=mg, accumulate=True)
+                dw = None
+            else:
+                dw = linear_wgrad(dy2, x2, out_dtype=torch.float32).to(w.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(dy.dtype)
+        return dx, dw, db, None
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
+           main_grad: torch.Tensor | None = None) -> torch.Tensor:
+    """Autograd linear layer on the tcgen05 GEMM.  When ``main_grad`` (fp32, same shape as ``w``) is given the
+    weight gradient is accumulated into it inside the GEMM epilogue and autograd sees no ``w.grad``."""
+    if x.dtype != torch.bfloat16 or not _lib.use_native(x):
+        return torch.nn.functional.linear(x, w, bias)
+    return _LinearFn.apply(x, w, bias, main_grad)

@@ -1,0 +1,331 @@
+"""GPU numerics of every hand-written kernel against a plain PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _rand(*shape, scale=1.0, dtype=torch.bfloat16):
+    return (torch.randn(*shape, device=DEV, dtype=torch.float32) * scale).to(dtype)
+
+
+def _close(a, b, rtol=2e-2, atol=2e-2):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    ref = b.abs().max().item()
+    assert err <= atol + rtol * ref, f"max err {err} vs ref magnitude {ref}"
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 512), (300, 200, 136), (1000, 3584, 1024), (64, 96, 64)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+def test_gemm_layouts(M, N, K, a_mn, b_mn):
+    from gcore_b200.ops.gemm import gemm
+    if (a_mn and M % 8) or (b_mn and N % 8):
+        pytest.skip("MN-major operands need a 16-byte aligned leading dimension")
+    torch.manual_seed(0)
+    A = _rand(M, K, scale=0.5)
+    B = _rand(N, K, scale=0.5)
+    a = A.t().contiguous() if a_mn else A
+    b = B.t().contiguous() if b_mn else B
+    ref = A.float() @ B.float().t()
+    out = gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    _close(out, ref, rtol=1e-2, atol=1e-2 * math.sqrt(K))
+    out32 = gemm(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+    _close(out32, ref, rtol=2e-3, atol=2e-3 * math.sqrt(K))
+
+
+@pytest.mark.parametrize("bn", [32, 64, 128, 256])
+def test_gemm_tile_widths_bias_accumulate(bn):
+    from gcore_b200.ops.gemm import gemm
+    torch.manual_seed(1)
+    M, N, K = 384, 520, 320
+    A, B = _rand(M, K, scale=0.5), _rand(N, K, scale=0.5)
+    bias = _rand(N)
+    C0 = torch.randn(M, N, device=DEV, dtype=torch.float32)
+    out = C0.clone()
+    gemm(A, B, out=out, bias=bias, alpha=0.5, accumulate=True, bn=bn)
+    ref = C0 + 0.5 * (A.float() @ B.float().t()) + bias.float()[None]
+    _close(out, ref, rtol=2e-3, atol=2e-2)
+
+
+@pytest.mark.parametrize("T", [1, 5, 32, 64, 100, 128])
+def test_gemm_decode_swap_ab_splitk(T):
+    from gcore_b200.ops.gemm import linear_forward
+    torch.manual_seed(2)
+    K, N = 3584, 4608
+    x, w, bias = _rand(T, K, scale=0.3), _rand(N, K, scale=0.05), _rand(N)
+    ref = x.float() @ w.float().t() + bias.float()[None]
+    y = linear_forward(x, w, bias)
+    assert y.shape == (T, N)
+    _close(y, ref, rtol=1e-2, atol=3e-2)
+    y2 = linear_forward(x, w, bias)  # counters must have been reset by the first call
+    assert torch.equal(y, y2)
+
+
+def test_gemm_grouped_ragged():
+    from gcore_b200.ops.gemm import grouped_gemm, grouped_wgrad
+    torch.manual_seed(3)
+    G, K, N = 5, 256, 384
+    real = [100, 0, 257, 128, 31]
+    padded = [((r + 127) // 128) * 128 for r in real]
+    offs = [0]
+    for p in padded:
+        offs.append(offs[-1] + p)
+    Mtot = offs[-1]
+    x = torch.zeros(Mtot, K, device=DEV, dtype=torch.bfloat16)
+    for g in range(G):
+        x[offs[g]:offs[g] + real[g]] = _rand(real[g], K, scale=0.5)
+    w = _rand(G, N, K, scale=0.1)
+    offsets = torch.tensor(offs, device=DEV, dtype=torch.int32)
+    y = grouped_gemm(x, w, offsets)
+    for g in range(G):
+        s, e = offs[g], offs[g] + real[g]
+        _close(y[s:e], x[s:e].float() @ w[g].float().t(), rtol=1e-2, atol=5e-2)
+    # dgrad layout: weights given as [G, K_contract, N_out]
+    wt = w.transpose(1, 2).contiguous()  # [G, K, N]: y = x @ wt[g]
+    y2 = grouped_gemm(x, wt, offsets, b_mn=True)
+    _close(y2, y, rtol=1e-2, atol=5e-2)
+    dy = torch.zeros(Mtot, N, device=DEV, dtype=torch.bfloat16)
+    for g in range(G):
+        dy[offs[g]:offs[g] + real[g]] = _rand(real[g], N, scale=0.5)
+    dw = grouped_wgrad(dy, x, offsets, G)
+    for g in range(G):
+        s, e = offs[g], offs[g + 1]
+        _close(dw[g], dy[s:e].float().t() @ x[s:e].float(), rtol=5e-3, atol=5e-2)
+
+
+def test_linear_autograd_matches_torch():
+    from gcore_b200.ops.gemm import linear
+    torch.manual_seed(4)
+    x = _rand(200, 512, scale=0.5).requires_grad_(True)
+    w = _rand(768, 512, scale=0.05).requires_grad_(True)
+    b = _rand(768).requires_grad_(True)
+    y = linear(x, w, b)
+    g = _rand(200, 768)
+    y.backward(g)
+    xr, wr, br = [t.detach().float().requires_grad_(True) for t in (x, w, b)]
+    yr = torch.nn.functional.linear(xr, wr, br)
+    yr.backward(g.float())
+    _close(y, yr, atol=5e-2)
+    _close(x.grad, xr.grad, atol=5e-2)
+    _close(w.grad, wr.grad, atol=1e-1)
+    _close(b.grad, br.grad, atol=1e-1)
+
+
+@pytest.mark.parametrize("T,H", [(7, 256), (513, 3584), (64, 8192)])
+def test_rmsnorm_fwd_bwd(T, H):
+    from gcore_b200.ops.fused import rmsnorm, rmsnorm_ref
+    torch.manual_seed(5)
+    x, r, w = _rand(T, H), _rand(T, H), (1 + 0.1 * torch.randn(H, device=DEV)).bfloat16()
+    for res in (None, r):
+        xi = x.clone().requires_grad_(True)
+        ri = res.clone().requires_grad_(True) if res is not None else None
+        wi = w.clone().requires_grad_(True)
+        y, s = rmsnorm(xi, wi, 1e-6, ri)
+        gy, gs = _rand(T, H), _rand(T, H)
+        (y.float() * gy.float()).sum().add((s.float() * gs.float()).sum()).backward()
+        xf = x.float().requires_grad_(True)
+        rf = res.float().requires_grad_(True) if res is not None else None
+        wf = w.float().requires_grad_(True)
+        yr, sr = rmsnorm_ref(xf, wf, 1e-6, rf)
+        (yr * gy.float()).sum().add((sr * gs.float()).sum()).backward()
+        _close(y, yr)
+        _close(s, sr)
+        _close(xi.grad, xf.grad, atol=5e-2)
+        _close(wi.grad, wf.grad, rtol=2e-2, atol=0.5)
+        if res is not None:
+            _close(ri.grad, rf.grad, atol=5e-2)
+
+
+def test_rope_and_swiglu():
+    from gcore_b200.ops.fused import rope, rope_ref, swiglu, swiglu_ref
+    torch.manual_seed(6)
+    T, nh, D = 300, 6, 128
+    x = _rand(T, nh, D).requires_grad_(True)
+    pos = torch.randint(0, 4000, (T,), device=DEV, dtype=torch.int32)
+    y = rope(x, pos, 1e6)
+    g = _rand(T, nh, D)
+    y.backward(g)
+    xf = x.detach().float().requires_grad_(True)
+    yr = rope_ref(xf, pos, 1e6)
+    yr.backward(g.float())
+    _close(y, yr)
+    _close(x.grad, xf.grad)
+    # partial rotary + packed slice
+    buf = _rand(T, 3 * nh * D)
+    view = buf.view(T, 3 * nh, D)[:, :nh]
+    from gcore_b200.ops.fused import rope_inplace
+    ref = rope_ref(view.clone(), pos, 1e4, rot=64)
+    rope_inplace(view, pos, 1e4, rot=64)
+    _close(view, ref)
+    z = _rand(257, 2 * 688).requires_grad_(True)
+    o = swiglu(z)
+    go = _rand(257, 688)
+    o.backward(go)
+    zf = z.detach().float().requires_grad_(True)
+    orf = swiglu_ref(zf)
+    orf.backward(go.float())
+    _close(o, orf)
+    _close(z.grad, zf.grad)
+
+
+def test_linear_logprob_entropy_fwd_bwd():
+    from gcore_b200.ops import vocab
+    torch.manual_seed(7)
+    T, H, V = 300, 256, 5000
+    old = vocab.CHUNK_TOKENS
+    vocab.CHUNK_TOKENS = 128
+    try:
+        h = _rand(T, H, scale=1.0).requires_grad_(True)
+        w = _rand(V, H, scale=0.1).requires_grad_(True)
+        tg = torch.randint(0, V, (T,), device=DEV)
+        lp, en = vocab.linear_logprob_entropy(h, w, tg, temperature=0.7)
+        g1, g2 = torch.randn(T, device=DEV), torch.randn(T, device=DEV)
+        (lp * g1 + en * g2).sum().backward()
+        hf, wf = h.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+        lpr, enr = vocab.logprob_entropy_ref(hf @ wf.t(), tg, 0.7)
+        (lpr * g1 + enr * g2).sum().backward()
+        _close(lp, lpr, atol=5e-2)
+        _close(en, enr, atol=5e-2)
+        _close(h.grad, hf.grad, atol=5e-2)
+        _close(w.grad, wf.grad, atol=5e-2)
+    finally:
+        vocab.CHUNK_TOKENS = old
+
+
+def test_sampling_distribution_and_logprob():
+    from gcore_b200.ops.vocab import sample
+    torch.manual_seed(8)
+    V = 50
+    logits = torch.randn(1, V, device=DEV).repeat(4096, 1).contiguous()
+    seeds = torch.arange(4096, device=DEV, dtype=torch.int64)
+    steps = torch.zeros(4096, device=DEV, dtype=torch.int32)
+    tok, lp = sample(logits, 1.0, seeds, steps)
+    ref_lp = torch.log_softmax(logits[0], -1)
+    assert torch.allclose(lp, ref_lp[tok], atol=1e-4)
+    freq = torch.bincount(tok, minlength=V).float() / 4096
+    assert (freq - ref_lp.exp()).abs().max().item() < 0.03
+    tok2, _ = sample(logits, 1.0, seeds, steps)
+    assert torch.equal(tok, tok2)
+    tokg, _ = sample(logits, 1.0, seeds, steps, greedy=True)
+    assert (tokg == logits[0].argmax()).all()
+
+
+def test_grpo_loss_and_gae():
+    from gcore_b200.ops.rl import gae, grpo_loss, grpo_token_loss_ref
+    torch.manual_seed(9)
+    n = 5000
+    logp = (-torch.rand(n, device=DEV) * 3).requires_grad_(True)
+    old = logp.detach() + 0.3 * torch.randn(n, device=DEV)
+    ref = logp.detach() + 0.2 * torch.randn(n, device=DEV)
+    adv = torch.randn(n, device=DEV)
+    w = (torch.rand(n, device=DEV) > 0.3).float() / n
+    kw = dict(clip_low=0.2, clip_high=0.28, dual_clip_c=3.0, kl_beta=0.01, ratio_clamp=10.0, kl_clamp=5.0)
+    loss, stats = grpo_loss(logp, old, ref, adv, w, **kw)
+    loss.backward()
+    lr = logp.detach().clone().requires_grad_(True)
+    tl, kl, ratio, clipped = grpo_token_loss_ref(lr, old, ref, adv, **kw)
+    (w * tl).sum().backward()
+    assert abs(loss.item() - (w * tl).sum().item()) < 1e-4
+    assert torch.allclose(logp.grad, lr.grad, atol=1e-6)
+    assert abs(stats[3].item() - (w * clipped.float()).sum().item()) < 1e-5
+    B, S = 37, 129
+    r, v = torch.randn(B, S, device=DEV), torch.randn(B, S, device=DEV)
+    mk = (torch.rand(B, S, device=DEV) > 0.2).float()
+    a1, r1 = gae(r, v, mk, 0.99, 0.95)
+    a2, r2 = gae(r.cpu(), v.cpu(), mk.cpu(), 0.99, 0.95)
+    assert torch.allclose(a1.cpu(), a2, atol=1e-4) and torch.allclose(r1.cpu(), r2, atol=1e-4)
+
+
+def test_adam_and_sumsq():
+    from gcore_b200.ops.optim import adam_step, sumsq
+    torch.manual_seed(10)
+    n = 100003
+    master = torch.randn(n, device=DEV)
+    m, v = torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    g = torch.randn(n, device=DEV).bfloat16()
+    p = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    mc, mm, vv = master.cpu().clone(), m.cpu().clone(), v.cpu().clone()
+    scale = torch.tensor([0.5], device=DEV)
+    for step in (1, 2):
+        adam_step(master, m, v, g, p, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step,
+                  grad_scale=scale)
+        adam_step(mc, mm, vv, g.cpu(), None, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step,
+                  grad_scale=scale.cpu())
+    assert torch.allclose(master.cpu(), mc, atol=1e-5)
+    assert torch.allclose(p.float().cpu(), mc.bfloat16().float(), atol=1e-2)
+    s = sumsq(g)
+    assert abs(s.item() - g.float().pow(2).sum().item()) / s.item() < 1e-3
+
+
+@pytest.mark.parametrize("window,use_sinks", [(0, False), (96, True)])
+def test_paged_decode_and_kv_append(window, use_sinks):
+    from gcore_b200.ops.attention import kv_append_rope, paged_decode
+    torch.manual_seed(11)
+    B, Hq, Hk, D, bs = 5, 28, 4, 128, 16
+    lens = [1, 17, 300, 513, 64]
+    max_blocks = 40
+    nblocks = 256
+    kc = torch.zeros(nblocks, bs, Hk, D, device=DEV, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    perm = torch.randperm(nblocks, device=DEV)[:B * max_blocks].view(B, max_blocks).to(torch.int32)
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    # fill the caches through the append kernel, token by token batches
+    T = sum(lens)
+    qkv = _rand(T, (Hq + 2 * Hk) * D, scale=0.5)
+    pos = torch.cat([torch.arange(l) for l in lens]).to(DEV).to(torch.int32)
+    bidx = torch.cat([torch.full((l,), i) for i, l in enumerate(lens)]).to(DEV)
+    slots = (perm[bidx, (pos // bs).long()] * bs + pos % bs).to(torch.int32)
+    qkv_ref = qkv.clone().cpu()
+    kv_append_rope(qkv, pos, slots, kc, vc, Hq, Hk, D, 1e6)
+    kv_append_rope(qkv_ref, pos.cpu(), slots.cpu(), kc_ref := kc_ref.cpu(), vc_ref := vc_ref.cpu(), Hq, Hk, D, 1e6)
+    _close(qkv, qkv_ref.to(DEV))
+    _close(kc, kc_ref.to(DEV))
+    _close(vc, vc_ref.to(DEV))
+    last = torch.tensor([sum(lens[:i + 1]) - 1 for i in range(B)], device=DEV)
+    q = qkv.view(T, Hq + 2 * Hk, D)[last][:, :Hq].contiguous()
+    ctx = torch.tensor(lens, device=DEV, dtype=torch.int32)
+    sinks = torch.randn(Hq, device=DEV) if use_sinks else None
+    out = paged_decode(q, kc, vc, perm, ctx, max(lens), window=window, sinks=sinks)
+    ref = paged_decode(q.cpu(), kc.cpu(), vc.cpu(), perm.cpu(), ctx.cpu(), max(lens), window=window,
+                       sinks=sinks.cpu() if use_sinks else None)
+    _close(out, ref.to(DEV), atol=2e-2)
+
+
+@pytest.mark.parametrize("D", [128, 64])
+@pytest.mark.parametrize("causal,window,use_sinks", [(True, 0, False), (True, 128, True), (False, 0, False),
+                                                     (True, 256, False)])
+def test_flash_attn_fwd_varlen(D, causal, window, use_sinks):
+    from gcore_b200.ops.attention import attn_varlen_ref, flash_attn_varlen
+    torch.manual_seed(12)
+    Hq, Hk = 8, 2
+    lens = [33, 1023, 3, 128, 129, 255]
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device=DEV, dtype=torch.int32)
+    T = sum(lens)
+    q, k, v = _rand(T, Hq, D), _rand(T, Hk, D), _rand(T, Hk, D)
+    sinks = torch.randn(Hq, device=DEV) if use_sinks else None
+    with torch.no_grad():
+        out = flash_attn_varlen(q, k, v, cu, cu, max(lens), max(lens), causal=causal, window=window, sinks=sinks)
+        ref = attn_varlen_ref(q, k, v, cu, cu, causal, window, sinks)
+    _close(out, ref, atol=3e-2)
+
+
+def test_flash_attn_prefix_k_and_packed_qkv():
+    from gcore_b200.ops.attention import attn_varlen_ref, flash_attn_varlen
+    torch.manual_seed(13)
+    Hq, Hk, D = 4, 4, 128
+    lq, lk = [5, 130], [200, 641]
+    cu_q = torch.tensor([0, 5, 135], device=DEV, dtype=torch.int32)
+    cu_k = torch.tensor([0, 200, 841], device=DEV, dtype=torch.int32)
+    q = _rand(sum(lq), Hq, D)
+    kv = _rand(sum(lk), 2 * Hk * D)
+    k = kv.view(-1, 2 * Hk, D)[:, :Hk]
+    v = kv.view(-1, 2 * Hk, D)[:, Hk:]
+    with torch.no_grad():
+        out = flash_attn_varlen(q, k, v, cu_q, cu_k, max(lq), max(lk), causal=True)
+        ref = attn_varlen_ref(q, k, v, cu_q, cu_k, True)
+    _close(out, ref, atol=3e-2)

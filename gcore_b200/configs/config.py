@@ -1,0 +1,602 @@
+"""Config dataclasses.  Section and field names follow the reference's YAML surface
+(gpatch_v4/configs/config.py:113-772, training_config.py, ppo_config.py, policy_config.py, dist_config.py,
+infer_engine_config.py, checkpoint_config.py, optimizer_config.py, lora_config.py) so its recipes carry over;
+cross-field validation lives in ``__post_init__``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional
+
+from .base import ConfigError, MappingMixin
+
+
+# ------------------------------------------------------------------------------------------------ leaves
+@dataclass
+class DistConfig(MappingMixin):
+    num_gpus_per_node: int = 8
+    nnodes: int = -1
+    num_cpu_nodes: int = 0
+    torch_dist_timeout_minutes: int = 30
+    use_tp_pp_dp_mapping: bool = False
+    expert_model_parallel_size: int = 1
+    expert_tensor_parallel_size: int = 1
+    context_parallel_size: int = 1
+    dynamic_context_parallel: bool = False
+    max_seqlen_per_dp_cp_rank: Optional[int] = None
+    max_seqlen_per_dp_cp_rank_fwd_only: Optional[int] = None
+    min_dynamic_context_parallel_size: int = 1
+    dynamic_cp_scheduler_type: str = "default"
+    tensor_model_parallel_size: int = 1
+    pipeline_model_parallel_size: int = 1
+    num_layers_in_first_pipeline_stage: Optional[int] = None
+    num_layers_in_last_pipeline_stage: Optional[int] = None
+    virtual_pipeline_model_parallel_size: Optional[int] = None
+    sequence_parallel: bool = True
+    custom_device_mesh: Optional[Dict[str, Any]] = None
+    fsdp2_forward_prefetch: int = 1
+    fsdp2_backward_prefetch: int = 1
+
+    def __post_init__(self):
+        for n in ("tensor_model_parallel_size", "pipeline_model_parallel_size", "context_parallel_size",
+                  "expert_model_parallel_size", "expert_tensor_parallel_size"):
+            if getattr(self, n) < 1:
+                raise ConfigError(f"dist_config.{n} must be >= 1")
+        if self.tensor_model_parallel_size == 1:
+            self.sequence_parallel = False
+        if self.dynamic_context_parallel and self.max_seqlen_per_dp_cp_rank is None:
+            raise ConfigError("dynamic_context_parallel needs max_seqlen_per_dp_cp_rank")
+
+    @property
+    def model_parallel_size(self):
+        return (self.tensor_model_parallel_size * self.pipeline_model_parallel_size * self.context_parallel_size)
+
+
+@dataclass
+class LoRAConfig(MappingMixin):
+    rank: int = 0
+    alpha: float = 32
+    type: str = "canonical_lora"
+    dropout: float = 0.0
+    target_modules: List[str] = field(default_factory=lambda: ["linear_qkv", "linear_proj", "linear_fc1",
+                                                               "linear_fc2"])
+    exclude_modules: List[str] = field(default_factory=list)
+    lora_A_init_method: str = "xavier"
+    lora_B_init_method: str = "zero"
+    dtype: Optional[str] = None
+    check_lora_all_coverage: bool = False
+    verify_weight_consistency: bool = True
+    share_expert_adapters: bool = True
+
+    def __post_init__(self):
+        if self.type not in ("lora", "canonical_lora"):
+            raise ConfigError(f"lora.type must be lora|canonical_lora, got {self.type}")
+
+    @property
+    def enabled(self):
+        return self.rank > 0
+
+
+@dataclass
+class ClientConfig(MappingMixin):
+    rpc_type: str = "local"
+    rpc_timeout: int = 60
+    update_weight_max_size_mb: int = 512
+    update_weight_use_bucketed_ipc: bool = True
+    split_generate_repeat_n: bool = False
+
+
+@dataclass
+class OptimizerConfig(MappingMixin):
+    lr: float = 1e-5
+    min_lr: float = 0.0
+    lr_warmup_steps: int = 0
+    lr_warmup_step_frac: Optional[float] = None
+    lr_warmup_init: float = 0.0
+    lr_decay_steps: Optional[int] = None
+    lr_decay_style: str = "linear"
+    lr_wsd_decay_steps: Optional[int] = None
+    lr_wsd_decay_style: str = "exponential"
+    weight_decay: float = 0.01
+    optimizer_type: str = "adam"
+    adam_beta1: float = 0.9
+    adam_beta2: float = 0.999
+    adam_eps: float = 1e-8
+    max_grad_norm: float = 1.0
+    use_distributed_optimizer: bool = True
+    grad_reduce_in_fp32: bool = True
+    overlap_grad_reduce: bool = False
+    overlap_param_gather: bool = False
+    bucket_size: Optional[int] = None
+    override_optimizer_config: Dict[str, Any] = field(default_factory=dict)
+    muon_momentum: float = 0.95
+    muon_ns_steps: int = 5
+    muon_scale_mode: str = "spectral"
+    per_module_lr: Dict[str, float] = field(default_factory=dict)
+
+    def __post_init__(self):
+        if self.lr_decay_style not in ("constant", "linear", "cosine", "inverse-square-root", "WSD"):
+            raise ConfigError(f"unknown lr_decay_style {self.lr_decay_style}")
+        if self.optimizer_type not in ("adam", "sgd", "muon"):
+            raise ConfigError(f"unknown optimizer_type {self.optimizer_type}")
+
+
+@dataclass
+class CheckpointConfig(MappingMixin):
+    load_ckpt_path: Optional[str] = None
+    save_ckpt_path: Optional[str] = None
+    no_load_optim: bool = False
+    no_save_optim: bool = False
+    no_load_rng: bool = False
+    ref_load_ckpt_path: Optional[str] = None
+    save_total_limit: Optional[int] = None
+    save_retain_interval: Optional[int] = None
+    use_dist_checkpointing: bool = True
+    async_save: bool = False
+    convert_mcore_to_hf_online: bool = False
+    convert_mcore_to_hf_offline: bool = False
+    export_hf_save_path: Optional[str] = None
+    strict_export: bool = True
+    skip_save_mcore_model: bool = False
+    save_merged_lora_weights: bool = True
+
+
+@dataclass
+class ProfileConfig(MappingMixin):
+    enable: bool = False
+    profile_start_step: int = 2
+    profile_end_step: int = 3
+    export_dir: Optional[str] = None
+    export_ranks: List[int] = field(default_factory=lambda: [0])
+    gzip: bool = False
+    with_stack: bool = False
+    record_shapes: bool = False
+    profile_memory: bool = False
+    use_nsys: bool = False
+    comm_summary: bool = True
+
+    def __post_init__(self):
+        if self.enable and self.profile_end_step < self.profile_start_step:
+            raise ConfigError("profile_end_step must be >= profile_start_step")
+
+
+@dataclass
+class ReportConfig(MappingMixin):
+    report_to: List[str] = field(default_factory=list)  # "wandb", "tensorboard", "jsonl"
+    project: str = "gcore_b200"
+    run_name: Optional[str] = None
+    log_dir: str = "./logs"
+    log_interval: int = 1
+    use_verl_metric_names: bool = False
+    profile: ProfileConfig = field(default_factory=ProfileConfig)
+
+
+@dataclass
+class DebugConfig(MappingMixin):
+    debug_update_weight: bool = False
+    replay_rollout_path: Optional[str] = None
+    dump_rollout_path: Optional[str] = None
+    check_rollout_batches: bool = True
+    check_a2a_legality: bool = False
+    trace_python_calls: bool = False
+    trace_roots: List[str] = field(default_factory=list)
+    ppo_padding_check: bool = False
+    fault_injection: Dict[str, Any] = field(default_factory=dict)  # host-side only: {"raise_at_step": n, ...}
+
+
+@dataclass
+class DataConfig(MappingMixin):
+    py_path: Optional[str] = None
+    fn_name: Optional[str] = None
+    train_data_path: Optional[str] = None
+    eval_data_path: Optional[str] = None
+    prompt_key: str = "prompt"
+    label_key: str = "answer"
+    max_prompt_length: int = 1024
+    num_workers: int = 0
+    shuffle: bool = True
+    seed: int = 42
+    synthetic: Dict[str, Any] = field(default_factory=dict)
+    extra: Dict[str, Any] = field(default_factory=dict)
+    _allow_extra = True
+
+
+@dataclass
+class RewardModelInfo(MappingMixin):
+    name: str = "rule"
+    py_path: Optional[str] = None
+    fn_name: Optional[str] = None
+    reward_weight: float = 1.0
+    hf_model_path: Optional[str] = None
+    gen_reward_repeat_n: int = 1
+
+
+@dataclass
+class RewardConfig(MappingMixin):
+    reward_type: str = "rule_only"  # rule_only | rm_only | mix
+    reward_model_info: List[RewardModelInfo] = field(default_factory=list)
+    rule_py_path: Optional[str] = None
+    rule_fn_name: Optional[str] = None
+    external_url: Optional[str] = None
+    external_timeout: int = 600
+    stream: bool = False
+
+    def __post_init__(self):
+        if self.reward_type not in ("rule_only", "rm_only", "mix"):
+            raise ConfigError(f"reward_type must be rule_only|rm_only|mix, got {self.reward_type}")
+
+
+@dataclass
+class InferEngineConfig(MappingMixin):
+    dist_config: DistConfig = field(default_factory=DistConfig)
+    dp_size: int = 1
+    dtype: str = "bfloat16"
+    gpu_memory_utilization: float = 0.7
+    max_running_requests: Optional[int] = None
+    max_model_len: Optional[int] = None
+    kv_block_size: int = 16
+    num_kv_blocks: Optional[int] = None
+    max_prefill_tokens: int = 16384
+    temperature: float = 1.0
+    top_k: int = -1
+    top_p: float = 1.0
+    min_p: float = 0.0
+    generate_max_tokens: int = 128
+    generate_params: Dict[str, Any] = field(default_factory=dict)
+    eval_generate_params: Dict[str, Any] = field(default_factory=dict)
+    seed: int = 42
+    engine_seed: int = 42
+    repetition_penalty: float = 1.0
+    load_format: str = "auto"
+    enable_weights_cpu_backup: bool = False
+    disable_cuda_graph: bool = False
+    attention_backend: str = "native"
+    return_routed_experts: bool = False
+    fp8_weights: bool = False
+    watchdog_timeout: int = 600
+    model_override_args: Dict[str, Any] = field(default_factory=dict)
+    override_infer_engine_config: Dict[str, Any] = field(default_factory=dict)
+
+    def __post_init__(self):
+        if self.dist_config.pipeline_model_parallel_size != 1:
+            raise ConfigError("rollout engines run with pipeline_model_parallel_size == 1")
+        if not 0 < self.gpu_memory_utilization <= 1:
+            raise ConfigError("gpu_memory_utilization must be in (0, 1]")
+
+
+@dataclass
+class ModelInfo(MappingMixin):
+    name: str = "policy"
+    hf_model_path: Optional[str] = None
+    model_arch: Optional[str] = None
+    gen_rollout_py_path: Optional[str] = None
+    gen_rollout_fn_name: Optional[str] = None
+
+
+@dataclass
+class SamplerConfig(MappingMixin):
+    backend: str = "native"
+    model_info: List[ModelInfo] = field(default_factory=lambda: [ModelInfo()])
+    infer_engine_configs: List[InferEngineConfig] = field(default_factory=lambda: [InferEngineConfig()])
+
+    def __post_init__(self):
+        if self.backend not in ("native", "eager", "sglang", "vllm"):
+            raise ConfigError(f"unknown sampler backend {self.backend}")
+        if self.backend in ("sglang", "vllm"):
+            # the external engines of the reference are replaced by the built-in decoder
+            self.backend = "native"
+
+
+@dataclass
+class PolicyConfig(MappingMixin):
+    dist_config: DistConfig = field(default_factory=DistConfig)
+    model_arch: str = "qwen2"
+    model_config: Dict[str, Any] = field(default_factory=dict)  # explicit architecture (random init) or overrides
+    hf_model_path: Optional[str] = None
+    hf_tokenizer_path: Optional[str] = None
+    ref_hf_model_path: Optional[str] = None
+    attn_implementation: str = "native"
+    ep_backend: str = "fused"
+    fp8: bool = False
+    fp8_qat: bool = False
+    fp4_qat: bool = False
+    rollout_gen_type: str = "base"
+    rollout_gen_py_path: Optional[str] = None
+    rollout_gen_cls: Optional[str] = None
+    forward_only_mbs: int = 1
+    dynamic_mbs_target_seqlen: Optional[int] = None
+    dynamic_mbs_limit: Optional[int] = None
+    ppo_pack_seq: bool = True
+    without_ref: bool = False
+    without_optim: bool = False
+    balance_dp_seqlen: bool = False
+    smart_pad_infer: bool = False
+    smart_pad_train: bool = False
+    wrap_with_ddp: bool = True
+    recompute: str = "full"  # none | full (per-layer activation recompute)
+    override_ddp_config: Dict[str, Any] = field(default_factory=dict)
+    override_transformer_config: Dict[str, Any] = field(default_factory=dict)
+    freeze_patterns: List[str] = field(default_factory=list)
+    unfreeze_patterns: List[str] = field(default_factory=list)
+    lora: LoRAConfig = field(default_factory=LoRAConfig)
+    offload_process_group: bool = False
+    manual_clear_memory: bool = False
+    export_weights_buffer_max_size_mb: int = 2048
+    share_rollout_weights: bool = True  # colocated trainer and decoder read the same bf16 parameter storage
+    sampler_client: ClientConfig = field(default_factory=ClientConfig)
+    bt_rm_client: ClientConfig = field(default_factory=ClientConfig)
+    gen_rm_client: ClientConfig = field(default_factory=ClientConfig)
+
+
+@dataclass
+class PpoConfig(MappingMixin):
+    advantage_type: str = "grpo"
+    loss_func: str = "grpo"
+    use_legacy_loss: bool = False
+    loss_func_py_path: Optional[str] = None
+    loss_func_fn_name: Optional[str] = None
+    advantage_py_path: Optional[str] = None
+    advantage_fn_name: Optional[str] = None
+    post_advantage_py_path: Optional[str] = None
+    post_advantage_fn_name: Optional[str] = None
+    ppo_initial_policy_kl_penalty: float = 0.0
+    ppo_discount_factor: float = 1.0
+    ppo_gae_lambda: float = 0.95
+    ppo_entropy_bonus: float = 0.0
+    adaptive_entropy: bool = False
+    adaptive_entropy_target: float = 0.0
+    adaptive_entropy_lr: float = 0.0
+    ppo_ratio_eps: float = 0.2
+    ppo_clip_ratio_low: Optional[float] = None
+    ppo_clip_ratio_high: Optional[float] = None
+    ppo_dual_clip_ratio_c: Optional[float] = None
+    grpo_advantage_epsilon: float = 1e-8
+    ppo_logps_ratio_clamp: Optional[float] = None
+    ppo_clamp_kl_val: Optional[float] = None
+    ppo_value_clip: Optional[float] = None
+    advantage_clip: bool = False
+    advantage_clip_low: float = -10.0
+    advantage_clip_high: float = 10.0
+    whiten_advantages: bool = False
+    grpo_kl_loss_beta: float = 1e-3
+    kl_estimator: str = "k3"
+    norm_adv_by_std_in_grpo: bool = True
+    per_token_loss: bool = True
+    # train-vs-rollout mismatch correction (truncate | clip | mask | icepop | kpop | none)
+    offpolicy_correction: str = "none"
+    offpolicy_correction_level: str = "token"  # token | sequence | geometric
+    offpolicy_correction_upper: float = 2.0
+    offpolicy_correction_lower: Optional[float] = None
+    offpolicy_correction_veto: Optional[float] = None
+    critic_model_warmup_steps: int = 0
+    mask_negative_samples: bool = False
+    gdpo_reward_weights: Dict[str, float] = field(default_factory=dict)
+    skip_prev_logps: bool = False
+    use_original_logprob: bool = False
+    feature_store_enable: bool = False
+    cispo_eps_high: float = 5.0
+    cispo_eps_low: float = 1.0
+    sapo_tau_pos: float = 1.0
+    sapo_tau_neg: float = 1.05
+    clip_cov_ratio: float = 0.0
+    kl_cov_ratio: float = 0.0
+    kl_cov_coef: float = 1.0
+
+    def __post_init__(self):
+        if self.advantage_type not in ("grpo", "gdpo", "ppo", "reinforce", "on_policy_distill", "g_opd",
+                                       "identity", "custom"):
+            raise ConfigError(f"unknown advantage_type {self.advantage_type}")
+        if self.loss_func == "gspo" and self.per_token_loss:
+            # sequence-level ratios are aggregated per sequence (gpatch_v4/configs/config.py:273-276)
+            raise ConfigError("loss_func=gspo requires per_token_loss=false")
+        if self.offpolicy_correction not in ("none", "truncate", "clip", "mask", "icepop", "kpop"):
+            raise ConfigError(f"unknown offpolicy_correction {self.offpolicy_correction}")
+
+    @property
+    def clip_low(self):
+        return self.ppo_clip_ratio_low if self.ppo_clip_ratio_low is not None else self.ppo_ratio_eps
+
+    @property
+    def clip_high(self):
+        return self.ppo_clip_ratio_high if self.ppo_clip_ratio_high is not None else self.ppo_ratio_eps
+
+
+@dataclass
+class DynamicSamplingConfig(MappingMixin):
+    enable: bool = False
+    oversampling_ratio: float = 1.2
+    ema_decay: float = 0.9
+    max_refill_times: int = 3
+    filter_py_path: Optional[str] = None
+    filter_fn_name: Optional[str] = None
+    epoch_mode: bool = False
+
+
+@dataclass
+class TrainingConfig(MappingMixin):
+    training_backend: str = "native"  # native (fused sm_100a kernels) | nccl_eager (library baseline)
+    train_gbs: int = 8
+    train_mbs: int = 1
+    gradient_accumulation_steps: Optional[int] = None
+    exit_step: Optional[int] = None
+    seed: int = 42
+    seq_length: int = 2048
+    total_training_step: Optional[int] = None
+    num_train_epoches: int = 1
+    apply_deterministic_mode: bool = False
+    save_interval: int = 100
+    eval_interval: Optional[int] = None
+    pad_to_mulitiple_of: int = 128
+    auto_load_from_save_ckpt: bool = True
+    allow_tf32: bool = True
+    max_train_step_waiting_time: float = 3600.0
+    max_restart_attempts: int = 0
+    node_replacer_cls: Optional[str] = None
+    attention_backend: str = "auto"
+    moe_token_dispatcher_type: str = "alltoall"
+    moe_router_load_balancing_type: str = "none"
+    moe_balance_loss_coef: float = 0.0
+    moe_router_replay: bool = False
+    offload_process_group: bool = False
+    use_dynamic_mbs: bool = False
+    ppo_dump_metrics_interval: Optional[int] = None
+    calc_mfu_freq: int = 1
+    use_linear_ce: bool = True
+    linear_ce_backend: str = "separate"
+    ce_compaction: bool = False
+    loss_func: str = "cross_entropy"
+    cross_entropy_loss_fusion: bool = True
+    per_token_loss: bool = True
+    sort_batched: bool = False
+    manual_gc: bool = False
+    # RL-only
+    total_ppo_step: Optional[int] = None
+    ppo_step_per_epoch: Optional[int] = None
+    dynamic_sampling: DynamicSamplingConfig = field(default_factory=DynamicSamplingConfig)
+    rollout_gbs: int = 8
+    rollout_mbs: int = 1
+    sampling_repeat_n: int = 8
+    sampling_keep_n: Optional[int] = None
+    sampling_keeping_strategy: str = "all"
+    filter_sampling_py_path: Optional[str] = None
+    filter_sampling_fn_name: Optional[str] = None
+    filter_sampling_stage: str = "pre"
+    metrics_report: List[str] = field(default_factory=list)
+    ppo_max_epochs_2: int = 1
+    use_bt_rm_reward: bool = False
+    use_gen_rm_reward: bool = False
+    use_external_reward: bool = False
+    stream_external_reward: bool = False
+    early_swap_model: bool = False
+    async_rollout: bool = False
+    single_controller: bool = False
+    dynamic_batch_train: bool = False
+    rollout_max_staleness: int = 0
+    rollout_over_dispatch_ratio: float = 1.0
+    rollout_reuse_unused_prompts: bool = False
+    num_agent_loop_workers: int = 4
+    load_aware_sampler_routing: bool = False
+    rb_multiplier: int = 1
+    custom_actors: Dict[str, Any] = field(default_factory=dict)
+
+    def __post_init__(self):
+        if self.training_backend in ("mcore", "fsdp2", "mlite"):
+            self.training_backend = "native"
+        if self.training_backend not in ("native", "nccl_eager"):
+            raise ConfigError(f"unknown training_backend {self.training_backend}")
+        if self.sampling_keep_n is None:
+            self.sampling_keep_n = self.sampling_repeat_n
+        if self.sampling_keep_n > self.sampling_repeat_n:
+            raise ConfigError("sampling_keep_n cannot exceed sampling_repeat_n")
+        if self.filter_sampling_stage not in ("pre", "post"):
+            raise ConfigError("filter_sampling_stage must be pre|post")
+        if self.rollout_max_staleness < 0:
+            raise ConfigError("rollout_max_staleness must be >= 0")
+
+
+@dataclass
+class MonitorConfig(MappingMixin):
+    heartbeat_interval: float = 30.0
+    heartbeat_dir: Optional[str] = None
+    enable_training_plt: bool = False
+
+
+@dataclass
+class CriticConfig(PolicyConfig):
+    optimizer: OptimizerConfig = field(default_factory=OptimizerConfig)
+    checkpoint: CheckpointConfig = field(default_factory=CheckpointConfig)
+
+
+# ------------------------------------------------------------------------------------------------ top level
+@dataclass
+class BaseTopConfig(MappingMixin):
+    data: DataConfig = field(default_factory=DataConfig)
+    training: TrainingConfig = field(default_factory=TrainingConfig)
+    policy: PolicyConfig = field(default_factory=PolicyConfig)
+    checkpoint: CheckpointConfig = field(default_factory=CheckpointConfig)
+    optimizer: OptimizerConfig = field(default_factory=OptimizerConfig)
+    report: ReportConfig = field(default_factory=ReportConfig)
+    monitor: MonitorConfig = field(default_factory=MonitorConfig)
+    debug: DebugConfig = field(default_factory=DebugConfig)
+    task: Dict[str, Any] = field(default_factory=dict)
+
+    def world_size_required(self) -> int:
+        d = self.policy.dist_config
+        return d.tensor_model_parallel_size * d.pipeline_model_parallel_size * d.context_parallel_size
+
+
+@dataclass
+class FinetuneConfig(BaseTopConfig):
+    def __post_init__(self):
+        d = self.policy.dist_config
+        if d.dynamic_context_parallel and not self.training.per_token_loss:
+            # per-sequence means cannot be rebuilt after per-sequence CP re-sharding
+            raise ConfigError("dynamic context parallel requires training.per_token_loss=true")
+
+
+@dataclass
+class PretrainConfig(FinetuneConfig):
+    pass
+
+
+@dataclass
+class RlConfig(BaseTopConfig):
+    placement_type: str = "colocate"
+    critic: Optional[CriticConfig] = None
+    sampler: SamplerConfig = field(default_factory=SamplerConfig)
+    gen_rm: Optional[SamplerConfig] = None
+    bt_rm: RewardConfig = field(default_factory=RewardConfig)
+    external_reward: Optional[RewardConfig] = None
+    ppo: PpoConfig = field(default_factory=PpoConfig)
+
+    def __post_init__(self):
+        if self.placement_type not in ("colocate", "disaggregated", "partial_colocated"):
+            raise ConfigError(f"unknown placement_type {self.placement_type}")
+        t = self.training
+        if (t.rollout_gbs * t.sampling_keep_n) % max(t.train_gbs, 1) and t.train_gbs > 0:
+            raise ConfigError("rollout_gbs * sampling_keep_n must be a multiple of train_gbs")
+        if self.ppo.advantage_type == "ppo" and self.critic is None:
+            raise ConfigError("advantage_type=ppo needs a `critic:` section")
+        if t.rollout_max_staleness > 0 and not (t.async_rollout or t.single_controller):
+            raise ConfigError("rollout_max_staleness > 0 needs async_rollout or single_controller")
+        if t.use_gen_rm_reward and self.gen_rm is None:
+            raise ConfigError("use_gen_rm_reward needs a `gen_rm:` section")
+        if self.policy.dist_config.dynamic_context_parallel and not self.ppo.per_token_loss:
+            raise ConfigError("dynamic context parallel requires ppo.per_token_loss=true")
+
+    def require_critic_model(self) -> bool:
+        return self.ppo.advantage_type == "ppo"
+
+
+@dataclass
+class DpoConfig(BaseTopConfig):
+    dpo_beta: float = 0.1
+    dpo_label_smoothing: float = 0.0
+    dpo_sft_loss_coef: float = 0.0
+    reference_free: bool = False
+
+
+@dataclass
+class RewardTrainConfig(BaseTopConfig):
+    rm_loss: str = "bt"  # Bradley-Terry pairwise
+    rm_margin: float = 0.0
+
+
+@dataclass
+class DistillConfig(RlConfig):
+    distill_type: str = "on_policy"  # on_policy | off_policy
+    distill_topk: int = 0
+    distill_loss: str = "reverse_kl"
+    teacher: Optional[PolicyConfig] = None
+    distill_alpha: float = 1.0
+
+
+@dataclass
+class EvaluateConfig(BaseTopConfig):
+    sampler: SamplerConfig = field(default_factory=SamplerConfig)
+    eval_repeat_n: int = 1
+
+
+@dataclass
+class InferenceConfig(EvaluateConfig):
+    output_path: Optional[str] = None

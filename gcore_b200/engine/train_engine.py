@@ -1,0 +1,421 @@
+"""Training engine: owns the model shard, the gradient / parameter buffers and the distributed optimizer of one rank.
+
+Public verbs are those of the reference's ``BaseEngine`` (gpatch_v4/training_backend/base_engine.py:8-102):
+``setup_model_and_get_optimizer``, ``compute_log_probs``, ``rl_train_actor``, ``finetune_step``, ``compute_values``,
+``rl_train_value``, ``offload_* / onload_*``, ``export_weights``.  One implementation serves both back ends:
+``native`` runs the sm_100a kernels, ``nccl_eager`` forces the PyTorch / library path of every op (the measured
+baseline); collectives sit at the same call sites in both.
+
+All sequence data is packed (THD).  Losses are normalised globally: per-token losses divide by the token count of the
+whole global batch (all micro-batches, all DP ranks), per-sequence losses by the number of sequences.
+"""
+from __future__ import annotations
+
+import contextlib
+import os
+import time
+from typing import Callable, Dict, List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from ..core import parallel_state as ps
+from ..core.packing import PackedBatch, make_microbatches, pack_samples
+from ..loss import policy_loss as PL
+from ..models.config import ModelConfig, build_model_config
+from ..models.gpt import GPTModel
+from ..models.lora import apply_lora, verify_lora_weight_consistency
+from ..ops import _lib
+from ..ops.rl import grpo_loss as fused_grpo_loss
+from ..ops.vocab import linear_logprob_entropy
+from ..parallel.distributed_optimizer import DistributedDataParallel, DistributedOptimizer, lr_at_step
+
+
+def _device():
+    return torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+
+
+@contextlib.contextmanager
+def backend_scope(backend: str):
+    """``nccl_eager`` forces the eager implementation of every op for the duration of the call."""
+    if backend != "nccl_eager":
+        yield
+        return
+    old = os.environ.get("GCORE_B200_FORCE_EAGER")
+    os.environ["GCORE_B200_FORCE_EAGER"] = "1"
+    try:
+        yield
+    finally:
+        if old is None:
+            os.environ.pop("GCORE_B200_FORCE_EAGER", None)
+        else:
+            os.environ["GCORE_B200_FORCE_EAGER"] = old
+
+
+class TrainingEngine:
+    def __init__(self, policy_cfg, optimizer_cfg, training_cfg, ppo_cfg=None, model_cfg: Optional[ModelConfig] = None,
+                 role: str = "policy", value_head: bool = False, total_steps: Optional[int] = None):
+        self.policy_cfg, self.opt_cfg, self.train_cfg, self.ppo_cfg = policy_cfg, optimizer_cfg, training_cfg, ppo_cfg
+        self.role = role
+        self.value_head = value_head
+        self.total_steps = total_steps
+        self.backend = training_cfg.training_backend
+        self.device = _device()
+        self.model_cfg = model_cfg or build_model_config(policy_cfg.model_arch, policy_cfg.model_config)
+        self.model: Optional[GPTModel] = None
+        self.ref_model: Optional[GPTModel] = None
+        self.ddp: Optional[DistributedDataParallel] = None
+        self.optimizer: Optional[DistributedOptimizer] = None
+        self.adapters = {}
+        self.step = 0
+        self.temperature = 1.0
+        self.metrics_hooks: List[Callable] = []
+        self.timers: Dict[str, float] = {}
+
+    # ------------------------------------------------------------------ setup
+    def _build(self, seed=None, value_head=False, recompute=None) -> GPTModel:
+        d = self.policy_cfg.dist_config
+        st = ps.get_state()
+        tp = st.tp if st.initialized else 1
+        ep = st.ep if st.initialized else 1
+        if self.device.type == "cpu" and self.model_cfg.dtype == "bfloat16" and os.environ.get("GCORE_CPU_FP32", "1") == "1":
+            pass
+        m = GPTModel(self.model_cfg, tp_size=tp, ep_size=ep, sequence_parallel=d.sequence_parallel,
+                     recompute=recompute if recompute is not None else self.policy_cfg.recompute,
+                     device=self.device, value_head=value_head)
+        if seed is not None:
+            m.reset_parameters(seed)
+        return m
+
+    def setup_model_and_get_optimizer(self, seed: Optional[int] = None, with_ref: Optional[bool] = None):
+        with_ref = (not self.policy_cfg.without_ref) if with_ref is None else with_ref
+        seed = self.train_cfg.seed if seed is None else seed
+        self.model = self._build(seed, self.value_head)
+        if with_ref and not self.value_head:
+            # the reference policy starts as a frozen copy of the initial weights
+            self.ref_model = self._build(seed, False, recompute="none")
+            for p in self.ref_model.parameters():
+                p.requires_grad_(False)
+            self.ref_model.eval()
+        if self.policy_cfg.lora.enabled:
+            self.adapters = apply_lora(self.model, self.policy_cfg.lora, seed)
+            if self.policy_cfg.lora.verify_weight_consistency:
+                assert verify_lora_weight_consistency(self.adapters, ps.get_tensor_model_parallel_group()), \
+                    "LoRA replicated halves differ across the TP group"
+        self._apply_freeze()
+        if not self.policy_cfg.without_optim:
+            oc = self.opt_cfg
+            self.ddp = DistributedDataParallel(self.model, oc.grad_reduce_in_fp32, oc.bucket_size,
+                                               oc.use_distributed_optimizer, oc.overlap_grad_reduce)
+            self.optimizer = DistributedOptimizer(self.ddp, oc, self.total_steps)
+        return self.model, self.optimizer
+
+    def _apply_freeze(self):
+        import re
+        for pat in self.policy_cfg.freeze_patterns:
+            for n, p in self.model.named_parameters():
+                if re.search(pat, n):
+                    p.requires_grad_(False)
+        for pat in self.policy_cfg.unfreeze_patterns:
+            for n, p in self.model.named_parameters():
+                if re.search(pat, n):
+                    p.requires_grad_(True)
+
+    def set_model_train(self):
+        self.model.train()
+
+    def set_model_eval(self):
+        self.model.eval()
+
+    # ------------------------------------------------------------------ forward helpers
+    def _hidden(self, model: GPTModel, mb: PackedBatch):
+        return model(mb.tokens, mb.position_ids, mb.cu_seqlens, mb.max_seqlen)
+
+    def _logprob_entropy(self, model: GPTModel, hidden, targets, want_entropy=True):
+        w = model.output_weight()
+        tp_group = ps.get_tensor_model_parallel_group() if model.tp_size > 1 else None
+        mg = getattr(w, "main_grad", None) if (w.requires_grad and torch.is_grad_enabled()) else None
+        return linear_logprob_entropy(hidden, w, targets, self.temperature, tp_group, model.vocab_start(), mg,
+                                      want_entropy)
+
+    def _tp_pad(self):
+        return ps.get_tensor_model_parallel_world_size() if (self.model is not None and self.model.sequence_parallel) \
+            else 1
+
+    def _pack(self, samples, idx, keys=()):
+        pad = max(self._tp_pad(), 1)
+        if self.device.type == "cuda":
+            pad = pad * 8 if pad > 1 else 8
+        return pack_samples(samples, idx, keys, pad_to_multiple=pad, pin=self.device.type == "cuda").to(self.device)
+
+    def _microbatches(self, samples, forward_only=False):
+        lens = [len(s["tokens"]) for s in samples]
+        pc = self.policy_cfg
+        max_tok = pc.dynamic_mbs_target_seqlen
+        mbs = pc.forward_only_mbs if forward_only else self.train_cfg.train_mbs
+        return make_microbatches(lens, mbs=mbs, max_tokens=max_tok)
+
+    # ------------------------------------------------------------------ log-probs (forward only)
+    @torch.no_grad()
+    def compute_log_probs(self, samples: Sequence[dict], use_ref: bool = False, with_entropy: bool = True,
+                          out_key: Optional[str] = None):
+        """Writes ``logprobs`` (or ``ref_logprobs``) and ``prev_per_token_entropies`` (fp32 CPU tensors of length
+        S-1... stored at length S with a trailing 0) into every sample."""
+        model = self.ref_model if use_ref else self.model
+        assert model is not None
+        was_training = model.training
+        model.eval()
+        key = out_key or ("ref_logprobs" if use_ref else "logprobs")
+        with backend_scope(self.backend):
+            for idx in self._microbatches(samples, forward_only=True):
+                mb = self._pack(samples, idx)
+                hidden, _ = self._hidden(model, mb)
+                lp, ent = self._logprob_entropy(model, hidden, mb.targets, with_entropy)
+                lp_c, ent_c = lp.float().cpu(), ent.float().cpu()
+                cu = mb.cu_seqlens.tolist()
+                for j, i in enumerate(idx):
+                    s, e = cu[j], cu[j + 1]
+                    samples[i][key] = lp_c[s:e].clone()
+                    if with_entropy and not use_ref:
+                        samples[i]["prev_per_token_entropies"] = ent_c[s:e].clone()
+        if was_training:
+            model.train()
+        return samples
+
+    @torch.no_grad()
+    def compute_values(self, samples: Sequence[dict]):
+        assert self.value_head
+        self.model.eval()
+        with backend_scope(self.backend):
+            for idx in self._microbatches(samples, forward_only=True):
+                mb = self._pack(samples, idx)
+                v, _ = self._hidden(self.model, mb)
+                vc = v.float().cpu()
+                cu = mb.cu_seqlens.tolist()
+                for j, i in enumerate(idx):
+                    samples[i]["values"] = vc[cu[j]:cu[j + 1]].clone()
+        return samples
+
+    # ------------------------------------------------------------------ shared step machinery
+    def _global_counts(self, samples, per_token: bool) -> float:
+        if per_token:
+            n = sum(float(torch.as_tensor(s["mask"] if "mask" in s else s["loss_mask"]).sum()) for s in samples)
+        else:
+            n = float(len(samples))
+        t = torch.tensor([n], dtype=torch.float64)
+        g = ps.get_data_parallel_group(with_context_parallel=True)
+        if g is not None and dist.get_world_size(g) > 1:
+            tt = t.float().to(self.device) if dist.get_backend(g) == "nccl" else t.float()
+            dist.all_reduce(tt, group=g)
+            n = float(tt.item())
+        return max(n, 1.0)
+
+    def _finish_step(self, lr=None):
+        dp = ps.get_data_parallel_world_size(with_context_parallel=True)
+        # micro-batch losses are already normalised by global counts: sum (not average) over data parallel ranks
+        self.ddp.finish_grad_sync(extra_scale=float(dp))
+        lr = self.optimizer.step(lr)
+        self.step += 1
+        return lr, float(self.optimizer.last_grad_norm.item())
+
+    def _reduce_metrics(self, acc: Dict[str, torch.Tensor]) -> Dict[str, float]:
+        """``[sum, count]`` pairs become ratios after a sum over DP; scalars are averaged."""
+        if not acc:
+            return {}
+        keys = sorted(acc)
+        flat = torch.stack([acc[k].reshape(-1)[:2] if acc[k].numel() >= 2 else
+                            torch.stack([acc[k].reshape(()), acc[k].new_tensor(1.0)]) for k in keys]).float()
+        g = ps.get_data_parallel_group(with_context_parallel=True)
+        if g is not None and dist.get_world_size(g) > 1:
+            dist.all_reduce(flat, group=g)
+        flat = flat.cpu()
+        return {k: float(flat[i, 0] / flat[i, 1].clamp_min(1e-12)) for i, k in enumerate(keys)}
+
+    # ------------------------------------------------------------------ SFT
+    def finetune_step(self, samples: Sequence[dict]) -> Dict[str, float]:
+        """One optimizer step of masked next-token cross-entropy over ``samples`` (this rank's share of the global
+        batch).  Loss = sum(mask * nll) / global mask count (gpatch_v4/training_backend/loss_factory.py:2250-2309)."""
+        per_token = self.train_cfg.per_token_loss
+        self.model.train()
+        self.ddp.zero_grad_buffer()
+        for s in samples:
+            if "mask" not in s and "loss_mask" not in s:
+                from ..core.packing import response_mask
+                s["mask"] = response_mask(int(s.get("prompt_length", 0)), len(s["tokens"]))
+        denom = self._global_counts(samples, per_token)
+        acc = {"lm_loss": torch.zeros(2, device=self.device)}
+        with backend_scope(self.backend):
+            for idx in self._microbatches(samples):
+                mb = self._pack(samples, idx)
+                hidden, aux = self._hidden(self.model, mb)
+                lp, _ = self._logprob_entropy(self.model, hidden, mb.targets, want_entropy=False)
+                w = PL.aggregation_weights(mb.loss_mask, mb.seq_ids, mb.num_seqs + 1, per_token, denom)
+                loss = -(lp * w).sum()
+                if aux is not None:
+                    loss = loss + aux / max(len(samples) // max(len(idx), 1), 1)
+                loss.backward()
+                with torch.no_grad():
+                    acc["lm_loss"] += torch.stack([-(lp.detach() * mb.loss_mask).sum(), mb.loss_mask.sum()])
+            lr, gn = self._finish_step()
+        out = self._reduce_metrics(acc)
+        out.update(lr=lr, grad_norm=gn)
+        return out
+
+    pretrain_step = finetune_step
+
+    # ------------------------------------------------------------------ RL actor
+    def rl_train_actor(self, samples: Sequence[dict]) -> Dict[str, float]:
+        """One policy update over ``samples`` (each holds tokens, mask, advantages, logprobs, ref_logprobs and
+        optionally rollout_log_probs).  Mirrors ``_update_policy`` (megatron_backend/mixin.py:2689-2912)."""
+        cfg = self.ppo_cfg
+        per_token = cfg.per_token_loss
+        self.model.train()
+        self.ddp.zero_grad_buffer()
+        denom = self._global_counts(samples, per_token)
+        keys = ["advantages"]
+        has_old = not cfg.skip_prev_logps and all("logprobs" in s for s in samples)
+        has_ref = cfg.grpo_kl_loss_beta != 0 and all("ref_logprobs" in s for s in samples)
+        has_roll = cfg.offpolicy_correction != "none" and all("rollout_log_probs" in s for s in samples)
+        if has_old:
+            keys.append("logprobs")
+        if has_ref:
+            keys.append("ref_logprobs")
+        if has_roll or cfg.loss_func == "vespo":
+            keys.append("rollout_log_probs")
+        want_ent = cfg.ppo_entropy_bonus != 0
+        fast = (cfg.loss_func == "grpo" and not has_roll and not want_ent and cfg.kl_estimator == "k3"
+                and cfg.loss_func_py_path is None)
+        loss_fn = None if fast else self._resolve_loss()
+        acc: Dict[str, torch.Tensor] = {}
+
+        def add(k, v):
+            acc[k] = acc[k] + v if k in acc else v.clone()
+
+        for s in samples:
+            s.setdefault("loss_mask", s["mask"])
+        with backend_scope(self.backend):
+            for idx in self._microbatches(samples):
+                mb = self._pack(samples, idx, keys)
+                hidden, aux = self._hidden(self.model, mb)
+                lp, ent = self._logprob_entropy(self.model, hidden, mb.targets, want_ent)
+                f = mb.fields
+                w = PL.aggregation_weights(mb.loss_mask, mb.seq_ids, mb.num_seqs + 1, per_token, denom)
+                old = f.get("logprobs") if has_old else None
+                ref = f.get("ref_logprobs") if has_ref else None
+                if fast:
+                    loss, st = fused_grpo_loss(lp, old, ref, f["advantages"], w, clip_low=cfg.clip_low,
+                                               clip_high=cfg.clip_high, dual_clip_c=cfg.ppo_dual_clip_ratio_c or 0.0,
+                                               kl_beta=cfg.grpo_kl_loss_beta if has_ref else 0.0,
+                                               ratio_clamp=cfg.ppo_logps_ratio_clamp or 0.0,
+                                               kl_clamp=cfg.ppo_clamp_kl_val or 0.0)
+                    cnt = mb.loss_mask.sum() / max(denom, 1.0) if per_token else st[2]
+                    add("ppo-metrics/pg_loss", torch.stack([st[0], st[2]]))
+                    add("ppo-metrics/kl_to_ref", torch.stack([st[1], st[2]]))
+                    add("ppo-metrics/clipfrac", torch.stack([st[3], st[2]]))
+                    add("ppo-metrics/ratio", torch.stack([st[4], st[2]]))
+                    add("ppo-metrics/approx_kl", torch.stack([st[5], st[2]]))
+                else:
+                    li = PL.LossInput(lp, old, ref, f.get("rollout_log_probs"), f["advantages"], mb.loss_mask,
+                                      mb.seq_ids, mb.num_seqs + 1, ent, None)
+                    lo = loss_fn(cfg, li)
+                    tl = lo.token_loss
+                    if has_roll and cfg.loss_func != "vespo":
+                        cw, cm = PL.offpolicy_correction(cfg, old if old is not None else lp.detach(),
+                                                         f["rollout_log_probs"], mb.loss_mask, mb.seq_ids,
+                                                         mb.num_seqs + 1)
+                        tl = tl * cw
+                        for k, v in cm.items():
+                            add(k, v)
+                    if has_ref:
+                        kl = PL.kl_penalty(lp, ref, cfg.kl_estimator, cfg.ppo_clamp_kl_val)
+                        tl = tl + cfg.grpo_kl_loss_beta * kl
+                        add("ppo-metrics/kl_to_ref", torch.stack([(kl.detach() * w).sum(), w.sum()]))
+                    if want_ent:
+                        tl = tl - cfg.ppo_entropy_bonus * ent
+                    loss = (tl * w).sum()
+                    add("ppo-metrics/pg_loss", torch.stack([(lo.token_loss.detach() * w).sum(), w.sum()]))
+                    add("ppo-metrics/ratio", torch.stack([(lo.ratios * w).sum(), w.sum()]))
+                    for k, v in lo.metrics.items():
+                        add("ppo-metrics/" + k, v)
+                if want_ent or not fast:
+                    if ent is not None:
+                        add("policy/entropy", torch.stack([(ent.detach() * mb.loss_mask).sum(), mb.loss_mask.sum()]))
+                if aux is not None:
+                    loss = loss + aux
+                loss.backward()
+            lr, gn = self._finish_step()
+        out = self._reduce_metrics(acc)
+        out.update({"policy/lr": lr, "policy/grad_norm": gn})
+        return out
+
+    def _resolve_loss(self):
+        cfg = self.ppo_cfg
+        if cfg.loss_func_py_path:
+            from ..configs.base import import_from_path
+            return import_from_path(cfg.loss_func_py_path, cfg.loss_func_fn_name or "loss_func")
+        return PL.get_loss(cfg.loss_func)
+
+    # ------------------------------------------------------------------ critic
+    def rl_train_value(self, samples: Sequence[dict]) -> Dict[str, float]:
+        assert self.value_head
+        cfg = self.ppo_cfg
+        self.model.train()
+        self.ddp.zero_grad_buffer()
+        denom = self._global_counts(samples, True)
+        acc = {"value/loss": torch.zeros(2, device=self.device)}
+        for s in samples:
+            s.setdefault("loss_mask", s["mask"])
+        with backend_scope(self.backend):
+            for idx in self._microbatches(samples):
+                mb = self._pack(samples, idx, ["returns", "values"])
+                v, _ = self._hidden(self.model, mb)
+                w = mb.loss_mask / denom
+                loss = PL.value_loss(v, mb.fields["values"], mb.fields["returns"], w, cfg.ppo_value_clip)
+                loss.backward()
+                acc["value/loss"] += torch.stack([loss.detach() * denom, mb.loss_mask.sum()])
+            lr, gn = self._finish_step()
+        out = self._reduce_metrics(acc)
+        out.update({"value/lr": lr, "value/grad_norm": gn})
+        return out
+
+    # ------------------------------------------------------------------ memory time-sharing
+    def offload_optimizer(self):
+        if self.optimizer is not None:
+            self.optimizer.offload()
+
+    def onload_optimizer(self):
+        if self.optimizer is not None:
+            self.optimizer.onload()
+
+    def release_grad_buffers(self):
+        if self.ddp is not None:
+            self.ddp.release_grads()
+            if torch.cuda.is_available():
+                torch.cuda.empty_cache()
+
+    def allocate_grad_buffers(self):
+        if self.ddp is not None:
+            self.ddp.allocate_grads()
+
+    # ------------------------------------------------------------------ weights
+    def named_local_weights(self, merged_lora: bool = True):
+        """(name, tensor) of this rank's parameter shards; LoRA deltas are folded into their base on the fly."""
+        from ..models.gpt import ParallelLinear
+        lora_of = {}
+        if merged_lora:
+            for n, m in self.model.named_modules():
+                if isinstance(m, ParallelLinear) and m.lora is not None:
+                    lora_of[n + ".weight"] = m.lora
+        for n, p in self.model.named_parameters():
+            if getattr(p, "is_lora", False):
+                continue
+            if n in lora_of:
+                yield n, (p.detach().float() + lora_of[n].delta_weight()).to(p.dtype)
+            else:
+                yield n, p.detach()
+
+    def export_weights(self, to_hf: bool = True):
+        """Generator of full (TP / EP gathered) tensors under HF names, the contract of mbridge ``export_weights``
+        used for resync and safetensors export (gpatch_v4/training_backend/megatron_backend/mcore_engine.py:366-370)."""
+        from ..checkpoint.layout import export_full_weights
+        yield from export_full_weights(self, to_hf=to_hf)

@@ -1,0 +1,252 @@
+"""Policy-gradient objectives on packed per-token tensors, behind a name registry.
+
+Semantics follow the reference's loss registry (gpatch_v4/training_backend/loss/registry.py:10-106 and
+ppo_loss.py:232-863): ``grpo`` (PPO clip with asymmetric / dual clip), ``gspo`` (sequence-level importance ratio with
+token-level gradient), ``cispo`` (clipped, detached IS weight on a REINFORCE term), ``sapo`` (soft sigmoid gate),
+``vespo`` (smooth sequence-level kernel), ``opd`` / ``reinforce``.  Every loss returns per-token values; the caller
+applies KL-to-reference, the entropy bonus, off-policy correction weights and the aggregation weights.
+
+All tensors are flat ``[T]`` fp32 on the log-prob axis; ``seq_ids`` maps a token to its sequence for the
+sequence-level variants (packing-safe, unlike a ``[B, S]`` reduction over the last dim).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Dict, Optional
+
+import torch
+
+from ..ops import rl as rl_ops
+
+_REGISTRY: Dict[str, Callable] = {}
+
+
+def register_loss(name: str):
+    def deco(fn):
+        if name in _REGISTRY:
+            raise KeyError(f"loss '{name}' already registered")
+        _REGISTRY[name] = fn
+        return fn
+    return deco
+
+
+def get_loss(name: str) -> Callable:
+    if name not in _REGISTRY:
+        raise KeyError(f"unknown loss '{name}'; registered: {sorted(_REGISTRY)}")
+    return _REGISTRY[name]
+
+
+def registered_losses():
+    return sorted(_REGISTRY)
+
+
+@dataclass
+class LossInput:
+    logp: torch.Tensor                      # current policy, requires grad
+    old_logp: Optional[torch.Tensor]        # behaviour policy under the trainer (None -> logp.detach())
+    ref_logp: Optional[torch.Tensor]
+    rollout_logp: Optional[torch.Tensor]    # behaviour policy as reported by the rollout engine
+    advantages: torch.Tensor
+    mask: torch.Tensor
+    seq_ids: torch.Tensor                   # [T] int
+    num_seqs: int
+    entropy: Optional[torch.Tensor] = None
+    old_entropy: Optional[torch.Tensor] = None
+
+
+@dataclass
+class LossOutput:
+    token_loss: torch.Tensor
+    ratios: torch.Tensor
+    metrics: Dict[str, torch.Tensor] = field(default_factory=dict)
+
+
+def _seg_sum(x, seq_ids, n):
+    out = torch.zeros(n, dtype=x.dtype, device=x.device)
+    return out.index_add_(0, seq_ids.long(), x)
+
+
+def _token_ratio(cfg, logp, old):
+    d = logp - old
+    if cfg.ppo_logps_ratio_clamp is not None:
+        d = d.clamp(-cfg.ppo_logps_ratio_clamp, cfg.ppo_logps_ratio_clamp)
+    return torch.exp(d)
+
+
+def _frac(flag, mask):
+    n = mask.sum()
+    return torch.stack([(flag.float() * mask).sum(), n])
+
+
+@register_loss("grpo")
+def grpo_loss(cfg, li: LossInput) -> LossOutput:
+    old = li.logp.detach() if li.old_logp is None else li.old_logp
+    tl, _, ratio, clipped = rl_ops.grpo_token_loss_ref(
+        li.logp, old, None, li.advantages, clip_low=cfg.clip_low, clip_high=cfg.clip_high,
+        dual_clip_c=cfg.ppo_dual_clip_ratio_c or 0.0, kl_beta=0.0, ratio_clamp=cfg.ppo_logps_ratio_clamp or 0.0)
+    return LossOutput(tl, ratio.detach(), {"ppo_ratio_clamped_frac": _frac(clipped, li.mask)})
+
+
+@register_loss("gspo")
+def gspo_loss(cfg, li: LossInput) -> LossOutput:
+    """Sequence importance ratio = exp(mean_t(logp - old)); the gradient still flows through every token."""
+    old = li.logp.detach() if li.old_logp is None else li.old_logp
+    d = (li.logp - old) * li.mask
+    lens = _seg_sum(li.mask, li.seq_ids, li.num_seqs).clamp_min(1.0)
+    seq_mean = _seg_sum(d, li.seq_ids, li.num_seqs) / lens
+    log_ratio = li.logp - li.logp.detach() + seq_mean.detach()[li.seq_ids.long()]
+    ratio = torch.exp(log_ratio.clamp(max=10.0))
+    l1 = -li.advantages * ratio
+    l2 = -li.advantages * ratio.clamp(1 - cfg.clip_low, 1 + cfg.clip_high)
+    return LossOutput(torch.maximum(l1, l2), ratio.detach(), {"ppo_ratio_clamped_frac": _frac(l2 > l1, li.mask)})
+
+
+@register_loss("cispo")
+def cispo_loss(cfg, li: LossInput) -> LossOutput:
+    old = li.logp.detach() if li.old_logp is None else li.old_logp
+    ratio = _token_ratio(cfg, li.logp, old)
+    clipped = ratio.clamp(1 - cfg.clip_low, 1 + cfg.clip_high)
+    tl = -clipped.detach() * li.advantages * li.logp
+    return LossOutput(tl, ratio.detach(), {"cispo/clipfrac": _frac(clipped.detach() != ratio.detach(), li.mask)})
+
+
+@register_loss("sapo")
+def sapo_loss(cfg, li: LossInput) -> LossOutput:
+    old = li.logp.detach() if li.old_logp is None else li.old_logp
+    ratio = _token_ratio(cfg, li.logp, old)
+    tau = torch.where(li.advantages > 0, torch.full_like(ratio, cfg.sapo_tau_pos),
+                      torch.full_like(ratio, cfg.sapo_tau_neg))
+    sg = torch.sigmoid(tau * (ratio - 1.0))
+    gate = (4.0 / tau) * sg
+    kern = 4.0 * sg.detach() * (1 - sg.detach())
+    return LossOutput(-li.advantages * gate, ratio.detach(),
+                      {"sapo/strong_attenuation_frac": _frac(kern < 0.5, li.mask)})
+
+
+@register_loss("vespo")
+def vespo_loss(cfg, li: LossInput) -> LossOutput:
+    """REINFORCE scaled by phi(W) = W^c1 * exp(c2 * (1 - W)), W = product of token ratios (policy lag times
+    train / rollout mismatch) over the sequence; phi is detached."""
+    assert li.old_logp is not None and li.rollout_logp is not None, "vespo needs prev and rollout log-probs"
+    clampv = cfg.ppo_logps_ratio_clamp or 20.0
+    with torch.no_grad():
+        tlr = (li.logp - li.old_logp).clamp(-clampv, clampv)
+        tis = (li.old_logp - li.rollout_logp).clamp(-clampv, clampv)
+        seq_log_w = _seg_sum((tlr + tis) * li.mask, li.seq_ids, li.num_seqs).clamp(-clampv, clampv)
+        w = seq_log_w.exp()
+        lens = _seg_sum(li.mask, li.seq_ids, li.num_seqs).clamp_min(1.0)
+        seq_adv = _seg_sum(li.advantages * li.mask, li.seq_ids, li.num_seqs) / lens
+        pos = (seq_adv >= 0).float()
+        c1 = pos * getattr(cfg, "vespo_c1_pos", 1.0) + (1 - pos) * getattr(cfg, "vespo_c1_neg", 1.0)
+        c2 = (pos * getattr(cfg, "vespo_c2_pos", 1.0) + (1 - pos) * getattr(cfg, "vespo_c2_neg", 1.0)).clamp_min(1e-4)
+        phi = torch.nan_to_num(torch.exp(c2 + c1 * torch.log(w.clamp_min(1e-8)) - c2 * w), 0.0, 0.0, 0.0)
+        ratio = tlr.exp()
+    tl = -phi[li.seq_ids.long()] * li.advantages * li.logp
+    return LossOutput(tl, ratio, {"vespo/phi_mean": torch.stack([phi.sum(), phi.new_tensor(float(phi.numel()))])})
+
+
+@register_loss("reinforce")
+def reinforce_loss(cfg, li: LossInput) -> LossOutput:
+    return LossOutput(-li.advantages * li.logp, torch.ones_like(li.logp), {})
+
+
+@register_loss("opd")
+def opd_loss(cfg, li: LossInput) -> LossOutput:
+    """On-policy distillation: advantages already hold (teacher - student) log-prob gaps; clip like grpo."""
+    return grpo_loss(cfg, li)
+
+
+# ------------------------------------------------------------------------------------------------ shared terms
+def kl_penalty(logp, ref_logp, kind: str = "k3", clamp: Optional[float] = None):
+    """Estimators of KL(pi || ref) from samples of pi (gpatch_v4/utils/ppo_utils.py:151-193)."""
+    d = ref_logp - logp
+    if kind == "k1":
+        kl = -d
+    elif kind == "k2":
+        kl = 0.5 * d * d
+    else:
+        kl = torch.exp(d) - d - 1
+    if clamp is not None and clamp > 0:
+        kl = kl.clamp(max=clamp) if kind == "k3" else kl.clamp(-clamp, clamp)
+    return kl
+
+
+def offpolicy_correction(cfg, old_logp, rollout_logp, mask, seq_ids, num_seqs):
+    """Train-vs-rollout importance weights (gpatch_v4/core/correction_helper.py:238-420).
+    Returns ``(weights [T] detached, metrics)``; ``weights`` multiply the actor loss."""
+    with torch.no_grad():
+        lr = (old_logp - rollout_logp).clamp(-20.0, 20.0)
+        if cfg.offpolicy_correction_level == "token":
+            w = lr.exp()
+        else:
+            lens = _seg_sum(mask, seq_ids, num_seqs).clamp_min(1.0)
+            s = _seg_sum(lr * mask, seq_ids, num_seqs)
+            if cfg.offpolicy_correction_level == "geometric":
+                s = s / lens
+            w = s.clamp(-20.0, 20.0).exp()[seq_ids.long()]
+        upper = cfg.offpolicy_correction_upper
+        lower = cfg.offpolicy_correction_lower if cfg.offpolicy_correction_lower is not None else 1.0 / upper
+        mode = cfg.offpolicy_correction
+        metrics = {"tis/weight_mean": torch.stack([(w * mask).sum(), mask.sum()]),
+                   "tis/out_of_range_frac": _frac((w > upper) | (w < lower), mask)}
+        if mode == "none":
+            out = torch.ones_like(w)
+        elif mode == "truncate":
+            out = w.clamp(max=upper)
+        elif mode == "clip":
+            out = w.clamp(lower, upper)
+        elif mode == "mask":
+            out = torch.where((w >= lower) & (w <= upper), torch.ones_like(w), torch.zeros_like(w))
+        elif mode == "icepop":
+            out = torch.where((w >= lower) & (w <= upper), w, torch.zeros_like(w))
+        elif mode == "kpop":
+            # drop whole sequences whose geometric-mean weight leaves the band
+            lens = _seg_sum(mask, seq_ids, num_seqs).clamp_min(1.0)
+            g = (_seg_sum(lr * mask, seq_ids, num_seqs) / lens).exp()
+            keep = ((g >= lower) & (g <= upper)).float()
+            out = w.clamp(max=upper) * keep[seq_ids.long()]
+        else:
+            raise ValueError(mode)
+        veto = cfg.offpolicy_correction_veto
+        if veto is not None:
+            bad = _seg_sum(((w < veto).float() * mask), seq_ids, num_seqs) > 0
+            out = out * (~bad).float()[seq_ids.long()]
+            metrics["tis/veto_frac"] = torch.stack([bad.float().sum(), bad.new_tensor(float(num_seqs)).float()])
+    return out, metrics
+
+
+def aggregation_weights(mask, seq_ids, num_seqs, per_token: bool, denom: float):
+    """Weights ``w`` such that ``sum(w * token_loss)`` is this micro-batch's share of the global loss.
+    per-token: ``mask / global_token_count``; else per-sequence masked means over ``global_alive_sequences``
+    (gpatch_v4/training_backend/loss/utils.py:8-55, megatron_backend/mixin.py:1949-1983)."""
+    if per_token:
+        return mask / max(denom, 1.0)
+    lens = _seg_sum(mask, seq_ids, num_seqs).clamp_min(1.0)
+    return mask / lens[seq_ids.long()] / max(denom, 1.0)
+
+
+def value_loss(values, old_values, returns, mask_w, clip: Optional[float]):
+    """0.5 * max((clip(V) - R)^2, (V - R)^2) (gpatch_v4/training_backend/loss_factory.py:3355-3371)."""
+    l1 = (values - returns) ** 2
+    if clip is not None and clip > 0:
+        vc = old_values + (values - old_values).clamp(-clip, clip)
+        l1 = torch.maximum(l1, (vc - returns) ** 2)
+    return 0.5 * (l1 * mask_w).sum()
+
+
+def dpo_loss(pol_chosen, pol_rejected, ref_chosen, ref_rejected, beta: float, label_smoothing: float = 0.0,
+             reference_free: bool = False):
+    """Sequence log-prob sums -> DPO loss and reward accuracies."""
+    pi = pol_chosen - pol_rejected
+    ref = torch.zeros_like(pi) if reference_free else ref_chosen - ref_rejected
+    logits = beta * (pi - ref)
+    loss = -(torch.nn.functional.logsigmoid(logits) * (1 - label_smoothing)
+             + torch.nn.functional.logsigmoid(-logits) * label_smoothing)
+    return loss.mean(), {"dpo/reward_acc": (logits > 0).float().mean().detach(),
+                         "dpo/margin": logits.detach().mean() / max(beta, 1e-12)}
+
+
+def rm_bt_loss(score_chosen, score_rejected, margin: float = 0.0):
+    """Bradley-Terry pairwise reward-model loss."""
+    d = score_chosen - score_rejected - margin
+    return -torch.nn.functional.logsigmoid(d).mean(), {"rm/acc": (d > 0).float().mean().detach()}

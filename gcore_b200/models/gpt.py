@@ -1,0 +1,408 @@
+"""Decoder-only transformer (Llama / Qwen2 / Qwen3 / Qwen3-MoE / DeepSeek-V3 families) over packed (THD) tokens with
+tensor + sequence parallelism.  Parameter names follow Megatron-Core's GPTModel (``embedding.word_embeddings``,
+``decoder.layers.N.self_attention.linear_qkv`` ..., see tools/px_ckpt_conv/moe_hf_to_mlm.py:26-244 in the reference)
+so torch_dist checkpoints and the HF converters address the same tensors.
+
+Internal weight layouts differ from mcore where the kernels want it and are converted at checkpoint / resync time
+(``gcore_b200/checkpoint/layout.py``):
+  * ``linear_qkv.weight`` rows are ``[Q heads | K heads | V heads]`` of this TP rank (mcore interleaves per KV group);
+  * ``linear_fc1.weight`` rows are ``[gate | up]`` of this TP rank.
+
+The forward returns the final hidden states; the vocabulary projection is fused into the loss / log-prob op
+(``ops.vocab.linear_logprob_entropy``) so ``[T, V]`` logits are never materialised.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn as nn
+from torch.utils.checkpoint import checkpoint
+
+from ..core import parallel_state as ps
+from ..ops import fused
+from ..ops.attention import flash_attn_qkvpacked, flash_attn_varlen
+from ..ops.gemm import linear
+from ..parallel import tp_ops
+from .config import ModelConfig
+from .lora import LoRAAdapter
+
+
+def _dtype(cfg: ModelConfig):
+    return {"bfloat16": torch.bfloat16, "float32": torch.float32, "float16": torch.float16}[cfg.dtype]
+
+
+class ParallelLinear(nn.Module):
+    """Weight ``[out_local, in_local]``.  ``mode``: 'column' shards the output dim over TP, 'row' the input dim,
+    'none' replicates.  ``main_grad`` (fp32, set by the DDP wrapper) receives the weight gradient directly from the
+    wgrad GEMM epilogue."""
+
+    def __init__(self, in_features, out_features, mode, cfg: ModelConfig, bias=False, tp_size=1, init_std=None,
+                 device=None):
+        super().__init__()
+        self.mode = mode
+        self.tp_size = tp_size
+        self.in_features, self.out_features = in_features, out_features
+        self.in_local = in_features // tp_size if mode == "row" else in_features
+        self.out_local = out_features // tp_size if mode == "column" else out_features
+        dt = _dtype(cfg)
+        self.weight = nn.Parameter(torch.empty(self.out_local, self.in_local, dtype=dt, device=device))
+        self.bias = nn.Parameter(torch.zeros(self.out_local, dtype=dt, device=device)) if bias else None
+        self.init_std = init_std if init_std is not None else cfg.init_std
+        self.weight.tp_mode = mode
+        if self.bias is not None:
+            self.bias.tp_mode = "column" if mode == "column" else "none"
+        self.lora: Optional[LoRAAdapter] = None
+
+    def forward(self, x):
+        w = self.weight
+        y = linear(x, w, self.bias, getattr(w, "main_grad", None) if w.requires_grad else None)
+        if self.lora is not None:
+            y = y + self.lora(x)
+        return y
+
+
+class RMSNormWeight(nn.Module):
+    def __init__(self, dim, cfg, device=None):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim, dtype=_dtype(cfg), device=device))
+        self.weight.tp_mode = "none"
+        self.weight.sequence_parallel = True
+
+
+class SelfAttention(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, tp_size: int, device=None):
+        super().__init__()
+        self.cfg, self.layer_idx, self.tp = cfg, layer_idx, tp_size
+        D = cfg.head_dim
+        self.hq, self.hk = cfg.num_attention_heads // tp_size, max(cfg.num_kv_heads // tp_size, 1)
+        assert cfg.num_attention_heads % tp_size == 0
+        assert cfg.num_kv_heads % tp_size == 0, "replicated KV heads (tp > num_kv_heads) are not supported"
+        self.linear_qkv = ParallelLinear(cfg.hidden_size, (cfg.num_attention_heads + 2 * cfg.num_kv_heads) * D,
+                                         "column", cfg, bias=cfg.qkv_bias, tp_size=tp_size, device=device)
+        self.linear_proj = ParallelLinear(cfg.num_attention_heads * D, cfg.hidden_size, "row", cfg, tp_size=tp_size,
+                                          init_std=cfg.init_std / math.sqrt(2 * cfg.num_layers), device=device)
+        if cfg.qk_layernorm:
+            self.q_layernorm = RMSNormWeight(D, cfg, device)
+            self.k_layernorm = RMSNormWeight(D, cfg, device)
+        self.window = cfg.layer_window(layer_idx)
+        if cfg.attention_sinks:
+            self.sinks = nn.Parameter(torch.zeros(self.hq, dtype=torch.float32, device=device))
+            self.sinks.tp_mode = "column"
+        else:
+            self.sinks = None
+
+    def forward(self, x, pos, cu_seqlens, max_seqlen):
+        cfg = self.cfg
+        T = x.shape[0]
+        D, hq, hk = cfg.head_dim, self.hq, self.hk
+        qkv = self.linear_qkv(x)  # [T, (hq + 2 hk) * D]
+        scale = 1.0 / math.sqrt(D)
+        if not cfg.qk_layernorm:
+            qkv = fused_rope_qk(qkv.view(T, hq + 2 * hk, D), pos, hq + hk, cfg.rope_theta, cfg.rotary_dim,
+                                cfg.rope_interleaved)
+            o = flash_attn_qkvpacked(qkv, hq, hk, cu_seqlens, max_seqlen, causal=True, window=self.window,
+                                     sinks=self.sinks, scale=scale)
+        else:
+            q, k, v = qkv.view(T, hq + 2 * hk, D).split([hq, hk, hk], dim=1)
+            q = fused.rmsnorm(q.reshape(-1, D), self.q_layernorm.weight, cfg.rms_norm_eps)[0].view(T, hq, D)
+            k = fused.rmsnorm(k.reshape(-1, D), self.k_layernorm.weight, cfg.rms_norm_eps)[0].view(T, hk, D)
+            q = fused.rope(q, pos, cfg.rope_theta, cfg.rotary_dim, cfg.rope_interleaved)
+            k = fused.rope(k, pos, cfg.rope_theta, cfg.rotary_dim, cfg.rope_interleaved)
+            o = flash_attn_varlen(q, k, v.contiguous(), cu_seqlens, cu_seqlens, max_seqlen, max_seqlen, causal=True,
+                                  window=self.window, sinks=self.sinks, scale=scale)
+        return self.linear_proj(o.reshape(T, hq * D))
+
+
+class _RopeQKInplace(torch.autograd.Function):
+    """Rotates the first ``nrot_heads`` heads of a packed ``[T, heads, D]`` buffer in place (the producing GEMM does
+    not need its output for backward, so overwriting it is safe); backward rotates the gradient back."""
+
+    @staticmethod
+    def forward(ctx, qkv, pos, nrot_heads, theta, rot, interleaved):
+        ctx.save_for_backward(pos)
+        ctx.args = (nrot_heads, theta, rot, interleaved)
+        fused.rope_inplace(qkv[:, :nrot_heads], pos, theta, rot, interleaved, False)
+        ctx.mark_dirty(qkv)
+        return qkv
+
+    @staticmethod
+    def backward(ctx, g):
+        (pos,) = ctx.saved_tensors
+        n, theta, rot, interleaved = ctx.args
+        g = g.contiguous() if not g.is_contiguous() else g
+        fused.rope_inplace(g[:, :n], pos, theta, rot, interleaved, True)
+        return g, None, None, None, None, None
+
+
+def fused_rope_qk(qkv, pos, nrot_heads, theta, rot, interleaved):
+    if qkv.requires_grad and torch.is_grad_enabled():
+        return _RopeQKInplace.apply(qkv, pos, nrot_heads, theta, rot, interleaved)
+    fused.rope_inplace(qkv[:, :nrot_heads], pos, theta, rot, interleaved, False)
+    return qkv
+
+
+class MLAttention(nn.Module):
+    """Multi-head latent attention (DeepSeek-V3): low-rank q and joint kv compression, decoupled RoPE key shared by
+    all heads.  Projections run on the tcgen05 GEMM; the (192 / 128)-dim attention core uses the reference path
+    until the kernel grows mixed qk / v head dims."""
+
+    def __init__(self, cfg: ModelConfig, layer_idx: int, tp_size: int, device=None):
+        super().__init__()
+        self.cfg, self.tp = cfg, tp_size
+        self.h = cfg.num_attention_heads // tp_size
+        dq, dn, dr, dv = cfg.qk_head_dim, cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim
+        H = cfg.hidden_size
+        if cfg.q_lora_rank:
+            self.linear_q_down_proj = ParallelLinear(H, cfg.q_lora_rank, "none", cfg, device=device)
+            self.q_layernorm = RMSNormWeight(cfg.q_lora_rank, cfg, device)
+            self.linear_q_up_proj = ParallelLinear(cfg.q_lora_rank, cfg.num_attention_heads * dq, "column", cfg,
+                                                   tp_size=tp_size, device=device)
+        else:
+            self.linear_q_proj = ParallelLinear(H, cfg.num_attention_heads * dq, "column", cfg, tp_size=tp_size,
+                                                device=device)
+        self.linear_kv_down_proj = ParallelLinear(H, cfg.kv_lora_rank + dr, "none", cfg, device=device)
+        self.kv_layernorm = RMSNormWeight(cfg.kv_lora_rank, cfg, device)
+        self.linear_kv_up_proj = ParallelLinear(cfg.kv_lora_rank, cfg.num_attention_heads * (dn + dv), "column", cfg,
+                                                tp_size=tp_size, device=device)
+        self.linear_proj = ParallelLinear(cfg.num_attention_heads * dv, H, "row", cfg, tp_size=tp_size,
+                                          init_std=cfg.init_std / math.sqrt(2 * cfg.num_layers), device=device)
+
+    def forward(self, x, pos, cu_seqlens, max_seqlen):
+        cfg = self.cfg
+        T, h = x.shape[0], self.h
+        dn, dr, dv = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim
+        if cfg.q_lora_rank:
+            ql = fused.rmsnorm(self.linear_q_down_proj(x), self.q_layernorm.weight, cfg.rms_norm_eps)[0]
+            q = self.linear_q_up_proj(ql).view(T, h, dn + dr)
+        else:
+            q = self.linear_q_proj(x).view(T, h, dn + dr)
+        kv = self.linear_kv_down_proj(x)
+        c_kv, k_rope = kv.split([cfg.kv_lora_rank, dr], dim=-1)
+        c_kv = fused.rmsnorm(c_kv.contiguous(), self.kv_layernorm.weight, cfg.rms_norm_eps)[0]
+        kvu = self.linear_kv_up_proj(c_kv).view(T, h, dn + dv)
+        k_nope, v = kvu.split([dn, dv], dim=-1)
+        q_nope, q_rope = q.split([dn, dr], dim=-1)
+        q_rope = fused.rope(q_rope.contiguous(), pos, cfg.rope_theta, dr, cfg.rope_interleaved)
+        k_rope = fused.rope(k_rope.reshape(T, 1, dr).contiguous(), pos, cfg.rope_theta, dr, cfg.rope_interleaved)
+        qf = torch.cat([q_nope, q_rope], -1)
+        kf = torch.cat([k_nope, k_rope.expand(T, h, dr)], -1)
+        # pad v to the qk head dim so one attention call serves both (extra columns are zero and sliced away)
+        vpad = torch.nn.functional.pad(v, (0, dn + dr - dv))
+        from ..ops.attention import attn_varlen_ref
+        o = attn_varlen_ref(qf, kf, vpad, cu_seqlens, cu_seqlens, True, 0, None, 1.0 / math.sqrt(dn + dr))
+        return self.linear_proj(o[..., :dv].reshape(T, h * dv))
+
+
+class MLP(nn.Module):
+    def __init__(self, cfg: ModelConfig, ffn: int, tp_size: int, device=None):
+        super().__init__()
+        self.linear_fc1 = ParallelLinear(cfg.hidden_size, 2 * ffn, "column", cfg, tp_size=tp_size, device=device)
+        self.linear_fc2 = ParallelLinear(ffn, cfg.hidden_size, "row", cfg, tp_size=tp_size,
+                                         init_std=cfg.init_std / math.sqrt(2 * cfg.num_layers), device=device)
+
+    def forward(self, x):
+        return self.linear_fc2(fused.swiglu(self.linear_fc1(x)))
+
+
+class TransformerLayer(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, tp_size: int, ep_size: int, device=None):
+        super().__init__()
+        self.cfg = cfg
+        self.layer_idx = layer_idx
+        self.input_layernorm = RMSNormWeight(cfg.hidden_size, cfg, device)
+        self.self_attention = (MLAttention if cfg.use_mla else SelfAttention)(cfg, layer_idx, tp_size, device)
+        self.pre_mlp_layernorm = RMSNormWeight(cfg.hidden_size, cfg, device)
+        if cfg.layer_is_moe(layer_idx):
+            from .moe import MoELayer
+            self.mlp = MoELayer(cfg, layer_idx, tp_size, ep_size, device)
+        else:
+            self.mlp = MLP(cfg, cfg.ffn_hidden_size, tp_size, device)
+        self.is_moe = cfg.layer_is_moe(layer_idx)
+
+    def forward(self, x, residual, pos, cu_seqlens, max_seqlen, tp_group, sp):
+        cfg = self.cfg
+        h, residual = fused.rmsnorm(x, self.input_layernorm.weight, cfg.rms_norm_eps, residual)
+        if sp:
+            h = tp_ops.gather_from_sequence_parallel(h, tp_group)
+        else:
+            h = tp_ops.copy_to_tensor_parallel(h, tp_group)
+        a = self.self_attention(h, pos, cu_seqlens, max_seqlen)
+        a = tp_ops.reduce_scatter_to_sequence_parallel(a, tp_group) if sp else \
+            tp_ops.reduce_from_tensor_parallel(a, tp_group)
+        h, residual = fused.rmsnorm(a, self.pre_mlp_layernorm.weight, cfg.rms_norm_eps, residual)
+        aux = None
+        if self.is_moe:
+            # experts see the sequence-parallel token shard: every TP rank routes its own tokens (ETP = 1)
+            m, aux = self.mlp(h)
+            return m, residual, aux
+        if sp:
+            h = tp_ops.gather_from_sequence_parallel(h, tp_group)
+        else:
+            h = tp_ops.copy_to_tensor_parallel(h, tp_group)
+        m = self.mlp(h)
+        m = tp_ops.reduce_scatter_to_sequence_parallel(m, tp_group) if sp else \
+            tp_ops.reduce_from_tensor_parallel(m, tp_group)
+        return m, residual, aux
+
+
+class GPTModel(nn.Module):
+    """One pipeline stage worth of layers (all of them when PP = 1)."""
+
+    def __init__(self, cfg: ModelConfig, tp_size: int = 1, ep_size: int = 1, sequence_parallel: bool = True,
+                 pre_process: bool = True, post_process: bool = True, layer_range=None, recompute: str = "none",
+                 device=None, value_head: bool = False):
+        super().__init__()
+        self.cfg = cfg
+        self.tp_size, self.ep_size = tp_size, ep_size
+        self.sequence_parallel = sequence_parallel and tp_size > 1
+        self.pre_process, self.post_process = pre_process, post_process
+        self.recompute = recompute
+        dt = _dtype(cfg)
+        self.vocab_local = _padded_vocab(cfg.vocab_size, tp_size) // tp_size
+        if pre_process:
+            self.embedding = nn.Module()
+            self.embedding.word_embeddings = nn.Module()
+            self.embedding.word_embeddings.weight = nn.Parameter(
+                torch.empty(self.vocab_local, cfg.hidden_size, dtype=dt, device=device))
+            self.embedding.word_embeddings.weight.tp_mode = "column"
+        lo, hi = layer_range if layer_range is not None else (0, cfg.num_layers)
+        self.layer_offset = lo
+        self.decoder = nn.Module()
+        self.decoder.layers = nn.ModuleList(
+            [TransformerLayer(cfg, i, tp_size, ep_size, device) for i in range(lo, hi)])
+        self.value_head = value_head
+        if post_process:
+            self.decoder.final_layernorm = RMSNormWeight(cfg.hidden_size, cfg, device)
+            if value_head:
+                # critic: hidden -> 1 (gpatch_v4/training_backend/megatron_backend/megatron_bridge.py:77-138)
+                self.output_layer = ParallelLinear(cfg.hidden_size, 1, "none", cfg, device=device)
+            elif not (cfg.tie_word_embeddings and pre_process):
+                self.output_layer = nn.Module()
+                self.output_layer.weight = nn.Parameter(
+                    torch.empty(self.vocab_local, cfg.hidden_size, dtype=dt, device=device))
+                self.output_layer.weight.tp_mode = "column"
+        self.reset_parameters()
+
+    # ------------------------------------------------------------------ init
+    def reset_parameters(self, seed: Optional[int] = None):
+        """Each parameter is drawn from its own generator keyed by (seed, parameter name, TP shard) so the values do
+        not depend on construction order.  TP-sharded tensors of small models are drawn at full size and sliced, which
+        makes a TP>1 model bit-identical to the TP=1 model (the CPU oracle tests rely on it)."""
+        import zlib
+        seed = 1234 if seed is None else seed
+        tp_rank = ps.get_tensor_model_parallel_rank() if self.tp_size > 1 else 0
+        for name, p in self.named_parameters():
+            mod_std = self.cfg.init_std
+            owner = self._owner(name)
+            if isinstance(owner, ParallelLinear):
+                mod_std = owner.init_std
+            if name.endswith("bias") or "sinks" in name:
+                with torch.no_grad():
+                    p.zero_()
+                continue
+            if p.dim() == 1:
+                with torch.no_grad():
+                    p.fill_(1.0)
+                continue
+            mode = getattr(p, "tp_mode", "none")
+            key = zlib.crc32(f"{self.layer_offset}:{name}".encode()) ^ seed
+            full_numel = p.numel() * (self.tp_size if mode in ("column", "row") else 1)
+            with torch.no_grad():
+                if self.tp_size > 1 and mode in ("column", "row") and full_numel <= (1 << 26) and p.dim() == 2:
+                    g = torch.Generator(device="cpu").manual_seed(key & 0x7FFFFFFF)
+                    if mode == "column":
+                        full = torch.randn(p.shape[0] * self.tp_size, p.shape[1], generator=g) * mod_std
+                        p.copy_(_column_shard(full, name, self, tp_rank))
+                    else:
+                        full = torch.randn(p.shape[0], p.shape[1] * self.tp_size, generator=g) * mod_std
+                        p.copy_(full.chunk(self.tp_size, 1)[tp_rank])
+                elif p.is_cuda and p.numel() > (1 << 22):
+                    g = torch.Generator(device=p.device).manual_seed((key + 7919 * tp_rank) & 0x7FFFFFFF)
+                    p.copy_(torch.randn(p.shape, generator=g, device=p.device, dtype=torch.float32) * mod_std)
+                else:
+                    g = torch.Generator(device="cpu").manual_seed(
+                        (key + (7919 * tp_rank if mode in ("column", "row") else 0)) & 0x7FFFFFFF)
+                    p.copy_(torch.randn(p.shape, generator=g) * mod_std)
+
+    def _owner(self, pname: str):
+        mod = self
+        for part in pname.split(".")[:-1]:
+            mod = getattr(mod, part)
+        return mod
+
+    # ------------------------------------------------------------------ forward
+    def output_weight(self):
+        if hasattr(self, "output_layer") and not self.value_head:
+            return self.output_layer.weight
+        return self.embedding.word_embeddings.weight
+
+    def vocab_start(self):
+        return self.vocab_local * (ps.get_tensor_model_parallel_rank() if self.tp_size > 1 else 0)
+
+    def forward(self, input_ids=None, position_ids=None, cu_seqlens=None, max_seqlen=None, hidden_in=None,
+                inputs_embeds=None):
+        """``input_ids`` [T] packed tokens (first stage) or ``hidden_in`` (later pipeline stages, sequence-parallel
+        shard).  Returns ``(hidden, aux_loss)``: on the last stage ``hidden`` is the final-normed ``[T, H]`` (gathered
+        over SP), otherwise the stage output to send downstream."""
+        tp_group = ps.get_tensor_model_parallel_group() if self.tp_size > 1 else None
+        sp = self.sequence_parallel
+        if self.pre_process:
+            if inputs_embeds is None:
+                x = tp_ops.vocab_parallel_embedding(input_ids, self.embedding.word_embeddings.weight,
+                                                    self.vocab_start(), tp_group)
+            else:
+                x = inputs_embeds
+            if sp:
+                x = tp_ops.scatter_to_sequence_parallel(x, tp_group)
+        else:
+            x = hidden_in
+        residual = None
+        aux_total = None
+        pos32 = position_ids.to(torch.int32) if position_ids.dtype != torch.int32 else position_ids
+        for layer in self.decoder.layers:
+            if self.recompute == "full" and torch.is_grad_enabled() and x.requires_grad:
+                x, residual, aux = checkpoint(layer, x, residual, pos32, cu_seqlens, max_seqlen, tp_group, sp,
+                                              use_reentrant=False)
+            else:
+                x, residual, aux = layer(x, residual, pos32, cu_seqlens, max_seqlen, tp_group, sp)
+            if aux is not None:
+                aux_total = aux if aux_total is None else aux_total + aux
+        if not self.post_process:
+            # carry the un-added residual forward as one tensor
+            return (x + residual if residual is not None else x), aux_total
+        h, _ = fused.rmsnorm(x, self.decoder.final_layernorm.weight, self.cfg.rms_norm_eps, residual)
+        if sp:
+            h = tp_ops.gather_from_sequence_parallel(h, tp_group)
+        if self.value_head:
+            return self.output_layer(h).squeeze(-1).float(), aux_total
+        return h, aux_total
+
+    def logits(self, hidden):
+        """Materialised (local-vocab) logits; only for small debugging / generation on CPU."""
+        return torch.nn.functional.linear(hidden, self.output_weight())
+
+
+def _padded_vocab(v: int, tp: int, multiple: int = 128) -> int:
+    m = multiple * tp
+    return (v + m - 1) // m * m
+
+
+def padded_vocab_size(cfg: ModelConfig, tp: int) -> int:
+    return _padded_vocab(cfg.vocab_size, tp)
+
+
+def _column_shard(full: torch.Tensor, name: str, model: "GPTModel", tp_rank: int) -> torch.Tensor:
+    """Slices this rank's rows out of a full column-parallel weight, honouring the fused layouts: QKV is
+    [Q | K | V] per rank and fc1 is [gate | up] per rank."""
+    tp = model.tp_size
+    cfg = model.cfg
+    if name.endswith("linear_qkv.weight") or name.endswith("linear_qkv.bias"):
+        D = cfg.head_dim
+        q, k, v = full.split([cfg.num_attention_heads * D, cfg.num_kv_heads * D, cfg.num_kv_heads * D], 0)
+        return torch.cat([q.chunk(tp, 0)[tp_rank], k.chunk(tp, 0)[tp_rank], v.chunk(tp, 0)[tp_rank]], 0)
+    if name.endswith("linear_fc1.weight") and "experts" not in name:
+        g, u = full.chunk(2, 0)
+        return torch.cat([g.chunk(tp, 0)[tp_rank], u.chunk(tp, 0)[tp_rank]], 0)
+    return full.chunk(tp, 0)[tp_rank]

@@ -1,0 +1,210 @@
+"""Mixture-of-experts layer: router (softmax top-k for Qwen3-MoE, sigmoid group-limited top-k with selection bias for
+DeepSeek-V3), capacity-free token dispatch into an expert-sorted buffer whose segments are padded to 128 rows, ragged
+grouped GEMMs on the tcgen05 kernel, weighted combine, optional shared expert, load-balancing / z losses, and router
+replay (recorded expert ids from the rollout engine override the top-k choice, as in
+gpatch_v4/training_backend/megatron_backend/router_replay_manager.py:15).
+
+Dispatch semantics follow ``DeepseekV4Experts._forward_eager`` (gpatch_v4/models/deepseek_v4/modeling_deepseek_v4.py:
+1221-1289): sort by destination rank, exchange counts, exchange tokens, sort by local expert, grouped MM, reverse.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from ..core import parallel_state as ps
+from ..ops import fused
+from ..ops.gemm import grouped_gemm, grouped_wgrad
+from .config import ModelConfig
+
+SEG = 128  # expert segments are padded to the GEMM tile height
+
+
+class RouterReplay:
+    """Per-step store of routed expert ids, keyed by layer index ([T, K] int64 each)."""
+    _store = {}
+    mode = "off"  # off | record | replay
+
+    @classmethod
+    def set(cls, mode, store=None):
+        cls.mode = mode
+        cls._store = store if store is not None else {}
+
+    @classmethod
+    def get(cls, layer):
+        return cls._store.get(layer)
+
+    @classmethod
+    def put(cls, layer, idx):
+        cls._store[layer] = idx
+
+
+class Router(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, device=None):
+        super().__init__()
+        self.cfg, self.layer_idx = cfg, layer_idx
+        self.weight = nn.Parameter(torch.empty(cfg.num_experts, cfg.hidden_size, dtype=torch.float32, device=device))
+        self.weight.tp_mode = "none"
+        self.weight.sequence_parallel = True
+        if cfg.moe_router_bias:
+            # selection-only bias updated outside autograd (aux-loss-free balancing)
+            self.register_buffer("expert_bias", torch.zeros(cfg.num_experts, dtype=torch.float32, device=device))
+        else:
+            self.expert_bias = None
+
+    def forward(self, x):
+        cfg = self.cfg
+        E, K = cfg.num_experts, cfg.moe_top_k
+        logits = torch.nn.functional.linear(x.float(), self.weight)  # [T, E]
+        replay = RouterReplay.get(self.layer_idx) if RouterReplay.mode == "replay" else None
+        if cfg.moe_router_type == "softmax":
+            probs = torch.softmax(logits, dim=-1)
+            if replay is not None:
+                idx = replay.to(x.device)
+                w = probs.gather(-1, idx)
+            else:
+                w, idx = torch.topk(probs, K, dim=-1)
+            if cfg.moe_norm_topk_prob:
+                w = w / w.sum(-1, keepdim=True).clamp_min(1e-20)
+            scores_for_aux = probs
+        else:
+            scores = torch.sigmoid(logits)
+            sel = scores + self.expert_bias if self.expert_bias is not None else scores
+            if replay is not None:
+                idx = replay.to(x.device)
+            else:
+                G = cfg.moe_n_group
+                if G > 1:
+                    grp = sel.view(-1, G, E // G).topk(2, dim=-1).values.sum(-1)  # [T, G]
+                    gidx = grp.topk(cfg.moe_topk_group, dim=-1).indices
+                    gmask = torch.zeros_like(grp).scatter_(1, gidx, 1.0)
+                    sel = sel.masked_fill(gmask[:, :, None].expand(-1, G, E // G).reshape(-1, E) == 0, float("-inf"))
+                idx = sel.topk(K, dim=-1).indices
+            w = scores.gather(-1, idx)
+            if cfg.moe_norm_topk_prob:
+                w = w / w.sum(-1, keepdim=True).clamp_min(1e-20)
+            w = w * cfg.moe_routed_scaling_factor
+            scores_for_aux = scores / scores.sum(-1, keepdim=True).clamp_min(1e-20)
+        if RouterReplay.mode == "record":
+            RouterReplay.put(self.layer_idx, idx.detach())
+        aux = None
+        if self.training and (cfg.moe_aux_loss_coef > 0 or cfg.moe_z_loss_coef > 0):
+            aux = x.new_zeros((), dtype=torch.float32)
+            if cfg.moe_aux_loss_coef > 0:
+                T = logits.shape[0]
+                f = torch.zeros(E, dtype=torch.float32, device=x.device)
+                f.scatter_add_(0, idx.reshape(-1), torch.ones(idx.numel(), dtype=torch.float32, device=x.device))
+                f = f * (E / (K * max(T, 1)))
+                P = scores_for_aux.mean(0)
+                aux = aux + cfg.moe_aux_loss_coef * (f * P).sum()
+            if cfg.moe_z_loss_coef > 0:
+                aux = aux + cfg.moe_z_loss_coef * torch.logsumexp(logits, -1).pow(2).mean()
+        return idx, w, aux
+
+
+def build_dispatch_plan(expert_ids: torch.Tensor, num_experts: int):
+    """expert_ids [N] (N = tokens * K, values in [0, E)) -> (dest_row [N], offsets [E+1] int32) for the padded
+    expert-sorted layout; no host synchronisation."""
+    N = expert_ids.numel()
+    counts = torch.bincount(expert_ids, minlength=num_experts)
+    padded = (counts + (SEG - 1)) // SEG * SEG
+    offsets = torch.zeros(num_experts + 1, dtype=torch.int64, device=expert_ids.device)
+    offsets[1:] = padded.cumsum(0)
+    starts = counts.cumsum(0) - counts
+    order = torch.argsort(expert_ids, stable=True)
+    e_sorted = expert_ids[order]
+    pos_in_e = torch.arange(N, device=expert_ids.device) - starts[e_sorted]
+    dest = torch.empty(N, dtype=torch.int64, device=expert_ids.device)
+    dest[order] = offsets[e_sorted] + pos_in_e
+    return dest, offsets.to(torch.int32)
+
+
+def padded_rows_bound(n_rows: int, num_experts: int) -> int:
+    return ((n_rows + num_experts * (SEG - 1)) + SEG - 1) // SEG * SEG
+
+
+class _GroupedLinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, offsets, main_grad):
+        ctx.save_for_backward(x, w, offsets)
+        ctx.main_grad = main_grad
+        return grouped_gemm(x, w, offsets)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, offsets = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = grouped_gemm(dy, w, offsets, b_mn=True) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            if ctx.main_grad is not None:
+                grouped_wgrad(dy, x, offsets, w.shape[0], out=ctx.main_grad, accumulate=True)
+            else:
+                dw = grouped_wgrad(dy, x, offsets, w.shape[0]).to(w.dtype)
+        return dx, dw, None, None
+
+
+def grouped_linear(x, w, offsets):
+    """``y[seg_g] = x[seg_g] @ w[g]^T`` with autograd; ``w`` [G, N, K]."""
+    mg = getattr(w, "main_grad", None) if w.requires_grad else None
+    return _GroupedLinearFn.apply(x, w, offsets, mg)
+
+
+class Experts(nn.Module):
+    def __init__(self, cfg: ModelConfig, num_local: int, device=None):
+        super().__init__()
+        dt = {"bfloat16": torch.bfloat16, "float32": torch.float32}[cfg.dtype]
+        F, H = cfg.moe_ffn_hidden_size, cfg.hidden_size
+        self.linear_fc1 = nn.Module()
+        self.linear_fc2 = nn.Module()
+        self.linear_fc1.weight = nn.Parameter(torch.empty(num_local, 2 * F, H, dtype=dt, device=device))
+        self.linear_fc2.weight = nn.Parameter(torch.empty(num_local, H, F, dtype=dt, device=device))
+        self.linear_fc1.weight.tp_mode = "expert"
+        self.linear_fc2.weight.tp_mode = "expert"
+        self.linear_fc1.weight.is_expert = True
+        self.linear_fc2.weight.is_expert = True
+
+    def forward(self, x_perm, offsets):
+        h = grouped_linear(x_perm, self.linear_fc1.weight, offsets)
+        h = fused.swiglu(h)
+        return grouped_linear(h, self.linear_fc2.weight, offsets)
+
+
+class MoELayer(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, tp_size: int, ep_size: int, device=None):
+        super().__init__()
+        self.cfg, self.layer_idx, self.ep_size = cfg, layer_idx, ep_size
+        assert cfg.num_experts % ep_size == 0
+        self.num_local = cfg.num_experts // ep_size
+        self.router = Router(cfg, layer_idx, device)
+        self.experts = Experts(cfg, self.num_local, device)
+        if cfg.moe_shared_expert_ffn:
+            from .gpt import MLP
+            # shared expert is replicated (not TP-sharded) because it runs on the sequence-parallel token shard
+            self.shared_experts = MLP(cfg, cfg.moe_shared_expert_ffn, 1, device)
+        else:
+            self.shared_experts = None
+
+    def forward(self, x):
+        cfg = self.cfg
+        T, H = x.shape
+        K = cfg.moe_top_k
+        idx, w, aux = self.router(x)
+        if self.ep_size > 1:
+            from ..parallel.ep import ep_moe_forward
+            y = ep_moe_forward(self, x, idx, w)
+        else:
+            flat_e = idx.reshape(-1)
+            dest, offsets = build_dispatch_plan(flat_e, cfg.num_experts)
+            rows = padded_rows_bound(T * K, cfg.num_experts)
+            x_perm = torch.zeros(rows, H, dtype=x.dtype, device=x.device)
+            token_of = torch.arange(T, device=x.device).repeat_interleave(K)
+            x_perm = x_perm.index_copy(0, dest, x[token_of])
+            y_perm = self.experts(x_perm, offsets)
+            y = (y_perm[dest].view(T, K, H) * w.to(x.dtype)[:, :, None]).sum(1)
+        if self.shared_experts is not None:
+            y = y + self.shared_experts(x)
+        return y, aux

@@ -189,3 +189,38 @@ def paged_decode(q, k_cache, v_cache, block_table, ctx_len, max_ctx, scale=None,
         p = torch.exp(s - l[:, None])
         out[b] = torch.einsum("hn,nhd->hd", p, vv).to(out.dtype)
     return out
+
+
+class _FlashAttnPackedFn(torch.autograd.Function):
+    """Attention over a packed ``[T, hq + 2*hk, D]`` buffer (the QKV GEMM output): one autograd input, so the
+    backward returns a single packed gradient instead of three strided view gradients."""
+
+    @staticmethod
+    def forward(ctx, qkv, sinks, cu, max_s, hq, hk, causal, window, scale):
+        q, k, v = qkv[:, :hq], qkv[:, hq:hq + hk], qkv[:, hq + hk:]
+        out, lse = _native_fwd(q, k, v, cu, cu, max_s, causal, window, sinks, scale)
+        ctx.save_for_backward(qkv, out, lse, sinks if sinks is not None else torch.empty(0), cu)
+        ctx.cfg = (max_s, hq, hk, causal, window, scale, sinks is not None)
+        return out
+
+    @staticmethod
+    def backward(ctx, do):
+        qkv, out, lse, sinks, cu = ctx.saved_tensors
+        max_s, hq, hk, causal, window, scale, has_sinks = ctx.cfg
+        q, k, v = qkv[:, :hq], qkv[:, hq:hq + hk], qkv[:, hq + hk:]
+        from .attention_bwd import attn_bwd
+        dq, dk, dv, ds = attn_bwd(do.contiguous(), q, k, v, out, lse, sinks if has_sinks else None, cu, cu, max_s,
+                                  max_s, causal, window, scale)
+        return torch.cat([dq, dk, dv], dim=1), ds, None, None, None, None, None, None, None
+
+
+def flash_attn_qkvpacked(qkv, hq, hk, cu_seqlens, max_seqlen, causal=True, window=0, sinks=None, scale=None):
+    """Self-attention where q, k, v are head ranges of one packed ``[T, hq + 2*hk, D]`` tensor."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(qkv.shape[-1])
+    q, k, v = qkv[:, :hq], qkv[:, hq:hq + hk], qkv[:, hq + hk:]
+    if _native_ok(q, k, v):
+        cu = cu_seqlens if cu_seqlens.dtype == torch.int32 else cu_seqlens.to(torch.int32)
+        if torch.is_grad_enabled() and qkv.requires_grad:
+            return _FlashAttnPackedFn.apply(qkv, sinks, cu, max_seqlen, hq, hk, causal, window, scale)
+        return _native_fwd(q, k, v, cu, cu, max_seqlen, causal, window, sinks, scale)[0]
+    return attn_varlen_ref(q, k, v, cu_seqlens, cu_seqlens, causal, window, sinks, scale)

@@ -27,6 +27,9 @@ inline EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+// Makes the device's primary context current on the calling thread (the driver entry points need one).
+inline void bind_primary_context() { cudaFree(nullptr); }
+
 // 2-D row-major tensor [rows, cols] of `elem_bytes`-wide elements with leading dimension `ld` (elements).
 // Box = [box_rows, box_cols]; 128-byte swizzle (box_cols * elem_bytes must be <= 128 when swizzled).
 inline int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols,
@@ -40,9 +43,21 @@ inline int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint
   CUtensorMapDataType dt = elem_bytes == 2   ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                            : elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                              : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
-  CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = CUDA_SUCCESS;
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+           swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_ERROR_INVALID_CONTEXT) break;
+    bind_primary_context();  // a thread that has made no runtime call yet (e.g. an autograd worker)
+  }
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr,
+            "[gcore_b200] cuTensorMapEncodeTiled(2d) failed: CUresult=%d base=%p elem=%d rows=%llu cols=%llu ld=%llu "
+            "box=[%u,%u]\n",
+            static_cast<int>(r), base, elem_bytes, (unsigned long long)rows, (unsigned long long)cols,
+            (unsigned long long)ld, box_rows, box_cols);
+  }
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
@@ -59,9 +74,14 @@ inline int make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, uint
   CUtensorMapDataType dt = elem_bytes == 2   ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                            : elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                              : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
-  CUresult r = fn(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = CUDA_SUCCESS;
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    r = fn(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+           swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_ERROR_INVALID_CONTEXT) break;
+    bind_primary_context();
+  }
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 

@@ -1,0 +1,370 @@
+"""Contiguous parameter / main-gradient buffers with bucketed gradient reduction, and the ZeRO-1 distributed
+optimizer on top of them (sharded fp32 master weights + Adam moments, bf16 parameter all-gather).
+
+Behavioural contract = Megatron-Core's ``DistributedDataParallel`` + ``DistributedOptimizer`` as configured by the
+reference (gpatch_v4/training_backend/megatron_backend/mixin.py:311-348, optimizer.py:53-169): fp32 gradient
+accumulation and reduction, bucket size ``max(40e6, 1e6 * dp_size)`` elements, reduce-scatter when the optimizer is
+distributed (all-reduce otherwise), gradient averaging over DP x CP, global-norm clipping across model-parallel
+ranks with replicated parameters counted once, linear / cosine / WSD learning-rate schedules with warm-up.
+
+Dense parameters reduce over the DP x CP group; expert parameters over the expert-data-parallel group.
+The update itself is one fused kernel per shard (``ops.optim.adam_step``): unscale + clip + AdamW + bf16 write.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..core import parallel_state as ps
+from ..ops import optim as optim_ops
+
+
+def _group_size(g):
+    return dist.get_world_size(g) if (g is not None and dist.is_initialized()) else 1
+
+
+def _group_rank(g):
+    return dist.get_rank(g) if (g is not None and dist.is_initialized()) else 0
+
+
+@dataclass
+class Bucket:
+    start: int
+    end: int
+    params: List[torch.nn.Parameter]
+    pending: int = 0
+    handle: Optional[object] = None
+
+
+class ParamAndGradBuffer:
+    """All parameters of one reduction domain in one flat bf16 buffer and their main grads in one flat fp32 buffer."""
+
+    def __init__(self, params: List[torch.nn.Parameter], names: List[str], group, grad_dtype=torch.float32,
+                 bucket_size: Optional[int] = None, use_distributed_optimizer: bool = True, alloc_grads: bool = True):
+        self.group = group
+        self.dp = _group_size(group)
+        self.dp_rank = _group_rank(group)
+        self.params, self.names = params, names
+        self.use_distributed_optimizer = use_distributed_optimizer
+        self.grad_dtype = grad_dtype
+        dev = params[0].device
+        dt = params[0].dtype
+        if bucket_size is None:
+            bucket_size = max(40_000_000, 1_000_000 * self.dp)
+        align = 128 * self.dp
+        # layout: parameters in reverse registration order so buckets fill in roughly backward order
+        self.offsets: Dict[int, int] = {}
+        self.buckets: List[Bucket] = []
+        off, bstart, bparams = 0, 0, []
+        for p in reversed(params):
+            self.offsets[id(p)] = off
+            off += p.numel()
+            bparams.append(p)
+            if off - bstart >= bucket_size:
+                off = (off + align - 1) // align * align
+                self.buckets.append(Bucket(bstart, off, bparams))
+                bstart, bparams = off, []
+        if bparams:
+            off = (off + align - 1) // align * align
+            self.buckets.append(Bucket(bstart, off, bparams))
+        self.numel = off
+        self.param_data = torch.zeros(self.numel, dtype=dt, device=dev)
+        self.grad_data = None
+        self.param_to_bucket: Dict[int, Bucket] = {}
+        for b in self.buckets:
+            for p in b.params:
+                self.param_to_bucket[id(p)] = b
+        with torch.no_grad():
+            for p in params:
+                o = self.offsets[id(p)]
+                view = self.param_data[o:o + p.numel()].view(p.shape)
+                view.copy_(p.data)
+                p.data = view
+        if alloc_grads:
+            self.allocate_grads()
+
+    # ---- gradient storage can be released between training phases (colocated rollout needs the memory)
+    def allocate_grads(self):
+        if self.grad_data is None:
+            self.grad_data = torch.zeros(self.numel, dtype=self.grad_dtype, device=self.param_data.device)
+        for p in self.params:
+            o = self.offsets[id(p)]
+            p.main_grad = self.grad_data[o:o + p.numel()].view(p.shape) if p.requires_grad else None
+
+    def release_grads(self):
+        self.grad_data = None
+        for p in self.params:
+            p.main_grad = None
+
+    def zero_grad(self):
+        if self.grad_data is not None:
+            self.grad_data.zero_()
+        for p in self.params:
+            p.grad = None
+
+    def shard_range(self, bucket: Bucket):
+        n = (bucket.end - bucket.start) // self.dp
+        s = bucket.start + self.dp_rank * n
+        return s, s + n
+
+    def reduce_bucket(self, bucket: Bucket, scale: float, async_op: bool = False):
+        g = self.grad_data[bucket.start:bucket.end]
+        if scale != 1.0:
+            g.mul_(scale)
+        if self.dp == 1:
+            return None
+        if self.use_distributed_optimizer:
+            s, e = self.shard_range(bucket)
+            return dist.reduce_scatter_tensor(self.grad_data[s:e], g, group=self.group, async_op=async_op)
+        return dist.all_reduce(g, group=self.group, async_op=async_op)
+
+    def gather_params(self, bucket: Bucket, async_op: bool = False):
+        if self.dp == 1 or not self.use_distributed_optimizer:
+            return None
+        s, e = self.shard_range(bucket)
+        return dist.all_gather_into_tensor(self.param_data[bucket.start:bucket.end], self.param_data[s:e],
+                                           group=self.group, async_op=async_op)
+
+
+class DistributedDataParallel:
+    """Owns the buffers of a model, routes autograd gradients into ``main_grad`` and runs the bucketed reduction."""
+
+    def __init__(self, model: torch.nn.Module, grad_reduce_in_fp32: bool = True, bucket_size: Optional[int] = None,
+                 use_distributed_optimizer: bool = True, overlap_grad_reduce: bool = False,
+                 average_in_collective: bool = True, alloc_grads: bool = True):
+        self.model = model
+        self.overlap = overlap_grad_reduce
+        dense_p, dense_n, exp_p, exp_n = [], [], [], []
+        for n, p in model.named_parameters():
+            if not p.requires_grad:
+                continue  # frozen weights (LoRA base, frozen towers) keep their own storage and get no grad / state
+            if getattr(p, "is_expert", False):
+                exp_p.append(p), exp_n.append(n)
+            else:
+                dense_p.append(p), dense_n.append(n)
+        gdt = torch.float32 if grad_reduce_in_fp32 else None
+        self.buffers: List[ParamAndGradBuffer] = []
+        by_dtype: Dict = {}
+        for plist, nlist, group in ((dense_p, dense_n, ps.get_data_parallel_group(with_context_parallel=True)),
+                                    (exp_p, exp_n, ps.get_expert_data_parallel_group())):
+            # one buffer per (domain, dtype): fp32 router weights do not share storage with bf16 weights
+            split: Dict = {}
+            for p, n in zip(plist, nlist):
+                key = (p.dtype, p.dim() >= 2)  # biases and norm gains take no weight decay
+                split.setdefault(key, ([], []))
+                split[key][0].append(p)
+                split[key][1].append(n)
+            for (dt, decays), (pl, nl) in split.items():
+                buf = ParamAndGradBuffer(pl, nl, group, gdt or dt, bucket_size, use_distributed_optimizer,
+                                         alloc_grads)
+                buf.weight_decay_mult = 1.0 if decays else 0.0
+                self.buffers.append(buf)
+        self._hooks = []
+        for buf in self.buffers:
+            for p in buf.params:
+                if p.requires_grad:
+                    self._hooks.append(p.register_post_accumulate_grad_hook(self._make_hook(buf, p)))
+        self.grad_scale_extra = 1.0
+
+    def _make_hook(self, buf: ParamAndGradBuffer, p):
+        def hook(param):
+            if param.grad is not None and param.main_grad is not None:
+                param.main_grad.add_(param.grad.to(param.main_grad.dtype))
+            param.grad = None
+        return hook
+
+    def zero_grad_buffer(self):
+        for b in self.buffers:
+            b.zero_grad()
+
+    def allocate_grads(self):
+        for b in self.buffers:
+            b.allocate_grads()
+
+    def release_grads(self):
+        for b in self.buffers:
+            b.release_grads()
+
+    def finish_grad_sync(self, extra_scale: float = 1.0):
+        """Averages over the reduction group (and applies ``extra_scale``, e.g. 1/num_tokens for per-token losses
+        summed over micro-batches) and reduces every bucket."""
+        tp_group = ps.get_tensor_model_parallel_group()
+        if ps.get_tensor_model_parallel_world_size() > 1 and getattr(self.model, "sequence_parallel", False):
+            # gains / router weights that act on sequence-parallel activations see only this rank's tokens
+            sp_grads = [p.main_grad for buf in self.buffers for p in buf.params
+                        if getattr(p, "sequence_parallel", False) and p.main_grad is not None]
+            if sp_grads:
+                flat = torch.cat([g.reshape(-1) for g in sp_grads])
+                dist.all_reduce(flat, group=tp_group)
+                o = 0
+                for g in sp_grads:
+                    g.copy_(flat[o:o + g.numel()].view_as(g))
+                    o += g.numel()
+        handles = []
+        for buf in self.buffers:
+            scale = extra_scale / buf.dp
+            for bucket in buf.buckets:
+                h = buf.reduce_bucket(bucket, scale, async_op=True)
+                if h is not None:
+                    handles.append(h)
+        for h in handles:
+            h.wait()
+
+    def parameters(self):
+        return self.model.parameters()
+
+    def __call__(self, *a, **kw):
+        return self.model(*a, **kw)
+
+
+def lr_at_step(cfg, step: int, total_steps: Optional[int]) -> float:
+    """``OptimizerParamScheduler`` semantics: linear warm-up from ``lr_warmup_init`` then constant / linear / cosine /
+    inverse-square-root / WSD decay to ``min_lr`` over ``lr_decay_steps``."""
+    warm = cfg.lr_warmup_steps
+    if cfg.lr_warmup_step_frac and total_steps:
+        warm = int(cfg.lr_warmup_step_frac * total_steps)
+    if warm > 0 and step <= warm:
+        return cfg.lr_warmup_init + (cfg.lr - cfg.lr_warmup_init) * step / warm
+    decay_steps = cfg.lr_decay_steps or total_steps
+    if cfg.lr_decay_style == "constant" or not decay_steps:
+        return cfg.lr
+    if step > decay_steps:
+        return cfg.min_lr
+    if cfg.lr_decay_style == "inverse-square-root":
+        return max(cfg.min_lr, cfg.lr * math.sqrt(max(warm, 1)) / math.sqrt(max(step, 1)))
+    frac = (step - warm) / max(decay_steps - warm, 1)
+    frac = min(max(frac, 0.0), 1.0)
+    if cfg.lr_decay_style == "linear":
+        coeff = 1.0 - frac
+    elif cfg.lr_decay_style == "cosine":
+        coeff = 0.5 * (math.cos(math.pi * frac) + 1.0)
+    elif cfg.lr_decay_style == "WSD":
+        wsd = cfg.lr_wsd_decay_steps or 0
+        anneal_start = decay_steps - wsd
+        if step <= anneal_start:
+            coeff = 1.0
+        else:
+            f = (step - anneal_start) / max(wsd, 1)
+            coeff = {"linear": 1 - f, "cosine": 0.5 * (math.cos(math.pi * f) + 1), "exponential": 2 ** (-f * 10)
+                     if False else (0.5 ** (f * 10))}.get(cfg.lr_wsd_decay_style, 1 - f)
+    else:
+        coeff = 1.0
+    return cfg.min_lr + coeff * (cfg.lr - cfg.min_lr)
+
+
+class DistributedOptimizer:
+    """AdamW with state sharded over the buffer's reduction group (ZeRO-1)."""
+
+    def __init__(self, ddp: DistributedDataParallel, cfg, total_steps: Optional[int] = None):
+        self.ddp, self.cfg, self.total_steps = ddp, cfg, total_steps
+        self.step_count = 0
+        self.shards = []  # per (buffer, bucket): dict(master, m, v, range)
+        for buf in ddp.buffers:
+            for bucket in buf.buckets:
+                s, e = buf.shard_range(bucket) if buf.use_distributed_optimizer else (bucket.start, bucket.end)
+                master = buf.param_data[s:e].float()
+                self.shards.append(dict(buf=buf, bucket=bucket, s=s, e=e, master=master,
+                                        m=torch.zeros_like(master), v=torch.zeros_like(master)))
+        self._wd_mask_cache = None
+        self.last_grad_norm = None
+        self.offloaded = False
+
+    # ------------------------------------------------------------------ grad norm / clip
+    def _local_sumsq(self) -> torch.Tensor:
+        """Sum of squares of this rank's gradient shards, with parameters replicated across TP counted on TP rank 0
+        only (their shard values are identical on every TP rank)."""
+        dev = self.shards[0]["master"].device
+        total = torch.zeros(1, dtype=torch.float32, device=dev)
+        tp_rank = ps.get_tensor_model_parallel_rank()
+        for sh in self.shards:
+            buf, s, e = sh["buf"], sh["s"], sh["e"]
+            g = buf.grad_data[s:e]
+            if tp_rank == 0 or ps.get_tensor_model_parallel_world_size() == 1:
+                optim_ops.sumsq(g, total)
+            else:
+                # subtract nothing here; replicated params are masked below
+                for p in sh["bucket"].params:
+                    if getattr(p, "tp_mode", "none") in ("column", "row", "expert"):
+                        o = buf.offsets[id(p)]
+                        lo, hi = max(o, s), min(o + p.numel(), e)
+                        if hi > lo:
+                            optim_ops.sumsq(buf.grad_data[lo:hi], total)
+        return total
+
+    def grad_norm(self) -> torch.Tensor:
+        total = self._local_sumsq()
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            # shards partition the DP x CP group, model-parallel ranks hold different parameters: sum over everyone
+            dist.all_reduce(total)
+        return total.sqrt()
+
+    # ------------------------------------------------------------------ step
+    def step(self, lr: Optional[float] = None):
+        cfg = self.cfg
+        self.step_count += 1
+        if lr is None:
+            lr = lr_at_step(cfg, self.step_count, self.total_steps)
+        norm = self.grad_norm()
+        self.last_grad_norm = norm
+        clip = None
+        if cfg.max_grad_norm and cfg.max_grad_norm > 0:
+            clip = torch.clamp(cfg.max_grad_norm / (norm + 1e-6), max=1.0)
+        for sh in self.shards:
+            buf, s, e = sh["buf"], sh["s"], sh["e"]
+            optim_ops.adam_step(sh["master"], sh["m"], sh["v"], buf.grad_data[s:e], buf.param_data[s:e], lr=lr,
+                                beta1=cfg.adam_beta1, beta2=cfg.adam_beta2, eps=cfg.adam_eps,
+                                weight_decay=cfg.weight_decay * getattr(buf, "weight_decay_mult", 1.0),
+                                step=self.step_count, grad_scale=clip)
+        handles = []
+        for sh in self.shards:
+            h = sh["buf"].gather_params(sh["bucket"], async_op=True)
+            if h is not None:
+                handles.append(h)
+        for h in handles:
+            h.wait()
+        return float(lr)
+
+    def reload_master_from_params(self):
+        for sh in self.shards:
+            sh["master"].copy_(sh["buf"].param_data[sh["s"]:sh["e"]].float())
+
+    # ------------------------------------------------------------------ host offload (time-sharing with rollout)
+    def offload(self):
+        """Moves master weights and moments to pinned host memory (CPU swap of the reference:
+        gpatch_v4/training_backend/megatron_backend/mcore_swap_impl.py:24-207)."""
+        if self.offloaded:
+            return
+        for sh in self.shards:
+            for k in ("master", "m", "v"):
+                t = sh[k]
+                host = torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=t.is_cuda)
+                host.copy_(t, non_blocking=True)
+                sh[k + "_dev"] = t.device
+                sh[k] = host
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+            torch.cuda.empty_cache()
+        self.offloaded = True
+
+    def onload(self):
+        if not self.offloaded:
+            return
+        for sh in self.shards:
+            for k in ("master", "m", "v"):
+                sh[k] = sh[k].to(sh.pop(k + "_dev"), non_blocking=True)
+        self.offloaded = False
+
+    # ------------------------------------------------------------------ state
+    def state_dict(self):
+        return {"step": self.step_count,
+                "shards": [dict(s=sh["s"], e=sh["e"], master=sh["master"], m=sh["m"], v=sh["v"]) for sh in self.shards]}
+
+    def load_state_dict(self, sd):
+        self.step_count = sd["step"]
+        for sh, src in zip(self.shards, sd["shards"]):
+            for k in ("master", "m", "v"):
+                sh[k].copy_(src[k])

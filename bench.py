@@ -1,0 +1,254 @@
+"""Headline benchmark: synchronous GRPO step on a Qwen2.5-7B-shaped dense decoder, bf16, random-init weights,
+synthetic prompts and rule reward (the benchmark recipe's config 2), colocated trainer + rollout engine.
+
+    python bench.py --gpus N --steps K --warmup W            (N = 1)
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W               (N > 1)
+
+Weak scaling: 8 prompts x 8 samples per GPU (64 x 8 at N = 8), prompts of 256 tokens, responses up to 1024 tokens,
+trainer TP = min(2, N), DP = N / TP, rollout engine with the same TP sharing the trainer's parameter storage.
+The metric is whole-job (prompt + response) tokens pushed through one GRPO step per second of step time:
+rollout, reward, previous- and reference-policy log-probs, advantages, policy update (with optimizer step) and the
+weight hand-over to the rollout engine, all inside the timed region.
+
+Prints ONE JSON line on rank 0.  ``--impl reference`` reports whether the unmodified reference can run here.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def reference_arm(args):
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    why = None
+    if not os.path.isdir(os.path.join(ref, "gpatch_v4")):
+        why = "baseline/_ref is empty: the offline install of the reference has not been run on this box"
+    else:
+        sys.path.insert(0, ref)
+        try:
+            import importlib
+            importlib.import_module("gpatch_v4.entry.train_lm_grpo")
+        except Exception as e:  # noqa: BLE001
+            why = (f"reference installs (--no-deps) but its GRPO entry point cannot import: {type(e).__name__}: {e}; "
+                   "hydra, omegaconf, ray, megatron.core, mbridge, transformer_engine and sglang are not in the "
+                   "image and cannot be fetched offline")
+    if why is None:
+        why = "reference imported, but its launch needs a Ray cluster and Megatron-LM checkouts that are absent here"
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why.replace("\n", " ")}))
+    return 0
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.idx)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:  # noqa: BLE001
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:  # noqa: BLE001
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_config(args, world):
+    from gcore_b200.configs.base import from_dict
+    from gcore_b200.configs.config import RlConfig
+    tp = 1 if world == 1 else 2
+    dp = world // tp
+    prompts_per_dp = args.prompts_per_gpu * tp
+    n = args.samples
+    cfg = from_dict(RlConfig, {
+        "training": {"rollout_gbs": prompts_per_dp * dp, "sampling_repeat_n": n, "train_gbs": prompts_per_dp * dp * n,
+                     "train_mbs": 1, "seed": 1234, "total_ppo_step": 1000},
+        "policy": {"model_arch": args.model, "recompute": args.recompute, "share_rollout_weights": True,
+                   "dist_config": {"tensor_model_parallel_size": tp, "sequence_parallel": tp > 1},
+                   "dynamic_mbs_target_seqlen": args.mb_tokens},
+        "optimizer": {"lr": 1e-6, "lr_decay_style": "constant", "weight_decay": 0.01, "max_grad_norm": 1.0},
+        "sampler": {"infer_engine_configs": [{"generate_max_tokens": args.max_response, "temperature": 1.0,
+                                               "max_model_len": args.prompt_len + args.max_response,
+                                               "kv_block_size": 16, "seed": 42,
+                                               "dist_config": {"tensor_model_parallel_size": tp}}]},
+        "data": {"max_prompt_length": args.prompt_len},
+        "ppo": {"ppo_ratio_eps": 0.2, "grpo_kl_loss_beta": 0.001, "advantage_type": "grpo", "loss_func": "grpo"},
+    })
+    return cfg, tp, dp, prompts_per_dp
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="native", choices=["native", "reference", "nccl_eager"])
+    ap.add_argument("--model", default="qwen2.5-7b")
+    ap.add_argument("--layers", type=int, default=None, help="debug only: truncating the model invalidates the number")
+    ap.add_argument("--prompts-per-gpu", type=int, default=8)
+    ap.add_argument("--samples", type=int, default=8)
+    ap.add_argument("--prompt-len", type=int, default=256)
+    ap.add_argument("--max-response", type=int, default=1024)
+    ap.add_argument("--mb-tokens", type=int, default=8192)
+    ap.add_argument("--recompute", default="full")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+    from gcore_b200.core import parallel_state as ps
+    from gcore_b200.models.config import get_preset
+    from gcore_b200.ops import _lib
+    from gcore_b200.trainer.grpo_trainer import GrpoTrainer, synthetic_reward
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run"
+    torch.cuda.set_device(local)
+    if world > 1:
+        ps.init_distributed("nccl")
+    cfg, tp, dp, prompts_per_dp = build_config(args, world)
+    if world > 1:
+        ps.initialize_model_parallel(tp=tp)
+    if args.impl == "nccl_eager":
+        cfg.training.training_backend = "nccl_eager"
+        os.environ["GCORE_B200_FORCE_EAGER"] = "1"
+    over = {"num_layers": args.layers} if args.layers else {}
+    mcfg = get_preset(args.model, **over)
+    trainer = GrpoTrainer(cfg, model_cfg=mcfg, reward_fn=synthetic_reward).setup()
+    dp_rank = ps.get_data_parallel_rank()
+
+    # synthetic prompts live in pinned host memory; every step copies its prompts to the device inside the timed region
+    g = torch.Generator().manual_seed(1000 + dp_rank)
+    total_steps = args.warmup + args.steps
+    host_prompts = torch.randint(100, 150000, (total_steps, prompts_per_dp, args.prompt_len), generator=g,
+                                 dtype=torch.int64).pin_memory()
+    from gcore_b200.utils import io_counters
+
+    def run_step(i):
+        # the engine uploads the prompt tokens (pinned host -> device) when it prefills them
+        return trainer.step(host_prompts[i])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        m = run_step(i)
+        if rank == 0:
+            print(f"[warmup {i}] step {m['time_perf/step']:.2f}s rollout {m['time_perf/rollout']:.2f}s "
+                  f"logps {m['time_perf/compute_logps']:.2f}s train {m['time_perf/train_step']:.2f}s "
+                  f"tokens {m['rollout-metrics/total_tokens']:.0f}", file=sys.stderr, flush=True)
+    _lib.check_device_errors()
+    io_counters.reset()
+    launches0 = trainer_launches(trainer)
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    ev0.record()
+    tokens = 0.0
+    phase = {}
+    for i in range(args.warmup, total_steps):
+        m = run_step(i)
+        tokens += m["rollout-metrics/total_tokens"]
+        for k, v in m.items():
+            if k.startswith("time_perf/"):
+                phase[k] = phase.get(k, 0.0) + v / args.steps
+    ev1.record()
+    barrier()
+    wall = time.perf_counter() - t0
+    dev_s = ev0.elapsed_time(ev1) / 1e3
+    clocks = sampler.stop()
+    _lib.check_device_errors()
+    t = torch.tensor([dev_s, wall], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_s, wall = float(t[0]), float(t[1])
+    launches = trainer_launches(trainer) - launches0
+    h2d, d2h = io_counters.get()
+    if rank == 0:
+        value = tokens / dev_s
+        out = {
+            "metric": "grpo_rollout_plus_train_tokens_per_s", "value": round(value, 1), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_s / args.steps * 1e3, 1),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "impl": args.impl,
+            "config": {"model": args.model + (f"-{args.layers}layers-DEBUG" if args.layers else ""),
+                       "global_batch": int(cfg.training.rollout_gbs * args.samples),
+                       "seq_len": args.prompt_len + args.max_response,
+                       "parallelism": f"tp{tp}dp{dp}", "prompts": int(cfg.training.rollout_gbs),
+                       "samples_per_prompt": args.samples, "weights": "random-init",
+                       "resync": "zero-copy shared parameter storage (trainer and rollout engine, same TP layout)",
+                       "l2": "inputs (15 GB of weights per pass) are larger than L2", "recompute": args.recompute},
+            "clocks": clocks,
+            "e2e": {"value": round(tokens / wall, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d / args.steps),
+                    "d2h_bytes_per_step": int(d2h / args.steps)},
+            "gpu_launches": int(launches),
+            "phases_s": {k.split("/")[1]: round(v, 3) for k, v in phase.items()},
+            "resync_ms": round(phase.get("time_perf/update_weights", 0.0) * 1e3, 3),
+            "reward_mean": round(m["rollout-rewards/mean"], 4),
+        }
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def trainer_launches(trainer) -> int:
+    from gcore_b200.ops import attention, fused, gemm, optim, rl, vocab
+    eager = sum(sum(m.LAUNCHES.values()) for m in (attention, fused, gemm, optim, rl, vocab))
+    eng = trainer.engine
+    return eager + eng.stats["graph_replays"] * getattr(eng, "graph_launches", 0)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -28,6 +28,7 @@ from ..models.lora import apply_lora, verify_lora_weight_consistency
 from ..ops import _lib
 from ..ops.rl import grpo_loss as fused_grpo_loss
 from ..ops.vocab import linear_logprob_entropy
+from ..utils import io_counters
 from ..parallel.distributed_optimizer import DistributedDataParallel, DistributedOptimizer, lr_at_step
 
 
@@ -146,7 +147,10 @@ class TrainingEngine:
         pad = max(self._tp_pad(), 1)
         if self.device.type == "cuda":
             pad = pad * 8 if pad > 1 else 8
-        return pack_samples(samples, idx, keys, pad_to_multiple=pad, pin=self.device.type == "cuda").to(self.device)
+        mb = pack_samples(samples, idx, keys, pad_to_multiple=pad, pin=self.device.type == "cuda")
+        io_counters.add_h2d(io_counters.tensor_bytes(mb.tokens, mb.position_ids, mb.cu_seqlens, mb.targets, mb.loss_mask,
+                                                     mb.seq_ids, *mb.fields.values()))
+        return mb.to(self.device)
 
     def _microbatches(self, samples, forward_only=False):
         lens = [len(s["tokens"]) for s in samples]
@@ -172,6 +176,7 @@ class TrainingEngine:
                 hidden, _ = self._hidden(model, mb)
                 lp, ent = self._logprob_entropy(model, hidden, mb.targets, with_entropy)
                 lp_c, ent_c = lp.float().cpu(), ent.float().cpu()
+                io_counters.add_d2h(io_counters.tensor_bytes(lp_c, ent_c))
                 cu = mb.cu_seqlens.tolist()
                 for j, i in enumerate(idx):
                     s, e = cu[j], cu[j + 1]
@@ -229,6 +234,7 @@ class TrainingEngine:
         if g is not None and dist.get_world_size(g) > 1:
             dist.all_reduce(flat, group=g)
         flat = flat.cpu()
+        io_counters.add_d2h(io_counters.tensor_bytes(flat))
         return {k: float(flat[i, 0] / flat[i, 1].clamp_min(1e-12)) for i, k in enumerate(keys)}
 
     # ------------------------------------------------------------------ SFT

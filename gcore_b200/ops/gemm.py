@@ -42,7 +42,7 @@ def _pick_bn(n: int) -> int:
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: torch.Tensor | None = None,
-         out_dtype: torch.dtype = torch.bfloat16, bias: torch.Tensor | None = None, bias_along_m: bool = False,
+         out_dtype: torch.dtype | None = None, bias: torch.Tensor | None = None, bias_along_m: bool = False,
          alpha: float = 1.0, accumulate: bool = False, transposed: bool = False, bn: int | None = None,
          ksplit: int = 1) -> torch.Tensor:
     """``C = alpha * A @ B^T (+ bias) (+ C)``; see the module docstring for the layout flags.
@@ -61,7 +61,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     assert K == Kb, f"contraction mismatch {K} vs {Kb}"
     if out is None:
         assert not accumulate
-        out = torch.empty((N, M) if transposed else (M, N), dtype=out_dtype, device=a.device)
+        out = torch.empty((N, M) if transposed else (M, N), dtype=out_dtype or a.dtype, device=a.device)
     if not _lib.use_native(a):
         af = (a.t() if a_mn else a).float()
         bf = (b.t() if b_mn else b).float()
@@ -169,7 +169,7 @@ def grouped_wgrad(dy: torch.Tensor, x: torch.Tensor, offsets: torch.Tensor, num_
 
 # ----------------------------------------------------------------------------------------------------------
 def linear_forward(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
-                   out: torch.Tensor | None = None, out_dtype=torch.bfloat16) -> torch.Tensor:
+                   out: torch.Tensor | None = None, out_dtype=None) -> torch.Tensor:
     """``y[T,N] = x[T,K] @ w[N,K]^T + bias``.  Few tokens (decode) run swap-AB + split-K so the weight streams
     from HBM exactly once with every SM busy."""
     T, K = x.shape

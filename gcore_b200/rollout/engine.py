@@ -1,0 +1,632 @@
+"""Continuous-batching rollout decoder with a paged KV cache.
+
+Replaces the vLLM / SGLang engines the reference wraps (``InferEngine``, gpatch_v4/generation_backend/
+infer_engine.py:158-768) and keeps its verbs: ``generate``, ``abort_all_requests``, ``flush_cache``, ``sleep`` /
+``wake_up`` (``weights`` / ``kv_cache`` tags), ``update_weights``, ``get_load``.
+
+B200-first choices:
+  * The engine lives in the trainer's process and, when the tensor-parallel layouts match, reads the trainer's bf16
+    parameter buffer directly: a weight "resync" is a pointer hand-over, not a copy.  Other layouts go through
+    ``rollout/weight_sync.py``.
+  * A decode step is one CUDA graph: embedding, per layer (RMSNorm, swap-AB split-K tcgen05 GEMMs, RoPE-fused cache
+    append, split-KV paged attention, SwiGLU), vocabulary GEMM, Gumbel-max sampling, and the state advance
+    (positions, context lengths, slot computation, output ring write), so the host only replays it.
+  * The host synchronises every ``sync_interval`` steps: it then reads the tokens produced, retires finished
+    requests, admits waiting ones (prefill) and tops up block tables for the next interval.  Requests that hit EOS
+    inside an interval produce a few discarded tokens instead of forcing a sync per token.
+  * ``n`` samples per prompt share the prompt's KV blocks (copy-on-write of the last partial block).
+  * Tensor-parallel ranks run the same host logic on the same inputs (SPMD) and agree on sampled tokens because the
+    sampler's random stream depends only on (seed, step, token id).
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from ..core import parallel_state as ps
+from ..models.config import ModelConfig
+from ..ops import _lib, fused
+from ..ops.attention import flash_attn_varlen, kv_append_rope, paged_decode
+from ..ops.gemm import linear_forward
+from ..ops.vocab import apply_top_k_top_p, sample
+from ..utils import io_counters
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 1.0
+    top_k: int = -1
+    top_p: float = 1.0
+    min_p: float = 0.0
+    max_new_tokens: int = 128
+    seed: int = 42
+    stop_token_ids: Sequence[int] = ()
+    greedy: bool = False
+
+
+@dataclass
+class Request:
+    rid: int
+    prompt: List[int]
+    params: SamplingParams
+    seed: int
+    out_tokens: List[int] = field(default_factory=list)
+    out_logprobs: List[float] = field(default_factory=list)
+    finished: bool = False
+    finish_reason: str = ""
+    parent: Optional[int] = None
+    slot: int = -1
+    routed_experts: Optional[list] = None
+
+
+class _Sched:
+    """ctypes face of the C++ scheduler / block manager (``runtime/csrc/scheduler.cpp``)."""
+
+    def __init__(self, num_blocks, block_size, max_running, max_prefill_tokens):
+        self.lib = _lib.runtime()
+        L = self.lib
+        L.gkrt_sched_create.restype = ctypes.c_void_p
+        L.gkrt_sched_create.argtypes = [ctypes.c_int] * 4
+        for fn, args, res in (
+            ("gkrt_sched_destroy", [ctypes.c_void_p], None),
+            ("gkrt_sched_add", [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_int], ctypes.c_int),
+            ("gkrt_sched_fork", [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,
+                                 ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)], ctypes.c_int),
+            ("gkrt_sched_step", [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64), ctypes.c_int,
+                                 ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int64), ctypes.c_int,
+                                 ctypes.POINTER(ctypes.c_int)], ctypes.c_int),
+            ("gkrt_sched_commit", [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int], None),
+            ("gkrt_sched_finish", [ctypes.c_void_p, ctypes.c_int64], None),
+            ("gkrt_sched_abort_all", [ctypes.c_void_p], None),
+            ("gkrt_sched_reserve", [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int], ctypes.c_int),
+            ("gkrt_sched_advance", [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int], None),
+            ("gkrt_sched_batch_tables", [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64), ctypes.c_int,
+                                         ctypes.POINTER(ctypes.c_int), ctypes.c_int, ctypes.POINTER(ctypes.c_int)],
+             ctypes.c_int),
+            ("gkrt_sched_stats", [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64)], None),
+        ):
+            f = getattr(L, fn)
+            f.argtypes, f.restype = args, res
+        self.h = L.gkrt_sched_create(num_blocks, block_size, max_running, max_prefill_tokens)
+
+    def __del__(self):
+        try:
+            self.lib.gkrt_sched_destroy(self.h)
+        except Exception:
+            pass
+
+    def add(self, rid, prompt_len, max_new):
+        return self.lib.gkrt_sched_add(self.h, rid, prompt_len, max_new)
+
+    def fork(self, parent, child, max_new):
+        a, b = ctypes.c_int(), ctypes.c_int()
+        rc = self.lib.gkrt_sched_fork(self.h, parent, child, max_new, ctypes.byref(a), ctypes.byref(b))
+        return rc, a.value, b.value
+
+    def step(self, cap_prefill, cap_decode):
+        pre = (ctypes.c_int64 * max(cap_prefill, 1))()
+        dec = (ctypes.c_int64 * max(cap_decode, 1))()
+        npre, ndec = ctypes.c_int(), ctypes.c_int()
+        self.lib.gkrt_sched_step(self.h, pre, cap_prefill, ctypes.byref(npre), dec, cap_decode, ctypes.byref(ndec))
+        return list(pre[:npre.value]), list(dec[:ndec.value])
+
+    def commit(self, rid, is_prefill):
+        self.lib.gkrt_sched_commit(self.h, rid, int(is_prefill))
+
+    def reserve(self, rid, tokens):
+        return self.lib.gkrt_sched_reserve(self.h, rid, tokens)
+
+    def advance(self, rid, tokens):
+        self.lib.gkrt_sched_advance(self.h, rid, tokens)
+
+    def finish(self, rid):
+        self.lib.gkrt_sched_finish(self.h, rid)
+
+    def abort_all(self):
+        self.lib.gkrt_sched_abort_all(self.h)
+
+    def tables(self, rids, max_blocks):
+        n = len(rids)
+        ids = (ctypes.c_int64 * max(n, 1))(*rids)
+        tab = (ctypes.c_int * (max(n, 1) * max_blocks))()
+        cached = (ctypes.c_int * max(n, 1))()
+        rc = self.lib.gkrt_sched_batch_tables(self.h, ids, n, tab, max_blocks, cached)
+        assert rc == 0
+        return (torch.frombuffer(tab, dtype=torch.int32).view(max(n, 1), max_blocks)[:n].clone(),
+                torch.frombuffer(cached, dtype=torch.int32)[:n].clone())
+
+    def stats(self):
+        out = (ctypes.c_int64 * 8)()
+        self.lib.gkrt_sched_stats(self.h, out)
+        return dict(free_blocks=out[0], running=out[1], waiting=out[2], preemptions=out[3], num_blocks=out[4])
+
+
+def _count_launches() -> int:
+    from ..ops import attention, gemm, optim, rl, vocab
+    return sum(sum(m.LAUNCHES.values()) for m in (attention, fused, gemm, optim, rl, vocab))
+
+
+class LayerWeights:
+    __slots__ = ("ln1", "qkv_w", "qkv_b", "o_w", "ln2", "fc1_w", "fc2_w", "q_ln", "k_ln", "sinks", "window", "moe")
+
+
+class RolloutWeights:
+    """Views of one model shard's parameters in the layout the decoder consumes.  ``from_model`` shares storage with
+    a ``GPTModel`` (zero-copy); ``clone_from_model`` owns its tensors (separate rollout copy, needed when the engine
+    must keep serving while the trainer's weights move)."""
+
+    def __init__(self):
+        self.layers: List[LayerWeights] = []
+        self.embed = self.final_ln = self.head = None
+
+    @classmethod
+    def from_model(cls, model, clone: bool = False):
+        f = (lambda t: t.detach().clone()) if clone else (lambda t: t.detach())
+        w = cls()
+        w.embed = f(model.embedding.word_embeddings.weight)
+        w.final_ln = f(model.decoder.final_layernorm.weight)
+        w.head = f(model.output_weight())
+        for layer in model.decoder.layers:
+            lw = LayerWeights()
+            a = layer.self_attention
+            lw.ln1 = f(layer.input_layernorm.weight)
+            lw.qkv_w = f(a.linear_qkv.weight)
+            lw.qkv_b = f(a.linear_qkv.bias) if a.linear_qkv.bias is not None else None
+            lw.o_w = f(a.linear_proj.weight)
+            lw.ln2 = f(layer.pre_mlp_layernorm.weight)
+            lw.q_ln = f(a.q_layernorm.weight) if hasattr(a, "q_layernorm") else None
+            lw.k_ln = f(a.k_layernorm.weight) if hasattr(a, "k_layernorm") else None
+            lw.sinks = f(a.sinks) if getattr(a, "sinks", None) is not None else None
+            lw.window = a.window
+            if layer.is_moe:
+                lw.moe = layer.mlp  # module reference: router + experts are used as they are
+                lw.fc1_w = lw.fc2_w = None
+            else:
+                lw.moe = None
+                lw.fc1_w = f(layer.mlp.linear_fc1.weight)
+                lw.fc2_w = f(layer.mlp.linear_fc2.weight)
+            w.layers.append(lw)
+        return w
+
+    def tensors(self):
+        for t in (self.embed, self.final_ln, self.head):
+            yield t
+        for lw in self.layers:
+            for k in ("ln1", "qkv_w", "qkv_b", "o_w", "ln2", "fc1_w", "fc2_w", "q_ln", "k_ln", "sinks"):
+                t = getattr(lw, k)
+                if t is not None:
+                    yield t
+
+
+class InferEngine:
+    def __init__(self, cfg: ModelConfig, weights: RolloutWeights, tp_size: int = 1, tp_group=None,
+                 max_running_requests: int = 64, max_model_len: int = 2048, kv_block_size: int = 16,
+                 num_kv_blocks: Optional[int] = None, gpu_memory_utilization: float = 0.7,
+                 max_prefill_tokens: int = 16384, use_cuda_graph: bool = True, sync_interval: int = 8,
+                 eos_token_id: Optional[int] = None, device=None):
+        self.cfg, self.w = cfg, weights
+        self.tp, self.tp_group = tp_size, tp_group
+        self.device = device or weights.embed.device
+        self.max_running = max_running_requests
+        self.max_model_len = max_model_len
+        self.bs = kv_block_size
+        self.max_blocks = (max_model_len + kv_block_size - 1) // kv_block_size + 1
+        self.hq = cfg.num_attention_heads // tp_size
+        self.hk = cfg.num_kv_heads // tp_size
+        self.D = cfg.head_dim
+        self.vocab_local = weights.head.shape[0]
+        self.vocab_start = self.vocab_local * (dist.get_rank(tp_group) if (tp_group is not None and tp_size > 1) else 0)
+        self.use_graph = use_cuda_graph and self.device.type == "cuda" and not _lib.force_eager()
+        self.sync_interval = max(1, sync_interval)
+        self.eos = eos_token_id
+        self.gpu_memory_utilization = gpu_memory_utilization
+        self._num_blocks_cfg = num_kv_blocks
+        self.max_prefill_tokens = max_prefill_tokens
+        self.k_cache: List[torch.Tensor] = []
+        self.v_cache: List[torch.Tensor] = []
+        self.sched: Optional[_Sched] = None
+        self.requests: Dict[int, Request] = {}
+        self._next_rid = 0
+        self._graphs: Dict[int, tuple] = {}
+        self._state = None
+        self.asleep = {"weights": False, "kv_cache": True}
+        self.stats = dict(decode_steps=0, prefill_tokens=0, generated_tokens=0, graph_replays=0)
+        self.record_routed_experts = False
+
+    # ------------------------------------------------------------------ memory
+    def _kv_bytes_per_block(self):
+        return 2 * len(self.w.layers) * self.bs * self.hk * self.D * 2
+
+    def wake_up(self, tags: Sequence[str] = ("weights", "kv_cache")):
+        """Allocates the KV cache (tag ``kv_cache``); weights are shared storage and are always resident."""
+        if "kv_cache" in tags and self.asleep["kv_cache"]:
+            n = self._num_blocks_cfg
+            if n is None:
+                need = self.max_running * self.max_blocks + 8
+                if self.device.type == "cuda":
+                    free, total = torch.cuda.mem_get_info(self.device)
+                    budget = int(free * self.gpu_memory_utilization)
+                    n = max(min(need, budget // self._kv_bytes_per_block()), self.max_blocks + 1)
+                else:
+                    n = need
+            self.num_blocks = n
+            dt = self.w.embed.dtype
+            self.k_cache = [torch.zeros(n, self.bs, self.hk, self.D, dtype=dt, device=self.device)
+                            for _ in self.w.layers]
+            self.v_cache = [torch.zeros(n, self.bs, self.hk, self.D, dtype=dt, device=self.device)
+                            for _ in self.w.layers]
+            self.sched = _Sched(n, self.bs, self.max_running, self.max_prefill_tokens)
+            self.asleep["kv_cache"] = False
+            self._graphs.clear()
+        if "weights" in tags:
+            self.asleep["weights"] = False
+
+    def sleep(self, tags: Sequence[str] = ("kv_cache",)):
+        """Releases the KV cache (and the captured graphs that reference it) so the trainer can use the memory."""
+        if "kv_cache" in tags and not self.asleep["kv_cache"]:
+            self._graphs.clear()
+            self._state = None
+            self.k_cache, self.v_cache = [], []
+            self.sched = None
+            self.asleep["kv_cache"] = True
+            if self.device.type == "cuda":
+                torch.cuda.empty_cache()
+        if "weights" in tags:
+            self.asleep["weights"] = True
+
+    def flush_cache(self):
+        if self.sched is not None:
+            self.sched.abort_all()
+        self.requests.clear()
+
+    def abort_all_requests(self):
+        self.flush_cache()
+
+    def get_load(self):
+        return self.sched.stats() if self.sched is not None else dict(running=0, waiting=0)
+
+    def update_weights(self, weights: Optional[RolloutWeights] = None):
+        """Shared storage: nothing moves; a new ``RolloutWeights`` re-points the engine (captured graphs are dropped
+        because they hold the old addresses)."""
+        if weights is not None and weights is not self.w:
+            same = all(a.data_ptr() == b.data_ptr() for a, b in zip(self.w.tensors(), weights.tensors()))
+            self.w = weights
+            if not same:
+                self._graphs.clear()
+        if self.device.type == "cuda":
+            torch.cuda.current_stream().synchronize()
+
+    # ------------------------------------------------------------------ model math (no autograd)
+    def _allreduce(self, x):
+        if self.tp > 1:
+            dist.all_reduce(x, group=self.tp_group)
+        return x
+
+    def _mlp(self, lw: LayerWeights, h):
+        if lw.moe is not None:
+            was = lw.moe.training
+            lw.moe.eval()
+            y, _ = lw.moe(h)
+            if was:
+                lw.moe.train()
+            return y
+        g = linear_forward(h, lw.fc1_w)
+        return self._allreduce(linear_forward(fused.swiglu(g), lw.fc2_w))
+
+    def _embed(self, tokens):
+        if self.tp == 1:
+            return torch.nn.functional.embedding(tokens, self.w.embed)
+        local = tokens - self.vocab_start
+        mine = (local >= 0) & (local < self.vocab_local)
+        x = self.w.embed[local.clamp(0, self.vocab_local - 1)] * mine[:, None].to(self.w.embed.dtype)
+        return self._allreduce(x)
+
+    def _qk_norm(self, lw, qkv, T):
+        if lw.q_ln is None:
+            return qkv
+        v = qkv.view(T, self.hq + 2 * self.hk, self.D)
+        q = fused.rmsnorm(v[:, :self.hq].reshape(-1, self.D), lw.q_ln, self.cfg.rms_norm_eps)[0]
+        k = fused.rmsnorm(v[:, self.hq:self.hq + self.hk].reshape(-1, self.D), lw.k_ln, self.cfg.rms_norm_eps)[0]
+        v[:, :self.hq] = q.view(T, self.hq, self.D)
+        v[:, self.hq:self.hq + self.hk] = k.view(T, self.hk, self.D)
+        return qkv
+
+    @torch.no_grad()
+    def _prefill(self, tokens, pos, cu, max_len, slots):
+        """Packed prompts through all layers; K/V go to the cache; returns the last-token hidden of every prompt."""
+        cfg = self.cfg
+        T = tokens.numel()
+        x = self._embed(tokens)
+        res = None
+        for li, lw in enumerate(self.w.layers):
+            h, res = fused.rmsnorm(x, lw.ln1, cfg.rms_norm_eps, res)
+            qkv = linear_forward(h, lw.qkv_w, lw.qkv_b)
+            qkv = self._qk_norm(lw, qkv, T)
+            kv_append_rope(qkv, pos, slots, self.k_cache[li], self.v_cache[li], self.hq, self.hk, self.D,
+                           cfg.rope_theta, cfg.rotary_dim)
+            v3 = qkv.view(T, self.hq + 2 * self.hk, self.D)
+            o = flash_attn_varlen(v3[:, :self.hq], v3[:, self.hq:self.hq + self.hk], v3[:, self.hq + self.hk:], cu, cu,
+                                  max_len, max_len, causal=True, window=lw.window, sinks=lw.sinks)
+            a = self._allreduce(linear_forward(o.reshape(T, self.hq * self.D), lw.o_w))
+            h, res = fused.rmsnorm(a, lw.ln2, cfg.rms_norm_eps, res)
+            x = self._mlp(lw, h)
+        last = (cu[1:] - 1).long()
+        hl, _ = fused.rmsnorm(x[last], self.w.final_ln, cfg.rms_norm_eps, res[last])
+        return hl
+
+    @torch.no_grad()
+    def _decode_math(self, st):
+        """One token for every row of the batch state ``st`` (all tensors static: graph-capturable)."""
+        cfg = self.cfg
+        B = st["tokens"].numel()
+        pos = st["pos"]
+        blk = st["block_table"].gather(1, (pos // self.bs).long()[:, None]).squeeze(1)
+        slots = torch.where(st["active"], blk * self.bs + pos % self.bs, torch.full_like(pos, -1))
+        ctx = torch.where(st["active"], pos + 1, torch.zeros_like(pos))
+        x = self._embed(st["tokens"])
+        res = None
+        for li, lw in enumerate(self.w.layers):
+            h, res = fused.rmsnorm(x, lw.ln1, cfg.rms_norm_eps, res)
+            qkv = linear_forward(h, lw.qkv_w, lw.qkv_b)
+            qkv = self._qk_norm(lw, qkv, B)
+            kv_append_rope(qkv, pos, slots, self.k_cache[li], self.v_cache[li], self.hq, self.hk, self.D,
+                           cfg.rope_theta, cfg.rotary_dim)
+            q = qkv.view(B, self.hq + 2 * self.hk, self.D)[:, :self.hq]
+            o = paged_decode(q, self.k_cache[li], self.v_cache[li], st["block_table"], ctx, self.max_model_len,
+                             window=lw.window, sinks=lw.sinks)
+            a = self._allreduce(linear_forward(o.view(B, self.hq * self.D), lw.o_w))
+            h, res = fused.rmsnorm(a, lw.ln2, cfg.rms_norm_eps, res)
+            x = self._mlp(lw, h)
+        hl, _ = fused.rmsnorm(x, self.w.final_ln, cfg.rms_norm_eps, res)
+        self._sample_into(hl, st)
+        # state advance
+        st["pos"].add_(st["active"].to(pos.dtype))
+        st["steps"].add_(1)
+        st["ring_idx"].add_(1)
+
+    def _sample_into(self, hidden, st):
+        logits = linear_forward(hidden, self.w.head, out_dtype=torch.float32)
+        sp = st["params"]
+        if sp["filtered"]:
+            logits = apply_top_k_top_p(logits / max(sp["temperature"], 1e-6), sp["top_k"], sp["top_p"], sp["min_p"])
+            tok, lp = sample(logits.contiguous(), 1.0, st["seeds"], st["steps"], sp["greedy"], self.tp_group
+                             if self.tp > 1 else None, self.vocab_start)
+        else:
+            tok, lp = sample(logits, sp["temperature"], st["seeds"], st["steps"], sp["greedy"],
+                             self.tp_group if self.tp > 1 else None, self.vocab_start)
+        st["tokens"].copy_(tok)
+        idx = st["ring_idx"] % st["ring_tok"].shape[0]
+        st["ring_tok"].index_copy_(0, idx, tok[None])
+        st["ring_lp"].index_copy_(0, idx, lp[None])
+
+    # ------------------------------------------------------------------ state / graphs
+    def _new_state(self, B, params: SamplingParams):
+        dev = self.device
+        R = self.sync_interval
+        return dict(
+            tokens=torch.zeros(B, dtype=torch.int64, device=dev), pos=torch.zeros(B, dtype=torch.int32, device=dev),
+            active=torch.zeros(B, dtype=torch.bool, device=dev),
+            block_table=torch.zeros(B, self.max_blocks, dtype=torch.int32, device=dev),
+            seeds=torch.zeros(B, dtype=torch.int64, device=dev), steps=torch.zeros(B, dtype=torch.int32, device=dev),
+            ring_tok=torch.zeros(R, B, dtype=torch.int64, device=dev),
+            ring_lp=torch.zeros(R, B, dtype=torch.float32, device=dev),
+            ring_idx=torch.zeros(1, dtype=torch.int64, device=dev),
+            params=dict(temperature=params.temperature, top_k=params.top_k, top_p=params.top_p, min_p=params.min_p,
+                        greedy=params.greedy,
+                        filtered=(params.top_k and params.top_k > 0) or params.top_p < 1.0 or params.min_p > 0.0))
+
+    def _run_decode(self, st):
+        B = st["tokens"].numel()
+        if not self.use_graph:
+            self._decode_math(st)
+            return
+        g = self._graphs.get(B)
+        if g is None or g[1] is not st:
+            # warm up once eagerly on a side stream (allocates scratch, configures kernels), then capture
+            keep = {k: v.clone() for k, v in st.items() if isinstance(v, torch.Tensor)}
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._decode_math(st)
+            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize()
+            for k, v in keep.items():
+                st[k].copy_(v)
+            graph = torch.cuda.CUDAGraph()
+            before = _count_launches()
+            with torch.cuda.graph(graph):
+                self._decode_math(st)
+            self.graph_launches = _count_launches() - before  # our kernels inside one replay
+            for k, v in keep.items():
+                st[k].copy_(v)
+            self._graphs[B] = (graph, st)
+            g = self._graphs[B]
+        g[0].replay()
+        self.stats["graph_replays"] += 1
+
+    # ------------------------------------------------------------------ public generate
+    @torch.no_grad()
+    def generate(self, prompts: Sequence[Sequence[int]], params: SamplingParams, n: int = 1,
+                 seeds: Optional[Sequence[int]] = None) -> List[Request]:
+        """Generates ``n`` samples for every prompt; returns requests ordered ``[p0s0, p0s1, ..., p1s0, ...]``.
+        Request ``(i, j)`` uses seed ``params.seed + i * n + j`` unless ``seeds`` is given
+        (gpatch_v4/extended_model/llm.py:57-68)."""
+        if self.asleep["kv_cache"]:
+            self.wake_up(("kv_cache",))
+        dev = self.device
+        reqs: List[Request] = []
+        if isinstance(prompts, torch.Tensor):
+            prompts = prompts.tolist()
+        for i, p in enumerate(prompts):
+            for j in range(n):
+                rid = self._next_rid
+                self._next_rid += 1
+                sd = seeds[i * n + j] if seeds is not None else params.seed + i * n + j
+                r = Request(rid, list(p), params, sd)
+                r.parent = reqs[i * n].rid if j > 0 else None
+                reqs.append(r)
+                self.requests[rid] = r
+        parents = [r for r in reqs if r.parent is None]
+        children: Dict[int, List[Request]] = {}
+        for r in reqs:
+            if r.parent is not None:
+                children.setdefault(r.parent, []).append(r)
+        for r in parents:
+            rc = self.sched.add(r.rid, len(r.prompt), params.max_new_tokens)
+            if rc != 0:
+                raise ValueError(f"request of {len(r.prompt)} + {params.max_new_tokens} tokens cannot fit the KV cache")
+        B = self.max_running
+        st = self._state
+        if st is None or st["tokens"].numel() != B or st["params"] != self._new_state(1, params)["params"]:
+            st = self._new_state(B, params)
+            self._state = st
+            self._graphs.clear()
+        slots_free = list(range(B - 1, -1, -1))
+        slot_req: Dict[int, Request] = {}
+        stop_ids = set(params.stop_token_ids) | ({self.eos} if self.eos is not None else set())
+        host_tok = torch.zeros(B, dtype=torch.int64)
+        host_pos = torch.zeros(B, dtype=torch.int32)
+        host_active = torch.zeros(B, dtype=torch.bool)
+        host_seed = torch.zeros(B, dtype=torch.int64)
+        host_step = torch.zeros(B, dtype=torch.int32)
+        host_bt = torch.zeros(B, self.max_blocks, dtype=torch.int32)
+
+        def place(r: Request, first_tok: int, first_lp: float):
+            """Request enters the decode batch after its first token is known."""
+            r.out_tokens.append(first_tok)
+            r.out_logprobs.append(first_lp)
+            if first_tok in stop_ids or len(r.out_tokens) >= params.max_new_tokens:
+                r.finished, r.finish_reason = True, "stop" if first_tok in stop_ids else "length"
+                self.sched.finish(r.rid)
+                return
+            s = slots_free.pop()
+            r.slot = s
+            slot_req[s] = r
+            host_tok[s] = first_tok
+            host_pos[s] = len(r.prompt)
+            host_active[s] = True
+            host_seed[s] = r.seed
+            host_step[s] = 1
+
+        while True:
+            # ---- admit: a prompt enters only when its whole sample group fits the batch
+            cap = len(slots_free) // max(n, 1)
+            pre_ids, _ = self.sched.step(cap, 0) if cap > 0 else ([], [])
+            if pre_ids:
+                pre = [self.requests[i] for i in pre_ids]
+                toks = torch.tensor([t for r in pre for t in r.prompt], dtype=torch.int64)
+                lens = [len(r.prompt) for r in pre]
+                cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+                pos = torch.cat([torch.arange(l, dtype=torch.int32) for l in lens])
+                bt, _ = self.sched.tables(pre_ids, self.max_blocks)
+                bidx = torch.repeat_interleave(torch.arange(len(pre)), torch.tensor(lens))
+                slots = bt[bidx, (pos // self.bs).long()] * self.bs + pos % self.bs
+                slots = slots.to(torch.int32)
+                if dev.type == "cuda":
+                    toks, pos, cu, slots = toks.pin_memory(), pos.pin_memory(), cu.pin_memory(), slots.pin_memory()
+                io_counters.add_h2d(io_counters.tensor_bytes(toks, pos, cu, slots))
+                hl = self._prefill(toks.to(dev, non_blocking=True), pos.to(dev, non_blocking=True),
+                                   cu.to(dev, non_blocking=True), max(lens), slots.to(dev, non_blocking=True))
+                self.stats["prefill_tokens"] += int(toks.numel())
+                for r in pre:
+                    self.sched.commit(r.rid, True)
+                # the first token of a prompt's samples all come from the same last-position hidden state
+                rows, owners = [], []
+                for k, r in enumerate(pre):
+                    for c in [r] + children.get(r.rid, []):
+                        rows.append(k)
+                        owners.append(c)
+                hsel = hl[torch.tensor(rows, device=dev)]
+                sd = torch.tensor([c.seed for c in owners], dtype=torch.int64, device=dev)
+                tmp = dict(tokens=torch.zeros(len(owners), dtype=torch.int64, device=dev), seeds=sd,
+                           steps=torch.zeros(len(owners), dtype=torch.int32, device=dev),
+                           ring_tok=torch.zeros(1, len(owners), dtype=torch.int64, device=dev),
+                           ring_lp=torch.zeros(1, len(owners), dtype=torch.float32, device=dev),
+                           ring_idx=torch.zeros(1, dtype=torch.int64, device=dev), params=st["params"])
+                self._sample_into(hsel, tmp)
+                ft, fl = tmp["ring_tok"][0].tolist(), tmp["ring_lp"][0].tolist()
+                io_counters.add_d2h(12 * len(owners))
+                first = {c.rid: (t, l) for c, t, l in zip(owners, ft, fl)}
+                # fork the samples before anything of the group can finish, then enter the decode batch
+                copies = []
+                for r in pre:
+                    for c in children.get(r.rid, []):
+                        rc, src, dst = self.sched.fork(r.rid, c.rid, params.max_new_tokens)
+                        if rc != 0:
+                            raise RuntimeError("KV cache exhausted while forking samples of a prompt; raise "
+                                               "num_kv_blocks or lower max_running_requests")
+                        if src >= 0:
+                            copies.append((src, dst))
+                if copies:
+                    src = torch.tensor([a for a, _ in copies], device=dev)
+                    dst = torch.tensor([b for _, b in copies], device=dev)
+                    for li in range(len(self.w.layers)):
+                        self.k_cache[li][dst] = self.k_cache[li][src]
+                        self.v_cache[li][dst] = self.v_cache[li][src]
+                for c in owners:
+                    place(c, *first[c.rid])
+            if not slot_req:
+                st_ = self.sched.stats()
+                if st_["waiting"] == 0:
+                    break
+                if st_["running"] == 0 and not pre_ids:
+                    raise RuntimeError("rollout engine cannot make progress: KV cache too small for one request")
+                continue
+            # ---- reserve KV for the next interval and push the batch state
+            interval = self.sync_interval
+            for s, r in list(slot_req.items()):
+                remaining = params.max_new_tokens - len(r.out_tokens)
+                self.sched.reserve(r.rid, min(interval, remaining) + 1)
+            rids = [slot_req[s].rid if s in slot_req else -1 for s in range(B)]
+            live = [s for s in range(B) if s in slot_req]
+            bt, _ = self.sched.tables([rids[s] for s in live], self.max_blocks)
+            host_bt.zero_()
+            host_bt[torch.tensor(live)] = bt
+            for k, src in (("tokens", host_tok), ("pos", host_pos), ("active", host_active), ("seeds", host_seed),
+                           ("steps", host_step), ("block_table", host_bt)):
+                st[k].copy_(src, non_blocking=True)
+                io_counters.add_h2d(io_counters.tensor_bytes(src))
+            st["ring_idx"].zero_()
+            for _ in range(interval):
+                self._run_decode(st)
+            self.stats["decode_steps"] += interval
+            ring_tok = st["ring_tok"].cpu()
+            ring_lp = st["ring_lp"].cpu()
+            io_counters.add_d2h(io_counters.tensor_bytes(ring_tok, ring_lp))
+            # ---- harvest
+            for s in live:
+                r = slot_req[s]
+                done = False
+                took = 0
+                for k in range(interval):
+                    t = int(ring_tok[k, s])
+                    r.out_tokens.append(t)
+                    r.out_logprobs.append(float(ring_lp[k, s]))
+                    took += 1
+                    if t in stop_ids:
+                        done, r.finish_reason = True, "stop"
+                        break
+                    if len(r.out_tokens) >= params.max_new_tokens:
+                        done, r.finish_reason = True, "length"
+                        break
+                self.stats["generated_tokens"] += took
+                if done:
+                    r.finished = True
+                    self.sched.finish(r.rid)
+                    del slot_req[s]
+                    slots_free.append(s)
+                    host_active[s] = False
+                    host_pos[s] = 0
+                else:
+                    self.sched.advance(r.rid, interval)
+                    host_tok[s] = r.out_tokens[-1]
+                    host_pos[s] += interval
+                    host_step[s] += interval
+        for r in reqs:
+            self.requests.pop(r.rid, None)
+        return reqs

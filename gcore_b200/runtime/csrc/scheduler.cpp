@@ -253,3 +253,21 @@ RT_EXPORT void gkrt_sched_stats(void* h, int64_t* out) {
   out[3] = s->preemptions;
   out[4] = s->num_blocks;
 }
+
+// Makes sure the request owns blocks for `tokens` more tokens beyond what is cached (multi-step decode reserves a
+// whole interval at once).  Returns 0, or -1 when the cache cannot provide them.
+RT_EXPORT int gkrt_sched_reserve(void* h, int64_t id, int tokens) {
+  auto* s = static_cast<Scheduler*>(h);
+  auto it = s->reqs.find(id);
+  if (it == s->reqs.end()) return -2;
+  return s->alloc(it->second, it->second.cached_tokens + tokens) ? 0 : -1;
+}
+
+// `tokens` decode steps have run: their KV is cached.
+RT_EXPORT void gkrt_sched_advance(void* h, int64_t id, int tokens) {
+  auto* s = static_cast<Scheduler*>(h);
+  auto it = s->reqs.find(id);
+  if (it == s->reqs.end()) return;
+  it->second.cached_tokens += tokens;
+  it->second.generated += tokens;
+}

@@ -1,0 +1,192 @@
+"""Synchronous GRPO / PPO step on one SPMD rank: rollout -> rewards -> prev / ref log-probs -> advantages -> policy
+(and critic) update -> weight hand-over to the rollout engine.
+
+Same phase structure and metric families as ``GrpoTrainActor.train_one_ppo_step`` (gpatch_v4/actor/
+grpo_train_actor.py:1231-1434), without the Ray actor boundary: trainer and rollout engine share the process and,
+when their tensor-parallel layouts match, the parameter storage.  The GPU is time-shared explicitly: the KV cache
+exists only during rollout, the fp32 gradient buffers only during the update.
+"""
+from __future__ import annotations
+
+import time
+from typing import Callable, Dict, List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from ..configs.base import import_from_path
+from ..configs.config import RlConfig
+from ..core import parallel_state as ps
+from ..core.advantage import compute_advantages
+from ..core.packing import response_mask
+from ..engine.train_engine import TrainingEngine
+from ..rollout.engine import InferEngine, RolloutWeights, SamplingParams
+from ..utils.timers import Timers
+
+
+def synthetic_reward(samples: Sequence[dict], **_) -> torch.Tensor:
+    """Rule reward of the benchmark recipe: 1.0 when the response contains token id
+    ``(sum(prompt) mod 150000) + 100``, else 0.0."""
+    out = []
+    for s in samples:
+        p = int(s["prompt_length"])
+        toks = s["tokens"]
+        target = (int(toks[:p].sum()) % 150000) + 100
+        out.append(1.0 if bool((toks[p:] == target).any()) else 0.0)
+    return torch.tensor(out, dtype=torch.float32)
+
+
+class GrpoTrainer:
+    def __init__(self, config: RlConfig, model_cfg=None, reward_fn: Optional[Callable] = None,
+                 prompt_source: Optional[Callable] = None):
+        self.cfg = config
+        self.timers = Timers()
+        self.reward_fn = reward_fn or self._load_reward_fn() or synthetic_reward
+        self.prompt_source = prompt_source
+        t = config.training
+        self.policy = TrainingEngine(config.policy, config.optimizer, t, config.ppo, model_cfg=model_cfg,
+                                     total_steps=t.total_ppo_step)
+        self.critic: Optional[TrainingEngine] = None
+        self.engine: Optional[InferEngine] = None
+        self.ppo_step = 0
+        self.last_metrics: Dict[str, float] = {}
+        self.advantage_fn = None
+        if config.ppo.advantage_py_path:
+            self.advantage_fn = import_from_path(config.ppo.advantage_py_path,
+                                                 config.ppo.advantage_fn_name or "advantage_fn")
+
+    def _load_reward_fn(self):
+        b = self.cfg.bt_rm
+        if b.rule_py_path:
+            return import_from_path(b.rule_py_path, b.rule_fn_name or "reward_fn")
+        return None
+
+    # ------------------------------------------------------------------ setup
+    def setup(self):
+        cfg = self.cfg
+        self.policy.setup_model_and_get_optimizer()
+        ie = cfg.sampler.infer_engine_configs[0]
+        self.policy.temperature = ie.temperature
+        if cfg.require_critic_model():
+            self.critic = TrainingEngine(cfg.critic, cfg.critic.optimizer, cfg.training, cfg.ppo,
+                                         model_cfg=self.policy.model_cfg, role="critic", value_head=True)
+            self.critic.setup_model_and_get_optimizer(with_ref=False)
+        model = self.policy.model
+        share = cfg.policy.share_rollout_weights
+        weights = RolloutWeights.from_model(model, clone=not share)
+        t = cfg.training
+        n_req = max(t.rollout_gbs // max(ps.get_data_parallel_world_size(), 1), 1) * t.sampling_repeat_n
+        self.engine = InferEngine(
+            self.policy.model_cfg, weights, tp_size=model.tp_size,
+            tp_group=ps.get_tensor_model_parallel_group() if model.tp_size > 1 else None,
+            max_running_requests=ie.max_running_requests or n_req,
+            max_model_len=ie.max_model_len or (cfg.data.max_prompt_length + ie.generate_max_tokens),
+            kv_block_size=ie.kv_block_size, num_kv_blocks=ie.num_kv_blocks,
+            gpu_memory_utilization=ie.gpu_memory_utilization, max_prefill_tokens=ie.max_prefill_tokens,
+            use_cuda_graph=not ie.disable_cuda_graph, device=self.policy.device)
+        self.sampling = SamplingParams(temperature=ie.temperature, top_k=ie.top_k, top_p=ie.top_p, min_p=ie.min_p,
+                                       max_new_tokens=ie.generate_max_tokens, seed=ie.seed,
+                                       stop_token_ids=tuple(ie.generate_params.get("stop_token_ids", ())))
+        # gradient buffers are only needed inside the update phase
+        self.policy.release_grad_buffers()
+        return self
+
+    # ------------------------------------------------------------------ phases
+    def rollout(self, prompts: Sequence[Sequence[int]]) -> List[dict]:
+        t = self.cfg.training
+        self.engine.wake_up(("kv_cache",))
+        sp = SamplingParams(**{**self.sampling.__dict__, "seed": self.sampling.seed + self.ppo_step * 1000003})
+        reqs = self.engine.generate(prompts, sp, n=t.sampling_repeat_n)
+        self.engine.sleep(("kv_cache",))
+        samples = []
+        dp_rank = ps.get_data_parallel_rank()
+        for k, r in enumerate(reqs):
+            toks = torch.tensor(r.prompt + r.out_tokens, dtype=torch.int64)
+            P, S = len(r.prompt), len(r.prompt) + len(r.out_tokens)
+            lp = torch.zeros(S, dtype=torch.float32)
+            lp[P - 1:S - 1] = torch.tensor(r.out_logprobs, dtype=torch.float32)
+            samples.append(dict(tokens=toks, prompt_length=P, sequence_length=S, rollout_log_probs=lp,
+                                group_id=k // t.sampling_repeat_n, unique_id=(self.ppo_step, dp_rank, k),
+                                mask=response_mask(P, S), finish_reason=r.finish_reason))
+        return samples
+
+    def score(self, samples: List[dict]) -> List[dict]:
+        out = self.reward_fn(samples)
+        rewards, per_tok, extra = (out if isinstance(out, tuple) else (out, None, {}))
+        rewards = torch.as_tensor(rewards, dtype=torch.float32).reshape(-1)
+        for i, s in enumerate(samples):
+            s["rewards"] = rewards[i]
+            if per_tok is not None:
+                s["per_token_rewards"] = per_tok[i]
+        self._reward_extra = extra
+        return samples
+
+    def step(self, prompts: Optional[Sequence[Sequence[int]]] = None) -> Dict[str, float]:
+        """One full PPO step; returns the metric dict (timers under ``time_perf/``)."""
+        cfg, t, tm = self.cfg, self.cfg.training, self.timers
+        if prompts is None:
+            prompts = self.prompt_source(self.ppo_step)
+        tm.start("step")
+        tm.start("rollout")
+        samples = self.rollout(prompts)
+        tm.stop("rollout")
+        tm.start("reward")
+        samples = self.score(samples)
+        tm.stop("reward")
+        tm.start("compute_logps")
+        if not cfg.ppo.skip_prev_logps:
+            self.policy.compute_log_probs(samples, use_ref=False)
+        if not cfg.policy.without_ref and cfg.ppo.grpo_kl_loss_beta != 0:
+            self.policy.compute_log_probs(samples, use_ref=True)
+        if self.critic is not None:
+            self.critic.compute_values(samples)
+        tm.stop("compute_logps")
+        tm.start("generate_ppo_data")
+        samples = compute_advantages(samples, cfg.ppo, ps.get_data_parallel_group(), self.advantage_fn)
+        tm.stop("generate_ppo_data")
+        tm.start("train_step")
+        metrics: Dict[str, float] = {}
+        self.policy.allocate_grad_buffers()
+        per_update = max(t.train_gbs // max(ps.get_data_parallel_world_size(), 1), 1)
+        for _ in range(t.ppo_max_epochs_2):
+            for s0 in range(0, len(samples), per_update):
+                if self.critic is not None:
+                    metrics.update(self.critic.rl_train_value(samples[s0:s0 + per_update]))
+                if self.critic is None or self.ppo_step >= cfg.ppo.critic_model_warmup_steps:
+                    metrics.update(self.policy.rl_train_actor(samples[s0:s0 + per_update]))
+        self.policy.release_grad_buffers()
+        tm.stop("train_step")
+        tm.start("update_weights")
+        self.update_weights()
+        tm.stop("update_weights")
+        tm.stop("step")
+        metrics.update(self._rollout_metrics(samples))
+        for k in ("step", "rollout", "reward", "compute_logps", "generate_ppo_data", "train_step", "update_weights"):
+            metrics[f"time_perf/{k}"] = tm.last(k)
+        self.ppo_step += 1
+        self.last_metrics = metrics
+        self.last_samples = samples
+        return metrics
+
+    def update_weights(self):
+        """Hands the updated weights to the rollout engine (zero-copy when storage is shared)."""
+        if self.cfg.policy.share_rollout_weights:
+            self.engine.update_weights(None)
+        else:
+            from ..rollout.weight_sync import sync_weights
+            sync_weights(self.policy, self.engine)
+
+    def _rollout_metrics(self, samples):
+        r = torch.stack([torch.as_tensor(s["rewards"]).float().sum() for s in samples])
+        resp = torch.tensor([float(s["sequence_length"] - s["prompt_length"]) for s in samples])
+        tot = torch.tensor([r.sum(), float(len(samples)), resp.sum(), float(sum(s["sequence_length"] for s in samples)),
+                            float(sum(1 for s in samples if s["finish_reason"] == "length"))])
+        g = ps.get_data_parallel_group()
+        if g is not None and dist.get_world_size(g) > 1:
+            tt = tot.to(self.policy.device) if dist.get_backend(g) == "nccl" else tot
+            dist.all_reduce(tt, group=g)
+            tot = tt.cpu()
+        n = max(float(tot[1]), 1.0)
+        return {"rollout-rewards/mean": float(tot[0]) / n, "rollout-metrics/response_length": float(tot[2]) / n,
+                "rollout-metrics/num_samples": n, "rollout-metrics/total_tokens": float(tot[3]),
+                "rollout-metrics/response_tokens": float(tot[2]), "rollout-metrics/truncated_frac": float(tot[4]) / n}

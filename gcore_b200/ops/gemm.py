@@ -198,25 +198,21 @@ def linear_wgrad(dy: torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = N
 
 class _LinearFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, bias, main_grad):
-        shp = x.shape
-        x2 = x.reshape(-1, shp[-1])
+    def forward(ctx, x2, w, bias, main_grad):
+        # 2-D in, 2-D out: the output must be a fresh tensor (not a view made inside the Function) because callers
+        # rotate / overwrite it in place
         ctx.save_for_backward(x2, w)
         ctx.has_bias = bias is not None
         ctx.main_grad = main_grad
-        ctx.in_shape = shp
-        y = linear_forward(x2, w, bias)
-        return y.reshape(*shp[:-1], w.shape[0])
+        return linear_forward(x2, w, bias)
 
     @staticmethod
     def backward(ctx, dy):
         x2, w = ctx.saved_tensors
-        dy2 = dy.reshape(-1, dy.shape[-1])
-        if not dy2.is_contiguous():
-            dy2 = dy2.contiguous()
+        dy2 = dy if dy.is_contiguous() else dy.contiguous()
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
-            dx = linear_dgrad(dy2, w).reshape(ctx.in_shape)
+            dx = linear_dgrad(dy2, w)
         if ctx.needs_input_grad[1]:
             mg = ctx.main_grad
             if mg is not None:
@@ -236,4 +232,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     weight gradient is accumulated into it inside the GEMM epilogue and autograd sees no ``w.grad``."""
     if x.dtype != torch.bfloat16 or not _lib.use_native(x):
         return torch.nn.functional.linear(x, w, bias)
-    return _LinearFn.apply(x, w, bias, main_grad)
+    shp = x.shape
+    x2 = x.reshape(-1, shp[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    y = _LinearFn.apply(x2, w, bias, main_grad)
+    return y if len(shp) == 2 else y.reshape(*shp[:-1], w.shape[0])

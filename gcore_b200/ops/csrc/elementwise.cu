@@ -411,3 +411,48 @@ GK_EXPORT int gk_axpy_cast(const void* src, int src_fp32, void* dst, int dst_fp3
                                                                                         accumulate);
   return launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Allocation-free variant of gk_rmsnorm_bwd (declared and documented in no_alloc.h).
+#include "no_alloc.h"
+
+namespace gk {
+// Scratch for the per-CTA weight-gradient partials.  In host code this name is only a handle for the symbol: the
+// device address has to be looked up (once per device) before it can be given to a kernel.
+static __device__ __align__(256) float g_noalloc_rms_scratch[GK_NOALLOC_RMSNORM_MAX_PARTS * GK_NOALLOC_RMSNORM_MAX_H];
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static float* g_noalloc_rms_ptr[NOALLOC_MAX_DEVICES] = {nullptr};
+}  // namespace gk
+
+GK_EXPORT int gk_rmsnorm_bwd_noalloc(const void* g, const void* x, const void* w, const float* rstd, const void* dres,
+                                     void* dx, float* dw, int dw_accumulate, int T, int H, void* stream) {
+  if (H % 8) return -1;
+  if (H > GK_NOALLOC_RMSNORM_MAX_H) {
+    fprintf(stderr, "[gcore_b200] gk_rmsnorm_bwd_noalloc: H=%d exceeds the built-in scratch (max H %d)\n", H,
+            GK_NOALLOC_RMSNORM_MAX_H);
+    return -2;
+  }
+  if (T <= 0) return 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return -3;
+  if (!g_noalloc_rms_ptr[dev]) {
+    // first call on this device: resolve the device address of the file-scope array
+    float* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_rms_scratch);
+    if (e != cudaSuccess || !p) {
+      fprintf(stderr, "[gcore_b200] gk_rmsnorm_bwd_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e));
+      return -3;
+    }
+    g_noalloc_rms_ptr[dev] = p;
+  }
+  float* scratch = g_noalloc_rms_ptr[dev];
+  int parts = gk_rmsnorm_bwd_parts(T);
+  if (parts > GK_NOALLOC_RMSNORM_MAX_PARTS) parts = GK_NOALLOC_RMSNORM_MAX_PARTS;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  rmsnorm_bwd_kernel<<<parts, 256, 0, st>>>(
+      reinterpret_cast<const __nv_bfloat16*>(g), reinterpret_cast<const __nv_bfloat16*>(x),
+      reinterpret_cast<const __nv_bfloat16*>(w), rstd, reinterpret_cast<const __nv_bfloat16*>(dres),
+      reinterpret_cast<__nv_bfloat16*>(dx), scratch, T, H);
+  colsum_partial_kernel<<<(H + 255) / 256, 256, 0, st>>>(scratch, dw, parts, H, dw_accumulate);
+  return launch_status();
+}

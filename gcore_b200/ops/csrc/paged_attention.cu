@@ -12,7 +12,7 @@ namespace gk {
 constexpr int PD_THREADS = 128;
 constexpr int PD_TILE = 32;     // tokens per shared-memory tile
 constexpr int PD_MAX_GROUP = 16;
-constexpr int PD_SPLIT = 256;   // tokens per KV split
+constexpr int PD_SPLIT = 128;   // tokens per KV split
 
 // qkv: [T, (Hq + 2*Hk) * D] as produced by the fused QKV projection ([q | k | v] per token).
 // Rotates q and k in place (rotate-half pairing) and writes k, v to cache slot `slots[t]`
@@ -177,6 +177,213 @@ __global__ void __launch_bounds__(PD_THREADS, 4) paged_decode_kernel(
   }
 }
 
+
+constexpr int PD2_WARPS = 4;
+constexpr int PD2_G = 8;
+constexpr int PD2_TOK_PER_WARP = PD_SPLIT / PD2_WARPS;  // 32: one tile per warp
+
+// ---------------------------------------------------------------------------------------------------------------
+// Tensor-core variant (GQA groups of up to 8 heads, D = 128).  The scalar kernels above spend ~128 FMAs per
+// (head, token) pair and end up issue-bound long before HBM is saturated; here the group's heads are the (padded)
+// M = 16 rows of mma.sync m16n8k16 tiles, so a 32-token tile costs 32 MMAs for Q K^T and 32 for P V per warp.
+// (tcgen05 needs M >= 64 per instruction and a TMEM / mbarrier set-up per CTA, which does not pay for 8 query rows.)
+//   * K and V tiles arrive with cp.async into chunk-swizzled shared memory (16-byte chunk c of row r at c ^ (r & 15)),
+//     so ldmatrix is bank-conflict free without padding;
+//   * S lives in the accumulator layout, P is re-packed in registers into the A-operand layout of the P V MMA;
+//   * rows 8..15 of every tile are padding and are ignored.
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(PD2_WARPS * 32, 3) paged_decode_mma_kernel(
+    const __nv_bfloat16* __restrict__ q, long long q_stride, const __nv_bfloat16* __restrict__ kc,
+    const __nv_bfloat16* __restrict__ vc, const int* __restrict__ block_table, int max_blocks,
+    const int* __restrict__ ctx_len, const float* __restrict__ sinks, __nv_bfloat16* __restrict__ out,
+    float* __restrict__ scratch, int Hq, int Hk, int block_size, int window, float scale, int nsplit) {
+  constexpr int D = 128;
+  __shared__ __align__(16) uint8_t sq[16 * 256];  // Q tile, 16 rows (heads, zero padded) x 256 B, chunk-swizzled
+  __shared__ long long slot_buf[PD2_WARPS][32];
+  __shared__ float m_all[PD2_WARPS][PD2_G], l_all[PD2_WARPS][PD2_G];
+  extern __shared__ __align__(16) uint8_t pd3_dyn[];  // K tiles | V tiles: 32 rows x 256 B per warp
+  uint8_t* k_tile = pd3_dyn;
+  uint8_t* v_tile = pd3_dyn + PD2_WARPS * 32 * 256;
+
+  const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  const int G = Hq / Hk;
+  const int len = ctx_len[b];
+  int start = 0;
+  if (window > 0 && len > window) start = len - window;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int w0 = start + split * PD_SPLIT + warp * PD2_TOK_PER_WARP;
+  int w1 = w0 + PD2_TOK_PER_WARP;
+  if (w1 > len) w1 = len;
+  const int nt = w1 > w0 ? w1 - w0 : 0;
+
+  // ---- request this warp's K / V tile first (one memory round trip per warp), then stage Q while it is in flight
+  uint8_t* kt = k_tile + warp * (32 * 256);
+  uint8_t* vt = v_tile + warp * (32 * 256);
+  {
+    long long slot = 0;
+    if (lane < nt) {
+      const int tok = w0 + lane;
+      slot = static_cast<long long>(block_table[static_cast<long long>(b) * max_blocks + tok / block_size]) *
+                 block_size + tok % block_size;
+    }
+    slot_buf[warp][lane] = slot;
+  }
+  __syncwarp();
+  if (nt > 0) {
+    const uint32_t kts = static_cast<uint32_t>(__cvta_generic_to_shared(kt));
+    const uint32_t vts = static_cast<uint32_t>(__cvta_generic_to_shared(vt));
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int idx = i * 32 + lane;
+      const int row = idx >> 4, ch = idx & 15;
+      const long long slot = slot_buf[warp][row];
+      const uint32_t nbytes = row < nt ? 16u : 0u;  // rows past the end are zero-filled
+      const uint32_t doff = static_cast<uint32_t>(row * 256 + ((ch ^ (row & 15)) << 4));
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(kts + doff),
+                   "l"(kc + (slot * Hk + kvh) * D + ch * 8), "r"(nbytes) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vts + doff),
+                   "l"(vc + (slot * Hk + kvh) * D + ch * 8), "r"(nbytes) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  for (int i = tid; i < 16 * 16; i += PD2_WARPS * 32) {
+    const int g = i >> 4, c = i & 15;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (g < G) v = reinterpret_cast<const uint4*>(q + b * q_stride + static_cast<long long>(kvh * G + g) * D)[c];
+    *reinterpret_cast<uint4*>(sq + g * 256 + ((c ^ (g & 15)) << 4)) = v;
+  }
+  __syncthreads();
+
+  const int r0 = lane >> 2;        // this thread's accumulator row = head index inside the group
+  const int cq = (lane & 3) * 2;   // first of its two columns inside an 8-wide tile
+  float m_run = -FLT_MAX, l_run = 0.f;
+  float o[16][4];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+
+  if (nt > 0) {
+    // Q as A fragments for the 8 k-steps (16 dims each)
+    uint32_t qa[8][4];
+    const uint32_t sqs = static_cast<uint32_t>(__cvta_generic_to_shared(sq));
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      const int row = (lane & 7) + ((lane >> 3) & 1) * 8;
+      const int ch = ks * 2 + (lane >> 4);
+      ldsm_x4(qa[ks], sqs + row * 256 + ((ch ^ (row & 15)) << 4));
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncwarp();
+    const uint32_t kts = static_cast<uint32_t>(__cvta_generic_to_shared(kt));
+    const uint32_t vts = static_cast<uint32_t>(__cvta_generic_to_shared(vt));
+    // ---- S = Q K^T : 4 token tiles of 8
+    float s[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+      for (int kp = 0; kp < 4; ++kp) {  // pairs of k-steps
+        uint32_t kb[4];
+        const int row = j * 8 + (lane & 7);
+        const int ch = kp * 4 + (lane >> 3);
+        ldsm_x4(kb, kts + row * 256 + ((ch ^ (row & 15)) << 4));
+        mma_bf16_16816(s[j], qa[2 * kp], kb[0], kb[1]);
+        mma_bf16_16816(s[j], qa[2 * kp + 1], kb[2], kb[3]);
+      }
+    }
+    // ---- softmax over this tile for row r0 (rows 8..15 are padding)
+    float mx = -FLT_MAX;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int ti = j * 8 + cq + e;
+        const float v = ti < nt ? s[j][e] * scale : -FLT_MAX;
+        s[j][e] = v;
+        mx = fmaxf(mx, v);
+      }
+    }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffff, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffff, mx, 2));
+    m_run = mx;
+    uint32_t pa[2][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float p0 = s[j][0] == -FLT_MAX ? 0.f : __expf(s[j][0] - mx);
+      const float p1 = s[j][1] == -FLT_MAX ? 0.f : __expf(s[j][1] - mx);
+      l_run += p0 + p1;
+      // A fragment of k-step j/2: regs {rows lo cols lo, rows hi cols lo, rows lo cols hi, rows hi cols hi}
+      pa[j >> 1][(j & 1) * 2] = pack2_bf16(p0, p1);
+      pa[j >> 1][(j & 1) * 2 + 1] = 0u;  // padding rows
+    }
+    // ---- O = P V : 2 k-steps of 16 tokens, 16 dim tiles of 8
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk) {
+#pragma unroll
+      for (int np = 0; np < 8; ++np) {  // pairs of dim tiles
+        uint32_t vb[4];
+        const int row = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int ch = np * 2 + (lane >> 4);
+        ldsm_x4_trans(vb, vts + row * 256 + ((ch ^ (row & 15)) << 4));
+        mma_bf16_16816(o[2 * np], pa[kk], vb[0], vb[1]);
+        mma_bf16_16816(o[2 * np + 1], pa[kk], vb[2], vb[3]);
+      }
+    }
+  }
+  // ---- merge the four warps (K tiles are dead after the barrier: their storage carries the partial outputs)
+  l_run += __shfl_xor_sync(0xffffffff, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffff, l_run, 2);
+  __syncthreads();
+  float (*o_all)[PD2_G][D] = reinterpret_cast<float (*)[PD2_G][D]>(k_tile);
+  if ((lane & 3) == 0) { m_all[warp][r0] = m_run; l_all[warp][r0] = l_run; }
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    *reinterpret_cast<float2*>(&o_all[warp][r0][j * 8 + cq]) = make_float2(o[j][0], o[j][1]);
+  }
+  __syncthreads();
+  const int d = tid;  // 128 threads <-> 128 dims
+  for (int g = 0; g < G; ++g) {
+    float mm = -FLT_MAX;
+#pragma unroll
+    for (int w = 0; w < PD2_WARPS; ++w) mm = fmaxf(mm, m_all[w][g]);
+    float acc = 0.f, ls = 0.f;
+#pragma unroll
+    for (int w = 0; w < PD2_WARPS; ++w) {
+      const float f = m_all[w][g] == -FLT_MAX ? 0.f : __expf(m_all[w][g] - mm);
+      acc += o_all[w][g][d] * f;
+      ls += l_all[w][g] * f;
+    }
+    const int h = kvh * G + g;
+    if (nsplit == 1) {
+      if (sinks) ls += __expf(sinks[h] - mm);
+      out[(static_cast<long long>(b) * Hq + h) * D + d] = __float2bfloat16(ls > 0.f ? acc / ls : 0.f);
+    } else {
+      float* dst = scratch + ((static_cast<long long>(b) * Hq + h) * nsplit + split) * (D + 2);
+      dst[d] = acc;
+      if (d == 0) { dst[D] = mm; dst[D + 1] = ls; }
+    }
+  }
+}
+
 template <int D>
 __global__ void paged_decode_combine_kernel(const float* __restrict__ scratch, const float* __restrict__ sinks,
                                             __nv_bfloat16* __restrict__ out, int Hq, int nsplit) {
@@ -229,6 +436,18 @@ GK_EXPORT int gk_paged_decode(const void* q, const void* kc, const void* vc, con
   if (nsplit > 1 && !scratch) return -2;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   dim3 grid(B, Hk, nsplit);
+  if (Hq / Hk <= PD2_G) {
+    constexpr int PD2_SMEM = 2 * PD2_WARPS * 32 * 128 * 2;
+    static bool configured = false;
+    if (!configured) {
+      cudaFuncSetAttribute(paged_decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PD2_SMEM);
+      configured = true;
+    }
+    paged_decode_mma_kernel<<<grid, PD2_WARPS * 32, PD2_SMEM, st>>>(
+        reinterpret_cast<const __nv_bfloat16*>(q), q_stride, reinterpret_cast<const __nv_bfloat16*>(kc),
+        reinterpret_cast<const __nv_bfloat16*>(vc), block_table, max_blocks, ctx_len, sinks,
+        reinterpret_cast<__nv_bfloat16*>(out), scratch, Hq, Hk, block_size, window, scale, nsplit);
+  } else
   paged_decode_kernel<128><<<grid, PD_THREADS, 0, st>>>(
       reinterpret_cast<const __nv_bfloat16*>(q), q_stride, reinterpret_cast<const __nv_bfloat16*>(kc),
       reinterpret_cast<const __nv_bfloat16*>(vc), block_table, max_blocks, ctx_len, sinks,

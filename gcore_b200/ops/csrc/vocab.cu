@@ -3,14 +3,13 @@
 //     final values or per-rank partials for vocab-parallel TP (one small all-gather replaces the three
 //     all-reduces of gpatch_v4/training_backend/vocab_parallel_entropy.py:20-29);
 //   * its backward, overwriting the logits chunk with d(logits);
-//   * Gumbel-max sampling with a per-request Philox stream, returning the sampled token's log-prob
+//   * Gumbel-max sampling with a per-request counter-based random stream, returning the sampled token's log-prob
 //     (per-request seed semantics of gpatch_v4/extended_model/llm.py:57-68);
 //   * the GRPO / PPO-clip token objective with k3 KL, fwd + grad in one pass
 //     (gpatch_v4/training_backend/loss/ppo_loss.py:232-346, gpatch_v4/utils/ppo_utils.py:151-193);
 //   * the GAE reverse scan (gpatch_v4/core/advantage_impl.py:394-444).
 #include "host_utils.h"
 #include <cuda_bf16.h>
-#include <curand_kernel.h>
 #include <float.h>
 
 namespace gk {
@@ -18,6 +17,18 @@ namespace gk {
 __device__ __forceinline__ float load_logit(const void* p, int is_fp32, long long i) {
   return is_fp32 ? reinterpret_cast<const float*>(p)[i]
                  : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+
+// Counter-based uniform in (0, 1): splitmix64 finaliser over (seed, step, token id).  Stateless, so the draw for a
+// token does not depend on which thread, CTA or tensor-parallel rank evaluates it.
+__device__ __forceinline__ float hash_uniform(unsigned long long seed, unsigned long long step,
+                                              unsigned long long idx) {
+  unsigned long long x = seed * 0x9E3779B97F4A7C15ULL + step * 0xD1B54A32D192ED03ULL + idx * 0x2545F4914F6CDD1DULL +
+                         0x632BE59BD9B4E019ULL;
+  x ^= x >> 30; x *= 0xBF58476D1CE4E5B9ULL;
+  x ^= x >> 27; x *= 0x94D049BB133111EBULL;
+  x ^= x >> 31;
+  return (static_cast<float>(x >> 40) + 0.5f) * (1.0f / 16777216.0f);
 }
 
 struct Online {
@@ -152,8 +163,8 @@ __global__ void __launch_bounds__(256) logprob_entropy_bwd_kernel(void* __restri
 }
 
 // Gumbel-max: argmax_j (z_j + G_j) is a sample from softmax(z).  One CTA per request.
-// Philox stream: seed = seeds[b], subsequence = global vocab id, offset = step[b]; the draw depends only on
-// (seed, token id, step), so any TP / batching layout reproduces the same sample.
+// The uniform for a token is a hash of (seeds[b], steps[b], global vocab id): the draw depends only on those three,
+// so any TP / batching layout reproduces the same sample.
 __global__ void __launch_bounds__(256) sample_kernel(const void* __restrict__ logits, int is_fp32, long long ld, int V,
                                                      int vocab_start, float inv_temp, int greedy,
                                                      const long long* __restrict__ seeds,
@@ -176,10 +187,8 @@ __global__ void __launch_bounds__(256) sample_kernel(const void* __restrict__ lo
     online_add(o, z);
     float score = z;
     if (!greedy) {
-      curandStatePhilox4_32_10_t st;
-      curand_init(seed, static_cast<unsigned long long>(vocab_start + j), step, &st);
-      const float u = curand_uniform(&st);  // (0, 1]
-      score = z - __logf(-__logf(u) + 1e-20f);
+      const float u = hash_uniform(seed, step, static_cast<unsigned long long>(vocab_start + j));  // (0, 1)
+      score = z - __logf(-__logf(u));
     }
     if (score > best) { best = score; bidx = vocab_start + j; bz = z; }
   }

@@ -167,7 +167,7 @@ def sample_ref(logits, temperature, seeds, steps, greedy=False):
 
 def sample(logits, temperature, seeds, steps, greedy=False, tp_group=None, vocab_start=0):
     """Draws one token per row from ``softmax(logits / temperature)`` (Gumbel-max) and returns
-    ``(tokens int64 [B], logp fp32 [B])``.  ``seeds`` int64 [B], ``steps`` int32 [B] select the Philox stream; the
+    ``(tokens int64 [B], logp fp32 [B])``.  ``seeds`` int64 [B], ``steps`` int32 [B] select the random stream; the
     draw for a given (seed, step, token id) is independent of batching and of the vocabulary sharding."""
     B, V = logits.shape
     if not (_lib.use_native(logits) and logits.dtype in (torch.bfloat16, torch.float32)):

@@ -76,5 +76,11 @@ def attn_bwd(do, q, k, v, out, lse, sinks, cu_q, cu_k, max_q, max_k, causal, win
     else:
         dk = dk_h.view(Tk, Hk, g, D).float().sum(2).to(q.dtype)
         dv = dv_h.view(Tk, Hk, g, D).float().sum(2).to(q.dtype)
-    ds = dsink_part.to(sinks.dtype) if sinks is not None else None
+    ds = None
+    if sinks is not None:
+        # d sink_h = -sum_t exp(sink_h - lse[h, t]) * delta[h, t]   (rows without any visible key carry lse = -max)
+        ok = lse > -1e30
+        wgt = torch.where(ok, torch.exp(sinks.float()[:, None] - torch.where(ok, lse, torch.zeros_like(lse))),
+                          torch.zeros_like(lse))
+        ds = (-(wgt * delta).sum(1)).to(sinks.dtype)
     return dq, dk, dv, ds

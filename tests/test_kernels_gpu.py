@@ -331,3 +331,44 @@ def test_flash_attn_prefix_k_and_packed_qkv():
         out = flash_attn_varlen(q, k, v, cu_q, cu_k, max(lq), max(lk), causal=True)
         ref = attn_varlen_ref(q, k, v, cu_q, cu_k, True)
     _close(out, ref, atol=3e-2)
+
+
+@pytest.mark.parametrize("D", [128, 64])
+@pytest.mark.parametrize("causal,window,use_sinks", [(True, 0, False), (True, 128, True), (False, 0, False)])
+def test_flash_attn_bwd_varlen(D, causal, window, use_sinks):
+    from gcore_b200.ops.attention import attn_varlen_ref, flash_attn_varlen
+    torch.manual_seed(14)
+    Hq, Hk = 8, 2
+    lens = [33, 700, 3, 128, 129, 255]
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device=DEV, dtype=torch.int32)
+    T = sum(lens)
+    q, k, v = [_rand(T, h, D).requires_grad_(True) for h in (Hq, Hk, Hk)]
+    sinks = torch.randn(Hq, device=DEV).requires_grad_(True) if use_sinks else None
+    out = flash_attn_varlen(q, k, v, cu, cu, max(lens), max(lens), causal=causal, window=window, sinks=sinks)
+    go = _rand(T, Hq, D)
+    out.backward(go)
+    qf, kf, vf = [t.detach().float().requires_grad_(True) for t in (q, k, v)]
+    sf = sinks.detach().clone().requires_grad_(True) if use_sinks else None
+    ref = attn_varlen_ref(qf, kf, vf, cu, cu, causal, window, sf)
+    ref.backward(go.float())
+    _close(q.grad, qf.grad, rtol=3e-2, atol=3e-2)
+    _close(k.grad, kf.grad, rtol=3e-2, atol=3e-2)
+    _close(v.grad, vf.grad, rtol=3e-2, atol=3e-2)
+    if use_sinks:
+        _close(sinks.grad, sf.grad, rtol=3e-2, atol=3e-2)
+
+
+def test_flash_attn_packed_qkv_bwd_matches_unpacked():
+    from gcore_b200.ops.attention import attn_varlen_ref, flash_attn_qkvpacked
+    torch.manual_seed(15)
+    hq, hk, D = 4, 2, 128
+    lens = [200, 56]
+    cu = torch.tensor([0, 200, 256], device=DEV, dtype=torch.int32)
+    qkv = _rand(256, hq + 2 * hk, D).requires_grad_(True)
+    out = flash_attn_qkvpacked(qkv, hq, hk, cu, 200)
+    go = _rand(256, hq, D)
+    out.backward(go)
+    x = qkv.detach().float().requires_grad_(True)
+    ref = attn_varlen_ref(x[:, :hq], x[:, hq:hq + hk], x[:, hq + hk:], cu, cu, True)
+    ref.backward(go.float())
+    _close(qkv.grad, x.grad, rtol=3e-2, atol=3e-2)

@@ -1,0 +1,25 @@
+"""Fused tensor-parallel GEMM + collective kernels on >= 2 GPUs (peer stores + flags), checked against NCCL."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_ag_gemm_and_gemm_rs_two_ranks(tmp_path):
+    out = tmp_path / "fused.json"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29571", os.path.join(ROOT, "tests", "workers", "fused_tp_worker.py"), str(out)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    res = json.load(open(out))
+    for k, v in res.items():
+        for name, ok in v.items():
+            if isinstance(ok, bool):
+                assert ok, (k, name, res)

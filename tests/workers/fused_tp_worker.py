@@ -1,0 +1,127 @@
+"""2+ rank worker: fused AG->GEMM / GEMM->RS kernels against the NCCL + reference-GEMM path."""
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+
+from gcore_b200.core import parallel_state as ps  # noqa: E402
+from gcore_b200.ops import _lib  # noqa: E402
+from gcore_b200.parallel import tp_ops  # noqa: E402
+from gcore_b200.parallel.symm import FusedTP  # noqa: E402
+
+
+def close(a, b, tol):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    ref = b.abs().max().item()
+    return err <= tol * max(ref, 1.0), err, ref
+
+
+def main():
+    out_path = sys.argv[1]
+    bench = len(sys.argv) > 2 and sys.argv[2] == "bench"
+    ps.init_distributed("nccl")
+    st = ps.initialize_model_parallel(tp=dist.get_world_size())
+    g = ps.get_tensor_model_parallel_group()
+    tp, rank = dist.get_world_size(), dist.get_rank()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    Tl, K, N = 512, 1024, 1536
+    ftp = FusedTP(g, max_rows_per_rank=4096 if bench else 512, max_width=18944 if bench else 2048)
+    res = {}
+    torch.manual_seed(100 + rank)
+    for it in range(3):  # several calls: both parities, growing epochs
+        x = (torch.randn(Tl, K, device=dev) * 0.5).bfloat16()
+        torch.manual_seed(7 + it)
+        w = (torch.randn(N, K, device=dev) * 0.05).bfloat16()  # same on every rank
+        bias = torch.randn(N, device=dev).bfloat16()
+        y, xg = ftp.ag_gemm(x, w, bias)
+        xg_ref = tp_ops.all_gather_dim0(x, g)
+        y_ref = xg_ref.float() @ w.float().t() + bias.float()
+        ok1, e1, r1 = close(y, y_ref, 2e-2)
+        ok2 = torch.equal(xg, xg_ref)
+        # row-parallel: every rank holds a different K slice of the activations and of the weight
+        torch.manual_seed(1000 * rank + it)
+        a = (torch.randn(tp * Tl, K, device=dev) * 0.5).bfloat16()
+        wr = (torch.randn(N, K, device=dev) * 0.05).bfloat16()
+        yl = ftp.gemm_rs(a, wr)
+        part = (a.float() @ wr.float().t())
+        yl_ref = tp_ops.reduce_scatter_dim0(part, g)
+        ok3, e3, r3 = close(yl, yl_ref, 2e-2)
+        res[f"it{it}"] = dict(ag=ok1, ag_err=e1, gathered=ok2, rs=ok3, rs_err=e3)
+    # autograd: fused column-parallel -> row-parallel MLP block vs the NCCL autograd twins
+    torch.manual_seed(55)
+    w1 = (torch.randn(N, K, device=dev) * 0.05).bfloat16().requires_grad_(True)
+    w2 = (torch.randn(K, N, device=dev) * 0.05).bfloat16().requires_grad_(True)
+    torch.manual_seed(200 + rank)
+    x = (torch.randn(Tl, K, device=dev) * 0.5).bfloat16().requires_grad_(True)
+    gy = (torch.randn(Tl, K, device=dev) * 0.5).bfloat16()
+    h = ftp.ag_linear(x, w1)
+    y = ftp.linear_rs(torch.nn.functional.gelu(h), w2)
+    y.backward(gy)
+    xr, w1r, w2r = [t.detach().float().requires_grad_(True) for t in (x, w1, w2)]
+    hr = tp_ops.gather_from_sequence_parallel(xr, g) @ w1r.t()
+    yr = tp_ops.reduce_scatter_to_sequence_parallel(torch.nn.functional.gelu(hr) @ w2r.t(), g)
+    yr.backward(gy.float())
+    res["autograd"] = dict(y=close(y, yr, 3e-2)[0], dx=close(x.grad, xr.grad, 3e-2)[0],
+                           dw1=close(w1.grad, w1r.grad, 5e-2)[0], dw2=close(w2.grad, w2r.grad, 5e-2)[0])
+    if bench:
+        # 7B-shaped TP=2 layer GEMMs at 8192 tokens: fused vs NCCL collective + plain GEMM, CUDA events, max over ranks
+        from gcore_b200.ops.gemm import gemm
+        T = 8192
+        Tl2 = T // tp
+        shapes = {"qkv(AG)": (4608 // tp, 3584, "ag"), "fc1(AG)": (37888 // tp, 3584, "ag"),
+                  "proj(RS)": (3584, 3584 // tp, "rs"), "fc2(RS)": (3584, 18944 // tp, "rs")}
+        timing = {}
+        for name, (n, k, kind) in shapes.items():
+            wq = (torch.randn(n, k, device=dev) * 0.02).bfloat16()
+            xl = torch.randn(Tl2, k, device=dev).bfloat16()
+            af = torch.randn(T, k, device=dev).bfloat16()
+
+            def fused():
+                return ftp.ag_gemm(xl, wq)[0] if kind == "ag" else ftp.gemm_rs(af, wq)
+
+            def unfused():
+                if kind == "ag":
+                    return gemm(tp_ops.all_gather_dim0(xl, g), wq)
+                return tp_ops.reduce_scatter_dim0(gemm(af, wq), g)
+
+            def gemm_only():
+                return gemm(af if kind == "rs" else torch.empty(T, k, device=dev, dtype=torch.bfloat16), wq)
+
+            row = {}
+            for label, fn in (("fused", fused), ("nccl_unfused", unfused), ("gemm_only", gemm_only)):
+                for _ in range(3):
+                    fn()
+                torch.cuda.synchronize()
+                dist.barrier()
+                ts = []
+                for _ in range(8):
+                    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    s.record()
+                    fn()
+                    e.record()
+                    torch.cuda.synchronize()
+                    ts.append(s.elapsed_time(e))
+                t = torch.tensor([sorted(ts)[len(ts) // 2]], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                row[label + "_ms"] = round(float(t), 4)
+            flops = 2.0 * T * n * k
+            nvl_bytes = (tp - 1) / tp * T * (k if kind == "ag" else n) * 2
+            row["roofline_ms"] = round(max(flops / 1628e9, nvl_bytes / 770e6), 4)
+            row["fused_frac_of_roofline"] = round(row["roofline_ms"] / row["fused_ms"], 3)
+            timing[name] = row
+        res["timing"] = timing
+    _lib.check_device_errors()
+    if rank == 0:
+        json.dump(res, open(out_path, "w"), indent=1)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -104,12 +104,28 @@ class TrainingEngine:
                 assert verify_lora_weight_consistency(self.adapters, ps.get_tensor_model_parallel_group()), \
                     "LoRA replicated halves differ across the TP group"
         self._apply_freeze()
+        self._maybe_enable_fused_tp()
         if not self.policy_cfg.without_optim:
             oc = self.opt_cfg
             self.ddp = DistributedDataParallel(self.model, oc.grad_reduce_in_fp32, oc.bucket_size,
                                                oc.use_distributed_optimizer, oc.overlap_grad_reduce)
             self.optimizer = DistributedOptimizer(self.ddp, oc, self.total_steps)
         return self.model, self.optimizer
+
+    def _maybe_enable_fused_tp(self):
+        """TP > 1 on GPUs: the sequence-parallel collectives of every layer run inside the GEMM kernels over NVLink
+        peer memory (``GCORE_FUSED_TP=0`` keeps the NCCL twins)."""
+        from ..models import gpt as gpt_mod
+        if (self.model.tp_size == 1 or not self.model.sequence_parallel or self.device.type != "cuda"
+                or self.backend != "native" or os.environ.get("GCORE_FUSED_TP", "1") == "0"
+                or self.policy_cfg.lora.enabled):
+            return
+        from ..parallel.symm import get_fused_tp
+        tp = self.model.tp_size
+        mb_tokens = self.policy_cfg.dynamic_mbs_target_seqlen or self.train_cfg.seq_length * self.train_cfg.train_mbs
+        rows = ((mb_tokens + 2 * self.train_cfg.seq_length) // tp + 127) // 128 * 128
+        gpt_mod.FUSED_TP["ftp"] = get_fused_tp(ps.get_tensor_model_parallel_group(), rows, self.model_cfg.hidden_size)
+        self.fused_tp_rows = rows
 
     def _apply_freeze(self):
         import re
@@ -146,7 +162,8 @@ class TrainingEngine:
     def _pack(self, samples, idx, keys=()):
         pad = max(self._tp_pad(), 1)
         if self.device.type == "cuda":
-            pad = pad * 8 if pad > 1 else 8
+            from ..models import gpt as gpt_mod
+            pad = pad * (128 if gpt_mod.FUSED_TP["ftp"] is not None else 8) if pad > 1 else 8
         mb = pack_samples(samples, idx, keys, pad_to_multiple=pad, pin=self.device.type == "cuda")
         io_counters.add_h2d(io_counters.tensor_bytes(mb.tokens, mb.position_ids, mb.cu_seqlens, mb.targets, mb.loss_mask,
                                                      mb.seq_ids, *mb.fields.values()))

@@ -29,6 +29,11 @@ from .config import ModelConfig
 from .lora import LoRAAdapter
 
 
+# Fused tensor-parallel communication (parallel/symm.py).  "ftp" is installed by the training engine when TP > 1 on a
+# GPU; "active" is switched on per layer call when the token count fits the fused kernels.
+FUSED_TP = {"ftp": None, "active": False}
+
+
 def _dtype(cfg: ModelConfig):
     return {"bfloat16": torch.bfloat16, "float32": torch.float32, "float16": torch.float16}[cfg.dtype]
 
@@ -57,6 +62,14 @@ class ParallelLinear(nn.Module):
 
     def forward(self, x):
         w = self.weight
+        ftp = FUSED_TP["ftp"] if FUSED_TP["active"] else None
+        if ftp is not None and self.lora is None and self.tp_size > 1 and self.mode in ("column", "row"):
+            # sequence-parallel layer with its collective fused into the GEMM (x is the local token shard for a
+            # column-parallel layer, the full token set for a row-parallel one)
+            mg = getattr(w, "main_grad", None) if w.requires_grad else None
+            if self.mode == "column":
+                return ftp.ag_linear(x, w, self.bias, mg)
+            return ftp.linear_rs(x, w, mg)
         y = linear(x, w, self.bias, getattr(w, "main_grad", None) if w.requires_grad else None)
         if self.lora is not None:
             y = y + self.lora(x)
@@ -95,9 +108,9 @@ class SelfAttention(nn.Module):
 
     def forward(self, x, pos, cu_seqlens, max_seqlen):
         cfg = self.cfg
-        T = x.shape[0]
         D, hq, hk = cfg.head_dim, self.hq, self.hk
-        qkv = self.linear_qkv(x)  # [T, (hq + 2 hk) * D]
+        qkv = self.linear_qkv(x)  # [T, (hq + 2 hk) * D]; with fused TP comm x is the local shard and T the full count
+        T = qkv.shape[0]
         scale = 1.0 / math.sqrt(D)
         if not cfg.qk_layernorm:
             qkv = fused_rope_qk(qkv.view(T, hq + 2 * hk, D), pos, hq + hk, cfg.rope_theta, cfg.rotary_dim,
@@ -223,6 +236,11 @@ class TransformerLayer(nn.Module):
 
     def forward(self, x, residual, pos, cu_seqlens, max_seqlen, tp_group, sp):
         cfg = self.cfg
+        ftp = FUSED_TP["ftp"]
+        fused_comm = (sp and ftp is not None and x.is_cuda and x.dtype == torch.bfloat16 and not cfg.use_mla
+                      and x.shape[0] % 128 == 0 and x.shape[0] <= ftp.max_rows)
+        if fused_comm:
+            return self._forward_fused(x, residual, pos, cu_seqlens, max_seqlen)
         h, residual = fused.rmsnorm(x, self.input_layernorm.weight, cfg.rms_norm_eps, residual)
         if sp:
             h = tp_ops.gather_from_sequence_parallel(h, tp_group)
@@ -245,6 +263,28 @@ class TransformerLayer(nn.Module):
         m = tp_ops.reduce_scatter_to_sequence_parallel(m, tp_group) if sp else \
             tp_ops.reduce_from_tensor_parallel(m, tp_group)
         return m, residual, aux
+
+
+def _layer_forward_fused(self, x, residual, pos, cu_seqlens, max_seqlen):
+    """Sequence-parallel layer whose four TP collectives run inside the GEMM kernels: the column-parallel layers
+    (QKV, FC1) are all-gather -> GEMM, the row-parallel ones (proj, FC2) GEMM -> reduce-scatter."""
+    cfg = self.cfg
+    FUSED_TP["active"] = True
+    try:
+        h, residual = fused.rmsnorm(x, self.input_layernorm.weight, cfg.rms_norm_eps, residual)
+        a = self.self_attention(h, pos, cu_seqlens, max_seqlen)
+        h, residual = fused.rmsnorm(a, self.pre_mlp_layernorm.weight, cfg.rms_norm_eps, residual)
+        if self.is_moe:
+            FUSED_TP["active"] = False
+            m, aux = self.mlp(h)
+            return m, residual, aux
+        m = self.mlp(h)
+        return m, residual, None
+    finally:
+        FUSED_TP["active"] = False
+
+
+TransformerLayer._forward_fused = _layer_forward_fused
 
 
 class GPTModel(nn.Module):

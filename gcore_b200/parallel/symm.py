@@ -183,6 +183,40 @@ def _regather(ftp: FusedTP, x_local: torch.Tensor) -> torch.Tensor:
     return out
 
 
+class PeerAllReduce:
+    """One-shot all-reduce over peer memory for small bf16 tensors (``ops/csrc/comm.cu``); in place, usable inside a
+    CUDA graph (the call epoch is kept on the device)."""
+
+    def __init__(self, group, max_elems: int, device=None):
+        self.group = group
+        self.tp = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.slot = (max_elems + 7) // 8 * 8
+        lib = _lib.kernels()
+        lib.gk_allreduce_ctas.restype = ctypes.c_int
+        self.ctas = lib.gk_allreduce_ctas()
+        self.inbox = SymmBuffer(2 * self.tp * self.slot, torch.bfloat16, group, self.device)
+        self.flags = SymmBuffer(2 * self.tp * self.ctas, torch.int32, group, self.device)
+        self.flags.t.zero_()
+        self.state = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self.ptrs = (ctypes.c_ulonglong * (2 * self.tp))(*(self.inbox.ptrs + self.flags.ptrs))
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        n = x.numel()
+        if n > self.slot or n % 8 or x.dtype != torch.bfloat16 or not x.is_contiguous():
+            dist.all_reduce(x, group=self.group)
+            return x
+        LAUNCHES["fused_comm"] += 1
+        rc = _lib.kernels().gk_allreduce_oneshot(_lib.ptr(x), _lib.ptr(x), n, self.rank, self.tp, self.slot, self.ptrs,
+                                                 _lib.ptr(self.state), _lib.ptr(_lib.err_flag(x.device)),
+                                                 _lib.stream_ptr())
+        _lib.check(rc, "gk_allreduce_oneshot")
+        return x
+
+
 _FUSED: dict = {}
 
 

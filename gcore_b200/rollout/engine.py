@@ -22,6 +22,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional, Sequence
 
@@ -237,6 +238,7 @@ class InferEngine:
         self.asleep = {"weights": False, "kv_cache": True}
         self.stats = dict(decode_steps=0, prefill_tokens=0, generated_tokens=0, graph_replays=0)
         self.record_routed_experts = False
+        self._peer_ar = None
 
     # ------------------------------------------------------------------ memory
     def _kv_bytes_per_block(self):
@@ -304,6 +306,12 @@ class InferEngine:
     # ------------------------------------------------------------------ model math (no autograd)
     def _allreduce(self, x):
         if self.tp > 1:
+            if self._peer_ar is None and self.device.type == "cuda" and not _lib.force_eager() \
+                    and x.dtype == torch.bfloat16 and os.environ.get("GCORE_PEER_ALLREDUCE", "1") != "0":
+                from ..parallel.symm import PeerAllReduce
+                self._peer_ar = PeerAllReduce(self.tp_group, self.max_running * self.cfg.hidden_size, self.device)
+            if self._peer_ar is not None and x.numel() <= self._peer_ar.slot and x.is_contiguous():
+                return self._peer_ar.all_reduce(x)  # one-shot push over NVLink peer memory (decode-sized tensors)
             dist.all_reduce(x, group=self.tp_group)
         return x
 

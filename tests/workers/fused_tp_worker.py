@@ -69,6 +69,54 @@ def main():
     yr.backward(gy.float())
     res["autograd"] = dict(y=close(y, yr, 3e-2)[0], dx=close(x.grad, xr.grad, 3e-2)[0],
                            dw1=close(w1.grad, w1r.grad, 5e-2)[0], dw2=close(w2.grad, w2r.grad, 5e-2)[0])
+    # one-shot peer all-reduce (decode-sized tensors), eager and replayed from a CUDA graph
+    from gcore_b200.parallel.symm import PeerAllReduce
+    par = PeerAllReduce(g, 128 * 3584)
+    ok_ar = True
+    for it in range(4):
+        torch.manual_seed(300 + 10 * it + rank)
+        v = torch.randn(64, 3584, device=dev).bfloat16()
+        ref = v.clone().float()
+        dist.all_reduce(ref, group=g)
+        par.all_reduce(v)
+        ok_ar = ok_ar and close(v, ref, 1e-2)[0]
+    buf = torch.zeros(64, 3584, device=dev, dtype=torch.bfloat16)
+    src = torch.randn(64, 3584, device=dev).bfloat16()
+    graph = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        buf.copy_(src)
+        par.all_reduce(buf)
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    with torch.cuda.graph(graph):
+        buf.copy_(src)
+        par.all_reduce(buf)
+    ref = src.clone().float()
+    dist.all_reduce(ref, group=g)
+    for _ in range(5):
+        graph.replay()
+    torch.cuda.synchronize()
+    res["peer_allreduce"] = dict(eager=ok_ar, graph=close(buf, ref, 1e-2)[0])
+    if bench:
+        x64 = torch.randn(64, 3584, device=dev).bfloat16()
+        row = {}
+        for label, fn in (("peer_oneshot", lambda: par.all_reduce(x64)), ("nccl", lambda: dist.all_reduce(x64, group=g))):
+            for _ in range(5):
+                fn()
+            torch.cuda.synchronize()
+            dist.barrier()
+            s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record()
+            for _ in range(50):
+                fn()
+            e0.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([s0.elapsed_time(e0) / 50], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            row[label + "_us"] = round(float(t) * 1e3, 2)
+        res["allreduce_64x3584_bf16"] = row
     if bench:
         # 7B-shaped TP=2 layer GEMMs at 8192 tokens: fused vs NCCL collective + plain GEMM, CUDA events, max over ranks
         from gcore_b200.ops.gemm import gemm

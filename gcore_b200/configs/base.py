@@ -116,6 +116,9 @@ def _build(tp, value, path):
     origin = get_origin(tp)
     if origin in (list, typing.List):
         (inner,) = get_args(tp) or (Any,)
+        if isinstance(value, dict) and value and all(str(k).isdigit() for k in value):
+            # an override such as ``a.0.b=c`` on a list that the YAML did not spell out
+            value = [value.get(str(i), value.get(i, {})) for i in range(max(int(k) for k in value) + 1)]
         if not isinstance(value, (list, tuple)):
             raise ConfigError(f"{path}: expected a list")
         return [_build(inner, v, f"{path}[{i}]") for i, v in enumerate(value)]

@@ -1,0 +1,126 @@
+"""SFT / pre-training loop on one SPMD rank (``FinetuneActor._train_loop``, gpatch_v4/actor/finetune_actor.py:393-528):
+dataloader batches -> ``TrainingEngine.finetune_step`` -> metrics / MFU -> periodic torch_dist checkpoint with dataloader
+state; resumes automatically from the newest checkpoint; stamps a heartbeat and honours host-side fault injection at
+every step boundary."""
+from __future__ import annotations
+
+import os
+import time
+from typing import Dict, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..checkpoint.torch_dist import load_checkpoint, read_latest_step, save_checkpoint
+from ..configs.base import import_from_path
+from ..core import parallel_state as ps
+from ..data.datasets import default_dataset_fn
+from ..engine.train_engine import TrainingEngine
+from ..orches.failure import FaultInjector, Heartbeat
+from ..utils.flops_counter import mfu, train_flops
+from ..utils.logging_utils import get_logger
+from ..utils.report import Reporter
+from ..utils.timers import Timers
+
+
+class FinetuneTrainer:
+    def __init__(self, config, model_cfg=None, tokenizer=None):
+        self.cfg, self.tokenizer = config, tokenizer
+        t = config.training
+        self.engine = TrainingEngine(config.policy, config.optimizer, t, None, model_cfg=model_cfg,
+                                     total_steps=t.total_training_step)
+        self.step = 0
+        self.log = get_logger("finetune")
+        self.timers = Timers()
+        rank = dist.get_rank() if dist.is_initialized() else 0
+        self.rank = rank
+        self.injector = FaultInjector(config.debug.fault_injection, rank, int(os.environ.get("GCORE_ATTEMPT", "0")))
+        hb = os.environ.get("GCORE_HEARTBEAT_DIR") or config.monitor.heartbeat_dir
+        self.heartbeat = Heartbeat(hb, rank) if hb else None
+        self.reporter: Optional[Reporter] = None
+        self.history = []
+
+    def setup(self):
+        cfg = self.cfg
+        cfg.policy.without_ref = True
+        self.engine.setup_model_and_get_optimizer()
+        ck = cfg.checkpoint
+        resume_from = ck.load_ckpt_path
+        if cfg.training.auto_load_from_save_ckpt and ck.save_ckpt_path and read_latest_step(ck.save_ckpt_path) is not None:
+            resume_from = ck.save_ckpt_path
+        meta = None
+        if resume_from and read_latest_step(resume_from) is not None:
+            self.step = load_checkpoint(self.engine, resume_from, load_optim=not ck.no_load_optim,
+                                        load_rng=not ck.no_load_rng)
+            meta = {"consumed_batches": self.engine.loaded_extra_state.get("consumed_batches", self.step),
+                    "resume_step": self.step}
+            self.log.info(f"resumed from {resume_from} at step {self.step}")
+        fn = default_dataset_fn
+        if cfg.data.py_path:
+            fn = import_from_path(cfg.data.py_path, cfg.data.fn_name or "build_dataset")
+        dp_rank, dp_size = ps.get_data_parallel_rank(), ps.get_data_parallel_world_size()
+        self.data = fn(cfg, self.tokenizer, dp_rank, dp_size, meta)
+        self.loader_iter = iter(self.data["train_dataloader"])
+        if ps.is_last_rank():
+            self.reporter = Reporter(cfg.report, os.path.join(cfg.report.log_dir, cfg.report.run_name or "finetune"))
+        return self
+
+    def _next_batch(self):
+        try:
+            return next(self.loader_iter)
+        except StopIteration:
+            s = self.data["train_sampler"]
+            s.set_epoch(getattr(s, "epoch", 0) + 1)
+            self.loader_iter = iter(self.data["train_dataloader"])
+            return next(self.loader_iter)
+
+    @staticmethod
+    def _to_samples(batch) -> list:
+        out = []
+        for toks, labels, pl in zip(batch["tokens"], batch["labels"], batch["prompt_lengths"]):
+            m = torch.zeros(toks.numel(), dtype=torch.float32)
+            m[:-1] = (labels[1:] != -100).float()
+            out.append({"tokens": toks, "loss_mask": m, "prompt_length": int(pl)})
+        return out
+
+    def train_one_step(self) -> Dict[str, float]:
+        self.injector.at_step(self.step)
+        self.timers.start("train_step")
+        samples = self._to_samples(self._next_batch())
+        m = self.engine.finetune_step(samples)
+        dt = self.timers.stop("train_step")
+        self.step += 1
+        m["time_perf/train_step"] = dt
+        if self.cfg.training.calc_mfu_freq and self.step % self.cfg.training.calc_mfu_freq == 0:
+            world = dist.get_world_size() if dist.is_initialized() else 1
+            fl = train_flops(self.engine.model_cfg, [len(s["tokens"]) for s in samples],
+                             self.cfg.policy.recompute == "full") * ps.get_data_parallel_world_size()
+            m["time_perf/mfu"] = mfu(fl, dt, world)
+        if self.heartbeat:
+            self.heartbeat.stamp(self.step)
+        if self.reporter:
+            self.reporter.log(m, self.step)
+        self.history.append(m)
+        return m
+
+    def save(self):
+        ck = self.cfg.checkpoint
+        if not ck.save_ckpt_path:
+            return None
+        return save_checkpoint(self.engine, ck.save_ckpt_path, self.step, extra_state={"consumed_batches": self.step},
+                               save_optim=not ck.no_save_optim, save_total_limit=ck.save_total_limit,
+                               save_retain_interval=ck.save_retain_interval)
+
+    def train_loop(self):
+        t = self.cfg.training
+        total = t.exit_step or t.total_training_step or 0
+        while self.step < total:
+            m = self.train_one_step()
+            if self.rank == 0 and self.step % max(self.cfg.report.log_interval, 1) == 0:
+                self.log.info(f"step {self.step} lm_loss {m['lm_loss']:.4f} grad_norm {m['grad_norm']:.3f} "
+                              f"{m['time_perf/train_step']:.3f}s")
+            if t.save_interval and self.step % t.save_interval == 0:
+                self.save()
+        if self.reporter:
+            self.reporter.close()
+        return self.history

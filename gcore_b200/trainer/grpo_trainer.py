@@ -133,6 +133,16 @@ class GrpoTrainer:
         tm.start("reward")
         samples = self.score(samples)
         tm.stop("reward")
+        metrics = self.train_on_samples(samples)
+        tm.stop("step")
+        for k in ("step", "rollout", "reward"):
+            metrics[f"time_perf/{k}"] = tm.last(k)
+        return metrics
+
+    def train_on_samples(self, samples: List[dict]) -> Dict[str, float]:
+        """Everything after rollout + reward: prev / ref log-probs, advantages, policy (and critic) update, weight
+        hand-over.  ``samples`` may come from an earlier weight version (stale rollouts)."""
+        cfg, t, tm = self.cfg, self.cfg.training, self.timers
         tm.start("compute_logps")
         if not cfg.ppo.skip_prev_logps:
             self.policy.compute_log_probs(samples, use_ref=False)
@@ -159,9 +169,8 @@ class GrpoTrainer:
         tm.start("update_weights")
         self.update_weights()
         tm.stop("update_weights")
-        tm.stop("step")
         metrics.update(self._rollout_metrics(samples))
-        for k in ("step", "rollout", "reward", "compute_logps", "generate_ppo_data", "train_step", "update_weights"):
+        for k in ("compute_logps", "generate_ppo_data", "train_step", "update_weights"):
             metrics[f"time_perf/{k}"] = tm.last(k)
         self.ppo_step += 1
         self.last_metrics = metrics

@@ -1,0 +1,126 @@
+import os
+import subprocess
+import sys
+import time
+
+import pytest
+import torch
+import yaml
+
+from gcore_b200.configs.base import ConfigError, apply_overrides, from_dict, load_config
+from gcore_b200.configs.config import FinetuneConfig, RlConfig
+from gcore_b200.core.parallel_state import plan_groups
+from gcore_b200.orches.failure import (FailureEvent, FailureType, FaultInjector, Heartbeat, InjectedFault,
+                                       MockNodeReplacer, check_liveness, run_with_recovery)
+from gcore_b200.orches.resource_allocator import allocation_from_config, expected_nnodes, sort_bundles
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_yaml_overrides_and_validation(tmp_path):
+    y = tmp_path / "rl.yaml"
+    y.write_text(yaml.safe_dump({"training": {"rollout_gbs": 16, "sampling_repeat_n": 4, "train_gbs": 64},
+                                 "policy": {"dist_config": {"tensor_model_parallel_size": 2}},
+                                 "ppo": {"ppo_ratio_eps": 0.3}}))
+    cfg = load_config(RlConfig, str(y), ["optimizer.lr=3e-6", "+task.name=demo", "ppo.ppo_clip_ratio_high=0.4",
+                                         "sampler.infer_engine_configs.0.temperature=0.7"])
+    assert cfg.optimizer.lr == 3e-6 and cfg.task["name"] == "demo"
+    assert cfg.ppo.clip_low == 0.3 and cfg.ppo.clip_high == 0.4
+    assert cfg.sampler.infer_engine_configs[0].temperature == 0.7
+    assert cfg["policy"]["dist_config"].sequence_parallel is True
+    assert cfg.training.sampling_keep_n == 4  # defaults to repeat_n
+    with pytest.raises(ConfigError):
+        from_dict(RlConfig, {"ppo": {"loss_func": "gspo"}})  # gspo forbids per-token loss
+    with pytest.raises(ConfigError):
+        from_dict(RlConfig, {"ppo": {"advantage_type": "ppo"}})  # needs critic
+    with pytest.raises(ConfigError):
+        from_dict(RlConfig, {"training": {"rollout_max_staleness": 2}})
+    with pytest.raises(ConfigError):
+        from_dict(RlConfig, {"trainnig": {}})
+    assert apply_overrides({"a": {"b": 1}}, ["~a.b", "a.c=[1,2]"]) == {"a": {"c": [1, 2]}}
+    ft = from_dict(FinetuneConfig, {"policy": {"dist_config": {"tensor_model_parallel_size": 1}}})
+    assert ft.policy.dist_config.sequence_parallel is False
+
+
+def test_plan_groups_rank_order_and_expert_groups():
+    fam, dense, expert = plan_groups(16, tp=2, pp=2, cp=2, ep=4, etp=1)
+    assert dense["dp"] == 2 and expert["edp"] == 2
+    assert fam["tp"][0] == [0, 1] and fam["cp"][0] == [0, 2] and fam["dp"][0] == [0, 4] and fam["pp"][0] == [0, 8]
+    assert fam["dp_cp"][0] == [0, 2, 4, 6]
+    assert fam["ep"][0] == [0, 1, 2, 3] and fam["edp"][0] == [0, 4]
+    # every family partitions the world
+    for name, lists in fam.items():
+        flat = sorted(r for g in lists for r in g)
+        assert flat == list(range(16)), name
+    with pytest.raises(ValueError):
+        plan_groups(6, tp=4)
+
+
+def test_allocation_modes():
+    base = {"training": {"rollout_gbs": 8, "sampling_repeat_n": 8, "train_gbs": 64},
+            "policy": {"dist_config": {"tensor_model_parallel_size": 2, "nnodes": 1}},
+            "sampler": {"infer_engine_configs": [{"dist_config": {"tensor_model_parallel_size": 2}}]}}
+    a = allocation_from_config(from_dict(RlConfig, base))
+    assert a.roles["train"].gpus == list(range(8)) and a.roles["sampler"].gpus == list(range(8))
+    assert a.roles["train"].dp == 4 and len(a.roles["sampler"].engines()) == 4
+    d = dict(base, placement_type="disaggregated")
+    a = allocation_from_config(from_dict(RlConfig, d), role_gpus={"train": 4, "sampler": 4})
+    assert a.roles["train"].gpus == [0, 1, 2, 3] and a.roles["sampler"].gpus == [4, 5, 6, 7]
+    with pytest.raises(ValueError):
+        allocation_from_config(from_dict(RlConfig, d), role_gpus={"train": 3, "sampler": 5})
+    assert expected_nnodes(17, 8) == 3
+    assert sort_bundles([("10.0.0.2", 1), ("10.0.0.1", 3), ("10.0.0.1", 0)]) == [2, 1, 0]
+
+
+def test_failure_primitives(tmp_path):
+    hb = Heartbeat(str(tmp_path), 0)
+    hb.stamp(3)
+    Heartbeat(str(tmp_path), 1).stamp(3)
+    assert check_liveness(str(tmp_path), 2, max_wait_s=60) is None
+    ev = check_liveness(str(tmp_path), 2, max_wait_s=60, now=time.time() + 120)
+    assert ev is not None and ev.type == FailureType.HANG
+    inj = FaultInjector({"raise_at_step": 2, "rank": 1, "only_attempt": 0}, rank=1, attempt=0)
+    inj.at_step(1)
+    with pytest.raises(InjectedFault):
+        inj.at_step(2)
+    FaultInjector({"raise_at_step": 2, "rank": 1, "only_attempt": 0}, rank=1, attempt=1).at_step(2)
+    calls = []
+
+    def attempt(i):
+        calls.append(i)
+        return FailureEvent(FailureType.CRASH, rank=0) if i == 0 else None
+
+    rep = MockNodeReplacer()
+    events = run_with_recovery(attempt, max_restart_attempts=2, node_replacer=rep)
+    assert calls == [0, 1] and len(events) == 1 and len(rep.evicted) == 1 and rep.provisioned == 1
+    with pytest.raises(RuntimeError):
+        run_with_recovery(lambda i: FailureEvent(FailureType.HANG), max_restart_attempts=1)
+
+
+def test_crash_is_detected_and_job_resumes_from_checkpoint(tmp_path):
+    """Two gloo ranks run SFT; rank 1 raises at step 3 of the first attempt.  The launcher reports a CRASH, the
+    recovery loop relaunches, the second attempt resumes from the step-2 checkpoint and finishes."""
+    from gcore_b200.orches.launcher import LocalLauncher
+    ckpt = tmp_path / "ckpt"
+    cfg = {"training": {"train_gbs": 4, "train_mbs": 2, "exit_step": 5, "save_interval": 2, "seq_length": 64,
+                        "calc_mfu_freq": 0},
+           "policy": {"model_arch": "tiny_llama", "model_config": {"dtype": "float32"}, "recompute": "none"},
+           "optimizer": {"lr": 1e-3, "lr_decay_style": "constant"},
+           "data": {"synthetic": {"num_samples": 64, "seq_len": 64, "loss_tokens": 32}},
+           "checkpoint": {"save_ckpt_path": str(ckpt)},
+           "report": {"log_dir": str(tmp_path / "logs")},
+           "debug": {"fault_injection": {"raise_at_step": 3, "rank": 1, "only_attempt": 0}}}
+    y = tmp_path / "sft.yaml"
+    y.write_text(yaml.safe_dump(cfg))
+    launcher = LocalLauncher(2, heartbeat_dir=str(tmp_path / "hb"), max_wait_s=600, poll_s=0.2,
+                             extra_env={"PYTHONPATH": ROOT, "OMP_NUM_THREADS": "2"})
+
+    def attempt(i):
+        launcher.launch(["-m", "gcore_b200.entry.train_lm_finetune", "--config", str(y)], attempt=i)
+        return launcher.wait()
+
+    events = run_with_recovery(attempt, max_restart_attempts=1, node_replacer=MockNodeReplacer())
+    assert len(events) == 1 and events[0].type == FailureType.CRASH
+    from gcore_b200.checkpoint.torch_dist import read_latest_step
+    assert read_latest_step(str(ckpt)) == 5
+    assert sorted(os.listdir(ckpt))[:3] == ["iter_0000002", "iter_0000004", "iter_0000005"]

@@ -350,7 +350,17 @@ class GPTModel(nn.Module):
             key = zlib.crc32(f"{self.layer_offset}:{name}".encode()) ^ seed
             full_numel = p.numel() * (self.tp_size if mode in ("column", "row") else 1)
             with torch.no_grad():
-                if self.tp_size > 1 and mode in ("column", "row") and full_numel <= (1 << 26) and p.dim() == 2:
+                if mode == "expert" and self.ep_size > 1:
+                    # experts are drawn as one [E_total, ...] tensor and sliced, so EP > 1 equals the EP = 1 model
+                    ep_rank = ps.get_expert_model_parallel_rank()
+                    if p.numel() * self.ep_size <= (1 << 26):
+                        g = torch.Generator(device="cpu").manual_seed(key & 0x7FFFFFFF)
+                        full = torch.randn(p.shape[0] * self.ep_size, *p.shape[1:], generator=g) * mod_std
+                        p.copy_(full[ep_rank * p.shape[0]:(ep_rank + 1) * p.shape[0]])
+                    else:
+                        g = torch.Generator(device=p.device).manual_seed((key + 104729 * ep_rank) & 0x7FFFFFFF)
+                        p.copy_(torch.randn(p.shape, generator=g, device=p.device, dtype=torch.float32) * mod_std)
+                elif self.tp_size > 1 and mode in ("column", "row") and full_numel <= (1 << 26) and p.dim() == 2:
                     g = torch.Generator(device="cpu").manual_seed(key & 0x7FFFFFFF)
                     if mode == "column":
                         full = torch.randn(p.shape[0] * self.tp_size, p.shape[1], generator=g) * mod_std

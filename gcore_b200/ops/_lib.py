@@ -117,6 +117,10 @@ def _declare_kernels(lib: ctypes.CDLL):
     P, I, L, F = c_void_p, c_int, c_ll, c_float
     d("gk_gemm_bf16", [P, L, L, I, P, L, L, I, P, L, I, I, I, P, I, I, F, I, I, I, I, I, I, I, P, I, L, I, P, P, P, P])
     d("gk_gemm_comm", [I, P, L, P, L, L, I, P, L, P, I, I, I, I, I, I, I, ctypes.c_uint, P, L, P, P])
+    d("gk_act_quant_1x128", [P, P, P, P, L, I, I, P])
+    d("gk_weight_quant_128x128", [P, P, P, P, I, I, I, P])
+    d("gk_fp4_quant_1x32", [P, P, P, P, P, L, P])
+    d("gk_gemm_fp8_blockscaled", [P, L, P, L, P, P, P, L, I, I, I, I, P, P])
     d("gk_allreduce_oneshot", [P, P, L, I, I, L, P, P, P, P])
     d("gk_gemm_splitk_scratch", [I, I, I, I, ctypes.POINTER(L), ctypes.POINTER(L)], None)
     d("gk_rmsnorm_fwd", [P, P, P, P, P, P, I, I, F, P])

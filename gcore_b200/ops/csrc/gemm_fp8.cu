@@ -1,0 +1,178 @@
+// Block-scaled e4m3 GEMM on tcgen05 (kind::f8f6f4): C[M,N] = sum_kb sA[m,kb] * sB[n/128,kb] * (A_kb * B_kb^T),
+// A [M,K] e4m3 with one fp32 scale per (row, 128-wide K block), B [N,K] e4m3 with one fp32 scale per 128x128 block
+// (the DeepSeek-V3 recipe; the reference's TileLang version is gfused/mygemm_fp8.py:45-97).
+//
+// Two-level accumulation: every 128-deep K block is multiplied on the tensor core into a fresh TMEM accumulator
+// (two buffers, ping-pong); the four epilogue warps pull that partial product out of TMEM, apply sA * sB and add it
+// into fp32 register accumulators while the tensor core already works on the next block.  bf16 or fp32 output.
+#include "ptx.cuh"
+#include "host_utils.h"
+
+namespace gk8 {
+using namespace gk;
+
+constexpr int BM = 128, BN = 128, BK = 128;  // BK bytes = 128 = one swizzle row of e4m3
+constexpr int UMMA_K = 32;
+constexpr int STAGES = 5;
+constexpr int THREADS = 192;
+constexpr int STAGE_BYTES = (BM + BN) * BK;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+
+struct P8 {
+  int M, N, K;
+  const float* sA;  // [M, KB]
+  const float* sB;  // [ceil(N/128), KB]
+  void* C;
+  long long ldc;
+  int out_fp32;
+  int* err;
+};
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, P8 p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;   // 2
+  uint64_t* tempty = tfull + 2;       // 2 (128 arrivals)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tempty + 2);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int mt = (p.M + BM - 1) / BM;
+  const int m0 = (blockIdx.x % mt) * BM, n0 = (blockIdx.x / mt) * BN;
+  const int KB = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 128); }
+    fence_barrier_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 2) { tmem_alloc(tmem_holder, 256); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
+
+  if (warp == 0) {
+    bool ok = true;
+    for (int kb = 0; kb < KB && ok; ++kb) {
+      const int s = kb % STAGES;
+      const uint32_t ph = (kb / STAGES) & 1;
+      ok = mbar_wait(&empty[s], ph ^ 1, p.err, ERR_WAIT_EMPTY);
+      if (!ok) break;
+      if (lane == 0) {
+        uint8_t* sa = smem + s * STAGE_BYTES;
+        mbar_expect_tx(&full[s], STAGE_BYTES);
+        tma_load_2d(sa, &tmA, &full[s], kb * BK, m0);
+        tma_load_2d(sa + BM * BK, &tmB, &full[s], kb * BK, n0);
+      }
+      __syncwarp();
+    }
+  } else if (warp == 1) {
+    constexpr uint32_t idesc = make_idesc(BM, BN, 0, 0, 0, 0);  // e4m3 x e4m3 -> f32
+    bool ok = true;
+    for (int kb = 0; kb < KB && ok; ++kb) {
+      const int s = kb % STAGES, a = kb & 1;
+      ok = mbar_wait(&tempty[a], ((kb >> 1) & 1) ^ 1, p.err, ERR_WAIT_TMEM_EMPTY);
+      if (!ok) break;
+      ok = mbar_wait(&full[s], (kb / STAGES) & 1, p.err, ERR_WAIT_FULL);
+      if (!ok) break;
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t ab = smem_u32(smem + s * STAGE_BYTES), bb = ab + BM * BK;
+#pragma unroll
+        for (int k4 = 0; k4 < BK / UMMA_K; ++k4) {
+          umma_f8(tmem_base + a * BN, make_smem_desc_sw128(ab + k4 * UMMA_K, 16, 1024),
+                  make_smem_desc_sw128(bb + k4 * UMMA_K, 16, 1024), idesc, k4 > 0 ? 1u : 0u);
+        }
+        umma_commit(&empty[s]);
+        umma_commit(&tfull[a]);
+      }
+      __syncwarp();
+    }
+  } else {
+    const int quad = warp & 3;
+    const int row = m0 + quad * 32 + lane;
+    float acc[BN];
+#pragma unroll
+    for (int j = 0; j < BN; ++j) acc[j] = 0.f;
+    bool ok = true;
+    const int nb = n0 / 128;
+    for (int kb = 0; kb < KB && ok; ++kb) {
+      const int a = kb & 1;
+      ok = mbar_wait(&tfull[a], (kb >> 1) & 1, p.err, ERR_WAIT_TMEM_FULL);
+      if (!ok) break;
+      tc_fence_after();
+      const float sc = (row < p.M ? p.sA[static_cast<long long>(row) * KB + kb] : 0.f) * p.sB[static_cast<long long>(nb) * KB + kb];
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + a * BN;
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[c * 32 + j] += sc * __uint_as_float(r[j]);
+      }
+      tc_fence_before();
+      mbar_arrive(&tempty[a]);
+    }
+    if (ok && row < p.M) {
+#pragma unroll
+      for (int c = 0; c < BN / 8; ++c) {
+        const int col = n0 + c * 8;
+        if (col + 8 <= p.N && (p.ldc & 7) == 0) {
+          if (p.out_fp32) {
+            float4* d = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col);
+            d[0] = make_float4(acc[c * 8], acc[c * 8 + 1], acc[c * 8 + 2], acc[c * 8 + 3]);
+            d[1] = make_float4(acc[c * 8 + 4], acc[c * 8 + 5], acc[c * 8 + 6], acc[c * 8 + 7]);
+          } else {
+            uint4 o;
+            o.x = pack_bf16x2(acc[c * 8], acc[c * 8 + 1]);
+            o.y = pack_bf16x2(acc[c * 8 + 2], acc[c * 8 + 3]);
+            o.z = pack_bf16x2(acc[c * 8 + 4], acc[c * 8 + 5]);
+            o.w = pack_bf16x2(acc[c * 8 + 6], acc[c * 8 + 7]);
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col) = o;
+          }
+        } else {
+          for (int j = 0; j < 8; ++j) {
+            if (col + j < p.N) {
+              if (p.out_fp32) reinterpret_cast<float*>(p.C)[static_cast<long long>(row) * p.ldc + col + j] = acc[c * 8 + j];
+              else reinterpret_cast<__nv_bfloat16*>(p.C)[static_cast<long long>(row) * p.ldc + col + j] = __float2bfloat16(acc[c * 8 + j]);
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) { tc_fence_after(); tmem_dealloc(tmem_base, 256); }
+}
+
+}  // namespace gk8
+
+using namespace gk8;
+
+// A [M,K] and B [N,K] are e4m3 bytes (row-major, K contiguous, K % 16 == 0); sA fp32 [M, ceil(K/128)],
+// sB fp32 [ceil(N/128), ceil(K/128)].
+GK_EXPORT int gk_gemm_fp8_blockscaled(const void* A, long long lda, const void* B, long long ldb, const float* sA,
+                                      const float* sB, void* C, long long ldc, int out_fp32, int M, int N, int K,
+                                      int* err, void* stream) {
+  if ((lda & 15) || (ldb & 15) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -1;
+  CUtensorMap tmA, tmB;
+  if (gk::make_tmap_2d(&tmA, A, 1, M, K, lda, BM, BK, true)) return -2;
+  if (gk::make_tmap_2d(&tmB, B, 1, N, K, ldb, BN, BK, true)) return -3;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+      return -4;
+    configured = true;
+  }
+  P8 p;
+  p.M = M; p.N = N; p.K = K; p.sA = sA; p.sB = sB; p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32; p.err = err;
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  gemm_fp8_kernel<<<tiles, THREADS, SMEM_BYTES, reinterpret_cast<cudaStream_t>(stream)>>>(tmA, tmB, p);
+  return gk::launch_status();
+}

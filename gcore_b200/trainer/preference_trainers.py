@@ -1,0 +1,97 @@
+"""Preference / reward-model / distillation steps built on ``TrainingEngine`` primitives.
+
+* ``dpo_step``      - DPO on (chosen, rejected) pairs with a frozen reference (``DpoTrainer`` / ``DpoActor``,
+  gpatch_v4/training_backend/loss_factory.py DPO losses): sequence log-probs from the packed forward.
+* ``rm_step``       - Bradley-Terry reward-model training with a value-head engine (``RewardTrainer``).
+* ``distill_step``  - on-policy distillation: student rollouts scored by a teacher engine; the per-token advantage is
+  the teacher-student log-prob gap (``advantage_type=on_policy_distill``); off-policy distillation is SFT on teacher
+  samples with an optional reverse-KL term on top-k teacher log-probs.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Sequence
+
+import torch
+import torch.distributed as dist
+
+from ..core import parallel_state as ps
+from ..engine.train_engine import TrainingEngine, backend_scope
+from ..loss import policy_loss as PL
+
+
+def _seq_logps(engine: TrainingEngine, model, samples: Sequence[dict], grad: bool) -> torch.Tensor:
+    """Sum of masked token log-probs per sample, differentiable when ``grad``."""
+    out = []
+    ctx = torch.enable_grad() if grad else torch.no_grad()
+    with ctx, backend_scope(engine.backend):
+        for idx in engine._microbatches(samples, forward_only=not grad):
+            mb = engine._pack(samples, idx)
+            hidden, _ = engine._hidden(model, mb)
+            lp, _ = engine._logprob_entropy(model, hidden, mb.targets, False)
+            seg = torch.zeros(mb.num_seqs + 1, dtype=lp.dtype, device=lp.device).index_add(0, mb.seq_ids.long(),
+                                                                                           lp * mb.loss_mask)
+            out.append((idx, seg[:len(idx)]))
+    res = [None] * len(samples)
+    for idx, seg in out:
+        for j, i in enumerate(idx):
+            res[i] = seg[j]
+    return torch.stack(res)
+
+
+def dpo_step(engine: TrainingEngine, chosen: List[dict], rejected: List[dict], beta: float = 0.1,
+             label_smoothing: float = 0.0, reference_free: bool = False, sft_coef: float = 0.0) -> Dict[str, float]:
+    assert len(chosen) == len(rejected)
+    engine.model.train()
+    engine.ddp.zero_grad_buffer()
+    allc = list(chosen) + list(rejected)
+    if reference_free or engine.ref_model is None:
+        ref = torch.zeros(len(allc), device=engine.device)
+    else:
+        ref = _seq_logps(engine, engine.ref_model, allc, grad=False)
+    pol = _seq_logps(engine, engine.model, allc, grad=True)
+    n = len(chosen)
+    loss, m = PL.dpo_loss(pol[:n], pol[n:], ref[:n], ref[n:], beta, label_smoothing, reference_free)
+    if sft_coef:
+        ntok = sum(float(torch.as_tensor(s.get("loss_mask", s.get("mask"))).sum()) for s in chosen)
+        loss = loss - sft_coef * pol[:n].sum() / max(ntok, 1.0)
+    dp = ps.get_data_parallel_world_size(with_context_parallel=True)
+    (loss / 1.0).backward()
+    engine.ddp.finish_grad_sync(extra_scale=1.0)
+    lr = engine.optimizer.step()
+    engine.step += 1
+    out = {"dpo/loss": float(loss.detach()), "lr": lr, "grad_norm": float(engine.optimizer.last_grad_norm)}
+    out.update({k: float(v) for k, v in m.items()})
+    return out
+
+
+def rm_step(engine: TrainingEngine, chosen: List[dict], rejected: List[dict], margin: float = 0.0) -> Dict[str, float]:
+    """``engine`` has a value head; the score of a sequence is the head's output at its last token."""
+    assert engine.value_head
+    engine.model.train()
+    engine.ddp.zero_grad_buffer()
+    allc = list(chosen) + list(rejected)
+    scores = []
+    with backend_scope(engine.backend):
+        for idx in engine._microbatches(allc):
+            mb = engine._pack(allc, idx)
+            v, _ = engine._hidden(engine.model, mb)
+            last = (mb.cu_seqlens[1:len(idx) + 1] - 1).long()
+            scores.append((idx, v[last]))
+    s = [None] * len(allc)
+    for idx, sc in scores:
+        for j, i in enumerate(idx):
+            s[i] = sc[j]
+    s = torch.stack(s)
+    n = len(chosen)
+    loss, m = PL.rm_bt_loss(s[:n], s[n:], margin)
+    loss.backward()
+    engine.ddp.finish_grad_sync(extra_scale=1.0)
+    lr = engine.optimizer.step()
+    engine.step += 1
+    return {"rm/loss": float(loss.detach()), "rm/acc": float(m["rm/acc"]), "lr": lr}
+
+
+def attach_teacher_logprobs(teacher: TrainingEngine, samples: List[dict]) -> List[dict]:
+    """Scores student samples under the teacher (forward only) -> ``teacher_logprobs`` for ``on_policy_distill``."""
+    teacher.compute_log_probs(samples, use_ref=False, with_entropy=False, out_key="teacher_logprobs")
+    return samples

@@ -372,3 +372,42 @@ def test_flash_attn_packed_qkv_bwd_matches_unpacked():
     ref = attn_varlen_ref(x[:, :hq], x[:, hq:hq + hk], x[:, hq + hk:], cu, cu, True)
     ref.backward(go.float())
     _close(qkv.grad, x.grad, rtol=3e-2, atol=3e-2)
+
+
+def test_quantisers_match_eager_definitions():
+    from gcore_b200.ops import quant
+    torch.manual_seed(16)
+    x = _rand(257, 512, scale=3.0)
+    for pow2 in (False, True):
+        q, s = quant.quant_act_1x128(x, pow2)
+        qr, sr = quant.act_quant_1x128_ref(x, pow2)
+        assert torch.allclose(s, sr, rtol=1e-6)
+        assert (q.float() - qr.float()).abs().max() <= 32  # at most one e4m3 code step at the largest magnitude
+        assert (quant.dequant_1x128(q, s) - x.float()).abs().max() / x.float().abs().max() < 0.07
+    w = _rand(300, 640, scale=0.1)
+    q, s = quant.quant_weight_128x128(w)
+    qr, sr = quant.weight_quant_128x128_ref(w)
+    assert torch.allclose(s, sr, rtol=1e-6) and q.shape == (300, 640)
+    assert (quant.dequant_128x128(q, s) - w.float()).abs().max() / w.float().abs().max() < 0.07
+    y = x.clone()
+    quant.qat_fp8_(y, "1x128", pow2=True)
+    qr, sr = quant.act_quant_1x128_ref(x, True)
+    _close(y, quant.dequant_1x128(qr, sr), rtol=2e-2, atol=2e-2)
+    packed, e8, s32 = quant.quant_fp4_1x32(x)
+    codes, sr, dq = quant.fp4_quant_1x32_ref(x)
+    assert torch.equal(s32, sr)
+    assert torch.equal(packed, (codes[0::2] | (codes[1::2] << 4)))
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (300, 520, 1024), (1024, 2048, 7168)])
+def test_gemm_fp8_blockscaled(M, N, K):
+    from gcore_b200.ops import quant
+    torch.manual_seed(17)
+    a, b = _rand(M, K, scale=1.0), _rand(N, K, scale=0.05)
+    aq, as_ = quant.quant_act_1x128(a)
+    bq, bs = quant.quant_weight_128x128(b)
+    ref = quant.dequant_1x128(aq, as_) @ quant.dequant_128x128(bq, bs).t()
+    out = quant.gemm_fp8_blockscaled(aq, as_, bq, bs)
+    _close(out, ref, rtol=1e-2, atol=1e-2)
+    full = a.float() @ b.float().t()
+    assert (out.float() - full).abs().max() / full.abs().max() < 0.1

@@ -1,0 +1,76 @@
+"""gloo worker for the parallelism parity tests: mode = tp | ep | ckpt."""
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+from gcore_b200.configs.config import OptimizerConfig, PolicyConfig, TrainingConfig  # noqa: E402
+from gcore_b200.core import parallel_state as ps  # noqa: E402
+from gcore_b200.engine.train_engine import TrainingEngine  # noqa: E402
+from gcore_b200.models.config import ModelConfig, get_preset  # noqa: E402
+
+
+def samples(n, seed, L=48, vocab=1024):
+    g = torch.Generator().manual_seed(seed)
+    out = []
+    for i in range(n):
+        ln = int(torch.randint(L // 2, L + 1, (1,), generator=g))
+        t = torch.randint(3, vocab, (ln,), generator=g)
+        m = torch.zeros(ln)
+        m[ln // 3:ln - 1] = 1
+        out.append({"tokens": t, "loss_mask": m})
+    return out
+
+
+def engine(mcfg, tp, sp=True, lr=1e-3):
+    pc = PolicyConfig(recompute="none", without_ref=True)
+    pc.dist_config.tensor_model_parallel_size = tp
+    pc.dist_config.sequence_parallel = sp and tp > 1
+    oc = OptimizerConfig(lr=lr, lr_decay_style="constant", weight_decay=0.0, max_grad_norm=1.0)
+    tc = TrainingConfig(train_mbs=2, train_gbs=8)
+    e = TrainingEngine(pc, oc, tc, model_cfg=mcfg)
+    e.setup_model_and_get_optimizer(seed=11)
+    return e
+
+
+def main():
+    mode, out = sys.argv[1], sys.argv[2]
+    ps.init_distributed("gloo")
+    world, rank = dist.get_world_size(), dist.get_rank()
+    res = {}
+    if mode == "tp":
+        ps.initialize_model_parallel(tp=2)
+        mcfg = get_preset("tiny_llama", dtype="float32", qkv_bias=True)
+        e = engine(mcfg, 2)
+        losses = []
+        for s in range(4):
+            losses.append(e.finetune_step(samples(8, 50 + s))["lm_loss"])  # TP ranks see the same data
+        res = {"losses": losses, "grad_norm": float(e.optimizer.last_grad_norm)}
+        if len(sys.argv) > 3:
+            from gcore_b200.checkpoint.hf import save_hf
+            from gcore_b200.checkpoint.torch_dist import save_checkpoint
+            save_checkpoint(e, os.path.join(sys.argv[3], "ckpt"), 4)
+            save_hf(e, os.path.join(sys.argv[3], "hf"))
+    elif mode == "ep":
+        ps.initialize_model_parallel(tp=1, ep=2)
+        mcfg = ModelConfig(arch="qwen3_moe", num_layers=2, hidden_size=128, num_attention_heads=4, num_kv_heads=2,
+                           ffn_hidden_size=256, vocab_size=512, num_experts=8, moe_top_k=2, moe_ffn_hidden_size=64,
+                           moe_aux_loss_coef=1e-2, dtype="float32", qk_layernorm=True)
+        e = engine(mcfg, 1)
+        losses = []
+        for s in range(3):
+            batch = samples(8, 70 + s, vocab=512)
+            losses.append(e.finetune_step(batch[rank::world])["lm_loss"])  # EP ranks are also DP ranks
+        res = {"losses": losses}
+    if rank == 0:
+        json.dump(res, open(out, "w"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -9,10 +9,17 @@ ranks with replicated parameters counted once, linear / cosine / WSD learning-ra
 
 Dense parameters reduce over the DP x CP group; expert parameters over the expert-data-parallel group.
 The update itself is one fused kernel per shard (``ops.optim.adam_step``): unscale + clip + AdamW + bf16 write.
+
+On GPUs of one NVLink domain the buffers live in symmetric memory and the collective halves of the step move into
+the optimizer kernel (``ops/csrc/zero1.cu``): the shard owner pulls its gradient shard from every peer, applies
+AdamW and pushes the bf16 parameters into every peer's buffer; NCCL moves no gradient or parameter bytes
+(``GCORE_FUSED_DP=0`` restores the reduce-scatter / all-gather path).
 """
 from __future__ import annotations
 
+import ctypes
 import math
+import os
 from dataclasses import dataclass
 from typing import Dict, List, Optional
 
@@ -20,7 +27,20 @@ import torch
 import torch.distributed as dist
 
 from ..core import parallel_state as ps
+from ..ops import _lib
 from ..ops import optim as optim_ops
+
+
+LAUNCHES = {"zero1": 0}
+
+
+def _peer_memory_ok(group, dev, dt, grad_dtype) -> bool:
+    if dev.type != "cuda" or not dist.is_initialized() or os.environ.get("GCORE_FUSED_DP", "1") == "0":
+        return False
+    n = _group_size(group)
+    if n < 2 or n > 8 or dt != torch.bfloat16 or grad_dtype != torch.float32 or not _lib.use_native():
+        return False
+    return hasattr(_lib.kernels(), "gk_zero1_step")
 
 
 def _group_size(g):
@@ -72,7 +92,21 @@ class ParamAndGradBuffer:
             off = (off + align - 1) // align * align
             self.buckets.append(Bucket(bstart, off, bparams))
         self.numel = off
-        self.param_data = torch.zeros(self.numel, dtype=dt, device=dev)
+        # Peer-memory mode: parameter and gradient buffers live in symmetric memory so that the optimizer kernel of
+        # every rank can pull gradient shards from, and push parameter shards to, its data-parallel peers.
+        self.peer = (use_distributed_optimizer and _peer_memory_ok(group, dev, dt, grad_dtype))
+        self.param_sym = self.grad_sym = self.flag_sym = None
+        if self.peer:
+            from .symm import SymmBuffer
+            self.param_sym = SymmBuffer(self.numel, dt, group, dev)
+            self.param_data = self.param_sym.t.zero_()
+            self.flag_sym = SymmBuffer(64 * 8, torch.int32, group, dev)
+            self.flag_sym.t.zero_()
+            self.flag_ptrs = torch.tensor(self.flag_sym.ptrs, dtype=torch.int64, device=dev)
+            self.barrier_epoch = 0
+            self.pending_scale = None
+        else:
+            self.param_data = torch.zeros(self.numel, dtype=dt, device=dev)
         self.grad_data = None
         self.param_to_bucket: Dict[int, Bucket] = {}
         for b in self.buckets:
@@ -90,15 +124,42 @@ class ParamAndGradBuffer:
     # ---- gradient storage can be released between training phases (colocated rollout needs the memory)
     def allocate_grads(self):
         if self.grad_data is None:
-            self.grad_data = torch.zeros(self.numel, dtype=self.grad_dtype, device=self.param_data.device)
+            if self.peer:
+                if self.grad_sym is None:
+                    from .symm import SymmBuffer
+                    self.grad_sym = SymmBuffer(self.numel, self.grad_dtype, self.group, self.param_data.device)
+                    self.ptrs = (ctypes.c_ulonglong * (2 * self.dp))(*(self.grad_sym.ptrs + self.param_sym.ptrs))
+                self.grad_data = self.grad_sym.t.zero_()
+            else:
+                self.grad_data = torch.zeros(self.numel, dtype=self.grad_dtype, device=self.param_data.device)
         for p in self.params:
             o = self.offsets[id(p)]
             p.main_grad = self.grad_data[o:o + p.numel()].view(p.shape) if p.requires_grad else None
 
     def release_grads(self):
+        if self.peer:
+            return  # symmetric buffers are rendezvoused once and stay mapped on the peers
         self.grad_data = None
         for p in self.params:
             p.main_grad = None
+
+    # ---- peer-memory optimizer path (ops/csrc/zero1.cu)
+    def peer_barrier(self):
+        """Device-side barrier over the reduction group on the current stream (bounded wait, error word on expiry)."""
+        self.barrier_epoch += 1
+        _lib.check(_lib.kernels().gk_peer_barrier(_lib.ptr(self.flag_ptrs), self.dp_rank, self.dp, 0,
+                                                  self.barrier_epoch, _lib.ptr(_lib.err_flag(self.param_data.device)),
+                                                  _lib.stream_ptr()), "peer_barrier")
+        LAUNCHES["zero1"] += 1
+
+    def zero1(self, mode: int, sh: dict, scale: float, clip, sumsq, lr=0.0, cfg=None, step=1, wd=0.0):
+        s, e = sh["s"], sh["e"]
+        _lib.check(_lib.kernels().gk_zero1_step(
+            mode, self.ptrs, self.dp_rank, self.dp, s, e - s, _lib.ptr(self.grad_data[s:e]), _lib.ptr(sh["master"]),
+            _lib.ptr(sh["m"]), _lib.ptr(sh["v"]), float(scale), _lib.ptr(clip), _lib.ptr(sumsq), float(lr),
+            float(cfg.adam_beta1 if cfg else 0.9), float(cfg.adam_beta2 if cfg else 0.999),
+            float(cfg.adam_eps if cfg else 1e-8), float(wd), int(step), 0, _lib.stream_ptr()), "zero1_step")
+        LAUNCHES["zero1"] += 1
 
     def zero_grad(self):
         if self.grad_data is not None:
@@ -207,6 +268,11 @@ class DistributedDataParallel:
         handles = []
         for buf in self.buffers:
             scale = extra_scale / buf.dp
+            if buf.peer:
+                # reduce-scatter happens inside the optimizer kernels (peer pulls); only order the ranks here
+                buf.pending_scale = scale
+                buf.peer_barrier()
+                continue
             for bucket in buf.buckets:
                 h = buf.reduce_bucket(bucket, scale, async_op=True)
                 if h is not None:
@@ -274,7 +340,7 @@ class DistributedOptimizer:
         self.offloaded = False
 
     # ------------------------------------------------------------------ grad norm / clip
-    def _local_sumsq(self) -> torch.Tensor:
+    def _local_sumsq(self, skip_peer: bool = False) -> torch.Tensor:
         """Sum of squares of this rank's gradient shards, with parameters replicated across TP counted on TP rank 0
         only (their shard values are identical on every TP rank)."""
         dev = self.shards[0]["master"].device
@@ -282,6 +348,8 @@ class DistributedOptimizer:
         tp_rank = ps.get_tensor_model_parallel_rank()
         for sh in self.shards:
             buf, s, e = sh["buf"], sh["s"], sh["e"]
+            if skip_peer and buf.peer:
+                continue
             g = buf.grad_data[s:e]
             if tp_rank == 0 or ps.get_tensor_model_parallel_world_size() == 1:
                 optim_ops.sumsq(g, total)
@@ -295,8 +363,10 @@ class DistributedOptimizer:
                             optim_ops.sumsq(buf.grad_data[lo:hi], total)
         return total
 
-    def grad_norm(self) -> torch.Tensor:
-        total = self._local_sumsq()
+    def grad_norm(self, skip_peer: bool = False, extra=None) -> torch.Tensor:
+        total = self._local_sumsq(skip_peer)
+        if extra is not None:
+            total += extra
         if dist.is_initialized() and dist.get_world_size() > 1:
             # shards partition the DP x CP group, model-parallel ranks hold different parameters: sum over everyone
             dist.all_reduce(total)
@@ -308,24 +378,54 @@ class DistributedOptimizer:
         self.step_count += 1
         if lr is None:
             lr = lr_at_step(cfg, self.step_count, self.total_steps)
-        norm = self.grad_norm()
+        clipping = bool(cfg.max_grad_norm and cfg.max_grad_norm > 0)
+        peer_shards = [sh for sh in self.shards if sh["buf"].peer and sh["buf"].pending_scale is not None]
+        fused_sumsq = None
+        if peer_shards:
+            if clipping:
+                # without tensor parallelism no parameter is replicated, so the kernel's own sum of squares is exact
+                if ps.get_tensor_model_parallel_world_size() == 1:
+                    fused_sumsq = torch.zeros(1, dtype=torch.float32, device=peer_shards[0]["master"].device)
+                for sh in peer_shards:  # pull + sum + scale -> own fp32 shard
+                    sh["buf"].zero1(1, sh, sh["buf"].pending_scale, None, fused_sumsq)
+            else:
+                fused_sumsq = torch.zeros(1, dtype=torch.float32, device=peer_shards[0]["master"].device)
+                for sh in peer_shards:  # pull + Adam + push in one pass
+                    buf = sh["buf"]
+                    buf.zero1(3, sh, buf.pending_scale, None, fused_sumsq, lr, cfg, self.step_count,
+                              cfg.weight_decay * getattr(buf, "weight_decay_mult", 1.0))
+        if fused_sumsq is None:
+            norm = self.grad_norm()
+        else:
+            norm = self.grad_norm(skip_peer=True, extra=fused_sumsq)
         self.last_grad_norm = norm
         clip = None
-        if cfg.max_grad_norm and cfg.max_grad_norm > 0:
+        if clipping:
             clip = torch.clamp(cfg.max_grad_norm / (norm + 1e-6), max=1.0)
         for sh in self.shards:
             buf, s, e = sh["buf"], sh["s"], sh["e"]
+            if buf.peer and buf.pending_scale is not None:
+                if clipping:  # Adam on the reduced shard + push of the bf16 parameters to every rank
+                    buf.zero1(2, sh, 1.0, clip, None, lr, cfg, self.step_count,
+                              cfg.weight_decay * getattr(buf, "weight_decay_mult", 1.0))
+                continue
             optim_ops.adam_step(sh["master"], sh["m"], sh["v"], buf.grad_data[s:e], buf.param_data[s:e], lr=lr,
                                 beta1=cfg.adam_beta1, beta2=cfg.adam_beta2, eps=cfg.adam_eps,
                                 weight_decay=cfg.weight_decay * getattr(buf, "weight_decay_mult", 1.0),
                                 step=self.step_count, grad_scale=clip)
         handles = []
         for sh in self.shards:
+            if sh["buf"].peer and sh["buf"].pending_scale is not None:
+                continue
             h = sh["buf"].gather_params(sh["bucket"], async_op=True)
             if h is not None:
                 handles.append(h)
         for h in handles:
             h.wait()
+        for buf in self.ddp.buffers:
+            if buf.peer and buf.pending_scale is not None:
+                buf.pending_scale = None
+                buf.peer_barrier()  # every peer's parameter pushes have landed; gradients may be overwritten
         return float(lr)
 
     def reload_master_from_params(self):

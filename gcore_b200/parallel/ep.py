@@ -58,6 +58,10 @@ def ep_moe_forward(layer, x, idx, w):
     T, H = x.shape
     K = idx.shape[1]
     E_local = layer.num_local
+    from .ep_fused import fused_ep_moe_forward, get_fused_ep
+    fe = get_fused_ep(group, H, E_local * ep, K, T, x)
+    if fe is not None:
+        return fused_ep_moe_forward(fe, layer, x, idx, w)
     flat_e = idx.reshape(-1)
     dest_rank = flat_e // E_local
     order = torch.argsort(dest_rank * (E_local * ep) + flat_e, stable=True)  # by rank, then by expert

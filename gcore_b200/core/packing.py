@@ -30,6 +30,7 @@ class PackedBatch:
     sample_index: List[int] = field(default_factory=list)  # indices into the originating sample list
     fields: Dict[str, torch.Tensor] = field(default_factory=dict)  # extra per-token tensors on the log-prob axis
     pad_tokens: int = 0
+    cp_ctx: Optional[object] = None  # parallel.cp.CPContext when the token axis is sharded over context-parallel ranks
 
     @property
     def num_seqs(self):
@@ -39,7 +40,8 @@ class PackedBatch:
         kw = dict(device=device, non_blocking=non_blocking)
         return PackedBatch(self.tokens.to(**kw), self.position_ids.to(**kw), self.cu_seqlens.to(**kw),
                            self.max_seqlen, self.targets.to(**kw), self.loss_mask.to(**kw), self.seq_ids.to(**kw),
-                           self.sample_index, {k: v.to(**kw) for k, v in self.fields.items()}, self.pad_tokens)
+                           self.sample_index, {k: v.to(**kw) for k, v in self.fields.items()}, self.pad_tokens,
+                           self.cp_ctx)
 
 
 def response_mask(prompt_len: int, seq_len: int) -> torch.Tensor:

@@ -146,7 +146,19 @@ class TrainingEngine:
 
     # ------------------------------------------------------------------ forward helpers
     def _hidden(self, model: GPTModel, mb: PackedBatch):
-        return model(mb.tokens, mb.position_ids, mb.cu_seqlens, mb.max_seqlen)
+        return model(mb.tokens, mb.position_ids, mb.cp_ctx if mb.cp_ctx is not None else mb.cu_seqlens, mb.max_seqlen)
+
+    def _cp_group(self):
+        return ps.get_context_parallel_group() if ps.get_context_parallel_world_size() > 1 else None
+
+    def _gather_cp(self, x: torch.Tensor) -> torch.Tensor:
+        """Token-axis tensors of a context-parallel shard -> the whole packed micro-batch (forward-only results)."""
+        g = self._cp_group()
+        if g is None:
+            return x
+        parts = [torch.empty_like(x) for _ in range(dist.get_world_size(g))]
+        dist.all_gather(parts, x.contiguous(), group=g)
+        return torch.cat(parts, dim=0)
 
     def _logprob_entropy(self, model: GPTModel, hidden, targets, want_entropy=True):
         w = model.output_weight()
@@ -164,7 +176,14 @@ class TrainingEngine:
         if self.device.type == "cuda":
             from ..models import gpt as gpt_mod
             pad = pad * (128 if gpt_mod.FUSED_TP["ftp"] is not None else 8) if pad > 1 else 8
+        cpg = self._cp_group()
+        if cpg is not None:
+            pad *= dist.get_world_size(cpg)
         mb = pack_samples(samples, idx, keys, pad_to_multiple=pad, pin=self.device.type == "cuda")
+        if cpg is not None:
+            from ..parallel.cp import shard_packed_batch
+            PL.set_context_parallel_group(cpg)
+            mb = shard_packed_batch(mb, cpg, self.device)
         io_counters.add_h2d(io_counters.tensor_bytes(mb.tokens, mb.position_ids, mb.cu_seqlens, mb.targets, mb.loss_mask,
                                                      mb.seq_ids, *mb.fields.values()))
         return mb.to(self.device)
@@ -192,7 +211,7 @@ class TrainingEngine:
                 mb = self._pack(samples, idx)
                 hidden, _ = self._hidden(model, mb)
                 lp, ent = self._logprob_entropy(model, hidden, mb.targets, with_entropy)
-                lp_c, ent_c = lp.float().cpu(), ent.float().cpu()
+                lp_c, ent_c = self._gather_cp(lp.float()).cpu(), self._gather_cp(ent.float()).cpu()
                 io_counters.add_d2h(io_counters.tensor_bytes(lp_c, ent_c))
                 cu = mb.cu_seqlens.tolist()
                 for j, i in enumerate(idx):
@@ -212,7 +231,7 @@ class TrainingEngine:
             for idx in self._microbatches(samples, forward_only=True):
                 mb = self._pack(samples, idx)
                 v, _ = self._hidden(self.model, mb)
-                vc = v.float().cpu()
+                vc = self._gather_cp(v.float()).cpu()
                 cu = mb.cu_seqlens.tolist()
                 for j, i in enumerate(idx):
                     samples[i]["values"] = vc[cu[j]:cu[j + 1]].clone()
@@ -224,6 +243,7 @@ class TrainingEngine:
             n = sum(float(torch.as_tensor(s["mask"] if "mask" in s else s["loss_mask"]).sum()) for s in samples)
         else:
             n = float(len(samples))
+        n /= ps.get_context_parallel_world_size()  # context-parallel ranks hold the same samples
         t = torch.tensor([n], dtype=torch.float64)
         g = ps.get_data_parallel_group(with_context_parallel=True)
         if g is not None and dist.get_world_size(g) > 1:

@@ -61,9 +61,40 @@ class LossOutput:
     metrics: Dict[str, torch.Tensor] = field(default_factory=dict)
 
 
+_CP_GROUP = None
+
+
+def set_context_parallel_group(group):
+    """Per-sequence sums span the ranks of this group when the tokens of a sequence are sharded over it."""
+    global _CP_GROUP
+    _CP_GROUP = group
+
+
+class _SumOverCP(torch.autograd.Function):
+    """Sum over the context-parallel ranks; every rank's loss depends on the total, so the gradient is summed too."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        import torch.distributed as dist
+        ctx.group = group
+        x = x.clone()
+        dist.all_reduce(x, group=group)
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        import torch.distributed as dist
+        g = g.clone()
+        dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
 def _seg_sum(x, seq_ids, n):
     out = torch.zeros(n, dtype=x.dtype, device=x.device)
-    return out.index_add_(0, seq_ids.long(), x)
+    out = out.index_add_(0, seq_ids.long(), x)
+    if _CP_GROUP is not None:
+        out = _SumOverCP.apply(out, _CP_GROUP)
+    return out
 
 
 def _token_ratio(cfg, logp, old):

@@ -25,6 +25,7 @@ from ..ops import fused
 from ..ops.attention import flash_attn_qkvpacked, flash_attn_varlen
 from ..ops.gemm import linear
 from ..parallel import tp_ops
+from ..parallel.cp import CPContext, cp_attention
 from .config import ModelConfig
 from .lora import LoRAAdapter
 
@@ -115,8 +116,20 @@ class SelfAttention(nn.Module):
         if not cfg.qk_layernorm:
             qkv = fused_rope_qk(qkv.view(T, hq + 2 * hk, D), pos, hq + hk, cfg.rope_theta, cfg.rotary_dim,
                                 cfg.rope_interleaved)
-            o = flash_attn_qkvpacked(qkv, hq, hk, cu_seqlens, max_seqlen, causal=True, window=self.window,
-                                     sinks=self.sinks, scale=scale)
+            if isinstance(cu_seqlens, CPContext):
+                q3 = qkv.view(T, hq + 2 * hk, D)
+                o = cp_attention(q3[:, :hq], q3[:, hq:hq + hk], q3[:, hq + hk:], cu_seqlens, self.window, self.sinks,
+                                 scale)
+            else:
+                o = flash_attn_qkvpacked(qkv, hq, hk, cu_seqlens, max_seqlen, causal=True, window=self.window,
+                                         sinks=self.sinks, scale=scale)
+        elif isinstance(cu_seqlens, CPContext):
+            q, k, v = qkv.view(T, hq + 2 * hk, D).split([hq, hk, hk], dim=1)
+            q = fused.rmsnorm(q.reshape(-1, D), self.q_layernorm.weight, cfg.rms_norm_eps)[0].view(T, hq, D)
+            k = fused.rmsnorm(k.reshape(-1, D), self.k_layernorm.weight, cfg.rms_norm_eps)[0].view(T, hk, D)
+            q = fused.rope(q, pos, cfg.rope_theta, cfg.rotary_dim, cfg.rope_interleaved)
+            k = fused.rope(k, pos, cfg.rope_theta, cfg.rotary_dim, cfg.rope_interleaved)
+            o = cp_attention(q, k, v, cu_seqlens, self.window, self.sinks, scale)
         else:
             q, k, v = qkv.view(T, hq + 2 * hk, D).split([hq, hk, hk], dim=1)
             q = fused.rmsnorm(q.reshape(-1, D), self.q_layernorm.weight, cfg.rms_norm_eps)[0].view(T, hq, D)

@@ -131,9 +131,68 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_oneshot_kernel(ArParams 
   }
 }
 
+// Segment gather / reduce over peer memory for context parallelism: out[i] = sum over the segments that cover i of
+// seg.src[i - seg.start], in segment order (fp32 accumulation, bf16 in and out).  With disjoint segments this is the
+// pull of the K/V rows a rank needs from the ranks that own them; with overlapping segments it is the return of the
+// partial dK/dV rows to their owner (a reduce-scatter whose summation order is fixed, hence deterministic).
+constexpr int MAX_SEGS = 16;
+struct RowsSeg { const __nv_bfloat16* src; long long start, end; };
+struct RowsParams { __nv_bfloat16* dst; long long n; int nseg; RowsSeg seg[MAX_SEGS]; };
+
+__global__ void __launch_bounds__(256) peer_rows_kernel(RowsParams p) {
+  const long long nvec = p.n >> 3;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long e = i << 3;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    uint4 only = make_uint4(0, 0, 0, 0);
+    int hits = 0;
+    for (int s = 0; s < p.nseg; ++s) {
+      if (e >= p.seg[s].start && e < p.seg[s].end) {
+        uint4 v;
+        asm volatile("ld.global.relaxed.sys.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p.seg[s].src + (e - p.seg[s].start)) : "memory");
+        add8(acc, v);
+        only = v;
+        ++hits;
+      }
+    }
+    uint4 o = only;  // a single source is copied bit-exactly
+    if (hits != 1) {
+      __nv_bfloat162 t2;
+      t2 = __floats2bfloat162_rn(acc[0], acc[1]); o.x = *reinterpret_cast<uint32_t*>(&t2);
+      t2 = __floats2bfloat162_rn(acc[2], acc[3]); o.y = *reinterpret_cast<uint32_t*>(&t2);
+      t2 = __floats2bfloat162_rn(acc[4], acc[5]); o.z = *reinterpret_cast<uint32_t*>(&t2);
+      t2 = __floats2bfloat162_rn(acc[6], acc[7]); o.w = *reinterpret_cast<uint32_t*>(&t2);
+    }
+    reinterpret_cast<uint4*>(p.dst)[i] = o;
+  }
+}
+
 }  // namespace gkx
 
 using namespace gkx;
+
+// segs: nseg triples (source address, first element, end element) in destination element coordinates; all multiples
+// of 8 elements.  Elements covered by no segment become zero.
+GK_EXPORT int gk_peer_rows(void* dst, long long n, int nseg, const unsigned long long* segs, void* stream) {
+  if (n % 8 || nseg < 0 || nseg > MAX_SEGS) return -1;
+  if (n == 0) return 0;
+  RowsParams p;
+  p.dst = reinterpret_cast<__nv_bfloat16*>(dst);
+  p.n = n;
+  p.nseg = nseg;
+  for (int s = 0; s < nseg; ++s) {
+    p.seg[s].src = reinterpret_cast<const __nv_bfloat16*>(segs[3 * s]);
+    p.seg[s].start = static_cast<long long>(segs[3 * s + 1]);
+    p.seg[s].end = static_cast<long long>(segs[3 * s + 2]);
+    if ((p.seg[s].start | p.seg[s].end) & 7) return -2;
+  }
+  long long want = (n / 8 + 255) / 256;
+  const long long cap = 8LL * gk::sm_count();
+  peer_rows_kernel<<<static_cast<unsigned>(want < cap ? want : cap), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  return gk::launch_status();
+}
 
 GK_EXPORT int gk_allreduce_ctas() { return AR_CTAS; }
 

@@ -83,3 +83,40 @@ def test_ep2_matches_single_process(tmp_path):
     ref = [e.finetune_step(pw.samples(8, 70 + s, vocab=512))["lm_loss"] for s in range(3)]
     for a, b in zip(ref, got["losses"]):
         assert abs(a - b) < 2e-3, (ref, got)
+
+
+def test_cp2_matches_single_process(tmp_path):
+    """Context parallel over the packed token stream (full + sliding-window-with-sink layers): same losses, gradient
+    norm and per-token log-probs as one process."""
+    import parallel_worker as pw
+    from gcore_b200.models.config import get_preset
+    out = tmp_path / "cp.json"
+    _spawn("cp", out, port="29545")
+    got = json.load(open(out))
+    mcfg = get_preset("tiny_llama", dtype="float32", qkv_bias=True, sliding_window=16, sliding_window_pattern=[0, 1],
+                      attention_sinks=True)
+    e = pw.engine(mcfg, 1)
+    ref = [e.finetune_step(pw.samples(8, 90 + s))["lm_loss"] for s in range(4)]
+    for a, b in zip(ref, got["losses"]):
+        assert abs(a - b) < 5e-4, (ref, got["losses"])
+    assert abs(float(e.optimizer.last_grad_norm) - got["grad_norm"]) < 5e-3
+    lp = e.compute_log_probs(pw.samples(3, 99))
+    for a, b in zip(lp, got["logprobs"]):
+        assert torch.allclose(a["logprobs"], torch.tensor(b), atol=2e-4)
+
+
+def test_cp_plan_covers_every_key_row_once():
+    from gcore_b200.parallel.cp import plan_cp
+    cu = [0, 37, 120, 121, 300, 512]
+    cp, s = 4, 128
+    for window in (0, 16):
+        plans = [plan_cp(cu, s, cp, r, window) for r in range(cp)]
+        for r, p in enumerate(plans):
+            assert p.cu_q[-1] == s and p.cu_k[-1] == p.rows
+            assert sum(n for *_, n in p.pulls) == p.rows
+            # every returned range lands inside the owner's chunk and matches what the source gathered
+            for src, src_row, dst_row, n in p.returns:
+                assert 0 <= dst_row and dst_row + n <= s
+                assert plans[src].k0 + src_row == r * s + dst_row
+        if window:
+            assert all(p.k0 >= r * s - (window - 1) for r, p in enumerate(plans))

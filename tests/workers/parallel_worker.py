@@ -1,4 +1,4 @@
-"""gloo worker for the parallelism parity tests: mode = tp | ep | ckpt."""
+"""gloo worker for the parallelism parity tests: mode = tp | ep | cp."""
 import json
 import os
 import sys
@@ -66,6 +66,17 @@ def main():
             batch = samples(8, 70 + s, vocab=512)
             losses.append(e.finetune_step(batch[rank::world])["lm_loss"])  # EP ranks are also DP ranks
         res = {"losses": losses}
+    elif mode == "cp":
+        ps.initialize_model_parallel(tp=1, cp=2)
+        mcfg = get_preset("tiny_llama", dtype="float32", qkv_bias=True, sliding_window=16,
+                          sliding_window_pattern=[0, 1], attention_sinks=True)
+        e = engine(mcfg, 1)
+        losses = []
+        for s in range(4):
+            losses.append(e.finetune_step(samples(8, 90 + s))["lm_loss"])  # CP ranks see the same data
+        lp = e.compute_log_probs(samples(3, 99))
+        res = {"losses": losses, "grad_norm": float(e.optimizer.last_grad_norm),
+               "logprobs": [x["logprobs"].tolist() for x in lp]}
     if rank == 0:
         json.dump(res, open(out, "w"))
     dist.barrier()

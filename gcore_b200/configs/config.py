@@ -343,9 +343,12 @@ class PpoConfig(MappingMixin):
     ppo_discount_factor: float = 1.0
     ppo_gae_lambda: float = 0.95
     ppo_entropy_bonus: float = 0.0
-    adaptive_entropy: bool = False
-    adaptive_entropy_target: float = 0.0
-    adaptive_entropy_lr: float = 0.0
+    use_adaptive_entropy: bool = False
+    entropy_target: float = 0.2
+    entropy_coef_delta: float = 0.005
+    entropy_coef_min: float = 0.0
+    entropy_coef_max: float = 1.0
+    feature_store_enable: bool = False
     ppo_ratio_eps: float = 0.2
     ppo_clip_ratio_low: Optional[float] = None
     ppo_clip_ratio_high: Optional[float] = None

@@ -1,0 +1,213 @@
+"""CPU tests of the algorithm-core and service modules: registry, Muon, feature store, adaptive entropy, filter
+sampling, DP balancing (gloo, 2 ranks), agentic envs and trajectory masks, RPC clients, transfer queue."""
+import os
+import types
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def test_registry_resolves_eager_on_cpu_and_accepts_overrides():
+    from gcore_b200.ops import registry
+    assert "gemm" in registry.available() and "rmsnorm" in registry.available()
+    fn = registry.resolve("rmsnorm")
+    assert fn.__name__.endswith("_ref")
+    registry.register_fn("rmsnorm", lambda *a, **k: "mine", "override")
+    assert registry.resolve("rmsnorm")() == "mine"
+    registry._REGISTRY["rmsnorm"].pop("override")
+    with pytest.raises(KeyError):
+        registry.resolve("no_such_op")
+
+
+def test_newton_schulz_orthogonalises_and_muon_descends():
+    from gcore_b200.core.muon import Muon, newton_schulz5
+    torch.manual_seed(0)
+    for shape in ((64, 128), (128, 48)):
+        X = newton_schulz5(torch.randn(*shape)).float()
+        sv = torch.linalg.svdvals(X)
+        assert sv.min() > 0.4 and sv.max() < 1.6  # singular values pushed into the quintic's band around 1
+    w = torch.nn.Parameter(torch.randn(32, 16))
+    b = torch.nn.Parameter(torch.zeros(32))
+    x, y = torch.randn(256, 16), torch.randn(256, 32)
+    opt = Muon([w], [b], lr=0.1, wd=0.0)
+    first = None
+    for _ in range(40):
+        loss = ((x @ w.t() + b - y) ** 2).mean()
+        first = first if first is not None else loss.item()
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+    assert loss.item() < 0.8 * first
+
+
+def test_feature_store_intervals_persistence_and_adaptive_entropy(tmp_path):
+    from gcore_b200.core import ppo_feature_store as fs
+    fs.reset_ppo_feature_store()
+    st = fs.get_ppo_feature_store()
+    st.configure("entropy", "mean")
+    st.configure("peak", "max")
+    with fs.ppo_step_interval(3) as iv:
+        st.record_weighted_sum("entropy", 6.0, 4.0)
+        st.record_weighted_sum("entropy", 2.0, 4.0)
+        st.record_weighted_sum("peak", 5.0, 1.0)
+        st.record_weighted_sum("peak", 9.0, 1.0)
+    assert iv.results == {"entropy": 1.0, "peak": 9.0}
+    assert st.get_history_mean("entropy") == 1.0 and st.list_pending_features() == []
+    cfg = types.SimpleNamespace(use_adaptive_entropy=True, ppo_entropy_bonus=0.01, entropy_target=0.5,
+                                entropy_coef_delta=0.005, entropy_coef_min=0.0, entropy_coef_max=0.02)
+    assert fs.get_entropy_bonus_coef(cfg) == 0.0           # no measurement yet: entropy treated as high
+    m = fs.update_adaptive_entropy(cfg, 0.3)               # below target -> coefficient rises, bonus switches on
+    assert abs(m["policy/entropy_coef"] - 0.015) < 1e-9 and abs(fs.get_entropy_bonus_coef(cfg) - 0.015) < 1e-9
+    fs.update_adaptive_entropy(cfg, 0.3)
+    fs.update_adaptive_entropy(cfg, 0.3)
+    assert abs(st.get(fs.ENTROPY_COEF_KEY) - 0.02) < 1e-9    # clamped at the maximum
+    fs.update_adaptive_entropy(cfg, 0.9)                   # above target -> falls, and the bonus is gated off
+    assert abs(st.get(fs.ENTROPY_COEF_KEY) - 0.015) < 1e-9 and fs.get_entropy_bonus_coef(cfg) == 0.0
+    st.save_to_ckpt(str(tmp_path), 3)
+    fs.reset_ppo_feature_store()
+    st2 = fs.get_ppo_feature_store()
+    assert st2.load_from_ckpt(str(tmp_path), 3) and abs(st2.get(fs.ENTROPY_COEF_KEY) - 0.015) < 1e-9
+    with pytest.raises(ValueError):
+        st2.load_from_ckpt(str(tmp_path), 4)
+
+
+def test_filter_sampling_strategies():
+    from gcore_b200.core import filter_samplings as F
+    groups = [[{"rewards": torch.tensor([r])} for r in (0.1, 0.9, 0.5, 0.0)]]
+    bw = F.get_group_filter("best-and-worst")(None, groups, 4, 2)
+    assert [float(s["rewards"]) for s in bw[0]] == pytest.approx([0.9, 0.0])
+    assert len(F.get_group_filter("test")(None, groups, 4, 3)[0]) == 3
+    flat = [{"group_id": g, "reward": r, "sample_mask": m} for g, r, m in
+            ((0, 1.0, 1), (0, 0.0, 1), (0, 0.5, 0), (1, 1.0, 1))]
+    out = F.filter_rollout_samples(None, flat, ["sample-mask", "valid_group", "best-and-worst"])
+    assert [(s["group_id"], s["reward"]) for s in out] == [(0, 0.0), (0, 1.0)]
+
+
+def _balance_worker(rank, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=2)
+    from gcore_b200.core.dp_balancing import rebalance_across_dp_ranks, restore_original_order
+    g = dist.group.WORLD
+    lens = [400, 390, 380, 370] if rank == 0 else [10, 10, 10, 10]
+    samples = [{"tokens": torch.full((n,), rank * 100 + i), "uid": (rank, i)} for i, n in enumerate(lens)]
+    mine, restore = rebalance_across_dp_ranks(samples, g)
+    load = sum(len(s["tokens"]) for s in mine)
+    for s in mine:
+        s["logprobs"] = s["tokens"].float() * 2
+    back = restore_original_order(mine, restore, g, keys=("logprobs", "uid"))
+    ok = all(b["uid"] == (rank, i) and torch.equal(b["logprobs"], samples[i]["tokens"].float() * 2)
+             for i, b in enumerate(back))
+    q.put((rank, load, ok))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_dp_rebalance_evens_tokens_and_restores_order():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_balance_worker, args=(r, 29561, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    loads = [r[1] for r in res]
+    assert all(r[2] for r in res)
+    assert sum(loads) == 1580 and max(loads) - min(loads) <= 20, loads  # was 1540 vs 40 before balancing
+
+
+def test_smart_pad_buckets_cut_padding():
+    from gcore_b200.core.dp_balancing import padding_waste, smart_pad_buckets
+    lens = [5, 100, 7, 90, 50, 49]
+    naive = [[0, 1], [2, 3], [4, 5]]
+    buckets, inv = smart_pad_buckets(lens, 2)
+    assert padding_waste(lens, buckets) < padding_waste(lens, naive)
+    flat = [i for b in buckets for i in b]
+    assert [flat[inv[i]] for i in range(len(lens))] == list(range(len(lens)))
+
+
+def test_envs_parsers_and_trajectory_mask():
+    from gcore_b200.agentic import (FrozenLakeEnv, SokobanEnv, ToolReasonEnvWrapper, ToolRegistry, TrajEnvManager,
+                                    make_env, parse_tool_calls, split_reasoning)
+    env = FrozenLakeEnv(size=4)
+    obs, info = env.reset(seed=3)
+    assert obs.count("P") == 1 and obs.count("G") == 1 and "instructions" in info
+    # a scripted shortest path exists (the generator guarantees one): BFS over the rendered board
+    from collections import deque
+    grid = env.map
+    prev, dq = {(0, 0): None}, deque([(0, 0)])
+    while dq:
+        r, c = dq.popleft()
+        for name, (dr, dc) in (("Left", (0, -1)), ("Down", (1, 0)), ("Right", (0, 1)), ("Up", (-1, 0))):
+            n = (r + dr, c + dc)
+            if 0 <= n[0] < 4 and 0 <= n[1] < 4 and grid[n[0]][n[1]] != "H" and n not in prev:
+                prev[n] = ((r, c), name)
+                dq.append(n)
+    path, cur = [], (3, 3)
+    while prev[cur] is not None:
+        cur, name = prev[cur][0], prev[cur][1]
+        path.append(name)
+    reward = done = None
+    for name in reversed(path):
+        _, reward, done, _, info = env.step(f"thinking... <answer>{name}</answer>")
+    assert done and reward == 1.0 and info["success"]
+    assert env.step("gibberish")[4]["action_is_valid"] is False
+    sk = SokobanEnv()
+    board, _ = sk.reset(seed=5)
+    assert board.count("P") + board.count("S") == 1 and sk.boxes != sk.targets
+    assert split_reasoning("<think>plan</think> go") == ("plan", "go")
+    text, calls = parse_tool_calls('x <tool_call>{"name": "add", "arguments": {"a": 1, "b": 2}}</tool_call>')
+    assert calls[0].name == "add" and text == "x"
+    tools = ToolRegistry()
+    tools.register("add", lambda a, b: a + b)
+    wrapped = ToolReasonEnvWrapper(make_env("simple"), tools)
+    wrapped.reset()
+    obs, r, done, _, info = wrapped.step('<tool_call>{"name": "add", "arguments": {"a": 1, "b": 2}}</tool_call>')
+    assert '"result": 3' in obs and not done and info["tool_calls"] == 1
+
+    class Tok:
+        def encode(self, t):
+            return [ord(c) % 250 + 3 for c in t]
+
+        def decode(self, ids):
+            return "<answer>1</answer>"
+
+    m = TrajEnvManager(make_env("simple", max_steps=2), Tok(), lambda ctx: {"token_ids": [5, 6, 7],
+                                                                            "logprobs": [-0.1, -0.2, -0.3]})
+    s = m.run(seed=0)
+    assert s["num_turns"] == 2 and s["reward"] == 1.0  # only the first answer "1" is right
+    assert int(s["mask"].sum()) == 6                    # 2 assistant turns x 3 generated tokens
+    pos = torch.nonzero(s["mask"]).flatten()
+    assert all(int(s["tokens"][p + 1]) in (5, 6, 7) for p in pos)
+    assert torch.allclose(s["rollout_log_probs"][pos[:3]], torch.tensor([-0.1, -0.2, -0.3]))
+
+
+def test_rpc_clients_and_transfer_queue():
+    from gcore_b200.client import HttpRpcClient, KvStore, KvStoreClient, LocalRpcClient, pick_endpoint_idx, serve
+    from gcore_b200.transfer import TransferQueue, make_key
+    assert [pick_endpoint_idx(r, 4, 2) for r in range(4)] == [0, 0, 1, 1]
+    assert [pick_endpoint_idx(r, 2, 4, 1) for r in range(2)] == [1, 3]
+    srv, url = serve(KvStore())
+    try:
+        c = KvStoreClient(HttpRpcClient([url]))
+        c.put("w", torch.arange(4))
+        assert torch.equal(c.get("w"), torch.arange(4)) and c.get("missing", 7) == 7
+    finally:
+        srv.shutdown()
+    a, b = KvStore(), KvStore()
+    a.put("k", 1), a.put("k2", 2)
+    lc = LocalRpcClient([a, b], dp_rank=0, dp_size=2, load_aware=True)
+    assert lc.pick() == 1  # the emptier endpoint wins
+    tq = TransferQueue()
+    tq.put_batch(3, range(4), [{"tokens": torch.ones(2) * i} for i in range(4)])
+    tq.storage.put(make_key(3, 1), {"advantages": torch.zeros(2)})
+    assert tq.ready(3, ["tokens", "advantages"]) == ["step3:1"]
+    r0 = tq.get_batch(3, ["tokens"], 8, dp_rank=0, dp_size=2)
+    r1 = tq.get_batch(3, ["tokens"], 8, dp_rank=1, dp_size=2)
+    assert len(r0) + len(r1) == 4 and not set(x["_key"] for x in r0) & set(x["_key"] for x in r1)
+    assert tq.get_batch(3, ["tokens"], 8, dp_rank=0, dp_size=1) == []  # everything was consumed once
+    tq.clear_step(3)
+    assert len(tq.storage) == 0

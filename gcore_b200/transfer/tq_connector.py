@@ -71,8 +71,9 @@ class TransferQueue:
         """Up to ``n`` unconsumed ready rows for this consumer; rows are split over DP ranks by a stable hash."""
         with self._lock:
             seen = self._consumed.setdefault(f"{consumer}:{step}", set())
-            keys = [k for k in sorted(self.ready(step, fields)) if k not in seen]
-            keys = [k for i, k in enumerate(keys) if i % dp_size == dp_rank][:n]
+            mine = [k for i, k in enumerate(sorted(self.storage.keys(f"step{step}:"))) if i % dp_size == dp_rank]
+            ready = set(self.ready(step, fields))
+            keys = [k for k in mine if k in ready and k not in seen][:n]
             seen.update(keys)
         return [dict(self.storage.get(k, fields), _key=k) for k in keys]
 

@@ -106,7 +106,8 @@ def build_config(args, world):
     cfg = from_dict(RlConfig, {
         "training": {"rollout_gbs": prompts_per_dp * dp, "sampling_repeat_n": n, "train_gbs": prompts_per_dp * dp * n,
                      "train_mbs": 1, "seed": 1234, "total_ppo_step": 1000},
-        "policy": {"model_arch": args.model, "recompute": args.recompute, "share_rollout_weights": True,
+        "policy": {"model_arch": args.model, "recompute": args.recompute,
+                   "recompute_num_layers": args.recompute_layers, "share_rollout_weights": True,
                    "dist_config": {"tensor_model_parallel_size": tp, "sequence_parallel": tp > 1},
                    "dynamic_mbs_target_seqlen": args.mb_tokens},
         "optimizer": {"lr": 1e-6, "lr_decay_style": "constant", "weight_decay": 0.01, "max_grad_norm": 1.0},
@@ -133,8 +134,13 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=256)
     ap.add_argument("--max-response", type=int, default=1024)
     ap.add_argument("--mb-tokens", type=int, default=8192)
-    ap.add_argument("--recompute", default="full")
+    ap.add_argument("--recompute", default=None, help="full | none; default: full on 1 GPU (optimizer state of the "
+                    "whole 7B model shares the GPU with the activations), none when tensor parallelism halves it")
+    ap.add_argument("--recompute-layers", type=int, default=None,
+                    help="with --recompute full: recompute only the first N layers")
     args = ap.parse_args()
+    if args.recompute is None:
+        args.recompute = "full" if args.gpus == 1 else "none"
     if args.impl == "reference":
         return reference_arm(args)
 
@@ -227,7 +233,7 @@ def main():
                        "parallelism": f"tp{tp}dp{dp}", "prompts": int(cfg.training.rollout_gbs),
                        "samples_per_prompt": args.samples, "weights": "random-init",
                        "resync": "zero-copy shared parameter storage (trainer and rollout engine, same TP layout)",
-                       "l2": "inputs (15 GB of weights per pass) are larger than L2", "recompute": args.recompute},
+                       "l2": "inputs (15 GB of weights per pass) are larger than L2", "recompute": args.recompute, "recompute_layers": args.recompute_layers},
             "clocks": clocks,
             "e2e": {"value": round(tokens / wall, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d / args.steps),
                     "d2h_bytes_per_step": int(d2h / args.steps)},

@@ -314,6 +314,7 @@ class PolicyConfig(MappingMixin):
     smart_pad_train: bool = False
     wrap_with_ddp: bool = True
     recompute: str = "full"  # none | full (per-layer activation recompute)
+    recompute_num_layers: Optional[int] = None  # with "full": only the first N layers are recomputed (None = all)
     override_ddp_config: Dict[str, Any] = field(default_factory=dict)
     override_transformer_config: Dict[str, Any] = field(default_factory=dict)
     freeze_patterns: List[str] = field(default_factory=list)

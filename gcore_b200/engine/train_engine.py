@@ -84,6 +84,7 @@ class TrainingEngine:
         m = GPTModel(self.model_cfg, tp_size=tp, ep_size=ep, sequence_parallel=d.sequence_parallel,
                      recompute=recompute if recompute is not None else self.policy_cfg.recompute,
                      device=self.device, value_head=value_head)
+        m.recompute_num_layers = getattr(self.policy_cfg, "recompute_num_layers", None)
         if seed is not None:
             m.reset_parameters(seed)
         return m

@@ -424,8 +424,10 @@ class GPTModel(nn.Module):
         residual = None
         aux_total = None
         pos32 = position_ids.to(torch.int32) if position_ids.dtype != torch.int32 else position_ids
-        for layer in self.decoder.layers:
-            if self.recompute == "full" and torch.is_grad_enabled() and x.requires_grad:
+        n_ckpt = getattr(self, "recompute_num_layers", None)
+        for li, layer in enumerate(self.decoder.layers):
+            if (self.recompute == "full" and torch.is_grad_enabled() and x.requires_grad
+                    and (n_ckpt is None or li < n_ckpt)):
                 x, residual, aux = checkpoint(layer, x, residual, pos32, cu_seqlens, max_seqlen, tp_group, sp,
                                               use_reentrant=False)
             else:

@@ -12,6 +12,8 @@ from __future__ import annotations
 
 import ctypes
 
+import math
+
 import torch
 
 from . import _lib
@@ -168,6 +170,34 @@ def grouped_wgrad(dy: torch.Tensor, x: torch.Tensor, offsets: torch.Tensor, num_
 
 
 # ----------------------------------------------------------------------------------------------------------
+_SKINNY = [__import__("os").environ.get("GCORE_SKINNY_GEMM", "1") != "0"]
+
+
+_SKINNY_PLANS: dict = {}
+
+
+def _skinny_plan(T: int, tiles: int, kb: int, K: int):
+    """Cluster size (CTAs that split K for one 128-feature tile) and padded token count: the largest cluster whose
+    tiles all fit on the GPU in one wave (asked from the occupancy API once per shape)."""
+    key = (T, tiles, kb)
+    plan = _SKINNY_PLANS.get(key)
+    if plan is None:
+        lib = _lib.kernels()
+        best = (1, (T + 15) // 16 * 16, tiles)
+        for ks in range(2, 9):
+            if kb // ks < 2:
+                break
+            step = 16 * ks // math.gcd(16, ks)
+            tpad = (T + step - 1) // step * step
+            if tpad > 256:
+                continue
+            if lib.gk_gemm_skinny_max_clusters(tpad, ks, K) >= tiles and tiles * ks > best[2]:
+                best = (ks, tpad, tiles * ks)
+        plan = best[:2]
+        _SKINNY_PLANS[key] = plan
+    return plan
+
+
 def linear_forward(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
                    out: torch.Tensor | None = None, out_dtype=None) -> torch.Tensor:
     """``y[T,N] = x[T,K] @ w[N,K]^T + bias``.  Few tokens (decode) run swap-AB + split-K so the weight streams
@@ -178,6 +208,23 @@ def linear_forward(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None =
         bn = 32 if T <= 32 else (64 if T <= 64 else 128)
         tiles = (N + 127) // 128
         kb = (K + 63) // 64
+        # measured on B200 under graph replay: the cluster kernel wins for few tiles and moderate K (projections of a
+        # tensor-parallel shard); the persistent kernel's global split-K wins for more tiles or very long K
+        if (tiles <= 32 and kb <= 160 and _SKINNY[0] and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+                and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+                and hasattr(_lib.kernels(), "gk_gemm_skinny")):
+            # few output tiles: cluster split-K with the reduction in distributed shared memory
+            ks, tpad = _skinny_plan(T, tiles, kb, K)
+            od = out_dtype or (out.dtype if out is not None else x.dtype)
+            y = out if out is not None else torch.empty((T, N), dtype=od, device=x.device)
+            if y.dtype in (torch.bfloat16, torch.float32) and y.stride(1) == 1:
+                LAUNCHES["gemm"] += 1
+                rc = _lib.kernels().gk_gemm_skinny(
+                    _lib.ptr(w), w.stride(0), _lib.ptr(x), x.stride(0), _lib.ptr(y), y.stride(0),
+                    int(y.dtype == torch.float32), _lib.ptr(bias), int(bias is not None and bias.dtype == torch.float32),
+                    T, tpad, N, K, ks, _lib.ptr(_lib.err_flag(x.device)), _lib.stream_ptr())
+                _lib.check(rc, "gk_gemm_skinny")
+                return y
         ksplit = max(1, min(148 // tiles, kb // 4, 16)) if tiles < 120 else 1
         return gemm(w, x, out=out, out_dtype=out_dtype, bias=bias, bias_along_m=True, transposed=True, bn=bn,
                     ksplit=ksplit)

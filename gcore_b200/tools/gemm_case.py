@@ -11,9 +11,9 @@ import torch
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--tokens", type=int, default=64)
-    ap.add_argument("--n", type=int, default=37888)
-    ap.add_argument("--k", type=int, default=3584)
+    ap.add_argument("--tokens", "--T", type=int, default=64)
+    ap.add_argument("--n", "--N", type=int, default=37888)
+    ap.add_argument("--k", "--K", type=int, default=3584)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--layout", default="fwd")
     args = ap.parse_args()

@@ -411,3 +411,34 @@ def test_gemm_fp8_blockscaled(M, N, K):
     _close(out, ref, rtol=1e-2, atol=1e-2)
     full = a.float() @ b.float().t()
     assert (out.float() - full).abs().max() / full.abs().max() < 0.1
+
+
+@pytest.mark.parametrize("T,N,K,bias,fp32", [(1, 512, 256, False, False), (8, 4608, 3584, True, False),
+                                              (64, 3584, 18944, False, False), (100, 1000, 1792, True, True),
+                                              (128, 2304, 3584, True, False), (128, 3584, 9472, False, True),
+                                              (17, 256, 128, False, False)])
+def test_skinny_cluster_splitk_gemm(T, N, K, bias, fp32):
+    from gcore_b200.ops import gemm as G
+    torch.manual_seed(18)
+    x, w = _rand(T, K, scale=0.5), _rand(N, K, scale=0.05)
+    b = _rand(N) if bias else None
+    assert G._SKINNY[0]
+    # call the cluster kernel directly: linear_forward only routes some shapes to it
+    tiles, kb = (N + 127) // 128, (K + 63) // 64
+    ks, tpad = G._skinny_plan(T, tiles, kb, K)
+    y = torch.empty(T, N, dtype=torch.float32 if fp32 else torch.bfloat16, device="cuda")
+    from gcore_b200.ops import _lib
+    rc = _lib.kernels().gk_gemm_skinny(_lib.ptr(w), w.stride(0), _lib.ptr(x), x.stride(0), _lib.ptr(y), y.stride(0),
+                                       int(fp32), _lib.ptr(b), 0, T, tpad, N, K, ks,
+                                       _lib.ptr(_lib.err_flag(x.device)), _lib.stream_ptr())
+    assert rc == 0
+    _lib.check_device_errors()
+    ref = x.float() @ w.float().t() + (b.float() if bias else 0.0)
+    _close(y, ref, rtol=1e-2, atol=1e-2 if not fp32 else 2e-3)
+    # same numbers as the general kernel's split-K path
+    G._SKINNY[0] = False
+    try:
+        y2 = G.linear_forward(x, w, b, out_dtype=torch.float32 if fp32 else None)
+    finally:
+        G._SKINNY[0] = True
+    _close(y, y2.float(), rtol=1e-2, atol=1e-2)

@@ -81,9 +81,19 @@ class TrainingEngine:
         ep = st.ep if st.initialized else 1
         if self.device.type == "cpu" and self.model_cfg.dtype == "bfloat16" and os.environ.get("GCORE_CPU_FP32", "1") == "1":
             pass
+        pp = st.pp if st.initialized else 1
+        stage_kw = {}
+        if pp > 1:
+            from ..parallel.pp import stage_layer_range
+            stage = ps.get_pipeline_model_parallel_rank()
+            assert not self.model_cfg.tie_word_embeddings, "tied embeddings are not supported across pipeline stages"
+            stage_kw = dict(pre_process=stage == 0, post_process=stage == pp - 1,
+                            layer_range=stage_layer_range(self.model_cfg.num_layers, pp, stage,
+                                                          d.num_layers_in_first_pipeline_stage,
+                                                          d.num_layers_in_last_pipeline_stage))
         m = GPTModel(self.model_cfg, tp_size=tp, ep_size=ep, sequence_parallel=d.sequence_parallel,
                      recompute=recompute if recompute is not None else self.policy_cfg.recompute,
-                     device=self.device, value_head=value_head)
+                     device=self.device, value_head=value_head, **stage_kw)
         m.recompute_num_layers = getattr(self.policy_cfg, "recompute_num_layers", None)
         if seed is not None:
             m.reset_parameters(seed)
@@ -161,6 +171,58 @@ class TrainingEngine:
         dist.all_gather(parts, x.contiguous(), group=g)
         return torch.cat(parts, dim=0)
 
+    def _for_each_microbatch(self, model: GPTModel, samples, batches, keys, step_fn, forward_only: bool = False):
+        """Drives ``step_fn(mb, hidden, aux)`` over the micro-batches ``batches`` (lists of sample indices).  In
+        training mode ``step_fn`` returns the micro-batch loss, which is back-propagated here; in forward-only mode
+        its return values are collected.  With pipeline parallelism the micro-batches run through the 1F1B schedule
+        and ``step_fn`` executes on the last stage only (other stages get an empty result list)."""
+        pp = ps.get_pipeline_model_parallel_world_size()
+        if pp == 1:
+            out = []
+            for idx in batches:
+                mb = self._pack(samples, idx, keys)
+                hidden, aux = self._hidden(model, mb)
+                r = step_fn(mb, hidden, aux)
+                if forward_only:
+                    out.append(r)
+                else:
+                    r.backward()
+            return out
+        from ..parallel.pp import PipelineComm, forward_backward_1f1b
+        comm = PipelineComm(ps.get_pipeline_model_parallel_group())
+        packed: Dict[int, PackedBatch] = {}
+
+        def get(i):
+            if i not in packed:
+                packed[i] = self._pack(samples, batches[i], keys)
+            return packed[i]
+
+        def forward_step(i, hidden_in):
+            mb = get(i)
+            return model(mb.tokens, mb.position_ids, mb.cp_ctx if mb.cp_ctx is not None else mb.cu_seqlens,
+                         mb.max_seqlen, hidden_in=hidden_in)
+
+        def loss_step(i, hidden, aux):
+            r = step_fn(get(i), hidden, aux)
+            if forward_only:
+                packed.pop(i, None)
+            return r
+
+        def act_shape(i):
+            mb = get(i)
+            t_local = mb.tokens.numel() // (ps.get_tensor_model_parallel_world_size() if model.sequence_parallel else 1)
+            dt = {"bfloat16": torch.bfloat16, "float32": torch.float32}[self.model_cfg.dtype]
+            return (t_local, self.model_cfg.hidden_size), dt, self.device
+
+        return forward_backward_1f1b(comm, len(batches), forward_step, loss_step, act_shape, forward_only)
+
+    def _from_last_stage(self, t, shape, dtype):
+        """Results computed at the end of the pipeline, made available on every stage."""
+        if ps.get_pipeline_model_parallel_world_size() == 1:
+            return t
+        from ..parallel.pp import broadcast_from_last_stage
+        return broadcast_from_last_stage(t, shape, dtype, self.device, ps.get_pipeline_model_parallel_group())
+
     def _logprob_entropy(self, model: GPTModel, hidden, targets, want_entropy=True):
         w = model.output_weight()
         tp_group = ps.get_tensor_model_parallel_group() if model.tp_size > 1 else None
@@ -172,7 +234,7 @@ class TrainingEngine:
         return ps.get_tensor_model_parallel_world_size() if (self.model is not None and self.model.sequence_parallel) \
             else 1
 
-    def _pack(self, samples, idx, keys=()):
+    def _pad_multiple(self) -> int:
         pad = max(self._tp_pad(), 1)
         if self.device.type == "cuda":
             from ..models import gpt as gpt_mod
@@ -180,6 +242,11 @@ class TrainingEngine:
         cpg = self._cp_group()
         if cpg is not None:
             pad *= dist.get_world_size(cpg)
+        return pad
+
+    def _pack(self, samples, idx, keys=()):
+        pad = self._pad_multiple()
+        cpg = self._cp_group()
         mb = pack_samples(samples, idx, keys, pad_to_multiple=pad, pin=self.device.type == "cuda")
         if cpg is not None:
             from ..parallel.cp import shard_packed_batch
@@ -208,18 +275,32 @@ class TrainingEngine:
         model.eval()
         key = out_key or ("ref_logprobs" if use_ref else "logprobs")
         with backend_scope(self.backend):
-            for idx in self._microbatches(samples, forward_only=True):
-                mb = self._pack(samples, idx)
-                hidden, _ = self._hidden(model, mb)
+            batches = self._microbatches(samples, forward_only=True)
+
+            def step(mb, hidden, aux):
                 lp, ent = self._logprob_entropy(model, hidden, mb.targets, with_entropy)
-                lp_c, ent_c = self._gather_cp(lp.float()).cpu(), self._gather_cp(ent.float()).cpu()
-                io_counters.add_d2h(io_counters.tensor_bytes(lp_c, ent_c))
-                cu = mb.cu_seqlens.tolist()
-                for j, i in enumerate(idx):
-                    s, e = cu[j], cu[j + 1]
-                    samples[i][key] = lp_c[s:e].clone()
-                    if with_entropy and not use_ref:
-                        samples[i]["prev_per_token_entropies"] = ent_c[s:e].clone()
+                return self._gather_cp(lp.float()), self._gather_cp(ent.float()) if ent is not None else None
+
+            results = self._for_each_microbatch(model, samples, batches, (), step, forward_only=True)
+            for bi, idx in enumerate(batches):
+                lens = [len(samples[i]["tokens"]) for i in idx]
+                total = sum(lens)
+                pad_mult = self._pad_multiple()
+                total_padded = (total + pad_mult - 1) // pad_mult * pad_mult
+                lp, ent = results[bi] if results else (None, None)
+                lp = self._from_last_stage(lp, (total_padded,), torch.float32)
+                if with_entropy and not use_ref:
+                    ent = self._from_last_stage(ent, (total_padded,), torch.float32)
+                lp_c = lp.cpu()
+                ent_c = ent.cpu() if (with_entropy and not use_ref and ent is not None) else None
+                io_counters.add_d2h(io_counters.tensor_bytes(lp_c) + (io_counters.tensor_bytes(ent_c) if ent_c is not None
+                                                                      else 0))
+                o = 0
+                for i, ln in zip(idx, lens):
+                    samples[i][key] = lp_c[o:o + ln].clone()
+                    if ent_c is not None:
+                        samples[i]["prev_per_token_entropies"] = ent_c[o:o + ln].clone()
+                    o += ln
         if was_training:
             model.train()
         return samples
@@ -263,6 +344,15 @@ class TrainingEngine:
 
     def _reduce_metrics(self, acc: Dict[str, torch.Tensor]) -> Dict[str, float]:
         """``[sum, count]`` pairs become ratios after a sum over DP; scalars are averaged."""
+        pp = ps.get_pipeline_model_parallel_world_size()
+        if pp > 1:
+            # only the last stage evaluated the loss: it tells the others which metrics exist
+            box = [sorted(acc) if ps.is_pipeline_last_stage() else None]
+            g_pp = ps.get_pipeline_model_parallel_group()
+            dist.broadcast_object_list(box, src=dist.get_process_group_ranks(g_pp)[-1], group=g_pp)
+            for k in box[0]:
+                if k not in acc:
+                    acc[k] = torch.zeros(2, device=self.device)
         if not acc:
             return {}
         keys = sorted(acc)
@@ -271,6 +361,10 @@ class TrainingEngine:
         g = ps.get_data_parallel_group(with_context_parallel=True)
         if g is not None and dist.get_world_size(g) > 1:
             dist.all_reduce(flat, group=g)
+        if ps.get_pipeline_model_parallel_world_size() > 1:
+            if not ps.is_pipeline_last_stage():
+                flat.zero_()  # only the last stage evaluates the loss
+            dist.all_reduce(flat, group=ps.get_pipeline_model_parallel_group())
         flat = flat.cpu()
         io_counters.add_d2h(io_counters.tensor_bytes(flat))
         return {k: float(flat[i, 0] / flat[i, 1].clamp_min(1e-12)) for i, k in enumerate(keys)}
@@ -289,17 +383,19 @@ class TrainingEngine:
         denom = self._global_counts(samples, per_token)
         acc = {"lm_loss": torch.zeros(2, device=self.device)}
         with backend_scope(self.backend):
-            for idx in self._microbatches(samples):
-                mb = self._pack(samples, idx)
-                hidden, aux = self._hidden(self.model, mb)
+            batches = self._microbatches(samples)
+
+            def step(mb, hidden, aux):
                 lp, _ = self._logprob_entropy(self.model, hidden, mb.targets, want_entropy=False)
                 w = PL.aggregation_weights(mb.loss_mask, mb.seq_ids, mb.num_seqs + 1, per_token, denom)
                 loss = -(lp * w).sum()
                 if aux is not None:
-                    loss = loss + aux / max(len(samples) // max(len(idx), 1), 1)
-                loss.backward()
+                    loss = loss + aux / max(len(batches), 1)
                 with torch.no_grad():
                     acc["lm_loss"] += torch.stack([-(lp.detach() * mb.loss_mask).sum(), mb.loss_mask.sum()])
+                return loss
+
+            self._for_each_microbatch(self.model, samples, batches, (), step)
             lr, gn = self._finish_step()
         out = self._reduce_metrics(acc)
         out.update(lr=lr, grad_norm=gn)
@@ -338,9 +434,7 @@ class TrainingEngine:
         for s in samples:
             s.setdefault("loss_mask", s["mask"])
         with backend_scope(self.backend):
-            for idx in self._microbatches(samples):
-                mb = self._pack(samples, idx, keys)
-                hidden, aux = self._hidden(self.model, mb)
+            def step(mb, hidden, aux):
                 lp, ent = self._logprob_entropy(self.model, hidden, mb.targets, want_ent)
                 f = mb.fields
                 w = PL.aggregation_weights(mb.loss_mask, mb.seq_ids, mb.num_seqs + 1, per_token, denom)
@@ -386,7 +480,9 @@ class TrainingEngine:
                         add("policy/entropy", torch.stack([(ent.detach() * mb.loss_mask).sum(), mb.loss_mask.sum()]))
                 if aux is not None:
                     loss = loss + aux
-                loss.backward()
+                return loss
+
+            self._for_each_microbatch(self.model, samples, self._microbatches(samples), keys, step)
             lr, gn = self._finish_step()
         out = self._reduce_metrics(acc)
         out.update({"policy/lr": lr, "policy/grad_norm": gn})

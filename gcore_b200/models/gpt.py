@@ -14,6 +14,7 @@ The forward returns the final hidden states; the vocabulary projection is fused 
 from __future__ import annotations
 
 import math
+import re
 from typing import Optional
 
 import torch
@@ -360,7 +361,10 @@ class GPTModel(nn.Module):
                     p.fill_(1.0)
                 continue
             mode = getattr(p, "tp_mode", "none")
-            key = zlib.crc32(f"{self.layer_offset}:{name}".encode()) ^ seed
+            # keyed by the parameter's name in the unpartitioned model, so a pipeline stage draws the same values
+            canon = re.sub(r"decoder\.layers\.(\d+)\.", lambda m: f"decoder.layers.{int(m.group(1)) + self.layer_offset}.",
+                           name)
+            key = zlib.crc32(f"0:{canon}".encode()) ^ seed
             full_numel = p.numel() * (self.tp_size if mode in ("column", "row") else 1)
             with torch.no_grad():
                 if mode == "expert" and self.ep_size > 1:

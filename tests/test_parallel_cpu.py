@@ -120,3 +120,27 @@ def test_cp_plan_covers_every_key_row_once():
                 assert plans[src].k0 + src_row == r * s + dst_row
         if window:
             assert all(p.k0 >= r * s - (window - 1) for r, p in enumerate(plans))
+
+
+def test_pp2_1f1b_matches_single_process(tmp_path):
+    """Two pipeline stages (1F1B over gloo p2p, 4 micro-batches): same losses, gradient norm and log-probs."""
+    import parallel_worker as pw
+    from gcore_b200.models.config import get_preset
+    out = tmp_path / "pp.json"
+    _spawn("pp", out, port="29547")
+    got = json.load(open(out))
+    mcfg = get_preset("tiny_llama", dtype="float32", qkv_bias=True, num_layers=4)
+    e = pw.engine(mcfg, 1)
+    ref = [e.finetune_step(pw.samples(8, 130 + s))["lm_loss"] for s in range(4)]
+    for a, b in zip(ref, got["losses"]):
+        assert abs(a - b) < 5e-4, (ref, got["losses"])
+    assert abs(float(e.optimizer.last_grad_norm) - got["grad_norm"]) < 5e-3
+    lp = e.compute_log_probs(pw.samples(3, 199))
+    for a, b in zip(lp, got["logprobs"]):
+        assert torch.allclose(a["logprobs"], torch.tensor(b), atol=2e-4)
+
+
+def test_stage_layer_ranges():
+    from gcore_b200.parallel.pp import stage_layer_range
+    assert [stage_layer_range(12, 4, s) for s in range(4)] == [(0, 3), (3, 6), (6, 9), (9, 12)]
+    assert [stage_layer_range(10, 4, s, 2, 2) for s in range(4)] == [(0, 2), (2, 5), (5, 8), (8, 10)]

@@ -1,4 +1,4 @@
-"""gloo worker for the parallelism parity tests: mode = tp | ep | cp."""
+"""gloo worker for the parallelism parity tests: mode = tp | ep | cp | pp."""
 import json
 import os
 import sys
@@ -75,6 +75,17 @@ def main():
         for s in range(4):
             losses.append(e.finetune_step(samples(8, 90 + s))["lm_loss"])  # CP ranks see the same data
         lp = e.compute_log_probs(samples(3, 99))
+        res = {"losses": losses, "grad_norm": float(e.optimizer.last_grad_norm),
+               "logprobs": [x["logprobs"].tolist() for x in lp]}
+    elif mode == "pp":
+        ps.initialize_model_parallel(tp=1, pp=2)
+        mcfg = get_preset("tiny_llama", dtype="float32", qkv_bias=True, num_layers=4)
+        e = engine(mcfg, 1)
+        assert len(e.model.decoder.layers) == 2
+        losses = []
+        for s in range(4):
+            losses.append(e.finetune_step(samples(8, 130 + s))["lm_loss"])  # pipeline ranks see the same data
+        lp = e.compute_log_probs(samples(3, 199))
         res = {"losses": losses, "grad_norm": float(e.optimizer.last_grad_norm),
                "logprobs": [x["logprobs"].tolist() for x in lp]}
     if rank == 0:

@@ -211,3 +211,51 @@ def test_rpc_clients_and_transfer_queue():
     assert tq.get_batch(3, ["tokens"], 8, dp_rank=0, dp_size=1) == []  # everything was consumed once
     tq.clear_step(3)
     assert len(tq.storage) == 0
+
+
+def test_async_rollout_controller_staleness_tail_and_dp_split():
+    import time
+
+    from gcore_b200.rollout_generator.async_rollout import RolloutController
+
+    class Sampler:
+        def __init__(self, delay):
+            self.delay = delay
+
+        def generate(self, prompts, params=None):
+            time.sleep(self.delay)
+            return [{"tokens": list(p) + [7, 8]} for p in prompts]
+
+    def prompts():
+        i = 0
+        while True:
+            yield [[i * 10 + j] for j in range(4)]
+            i += 1
+
+    def score(samples):
+        for s in samples:
+            s["rewards"] = float(len(s["tokens"]))
+        return samples
+
+    c = RolloutController(prompts(), [Sampler(0.002), Sampler(0.004)], score, repeat_n=3, groups_per_batch=4,
+                          max_staleness=1)
+    c.set_weight_version(0)
+    b0 = c.collect(timeout_s=30)
+    assert len(b0) == 12 and all(s["weight_version"] == 0 for s in b0)
+    assert len({s["group_id"] for s in b0}) == 4 and all(s["prompt_length"] == 1 for s in b0)
+    # two versions later the groups still queued from version 0 are too stale and must be dropped
+    time.sleep(0.05)
+    c.set_weight_version(2)
+    b1 = c.collect(timeout_s=30)
+    assert all(2 - s["weight_version"] <= 1 for s in b1) and c.stats["dropped_stale"] > 0
+    parts = RolloutController.split_for_dp(b1, 2, 3)
+    assert [len(p) for p in parts] == [6, 6]
+    assert not {s["group_id"] for s in parts[0]} & {s["group_id"] for s in parts[1]}
+    c.shutdown()
+    # tail batching: a straggling sampler does not hold the batch back for ever
+    c2 = RolloutController(prompts(), [Sampler(0.001), Sampler(1.5)], score, repeat_n=2, groups_per_batch=6,
+                           max_staleness=0, max_inflight=6, tail_wait_s=0.2)
+    t0 = time.time()
+    b = c2.collect(timeout_s=30)
+    assert 0 < len(b) < 12 and time.time() - t0 < 1.4 and c2.stats["tail_batches"] == 1
+    c2.shutdown()

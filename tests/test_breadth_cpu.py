@@ -259,3 +259,62 @@ def test_async_rollout_controller_staleness_tail_and_dp_split():
     b = c2.collect(timeout_s=30)
     assert 0 < len(b) < 12 and time.time() - t0 < 1.4 and c2.stats["tail_batches"] == 1
     c2.shutdown()
+
+
+def test_dynamic_cp_schedule_invariants():
+    from gcore_b200.parallel.dynamic_cp import cp_size_for, imbalance, schedule
+    assert [cp_size_for(n, 1000, 8) for n in (10, 1000, 1001, 3500, 8000)] == [1, 1, 2, 4, 8]
+    with pytest.raises(ValueError):
+        cp_size_for(9000, 1000, 8)
+    g = torch.Generator().manual_seed(0)
+    lens = torch.exp(torch.randn(64, generator=g) * 1.2 + 6).clamp(16, 7000).long().tolist()
+    plan = schedule(lens, 8, 1000)
+    assert sorted(a.gid for a in plan) == list(range(64))
+    for a in plan:
+        assert a.block_start % a.cp_size == 0 and a.block_start + a.cp_size <= 8
+        assert -(-lens[a.gid] // a.cp_size) <= 1000
+    # per micro-step and rank the token budget holds
+    load = {}
+    for a in plan:
+        for r in range(a.block_start, a.block_start + a.cp_size):
+            load[(a.step, r)] = load.get((a.step, r), 0) + -(-lens[a.gid] // a.cp_size)
+    assert max(load.values()) <= 1000
+    assert imbalance(plan, lens, 8) < 1.35
+
+
+def _dyncp_worker(rank, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=4)
+    from gcore_b200.parallel import dynamic_cp as D
+    g = dist.group.WORLD
+    groups = D.build_block_groups(g)
+    lens = {0: [900, 30], 1: [40, 2100], 2: [50], 3: [3900, 20, 10]}[rank]
+    samples = [{"tokens": torch.full((n,), rank * 10 + i)} for i, n in enumerate(lens)]
+    all_lens, offsets = D.gather_lengths(samples, g)
+    plan = D.schedule(all_lens, 4, 1000)
+    steps = D.reroute_samples(samples, plan, offsets, g)
+    mine = [s for st in steps for s in st]
+    ok_blocks = all(s["_block"][0] <= rank < s["_block"][0] + s["_block"][1] for s in mine)
+    for s in mine:
+        s["logprobs"] = s["tokens"].float() + 0.5
+    back = D.reverse_reroute(mine, len(samples), g)
+    ok_back = all(torch.equal(b["logprobs"], samples[i]["tokens"].float() + 0.5) for i, b in enumerate(back))
+    q.put((rank, ok_blocks, ok_back, sorted(groups), len(mine)))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_dynamic_cp_reroute_round_trip():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_dyncp_worker, args=(r, 29563, q)) for r in range(4)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in range(4))
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    assert all(r[1] and r[2] for r in res)
+    assert res[0][3] == [(0, 2), (0, 4), (2, 2)]
+    # the 3900-token sample needs all four ranks, the 2100-token one a block of four too (3 -> 4): everyone sees them
+    assert all(r[4] >= 2 for r in res)

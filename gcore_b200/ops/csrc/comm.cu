@@ -169,9 +169,42 @@ __global__ void __launch_bounds__(256) peer_rows_kernel(RowsParams p) {
   }
 }
 
+// dst[i, 0:cols] = src[i, 0:cols] for i < rows; src may be a peer GPU's memory (weight resync pulls the pieces of a
+// rollout tensor straight out of the trainer ranks' staged shards).  16-byte vectors; cols, leading dimensions and
+// both base addresses are multiples of 8 elements.
+__global__ void __launch_bounds__(256) peer_copy_2d_kernel(__nv_bfloat16* __restrict__ dst, long long dst_ld,
+                                                           const __nv_bfloat16* __restrict__ src, long long src_ld,
+                                                           long long rows, int cols) {
+  const int cv = cols >> 3;
+  const long long n = rows * cv;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / cv;
+    const int c = static_cast<int>(i - r * cv);
+    uint4 v;
+    asm volatile("ld.global.relaxed.sys.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src + r * src_ld + c * 8) : "memory");
+    *reinterpret_cast<uint4*>(dst + r * dst_ld + c * 8) = v;
+  }
+}
+
 }  // namespace gkx
 
 using namespace gkx;
+
+GK_EXPORT int gk_peer_copy_2d(void* dst, long long dst_ld, const void* src, long long src_ld, long long rows, int cols,
+                              void* stream) {
+  if ((cols & 7) || (dst_ld & 7) || (src_ld & 7) || (reinterpret_cast<uintptr_t>(dst) & 15) ||
+      (reinterpret_cast<uintptr_t>(src) & 15))
+    return -1;
+  if (rows == 0 || cols == 0) return 0;
+  const long long n = rows * (cols >> 3);
+  long long want = (n + 255) / 256;
+  const long long cap = 8LL * gk::sm_count();
+  peer_copy_2d_kernel<<<static_cast<unsigned>(want < cap ? want : cap), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<__nv_bfloat16*>(dst), dst_ld, reinterpret_cast<const __nv_bfloat16*>(src), src_ld, rows, cols);
+  return gk::launch_status();
+}
 
 // segs: nseg triples (source address, first element, end element) in destination element coordinates; all multiples
 // of 8 elements.  Elements covered by no segment become zero.

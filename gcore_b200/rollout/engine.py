@@ -239,6 +239,7 @@ class InferEngine:
         self.stats = dict(decode_steps=0, prefill_tokens=0, generated_tokens=0, graph_replays=0)
         self.record_routed_experts = False
         self._peer_ar = None
+        self.weight_scales: dict = {}  # name -> fp32 128x128 block scales when weights are held in e4m3
 
     # ------------------------------------------------------------------ memory
     def _kv_bytes_per_block(self):

@@ -12,6 +12,7 @@ on-the-fly 128x128 block-fp8 quantisation of the destination; no host staging an
 """
 from __future__ import annotations
 
+import ctypes
 import hashlib
 from typing import Dict, List, Optional, Tuple
 
@@ -58,6 +59,116 @@ def reshard_tensor(name: str, shards: List[torch.Tensor], mode: str, dst_tp: int
     return torch.cat([full[a:b] for a, b in _rows_for_rank(name, full_rows, dst_tp, dst_rank, cfg)], 0)
 
 
+def copy_segments(name: str, shape, mode: str, src_tp: int, dst_tp: int, dst_rank: int, cfg):
+    """Which pieces of which trainer ranks' shards make up rollout rank ``dst_rank``'s tensor:
+    ``[(src_rank, src_row0, src_col0, dst_row0, dst_col0, rows, cols)]`` in element coordinates of the local
+    (sharded) tensors.  ``shape`` is the trainer-side local shape."""
+    rows = shape[0]
+    cols = 1
+    for d in shape[1:]:
+        cols *= d
+    if mode == "none" or (src_tp == 1 and dst_tp == 1):
+        return [(0, 0, 0, 0, 0, rows, cols)]
+    if mode == "row":
+        full_c = cols * src_tp
+        c = full_c // dst_tp
+        a, b = dst_rank * c, (dst_rank + 1) * c
+        segs = []
+        for r in range(src_tp):
+            lo, hi = max(a, r * cols), min(b, (r + 1) * cols)
+            if lo < hi:
+                segs.append((r, 0, lo - r * cols, 0, lo - a, rows, hi - lo))
+        return segs
+    full_rows = rows * src_tp
+    src_ranges = []
+    for r in range(src_tp):
+        o = 0
+        for a, b in _rows_for_rank(name, full_rows, src_tp, r, cfg):
+            src_ranges.append((a, b, r, o))
+            o += b - a
+    src_ranges.sort()
+    segs, d = [], 0
+    for a, b in _rows_for_rank(name, full_rows, dst_tp, dst_rank, cfg):
+        for sa, sb, r, o in src_ranges:
+            lo, hi = max(a, sa), min(b, sb)
+            if lo < hi:
+                segs.append((r, o + lo - sa, 0, d + lo - a, 0, hi - lo, cols))
+        d += b - a
+    return segs
+
+
+class PeerWeightSync:
+    """Trainer TP shards -> rollout layout over NVLink peer memory: every trainer rank stages its shards of a bucket
+    in a symmetric buffer, and each rank pulls exactly the row / column ranges its rollout tensors are made of from
+    the owners' staging memory straight into the rollout tensors (``gk_peer_copy_2d``).  No all-gather, no full-size
+    intermediate, no host staging."""
+
+    def __init__(self, group, bucket_bytes: int, device):
+        from ..parallel.symm import SymmBuffer
+        from ..ops import _lib
+        self._lib = _lib
+        self.group, self.device = group, device
+        self.n, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.bucket_elems = bucket_bytes // 2
+        self.stage = [SymmBuffer(self.bucket_elems, torch.bfloat16, group, device) for _ in range(2)]
+        self.flags = SymmBuffer(64 * 8, torch.int32, group, device)
+        self.flags.t.zero_()
+        self.flag_ptrs = torch.tensor(self.flags.ptrs, dtype=torch.int64, device=device)
+        self.epoch = 0
+        self.buckets_done = 0
+        self.launches = 0
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+
+    def _barrier(self):
+        lib = self._lib
+        self.epoch += 1
+        self.launches += 1
+        lib.check(lib.kernels().gk_peer_barrier(lib.ptr(self.flag_ptrs), self.rank, self.n, 0, self.epoch,
+                                                lib.ptr(lib.err_flag(self.device)), lib.stream_ptr()), "sync_barrier")
+
+    def sync_bucket(self, names, src: Dict[str, torch.Tensor], dst: Dict[str, torch.Tensor], modes, tp_dst, dst_rank, cfg,
+                    quantize=None):
+        lib = self._lib
+        st = self.stage[self.buckets_done & 1]
+        offs, o = {}, 0
+        sharded = [n_ for n_ in names if modes[n_] in ("column", "row") and src[n_].dim() >= 2]
+        for n_ in names:
+            if n_ in sharded:
+                continue
+            if modes[n_] in ("column", "row"):  # sharded vectors (biases): a few KB, gathered with the library
+                shards = [torch.empty_like(src[n_]) for _ in range(self.n)]
+                dist.all_gather(shards, src[n_].contiguous(), group=self.group)
+                dst[n_].copy_(reshard_tensor(n_, shards, modes[n_], tp_dst, dst_rank, cfg).to(dst[n_].dtype))
+            else:  # replicated on every trainer rank: a local copy
+                dst[n_].copy_(src[n_].to(dst[n_].dtype))
+        for n_ in sharded:
+            t = src[n_]
+            offs[n_] = o
+            st.t[o:o + t.numel()].copy_(t.reshape(-1))
+            o += (t.numel() + 7) // 8 * 8
+        assert o <= self.bucket_elems
+        self._barrier()
+        for n_ in sharded:
+            s, d = src[n_], dst[n_]
+            s_cols = s.numel() // s.shape[0]
+            target = d if (quantize is None or d.dtype == torch.bfloat16) else torch.empty(d.shape, dtype=torch.bfloat16,
+                                                                                           device=d.device)
+            d_cols = target.numel() // target.shape[0]
+            for (r, sr, sc, dr, dc, rows, cols) in copy_segments(n_, tuple(s.shape), modes[n_], self.n, tp_dst, dst_rank, cfg):
+                sp = st.ptrs[r] + (offs[n_] + sr * s_cols + sc) * 2
+                dp = target.data_ptr() + (dr * d_cols + dc) * 2
+                self.launches += 1
+                lib.check(lib.kernels().gk_peer_copy_2d(ctypes.c_void_p(dp), d_cols, ctypes.c_void_p(sp), s_cols, rows,
+                                                        cols, lib.stream_ptr()), f"peer_copy_2d[{n_}]")
+            if target is not d:
+                quantize(n_, target, d)
+        self.buckets_done += 1
+
+    def finish(self):
+        self._barrier()  # nobody may restage while a peer is still pulling
+
+
 def plan_buckets(named_sizes: List[Tuple[str, int]], max_bytes: int) -> List[List[str]]:
     """Sequential buckets of at most ``max_bytes`` (native planner)."""
     import ctypes
@@ -89,6 +200,23 @@ def sync_weights(policy_engine, infer_engine, max_bucket_mb: int = 512, quantize
     dst = _engine_tensor_map(infer_engine, model)
     order = [(n, src[n].numel() * src[n].element_size()) for n in dst if n in src]
     moved = 0
+    peer = _peer_sync(policy_engine, tp_src, tp_dst, max_bucket_mb, src, dst)
+    if peer is not None:
+        dst_rank = dist.get_rank(infer_engine.tp_group) if (infer_engine.tp_group is not None and tp_dst > 1) else 0
+
+        def quant(name, bf16_tensor, d):
+            from ..ops.quant import quant_weight_128x128
+            q, scale = quant_weight_128x128(bf16_tensor.contiguous())
+            d.copy_(q)
+            infer_engine.weight_scales[name] = scale
+
+        for bucket in plan_buckets(order, max_bucket_mb << 20):
+            peer.sync_bucket(bucket, src, dst, modes, tp_dst, dst_rank, cfg, quant if quantize_fp8 else None)
+            moved += sum(dst[n].numel() * dst[n].element_size() for n in bucket)
+        peer.finish()
+        torch.cuda.current_stream().synchronize()
+        infer_engine.update_weights(infer_engine.w)
+        return {"bytes": float(moved), "peer_memory": 1.0, "launches": float(peer.launches)}
     for bucket in plan_buckets(order, max_bucket_mb << 20):
         for name in bucket:
             s = src[name]
@@ -114,6 +242,34 @@ def sync_weights(policy_engine, infer_engine, max_bucket_mb: int = 512, quantize
         torch.cuda.current_stream().synchronize()
     infer_engine.update_weights(infer_engine.w)
     return {"bytes": float(moved)}
+
+
+_PEER_SYNC: Dict = {}
+
+
+def _peer_sync(policy_engine, tp_src, tp_dst, max_bucket_mb, src, dst) -> Optional[PeerWeightSync]:
+    """The peer-memory path needs a GPU, trainer TP > 1 (otherwise everything is local), bf16 sources and
+    16-byte-aligned pieces; ``GCORE_PEER_WEIGHT_SYNC=0`` selects the all-gather path."""
+    import os
+    from ..ops import _lib
+    dev = next(iter(src.values())).device
+    if tp_src == 1 or tp_src == tp_dst or dev.type != "cuda" or not _lib.use_native() or \
+            os.environ.get("GCORE_PEER_WEIGHT_SYNC", "1") == "0" or not hasattr(_lib.kernels(), "gk_peer_copy_2d"):
+        return None
+    modes = {n: getattr(p, "tp_mode", "none") for n, p in policy_engine.model.named_parameters()}
+    for n in dst:
+        if n in src and modes.get(n) in ("column", "row") and src[n].dim() >= 2:
+            t = src[n]
+            width = t.numel() // max(t.shape[0], 1)
+            # every piece must start and end on a 16-byte boundary (row pieces: whole rows; column pieces: K / tp)
+            if t.dtype != torch.bfloat16 or width % 8 or (modes[n] == "row" and (width * tp_src // tp_dst) % 8):
+                return None
+    group = ps.get_tensor_model_parallel_group()
+    key = (id(group), max_bucket_mb)
+    if key not in _PEER_SYNC:
+        biggest = max(src[n].numel() * 2 for n in dst if n in src)  # a bucket holds at least the largest tensor
+        _PEER_SYNC[key] = PeerWeightSync(group, max(max_bucket_mb << 20, biggest + 4096), dev)
+    return _PEER_SYNC[key]
 
 
 def _engine_tensor_map(infer_engine, model) -> Dict[str, torch.Tensor]:

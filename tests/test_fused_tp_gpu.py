@@ -65,3 +65,18 @@ def test_context_parallel_attention_over_peer_memory(tmp_path):
         for name, ok in v.items():
             if isinstance(ok, bool):
                 assert ok, (k, name, res)
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_weight_resync_over_peer_memory_tp2_to_tp1(tmp_path):
+    out = tmp_path / "ws.json"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29579", os.path.join(ROOT, "tests", "workers", "weight_sync_worker.py"),
+           str(out)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    res = json.load(open(out))
+    for k, v in res.items():
+        for name, ok in v.items():
+            if isinstance(ok, bool):
+                assert ok, (k, name, res)

@@ -75,7 +75,7 @@ struct Cfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES_RAW = (192 * 1024) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr int TMEM_COLS = 2 * BN <= 32 ? 32 : 2 * BN <= 64 ? 64 : 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ +
                                     (MAX_GROUPS + 1) * 4;
 };
@@ -538,7 +538,12 @@ GK_EXPORT int gk_gemm_bf16(const void* A, long long lda, long long a_rows, int a
   GK_DISPATCH(32)
   GK_DISPATCH(64)
   GK_DISPATCH(128)
+  GK_DISPATCH(192)
   GK_DISPATCH(256)
+  if (bn == 224 && !b_mn) {  // 224 is not a whole number of 64-column chunks, which the MN-major B loads need
+    if (!a_mn) return launch_gemm<224, false, false>(tmA, tmB, p, grid, st);
+    return launch_gemm<224, true, false>(tmA, tmB, p, grid, st);
+  }
 #undef GK_DISPATCH
   return -16;
 }

@@ -33,14 +33,15 @@ def _scratch(device, ws_floats: int, counters: int):
     return ws, cnt
 
 
-def _pick_bn(n: int) -> int:
-    if n >= 192:
-        return 256
-    if n > 64:
-        return 128
-    if n > 32:
-        return 64
-    return 32
+def _pick_bn(n: int, m: int = 0, b_mn: bool = False) -> int:
+    """Tile width: the widest tile the output allows (most reuse per byte of L2 traffic)."""
+    if n < 192:
+        if n > 64:
+            return 128
+        if n > 32:
+            return 64
+        return 32
+    return 256  # 192 / 224 wide tiles exist in the kernel but did not pay off on B200 (the kernel is L2-bound)
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: torch.Tensor | None = None,
@@ -84,7 +85,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
             out.zero_()
         return out
     if bn is None:
-        bn = _pick_bn(N)
+        bn = _pick_bn(N, M, b_mn) if (ksplit == 1 and not transposed) else _pick_bn(N)
     if b_mn and bn < 64:
         bn = 64
     lib = _lib.kernels()

@@ -442,3 +442,19 @@ def test_skinny_cluster_splitk_gemm(T, N, K, bias, fp32):
     finally:
         G._SKINNY[0] = True
     _close(y, y2.float(), rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("bn,a_mn,b_mn", [(224, False, False), (224, True, False), (192, False, False),
+                                           (192, False, True), (192, True, True)])
+def test_gemm_intermediate_tile_widths(bn, a_mn, b_mn):
+    from gcore_b200.ops.gemm import gemm
+    torch.manual_seed(19)
+    M, N, K = 384, 1000, 512
+    a = _rand(K, M) if a_mn else _rand(M, K)
+    b = _rand(K, N, scale=0.05) if b_mn else _rand(N, K, scale=0.05)
+    ref = (a.float().t() if a_mn else a.float()) @ (b.float() if b_mn else b.float().t())
+    out = gemm(a, b, a_mn=a_mn, b_mn=b_mn, bn=bn)
+    _close(out, ref, rtol=1e-2, atol=1e-2)
+    acc = torch.ones(M, N, dtype=torch.float32, device="cuda")
+    gemm(a, b, a_mn=a_mn, b_mn=b_mn, bn=bn, out=acc, accumulate=True)
+    _close(acc, ref + 1.0, rtol=1e-2, atol=1e-2)

@@ -52,6 +52,8 @@ __device__ __forceinline__ void add8(float (&acc)[8], const uint4& w) {
 
 __global__ void __launch_bounds__(AR_THREADS) allreduce_oneshot_kernel(ArParams p) {
   __shared__ int s_ok;
+  gk::pdl_launch_dependents();
+  gk::pdl_wait();
   const unsigned int calls = *reinterpret_cast<volatile unsigned int*>(p.state);
   const int parity = calls & 1;
   const uint32_t epoch = (calls >> 1) + 1;
@@ -227,6 +229,9 @@ GK_EXPORT int gk_peer_rows(void* dst, long long n, int nseg, const unsigned long
   return gk::launch_status();
 }
 
+// 1: kernels of the decode chain are launched with programmatic stream serialization (see host_utils.h)
+GK_EXPORT void gk_set_pdl(int on) { gk::pdl_flag() = on; }
+
 GK_EXPORT int gk_allreduce_ctas() { return AR_CTAS; }
 
 // ptrs: [0..n) inbox base of every rank, [n..2n) flag base of every rank (device pointers as integers).
@@ -245,6 +250,6 @@ GK_EXPORT int gk_allreduce_oneshot(const void* in, void* out, long long n, int r
   }
   p.state = state;
   p.err = err;
-  allreduce_oneshot_kernel<<<AR_CTAS, AR_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  gk::launch_k(allreduce_oneshot_kernel, dim3(AR_CTAS), dim3(AR_THREADS), 0, reinterpret_cast<cudaStream_t>(stream), p);
   return gk::launch_status();
 }

@@ -58,6 +58,8 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const __nv_bfloat16* _
                                                           __nv_bfloat16* __restrict__ res_out,
                                                           float* __restrict__ rstd_out, int T, int H, float eps) {
   __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int nv = H >> 3;
   for (int row = blockIdx.x; row < T; row += gridDim.x) {
     const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + static_cast<size_t>(row) * H);
@@ -217,6 +219,8 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const int* __restrict
 // in [T, 2F] = [gate | up]; out [T, F] = silu(gate) * up
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, long long T,
                                   int F) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int nv = F >> 3;
   const long long total = T * nv;
   for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
@@ -330,7 +334,7 @@ GK_EXPORT int gk_rmsnorm_fwd(const void* x, const void* res, const void* w, void
                              int T, int H, float eps, void* stream) {
   if (H % 8) return -1;
   const int grid = T < sm_count() * 8 ? T : sm_count() * 8;
-  rmsnorm_fwd_kernel<<<grid > 0 ? grid : 1, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_k(rmsnorm_fwd_kernel, dim3(grid > 0 ? grid : 1), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
       reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(res),
       reinterpret_cast<const __nv_bfloat16*>(w), reinterpret_cast<__nv_bfloat16*>(y),
       reinterpret_cast<__nv_bfloat16*>(res_out), rstd, T, H, eps);
@@ -370,7 +374,7 @@ GK_EXPORT int gk_rope(void* x, const int* pos, int T, int nheads, int D, int rot
 GK_EXPORT int gk_swiglu_fwd(const void* in, void* out, long long T, int F, void* stream) {
   if (F % 8) return -1;
   if (T == 0) return 0;
-  swiglu_fwd_kernel<<<grid_for(T * (F / 8), 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_k(swiglu_fwd_kernel, dim3(grid_for(T * (F / 8), 256)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
       reinterpret_cast<const __nv_bfloat16*>(in), reinterpret_cast<__nv_bfloat16*>(out), T, F);
   return launch_status();
 }

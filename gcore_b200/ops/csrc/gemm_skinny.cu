@@ -80,17 +80,20 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   // Lane 0 of the producer warp initialises the barriers and puts the first loads in flight before anything else
   // happens in the CTA: the tensor-memory allocation, the CTA barrier and the cluster hand-shake all overlap them.
   int pre = 0;
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     mbar_init(tfull, 1);
     fence_barrier_init();
     pre = kblocks < p.stages ? kblocks : p.stages;
+    // the weight tiles do not depend on the previous kernel: they start streaming while it drains
     for (int kb = 0; kb < pre; ++kb) {
-      uint8_t* sa = smem + kb * stage_bytes;
       mbar_expect_tx(&full[kb], stage_bytes);
-      tma_load_2d(sa, &tmW, &full[kb], (kb0 + kb) * BK, n0);
-      tma_load_2d(sa + A_BYTES, &tmX, &full[kb], (kb0 + kb) * BK, 0);
+      tma_load_2d(smem + kb * stage_bytes, &tmW, &full[kb], (kb0 + kb) * BK, n0);
     }
+    pdl_wait();  // the activations do
+    for (int kb = 0; kb < pre; ++kb)
+      tma_load_2d(smem + kb * stage_bytes + A_BYTES, &tmX, &full[kb], (kb0 + kb) * BK, 0);
   }
   if (warp == 2) { tmem_alloc(tmem_holder, tmem_cols); tmem_relinquish(); }
   tc_fence_before();
@@ -99,6 +102,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
   // first half of "every CTA of the cluster is running"; the matching wait sits right before the first remote store
   if (p.ks > 1) cluster_arrive();
+  pdl_wait();
 
   bool ok = true;
   if (warp == 0) {
@@ -294,13 +298,15 @@ GK_EXPORT int gk_gemm_skinny(const void* W, long long ldw, const void* X, long l
   cfg.blockDim = dim3(THREADS, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = reinterpret_cast<cudaStream_t>(stream);
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = ks;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = gk::pdl_flag() ? 1 : 0;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   if (cudaLaunchKernelEx(&cfg, gemm_skinny_kernel, tmW, tmX, p) != cudaSuccess) return gk::launch_status() ? gk::launch_status() : -7;
   return gk::launch_status();
 }

@@ -259,6 +259,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -274,6 +275,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     prefetch_tmap(&tmB);
   }
   if (threadIdx.x == 32 && p.group_mode == 1) {
+    pdl_wait();  // the group offsets come from the kernel before this one
     int acc = 0;
     s_prefix[0] = 0;
     for (int g = 0; g < p.num_groups; ++g) {
@@ -290,6 +292,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
   const int ntiles = total_tiles(p, s_prefix, BN);
+  pdl_wait();  // barrier set-up, tensor-memory allocation and descriptor prefetch overlapped the previous kernel
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -455,7 +458,7 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  gemm_bf16_kernel<BN, A_MN, B_MN><<<grid, GEMM_THREADS, C::SMEM_BYTES, st>>>(tmA, tmB, p);
+  launch_k(gemm_bf16_kernel<BN, A_MN, B_MN>, dim3(grid), dim3(GEMM_THREADS), C::SMEM_BYTES, st, tmA, tmB, p);
   return launch_status();
 }
 

@@ -96,6 +96,36 @@ inline int sm_count() {
   return n;
 }
 
+// ---- programmatic dependent launch: a kernel launched through launch_k may start its prologue while the previous
+// kernel of the stream is still draining; it must call pdl_wait() before it touches global memory, and it calls
+// pdl_launch_dependents() first so that its own successor may be scheduled early.  Both instructions are no-ops in a
+// kernel that was launched the ordinary way.  Off unless gk_set_pdl(1) (the rollout engine switches it on around the
+// decode chain, where ~300 short kernels per step make the launch gaps a measurable share of the step).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+inline int& pdl_flag() {
+  static int flag = 0;
+  return flag;
+}
+template <typename... KArgs, typename... Args>
+inline void launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  if (!pdl_flag()) {
+    kernel<<<grid, block, smem, st>>>(args...);
+    return;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 inline int launch_status() {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {

@@ -1,7 +1,8 @@
 // Rollout-decoder attention: RoPE-fused KV-cache append and split-KV paged decode attention (GQA, optional
-// sliding window and per-head sink logit).  Both are HBM-bandwidth bound, so they run on CUDA cores with
-// 128-bit loads; a CTA serves one (request, kv-head, KV split) and all query heads of the group so every K/V
-// byte is read once.  Stands in for the vLLM / SGLang attention back ends the reference drives
+// sliding window and per-head sink logit).  Both are HBM-bandwidth bound: a CTA serves one (request, kv-head, KV split)
+// and all query heads of the group so every K/V byte is read once (16-byte cp.async into swizzled shared memory); the
+// scores run on mma.sync tiles (8 query heads are far below the 64-row minimum of a tcgen05 instruction), with a
+// CUDA-core kernel for GQA groups wider than 8.  Stands in for the vLLM / SGLang attention back ends the reference drives
 // (gpatch_v4/generation_backend/infer_engine.py:479-768).
 #include "host_utils.h"
 #include <cuda_bf16.h>
@@ -21,6 +22,8 @@ __global__ void kv_append_rope_kernel(__nv_bfloat16* __restrict__ qkv, const int
                                       const int* __restrict__ slots, __nv_bfloat16* __restrict__ kc,
                                       __nv_bfloat16* __restrict__ vc, int T, int Hq, int Hk, int D, int rot,
                                       float theta, int do_rope) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   if (t >= T) return;
   const int half = rot >> 1;
@@ -73,6 +76,7 @@ __global__ void __launch_bounds__(PD_THREADS, 4) paged_decode_kernel(
   const int len = ctx_len[b];
   int start = 0;
   if (window > 0 && len > window) start = len - window;
+  if (split > 0 && start + split * PD_SPLIT >= len) return;  // dead split: the combine kernel skips it
   const int s0 = start + split * PD_SPLIT;
   int s1 = s0 + PD_SPLIT;
   if (s1 > len) s1 = len;
@@ -224,11 +228,15 @@ __global__ void __launch_bounds__(PD2_WARPS * 32, 3) paged_decode_mma_kernel(
   uint8_t* k_tile = pd3_dyn;
   uint8_t* v_tile = pd3_dyn + PD2_WARPS * 32 * 256;
 
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
   const int G = Hq / Hk;
   const int len = ctx_len[b];
   int start = 0;
   if (window > 0 && len > window) start = len - window;
+  // splits beyond this request's context have nothing to do (the combine kernel only reads the live ones)
+  if (split > 0 && start + split * PD_SPLIT >= len) return;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int w0 = start + split * PD_SPLIT + warp * PD2_TOK_PER_WARP;
   int w1 = w0 + PD2_TOK_PER_WARP;
@@ -386,9 +394,17 @@ __global__ void __launch_bounds__(PD2_WARPS * 32, 3) paged_decode_mma_kernel(
 
 template <int D>
 __global__ void paged_decode_combine_kernel(const float* __restrict__ scratch, const float* __restrict__ sinks,
-                                            __nv_bfloat16* __restrict__ out, int Hq, int nsplit) {
+                                            const int* __restrict__ ctx_len, int window,
+                                            __nv_bfloat16* __restrict__ out, int Hq, int nsplit_total) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
-  const float* base = scratch + (static_cast<long long>(b) * Hq + h) * nsplit * (D + 2);
+  const float* base = scratch + (static_cast<long long>(b) * Hq + h) * nsplit_total * (D + 2);
+  int span = ctx_len[b];
+  if (window > 0 && span > window) span = window;
+  int nsplit = (span + PD_SPLIT - 1) / PD_SPLIT;  // live splits: the others were never written
+  if (nsplit < 1) nsplit = 1;
+  if (nsplit > nsplit_total) nsplit = nsplit_total;
   float m = -FLT_MAX;
   for (int s = 0; s < nsplit; ++s) m = fmaxf(m, base[s * (D + 2) + D]);
   float l = 0.f, acc = 0.f;
@@ -411,7 +427,7 @@ GK_EXPORT int gk_kv_append_rope(void* qkv, const int* pos, const int* slots, voi
   (void)reserved;
   if (T == 0) return 0;
   if ((Hk * D) % 8) return -1;
-  kv_append_rope_kernel<<<T, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_k(kv_append_rope_kernel, dim3(T), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream),
       reinterpret_cast<__nv_bfloat16*>(qkv), pos, slots, reinterpret_cast<__nv_bfloat16*>(kc),
       reinterpret_cast<__nv_bfloat16*>(vc), T, Hq, Hk, D, rot, theta, do_rope);
   return launch_status();
@@ -443,7 +459,7 @@ GK_EXPORT int gk_paged_decode(const void* q, const void* kc, const void* vc, con
       cudaFuncSetAttribute(paged_decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PD2_SMEM);
       configured = true;
     }
-    paged_decode_mma_kernel<<<grid, PD2_WARPS * 32, PD2_SMEM, st>>>(
+    launch_k(paged_decode_mma_kernel, grid, dim3(PD2_WARPS * 32), PD2_SMEM, st,
         reinterpret_cast<const __nv_bfloat16*>(q), q_stride, reinterpret_cast<const __nv_bfloat16*>(kc),
         reinterpret_cast<const __nv_bfloat16*>(vc), block_table, max_blocks, ctx_len, sinks,
         reinterpret_cast<__nv_bfloat16*>(out), scratch, Hq, Hk, block_size, window, scale, nsplit);
@@ -453,7 +469,7 @@ GK_EXPORT int gk_paged_decode(const void* q, const void* kc, const void* vc, con
       reinterpret_cast<const __nv_bfloat16*>(vc), block_table, max_blocks, ctx_len, sinks,
       reinterpret_cast<__nv_bfloat16*>(out), scratch, Hq, Hk, block_size, window, scale, nsplit);
   if (nsplit > 1) {
-    paged_decode_combine_kernel<128><<<dim3(B, Hq), 128, 0, st>>>(scratch, sinks,
+    launch_k(paged_decode_combine_kernel<128>, dim3(B, Hq), dim3(128), 0, st, scratch, sinks, ctx_len, window,
                                                                   reinterpret_cast<__nv_bfloat16*>(out), Hq, nsplit);
   }
   return launch_status();

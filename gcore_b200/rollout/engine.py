@@ -370,7 +370,20 @@ class InferEngine:
 
     @torch.no_grad()
     def _decode_math(self, st):
-        """One token for every row of the batch state ``st`` (all tensors static: graph-capturable)."""
+        """One token for every row of the batch state ``st`` (all tensors static: graph-capturable).  The chain of
+        ~10 short kernels per layer is launched with programmatic dependent launch: each kernel's set-up (and, for the
+        cluster GEMM, its first weight tiles) overlaps the tail of the one before (``GCORE_PDL=0`` disables)."""
+        pdl = (self.device.type == "cuda" and not _lib.force_eager() and os.environ.get("GCORE_PDL", "1") != "0"
+               and hasattr(_lib.kernels(), "gk_set_pdl"))
+        if pdl:
+            _lib.kernels().gk_set_pdl(1)
+        try:
+            self._decode_layers(st)
+        finally:
+            if pdl:
+                _lib.kernels().gk_set_pdl(0)
+
+    def _decode_layers(self, st):
         cfg = self.cfg
         B = st["tokens"].numel()
         pos = st["pos"]

@@ -43,11 +43,14 @@ def main():
     ap.add_argument("--tokens", type=int, default=64)
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--json", default=None)
+    ap.add_argument("--pdl", type=int, default=0, help="launch the native kernels with programmatic dependent launch")
     args = ap.parse_args()
     from gcore_b200.ops import _lib, fused
     from gcore_b200.ops.attention import kv_append_rope, paged_decode
     from gcore_b200.ops.gemm import gemm, linear_forward
     dev = torch.device("cuda")
+    if args.pdl:
+        _lib.kernels().gk_set_pdl(1)
     T, tp = args.tokens, args.tp
     H, F, hq, hk, D = 3584, 18944 // tp, 28 // tp, 4 // tp, 128
     res = {}
@@ -93,6 +96,25 @@ def main():
     slots = (bt[:, (ctx_len - 1) // bs] * bs + (ctx_len - 1) % bs).to(torch.int32)
     res["kv_append_rope"] = round(graph_time(
         [lambda: kv_append_rope(qkv, pos, slots, kc[0], vc[0], hq, hk, D, 1e6) for _ in range(24)]), 2)
+    # one decoder layer as the rollout engine chains it (without the all-reduces)
+    Hd = H
+    wq = (torch.randn((hq + 2 * hk) * D, Hd, device=dev) * 0.02).bfloat16()
+    wo = (torch.randn(Hd, hq * D, device=dev) * 0.02).bfloat16()
+    w1 = (torch.randn(2 * F, Hd, device=dev) * 0.02).bfloat16()
+    w2 = (torch.randn(Hd, F, device=dev) * 0.02).bfloat16()
+    layers = [[t.clone() for t in (wq, wo, w1, w2)] for _ in range(6)]
+
+    def layer(i):
+        a, b, c, d2 = layers[i % 6]
+        h, r2 = fused.rmsnorm(x, g, 1e-6, r)
+        qkv2 = linear_forward(h, a)
+        kv_append_rope(qkv2, pos, slots, kc[i % 4], vc[i % 4], hq, hk, D, 1e6)
+        o = paged_decode(qkv2.view(T, hq + 2 * hk, D)[:, :hq], kc[i % 4], vc[i % 4], bt, ctx, max_len)
+        y = linear_forward(o.view(T, hq * D), b)
+        h2, _ = fused.rmsnorm(y, g, 1e-6, r2)
+        return linear_forward(fused.swiglu(linear_forward(h2, c)), d2)
+
+    res["layer_chain_us"] = round(graph_time([lambda i=i: layer(i) for i in range(12)]), 2)
     _lib.check_device_errors()
     print(json.dumps(res, indent=1))
     if args.json:

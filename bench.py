@@ -240,6 +240,8 @@ def main():
             "gpu_launches": int(launches),
             "phases_s": {k.split("/")[1]: round(v, 3) for k, v in phase.items()},
             "resync_ms": round(phase.get("time_perf/update_weights", 0.0) * 1e3, 3),
+            "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1),
+            "peak_reserved_gb": round(torch.cuda.max_memory_reserved() / 2**30, 1),
             "reward_mean": round(m["rollout-rewards/mean"], 4),
         }
         print(json.dumps(out), flush=True)

@@ -1,0 +1,215 @@
+"""Numerical definitions of the algorithm core against hand-written formulas: policy losses, KL estimators,
+off-policy correction, aggregation weights, value / DPO / Bradley-Terry losses, group-normalised and GAE advantages,
+rule rewards and datasets."""
+import json
+import math
+import types
+
+import pytest
+import torch
+
+from gcore_b200.core import advantage as A
+from gcore_b200.loss import policy_loss as PL
+
+
+def _cfg(**kw):
+    d = dict(clip_low=0.2, clip_high=0.3, ppo_dual_clip_ratio_c=None, ppo_logps_ratio_clamp=None, sapo_tau_pos=1.0,
+             sapo_tau_neg=1.05, offpolicy_correction="none", offpolicy_correction_level="token",
+             offpolicy_correction_upper=2.0, offpolicy_correction_lower=None, offpolicy_correction_veto=None)
+    d.update(kw)
+    return types.SimpleNamespace(**d)
+
+
+def _li(T=12, seqs=3, seed=0, roll=False):
+    g = torch.Generator().manual_seed(seed)
+    lp = (torch.randn(T, generator=g) * 0.3 - 1).requires_grad_(True)
+    old = lp.detach() + torch.randn(T, generator=g) * 0.3
+    adv = torch.randn(T, generator=g)
+    mask = (torch.rand(T, generator=g) > 0.2).float()
+    sid = torch.arange(T) * seqs // T
+    rl = old + torch.randn(T, generator=g) * 0.1 if roll else None
+    return PL.LossInput(lp, old, None, rl, adv, mask, sid.int(), seqs)
+
+
+def test_grpo_clip_asymmetric_and_dual_clip():
+    li = _li()
+    cfg = _cfg()
+    out = PL.get_loss("grpo")(cfg, li)
+    ratio = torch.exp(li.logp - li.old_logp)
+    ref = torch.maximum(-li.advantages * ratio, -li.advantages * ratio.clamp(0.8, 1.3))
+    assert torch.allclose(out.token_loss, ref, atol=1e-6)
+    # dual clip bounds the loss of negative-advantage tokens by -c * A
+    cfg2 = _cfg(ppo_dual_clip_ratio_c=3.0)
+    out2 = PL.get_loss("grpo")(cfg2, li)
+    neg = li.advantages < 0
+    ref2 = torch.where(neg, torch.minimum(ref, -3.0 * li.advantages), ref)
+    assert torch.allclose(out2.token_loss, ref2, atol=1e-6)
+    # gradient of an unclipped token is -A * ratio
+    out.token_loss.sum().backward()
+    unclipped = (ratio > 0.8) & (ratio < 1.3)
+    assert torch.allclose(li.logp.grad[unclipped], (-li.advantages * ratio).detach()[unclipped], atol=1e-5)
+
+
+def test_gspo_uses_one_ratio_per_sequence():
+    li = _li()
+    out = PL.get_loss("gspo")(_cfg(), li)
+    d = (li.logp - li.old_logp).detach() * li.mask
+    for s in range(3):
+        sel = li.seq_ids == s
+        expect = math.exp(float(d[sel].sum() / li.mask[sel].sum().clamp_min(1)))
+        assert torch.allclose(out.ratios[sel], torch.full_like(out.ratios[sel], expect), rtol=1e-5)
+
+
+def test_cispo_sapo_reinforce_gradients():
+    li = _li()
+    cfg = _cfg()
+    out = PL.get_loss("cispo")(cfg, li)
+    out.token_loss.sum().backward()
+    ratio = torch.exp(li.logp - li.old_logp).detach()
+    assert torch.allclose(li.logp.grad, -ratio.clamp(0.8, 1.3) * li.advantages, atol=1e-6)  # clipped IS weight, detached
+    li2 = _li(seed=1)
+    out2 = PL.get_loss("sapo")(cfg, li2)
+    r2 = torch.exp(li2.logp - li2.old_logp)
+    tau = torch.where(li2.advantages > 0, torch.tensor(1.0), torch.tensor(1.05))
+    assert torch.allclose(out2.token_loss, -li2.advantages * (4 / tau) * torch.sigmoid(tau * (r2 - 1)), atol=1e-6)
+    li3 = _li(seed=2)
+    assert torch.allclose(PL.get_loss("reinforce")(cfg, li3).token_loss, -li3.advantages * li3.logp)
+    with pytest.raises(KeyError):
+        PL.get_loss("no_such_loss")
+
+
+def test_vespo_sequence_kernel_is_detached():
+    li = _li(roll=True)
+    out = PL.get_loss("vespo")(_cfg(vespo_c1_pos=1.0, vespo_c1_neg=2.0, vespo_c2_pos=1.0, vespo_c2_neg=0.5), li)
+    out.token_loss.sum().backward()
+    # gradient = -phi(seq) * A : constant per sequence up to the advantage
+    g = -li.logp.grad / li.advantages
+    for s in range(3):
+        sel = (li.seq_ids == s)
+        assert torch.allclose(g[sel], g[sel][0].expand_as(g[sel]), rtol=1e-4, atol=1e-6)
+
+
+def test_kl_estimators():
+    lp, ref = torch.tensor([-1.0, -2.0, -0.5]), torch.tensor([-1.5, -1.0, -0.5])
+    d = ref - lp
+    assert torch.allclose(PL.kl_penalty(lp, ref, "k1"), -d)
+    assert torch.allclose(PL.kl_penalty(lp, ref, "k2"), 0.5 * d * d)
+    k3 = PL.kl_penalty(lp, ref, "k3")
+    assert torch.allclose(k3, torch.exp(d) - d - 1) and bool((k3 >= 0).all()) and k3[2] == 0
+    assert float(PL.kl_penalty(lp, ref, "k3", clamp=0.1).max()) <= 0.1 + 1e-7
+
+
+@pytest.mark.parametrize("mode", ["truncate", "clip", "mask", "icepop", "kpop"])
+def test_offpolicy_correction_modes(mode):
+    li = _li(T=16, seqs=4, roll=True)
+    cfg = _cfg(offpolicy_correction=mode, offpolicy_correction_upper=1.1)
+    w, m = PL.offpolicy_correction(cfg, li.old_logp, li.rollout_logp, li.mask, li.seq_ids, 4)
+    raw = torch.exp(li.old_logp - li.rollout_logp)
+    lo, hi = 1 / 1.1, 1.1
+    if mode == "truncate":
+        assert torch.allclose(w, raw.clamp(max=hi))
+    elif mode == "clip":
+        assert torch.allclose(w, raw.clamp(lo, hi))
+    elif mode == "mask":
+        assert torch.equal(w, ((raw >= lo) & (raw <= hi)).float())
+    elif mode == "icepop":
+        assert torch.allclose(w, torch.where((raw >= lo) & (raw <= hi), raw, torch.zeros_like(raw)))
+    else:
+        for s in range(4):
+            sel = li.seq_ids == s
+            assert bool((w[sel] == 0).all()) or bool((w[sel] > 0).all())  # whole sequences are kept or dropped
+    assert not w.requires_grad and "tis/weight_mean" in m
+    cfg_seq = _cfg(offpolicy_correction="truncate", offpolicy_correction_level="sequence")
+    ws, _ = PL.offpolicy_correction(cfg_seq, li.old_logp, li.rollout_logp, li.mask, li.seq_ids, 4)
+    for s in range(4):
+        sel = li.seq_ids == s
+        assert torch.allclose(ws[sel], ws[sel][0].expand_as(ws[sel]))
+
+
+def test_aggregation_weights_sum_to_share_of_global_loss():
+    mask = torch.tensor([1, 1, 0, 1, 1, 1.0])
+    sid = torch.tensor([0, 0, 0, 1, 1, 1], dtype=torch.int32)
+    w_tok = PL.aggregation_weights(mask, sid, 2, True, 10.0)
+    assert torch.allclose(w_tok, mask / 10) and abs(float(w_tok.sum()) - 0.5) < 1e-6
+    w_seq = PL.aggregation_weights(mask, sid, 2, False, 4.0)   # 4 alive sequences globally, 2 of them here
+    assert torch.allclose(w_seq, torch.tensor([1 / 2, 1 / 2, 0, 1 / 3, 1 / 3, 1 / 3]) / 4)
+    assert abs(float(w_seq.sum()) - 0.5) < 1e-6
+
+
+def test_value_dpo_and_bt_losses():
+    v, old, ret = torch.tensor([1.0, 3.0]), torch.tensor([0.0, 0.0]), torch.tensor([0.5, 0.5])
+    w = torch.tensor([0.5, 0.5])
+    assert abs(float(PL.value_loss(v, old, ret, w, None)) - 0.5 * (0.25 * 0.5 + 6.25 * 0.5)) < 1e-6
+    # clipping V to old +- 0.2 can only increase the loss (max of the two branches)
+    assert float(PL.value_loss(v, old, ret, w, 0.2)) >= float(PL.value_loss(v, old, ret, w, None))
+    pc, pr, rc, rr = torch.tensor([-5.0]), torch.tensor([-7.0]), torch.tensor([-6.0]), torch.tensor([-6.5])
+    out = PL.dpo_loss(pc, pr, rc, rr, beta=0.1)
+    loss = out[0] if isinstance(out, tuple) else out["loss"]
+    assert abs(float(loss) - float(-torch.nn.functional.logsigmoid(torch.tensor(0.1 * ((-5 + 7) - (-6 + 6.5)))))) < 1e-6
+    bt = PL.rm_bt_loss(torch.tensor([2.0, 0.0]), torch.tensor([1.0, 1.0]))
+    bt_loss = bt[0] if isinstance(bt, tuple) else bt["loss"] if isinstance(bt, dict) else bt
+    assert abs(float(bt_loss) - float(-torch.nn.functional.logsigmoid(torch.tensor([1.0, -1.0])).mean())) < 1e-6
+
+
+def test_group_normalised_advantages():
+    r = torch.tensor([1.0, 0.0, 0.0, 1.0, 5.0, 5.0, 5.0, 5.0])
+    gid = torch.tensor([0, 0, 0, 0, 1, 1, 1, 1])
+    adv = A.group_normalize(r, gid, None, eps=1e-6)
+    g0 = r[:4]
+    assert torch.allclose(adv[:4], (g0 - g0.mean()) / (g0.std() + 1e-6), atol=1e-5)
+    assert torch.allclose(adv[4:], torch.zeros(4), atol=1e-4)       # no spread: no signal
+    sm = torch.tensor([1, 1, 1, 0, 1, 1, 1, 1.0])
+    adv2 = A.group_normalize(r, gid, sm, eps=1e-6)
+    assert adv2[3] == 0 and abs(float(adv2[:3].sum())) < 1e-5        # invalid sample excluded from the statistics
+    adv3 = A.group_normalize(r, gid, None, eps=1e-6, norm_by_std=False)
+    assert torch.allclose(adv3[:4], g0 - g0.mean())
+
+
+def test_gae_matches_backward_recursion():
+    from gcore_b200.ops.rl import gae
+    torch.manual_seed(0)
+    B, S, gamma, lam = 3, 9, 0.97, 0.9
+    r, v = torch.randn(B, S), torch.randn(B, S)
+    m = torch.ones(B, S)
+    m[0, 6:] = 0
+    m[1, :2] = 0
+    adv, ret = gae(r, v, m, gamma, lam)
+    for b in range(B):
+        last = 0.0
+        idx = [t for t in range(S) if m[b, t] > 0]
+        exp = {}
+        for j in reversed(range(len(idx))):
+            t = idx[j]
+            nv = float(v[b, idx[j + 1]]) if j + 1 < len(idx) else 0.0
+            delta = float(r[b, t]) + gamma * nv - float(v[b, t])
+            last = delta + gamma * lam * last
+            exp[t] = last
+        for t in idx:
+            assert abs(float(adv[b, t]) - exp[t]) < 1e-4
+            assert abs(float(ret[b, t]) - (exp[t] + float(v[b, t]))) < 1e-4
+        assert all(float(adv[b, t]) == 0 for t in range(S) if m[b, t] == 0)
+
+
+def test_rule_reward_and_datasets(tmp_path):
+    from gcore_b200.data.datasets import IndexedJsonlDataset, ResumableDistributedSampler
+    from gcore_b200.reward.rewards import boxed_answer
+    assert boxed_answer("so the answer is \\boxed{42}.") == "42"
+    assert boxed_answer("nested \\boxed{\\frac{1}{2}} done") == "\\frac{1}{2}"
+    assert boxed_answer("none here") is None
+    p = tmp_path / "d.jsonl"
+    with open(p, "w") as f:
+        for i in range(10):
+            f.write(json.dumps({"id": i, "prompt": [1, 2, i]}) + "\n")
+    ds = IndexedJsonlDataset(str(p))
+    assert len(ds) == 10 and ds[7]["id"] == 7
+    s0 = ResumableDistributedSampler(len(ds), dp_rank=0, dp_size=2, shuffle=True, seed=3)
+    s1 = ResumableDistributedSampler(len(ds), dp_rank=1, dp_size=2, shuffle=True, seed=3)
+    a, b = list(iter(s0)), list(iter(s1))
+    assert sorted(a + b) == list(range(10))
+    # resume in the middle of an epoch: the remaining indices are exactly the tail of the same order
+    s0.set_start_index(3)
+    assert list(iter(s0)) == a[3:]
+    sd = s0.state_dict()
+    s2 = ResumableDistributedSampler(len(ds), dp_rank=0, dp_size=2, shuffle=True, seed=3)
+    s2.load_state_dict(sd)
+    assert list(iter(s2)) == a

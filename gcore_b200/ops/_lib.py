@@ -131,6 +131,7 @@ def _declare_kernels(lib: ctypes.CDLL):
     d("gk_ep_pull", [P, P, P, P, P, I, I, I, I, L, P])
     d("gk_peer_copy_2d", [P, L, P, L, L, I, P])
     d("gk_set_pdl", [I], None)
+    d("gk_set_peer_wait_budget", [L], None)
     d("gk_peer_rows", [P, L, I, P, P])
     d("gk_allreduce_oneshot", [P, P, L, I, I, L, P, P, P, P])
     d("gk_gemm_splitk_scratch", [I, I, I, I, ctypes.POINTER(L), ctypes.POINTER(L)], None)

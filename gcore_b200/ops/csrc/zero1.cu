@@ -141,7 +141,7 @@ __global__ void __launch_bounds__(THREADS) zero1_kernel(Z1Params p) {
 // Barrier across the ranks of a group: publish `epoch` into slot [slot][rank] of every peer's flag array, then wait
 // until every peer's epoch shows up in the own array.  One CTA, one thread per peer; waits are bounded.
 __global__ void peer_barrier_kernel(uint32_t* const* flags_by_rank, int rank, int nranks, int slot, uint32_t epoch,
-                                    int* err) {
+                                    int* err, long long budget) {
   __threadfence_system();
   const int t = threadIdx.x;
   if (t < nranks && t != rank) {
@@ -154,13 +154,15 @@ __global__ void peer_barrier_kernel(uint32_t* const* flags_by_rank, int rank, in
       uint32_t v;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
       if (static_cast<int32_t>(v - epoch) >= 0) break;
-      if ((++spins & 63) == 0 && (clock64() - t0 > WAIT_CYCLES || *reinterpret_cast<volatile int*>(err) != 0)) {
+      if ((++spins & 63) == 0 && (clock64() - t0 > budget || *reinterpret_cast<volatile int*>(err) != 0)) {
         atomicCAS(err, 0, 6);
         break;
       }
     }
   }
 }
+
+static long long g_barrier_budget = WAIT_CYCLES;
 
 }  // namespace gkz
 
@@ -195,6 +197,10 @@ GK_EXPORT int gk_peer_barrier(const void* flags_dev, int rank, int nranks, int s
                               void* stream) {
   if (nranks < 1 || nranks > MAX_RANKS) return -1;
   peer_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<uint32_t* const*>(flags_dev), rank, nranks, slot, epoch, err);
+      reinterpret_cast<uint32_t* const*>(flags_dev), rank, nranks, slot, epoch, err, gkz::g_barrier_budget);
   return gk::launch_status();
 }
+
+// Clock cycles a rank waits for its peers in gk_peer_barrier before it gives up, writes error code 6 and returns
+// (0 restores the default of ~20 s).  Failure-detection tests shorten it so that a missing peer shows up quickly.
+GK_EXPORT void gk_set_peer_wait_budget(long long cycles) { gkz::g_barrier_budget = cycles > 0 ? cycles : gkz::WAIT_CYCLES; }

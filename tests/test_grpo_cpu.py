@@ -55,3 +55,22 @@ def test_alternative_losses_run():
                          reward_fn=reward_has_small_token).setup()
         m = tr.step([[5, 6, 7, 8, 9], [10, 11, 12], [13, 14, 15, 16], [20, 21]])
         assert m["policy/grad_norm"] >= 0 and "ppo-metrics/pg_loss" in m
+
+
+def test_grpo_step_with_moe_policy_and_ppo_critic_value_path():
+    """MoE decoder through the whole loop (the rollout engine runs the router + grouped experts of the shared
+    module), and the trainer's log-probs still agree with the decoder's."""
+    from gcore_b200.models.config import ModelConfig
+    torch.manual_seed(1)
+    mcfg = ModelConfig(arch="qwen3_moe", num_layers=2, hidden_size=128, num_attention_heads=4, num_kv_heads=2,
+                       ffn_hidden_size=256, vocab_size=512, num_experts=8, moe_top_k=2, moe_ffn_hidden_size=64,
+                       moe_aux_loss_coef=1e-3, dtype="float32", qk_layernorm=True)
+    tr = GrpoTrainer(make_cfg(), model_cfg=mcfg, reward_fn=reward_has_small_token).setup()
+    g = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(3, 512, (6,), generator=g).tolist() for _ in range(4)]
+    for _ in range(2):
+        m = tr.step(prompts)
+    assert m["policy/grad_norm"] > 0
+    s = tr.last_samples[0]
+    P, S = s["prompt_length"], s["sequence_length"]
+    assert torch.allclose(s["logprobs"][P - 1:S - 1], s["rollout_log_probs"][P - 1:S - 1], atol=5e-3)

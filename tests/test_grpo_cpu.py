@@ -8,8 +8,9 @@ from gcore_b200.models.config import get_preset
 from gcore_b200.trainer.grpo_trainer import GrpoTrainer
 
 
-def make_cfg(**ppo):
-    return from_dict(RlConfig, {
+def make_cfg(critic=None, **ppo):
+    extra = {"critic": critic} if critic is not None else {}
+    return from_dict(RlConfig, {**extra,
         "training": {"rollout_gbs": 4, "sampling_repeat_n": 4, "train_gbs": 16, "train_mbs": 4, "seed": 3},
         "policy": {"recompute": "none"},
         "optimizer": {"lr": 3e-3, "lr_decay_style": "constant", "weight_decay": 0.0},
@@ -74,3 +75,18 @@ def test_grpo_step_with_moe_policy_and_ppo_critic_value_path():
     s = tr.last_samples[0]
     P, S = s["prompt_length"], s["sequence_length"]
     assert torch.allclose(s["logprobs"][P - 1:S - 1], s["rollout_log_probs"][P - 1:S - 1], atol=5e-3)
+
+
+def test_ppo_with_critic_runs_gae_and_value_update():
+    """advantage_type=ppo: a value-head critic supplies values, GAE builds advantages / returns, both models step."""
+    torch.manual_seed(2)
+    cfg = make_cfg(critic={"recompute": "none", "optimizer": {"lr": 1e-3, "lr_decay_style": "constant"}},
+                   advantage_type="ppo", ppo_gae_lambda=0.95, ppo_discount_factor=1.0)
+    tr = GrpoTrainer(cfg, model_cfg=get_preset("tiny_llama", dtype="float32"), reward_fn=reward_has_small_token).setup()
+    assert tr.critic is not None
+    g = torch.Generator().manual_seed(7)
+    prompts = [torch.randint(3, 1024, (8,), generator=g).tolist() for _ in range(4)]
+    m = tr.step(prompts)
+    assert "value/loss" in m and m["policy/grad_norm"] >= 0
+    s = tr.last_samples[0]
+    assert "values" in s and "returns" in s and s["advantages"].numel() == s["tokens"].numel()

@@ -425,11 +425,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             float v[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = 0.f;
-            for (int ks = 0; ks < p.ksplit; ++ks) {
-              const float* w = p.ws + (static_cast<long long>(t.mn_index) * p.ksplit + ks) * (BM * BN) +
-                               static_cast<long long>(c * 32) * BM + row_in_tile;
+            // four partials' loads are in flight together: the reduction costs ksplit / 4 trips to L2, not ksplit
+            for (int ks0 = 0; ks0 < p.ksplit; ks0 += 4) {
+              float part[4][32];
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] += __ldcg(w + j * BM);
+              for (int u = 0; u < 4; ++u) {
+                const int ks = ks0 + u < p.ksplit ? ks0 + u : ks0;  // a repeated slice is loaded but not added
+                const float* w = p.ws + (static_cast<long long>(t.mn_index) * p.ksplit + ks) * (BM * BN) +
+                                 static_cast<long long>(c * 32) * BM + row_in_tile;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) part[u][j] = __ldcg(w + j * BM);
+              }
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                if (ks0 + u < p.ksplit) {
+#pragma unroll
+                  for (int j = 0; j < 32; ++j) v[j] += part[u][j];
+                }
+              }
             }
             store_chunk(p, t, v, row, t.n0 + c * 32);
           }

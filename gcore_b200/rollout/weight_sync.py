@@ -244,6 +244,55 @@ def sync_weights(policy_engine, infer_engine, max_bucket_mb: int = 512, quantize
     return {"bytes": float(moved)}
 
 
+def _lora_targets(policy_engine) -> Dict[str, object]:
+    from ..models.gpt import ParallelLinear
+    return {n + ".weight": m.lora for n, m in policy_engine.model.named_modules()
+            if isinstance(m, ParallelLinear) and m.lora is not None}
+
+
+def detach_lora_targets(policy_engine, weights) -> List[str]:
+    """Gives the rollout weights private storage for every LoRA-adapted projection (everything else keeps sharing the
+    trainer's parameter storage) and fills it with base + delta."""
+    targets = _lora_targets(policy_engine)
+
+    class _W:  # minimal stand-in so that _engine_tensor_map can be reused before an engine exists
+        w = weights
+    tmap = _engine_tensor_map(_W, policy_engine.model)
+    attr = {"self_attention.linear_qkv.weight": "qkv_w", "self_attention.linear_proj.weight": "o_w",
+            "mlp.linear_fc1.weight": "fc1_w", "mlp.linear_fc2.weight": "fc2_w"}
+    done = []
+    for name in targets:
+        if name not in tmap:
+            continue
+        layer = int(name.split(".")[2])
+        suffix = name.split(".", 3)[3]
+        setattr(weights.layers[layer], attr[suffix], tmap[name].clone())
+        done.append(name)
+    return done
+
+
+def sync_lora_deltas(policy_engine, infer_engine) -> Dict[str, float]:
+    """LoRA resync: only the adapted projections change, and only the adapter factors (rank x (in + out) numbers per
+    projection) carry information, so the rollout copy of each adapted weight is rebuilt in place as
+    ``base + scale * B A`` and nothing else is touched (the reference re-exports adapters alone for its engines:
+    gpatch_v4/training_backend/megatron_backend/checkpoint.py:520-700, BASELINE config 5 "only LoRA deltas are
+    resynced")."""
+    targets = _lora_targets(policy_engine)
+    dst = _engine_tensor_map(infer_engine, policy_engine.model)
+    params = dict(policy_engine.model.named_parameters())
+    moved = factors = 0
+    with torch.no_grad():
+        for name, lora in targets.items():
+            if name not in dst:
+                continue
+            d = dst[name]
+            assert d.data_ptr() != params[name].data_ptr(), "LoRA target still shares the frozen base storage"
+            d.copy_((params[name].detach().float() + lora.delta_weight()).to(d.dtype))
+            moved += d.numel() * d.element_size()
+            factors += sum(p.numel() * p.element_size() for p in lora.parameters())
+    return {"bytes_rewritten": float(moved), "adapter_bytes": float(factors), "tensors": float(len(targets))}
+
+
 _PEER_SYNC: Dict = {}
 
 

@@ -72,8 +72,14 @@ class GrpoTrainer:
                                          model_cfg=self.policy.model_cfg, role="critic", value_head=True)
             self.critic.setup_model_and_get_optimizer(with_ref=False)
         model = self.policy.model
+        # with LoRA only the adapted projections differ from the frozen base: the rollout engine then owns copies of
+        # those tensors (base + delta, rewritten at every resync) and shares the storage of all the others
+        self.lora = bool(cfg.policy.lora.enabled)
         share = cfg.policy.share_rollout_weights
         weights = RolloutWeights.from_model(model, clone=not share)
+        if self.lora and share:
+            from ..rollout.weight_sync import detach_lora_targets
+            detach_lora_targets(self.policy, weights)
         t = cfg.training
         n_req = max(t.rollout_gbs // max(ps.get_data_parallel_world_size(), 1), 1) * t.sampling_repeat_n
         self.engine = InferEngine(
@@ -180,6 +186,9 @@ class GrpoTrainer:
     def update_weights(self):
         """Hands the updated weights to the rollout engine (zero-copy when storage is shared)."""
         if self.cfg.policy.share_rollout_weights:
+            if self.lora:
+                from ..rollout.weight_sync import sync_lora_deltas
+                sync_lora_deltas(self.policy, self.engine)
             self.engine.update_weights(None)
         else:
             from ..rollout.weight_sync import sync_weights

@@ -90,3 +90,30 @@ def test_ppo_with_critic_runs_gae_and_value_update():
     assert "value/loss" in m and m["policy/grad_norm"] >= 0
     s = tr.last_samples[0]
     assert "values" in s and "returns" in s and s["advantages"].numel() == s["tokens"].numel()
+
+
+def test_lora_grpo_resyncs_only_the_adapted_projections():
+    """LoRA on q/kv/o: the base stays frozen and shared with the rollout engine, the adapted projections get a private
+    rollout copy that is rebuilt from base + delta at every hand-over; the decoder's log-probs follow the adapters."""
+    torch.manual_seed(3)
+    cfg = make_cfg()
+    cfg.policy.lora.rank = 4      # rank > 0 switches LoRA on
+    cfg.policy.lora.alpha = 8
+    cfg.policy.lora.target_modules = ["linear_qkv", "linear_proj"]
+    tr = GrpoTrainer(cfg, model_cfg=get_preset("tiny_llama", dtype="float32"), reward_fn=reward_has_small_token).setup()
+    layer = tr.policy.model.decoder.layers[0]
+    lw = tr.engine.w.layers[0]
+    assert lw.qkv_w.data_ptr() != layer.self_attention.linear_qkv.weight.data_ptr()   # private (adapted)
+    assert lw.fc1_w.data_ptr() == layer.mlp.linear_fc1.weight.data_ptr()              # shared (not adapted)
+    base_before = layer.self_attention.linear_qkv.weight.detach().clone()
+    g = torch.Generator().manual_seed(8)
+    prompts = [torch.randint(3, 1024, (8,), generator=g).tolist() for _ in range(4)]
+    for _ in range(3):
+        m = tr.step(prompts)
+    assert m["policy/grad_norm"] > 0
+    assert torch.equal(layer.self_attention.linear_qkv.weight.detach(), base_before)  # frozen base
+    merged = base_before + layer.self_attention.linear_qkv.lora.delta_weight()
+    assert torch.allclose(lw.qkv_w, merged, atol=1e-6) and not torch.allclose(lw.qkv_w, base_before, atol=1e-6)
+    s = tr.last_samples[0]
+    P, S = s["prompt_length"], s["sequence_length"]
+    assert torch.allclose(s["logprobs"][P - 1:S - 1], s["rollout_log_probs"][P - 1:S - 1], atol=5e-3)

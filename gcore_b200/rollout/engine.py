@@ -153,7 +153,8 @@ def _count_launches() -> int:
 
 
 class LayerWeights:
-    __slots__ = ("ln1", "qkv_w", "qkv_b", "o_w", "ln2", "fc1_w", "fc2_w", "q_ln", "k_ln", "sinks", "window", "moe")
+    __slots__ = ("ln1", "qkv_w", "qkv_b", "o_w", "ln2", "fc1_w", "fc2_w", "q_ln", "k_ln", "sinks", "window", "moe",
+                 "fp8")  # fp8: {"qkv_w": (e4m3 codes, 128x128 fp32 scales), ...} when the engine serves in block fp8
 
 
 class RolloutWeights:
@@ -174,6 +175,7 @@ class RolloutWeights:
         w.head = f(model.output_weight())
         for layer in model.decoder.layers:
             lw = LayerWeights()
+            lw.fp8 = None
             a = layer.self_attention
             lw.ln1 = f(layer.input_layernorm.weight)
             lw.qkv_w = f(a.linear_qkv.weight)
@@ -301,8 +303,34 @@ class InferEngine:
             self.w = weights
             if not same:
                 self._graphs.clear()
+        if getattr(self, "fp8_enabled", False):
+            self.quantize_weights_fp8()
         if self.device.type == "cuda":
             torch.cuda.current_stream().synchronize()
+
+    # ------------------------------------------------------------------ block-fp8 serving
+    def quantize_weights_fp8(self):
+        """(Re)builds e4m3 + 128x128-scale copies of every dense projection whose contraction length is a multiple of
+        128; called after each weight hand-over when the engine serves in fp8 (the reference's fp8 rollout:
+        gpatch_v4/generation_backend/sglang_model_specific/sglang_weight_update_dsv4.py:267-321)."""
+        from ..ops.quant import quant_weight_128x128
+        self.fp8_enabled = True
+        for lw in self.w.layers:
+            lw.fp8 = {}
+            for name in ("qkv_w", "o_w", "fc1_w", "fc2_w"):
+                w = getattr(lw, name)
+                if w is not None and w.dim() == 2 and w.shape[1] % 128 == 0:
+                    lw.fp8[name] = quant_weight_128x128(w.to(torch.bfloat16).contiguous())
+        self._graphs.clear()
+
+    def _lin(self, h, lw: LayerWeights, name: str, bias=None):
+        if lw.fp8 and name in lw.fp8:
+            from ..ops import quant
+            q, sc = lw.fp8[name]
+            aq, asc = quant.quant_act_1x128(h.to(torch.bfloat16).contiguous())
+            y = quant.gemm_fp8_blockscaled(aq, asc, q, sc, out_dtype=torch.bfloat16).to(h.dtype)
+            return y + bias if bias is not None else y
+        return linear_forward(h, getattr(lw, name), bias)
 
     # ------------------------------------------------------------------ model math (no autograd)
     def _allreduce(self, x):
@@ -324,8 +352,8 @@ class InferEngine:
             if was:
                 lw.moe.train()
             return y
-        g = linear_forward(h, lw.fc1_w)
-        return self._allreduce(linear_forward(fused.swiglu(g), lw.fc2_w))
+        g = self._lin(h, lw, "fc1_w")
+        return self._allreduce(self._lin(fused.swiglu(g), lw, "fc2_w"))
 
     def _embed(self, tokens):
         if self.tp == 1:
@@ -354,14 +382,14 @@ class InferEngine:
         res = None
         for li, lw in enumerate(self.w.layers):
             h, res = fused.rmsnorm(x, lw.ln1, cfg.rms_norm_eps, res)
-            qkv = linear_forward(h, lw.qkv_w, lw.qkv_b)
+            qkv = self._lin(h, lw, "qkv_w", lw.qkv_b)
             qkv = self._qk_norm(lw, qkv, T)
             kv_append_rope(qkv, pos, slots, self.k_cache[li], self.v_cache[li], self.hq, self.hk, self.D,
                            cfg.rope_theta, cfg.rotary_dim)
             v3 = qkv.view(T, self.hq + 2 * self.hk, self.D)
             o = flash_attn_varlen(v3[:, :self.hq], v3[:, self.hq:self.hq + self.hk], v3[:, self.hq + self.hk:], cu, cu,
                                   max_len, max_len, causal=True, window=lw.window, sinks=lw.sinks)
-            a = self._allreduce(linear_forward(o.reshape(T, self.hq * self.D), lw.o_w))
+            a = self._allreduce(self._lin(o.reshape(T, self.hq * self.D), lw, "o_w"))
             h, res = fused.rmsnorm(a, lw.ln2, cfg.rms_norm_eps, res)
             x = self._mlp(lw, h)
         last = (cu[1:] - 1).long()
@@ -394,14 +422,14 @@ class InferEngine:
         res = None
         for li, lw in enumerate(self.w.layers):
             h, res = fused.rmsnorm(x, lw.ln1, cfg.rms_norm_eps, res)
-            qkv = linear_forward(h, lw.qkv_w, lw.qkv_b)
+            qkv = self._lin(h, lw, "qkv_w", lw.qkv_b)
             qkv = self._qk_norm(lw, qkv, B)
             kv_append_rope(qkv, pos, slots, self.k_cache[li], self.v_cache[li], self.hq, self.hk, self.D,
                            cfg.rope_theta, cfg.rotary_dim)
             q = qkv.view(B, self.hq + 2 * self.hk, self.D)[:, :self.hq]
             o = paged_decode(q, self.k_cache[li], self.v_cache[li], st["block_table"], ctx, self.max_model_len,
                              window=lw.window, sinks=lw.sinks)
-            a = self._allreduce(linear_forward(o.view(B, self.hq * self.D), lw.o_w))
+            a = self._allreduce(self._lin(o.view(B, self.hq * self.D), lw, "o_w"))
             h, res = fused.rmsnorm(a, lw.ln2, cfg.rms_norm_eps, res)
             x = self._mlp(lw, h)
         hl, _ = fused.rmsnorm(x, self.w.final_ln, cfg.rms_norm_eps, res)

@@ -80,3 +80,38 @@ def test_sampling_seeds_are_per_request_and_reproducible():
     assert eng.asleep["kv_cache"]
     c = eng.generate(p, SamplingParams(max_new_tokens=5, seed=11), n=4)
     assert [r.out_tokens for r in a] == [r.out_tokens for r in c]
+
+
+def test_block_fp8_serving_tracks_bf16_logprobs():
+    """The engine can hold its dense projections in e4m3 with 128x128 scales and quantise activations 1x128 on the fly;
+    generated log-probs stay close to the full-precision engine's for the same tokens."""
+    import torch
+    from gcore_b200.models.config import ModelConfig
+    from gcore_b200.models.gpt import GPTModel
+    from gcore_b200.rollout.engine import InferEngine, RolloutWeights, SamplingParams
+    mcfg = ModelConfig(num_layers=2, hidden_size=256, num_attention_heads=4, num_kv_heads=2, ffn_hidden_size=768,
+                       vocab_size=512, dtype="float32")
+    model = GPTModel(mcfg, tp_size=1)
+    model.reset_parameters(4)
+    mk = lambda: InferEngine(mcfg, RolloutWeights.from_model(model, clone=True), num_kv_blocks=64, kv_block_size=4,  # noqa: E731
+                             max_model_len=48, use_cuda_graph=False)
+    ref, q8 = mk(), mk()
+    q8.quantize_weights_fp8()
+    assert set(q8.w.layers[0].fp8) == {"qkv_w", "o_w", "fc1_w", "fc2_w"}
+    assert q8.w.layers[0].fp8["fc1_w"][0].dtype == torch.float8_e4m3fn
+    prompts = [[5, 9, 33, 70, 2], [100, 101, 102]]
+    # sampling with the same seeds: the Gumbel noise is identical, so tokens differ only where quantisation moves the
+    # logits by more than the noise gap; log-probs are compared on the common prefix
+    sp = SamplingParams(temperature=1.0, max_new_tokens=8, seed=11)
+    for e in (ref, q8):
+        e.wake_up(("kv_cache",))
+    a = ref.generate(prompts, sp)
+    b = q8.generate(prompts, sp)
+    compared = 0
+    for ra, rb in zip(a, b):
+        for t, (x, y) in enumerate(zip(ra.out_tokens, rb.out_tokens)):
+            if x != y:
+                break
+            assert abs(ra.out_logprobs[t] - rb.out_logprobs[t]) < 0.1
+            compared += 1
+    assert compared >= 8

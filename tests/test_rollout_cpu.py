@@ -115,3 +115,37 @@ def test_block_fp8_serving_tracks_bf16_logprobs():
             assert abs(ra.out_logprobs[t] - rb.out_logprobs[t]) < 0.1
             compared += 1
     assert compared >= 8
+
+
+def test_weight_sync_into_a_separate_rollout_copy_and_verify():
+    """Engine with its own weight copy (not sharing storage): ``sync_weights`` moves the trainer's current weights in
+    bucketed copies and ``verify`` (per-tensor hashes) finds no difference afterwards."""
+    import torch
+    from gcore_b200.configs.config import OptimizerConfig, PolicyConfig, TrainingConfig
+    from gcore_b200.engine.train_engine import TrainingEngine
+    from gcore_b200.models.config import get_preset
+    from gcore_b200.rollout.engine import InferEngine, RolloutWeights
+    from gcore_b200.rollout.weight_sync import plan_buckets, reshard_tensor, sync_weights, verify
+    mcfg = get_preset("tiny_llama", dtype="float32")
+    eng = TrainingEngine(PolicyConfig(recompute="none", without_ref=True), OptimizerConfig(lr=1e-2), TrainingConfig(),
+                         model_cfg=mcfg)
+    eng.setup_model_and_get_optimizer(seed=1, with_ref=False)
+    ie = InferEngine(mcfg, RolloutWeights.from_model(eng.model, clone=True), num_kv_blocks=32, kv_block_size=4,
+                     max_model_len=32, use_cuda_graph=False)
+    assert verify(eng, ie) == []
+    with torch.no_grad():
+        for p in eng.model.parameters():
+            p.add_(0.01)
+    stale = verify(eng, ie)
+    assert len(stale) > 5                                   # the copy is now out of date ...
+    stats = sync_weights(eng, ie, max_bucket_mb=1)
+    assert stats["bytes"] > 0 and verify(eng, ie) == []     # ... and in sync again
+    # bucket planner: sequential buckets below the byte limit
+    b = plan_buckets([("a", 600), ("b", 500), ("c", 300), ("d", 900)], 1000)
+    assert b == [["a"], ["b", "c"], ["d"]]
+    # re-sharding a fused QKV weight from TP=2 to TP=1 restores the [Q | K | V] layout
+    D, hq, hk = mcfg.head_dim, mcfg.num_attention_heads, mcfg.num_kv_heads
+    full = torch.arange((hq + 2 * hk) * D, dtype=torch.float32)[:, None].repeat(1, 4)
+    name = "decoder.layers.0.self_attention.linear_qkv.weight"
+    shards = [reshard_tensor(name, [full], "column", 2, r, mcfg) for r in range(2)]
+    assert torch.equal(reshard_tensor(name, shards, "column", 1, 0, mcfg), full)

@@ -133,12 +133,16 @@ def main():
     ap.add_argument("--samples", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=256)
     ap.add_argument("--max-response", type=int, default=1024)
-    ap.add_argument("--mb-tokens", type=int, default=8192)
+    ap.add_argument("--mb-tokens", type=int, default=None,
+                    help="token budget of a packed micro-batch; default 8192 on one GPU (activations share the GPU with "
+                    "the optimizer state of the whole model), 16384 when tensor parallelism halves the state")
     ap.add_argument("--recompute", default=None, help="full | none; default: full on 1 GPU (optimizer state of the "
                     "whole 7B model shares the GPU with the activations), none when tensor parallelism halves it")
     ap.add_argument("--recompute-layers", type=int, default=None,
                     help="with --recompute full: recompute only the first N layers")
     args = ap.parse_args()
+    if args.mb_tokens is None:
+        args.mb_tokens = 8192 if args.gpus == 1 else 16384
     if args.recompute is None:
         args.recompute = "full" if args.gpus == 1 else "none"
         if args.gpus == 1 and args.recompute_layers is None and args.layers is None and args.model == "qwen2.5-7b":

@@ -241,7 +241,8 @@ def main():
                        "parallelism": f"tp{tp}dp{dp}", "prompts": int(cfg.training.rollout_gbs),
                        "samples_per_prompt": args.samples, "weights": "random-init",
                        "resync": "zero-copy shared parameter storage (trainer and rollout engine, same TP layout)",
-                       "l2": "inputs (15 GB of weights per pass) are larger than L2", "recompute": args.recompute, "recompute_layers": args.recompute_layers},
+                       "l2": "inputs (15 GB of weights per pass) are larger than L2", "recompute": args.recompute, "recompute_layers": args.recompute_layers,
+                       "micro_batch_tokens": args.mb_tokens},
             "clocks": clocks,
             "e2e": {"value": round(tokens / wall, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d / args.steps),
                     "d2h_bytes_per_step": int(d2h / args.steps)},

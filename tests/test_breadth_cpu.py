@@ -318,3 +318,50 @@ def test_dynamic_cp_reroute_round_trip():
     assert res[0][3] == [(0, 2), (0, 4), (2, 2)]
     # the 3900-token sample needs all four ranks, the 2100-token one a block of four too (3 -> 4): everyone sees them
     assert all(r[4] >= 2 for r in res)
+
+
+def test_task_recipes_load_and_small_packages(tmp_path):
+    import glob
+
+    from gcore_b200.configs.base import load_config
+    from gcore_b200.configs.config import RlConfig
+    from gcore_b200.custom import load_custom_module, register_custom_module
+    from gcore_b200.evaluate import EvaluateRunner, pass_at_k
+    from gcore_b200.gdebug import check_rollout_batches, find_risky_settings
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    yamls = sorted(glob.glob(os.path.join(root, "tasks", "math_rl", "yaml", "*.yaml")))
+    assert len(yamls) >= 4
+    for y in yamls:
+        cfg = load_config(RlConfig, y)
+        assert cfg.policy.model_arch
+    cfg = load_config(RlConfig, os.path.join(root, "tasks", "math_rl", "yaml", "grpo_qwen2.5_7b.yaml"),
+                      ["ppo.skip_prev_logps=true", "training.train_gbs=256"])
+    assert any("skip_prev_logps" in r for r in find_risky_settings(cfg))
+    # rule reward of the recipe
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("math_reward_mod", os.path.join(root, "tasks", "math_rl", "reward.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    r = mod.math_reward([{"response_text": "thus \\boxed{ 42 }.", "answer": "42"},
+                         {"response_text": "\\boxed{41}", "answer": "42"}, {"response_text": "no box", "answer": "1"}])
+    assert r.tolist() == [1.0, 0.0, 0.0]
+    # custom module registry
+    p = tmp_path / "my_mod.py"
+    p.write_text("VALUE = 7\n")
+    os.environ.pop("GCORE_CUSTOM_MODULE_REGISTRY_PATH", None)
+    register_custom_module("my_custom_mod", str(p))
+    assert load_custom_module("my_custom_mod").VALUE == 7
+    with pytest.raises(ValueError):
+        register_custom_module("my_custom_mod", str(tmp_path / "other.py"))
+    # evaluation
+    assert pass_at_k(4, 0, 1) == 0.0 and pass_at_k(4, 4, 1) == 1.0 and abs(pass_at_k(4, 1, 2) - 0.5) < 1e-12
+    gen = lambda prompts: [{"tokens": p + [1, 2], "prompt_length": len(p), "ok": (i % 2 == 0)}  # noqa: E731
+                           for p in prompts for i in range(4)]
+    ev = EvaluateRunner(gen, lambda ss: torch.tensor([1.0 if s["ok"] else 0.0 for s in ss]), n=4, ks=(1, 2))
+    m = ev.run([[5, 6], [7]])
+    assert m["eval/reward_mean"] == 0.5 and abs(m["eval/pass@1"] - 0.5) < 1e-9 and m["eval/pass@2"] > 0.8
+    # sample format check
+    good = {"tokens": torch.arange(6), "prompt_length": 2, "mask": torch.tensor([0, 1, 1, 1, 1, 0.0])}
+    check_rollout_batches([good])
+    with pytest.raises(AssertionError):
+        check_rollout_batches([dict(good, mask=torch.tensor([1, 1, 1, 1, 1, 0.0]))])

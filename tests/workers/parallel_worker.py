@@ -1,4 +1,4 @@
-"""gloo worker for the parallelism parity tests: mode = tp | ep | cp | pp."""
+"""gloo worker for the parallelism parity tests: mode = tp | ep | cp | pp | fsdp."""
 import json
 import os
 import sys
@@ -88,6 +88,27 @@ def main():
         lp = e.compute_log_probs(samples(3, 199))
         res = {"losses": losses, "grad_norm": float(e.optimizer.last_grad_norm),
                "logprobs": [x["logprobs"].tolist() for x in lp]}
+    elif mode == "fsdp":
+        from gcore_b200.engine.fsdp2_engine import Fsdp2Engine
+        ps.initialize_model_parallel(tp=1)
+        mcfg = get_preset("tiny_llama", dtype="float32", qkv_bias=True)
+        pc = PolicyConfig(recompute="none", without_ref=True)
+        oc = OptimizerConfig(lr=1e-3, lr_decay_style="constant", weight_decay=0.0, max_grad_norm=1.0)
+        e = Fsdp2Engine(pc, oc, TrainingConfig(train_mbs=2, train_gbs=8), model_cfg=mcfg)
+        e.setup_model_and_get_optimizer(seed=11)
+        losses = []
+        for s in range(4):
+            batch = samples(8, 150 + s)
+            losses.append(e.finetune_step(batch[rank::world])["lm_loss"])
+        local = sum(p.to_local().numel() if hasattr(p, "to_local") else p.numel() for p in e.model.parameters())
+        total = sum(p.numel() for p in e.model.parameters())
+        res = {"losses": losses, "grad_norm": float(e.optimizer.last_grad_norm), "local_frac": local / total}
+        if len(sys.argv) > 3:
+            e.save_checkpoint(sys.argv[3], 4)
+            e2 = Fsdp2Engine(pc, oc, TrainingConfig(train_mbs=2, train_gbs=8), model_cfg=mcfg)
+            e2.setup_model_and_get_optimizer(seed=99)
+            assert e2.load_checkpoint(sys.argv[3]) == 4
+            res["next_loss"] = [x.finetune_step(samples(8, 160)[rank::world])["lm_loss"] for x in (e, e2)]
     if rank == 0:
         json.dump(res, open(out, "w"))
     dist.barrier()

@@ -458,3 +458,33 @@ def test_gemm_intermediate_tile_widths(bn, a_mn, b_mn):
     acc = torch.ones(M, N, dtype=torch.float32, device="cuda")
     gemm(a, b, a_mn=a_mn, b_mn=b_mn, bn=bn, out=acc, accumulate=True)
     _close(acc, ref + 1.0, rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(1024, 768, 512), (1300, 1000, 320), (2048, 512, 4096)])
+def test_gemm_wide_tiles(M, N, K, a_mn, b_mn):
+    from gcore_b200.ops import _lib
+    from gcore_b200.ops import gemm as G
+    torch.manual_seed(20)
+    Np = (N + 7) // 8 * 8
+    a = _rand(K, (M + 7) // 8 * 8)[:, :M] if a_mn else _rand(M, K)
+    b = _rand(K, Np, scale=0.05)[:, :N] if b_mn else _rand(N, K, scale=0.05)
+    bias = _rand(N)
+    ref = (a.float().t() if a_mn else a.float()) @ (b.float() if b_mn else b.float().t())
+    lib = _lib.kernels()
+
+    def run(out, accumulate, bias_t, alpha):
+        rc = lib.gk_gemm_wide(_lib.ptr(a), a.stride(0), a.shape[0], int(a_mn), _lib.ptr(b), b.stride(0), b.shape[0],
+                              int(b_mn), _lib.ptr(out), out.stride(0), int(out.dtype == torch.float32), int(accumulate),
+                              _lib.ptr(bias_t), 0, alpha, M, N, K, _lib.ptr(_lib.err_flag(a.device)), _lib.stream_ptr())
+        assert rc == 0
+        _lib.check_device_errors()
+
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    run(out, False, bias, 1.0)
+    _close(out, ref + bias.float(), rtol=1e-2, atol=1e-2 * max(1.0, K / 512) ** 0.5)
+    acc = torch.full((M, N), 2.0, dtype=torch.float32, device="cuda")
+    run(acc, True, None, 0.5)
+    _close(acc, 0.5 * ref + 2.0, rtol=1e-2, atol=1e-2 * max(1.0, K / 512) ** 0.5)
+    # the dispatcher sends large well-quantised problems here and keeps the rest on the 128-row kernel
+    assert G._use_wide(8192, 37888, 3584) and not G._use_wide(512, 4096, 4096)

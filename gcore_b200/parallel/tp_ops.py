@@ -1,8 +1,8 @@
 """Autograd-aware tensor-parallel / sequence-parallel collectives and the eager vocab-parallel log-prob + entropy.
 
 These are the unfused NCCL (or gloo) twins of the fused kernels: the call sites match where Megatron-Core issues
-them for the reference (column-parallel: all-gather -> GEMM, row-parallel: GEMM -> reduce-scatter; vocab
-parallel CE: gpatch_v4/utils/training_utils.py:1139-1208, gpatch_v4/training_backend/vocab_parallel_entropy.py:12-81).
+them for the reference (column-parallel: all-gather -> GEMM, row-parallel: GEMM -> reduce-scatter, configured in
+gpatch_v4/training_backend/megatron_backend/mixin.py:404-410; vocab parallel CE: gpatch_v4/utils/training_utils.py:1139-1208, gpatch_v4/training_backend/vocab_parallel_entropy.py:12-81).
 """
 from __future__ import annotations
 

@@ -31,6 +31,7 @@ class PackedBatch:
     fields: Dict[str, torch.Tensor] = field(default_factory=dict)  # extra per-token tensors on the log-prob axis
     pad_tokens: int = 0
     cp_ctx: Optional[object] = None  # parallel.cp.CPContext when the token axis is sharded over context-parallel ranks
+    vision: Optional[tuple] = None   # (patches [sum(h*w), patch_dim], [(h, w), ...]) for vision-language batches
 
     @property
     def num_seqs(self):
@@ -41,7 +42,8 @@ class PackedBatch:
         return PackedBatch(self.tokens.to(**kw), self.position_ids.to(**kw), self.cu_seqlens.to(**kw),
                            self.max_seqlen, self.targets.to(**kw), self.loss_mask.to(**kw), self.seq_ids.to(**kw),
                            self.sample_index, {k: v.to(**kw) for k, v in self.fields.items()}, self.pad_tokens,
-                           self.cp_ctx)
+                           self.cp_ctx,
+                           None if self.vision is None else (self.vision[0].to(**kw), self.vision[1]))
 
 
 def response_mask(prompt_len: int, seq_len: int) -> torch.Tensor:
@@ -106,8 +108,13 @@ def pack_samples(samples: Sequence[Dict], indices: Sequence[int], per_token_keys
         out = torch.cat(xs)
         return out.pin_memory() if pin else out
 
+    vision = None
+    imgs = [(samples[i]["pixel_patches"], samples[i]["image_grid"]) for i in indices if "pixel_patches" in samples[i]]
+    if imgs:
+        grids = [tuple(g) for _, gs in imgs for g in (gs if isinstance(gs[0], (list, tuple)) else [gs])]
+        vision = (cat([torch.as_tensor(p, dtype=torch.float32) for p, _ in imgs]), grids)
     return PackedBatch(cat(toks), cat(pos), torch.tensor(cu, dtype=torch.int32), max_len, cat(tgt), cat(mask),
-                       cat(sid), list(indices), {k: cat(v) for k, v in extra.items()}, pad)
+                       cat(sid), list(indices), {k: cat(v) for k, v in extra.items()}, pad, None, vision)
 
 
 # ------------------------------------------------------------------------------------------------ planners

@@ -55,9 +55,11 @@ def backend_scope(backend: str):
 
 class TrainingEngine:
     def __init__(self, policy_cfg, optimizer_cfg, training_cfg, ppo_cfg=None, model_cfg: Optional[ModelConfig] = None,
-                 role: str = "policy", value_head: bool = False, total_steps: Optional[int] = None):
+                 role: str = "policy", value_head: bool = False, total_steps: Optional[int] = None,
+                 vision_cfg=None, image_token_id: Optional[int] = None):
         self.policy_cfg, self.opt_cfg, self.train_cfg, self.ppo_cfg = policy_cfg, optimizer_cfg, training_cfg, ppo_cfg
         self.role = role
+        self.vision_cfg, self.image_token_id = vision_cfg, image_token_id  # set: the model is a vision-language model
         self.value_head = value_head
         self.total_steps = total_steps
         self.backend = training_cfg.training_backend
@@ -91,9 +93,16 @@ class TrainingEngine:
                             layer_range=stage_layer_range(self.model_cfg.num_layers, pp, stage,
                                                           d.num_layers_in_first_pipeline_stage,
                                                           d.num_layers_in_last_pipeline_stage))
-        m = GPTModel(self.model_cfg, tp_size=tp, ep_size=ep, sequence_parallel=d.sequence_parallel,
-                     recompute=recompute if recompute is not None else self.policy_cfg.recompute,
-                     device=self.device, value_head=value_head, **stage_kw)
+        if self.vision_cfg is not None:
+            from ..models.vlm import VLModel
+            assert tp == 1 and pp == 1, "vision-language models run with TP = PP = 1"
+            m = VLModel(self.model_cfg, self.vision_cfg, self.image_token_id, device=self.device,
+                        recompute=recompute if recompute is not None else self.policy_cfg.recompute,
+                        value_head=value_head)
+        else:
+            m = GPTModel(self.model_cfg, tp_size=tp, ep_size=ep, sequence_parallel=d.sequence_parallel,
+                         recompute=recompute if recompute is not None else self.policy_cfg.recompute,
+                         device=self.device, value_head=value_head, **stage_kw)
         m.recompute_num_layers = getattr(self.policy_cfg, "recompute_num_layers", None)
         if seed is not None:
             m.reset_parameters(seed)
@@ -157,7 +166,9 @@ class TrainingEngine:
 
     # ------------------------------------------------------------------ forward helpers
     def _hidden(self, model: GPTModel, mb: PackedBatch):
-        return model(mb.tokens, mb.position_ids, mb.cp_ctx if mb.cp_ctx is not None else mb.cu_seqlens, mb.max_seqlen)
+        kw = {"vision": mb.vision} if (mb.vision is not None and hasattr(model, "vision")) else {}
+        return model(mb.tokens, mb.position_ids, mb.cp_ctx if mb.cp_ctx is not None else mb.cu_seqlens, mb.max_seqlen,
+                     **kw)
 
     def _cp_group(self):
         return ps.get_context_parallel_group() if ps.get_context_parallel_world_size() > 1 else None

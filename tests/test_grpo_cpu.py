@@ -117,3 +117,38 @@ def test_lora_grpo_resyncs_only_the_adapted_projections():
     s = tr.last_samples[0]
     P, S = s["prompt_length"], s["sequence_length"]
     assert torch.allclose(s["logprobs"][P - 1:S - 1], s["rollout_log_probs"][P - 1:S - 1], atol=5e-3)
+
+
+def test_generative_and_bt_reward_models_drive_a_grpo_step():
+    """Generative-reward RL: a second decoder judges every response (votes parsed from its sampled tokens), a
+    Bradley-Terry reward model (value-head engine) scores the same responses, and a rule reward is mixed in."""
+    from gcore_b200.configs.config import OptimizerConfig, PolicyConfig, TrainingConfig
+    from gcore_b200.engine.train_engine import TrainingEngine
+    from gcore_b200.models.gpt import GPTModel
+    from gcore_b200.reward.rewards import BtRmReward, GenRmReward, MixReward, RuleReward
+    from gcore_b200.rollout.engine import InferEngine, RolloutWeights, SamplingParams
+    torch.manual_seed(4)
+    mcfg = get_preset("tiny_llama", dtype="float32")
+    judge_model = GPTModel(mcfg, tp_size=1)
+    judge_model.reset_parameters(21)
+    judge = InferEngine(mcfg, RolloutWeights.from_model(judge_model), num_kv_blocks=256, kv_block_size=4,
+                        max_model_len=64, use_cuda_graph=False)
+    judge.wake_up(("kv_cache",))
+    gen_rm = GenRmReward(judge, build_prompt=lambda s: s["tokens"][-12:].tolist() + [7],
+                         parse=lambda toks: 1.0 if toks[0] % 2 == 0 else -1.0,
+                         sampling=SamplingParams(temperature=1.0, max_new_tokens=2, seed=3), repeat_n=3)
+    rm = TrainingEngine(PolicyConfig(recompute="none", without_ref=True), OptimizerConfig(), TrainingConfig(),
+                        model_cfg=mcfg, value_head=True)
+    rm.setup_model_and_get_optimizer(seed=22, with_ref=False)
+    reward = MixReward([("rule", RuleReward(reward_has_small_token), 1.0), ("gen_rm", gen_rm, 0.5),
+                        ("bt_rm", BtRmReward(rm), 0.25)])
+    tr = GrpoTrainer(make_cfg(), model_cfg=mcfg, reward_fn=reward).setup()
+    g = torch.Generator().manual_seed(9)
+    prompts = [torch.randint(3, 1024, (8,), generator=g).tolist() for _ in range(4)]
+    m = tr.step(prompts)
+    assert m["policy/grad_norm"] > 0
+    s = tr.last_samples[0]
+    assert set(s["reward_dict"]) == {"rule", "gen_rm", "bt_rm"}
+    assert -1.0 <= s["reward_dict"]["gen_rm"] <= 1.0
+    total = s["reward_dict"]["rule"] + 0.5 * s["reward_dict"]["gen_rm"] + 0.25 * s["reward_dict"]["bt_rm"]
+    assert abs(float(s["rewards"]) - total) < 1e-5

@@ -10,7 +10,9 @@
 //   warp 4     TMA producer (Q once, then K_j / V_j into a 2-stage ring)
 //   warp 5     MMA issuer: S_{j+1} is issued before P_j V_j so QK^T overlaps the softmax of the previous tile
 //
-// TMEM columns: S buffers at [0,128) and [128,256), O at [256, 256 + D).
+// TMEM columns (256 allocated per CTA, two CTAs per SM): S buffers at [0,64) and [64,128), O at [128, 128 + D).
+// With one CTA per SM the four softmax warps (one per scheduler) left every pipe under 35 % busy (ncu): the kernel was
+// bound by the latency of each warp's dependent chain, so the tile is 64 keys wide and two CTAs interleave on an SM.
 // P is written as bf16 into a 128-byte-swizzled K-major shared tile and consumed as the A operand of P V.
 #include "ptx.cuh"
 #include "host_utils.h"
@@ -19,7 +21,7 @@
 namespace gk {
 
 constexpr int FA_BM = 128;
-constexpr int FA_BN = 128;
+constexpr int FA_BN = 64;   // keys per tile: 64 keeps a CTA at 112 KB of shared memory, so two CTAs share an SM
 constexpr int FA_THREADS = 192;
 
 struct FaParams {
@@ -37,18 +39,22 @@ struct FaParams {
 };
 
 template <int D>
-__global__ void __launch_bounds__(FA_THREADS, 1)
+__global__ void __launch_bounds__(FA_THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, FaParams p) {
   constexpr int NCH = D / 64;              // 64-element (128-byte) chunks along the head dim
-  constexpr int TILE_BYTES = 128 * D * 2;  // one Q / K / V tile
+  constexpr int TILE_BYTES = 128 * D * 2;      // the Q tile
+  constexpr int KV_BYTES = FA_BN * D * 2;      // one K or V tile
+  constexpr int KV_CHUNK = FA_BN * 128;        // one 64-dim (128-byte) chunk of a K / V tile
   constexpr int P_BYTES = 128 * FA_BN * 2;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // no alignment slack: two CTAs must fit in one SM.  The dynamic segment starts on a 1024-byte boundary when the
+  // kernel has no static shared memory; checked below instead of assumed.
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
   uint8_t* sQ = smem;
-  uint8_t* sK = sQ + TILE_BYTES;      // 2 stages
-  uint8_t* sV = sK + 2 * TILE_BYTES;  // 2 stages
-  uint8_t* sP = sV + 2 * TILE_BYTES;
+  uint8_t* sK = sQ + TILE_BYTES;    // 2 stages
+  uint8_t* sV = sK + 2 * KV_BYTES;  // 2 stages
+  uint8_t* sP = sV + 2 * KV_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
   uint64_t* q_full = bars;         // 1
   uint64_t* k_full = bars + 1;     // 2
@@ -66,6 +72,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int k_beg = p.cu_k[b], lk = p.cu_k[b + 1] - k_beg;
   const int q0 = qt * FA_BM;
   if (q0 >= lq) return;  // uniform across the CTA, before any allocation
+  if (smem_u32(smem_raw) & 1023u) {  // swizzled tiles need 1024-byte alignment
+    if (threadIdx.x == 0) atomicCAS(p.err, 0, ERR_WAIT_MISC);
+    return;
+  }
   const int hk = h / (p.Hq / p.Hk);
   const int off = lk - lq;  // key index of query row i's diagonal is i + off
   const int q_hi = (q0 + FA_BM - 1 < lq - 1) ? q0 + FA_BM - 1 : lq - 1;
@@ -99,14 +109,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     prefetch_tmap(&tmV);
   }
   if (warp == 5) {
-    tmem_alloc(tmem_holder, 512);
+    tmem_alloc(tmem_holder, 256);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
-  const uint32_t tmem_o = tmem_base + 256;
+  const uint32_t tmem_o = tmem_base + 2 * FA_BN;
 
   if (warp == 4) {
     // ------------------------------------------------------------------ TMA producer
@@ -125,12 +135,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!ok) break;
         if (lane == 0) {
           const int krow = k_beg + (j_beg + it) * FA_BN;
-          mbar_expect_tx(&k_full[s], TILE_BYTES);
+          mbar_expect_tx(&k_full[s], KV_BYTES);
 #pragma unroll
-          for (int c = 0; c < NCH; ++c) tma_load_3d(sK + s * TILE_BYTES + c * 16384, &tmK, &k_full[s], c * 64, hk, krow);
-          mbar_expect_tx(&v_full[s], TILE_BYTES);
+          for (int c = 0; c < NCH; ++c) tma_load_3d(sK + s * KV_BYTES + c * KV_CHUNK, &tmK, &k_full[s], c * 64, hk, krow);
+          mbar_expect_tx(&v_full[s], KV_BYTES);
 #pragma unroll
-          for (int c = 0; c < NCH; ++c) tma_load_3d(sV + s * TILE_BYTES + c * 16384, &tmV, &v_full[s], c * 64, hk, krow);
+          for (int c = 0; c < NCH; ++c) tma_load_3d(sV + s * KV_BYTES + c * KV_CHUNK, &tmV, &v_full[s], c * 64, hk, krow);
         }
         __syncwarp();
       }
@@ -147,12 +157,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (it >= 2 && !mbar_wait(&s_empty[s], ((it - 2) >> 1) & 1, p.err, ERR_WAIT_TMEM_EMPTY)) return false;
       tc_fence_after();
       if (lane == 0) {
-        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + s * TILE_BYTES);
+        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + s * KV_BYTES);
 #pragma unroll
         for (int k4 = 0; k4 < D / 16; ++k4) {
-          const uint32_t o = (k4 >> 2) * 16384 + (k4 & 3) * 32;
-          umma_f16(tmem_base + s * FA_BN, make_smem_desc_sw128(qa + o, 16, 1024),
-                   make_smem_desc_sw128(ka + o, 16, 1024), idesc_s, k4 > 0 ? 1u : 0u);
+          const uint32_t oq = (k4 >> 2) * 16384 + (k4 & 3) * 32;     // Q chunks are 128 rows x 128 B apart
+          const uint32_t okk = (k4 >> 2) * KV_CHUNK + (k4 & 3) * 32;  // K chunks FA_BN rows x 128 B
+          umma_f16(tmem_base + s * FA_BN, make_smem_desc_sw128(qa + oq, 16, 1024),
+                   make_smem_desc_sw128(ka + okk, 16, 1024), idesc_s, k4 > 0 ? 1u : 0u);
         }
         umma_commit(&s_full[s]);
       }
@@ -172,11 +183,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (!ok) break;
       tc_fence_after();
       if (lane == 0) {
-        const uint32_t pa = smem_u32(sP), va = smem_u32(sV + s * TILE_BYTES);
+        const uint32_t pa = smem_u32(sP), va = smem_u32(sV + s * KV_BYTES);
 #pragma unroll
         for (int k4 = 0; k4 < FA_BN / 16; ++k4) {
           const uint64_t adesc = make_smem_desc_sw128(pa + (k4 >> 2) * 16384 + (k4 & 3) * 32, 16, 1024);
-          const uint64_t bdesc = make_smem_desc_sw128(va + k4 * 2048, 16384, 1024);
+          const uint64_t bdesc = make_smem_desc_sw128(va + k4 * 2048, KV_CHUNK, 1024);
           umma_f16(tmem_o, adesc, bdesc, idesc_pv, (it > 0 || k4 > 0) ? 1u : 0u);
         }
         umma_commit(&kv_empty[s]);
@@ -214,26 +225,38 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (p.causal && qi + off < hi) hi = qi + off;
       int lo = 0;
       if (p.window > 0) { lo = qi + off - p.window + 1; if (lo < 0) lo = 0; }
+      // row maximum of the raw scores; tiles that lie entirely inside this row's visible range skip the masking
       float mx = -FLT_MAX;
+      if (kbase >= lo && kbase + FA_BN - 1 <= hi) {
 #pragma unroll
-      for (int j = 0; j < FA_BN; ++j) {
-        const int kj = kbase + j;
-        const float v = (kj >= lo && kj <= hi) ? sv[j] * sl2 : -FLT_MAX;
-        sv[j] = v;
-        mx = fmaxf(mx, v);
+        for (int j = 0; j < FA_BN; ++j) mx = fmaxf(mx, sv[j]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < FA_BN; ++j) {
+          const int kj = kbase + j;
+          const float v = (kj >= lo && kj <= hi) ? sv[j] : -FLT_MAX;
+          sv[j] = v;
+          mx = fmaxf(mx, v);
+        }
       }
-      const float m_new = fmaxf(m, mx);
+      mx = mx == -FLT_MAX ? -FLT_MAX : mx * sl2;  // to the log2 domain (sl2 > 0 keeps the ordering)
+      // Lazy rescale: the running reference maximum only moves when the tile's maximum exceeds it by more than 2^8.
+      // Probabilities then reach at most 256 (exact in fp32 accumulation, fine in bf16) and the read-scale-write of
+      // the O accumulator in tensor memory, the most expensive step of the loop, is skipped on almost every tile.
+      const float m_cand = fmaxf(m, mx);
+      const bool grow = (m == -FLT_MAX) ? (m_cand != -FLT_MAX) : (m_cand > m + 8.f);
+      const float m_new = grow ? m_cand : m;
       const float m_use = m_new == -FLT_MAX ? 0.f : m_new;
-      const float corr = exp2f(m - m_use);  // m == -FLT_MAX on the first tile -> 0
+      const float corr = grow ? exp2f(m - m_use) : 1.f;  // m == -FLT_MAX on the first tile -> 0
       float ps = 0.f;
 #pragma unroll
       for (int j = 0; j < FA_BN; ++j) {
-        const float e = sv[j] == -FLT_MAX ? 0.f : exp2f(sv[j] - m_use);
+        const float e = exp2f(fmaf(sv[j], sl2, -m_use));  // masked scores (-FLT_MAX) underflow to exactly 0
         sv[j] = e;
         ps += e;
       }
       l = l * corr + ps;
-      const bool changed = m_new != m;
+      const bool changed = grow;
       m = m_new;
       // previous P V must have retired before P is overwritten and O is rescaled
       if (it > 0) {
@@ -315,18 +338,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   if (warp == 5) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc(tmem_base, 256);
   }
 }
 
 template <int D>
 int launch_fa(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& p, dim3 grid,
               cudaStream_t st) {
-  constexpr int SMEM = 5 * 128 * D * 2 + 128 * FA_BN * 2 + 1024 + 256;
+  constexpr int SMEM = 128 * D * 2 + 4 * FA_BN * D * 2 + 128 * FA_BN * 2 + 256;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return static_cast<int>(e);
+    // the whole L1 / shared array as shared memory, so that two CTAs fit
+    cudaFuncSetAttribute(attn_fwd_kernel<D>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
     configured = true;
   }
   attn_fwd_kernel<D><<<grid, FA_THREADS, SMEM, st>>>(tq, tk, tv, p);
@@ -351,8 +377,8 @@ GK_EXPORT int gk_attn_fwd(const void* q, const void* k, const void* v, void* out
   if (Hq % Hk) return -2;
   CUtensorMap tq, tk, tv;
   if (make_tmap_3d(&tq, q, 2, Tq, Hq, D, sd[0], D, 128, 1, 64, true)) return -3;
-  if (make_tmap_3d(&tk, k, 2, Tk, Hk, D, sd[1], D, 128, 1, 64, true)) return -4;
-  if (make_tmap_3d(&tv, v, 2, Tk, Hk, D, sd[2], D, 128, 1, 64, true)) return -5;
+  if (make_tmap_3d(&tk, k, 2, Tk, Hk, D, sd[1], D, FA_BN, 1, 64, true)) return -4;
+  if (make_tmap_3d(&tv, v, 2, Tk, Hk, D, sd[2], D, FA_BN, 1, 64, true)) return -5;
   FaParams p;
   p.cu_q = cu_q; p.cu_k = cu_k; p.sinks = sinks;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);

@@ -262,7 +262,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         const int qi = q0 + row;
         const bool in = qi < lq;
         const long long idx = static_cast<long long>(h) * p.tq_total + q_beg + qi;
-        s_lse[s * 64 + row] = in ? p.lse[idx] : -FLT_MAX;
+        // log2-domain lse; rows without any visible key (or past the sequence) get +FLT_MAX so that their
+        // probabilities evaluate to exp2(-huge) = 0 without a branch
+        const float l = in ? p.lse[idx] : -FLT_MAX;
+        s_lse[s * 64 + row] = l != -FLT_MAX ? l * LOG2E : FLT_MAX;
         s_delta[s * 64 + row] = in ? p.delta[idx] : 0.f;
         mbar_arrive(&lse_full[s]);
       }
@@ -271,6 +274,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       ok = mbar_wait(&s_full[s], (it >> 1) & 1, p.err, ERR_WAIT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
+      // interior tile for this warp's 32 keys: every (query, key) pair is visible, no mask arithmetic needed
+      const int kmin = k0 + warp * 32, kmax = kmin + 31;
+      const bool interior = kmax < lk && q0 + 63 < lq && (!p.causal || kmax <= q0 + off) &&
+                            (p.window <= 0 || kmin > q0 + 63 + off - p.window);
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t rs[32], rp[32];
@@ -278,14 +285,35 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tmem_ld32(tmem_base + lane_addr + 128 + s * 64 + c * 32, rp);
         tmem_ld_wait();
         float pv[32], dsv[32];
+        const float4* l4 = reinterpret_cast<const float4*>(s_lse + s * 64 + c * 32);
+        const float4* d4 = reinterpret_cast<const float4*>(s_delta + s * 64 + c * 32);
+        if (interior) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int col = c * 32 + j;
-          const float lse = s_lse[s * 64 + col];
-          const bool vis = lse != -FLT_MAX && visible(q0 + col, kj, off, lq, lk, p.causal, p.window);
-          const float pe = vis ? exp2f(__uint_as_float(rs[j]) * sl2 - lse * LOG2E) : 0.f;
-          pv[j] = pe;
-          dsv[j] = pe * (__uint_as_float(rp[j]) - s_delta[s * 64 + col]);
+          for (int j4 = 0; j4 < 8; ++j4) {
+            const float4 l = l4[j4], d = d4[j4];
+            const float lv[4] = {l.x, l.y, l.z, l.w}, dv[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int j = j4 * 4 + u;
+              const float pe = exp2f(fmaf(__uint_as_float(rs[j]), sl2, -lv[u]));
+              pv[j] = pe;
+              dsv[j] = pe * (__uint_as_float(rp[j]) - dv[u]);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j4 = 0; j4 < 8; ++j4) {
+            const float4 l = l4[j4], d = d4[j4];
+            const float lv[4] = {l.x, l.y, l.z, l.w}, dv[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int j = j4 * 4 + u;
+              const bool vis = visible(q0 + c * 32 + j, kj, off, lq, lk, p.causal, p.window);
+              const float pe = vis ? exp2f(fmaf(__uint_as_float(rs[j]), sl2, -lv[u])) : 0.f;
+              pv[j] = pe;
+              dsv[j] = pe * (__uint_as_float(rp[j]) - dv[u]);
+            }
+          }
         }
         store_row_chunk_sw128(sP + s * PS_BYTES, row, c * 32, pv);
         store_row_chunk_sw128(sDS + s * PS_BYTES, row, c * 32, dsv);
@@ -501,7 +529,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const long long idx = static_cast<long long>(h) * p.tq_total + q_beg + qi;
     const float lse = in ? p.lse[idx] : -FLT_MAX;
     const float delta = in ? p.delta[idx] : 0.f;
-    const float lse2 = lse * LOG2E;
+    // rows without any visible key get +FLT_MAX: their probabilities evaluate to exp2(-huge) = 0
+    const float lse2 = lse != -FLT_MAX ? lse * LOG2E : FLT_MAX;
+    const int qmin = q0 + warp * 32, qmax = qmin + 31;
     bool ok = true;
     for (int it = 0; it < ntiles && ok; ++it) {
       const int s = it & 1;
@@ -513,6 +543,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       ok = mbar_wait(&s_full[s], (it >> 1) & 1, p.err, ERR_WAIT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
+      // interior tile for this warp's 32 queries: every pair visible, no mask arithmetic needed
+      const bool interior = qmax < lq && kbase + 63 < lk && (!p.causal || kbase + 63 <= qmin + off) &&
+                            (p.window <= 0 || kbase > qmax + off - p.window);
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t rs[32], rp[32];
@@ -520,12 +553,20 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tmem_ld32(tmem_base + lane_addr + 128 + s * 64 + c * 32, rp);
         tmem_ld_wait();
         float dsv[32];
+        if (interior) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int kj = kbase + c * 32 + j;
-          const bool vis = lse != -FLT_MAX && visible(qi, kj, off, lq, lk, p.causal, p.window);
-          const float pe = vis ? exp2f(__uint_as_float(rs[j]) * sl2 - lse2) : 0.f;
-          dsv[j] = pe * (__uint_as_float(rp[j]) - delta);
+          for (int j = 0; j < 32; ++j) {
+            const float pe = exp2f(fmaf(__uint_as_float(rs[j]), sl2, -lse2));
+            dsv[j] = pe * (__uint_as_float(rp[j]) - delta);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int kj = kbase + c * 32 + j;
+            const bool vis = visible(qi, kj, off, lq, lk, p.causal, p.window);
+            const float pe = vis ? exp2f(fmaf(__uint_as_float(rs[j]), sl2, -lse2)) : 0.f;
+            dsv[j] = pe * (__uint_as_float(rp[j]) - delta);
+          }
         }
         store_row_chunk_sw128(sDS + s * DS_BYTES, row, c * 32, dsv);
       }

@@ -545,6 +545,12 @@ class InferEngine:
         host_seed = torch.zeros(B, dtype=torch.int64)
         host_step = torch.zeros(B, dtype=torch.int32)
         host_bt = torch.zeros(B, self.max_blocks, dtype=torch.int32)
+        if dev.type == "cuda":
+            host_tok, host_pos, host_active, host_seed, host_step, host_bt = (
+                t.pin_memory() for t in (host_tok, host_pos, host_active, host_seed, host_step, host_bt))
+        # numpy views: scalar writes through a tensor cost microseconds each, and there are hundreds per interval
+        n_tok, n_pos, n_active, n_seed, n_step = (t.numpy() for t in (host_tok, host_pos, host_active, host_seed,
+                                                                      host_step))
 
         def place(r: Request, first_tok: int, first_lp: float):
             """Request enters the decode batch after its first token is known."""
@@ -557,11 +563,11 @@ class InferEngine:
             s = slots_free.pop()
             r.slot = s
             slot_req[s] = r
-            host_tok[s] = first_tok
-            host_pos[s] = len(r.prompt)
-            host_active[s] = True
-            host_seed[s] = r.seed
-            host_step[s] = 1
+            n_tok[s] = first_tok
+            n_pos[s] = len(r.prompt)
+            n_active[s] = True
+            n_seed[s] = r.seed
+            n_step[s] = 1
 
         while True:
             # ---- admit: a prompt enters only when its whole sample group fits the batch
@@ -648,15 +654,18 @@ class InferEngine:
             ring_tok = st["ring_tok"].cpu()
             ring_lp = st["ring_lp"].cpu()
             io_counters.add_d2h(io_counters.tensor_bytes(ring_tok, ring_lp))
-            # ---- harvest
+            # ---- harvest (plain lists: per-element tensor indexing would keep the GPU idle for milliseconds)
+            tok_cols = ring_tok.t().tolist()
+            lp_cols = ring_lp.t().tolist()
             for s in live:
                 r = slot_req[s]
                 done = False
                 took = 0
+                col_t, col_l = tok_cols[s], lp_cols[s]
                 for k in range(interval):
-                    t = int(ring_tok[k, s])
+                    t = col_t[k]
                     r.out_tokens.append(t)
-                    r.out_logprobs.append(float(ring_lp[k, s]))
+                    r.out_logprobs.append(col_l[k])
                     took += 1
                     if t in stop_ids:
                         done, r.finish_reason = True, "stop"
@@ -670,13 +679,13 @@ class InferEngine:
                     self.sched.finish(r.rid)
                     del slot_req[s]
                     slots_free.append(s)
-                    host_active[s] = False
-                    host_pos[s] = 0
+                    n_active[s] = False
+                    n_pos[s] = 0
                 else:
                     self.sched.advance(r.rid, interval)
-                    host_tok[s] = r.out_tokens[-1]
-                    host_pos[s] += interval
-                    host_step[s] += interval
+                    n_tok[s] = r.out_tokens[-1]
+                    n_pos[s] += interval
+                    n_step[s] += interval
         for r in reqs:
             self.requests.pop(r.rid, None)
         return reqs

@@ -16,6 +16,7 @@ import json
 import os
 import pickle
 import random
+import re
 import shutil
 import threading
 from typing import Dict, List, Optional, Tuple
@@ -109,6 +110,18 @@ def set_rng_state(st: dict):
         torch.cuda.set_rng_state(st["cuda"])
 
 
+_LOCAL_LAYER = re.compile(r"decoder\.layers\.(\d+)\.")
+
+
+def _canonical(model, name: str) -> str:
+    """Parameter name in the unpartitioned model: a pipeline stage numbers its layers from zero, the checkpoint uses
+    the global layer index (the stacked-layer axis spans all stages), so any pipeline layout can load any other's."""
+    off = getattr(model, "layer_offset", 0)
+    if not off:
+        return name
+    return _LOCAL_LAYER.sub(lambda m: f"decoder.layers.{int(m.group(1)) + off}.", name, count=1)
+
+
 def _model_chunks(engine) -> List[Chunk]:
     st = ps.get_state()
     model = engine.model
@@ -122,7 +135,8 @@ def _model_chunks(engine) -> List[Chunk]:
         owner_dp = edp_rank if mode == "expert" else dp_rank
         if owner_dp != 0:
             continue
-        for c in param_chunks(name, p.detach(), model.cfg, tp_rank if tp > 1 else 0, tp, ep_rank, ep, mode):
+        for c in param_chunks(_canonical(model, name), p.detach(), model.cfg, tp_rank if tp > 1 else 0, tp, ep_rank, ep,
+                              mode):
             if c.replicated and tp_rank != 0:
                 continue
             c.key = "model." + c.key
@@ -137,7 +151,7 @@ def _optimizer_chunks(engine) -> List[Chunk]:
     model = engine.model
     tp_rank, tp = ps.get_tensor_model_parallel_rank(), model.tp_size
     ep_rank, ep = ps.get_expert_model_parallel_rank(), model.ep_size
-    names = {id(p): n for n, p in model.named_parameters()}
+    names = {id(p): _canonical(model, n) for n, p in model.named_parameters()}
     out = []
     for bi, sh in enumerate(opt.shards):
         buf, bucket = sh["buf"], sh["bucket"]
@@ -200,7 +214,8 @@ def save_checkpoint(engine, root: str, step: int, extra_state: Optional[dict] = 
         common = {"iteration": step, "checkpoint_version": 3.0,
                   "optimizer_step": engine.optimizer.step_count if engine.optimizer is not None else 0,
                   "engine_step": engine.step, "model_config": engine.model_cfg.to_dict(),
-                  "topology": dict(tp=engine.model.tp_size, ep=engine.model.ep_size, world=world),
+                  "topology": dict(tp=engine.model.tp_size, ep=engine.model.ep_size,
+                                   pp=ps.get_pipeline_model_parallel_world_size(), world=world),
                   "extra_state": extra_state or {}}
         torch.save(common, os.path.join(path, "common.pt"))
         with open(os.path.join(path, "metadata.json"), "w") as f:
@@ -309,6 +324,7 @@ def load_checkpoint(engine, root: str, step: Optional[int] = None, load_optim: b
 
     missing = []
     for name, p in model.named_parameters():
+        name = _canonical(model, name)
         mode = getattr(p, "tp_mode", "none")
         probe = param_chunks(name, p.detach(), model.cfg, tp_rank if tp > 1 else 0, tp, ep_rank, ep, mode)
         if any(("model." + c.key) not in have for c in probe):
@@ -323,7 +339,7 @@ def load_checkpoint(engine, root: str, step: Optional[int] = None, load_optim: b
     if opt is not None:
         has_opt = any(k.startswith("optimizer.state.") for k in have)
         if load_optim and has_opt:
-            names = {id(p): n for n, p in model.named_parameters()}
+            names = {id(p): _canonical(model, n) for n, p in model.named_parameters()}
             for sh in opt.shards:
                 buf, bucket = sh["buf"], sh["bucket"]
                 s, e = sh["s"], sh["e"]

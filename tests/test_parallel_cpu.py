@@ -127,7 +127,7 @@ def test_pp2_1f1b_matches_single_process(tmp_path):
     import parallel_worker as pw
     from gcore_b200.models.config import get_preset
     out = tmp_path / "pp.json"
-    _spawn("pp", out, port="29547")
+    _spawn("pp", out, [str(tmp_path)], port="29547")
     got = json.load(open(out))
     mcfg = get_preset("tiny_llama", dtype="float32", qkv_bias=True, num_layers=4)
     e = pw.engine(mcfg, 1)
@@ -138,6 +138,21 @@ def test_pp2_1f1b_matches_single_process(tmp_path):
     lp = e.compute_log_probs(pw.samples(3, 199))
     for a, b in zip(lp, got["logprobs"]):
         assert torch.allclose(a["logprobs"], torch.tensor(b), atol=2e-4)
+    # the two-stage checkpoint resumes on two stages ...
+    assert abs(got["next_loss"][0] - got["next_loss"][1]) < 1e-5, got["next_loss"]
+    # ... and loads into the unpartitioned model: layers are stored under their global index
+    from gcore_b200.checkpoint.torch_dist import CheckpointReader, load_checkpoint
+    rd = CheckpointReader(str(tmp_path / "ckpt" / "iter_0000004"))
+    assert tuple(rd.full_tensor("model.decoder.layers.mlp.linear_fc2.weight").shape)[0] == 4
+    e2 = pw.engine(mcfg, 1)
+    e2.setup_model_and_get_optimizer(seed=5)
+    assert load_checkpoint(e2, str(tmp_path / "ckpt")) == 4
+    for (n, p), (_, q) in zip(e.model.named_parameters(), e2.model.named_parameters()):
+        assert torch.allclose(p, q, atol=2e-4), n
+    for a, b in zip(e.optimizer.shards, e2.optimizer.shards):
+        assert torch.allclose(a["m"], b["m"], atol=1e-5) and torch.allclose(a["v"], b["v"], atol=1e-6)
+    nxt = [x.finetune_step(pw.samples(8, 140))["lm_loss"] for x in (e, e2)]
+    assert abs(nxt[0] - nxt[1]) < 5e-4 and abs(nxt[0] - got["next_loss"][0]) < 5e-4
 
 
 def test_stage_layer_ranges():

@@ -88,6 +88,14 @@ def main():
         lp = e.compute_log_probs(samples(3, 199))
         res = {"losses": losses, "grad_norm": float(e.optimizer.last_grad_norm),
                "logprobs": [x["logprobs"].tolist() for x in lp]}
+        if len(sys.argv) > 3:
+            from gcore_b200.checkpoint.torch_dist import load_checkpoint, save_checkpoint
+            save_checkpoint(e, os.path.join(sys.argv[3], "ckpt"), 4)
+            # a fresh two-stage engine (other seed) resumes from it and takes the same next step
+            e2 = engine(mcfg, 1)
+            e2.setup_model_and_get_optimizer(seed=77)
+            assert load_checkpoint(e2, os.path.join(sys.argv[3], "ckpt")) == 4
+            res["next_loss"] = [x.finetune_step(samples(8, 140))["lm_loss"] for x in (e, e2)]
     elif mode == "fsdp":
         from gcore_b200.engine.fsdp2_engine import Fsdp2Engine
         ps.initialize_model_parallel(tp=1)

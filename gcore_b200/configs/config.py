@@ -324,6 +324,9 @@ class PolicyConfig(MappingMixin):
     manual_clear_memory: bool = False
     export_weights_buffer_max_size_mb: int = 2048
     share_rollout_weights: bool = True  # colocated trainer and decoder read the same bf16 parameter storage
+    # vision-language policy: fields of ``models.vlm.VisionConfig`` (empty = text-only) and the placeholder token id
+    vision_config: Dict[str, Any] = field(default_factory=dict)
+    image_token_id: Optional[int] = None
     sampler_client: ClientConfig = field(default_factory=ClientConfig)
     bt_rm_client: ClientConfig = field(default_factory=ClientConfig)
     gen_rm_client: ClientConfig = field(default_factory=ClientConfig)

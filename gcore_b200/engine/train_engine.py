@@ -59,6 +59,10 @@ class TrainingEngine:
                  vision_cfg=None, image_token_id: Optional[int] = None):
         self.policy_cfg, self.opt_cfg, self.train_cfg, self.ppo_cfg = policy_cfg, optimizer_cfg, training_cfg, ppo_cfg
         self.role = role
+        if vision_cfg is None and getattr(policy_cfg, "vision_config", None):
+            from ..models.vlm import VisionConfig
+            vision_cfg = VisionConfig(**dict(policy_cfg.vision_config))
+            image_token_id = policy_cfg.image_token_id if image_token_id is None else image_token_id
         self.vision_cfg, self.image_token_id = vision_cfg, image_token_id  # set: the model is a vision-language model
         self.value_head = value_head
         self.total_steps = total_steps

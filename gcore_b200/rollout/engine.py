@@ -63,6 +63,7 @@ class Request:
     parent: Optional[int] = None
     slot: int = -1
     routed_experts: Optional[list] = None
+    prompt_index: int = 0
 
 
 class _Sched:
@@ -170,6 +171,7 @@ class RolloutWeights:
     def from_model(cls, model, clone: bool = False):
         f = (lambda t: t.detach().clone()) if clone else (lambda t: t.detach())
         w = cls()
+        model = getattr(model, "language_model", model)  # vision-language wrapper: the decoder is what serves
         w.embed = f(model.embedding.word_embeddings.weight)
         w.final_ln = f(model.decoder.final_layernorm.weight)
         w.head = f(model.output_weight())
@@ -374,11 +376,14 @@ class InferEngine:
         return qkv
 
     @torch.no_grad()
-    def _prefill(self, tokens, pos, cu, max_len, slots):
-        """Packed prompts through all layers; K/V go to the cache; returns the last-token hidden of every prompt."""
+    def _prefill(self, tokens, pos, cu, max_len, slots, embed_rows=None):
+        """Packed prompts through all layers; K/V go to the cache; returns the last-token hidden of every prompt.
+        ``embed_rows = (row_index, rows)`` overwrites embedding rows (image features at placeholder tokens)."""
         cfg = self.cfg
         T = tokens.numel()
         x = self._embed(tokens)
+        if embed_rows is not None:
+            x = x.index_copy(0, embed_rows[0], embed_rows[1].to(x.dtype))
         res = None
         for li, lw in enumerate(self.w.layers):
             h, res = fused.rmsnorm(x, lw.ln1, cfg.rms_norm_eps, res)
@@ -502,10 +507,13 @@ class InferEngine:
     # ------------------------------------------------------------------ public generate
     @torch.no_grad()
     def generate(self, prompts: Sequence[Sequence[int]], params: SamplingParams, n: int = 1,
-                 seeds: Optional[Sequence[int]] = None) -> List[Request]:
+                 seeds: Optional[Sequence[int]] = None, image_embeds: Optional[Sequence] = None,
+                 image_token_id: Optional[int] = None) -> List[Request]:
         """Generates ``n`` samples for every prompt; returns requests ordered ``[p0s0, p0s1, ..., p1s0, ...]``.
         Request ``(i, j)`` uses seed ``params.seed + i * n + j`` unless ``seeds`` is given
-        (gpatch_v4/extended_model/llm.py:57-68)."""
+        (gpatch_v4/extended_model/llm.py:57-68).  Vision-language prompts: ``image_embeds[i]`` holds one row of
+        merged vision features per ``image_token_id`` placeholder of prompt ``i`` (or None); the rows replace the
+        placeholder embeddings in the prefill, decoding is unchanged."""
         if self.asleep["kv_cache"]:
             self.wake_up(("kv_cache",))
         dev = self.device
@@ -518,6 +526,7 @@ class InferEngine:
                 self._next_rid += 1
                 sd = seeds[i * n + j] if seeds is not None else params.seed + i * n + j
                 r = Request(rid, list(p), params, sd)
+                r.prompt_index = i
                 r.parent = reqs[i * n].rid if j > 0 else None
                 reqs.append(r)
                 self.requests[rid] = r
@@ -586,8 +595,25 @@ class InferEngine:
                 if dev.type == "cuda":
                     toks, pos, cu, slots = toks.pin_memory(), pos.pin_memory(), cu.pin_memory(), slots.pin_memory()
                 io_counters.add_h2d(io_counters.tensor_bytes(toks, pos, cu, slots))
+                embed_rows = None
+                if image_embeds is not None:
+                    rows_idx, feats, base = [], [], 0
+                    for r, l in zip(pre, lens):
+                        fe = image_embeds[r.prompt_index]
+                        if fe is not None:
+                            where = [base + k for k, t in enumerate(r.prompt) if t == image_token_id]
+                            if len(where) != fe.shape[0]:
+                                raise ValueError(f"prompt {r.prompt_index}: {len(where)} image placeholder tokens for "
+                                                 f"{fe.shape[0]} vision feature rows")
+                            rows_idx += where
+                            feats.append(fe)
+                        base += l
+                    if rows_idx:
+                        embed_rows = (torch.tensor(rows_idx, dtype=torch.int64, device=dev),
+                                      torch.cat(feats).to(dev))
                 hl = self._prefill(toks.to(dev, non_blocking=True), pos.to(dev, non_blocking=True),
-                                   cu.to(dev, non_blocking=True), max(lens), slots.to(dev, non_blocking=True))
+                                   cu.to(dev, non_blocking=True), max(lens), slots.to(dev, non_blocking=True),
+                                   embed_rows)
                 self.stats["prefill_tokens"] += int(toks.numel())
                 for r in pre:
                     self.sched.commit(r.rid, True)

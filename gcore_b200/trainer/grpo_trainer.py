@@ -38,14 +38,15 @@ def synthetic_reward(samples: Sequence[dict], **_) -> torch.Tensor:
 
 class GrpoTrainer:
     def __init__(self, config: RlConfig, model_cfg=None, reward_fn: Optional[Callable] = None,
-                 prompt_source: Optional[Callable] = None):
+                 prompt_source: Optional[Callable] = None, vision_cfg=None, image_token_id: Optional[int] = None):
         self.cfg = config
         self.timers = Timers()
         self.reward_fn = reward_fn or self._load_reward_fn() or synthetic_reward
         self.prompt_source = prompt_source
         t = config.training
         self.policy = TrainingEngine(config.policy, config.optimizer, t, config.ppo, model_cfg=model_cfg,
-                                     total_steps=t.total_ppo_step)
+                                     total_steps=t.total_ppo_step, vision_cfg=vision_cfg,
+                                     image_token_id=image_token_id)
         self.critic: Optional[TrainingEngine] = None
         self.engine: Optional[InferEngine] = None
         self.ppo_step = 0
@@ -98,11 +99,30 @@ class GrpoTrainer:
         return self
 
     # ------------------------------------------------------------------ phases
-    def rollout(self, prompts: Sequence[Sequence[int]]) -> List[dict]:
+    def rollout(self, prompts: Sequence) -> List[dict]:
+        """``prompts``: token-id lists, or for a vision-language policy dicts with ``tokens``, ``pixel_patches`` and
+        ``image_grid`` (the vision tower runs here, once per prompt; the engine only sees feature rows)."""
         t = self.cfg.training
         self.engine.wake_up(("kv_cache",))
         sp = SamplingParams(**{**self.sampling.__dict__, "seed": self.sampling.seed + self.ppo_step * 1000003})
-        reqs = self.engine.generate(prompts, sp, n=t.sampling_repeat_n)
+        images = [p if isinstance(p, dict) and "pixel_patches" in p else None for p in prompts]
+        prompts = [list(p["tokens"]) if isinstance(p, dict) else p for p in prompts]
+        vl_kw = {}
+        if any(im is not None for im in images):
+            model = self.policy.model
+            assert hasattr(model, "vision"), "image prompts need a vision-language policy"
+            embeds = []
+            with torch.no_grad():
+                for im in images:
+                    if im is None:
+                        embeds.append(None)
+                        continue
+                    g = im["image_grid"]
+                    grids = [tuple(x) for x in (g if isinstance(g[0], (list, tuple)) else [g])]
+                    patches = torch.as_tensor(im["pixel_patches"], dtype=torch.float32).to(self.policy.device)
+                    embeds.append(model.vision(patches.to(next(model.vision.parameters()).dtype), grids))
+            vl_kw = dict(image_embeds=embeds, image_token_id=model.image_token_id)
+        reqs = self.engine.generate(prompts, sp, n=t.sampling_repeat_n, **vl_kw)
         self.engine.sleep(("kv_cache",))
         samples = []
         dp_rank = ps.get_data_parallel_rank()
@@ -114,6 +134,9 @@ class GrpoTrainer:
             samples.append(dict(tokens=toks, prompt_length=P, sequence_length=S, rollout_log_probs=lp,
                                 group_id=k // t.sampling_repeat_n, unique_id=(self.ppo_step, dp_rank, k),
                                 mask=response_mask(P, S), finish_reason=r.finish_reason))
+            im = images[k // t.sampling_repeat_n]
+            if im is not None:  # the training passes re-run the vision tower on the same pixels
+                samples[-1]["pixel_patches"], samples[-1]["image_grid"] = im["pixel_patches"], im["image_grid"]
         return samples
 
     def score(self, samples: List[dict]) -> List[dict]:

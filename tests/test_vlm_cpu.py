@@ -85,3 +85,47 @@ def test_vlm_sft_through_the_training_engine():
     losses = [eng.finetune_step(samples(200 + s % 4))["lm_loss"] for s in range(30)]
     assert sum(losses[-4:]) / 4 < 0.6 * sum(losses[:4]) / 4, losses
     assert any(n.startswith("vision.") for n, _ in eng.model.named_parameters())
+
+
+def test_vlm_grpo_step_rolls_out_with_images():
+    """GRPO with image prompts: the rollout engine's prefill takes the vision tower's rows at the placeholder tokens
+    (its log-probs agree with the trainer's, which re-runs the tower), and the update reaches the vision tower."""
+    from test_grpo_cpu import make_cfg, reward_has_small_token
+    from gcore_b200.trainer.grpo_trainer import GrpoTrainer
+    torch.manual_seed(0)
+    vc = VisionConfig(patch_size=2, hidden_size=64, num_layers=2, num_heads=2, ffn_hidden_size=128, max_grid=8)
+    tr = GrpoTrainer(make_cfg(), model_cfg=get_preset("tiny_llama", dtype="float32"), reward_fn=reward_has_small_token,
+                     vision_cfg=vc, image_token_id=5).setup()
+    g = torch.Generator().manual_seed(3)
+    prompts = []
+    for i in range(4):
+        h, w = (4, 4) if i % 2 == 0 else (2, 6)
+        n_vis = h * w // 4
+        prompts.append({"tokens": [3] + [5] * n_vis + [4, 30 + i],
+                        "pixel_patches": torch.randn(h * w, vc.patch_dim, generator=g), "image_grid": (h, w)})
+    prompts[3] = [3, 40, 41, 42]  # a text-only prompt in the same batch
+    before = tr.policy.model.vision.patch_embed.weight.detach().clone()
+    m = tr.step(prompts)
+    assert m["policy/grad_norm"] > 0
+    assert not torch.equal(before, tr.policy.model.vision.patch_embed.weight)
+    s = tr.last_samples[0]
+    assert "pixel_patches" in s and "pixel_patches" not in tr.last_samples[-1]
+    P, S = s["prompt_length"], s["sequence_length"]
+    assert torch.allclose(s["logprobs"][P - 1:S - 1], s["rollout_log_probs"][P - 1:S - 1], atol=2e-3)
+    # the images matter: the same tokens without the pixels give other log-probs
+    blind = [dict(tokens=s["tokens"], prompt_length=P, sequence_length=S, mask=s["mask"])]
+    tr.policy.compute_log_probs(blind, use_ref=False)
+    assert not torch.allclose(blind[0]["logprobs"][P - 1:S - 1], s["logprobs"][P - 1:S - 1], atol=1e-3)
+
+
+def test_vision_policy_from_config():
+    from gcore_b200.configs.base import from_dict
+    from gcore_b200.configs.config import OptimizerConfig, PolicyConfig, TrainingConfig
+    from gcore_b200.engine.train_engine import TrainingEngine
+    pc = from_dict(PolicyConfig, {"recompute": "none", "without_ref": True, "image_token_id": 5,
+                                  "vision_config": {"patch_size": 2, "hidden_size": 64, "num_layers": 1, "num_heads": 2,
+                                                    "ffn_hidden_size": 128, "max_grid": 8}})
+    e = TrainingEngine(pc, OptimizerConfig(lr=1e-3), TrainingConfig(train_mbs=2, train_gbs=2),
+                       model_cfg=get_preset("tiny_llama", dtype="float32"))
+    e.setup_model_and_get_optimizer(seed=1)
+    assert isinstance(e.model, VLModel) and e.model.image_token_id == 5 and e.model.vc.num_layers == 1

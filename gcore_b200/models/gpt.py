@@ -196,10 +196,12 @@ class MLAttention(nn.Module):
         self.linear_proj = ParallelLinear(cfg.num_attention_heads * dv, H, "row", cfg, tp_size=tp_size,
                                           init_std=cfg.init_std / math.sqrt(2 * cfg.num_layers), device=device)
 
-    def forward(self, x, pos, cu_seqlens, max_seqlen):
+    def project(self, x, pos):
+        """Per-token projections: ``q_nope [T, h, dn]``, rotated ``q_rope [T, h, dr]``, the normalised latent
+        ``c_kv [T, kv_lora]`` and the rotated shared key ``k_rope [T, dr]`` (the last two are what a decoder caches)."""
         cfg = self.cfg
         T, h = x.shape[0], self.h
-        dn, dr, dv = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim
+        dn, dr = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim
         if cfg.q_lora_rank:
             ql = fused.rmsnorm(self.linear_q_down_proj(x), self.q_layernorm.weight, cfg.rms_norm_eps)[0]
             q = self.linear_q_up_proj(ql).view(T, h, dn + dr)
@@ -208,18 +210,28 @@ class MLAttention(nn.Module):
         kv = self.linear_kv_down_proj(x)
         c_kv, k_rope = kv.split([cfg.kv_lora_rank, dr], dim=-1)
         c_kv = fused.rmsnorm(c_kv.contiguous(), self.kv_layernorm.weight, cfg.rms_norm_eps)[0]
-        kvu = self.linear_kv_up_proj(c_kv).view(T, h, dn + dv)
-        k_nope, v = kvu.split([dn, dv], dim=-1)
         q_nope, q_rope = q.split([dn, dr], dim=-1)
         q_rope = fused.rope(q_rope.contiguous(), pos, cfg.rope_theta, dr, cfg.rope_interleaved)
         k_rope = fused.rope(k_rope.reshape(T, 1, dr).contiguous(), pos, cfg.rope_theta, dr, cfg.rope_interleaved)
+        return q_nope, q_rope, c_kv, k_rope.reshape(T, dr)
+
+    def attend(self, q_nope, q_rope, c_kv, k_rope, cu_seqlens):
+        """Causal attention over packed sequences with the latent expanded to per-head keys and values."""
+        cfg = self.cfg
+        T, h = q_nope.shape[0], self.h
+        dn, dr, dv = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim
+        kvu = self.linear_kv_up_proj(c_kv).view(T, h, dn + dv)
+        k_nope, v = kvu.split([dn, dv], dim=-1)
         qf = torch.cat([q_nope, q_rope], -1)
-        kf = torch.cat([k_nope, k_rope.expand(T, h, dr)], -1)
+        kf = torch.cat([k_nope, k_rope.reshape(T, 1, dr).expand(T, h, dr)], -1)
         # pad v to the qk head dim so one attention call serves both (extra columns are zero and sliced away)
         vpad = torch.nn.functional.pad(v, (0, dn + dr - dv))
         from ..ops.attention import attn_varlen_ref
         o = attn_varlen_ref(qf, kf, vpad, cu_seqlens, cu_seqlens, True, 0, None, 1.0 / math.sqrt(dn + dr))
-        return self.linear_proj(o[..., :dv].reshape(T, h * dv))
+        return o[..., :dv].reshape(T, h * dv)
+
+    def forward(self, x, pos, cu_seqlens, max_seqlen):
+        return self.linear_proj(self.attend(*self.project(x, pos), cu_seqlens))
 
 
 class MLP(nn.Module):

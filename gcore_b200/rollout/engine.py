@@ -155,7 +155,7 @@ def _count_launches() -> int:
 
 class LayerWeights:
     __slots__ = ("ln1", "qkv_w", "qkv_b", "o_w", "ln2", "fc1_w", "fc2_w", "q_ln", "k_ln", "sinks", "window", "moe",
-                 "fp8")  # fp8: {"qkv_w": (e4m3 codes, 128x128 fp32 scales), ...} when the engine serves in block fp8
+                 "mla", "fp8")  # fp8: {"qkv_w": (e4m3 codes, 128x128 fp32 scales), ...} when the engine serves in block fp8
 
 
 class RolloutWeights:
@@ -180,6 +180,24 @@ class RolloutWeights:
             lw.fp8 = None
             a = layer.self_attention
             lw.ln1 = f(layer.input_layernorm.weight)
+            lw.mla = None
+            if hasattr(a, "linear_kv_down_proj"):
+                # multi-head latent attention: the module itself serves (its projections carry LoRA adapters and
+                # fp8 wrappers as they are); the cache holds the latent and the shared rotated key
+                import copy
+                lw.mla = copy.deepcopy(a) if clone else a
+                lw.qkv_w = lw.qkv_b = lw.o_w = lw.q_ln = lw.k_ln = lw.sinks = None
+                lw.window = 0
+                lw.ln2 = f(layer.pre_mlp_layernorm.weight)
+                if layer.is_moe:
+                    lw.moe = layer.mlp
+                    lw.fc1_w = lw.fc2_w = None
+                else:
+                    lw.moe = None
+                    lw.fc1_w = f(layer.mlp.linear_fc1.weight)
+                    lw.fc2_w = f(layer.mlp.linear_fc2.weight)
+                w.layers.append(lw)
+                continue
             lw.qkv_w = f(a.linear_qkv.weight)
             lw.qkv_b = f(a.linear_qkv.bias) if a.linear_qkv.bias is not None else None
             lw.o_w = f(a.linear_proj.weight)
@@ -224,6 +242,7 @@ class InferEngine:
         self.hq = cfg.num_attention_heads // tp_size
         self.hk = cfg.num_kv_heads // tp_size
         self.D = cfg.head_dim
+        self.mla_dim = (cfg.kv_lora_rank + cfg.qk_rope_head_dim) if getattr(cfg, "use_mla", False) else 0
         self.vocab_local = weights.head.shape[0]
         self.vocab_start = self.vocab_local * (dist.get_rank(tp_group) if (tp_group is not None and tp_size > 1) else 0)
         self.use_graph = use_cuda_graph and self.device.type == "cuda" and not _lib.force_eager()
@@ -247,6 +266,8 @@ class InferEngine:
 
     # ------------------------------------------------------------------ memory
     def _kv_bytes_per_block(self):
+        if self.mla_dim:
+            return len(self.w.layers) * self.bs * self.mla_dim * 2
         return 2 * len(self.w.layers) * self.bs * self.hk * self.D * 2
 
     def wake_up(self, tags: Sequence[str] = ("weights", "kv_cache")):
@@ -263,10 +284,17 @@ class InferEngine:
                     n = need
             self.num_blocks = n
             dt = self.w.embed.dtype
-            self.k_cache = [torch.zeros(n, self.bs, self.hk, self.D, dtype=dt, device=self.device)
-                            for _ in self.w.layers]
-            self.v_cache = [torch.zeros(n, self.bs, self.hk, self.D, dtype=dt, device=self.device)
-                            for _ in self.w.layers]
+            if self.mla_dim:
+                # latent cache: one row of (kv_lora + rope) values per token, shared by all heads; block ``n`` is a
+                # sink for the rows of inactive batch slots
+                self.k_cache = [torch.zeros(n + 1, self.bs, 1, self.mla_dim, dtype=dt, device=self.device)
+                                for _ in self.w.layers]
+                self.v_cache = [torch.zeros(n + 1, 0, dtype=dt, device=self.device) for _ in self.w.layers]
+            else:
+                self.k_cache = [torch.zeros(n, self.bs, self.hk, self.D, dtype=dt, device=self.device)
+                                for _ in self.w.layers]
+                self.v_cache = [torch.zeros(n, self.bs, self.hk, self.D, dtype=dt, device=self.device)
+                                for _ in self.w.layers]
             self.sched = _Sched(n, self.bs, self.max_running, self.max_prefill_tokens)
             self.asleep["kv_cache"] = False
             self._graphs.clear()
@@ -387,6 +415,13 @@ class InferEngine:
         res = None
         for li, lw in enumerate(self.w.layers):
             h, res = fused.rmsnorm(x, lw.ln1, cfg.rms_norm_eps, res)
+            if lw.mla is not None:
+                q_nope, q_rope, c_kv, k_rope = lw.mla.project(h, pos)
+                self.k_cache[li].view(-1, self.mla_dim).index_copy_(0, slots.long(), torch.cat([c_kv, k_rope], -1))
+                a = self._allreduce(lw.mla.linear_proj(lw.mla.attend(q_nope, q_rope, c_kv, k_rope, cu)))
+                h, res = fused.rmsnorm(a, lw.ln2, cfg.rms_norm_eps, res)
+                x = self._mlp(lw, h)
+                continue
             qkv = self._lin(h, lw, "qkv_w", lw.qkv_b)
             qkv = self._qk_norm(lw, qkv, T)
             kv_append_rope(qkv, pos, slots, self.k_cache[li], self.v_cache[li], self.hq, self.hk, self.D,
@@ -425,8 +460,21 @@ class InferEngine:
         ctx = torch.where(st["active"], pos + 1, torch.zeros_like(pos))
         x = self._embed(st["tokens"])
         res = None
+        if self.mla_dim:
+            # latent rows of every request, gathered once per step for all layers' index arithmetic
+            p_all = torch.arange(self.max_model_len, device=pos.device)
+            lat_idx = (st["block_table"].long()[:, p_all // self.bs] * self.bs + p_all % self.bs)  # [B, Lmax]
+            lat_mask = p_all[None, :] < ctx[:, None]
+            sink = (self.k_cache[0].shape[0] - 1) * self.bs
+            lat_slots = torch.where(slots >= 0, slots, torch.full_like(slots, sink)).long()
         for li, lw in enumerate(self.w.layers):
             h, res = fused.rmsnorm(x, lw.ln1, cfg.rms_norm_eps, res)
+            if lw.mla is not None:
+                o = self._mla_decode(lw.mla, h, pos, self.k_cache[li], lat_slots, lat_idx, lat_mask)
+                a = self._allreduce(lw.mla.linear_proj(o))
+                h, res = fused.rmsnorm(a, lw.ln2, cfg.rms_norm_eps, res)
+                x = self._mlp(lw, h)
+                continue
             qkv = self._lin(h, lw, "qkv_w", lw.qkv_b)
             qkv = self._qk_norm(lw, qkv, B)
             kv_append_rope(qkv, pos, slots, self.k_cache[li], self.v_cache[li], self.hq, self.hk, self.D,
@@ -443,6 +491,32 @@ class InferEngine:
         st["pos"].add_(st["active"].to(pos.dtype))
         st["steps"].add_(1)
         st["ring_idx"].add_(1)
+
+    def _mla_decode(self, mla, h, pos, cache, slots, lat_idx, lat_mask):
+        """One token per request of multi-head latent attention on the latent cache, in the absorbed form: the key
+        up-projection is folded into the query and the value up-projection is applied after the weighted sum, so a
+        step reads ``kv_lora + rope`` values per cached token instead of per-head keys and values
+        (the role of the latent decode kernels the reference reaches through its serving engines)."""
+        cfg = self.cfg
+        dn, dr, dv, C = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
+        B = h.shape[0]
+        q_nope, q_rope, c_kv, k_rope = mla.project(h, pos)
+        flat = cache.view(-1, self.mla_dim)
+        flat.index_copy_(0, slots, torch.cat([c_kv, k_rope], -1))
+        lat = flat[lat_idx]                                            # [B, Lmax, C + dr]
+        w_up = mla.linear_kv_up_proj.weight.view(mla.h, dn + dv, C)
+        up_lora = getattr(mla.linear_kv_up_proj, "lora", None)
+        if up_lora is not None:  # adapters on the up-projection: fold their delta into the absorbed matrices
+            w_up = w_up + up_lora.delta_weight().view(mla.h, dn + dv, C).to(w_up.dtype)
+        q_abs = torch.einsum("bhd,hdc->bhc", q_nope.float(), w_up[:, :dn].float())
+        s = torch.einsum("bhc,blc->bhl", q_abs, lat[..., :C].float())
+        s = s + torch.einsum("bhr,blr->bhl", q_rope.float(), lat[..., C:].float())
+        s = (s / math.sqrt(dn + dr)).masked_fill(~lat_mask[:, None, :], float("-inf"))
+        p = torch.softmax(s, -1)
+        p = torch.where(lat_mask[:, None, :], p, torch.zeros_like(p))   # rows of inactive slots: all masked -> zeros
+        o_lat = torch.einsum("bhl,blc->bhc", p, lat[..., :C].float())
+        o = torch.einsum("bhc,hvc->bhv", o_lat, w_up[:, dn:].float())
+        return o.reshape(B, mla.h * dv).to(h.dtype)
 
     def _sample_into(self, hidden, st):
         logits = linear_forward(hidden, self.w.head, out_dtype=torch.float32)

@@ -149,3 +149,38 @@ def test_weight_sync_into_a_separate_rollout_copy_and_verify():
     name = "decoder.layers.0.self_attention.linear_qkv.weight"
     shards = [reshard_tensor(name, [full], "column", 2, r, mcfg) for r in range(2)]
     assert torch.equal(reshard_tensor(name, shards, "column", 1, 0, mcfg), full)
+
+
+def test_mla_moe_model_serves_from_latent_cache():
+    """DeepSeek-V3-style model (multi-head latent attention, sigmoid group routing with a shared expert, first layer
+    dense): the decoder caches only the latent + shared rotated key and attends in the absorbed form; it must equal
+    the trainer model's full recompute, with more requests than batch slots and shared prompt prefixes."""
+    from gcore_b200.models.config import ModelConfig
+    cfg = ModelConfig(arch="deepseek_v3", num_layers=3, hidden_size=64, num_attention_heads=4, num_kv_heads=4,
+                      ffn_hidden_size=128, vocab_size=256, use_mla=True, q_lora_rank=32, kv_lora_rank=32,
+                      qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16, head_dim=24, num_experts=8, moe_top_k=2,
+                      moe_ffn_hidden_size=32, moe_shared_expert_ffn=32, moe_router_type="sigmoid_group", moe_n_group=4,
+                      moe_topk_group=2, first_k_dense=1, moe_routed_scaling_factor=2.5, moe_router_bias=True,
+                      rope_interleaved=True, dtype="float32")
+    torch.manual_seed(0)
+    model = GPTModel(cfg, recompute="none")
+    model.eval()
+    # the model trains: gradients reach the latent projections
+    t = torch.randint(3, 256, (12,))
+    h, _ = model(t, torch.arange(12, dtype=torch.int32), torch.tensor([0, 12], dtype=torch.int32), 12)
+    model.logits(h).float().logsumexp(-1).sum().backward()
+    a = model.decoder.layers[1].self_attention
+    assert a.linear_kv_down_proj.weight.grad.abs().sum() > 0 and a.linear_q_up_proj.weight.grad.abs().sum() > 0
+    eng = InferEngine(cfg, RolloutWeights.from_model(model), max_running_requests=4, max_model_len=48,
+                      kv_block_size=4, sync_interval=3, use_cuda_graph=False)
+    assert eng.k_cache == [] and eng.mla_dim == 40
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(3, 256, (l,), generator=g).tolist() for l in (5, 9, 7)]
+    reqs = eng.generate(prompts, SamplingParams(max_new_tokens=6, greedy=True), n=2)
+    assert tuple(eng.k_cache[0].shape[2:]) == (1, 40) and eng.v_cache[0].numel() == 0
+    for i, p in enumerate(prompts):
+        ref_t, ref_lp = naive_greedy(model, p, 6)
+        for j in range(2):
+            r = reqs[i * 2 + j]
+            assert r.out_tokens == ref_t, (i, j, r.out_tokens, ref_t)
+            assert max(abs(x - y) for x, y in zip(r.out_logprobs, ref_lp)) < 1e-3

@@ -109,7 +109,10 @@ def build_dispatch_plan(expert_ids: torch.Tensor, num_experts: int):
     """expert_ids [N] (N = tokens * K, values in [0, E)) -> (dest_row [N], offsets [E+1] int32) for the padded
     expert-sorted layout; no host synchronisation."""
     N = expert_ids.numel()
-    counts = torch.bincount(expert_ids, minlength=num_experts)
+    # scatter_add, not bincount: bincount reads its maximum back to the host, which a CUDA-graph capture (decode
+    # steps of the rollout engine) does not allow
+    counts = torch.zeros(num_experts, dtype=torch.int64, device=expert_ids.device).scatter_add_(
+        0, expert_ids, torch.ones_like(expert_ids, dtype=torch.int64))
     padded = (counts + (SEG - 1)) // SEG * SEG
     offsets = torch.zeros(num_experts + 1, dtype=torch.int64, device=expert_ids.device)
     offsets[1:] = padded.cumsum(0)

@@ -246,6 +246,10 @@ class InferEngine:
         self.vocab_local = weights.head.shape[0]
         self.vocab_start = self.vocab_local * (dist.get_rank(tp_group) if (tp_group is not None and tp_size > 1) else 0)
         self.use_graph = use_cuda_graph and self.device.type == "cuda" and not _lib.force_eager()
+        if any(getattr(lw.moe, "ep_size", 1) > 1 for lw in weights.layers if lw.moe is not None):
+            # expert-parallel dispatch sizes its exchanges on the host (and the peer-memory path numbers its epochs
+            # there), so a decode step cannot be replayed from a captured graph
+            self.use_graph = False
         self.sync_interval = max(1, sync_interval)
         self.eos = eos_token_id
         self.gpu_memory_utilization = gpu_memory_utilization

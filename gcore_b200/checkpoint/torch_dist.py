@@ -16,7 +16,6 @@ import json
 import os
 import pickle
 import random
-import re
 import shutil
 import threading
 from typing import Dict, List, Optional, Tuple
@@ -110,16 +109,16 @@ def set_rng_state(st: dict):
         torch.cuda.set_rng_state(st["cuda"])
 
 
-_LOCAL_LAYER = re.compile(r"decoder\.layers\.(\d+)\.")
-
-
 def _canonical(model, name: str) -> str:
     """Parameter name in the unpartitioned model: a pipeline stage numbers its layers from zero, the checkpoint uses
     the global layer index (the stacked-layer axis spans all stages), so any pipeline layout can load any other's."""
-    off = getattr(model, "layer_offset", 0)
-    if not off:
-        return name
-    return _LOCAL_LAYER.sub(lambda m: f"decoder.layers.{int(m.group(1)) + off}.", name, count=1)
+    fn = getattr(model, "canonical_name", None)
+    if fn is not None:
+        return fn(name)
+    inner = getattr(model, "language_model", None)  # vision-language wrapper
+    if inner is not None and name.startswith("language_model."):
+        return "language_model." + inner.canonical_name(name[len("language_model."):])
+    return name
 
 
 def _model_chunks(engine) -> List[Chunk]:

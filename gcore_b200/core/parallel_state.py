@@ -104,6 +104,9 @@ def plan_groups(world_size: int, tp: int = 1, pp: int = 1, cp: int = 1, ep: int 
         "cp": _enumerate_groups(dense, order, ["cp"]),
         "dp": _enumerate_groups(dense, order, ["dp"]),
         "pp": _enumerate_groups(dense, order, ["pp"]),
+        # a second communicator over the same ranks: gradients travel on it, so that with two stages (where the next
+        # and the previous stage are the same peer) forward and backward messages never share a FIFO
+        "pp_bwd": _enumerate_groups(dense, order, ["pp"]),
         "dp_cp": _enumerate_groups(dense, order, ["dp", "cp"]),
         "tp_cp": _enumerate_groups(dense, order, ["tp", "cp"]),
         "mp": _enumerate_groups(dense, order, ["tp", "pp"]),
@@ -203,6 +206,10 @@ def get_tensor_model_parallel_rank():
 
 def get_pipeline_model_parallel_group():
     return _STATE.group("pp")
+
+
+def get_pipeline_backward_group():
+    return _STATE.group("pp_bwd")
 
 
 def get_pipeline_model_parallel_world_size():

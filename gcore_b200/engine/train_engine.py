@@ -93,10 +93,17 @@ class TrainingEngine:
             from ..parallel.pp import stage_layer_range
             stage = ps.get_pipeline_model_parallel_rank()
             assert not self.model_cfg.tie_word_embeddings, "tied embeddings are not supported across pipeline stages"
-            stage_kw = dict(pre_process=stage == 0, post_process=stage == pp - 1,
-                            layer_range=stage_layer_range(self.model_cfg.num_layers, pp, stage,
-                                                          d.num_layers_in_first_pipeline_stage,
-                                                          d.num_layers_in_last_pipeline_stage))
+            vpp = d.virtual_pipeline_model_parallel_size or 1
+            if vpp > 1:
+                # interleaved stages: this rank holds chunks v = 0 .. vpp-1, chunk v being virtual stage v * pp + stage
+                assert d.num_layers_in_first_pipeline_stage is None and d.num_layers_in_last_pipeline_stage is None, \
+                    "uneven first / last stages are not combined with virtual pipeline stages"
+                assert self.model_cfg.num_layers % (pp * vpp) == 0, "layers must divide evenly over pp * vpp chunks"
+                rng = [stage_layer_range(self.model_cfg.num_layers, pp * vpp, v * pp + stage) for v in range(vpp)]
+            else:
+                rng = stage_layer_range(self.model_cfg.num_layers, pp, stage, d.num_layers_in_first_pipeline_stage,
+                                        d.num_layers_in_last_pipeline_stage)
+            stage_kw = dict(pre_process=stage == 0, post_process=stage == pp - 1, layer_range=rng)
         if self.vision_cfg is not None:
             from ..models.vlm import VLModel
             assert tp == 1 and pp == 1, "vision-language models run with TP = PP = 1"
@@ -203,8 +210,9 @@ class TrainingEngine:
                 else:
                     r.backward()
             return out
-        from ..parallel.pp import PipelineComm, forward_backward_1f1b
-        comm = PipelineComm(ps.get_pipeline_model_parallel_group())
+        from ..parallel.pp import PipelineComm, forward_backward_1f1b, forward_backward_interleaved
+        comm = PipelineComm(ps.get_pipeline_model_parallel_group(), ps.get_pipeline_backward_group())
+        n_chunks = len(getattr(model, "chunk_bounds", [0]))
         packed: Dict[int, PackedBatch] = {}
 
         def get(i):
@@ -212,10 +220,10 @@ class TrainingEngine:
                 packed[i] = self._pack(samples, batches[i], keys)
             return packed[i]
 
-        def forward_step(i, hidden_in):
+        def forward_step(i, hidden_in, chunk=None):
             mb = get(i)
             return model(mb.tokens, mb.position_ids, mb.cp_ctx if mb.cp_ctx is not None else mb.cu_seqlens,
-                         mb.max_seqlen, hidden_in=hidden_in)
+                         mb.max_seqlen, hidden_in=hidden_in, chunk=chunk)
 
         def loss_step(i, hidden, aux):
             r = step_fn(get(i), hidden, aux)
@@ -229,6 +237,10 @@ class TrainingEngine:
             dt = {"bfloat16": torch.bfloat16, "float32": torch.float32}[self.model_cfg.dtype]
             return (t_local, self.model_cfg.hidden_size), dt, self.device
 
+        if n_chunks > 1:
+            return forward_backward_interleaved(comm, len(batches), n_chunks,
+                                                lambda i, v, x: forward_step(i, x, v), loss_step, act_shape,
+                                                forward_only)
         return forward_backward_1f1b(comm, len(batches), forward_step, loss_step, act_shape, forward_only)
 
     def _from_last_stage(self, t, shape, dtype):

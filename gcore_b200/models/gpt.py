@@ -333,11 +333,24 @@ class GPTModel(nn.Module):
             self.embedding.word_embeddings.weight = nn.Parameter(
                 torch.empty(self.vocab_local, cfg.hidden_size, dtype=dt, device=device))
             self.embedding.word_embeddings.weight.tp_mode = "column"
-        lo, hi = layer_range if layer_range is not None else (0, cfg.num_layers)
-        self.layer_offset = lo
+        # one (lo, hi) range of global layer indices, or a list of them: the model chunks of an interleaved
+        # (virtual) pipeline stage, run one at a time with ``forward(chunk=v)``
+        if layer_range is None:
+            ranges = [(0, cfg.num_layers)]
+        elif isinstance(layer_range[0], (tuple, list)):
+            ranges = [tuple(r) for r in layer_range]
+        else:
+            ranges = [tuple(layer_range)]
+        self.layer_ranges = ranges
+        self.layer_offset = ranges[0][0]
+        self.global_layer_ids = [i for lo, hi in ranges for i in range(lo, hi)]
+        self.chunk_bounds, n0 = [], 0
+        for lo, hi in ranges:
+            self.chunk_bounds.append((n0, n0 + hi - lo))
+            n0 += hi - lo
         self.decoder = nn.Module()
         self.decoder.layers = nn.ModuleList(
-            [TransformerLayer(cfg, i, tp_size, ep_size, device) for i in range(lo, hi)])
+            [TransformerLayer(cfg, i, tp_size, ep_size, device) for i in self.global_layer_ids])
         self.value_head = value_head
         if post_process:
             self.decoder.final_layernorm = RMSNormWeight(cfg.hidden_size, cfg, device)
@@ -374,8 +387,7 @@ class GPTModel(nn.Module):
                 continue
             mode = getattr(p, "tp_mode", "none")
             # keyed by the parameter's name in the unpartitioned model, so a pipeline stage draws the same values
-            canon = re.sub(r"decoder\.layers\.(\d+)\.", lambda m: f"decoder.layers.{int(m.group(1)) + self.layer_offset}.",
-                           name)
+            canon = self.canonical_name(name)
             key = zlib.crc32(f"0:{canon}".encode()) ^ seed
             full_numel = p.numel() * (self.tp_size if mode in ("column", "row") else 1)
             with torch.no_grad():
@@ -405,6 +417,11 @@ class GPTModel(nn.Module):
                         (key + (7919 * tp_rank if mode in ("column", "row") else 0)) & 0x7FFFFFFF)
                     p.copy_(torch.randn(p.shape, generator=g) * mod_std)
 
+    def canonical_name(self, name: str) -> str:
+        """Parameter name in the unpartitioned model (local layer position -> global layer index)."""
+        ids = self.global_layer_ids
+        return re.sub(r"decoder\.layers\.(\d+)\.", lambda m: f"decoder.layers.{ids[int(m.group(1))]}.", name, count=1)
+
     def _owner(self, pname: str):
         mod = self
         for part in pname.split(".")[:-1]:
@@ -421,13 +438,18 @@ class GPTModel(nn.Module):
         return self.vocab_local * (ps.get_tensor_model_parallel_rank() if self.tp_size > 1 else 0)
 
     def forward(self, input_ids=None, position_ids=None, cu_seqlens=None, max_seqlen=None, hidden_in=None,
-                inputs_embeds=None):
+                inputs_embeds=None, chunk=None):
         """``input_ids`` [T] packed tokens (first stage) or ``hidden_in`` (later pipeline stages, sequence-parallel
         shard).  Returns ``(hidden, aux_loss)``: on the last stage ``hidden`` is the final-normed ``[T, H]`` (gathered
-        over SP), otherwise the stage output to send downstream."""
+        over SP), otherwise the stage output to send downstream.  ``chunk`` selects one model chunk of an interleaved
+        pipeline stage (embedding only in front of the first, final norm only behind the last); None runs them all."""
         tp_group = ps.get_tensor_model_parallel_group() if self.tp_size > 1 else None
         sp = self.sequence_parallel
-        if self.pre_process:
+        n_chunks = len(self.chunk_bounds)
+        first = self.pre_process and (chunk is None or chunk == 0)
+        last = self.post_process and (chunk is None or chunk == n_chunks - 1)
+        l0, l1 = (0, len(self.decoder.layers)) if chunk is None else self.chunk_bounds[chunk]
+        if first:
             if inputs_embeds is None:
                 x = tp_ops.vocab_parallel_embedding(input_ids, self.embedding.word_embeddings.weight,
                                                     self.vocab_start(), tp_group)
@@ -441,7 +463,8 @@ class GPTModel(nn.Module):
         aux_total = None
         pos32 = position_ids.to(torch.int32) if position_ids.dtype != torch.int32 else position_ids
         n_ckpt = getattr(self, "recompute_num_layers", None)
-        for li, layer in enumerate(self.decoder.layers):
+        for li in range(l0, l1):
+            layer = self.decoder.layers[li]
             if (self.recompute == "full" and torch.is_grad_enabled() and x.requires_grad
                     and (n_ckpt is None or li < n_ckpt)):
                 x, residual, aux = checkpoint(layer, x, residual, pos32, cu_seqlens, max_seqlen, tp_group, sp,
@@ -450,7 +473,7 @@ class GPTModel(nn.Module):
                 x, residual, aux = layer(x, residual, pos32, cu_seqlens, max_seqlen, tp_group, sp)
             if aux is not None:
                 aux_total = aux if aux_total is None else aux_total + aux
-        if not self.post_process:
+        if not last:
             # carry the un-added residual forward as one tensor
             return (x + residual if residual is not None else x), aux_total
         h, _ = fused.rmsnorm(x, self.decoder.final_layernorm.weight, self.cfg.rms_norm_eps, residual)

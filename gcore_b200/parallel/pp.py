@@ -43,8 +43,13 @@ def stage_layer_range(num_layers: int, pp: int, stage: int, first_stage_layers: 
 
 
 class PipelineComm:
-    def __init__(self, group):
+    """Point-to-point plumbing of one pipeline.  Activations travel on ``group`` and gradients on ``bwd_group`` (a
+    second communicator over the same ranks when given): with two stages the next and the previous stage are the
+    same peer, and an interleaved schedule would otherwise mix both kinds of message in one FIFO."""
+
+    def __init__(self, group, bwd_group=None):
         self.group = group
+        self.bwd_group = bwd_group if bwd_group is not None else group
         self.size = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.ranks = dist.get_process_group_ranks(group)
@@ -59,13 +64,13 @@ class PipelineComm:
         return self.rank == self.size - 1
 
     def _peer(self, delta):
-        return self.ranks[self.rank + delta]
+        return self.ranks[(self.rank + delta) % self.size]  # the ring closes for interleaved stages
 
     def send_forward(self, t):
         self._pending.append((dist.isend(t.contiguous(), self._peer(+1), group=self.group), t))
 
     def send_backward(self, t):
-        self._pending.append((dist.isend(t.contiguous(), self._peer(-1), group=self.group), t))
+        self._pending.append((dist.isend(t.contiguous(), self._peer(-1), group=self.bwd_group), t))
 
     def recv_forward(self, shape, dtype, device):
         t = torch.empty(shape, dtype=dtype, device=device)
@@ -74,7 +79,7 @@ class PipelineComm:
 
     def recv_backward(self, shape, dtype, device):
         t = torch.empty(shape, dtype=dtype, device=device)
-        dist.recv(t, self._peer(+1), group=self.group)
+        dist.recv(t, self._peer(+1), group=self.bwd_group)
         return t
 
     def drain(self):
@@ -145,6 +150,91 @@ def forward_backward_1f1b(comm: PipelineComm, num_microbatches: int,
         bwd(i)
     for i in range(M - warm, M):
         bwd(i)
+    comm.drain()
+    return results
+
+
+def interleaved_order(num_microbatches: int, pp: int, vpp: int) -> List[Tuple[int, int]]:
+    """Forward order of (chunk, micro-batch) pairs of the interleaved schedule, identical on every stage:
+    micro-batches go in groups of ``pp``; a group passes through chunk 0 on all stages, then chunk 1, ...  The
+    backward order is the same list with the chunks mirrored."""
+    order = []
+    for g0 in range(0, num_microbatches, pp):
+        group = range(g0, min(g0 + pp, num_microbatches))
+        for v in range(vpp):
+            order += [(v, i) for i in group]
+    return order
+
+
+def forward_backward_interleaved(comm: PipelineComm, num_microbatches: int, num_chunks: int,
+                                 forward_step: Callable[[int, int, Optional[torch.Tensor]], Tuple[torch.Tensor, object]],
+                                 loss_step: Callable[[int, torch.Tensor, object], torch.Tensor],
+                                 act_shape: Callable[[int], Tuple[Sequence[int], torch.dtype, torch.device]],
+                                 forward_only: bool = False) -> List[object]:
+    """Interleaved 1F1B (virtual pipeline stages): stage ``s`` holds model chunks ``v = 0 .. V-1``, chunk ``v`` being
+    virtual stage ``v * P + s``; the bubble shrinks by a factor ``V`` for ``V`` times as many (smaller) messages.
+    ``forward_step(i, v, hidden_in)`` runs chunk ``v`` on micro-batch ``i``.  The steady state needs the number of
+    micro-batches to be a multiple of ``P``; otherwise (and when it equals ``P``) all forwards run before all
+    backwards, which is always consistent.  (The schedule the reference gets from Megatron-Core's
+    ``get_forward_backward_func`` when ``virtual_pipeline_model_parallel_size`` is set:
+    gpatch_v4/training_backend/megatron_backend/mixin.py:411-414.)"""
+    P, s, M, V = comm.size, comm.rank, num_microbatches, num_chunks
+    order_f = interleaved_order(M, P, V)
+    order_b = [(V - 1 - v, i) for v, i in order_f]
+    total = len(order_f)
+    inputs, outputs = {}, {}
+    results: List[object] = []
+
+    def fwd(k):
+        v, i = order_f[k]
+        x = None
+        if not (s == 0 and v == 0):
+            x = comm.recv_forward(*act_shape(i))
+            if not forward_only:
+                x.requires_grad_(True)
+        with torch.set_grad_enabled(not forward_only):
+            out, aux = forward_step(i, v, x)
+            if s == P - 1 and v == V - 1:
+                out = loss_step(i, out, aux)
+                if forward_only:
+                    results.append(out)
+            else:
+                comm.send_forward(out.detach())
+                if aux is not None and not forward_only:
+                    out = (out, aux)
+        if not forward_only:
+            inputs[(v, i)], outputs[(v, i)] = x, out
+
+    def bwd(k):
+        v, i = order_b[k]
+        out, x = outputs.pop((v, i)), inputs.pop((v, i))
+        if s == P - 1 and v == V - 1:
+            out.backward()
+        else:
+            g = comm.recv_backward(*act_shape(i))
+            if isinstance(out, tuple):
+                torch.autograd.backward([out[0], out[1]], [g, torch.ones_like(out[1])])
+            else:
+                out.backward(g)
+        if x is not None:
+            comm.send_backward(x.grad)
+
+    if forward_only:
+        for k in range(total):
+            fwd(k)
+        comm.drain()
+        return results
+    if M % P != 0 or M == P:
+        warm = total
+    else:
+        warm = min((P - s - 1) * 2 + (V - 1) * P, total)
+    for k in range(warm):
+        fwd(k)
+    for k in range(total - warm):
+        fwd(warm + k)
+        bwd(k)
+    for k in range(total - warm, total):
+        bwd(k)
     comm.drain()
     return results
 

@@ -1,4 +1,4 @@
-"""gloo worker for the parallelism parity tests: mode = tp | ep | cp | pp | fsdp."""
+"""gloo worker for the parallelism parity tests: mode = tp | ep | cp | pp | vpp | fsdp."""
 import json
 import os
 import sys
@@ -26,9 +26,10 @@ def samples(n, seed, L=48, vocab=1024):
     return out
 
 
-def engine(mcfg, tp, sp=True, lr=1e-3):
+def engine(mcfg, tp, sp=True, lr=1e-3, vpp=None):
     pc = PolicyConfig(recompute="none", without_ref=True)
     pc.dist_config.tensor_model_parallel_size = tp
+    pc.dist_config.virtual_pipeline_model_parallel_size = vpp
     pc.dist_config.sequence_parallel = sp and tp > 1
     oc = OptimizerConfig(lr=lr, lr_decay_style="constant", weight_decay=0.0, max_grad_norm=1.0)
     tc = TrainingConfig(train_mbs=2, train_gbs=8)
@@ -77,11 +78,13 @@ def main():
         lp = e.compute_log_probs(samples(3, 99))
         res = {"losses": losses, "grad_norm": float(e.optimizer.last_grad_norm),
                "logprobs": [x["logprobs"].tolist() for x in lp]}
-    elif mode == "pp":
+    elif mode in ("pp", "vpp"):
         ps.initialize_model_parallel(tp=1, pp=2)
         mcfg = get_preset("tiny_llama", dtype="float32", qkv_bias=True, num_layers=4)
-        e = engine(mcfg, 1)
+        e = engine(mcfg, 1, vpp=2 if mode == "vpp" else None)
         assert len(e.model.decoder.layers) == 2
+        if mode == "vpp":  # interleaved: stage 0 holds layers 0 and 2, stage 1 holds 1 and 3
+            assert e.model.global_layer_ids == [rank, rank + 2] and len(e.model.chunk_bounds) == 2
         losses = []
         for s in range(4):
             losses.append(e.finetune_step(samples(8, 130 + s))["lm_loss"])  # pipeline ranks see the same data
@@ -92,7 +95,7 @@ def main():
             from gcore_b200.checkpoint.torch_dist import load_checkpoint, save_checkpoint
             save_checkpoint(e, os.path.join(sys.argv[3], "ckpt"), 4)
             # a fresh two-stage engine (other seed) resumes from it and takes the same next step
-            e2 = engine(mcfg, 1)
+            e2 = engine(mcfg, 1, vpp=2 if mode == "vpp" else None)
             e2.setup_model_and_get_optimizer(seed=77)
             assert load_checkpoint(e2, os.path.join(sys.argv[3], "ckpt")) == 4
             res["next_loss"] = [x.finetune_step(samples(8, 140))["lm_loss"] for x in (e, e2)]

@@ -107,6 +107,11 @@ def plan_groups(world_size: int, tp: int = 1, pp: int = 1, cp: int = 1, ep: int 
         # a second communicator over the same ranks: gradients travel on it, so that with two stages (where the next
         # and the previous stage are the same peer) forward and backward messages never share a FIFO
         "pp_bwd": _enumerate_groups(dense, order, ["pp"]),
+        # interleaved stages close the ring (last stage -> first stage); that traffic gets communicators of its own so
+        # that on each communicator the send / receive dependencies form a line, never a cycle: a send that has to
+        # wait for its receiver then cannot hold up the receive its receiver is waiting for
+        "pp_wrap": _enumerate_groups(dense, order, ["pp"]),
+        "pp_bwd_wrap": _enumerate_groups(dense, order, ["pp"]),
         "dp_cp": _enumerate_groups(dense, order, ["dp", "cp"]),
         "tp_cp": _enumerate_groups(dense, order, ["tp", "cp"]),
         "mp": _enumerate_groups(dense, order, ["tp", "pp"]),
@@ -210,6 +215,10 @@ def get_pipeline_model_parallel_group():
 
 def get_pipeline_backward_group():
     return _STATE.group("pp_bwd")
+
+
+def get_pipeline_wrap_groups():
+    return _STATE.group("pp_wrap"), _STATE.group("pp_bwd_wrap")
 
 
 def get_pipeline_model_parallel_world_size():

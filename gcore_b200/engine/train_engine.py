@@ -211,7 +211,8 @@ class TrainingEngine:
                     r.backward()
             return out
         from ..parallel.pp import PipelineComm, forward_backward_1f1b, forward_backward_interleaved
-        comm = PipelineComm(ps.get_pipeline_model_parallel_group(), ps.get_pipeline_backward_group())
+        comm = PipelineComm(ps.get_pipeline_model_parallel_group(), ps.get_pipeline_backward_group(),
+                            *ps.get_pipeline_wrap_groups())
         n_chunks = len(getattr(model, "chunk_bounds", [0]))
         packed: Dict[int, PackedBatch] = {}
 

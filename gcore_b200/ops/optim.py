@@ -16,12 +16,17 @@ def adam_step(master, m, v, grad, param, *, lr, beta1, beta2, eps, weight_decay,
     ``grad`` may be fp32 or bf16; ``param`` (bf16, optional) receives the rounded master weights;
     ``grad_scale`` is an optional 1-element device tensor multiplied into every gradient (clip coefficient)."""
     n = master.numel()
-    if _lib.use_native(master):
+    if _lib.use_native(master) and grad.dtype in (torch.float32, torch.bfloat16):
         LAUNCHES["optim"] += 1
+        # the kernel rounds the master weights to bf16 parameters; parameters of another dtype (fp32 models) are
+        # refreshed from the master weights afterwards
+        fused_param = param if (param is not None and param.dtype == torch.bfloat16) else None
         _lib.check(_lib.kernels().gk_adam(_lib.ptr(master), _lib.ptr(m), _lib.ptr(v), _lib.ptr(grad),
-                                          int(grad.dtype == torch.float32), _lib.ptr(param), n, float(lr),
+                                          int(grad.dtype == torch.float32), _lib.ptr(fused_param), n, float(lr),
                                           float(beta1), float(beta2), float(eps), float(weight_decay), int(step),
                                           _lib.ptr(grad_scale), float(scale_val), _lib.stream_ptr()), "adam")
+        if param is not None and fused_param is None:
+            param.copy_(master.to(param.dtype))
         return
     g = grad.float() * scale_val
     if grad_scale is not None:

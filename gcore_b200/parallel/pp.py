@@ -47,9 +47,12 @@ class PipelineComm:
     second communicator over the same ranks when given): with two stages the next and the previous stage are the
     same peer, and an interleaved schedule would otherwise mix both kinds of message in one FIFO."""
 
-    def __init__(self, group, bwd_group=None):
+    def __init__(self, group, bwd_group=None, wrap_group=None, bwd_wrap_group=None):
         self.group = group
         self.bwd_group = bwd_group if bwd_group is not None else group
+        # last stage -> first stage (interleaved chunks) and the gradients coming back
+        self.wrap_group = wrap_group if wrap_group is not None else group
+        self.bwd_wrap_group = bwd_wrap_group if bwd_wrap_group is not None else self.bwd_group
         self.size = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.ranks = dist.get_process_group_ranks(group)
@@ -67,19 +70,21 @@ class PipelineComm:
         return self.ranks[(self.rank + delta) % self.size]  # the ring closes for interleaved stages
 
     def send_forward(self, t):
-        self._pending.append((dist.isend(t.contiguous(), self._peer(+1), group=self.group), t))
+        g = self.wrap_group if self.is_last else self.group
+        self._pending.append((dist.isend(t.contiguous(), self._peer(+1), group=g), t))
 
     def send_backward(self, t):
-        self._pending.append((dist.isend(t.contiguous(), self._peer(-1), group=self.bwd_group), t))
+        g = self.bwd_wrap_group if self.is_first else self.bwd_group
+        self._pending.append((dist.isend(t.contiguous(), self._peer(-1), group=g), t))
 
     def recv_forward(self, shape, dtype, device):
         t = torch.empty(shape, dtype=dtype, device=device)
-        dist.recv(t, self._peer(-1), group=self.group)
+        dist.recv(t, self._peer(-1), group=self.wrap_group if self.is_first else self.group)
         return t
 
     def recv_backward(self, shape, dtype, device):
         t = torch.empty(shape, dtype=dtype, device=device)
-        dist.recv(t, self._peer(+1), group=self.bwd_group)
+        dist.recv(t, self._peer(+1), group=self.bwd_wrap_group if self.is_last else self.bwd_group)
         return t
 
     def drain(self):

@@ -80,3 +80,34 @@ def test_weight_resync_over_peer_memory_tp2_to_tp1(tmp_path):
         for name, ok in v.items():
             if isinstance(ok, bool):
                 assert ok, (k, name, res)
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("mode", ["pp", "vpp"])
+def test_pipeline_stages_over_nccl_p2p(tmp_path, mode):
+    """1F1B and interleaved 1F1B with activations and gradients on NCCL send / recv (two communicators): losses and
+    log-probs equal the single-GPU run, and the two-stage checkpoint resumes."""
+    sys.path.insert(0, os.path.join(ROOT, "tests", "workers"))
+    import parallel_worker as pw
+    from gcore_b200.models.config import get_preset
+    out = tmp_path / "pp.json"
+    env = dict(os.environ, PYTHONPATH=ROOT, MASTER_ADDR="127.0.0.1", MASTER_PORT="29591", GCORE_TEST_BACKEND="nccl",
+               NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "workers", "parallel_worker.py"), mode,
+                               str(out), str(tmp_path)], env=dict(env, RANK=str(r), WORLD_SIZE="2", LOCAL_RANK=str(r)))
+             for r in range(2)]
+    for p in procs:
+        assert p.wait(timeout=150) == 0
+    got = json.load(open(out))
+    mcfg = get_preset("tiny_llama", dtype="float32", qkv_bias=True, num_layers=4)
+    e = pw.engine(mcfg, 1)
+    ref, norms = [], []
+    for s in range(4):
+        ref.append(e.finetune_step(pw.samples(8, 130 + s))["lm_loss"])
+        norms.append(float(e.optimizer.last_grad_norm))
+    for a, b in zip(ref, got["losses"]):
+        assert abs(a - b) < 2e-3, (ref, got["losses"], norms, got["grad_norms"])
+    lp = e.compute_log_probs(pw.samples(3, 199))
+    for a, b in zip(lp, got["logprobs"]):
+        assert torch.allclose(a["logprobs"].cpu(), torch.tensor(b), atol=2e-3)
+    assert abs(got["next_loss"][0] - got["next_loss"][1]) < 1e-4, got["next_loss"]

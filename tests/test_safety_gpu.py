@@ -88,3 +88,28 @@ def test_rmsnorm_and_swiglu_write_only_their_output():
     assert s.shape == (37, 256)
     assert torch.allclose(s.float(), torch.nn.functional.silu(gu[:, :256].float()) * gu[:, 256:].float(), rtol=2e-2,
                           atol=2e-2)
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 1e-3), ("bfloat16", 3e-3)])
+def test_training_steps_match_the_eager_backend(dtype, tol, monkeypatch):
+    """Four optimisation steps of a small decoder through the engine: native kernels against the PyTorch definitions
+    of the same ops (losses and gradient norms).  fp32 models included: the fused Adam kernel only writes bf16
+    parameters, other dtypes are refreshed from the master weights."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "workers"))
+    import parallel_worker as pw
+    from gcore_b200.models.config import get_preset
+
+    def run(eager):
+        monkeypatch.setenv("GCORE_B200_FORCE_EAGER", "1" if eager else "0")
+        e = pw.engine(get_preset("tiny_llama", dtype=dtype, qkv_bias=True, num_layers=4), 1)
+        out = []
+        for s in range(4):
+            loss = e.finetune_step(pw.samples(8, 130 + s))["lm_loss"]
+            out.append((float(loss), float(e.optimizer.last_grad_norm)))
+        return out
+
+    native, eager = run(False), run(True)
+    for (l0, n0), (l1, n1) in zip(native, eager):
+        assert abs(l0 - l1) < tol and abs(n0 - n1) < 10 * tol * max(1.0, n1), (native, eager)

@@ -40,7 +40,7 @@ def engine(mcfg, tp, sp=True, lr=1e-3, vpp=None):
 
 def main():
     mode, out = sys.argv[1], sys.argv[2]
-    ps.init_distributed("gloo")
+    ps.init_distributed(os.environ.get("GCORE_TEST_BACKEND", "gloo"))  # nccl: the same parity check on GPUs
     world, rank = dist.get_world_size(), dist.get_rank()
     res = {}
     if mode == "tp":
@@ -85,11 +85,12 @@ def main():
         assert len(e.model.decoder.layers) == 2
         if mode == "vpp":  # interleaved: stage 0 holds layers 0 and 2, stage 1 holds 1 and 3
             assert e.model.global_layer_ids == [rank, rank + 2] and len(e.model.chunk_bounds) == 2
-        losses = []
+        losses, norms = [], []
         for s in range(4):
             losses.append(e.finetune_step(samples(8, 130 + s))["lm_loss"])  # pipeline ranks see the same data
+            norms.append(float(e.optimizer.last_grad_norm))
         lp = e.compute_log_probs(samples(3, 199))
-        res = {"losses": losses, "grad_norm": float(e.optimizer.last_grad_norm),
+        res = {"losses": losses, "grad_norm": float(e.optimizer.last_grad_norm), "grad_norms": norms,
                "logprobs": [x["logprobs"].tolist() for x in lp]}
         if len(sys.argv) > 3:
             from gcore_b200.checkpoint.torch_dist import load_checkpoint, save_checkpoint

@@ -90,8 +90,25 @@ def test_rmsnorm_and_swiglu_write_only_their_output():
                           atol=2e-2)
 
 
-@pytest.mark.parametrize("dtype,tol", [("float32", 1e-3), ("bfloat16", 3e-3)])
-def test_training_steps_match_the_eager_backend(dtype, tol, monkeypatch):
+def _parity_model(kind, dtype):
+    from gcore_b200.models.config import ModelConfig, get_preset
+    if kind == "dense":
+        return get_preset("tiny_llama", dtype=dtype, qkv_bias=True, num_layers=4)
+    if kind == "moe":
+        return ModelConfig(arch="qwen3_moe", num_layers=2, hidden_size=256, num_attention_heads=2, num_kv_heads=1,
+                           head_dim=128, ffn_hidden_size=512, vocab_size=1024, num_experts=8, moe_top_k=2,
+                           moe_ffn_hidden_size=128, moe_aux_loss_coef=1e-2, dtype=dtype, qk_layernorm=True)
+    return ModelConfig(arch="deepseek_v3", num_layers=2, hidden_size=256, num_attention_heads=4, num_kv_heads=4,
+                       ffn_hidden_size=512, vocab_size=1024, use_mla=True, q_lora_rank=128, kv_lora_rank=128,
+                       qk_nope_head_dim=64, qk_rope_head_dim=32, v_head_dim=64, head_dim=96, num_experts=8,
+                       moe_top_k=2, moe_ffn_hidden_size=128, moe_shared_expert_ffn=128,
+                       moe_router_type="sigmoid_group", moe_n_group=4, moe_topk_group=2, first_k_dense=1,
+                       moe_routed_scaling_factor=2.5, moe_router_bias=True, rope_interleaved=True, dtype=dtype)
+
+
+@pytest.mark.parametrize("kind,dtype,tol", [("dense", "float32", 1e-3), ("dense", "bfloat16", 3e-3),
+                                            ("moe", "bfloat16", 5e-3), ("mla_moe", "bfloat16", 5e-3)])
+def test_training_steps_match_the_eager_backend(kind, dtype, tol, monkeypatch):
     """Four optimisation steps of a small decoder through the engine: native kernels against the PyTorch definitions
     of the same ops (losses and gradient norms).  fp32 models included: the fused Adam kernel only writes bf16
     parameters, other dtypes are refreshed from the master weights."""
@@ -99,11 +116,10 @@ def test_training_steps_match_the_eager_backend(dtype, tol, monkeypatch):
     import sys
     sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "workers"))
     import parallel_worker as pw
-    from gcore_b200.models.config import get_preset
 
     def run(eager):
         monkeypatch.setenv("GCORE_B200_FORCE_EAGER", "1" if eager else "0")
-        e = pw.engine(get_preset("tiny_llama", dtype=dtype, qkv_bias=True, num_layers=4), 1)
+        e = pw.engine(_parity_model(kind, dtype), 1)
         out = []
         for s in range(4):
             loss = e.finetune_step(pw.samples(8, 130 + s))["lm_loss"]

@@ -246,10 +246,12 @@ class InferEngine:
         self.vocab_local = weights.head.shape[0]
         self.vocab_start = self.vocab_local * (dist.get_rank(tp_group) if (tp_group is not None and tp_size > 1) else 0)
         self.use_graph = use_cuda_graph and self.device.type == "cuda" and not _lib.force_eager()
+        self.ep_group = None  # set when experts are parallel: engines of the group then run their passes in lockstep
         if any(getattr(lw.moe, "ep_size", 1) > 1 for lw in weights.layers if lw.moe is not None):
             # expert-parallel dispatch sizes its exchanges on the host (and the peer-memory path numbers its epochs
             # there), so a decode step cannot be replayed from a captured graph
             self.use_graph = False
+            self.ep_group = ps.get_expert_model_parallel_group()
         self.sync_interval = max(1, sync_interval)
         self.eos = eos_token_id
         self.gpu_memory_utilization = gpu_memory_utilization
@@ -421,7 +423,9 @@ class InferEngine:
             h, res = fused.rmsnorm(x, lw.ln1, cfg.rms_norm_eps, res)
             if lw.mla is not None:
                 q_nope, q_rope, c_kv, k_rope = lw.mla.project(h, pos)
-                self.k_cache[li].view(-1, self.mla_dim).index_copy_(0, slots.long(), torch.cat([c_kv, k_rope], -1))
+                sink = (self.k_cache[li].shape[0] - 1) * self.bs  # rows without a slot land in the spare block
+                self.k_cache[li].view(-1, self.mla_dim).index_copy_(
+                    0, torch.where(slots >= 0, slots, torch.full_like(slots, sink)).long(), torch.cat([c_kv, k_rope], -1))
                 a = self._allreduce(lw.mla.linear_proj(lw.mla.attend(q_nope, q_rope, c_kv, k_rope, cu)))
                 h, res = fused.rmsnorm(a, lw.ln2, cfg.rms_norm_eps, res)
                 x = self._mlp(lw, h)
@@ -495,6 +499,13 @@ class InferEngine:
         st["pos"].add_(st["active"].to(pos.dtype))
         st["steps"].add_(1)
         st["ring_idx"].add_(1)
+
+    def _ep_any(self, *flags):
+        """Logical OR of each flag over the engines of the expert-parallel group (one small all-reduce)."""
+        dev = self.device if dist.get_backend(self.ep_group) == "nccl" else torch.device("cpu")
+        t = torch.tensor([float(bool(f)) for f in flags], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.ep_group)
+        return [bool(x) for x in t.tolist()]
 
     def _mla_decode(self, mla, h, pos, cache, slots, lat_idx, lat_mask):
         """One token per request of multi-head latent attention on the latent cache, in the absorbed form: the key
@@ -660,6 +671,11 @@ class InferEngine:
             # ---- admit: a prompt enters only when its whole sample group fits the batch
             cap = len(slots_free) // max(n, 1)
             pre_ids, _ = self.sched.step(cap, 0) if cap > 0 else ([], [])
+            if self.ep_group is not None and self._ep_any(bool(pre_ids))[0] and not pre_ids:
+                # another engine of the expert-parallel group prefills now: join its all-to-alls with one dummy token
+                self._prefill(torch.zeros(1, dtype=torch.int64, device=dev), torch.zeros(1, dtype=torch.int32, device=dev),
+                              torch.tensor([0, 1], dtype=torch.int32, device=dev), 1,
+                              torch.full((1,), -1, dtype=torch.int32, device=dev))
             if pre_ids:
                 pre = [self.requests[i] for i in pre_ids]
                 toks = torch.tensor([t for r in pre for t in r.prompt], dtype=torch.int64)
@@ -730,6 +746,19 @@ class InferEngine:
                         self.v_cache[li][dst] = self.v_cache[li][src]
                 for c in owners:
                     place(c, *first[c.rid])
+            if self.ep_group is not None:
+                # expert-parallel engines agree on what the group does next: decode if anyone has running requests,
+                # stop only when everyone is done; an engine without requests decodes an all-inactive batch so that
+                # its experts keep serving the others' tokens
+                any_decode, any_left = self._ep_any(bool(slot_req), bool(slot_req) or self.sched.stats()["waiting"] > 0)
+                if not any_left:
+                    break
+                if not slot_req:
+                    if any_decode:
+                        st["active"].zero_()
+                        for _ in range(self.sync_interval):
+                            self._run_decode(st)
+                    continue
             if not slot_req:
                 st_ = self.sched.stats()
                 if st_["waiting"] == 0:

@@ -181,6 +181,30 @@ def test_pp2_interleaved_virtual_stages_match_single_process(tmp_path):
         assert torch.allclose(p, q, atol=2e-4), n
 
 
+def test_expert_parallel_rollout_engines_stay_in_lockstep(tmp_path):
+    """Two rollout engines share their experts (EP = 2) and get unequal work; the one that finishes early keeps
+    stepping with an inactive batch.  Both must reproduce the full-recompute greedy decode of the EP = 1 model."""
+    from test_rollout_cpu import naive_greedy
+    from gcore_b200.models.config import ModelConfig
+    from gcore_b200.models.gpt import GPTModel
+    out = tmp_path / "ep_rollout.json"
+    _spawn("ep_rollout", out, port="29551")
+    mcfg = ModelConfig(arch="qwen3_moe", num_layers=2, hidden_size=128, num_attention_heads=4, num_kv_heads=2,
+                       ffn_hidden_size=256, vocab_size=512, num_experts=8, moe_top_k=2, moe_ffn_hidden_size=64,
+                       dtype="float32", qk_layernorm=True)
+    torch.manual_seed(0)
+    model = GPTModel(mcfg, recompute="none")
+    model.reset_parameters(21)
+    model.eval()
+    for rank, n_new in ((0, 9), (1, 3)):
+        got = json.load(open(f"{out}.{rank}"))
+        assert len(got["prompts"]) == (3 if rank == 0 else 1)
+        for p, toks, lps in zip(got["prompts"], got["tokens"], got["logprobs"]):
+            ref_t, ref_lp = naive_greedy(model, p, n_new)
+            assert toks == ref_t, (rank, toks, ref_t)
+            assert max(abs(a - b) for a, b in zip(lps, ref_lp)) < 1e-3
+
+
 def test_stage_layer_ranges():
     from gcore_b200.parallel.pp import stage_layer_range
     assert [stage_layer_range(12, 4, s) for s in range(4)] == [(0, 3), (3, 6), (6, 9), (9, 12)]

@@ -1,4 +1,4 @@
-"""gloo worker for the parallelism parity tests: mode = tp | ep | cp | pp | vpp | fsdp."""
+"""gloo worker for the parallelism parity tests: mode = tp | ep | ep_rollout | cp | pp | vpp | fsdp."""
 import json
 import os
 import sys
@@ -67,6 +67,28 @@ def main():
             batch = samples(8, 70 + s, vocab=512)
             losses.append(e.finetune_step(batch[rank::world])["lm_loss"])  # EP ranks are also DP ranks
         res = {"losses": losses}
+    elif mode == "ep_rollout":
+        # two engines whose experts are split over both ranks serve different workloads (3 prompts x 9 tokens against
+        # 1 prompt x 3 tokens): the engine that finishes first has to keep its experts in the others' all-to-alls
+        from gcore_b200.models.gpt import GPTModel
+        from gcore_b200.rollout.engine import InferEngine, RolloutWeights, SamplingParams
+        ps.initialize_model_parallel(tp=1, ep=2)
+        mcfg = ModelConfig(arch="qwen3_moe", num_layers=2, hidden_size=128, num_attention_heads=4, num_kv_heads=2,
+                           ffn_hidden_size=256, vocab_size=512, num_experts=8, moe_top_k=2, moe_ffn_hidden_size=64,
+                           dtype="float32", qk_layernorm=True)
+        torch.manual_seed(0)
+        model = GPTModel(mcfg, ep_size=2, recompute="none")
+        model.reset_parameters(21)
+        model.eval()
+        eng = InferEngine(mcfg, RolloutWeights.from_model(model), max_running_requests=2, max_model_len=48,
+                          kv_block_size=4, sync_interval=2, use_cuda_graph=False)
+        assert eng.ep_group is not None
+        g = torch.Generator().manual_seed(100 + rank)
+        n_prompts, n_new = (3, 9) if rank == 0 else (1, 3)
+        prompts = [torch.randint(3, 512, (5 + 2 * i,), generator=g).tolist() for i in range(n_prompts)]
+        reqs = eng.generate(prompts, SamplingParams(max_new_tokens=n_new, greedy=True))
+        json.dump({"prompts": prompts, "tokens": [r.out_tokens for r in reqs],
+                   "logprobs": [r.out_logprobs for r in reqs]}, open(f"{out}.{rank}", "w"))
     elif mode == "cp":
         ps.initialize_model_parallel(tp=1, cp=2)
         mcfg = get_preset("tiny_llama", dtype="float32", qkv_bias=True, sliding_window=16,

@@ -111,3 +111,22 @@ def test_pipeline_stages_over_nccl_p2p(tmp_path, mode):
     for a, b in zip(lp, got["logprobs"]):
         assert torch.allclose(a["logprobs"].cpu(), torch.tensor(b), atol=2e-3)
     assert abs(got["next_loss"][0] - got["next_loss"][1]) < 1e-4, got["next_loss"]
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_grpo_steps_with_experts_split_over_two_gpus(tmp_path):
+    """Two GRPO steps of a small MoE policy in bf16 with the experts split over both GPUs, in the trainer (peer-memory
+    dispatch / combine) and in the colocated rollout engines (lockstep passes, different stop tokens per rank)."""
+    out = tmp_path / "ep_grpo.json"
+    env = dict(os.environ, PYTHONPATH=ROOT, MASTER_ADDR="127.0.0.1", MASTER_PORT="29593", GCORE_TEST_BACKEND="nccl",
+               NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "workers", "parallel_worker.py"), "ep_grpo",
+                               str(out)], env=dict(env, RANK=str(r), WORLD_SIZE="2", LOCAL_RANK=str(r)))
+             for r in range(2)]
+    for p in procs:
+        assert p.wait(timeout=150) == 0
+    got = json.load(open(out))["ranks"]
+    for r in got:
+        assert r["dtype"] == "bfloat16"
+        assert all(g > 0 for g in r["grad_norm"]) and all(abs(x - 1.0) < 2e-2 for x in r["ratio"]), got
+        assert r["logprob_gap"] < 0.15, got

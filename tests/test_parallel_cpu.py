@@ -205,6 +205,18 @@ def test_expert_parallel_rollout_engines_stay_in_lockstep(tmp_path):
             assert max(abs(a - b) for a, b in zip(lps, ref_lp)) < 1e-3
 
 
+def test_grpo_steps_with_expert_parallel_trainer_and_rollout(tmp_path):
+    """GRPO on two ranks that split the experts (trainer and colocated rollout engine), different prompts and stop
+    tokens per rank: steps complete, the first-epoch ratio is 1 and rollout log-probs agree with the trainer's."""
+    out = tmp_path / "ep_grpo.json"
+    _spawn("ep_grpo", out, port="29553")
+    got = json.load(open(out))["ranks"]
+    assert len(got) == 2
+    for r in got:
+        assert all(g > 0 for g in r["grad_norm"]) and all(abs(x - 1.0) < 1e-3 for x in r["ratio"]), got
+        assert r["logprob_gap"] < 2e-3, got
+
+
 def test_stage_layer_ranges():
     from gcore_b200.parallel.pp import stage_layer_range
     assert [stage_layer_range(12, 4, s) for s in range(4)] == [(0, 3), (3, 6), (6, 9), (9, 12)]

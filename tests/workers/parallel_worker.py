@@ -1,4 +1,4 @@
-"""gloo worker for the parallelism parity tests: mode = tp | ep | ep_rollout | cp | pp | vpp | fsdp."""
+"""gloo worker for the parallelism parity tests: mode = tp | ep | ep_rollout | ep_grpo | cp | pp | vpp | fsdp."""
 import json
 import os
 import sys
@@ -89,6 +89,34 @@ def main():
         reqs = eng.generate(prompts, SamplingParams(max_new_tokens=n_new, greedy=True))
         json.dump({"prompts": prompts, "tokens": [r.out_tokens for r in reqs],
                    "logprobs": [r.out_logprobs for r in reqs]}, open(f"{out}.{rank}", "w"))
+    elif mode == "ep_grpo":
+        # whole GRPO steps with experts split over both ranks, in the trainer and in the colocated rollout engine
+        sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+        from test_grpo_cpu import make_cfg, reward_has_small_token
+        from gcore_b200.trainer.grpo_trainer import GrpoTrainer
+        ps.initialize_model_parallel(tp=1, ep=2)
+        dt = "bfloat16" if torch.cuda.is_available() else "float32"
+        mcfg = ModelConfig(arch="qwen3_moe", num_layers=2, hidden_size=256, num_attention_heads=2, num_kv_heads=1,
+                           head_dim=128, ffn_hidden_size=512, vocab_size=1024, num_experts=8, moe_top_k=2,
+                           moe_ffn_hidden_size=128, moe_aux_loss_coef=1e-3, dtype=dt, qk_layernorm=True)
+        cfg = make_cfg()
+        cfg.policy.dist_config.expert_model_parallel_size = 2
+        cfg.training.rollout_gbs, cfg.training.train_gbs = 8, 32   # 4 prompts x 4 samples per rank
+        cfg.sampler.infer_engine_configs[0].generate_params = {"stop_token_ids": [7 + rank]}
+        torch.manual_seed(0)
+        tr = GrpoTrainer(cfg, model_cfg=mcfg, reward_fn=reward_has_small_token).setup()
+        assert tr.engine.ep_group is not None and tr.policy.model.ep_size == 2
+        g = torch.Generator().manual_seed(5 + rank)
+        prompts = [torch.randint(3, 1024, (6 + i,), generator=g).tolist() for i in range(4)]
+        ms = [tr.step(prompts) for _ in range(2)]
+        smp = tr.last_samples[0]
+        P, S = smp["prompt_length"], smp["sequence_length"]
+        gap = float((smp["logprobs"][P - 1:S - 1] - smp["rollout_log_probs"][P - 1:S - 1]).abs().max())
+        res = {"grad_norm": [m["policy/grad_norm"] for m in ms], "ratio": [m["ppo-metrics/ratio"] for m in ms],
+               "logprob_gap": gap, "dtype": dt}
+        allres = [None, None]
+        dist.all_gather_object(allres, res)
+        res = {"ranks": allres}
     elif mode == "cp":
         ps.initialize_model_parallel(tp=1, cp=2)
         mcfg = get_preset("tiny_llama", dtype="float32", qkv_bias=True, sliding_window=16,

@@ -550,6 +550,7 @@ class PretrainConfig(FinetuneConfig):
 class RlConfig(BaseTopConfig):
     placement_type: str = "colocate"
     critic: Optional[CriticConfig] = None
+    teacher: Optional[PolicyConfig] = None  # frozen teacher for on-policy distillation (advantage_type on_policy_distill)
     sampler: SamplerConfig = field(default_factory=SamplerConfig)
     gen_rm: Optional[SamplerConfig] = None
     bt_rm: RewardConfig = field(default_factory=RewardConfig)
@@ -564,6 +565,8 @@ class RlConfig(BaseTopConfig):
             raise ConfigError("rollout_gbs * sampling_keep_n must be a multiple of train_gbs")
         if self.ppo.advantage_type == "ppo" and self.critic is None:
             raise ConfigError("advantage_type=ppo needs a `critic:` section")
+        if self.ppo.advantage_type in ("on_policy_distill", "g_opd") and self.teacher is None:
+            raise ConfigError(f"advantage_type={self.ppo.advantage_type} needs a `teacher:` section")
         if t.rollout_max_staleness > 0 and not (t.async_rollout or t.single_controller):
             raise ConfigError("rollout_max_staleness > 0 needs async_rollout or single_controller")
         if t.use_gen_rm_reward and self.gen_rm is None:

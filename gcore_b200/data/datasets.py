@@ -169,6 +169,66 @@ class PackedSftDataset(Dataset):
         return {"members": members, "num_tokens": sum(m["sequence_length"] for m in members)}
 
 
+class PretrainTokenDataset(Dataset):
+    """Pre-training rows: the documents of an indexed jsonl file (``{"tokens": [...]}`` or ``{"text": ...}`` lines) are
+    laid end to end (an optional separator id between them) and cut into rows of ``seq_length`` tokens; the loss covers
+    every token.  The (document, offset) of each row start is computed once from the document lengths, so a resumed
+    job seeks straight to its row (the reference's indexed-jsonl pretrain datasets with an offset index:
+    ``megatron_datasets/``)."""
+
+    def __init__(self, base: Dataset, tokenizer, seq_length: int, eod_id: Optional[int] = None, key: str = "tokens"):
+        self.base, self.tokenizer, self.seq_length, self.eod, self.key = base, tokenizer, seq_length, eod_id, key
+        lens = [len(self._doc(i)) for i in range(len(base))]
+        self.starts, pos = [], 0                       # global token offset of every document
+        for n in lens:
+            self.starts.append(pos)
+            pos += n
+        self.total = pos
+        self.n_rows = self.total // seq_length
+
+    def _doc(self, i) -> List[int]:
+        row = self.base[i]
+        ids = _encode(self.tokenizer, row[self.key] if self.key in row else row.get("text"))
+        return ids + ([self.eod] if self.eod is not None else [])
+
+    def __len__(self):
+        return self.n_rows
+
+    def __getitem__(self, r):
+        import bisect
+        lo = r * self.seq_length
+        d = bisect.bisect_right(self.starts, lo) - 1
+        out: List[int] = []
+        off = lo - self.starts[d]
+        while len(out) < self.seq_length:
+            doc = self._doc(d)
+            out += doc[off:off + self.seq_length - len(out)]
+            d, off = d + 1, 0
+        t = torch.tensor(out, dtype=torch.int64)
+        return {"tokens": t, "labels": t.clone(), "prompt_length": 0, "sequence_length": t.numel()}
+
+
+def pretrain_dataset_fn(config, tokenizer, dp_rank: int, dp_size: int, meta_info: Optional[dict] = None) -> dict:
+    """``default_dataset_fn`` for pre-training: token-stream rows (or synthetic rows) with the loss on all tokens."""
+    d, t = config.data, config.training
+    syn = dict(d.synthetic or {})
+    if d.train_data_path:
+        ds = PretrainTokenDataset(IndexedJsonlDataset(d.train_data_path), tokenizer, t.seq_length,
+                                  syn.get("eod_id"), syn.get("key", "tokens"))
+    else:
+        L = syn.get("seq_len", t.seq_length)
+        ds = SyntheticSftDataset(syn.get("num_samples", 1024), L, syn.get("lo", 3), syn.get("hi", 1024), L, seed=d.seed)
+    bs = t.train_gbs // max(dp_size, 1)
+    sampler = ResumableDistributedSampler(len(ds), dp_rank, dp_size, d.shuffle, d.seed)
+    if meta_info and meta_info.get("consumed_batches"):
+        per_epoch = max(sampler.per_rank // bs, 1)
+        sampler.set_epoch(meta_info["consumed_batches"] // per_epoch)
+        sampler.set_start_index((meta_info["consumed_batches"] % per_epoch) * bs)
+    dl = build_dataloader(ds, sampler, bs, sft_collate, d.num_workers)
+    return {"train_dataset": ds, "train_sampler": sampler, "train_dataloader": dl, "eval_dataset": None,
+            "eval_dataloader": None}
+
+
 class SyntheticSftDataset(Dataset):
     """Sequences of ``seq_len`` token ids uniform in [lo, hi); the loss mask covers the last ``loss_tokens`` tokens."""
 
@@ -215,7 +275,8 @@ def default_dataset_fn(config, tokenizer, dp_rank: int, dp_size: int, meta_info:
         ds = (PromptDataset(raw, tokenizer, d.max_prompt_length, d.prompt_key, d.label_key) if rl
               else SftDataset(raw, tokenizer, config.training.seq_length, d.prompt_key, "response"))
     elif rl:
-        ds = SyntheticPromptDataset(syn.get("num_samples", 1024), syn.get("prompt_len", 256), seed=d.seed)
+        ds = SyntheticPromptDataset(syn.get("num_samples", 1024), syn.get("prompt_len", 256), syn.get("lo", 100),
+                                    syn.get("hi", 150000), seed=d.seed)
     else:
         ds = SyntheticSftDataset(syn.get("num_samples", 1024), syn.get("seq_len", 512), syn.get("lo", 3),
                                  syn.get("hi", 1024), syn.get("loss_tokens", 256), seed=d.seed)

@@ -1,7 +1,7 @@
 """Batch inference entry point (``gpatch_v4/entry`` infer / eval mains): loads a checkpoint (torch_dist or HF) into
 the rollout engine and writes one jsonl line per prompt with the generated token ids and log-probs.
 
-    python -m gcore_b200.entry.lm_infer --config rl.yaml +infer.prompts=prompts.jsonl +infer.out=out.jsonl
+    python -m gcore_b200.entry.lm_infer --config rl.yaml +task.infer.prompts=prompts.jsonl +task.infer.out=out.jsonl
 """
 import json
 import sys
@@ -18,8 +18,7 @@ def main(argv=None):
     init_runtime(cfg)
     tr = GrpoTrainer(cfg)
     tr.setup()
-    extra = getattr(cfg, "extra", {}) or {}
-    inf = extra.get("infer", {}) if isinstance(extra, dict) else {}
+    inf = dict((cfg.task or {}).get("infer", {}) or {})
     if cfg.checkpoint.load_ckpt_path:
         from ..checkpoint.torch_dist import load_checkpoint, read_latest_step
         if read_latest_step(cfg.checkpoint.load_ckpt_path) is not None:

@@ -24,8 +24,8 @@ from ..utils.timers import Timers
 
 
 class FinetuneTrainer:
-    def __init__(self, config, model_cfg=None, tokenizer=None):
-        self.cfg, self.tokenizer = config, tokenizer
+    def __init__(self, config, model_cfg=None, tokenizer=None, dataset_fn=None):
+        self.cfg, self.tokenizer, self.dataset_fn = config, tokenizer, dataset_fn
         t = config.training
         self.engine = TrainingEngine(config.policy, config.optimizer, t, None, model_cfg=model_cfg,
                                      total_steps=t.total_training_step)
@@ -55,7 +55,7 @@ class FinetuneTrainer:
             meta = {"consumed_batches": self.engine.loaded_extra_state.get("consumed_batches", self.step),
                     "resume_step": self.step}
             self.log.info(f"resumed from {resume_from} at step {self.step}")
-        fn = default_dataset_fn
+        fn = self.dataset_fn or default_dataset_fn
         if cfg.data.py_path:
             fn = import_from_path(cfg.data.py_path, cfg.data.fn_name or "build_dataset")
         dp_rank, dp_size = ps.get_data_parallel_rank(), ps.get_data_parallel_world_size()

@@ -38,7 +38,8 @@ def synthetic_reward(samples: Sequence[dict], **_) -> torch.Tensor:
 
 class GrpoTrainer:
     def __init__(self, config: RlConfig, model_cfg=None, reward_fn: Optional[Callable] = None,
-                 prompt_source: Optional[Callable] = None, vision_cfg=None, image_token_id: Optional[int] = None):
+                 prompt_source: Optional[Callable] = None, vision_cfg=None, image_token_id: Optional[int] = None,
+                 teacher_model_cfg=None):
         self.cfg = config
         self.timers = Timers()
         self.reward_fn = reward_fn or self._load_reward_fn() or synthetic_reward
@@ -48,6 +49,8 @@ class GrpoTrainer:
                                      total_steps=t.total_ppo_step, vision_cfg=vision_cfg,
                                      image_token_id=image_token_id)
         self.critic: Optional[TrainingEngine] = None
+        self.teacher: Optional[TrainingEngine] = None
+        self.teacher_model_cfg = teacher_model_cfg
         self.engine: Optional[InferEngine] = None
         self.ppo_step = 0
         self.last_metrics: Dict[str, float] = {}
@@ -72,6 +75,16 @@ class GrpoTrainer:
             self.critic = TrainingEngine(cfg.critic, cfg.critic.optimizer, cfg.training, cfg.ppo,
                                          model_cfg=self.policy.model_cfg, role="critic", value_head=True)
             self.critic.setup_model_and_get_optimizer(with_ref=False)
+        if cfg.teacher is not None:
+            # on-policy distillation: a frozen teacher scores the student's rollouts (forward only, no optimizer;
+            # gpatch_v4/trainer on-policy distill trainer + teacher client)
+            cfg.teacher.without_optim = True
+            self.teacher = TrainingEngine(cfg.teacher, cfg.optimizer, cfg.training, cfg.ppo,
+                                          model_cfg=self.teacher_model_cfg or self.policy.model_cfg, role="teacher")
+            self.teacher.setup_model_and_get_optimizer(with_ref=False, seed=cfg.training.seed + 7919)
+            if cfg.teacher.hf_model_path:
+                from ..checkpoint.hf import load_hf
+                load_hf(self.teacher, cfg.teacher.hf_model_path)
         model = self.policy.model
         # with LoRA only the adapted projections differ from the frozen base: the rollout engine then owns copies of
         # those tensors (base + delta, rewritten at every resync) and shares the storage of all the others
@@ -179,6 +192,8 @@ class GrpoTrainer:
             self.policy.compute_log_probs(samples, use_ref=True)
         if self.critic is not None:
             self.critic.compute_values(samples)
+        if self.teacher is not None:
+            self.teacher.compute_log_probs(samples, use_ref=False, with_entropy=False, out_key="teacher_logprobs")
         tm.stop("compute_logps")
         tm.start("generate_ppo_data")
         samples = compute_advantages(samples, cfg.ppo, ps.get_data_parallel_group(), self.advantage_fn)

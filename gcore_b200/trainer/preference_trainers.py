@@ -95,3 +95,54 @@ def attach_teacher_logprobs(teacher: TrainingEngine, samples: List[dict]) -> Lis
     """Scores student samples under the teacher (forward only) -> ``teacher_logprobs`` for ``on_policy_distill``."""
     teacher.compute_log_probs(samples, use_ref=False, with_entropy=False, out_key="teacher_logprobs")
     return samples
+
+
+def _pooled(engine: TrainingEngine, samples: Sequence[dict], grad: bool, pooling: str = "last") -> torch.Tensor:
+    """One unit-norm vector per sequence: the final hidden state of its last token, or the mean over its tokens."""
+    out = []
+    ctx = torch.enable_grad() if grad else torch.no_grad()
+    with ctx, backend_scope(engine.backend):
+        for idx in engine._microbatches(samples, forward_only=not grad):
+            mb = engine._pack(samples, idx)
+            h, _ = engine._hidden(engine.model, mb)
+            if pooling == "mean":
+                n = mb.num_seqs + 1
+                seg = torch.zeros(n, h.shape[1], dtype=torch.float32, device=h.device).index_add(
+                    0, mb.seq_ids.long(), h.float())
+                cnt = torch.zeros(n, dtype=torch.float32, device=h.device).index_add(
+                    0, mb.seq_ids.long(), torch.ones(h.shape[0], device=h.device))
+                vec = seg[:len(idx)] / cnt[:len(idx), None].clamp_min(1.0)
+            else:
+                vec = h[(mb.cu_seqlens[1:len(idx) + 1] - 1).long()].float()
+            out.append((idx, torch.nn.functional.normalize(vec, dim=-1)))
+    res = [None] * len(samples)
+    for idx, v in out:
+        for j, i in enumerate(idx):
+            res[i] = v[j]
+    return torch.stack(res)
+
+
+def embedding_step(engine: TrainingEngine, queries: List[dict], positives: List[dict], temperature: float = 0.05,
+                   pooling: str = "last") -> Dict[str, float]:
+    """Contrastive embedding training (the reference's embedding main): query ``i`` must pick ``positives[i]`` among
+    all positives of the batch (in-batch negatives, symmetric InfoNCE on cosine similarity / ``temperature``)."""
+    assert len(queries) == len(positives)
+    engine.model.train()
+    engine.ddp.zero_grad_buffer()
+    n = len(queries)
+    vec = _pooled(engine, list(queries) + list(positives), True, pooling)
+    sim = vec[:n] @ vec[n:].t() / temperature
+    tgt = torch.arange(n, device=sim.device)
+    loss = 0.5 * (torch.nn.functional.cross_entropy(sim, tgt) + torch.nn.functional.cross_entropy(sim.t(), tgt))
+    loss.backward()
+    engine.ddp.finish_grad_sync(extra_scale=1.0)
+    lr = engine.optimizer.step()
+    engine.step += 1
+    return {"embedding/loss": float(loss.detach()), "embedding/acc": float((sim.argmax(1) == tgt).float().mean()),
+            "lr": lr, "grad_norm": float(engine.optimizer.last_grad_norm)}
+
+
+@torch.no_grad()
+def embed(engine: TrainingEngine, samples: List[dict], pooling: str = "last") -> torch.Tensor:
+    engine.model.eval()
+    return _pooled(engine, samples, False, pooling)

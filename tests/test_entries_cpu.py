@@ -1,0 +1,130 @@
+"""Every entry point runs in-process on a tiny CPU model from a YAML file plus dotted overrides."""
+import json
+
+import pytest
+import torch
+import yaml
+
+TINY = {"model_arch": "tiny_llama", "model_config": {"dtype": "float32"}, "recompute": "none"}
+
+
+def _rl_yaml(tmp_path, **extra):
+    cfg = {"training": {"rollout_gbs": 4, "sampling_repeat_n": 2, "train_gbs": 8, "train_mbs": 4, "total_ppo_step": 2,
+                        "seed": 3},
+           "policy": dict(TINY), "optimizer": {"lr": 1e-3, "lr_decay_style": "constant", "weight_decay": 0.0},
+           "sampler": {"infer_engine_configs": [{"generate_max_tokens": 8, "max_model_len": 40, "kv_block_size": 4,
+                                                  "disable_cuda_graph": True}]},
+           "data": {"max_prompt_length": 16, "synthetic": {"num_samples": 32, "prompt_len": 8, "lo": 3, "hi": 1000}},
+           "report": {"log_dir": str(tmp_path / "logs")}}
+    cfg.update(extra)
+    p = tmp_path / "rl.yaml"
+    p.write_text(yaml.safe_dump(cfg))
+    return str(p)
+
+
+def _sft_yaml(tmp_path):
+    cfg = {"training": {"train_gbs": 4, "train_mbs": 2, "exit_step": 3, "seq_length": 32, "calc_mfu_freq": 0},
+           "policy": dict(TINY), "optimizer": {"lr": 1e-3, "lr_decay_style": "constant"},
+           "data": {"synthetic": {"num_samples": 64, "seq_len": 32, "loss_tokens": 16}},
+           "report": {"log_dir": str(tmp_path / "logs")}}
+    p = tmp_path / "sft.yaml"
+    p.write_text(yaml.safe_dump(cfg))
+    return str(p)
+
+
+def test_rl_and_preference_entries(tmp_path):
+    from gcore_b200.entry import (train_lm_dpo, train_lm_grpo, train_lm_grpo_single_ctrl, train_lm_reward_model)
+    y = _rl_yaml(tmp_path)
+    assert train_lm_grpo.main(["--config", y]) == 0
+    assert train_lm_grpo_single_ctrl.main(["--config", y, "training.single_controller=true"]) == 0
+    small = ["training.train_gbs=4", "training.rollout_gbs=4"]
+    assert train_lm_dpo.main(["--config", y] + small) == 0
+    assert train_lm_reward_model.main(["--config", y] + small) == 0
+
+
+def test_distillation_entry_on_and_off_policy(tmp_path):
+    from gcore_b200.configs.base import ConfigError
+    from gcore_b200.entry import train_lm_distill
+    y = _rl_yaml(tmp_path, teacher=dict(TINY), ppo={"advantage_type": "on_policy_distill", "loss_func": "opd"})
+    hist = train_lm_distill.main(["--config", y])
+    assert len(hist) == 2 and all(m["policy/grad_norm"] > 0 for m in hist)
+    hist = train_lm_distill.main(["--config", y, "+distill_mode=off_policy", "training.total_ppo_step=3"])
+    assert len(hist) == 3 and all(torch.isfinite(torch.tensor(m["lm_loss"])) for m in hist)
+    with pytest.raises(ConfigError):   # the distillation advantage without a teacher is a configuration error
+        train_lm_distill.main(["--config", y, "~teacher"])
+
+
+def test_on_policy_distillation_moves_the_student_towards_the_teacher():
+    """The per-token advantage is the teacher - student log-prob gap: after some steps the student assigns its own
+    samples a likelihood closer to the teacher's."""
+    from test_grpo_cpu import make_cfg
+    from gcore_b200.configs.config import PolicyConfig
+    from gcore_b200.models.config import get_preset
+    from gcore_b200.trainer.grpo_trainer import GrpoTrainer
+    torch.manual_seed(0)
+    cfg = make_cfg()
+    cfg.teacher = PolicyConfig(recompute="none", without_ref=True)
+    cfg.ppo.advantage_type, cfg.ppo.loss_func = "on_policy_distill", "opd"
+    cfg.optimizer.lr = 5e-3
+    # a small vocabulary (the student's samples cover it) and a sharpened teacher (x10 output weights) make the
+    # signal visible within a few dozen steps
+    tr = GrpoTrainer(cfg, model_cfg=get_preset("tiny_llama", dtype="float32", vocab_size=32)).setup()
+    assert tr.teacher is not None and tr.teacher.optimizer is None
+    with torch.no_grad():
+        tr.teacher.model.output_weight().mul_(10.0)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(3, 32, (8,), generator=g).tolist() for _ in range(4)]
+
+    def gap():
+        tot, n = 0.0, 0.0
+        for s in tr.last_samples:
+            m = torch.as_tensor(s["mask"]).float()
+            tot += float(((s["teacher_logprobs"] - s["logprobs"]) * m).sum())
+            n += float(m.sum())
+        return tot / n
+
+    gaps = []
+    for _ in range(28):
+        tr.step(prompts)
+        gaps.append(gap())
+    # the gap is -KL(student || teacher) estimated on the student's samples: it rises towards zero
+    assert sum(gaps[-4:]) / 4 > sum(gaps[:2]) / 2 + 0.8, gaps
+
+
+def test_pretrain_entry_reads_a_token_stream_and_dataloader_verifies(tmp_path):
+    from gcore_b200.data.datasets import IndexedJsonlDataset, PretrainTokenDataset
+    from gcore_b200.entry import train_lm_pretrain, verify_dataloader
+    docs = [[(i * 7 + j) % 500 + 3 for j in range(11 + i % 5)] for i in range(40)]
+    f = tmp_path / "pre.jsonl"
+    f.write_text("\n".join(json.dumps({"tokens": d}) for d in docs) + "\n")
+    ds = PretrainTokenDataset(IndexedJsonlDataset(str(f)), None, 32, eod_id=1)
+    stream = [t for d in docs for t in d + [1]]
+    assert len(ds) == len(stream) // 32
+    for r in (0, 3, len(ds) - 1):       # rows are exact slices of the concatenated documents, loss on every token
+        assert ds[r]["tokens"].tolist() == stream[r * 32:(r + 1) * 32] and ds[r]["prompt_length"] == 0
+    y = _sft_yaml(tmp_path)
+    hist = train_lm_pretrain.main(["--config", y, f"data.train_data_path={f}"])
+    assert len(hist) == 3
+    rep = verify_dataloader.main(["--config", y, "+verify.batches=6", "+verify.dp_size=2"])
+    assert rep["resume_ok"] and rep["disjoint_ok"] and rep["tokens"] == 6 * 2 * 2 * 32
+
+
+def test_eval_infer_embedding_and_vlm_entries(tmp_path):
+    from gcore_b200.entry import lm_eval, lm_infer, train_lm_embedding, train_vlm
+    y = _rl_yaml(tmp_path)
+    out = tmp_path / "metrics.json"
+    m = lm_eval.main(["--config", y, "+task.eval.batches=2", "+task.eval.ks=[1,2]", f"+task.eval.out={out}"])
+    assert m["eval/num_samples"] == 16 and "eval/pass@2" in m and json.load(open(out)) == m
+    gen = tmp_path / "gen.jsonl"
+    assert lm_infer.main(["--config", y, f"+task.infer.out={gen}"]) == 0
+    assert len(open(gen).read().splitlines()) == 8
+    hist = train_lm_embedding.main(["--config", _sft_yaml(tmp_path), "training.exit_step=4", "training.train_gbs=8",
+                                    "training.train_mbs=16"])
+    assert len(hist) == 4 and all(0.0 <= h["embedding/acc"] <= 1.0 for h in hist)
+    vlm = ["policy.image_token_id=5", "+policy.vision_config.patch_size=2", "+policy.vision_config.hidden_size=64",
+           "+policy.vision_config.num_layers=1", "+policy.vision_config.num_heads=2",
+           "+policy.vision_config.ffn_hidden_size=128", "+policy.vision_config.max_grid=8"]
+    hist = train_vlm.main(["--config", y, "training.total_ppo_step=4"] + vlm)
+    assert len(hist) == 4 and hist[-1]["lm_loss"] < hist[0]["lm_loss"]
+    hist = train_vlm.main(["--config", y, "+task.vlm.mode=grpo"] + vlm)
+    assert len(hist) == 2 and "rollout-rewards/mean" in hist[0]

@@ -9,6 +9,8 @@
   ``prompt_token_ids, prompt_lens, gt_label``).
 * ``PackedSftDataset`` - greedy packing of short samples up to ``seq_length`` tokens (pretrain-packed / SFT packing).
 * ``SyntheticSftDataset`` / ``SyntheticPromptDataset`` - the benchmark recipes' random-token data.
+* ``StreamingJsonlDataset`` - lazy multi-shard iterable dataset: DP / worker sharding, shuffle buffer, resume by
+  consumed count.  ``PretrainTokenDataset`` - documents laid end to end and cut into fixed rows.
 """
 from __future__ import annotations
 
@@ -95,6 +97,72 @@ class IndexedJsonlDataset(Dataset):
             self._fh = open(self.path, "rb")
         self._fh.seek(self.offsets[i])
         return json.loads(self._fh.readline())
+
+
+class StreamingJsonlDataset(torch.utils.data.IterableDataset):
+    """Iterable dataset over several jsonl shards, read lazily: record ``k`` of the (epoch-shuffled) shard sequence
+    belongs to data-parallel rank ``k % dp_size`` (and, inside a rank, to loader worker ``(k // dp_size) % workers``),
+    records pass through a seeded shuffle buffer, an optional ``transform`` maps a raw record to a sample, and
+    ``state_dict()`` records how many records this rank has handed out, so a resumed job skips exactly those and
+    continues with the same stream (the reference's iterable dataset with shuffle buffer, DP sharding and
+    consumed-offset resume: ``gdataset/``)."""
+
+    def __init__(self, paths: Sequence[str], dp_rank: int = 0, dp_size: int = 1, shuffle_buffer: int = 0,
+                 seed: int = 0, transform: Optional[Callable[[dict], dict]] = None, epochs: Optional[int] = 1):
+        self.paths, self.rank, self.size = list(paths), dp_rank, dp_size
+        self.buffer, self.seed, self.transform, self.epochs = shuffle_buffer, seed, transform, epochs
+        self.consumed = 0   # records handed out by this rank since the beginning of training
+        self._skip = 0
+
+    def state_dict(self):
+        return {"consumed": self.consumed}
+
+    def load_state_dict(self, sd):
+        self.consumed = self._skip = int(sd["consumed"])
+
+    def _records(self, worker: int, workers: int):
+        epoch = 0
+        while self.epochs is None or epoch < self.epochs:
+            order = list(range(len(self.paths)))
+            if self.buffer:
+                g = torch.Generator().manual_seed(self.seed + epoch)
+                order = torch.randperm(len(order), generator=g).tolist()
+            k = 0
+            for pi in order:
+                with open(self.paths[pi], "rb") as f:
+                    for line in f:
+                        if not line.strip():
+                            continue
+                        mine = k % self.size == self.rank and (k // self.size) % workers == worker
+                        k += 1
+                        if mine:
+                            yield json.loads(line)
+            epoch += 1
+
+    def __iter__(self):
+        info = torch.utils.data.get_worker_info()
+        worker, workers = (info.id, info.num_workers) if info is not None else (0, 1)
+        import random
+        rng = random.Random(self.seed * 1000003 + self.rank * 1009 + worker)
+        buf: List[dict] = []
+
+        def shuffled():
+            for rec in self._records(worker, workers):
+                if not self.buffer:
+                    yield rec
+                    continue
+                buf.append(rec)
+                if len(buf) >= self.buffer:
+                    yield buf.pop(rng.randrange(len(buf)))
+            while buf:
+                yield buf.pop(rng.randrange(len(buf)))
+
+        skip = self._skip // workers + (1 if worker < self._skip % workers else 0)
+        for n, rec in enumerate(shuffled()):
+            if n < skip:      # replay the stream up to the resume point: same buffer state as the interrupted run
+                continue
+            self.consumed += 1
+            yield self.transform(rec) if self.transform is not None else rec
 
 
 def _encode(tokenizer, text_or_ids) -> List[int]:

@@ -365,3 +365,34 @@ def test_task_recipes_load_and_small_packages(tmp_path):
     check_rollout_batches([good])
     with pytest.raises(AssertionError):
         check_rollout_batches([dict(good, mask=torch.tensor([1, 1, 1, 1, 1, 0.0]))])
+
+
+def test_streaming_dataset_shards_shuffles_and_resumes(tmp_path):
+    import json
+    from gcore_b200.data.datasets import StreamingJsonlDataset
+    paths = []
+    for s in range(3):
+        p = tmp_path / f"shard{s}.jsonl"
+        p.write_text("\n".join(json.dumps({"id": s * 100 + i}) for i in range(17 + s)) + "\n")
+        paths.append(str(p))
+    total = 17 + 18 + 19
+    # data-parallel ranks partition the records
+    parts = [[r["id"] for r in StreamingJsonlDataset(paths, rank, 2)] for rank in range(2)]
+    assert sorted(parts[0] + parts[1]) == sorted(s * 100 + i for s in range(3) for i in range(17 + s))
+    assert abs(len(parts[0]) - len(parts[1])) <= 1 and len(parts[0]) + len(parts[1]) == total
+    # the shuffle buffer permutes (seeded, repeatable) without losing records
+    a = [r["id"] for r in StreamingJsonlDataset(paths, 0, 2, shuffle_buffer=8, seed=3)]
+    b = [r["id"] for r in StreamingJsonlDataset(paths, 0, 2, shuffle_buffer=8, seed=3)]
+    assert a == b and sorted(a) != a and len(a) in (total // 2, total - total // 2)
+    # resume: a fresh dataset that loads the consumed count continues with exactly the rest of the stream
+    ds = StreamingJsonlDataset(paths, 1, 2, shuffle_buffer=8, seed=3, transform=lambda r: r["id"])
+    it = iter(ds)
+    head = [next(it) for _ in range(10)]
+    ds2 = StreamingJsonlDataset(paths, 1, 2, shuffle_buffer=8, seed=3, transform=lambda r: r["id"])
+    ds2.load_state_dict(ds.state_dict())
+    full = list(StreamingJsonlDataset(paths, 1, 2, shuffle_buffer=8, seed=3, transform=lambda r: r["id"]))
+    assert head == full[:10] and list(ds2) == full[10:] and ds2.consumed == len(full)
+    # loader workers split a rank's records between them
+    dl = torch.utils.data.DataLoader(StreamingJsonlDataset(paths, 0, 1, transform=lambda r: r["id"]), batch_size=None,
+                                     num_workers=2)
+    assert sorted(int(x) for x in dl) == sorted(s * 100 + i for s in range(3) for i in range(17 + s))

@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import hashlib
 import math
+import zlib
 from typing import Dict, List
 
 import torch
@@ -96,7 +97,7 @@ def apply_lora(model: nn.Module, lora_cfg, seed: int = 0) -> Dict[str, LoRAAdapt
         ad = LoRAAdapter(mod.in_local, _splits_for(name, mod, cfg, mod.tp_size, lora_cfg.type == "canonical_lora"),
                          lora_cfg.rank, lora_cfg.alpha, lora_cfg.dropout, dtype or w.dtype, w.device,
                          lora_cfg.lora_A_init_method, lora_cfg.lora_B_init_method,
-                         seed=(seed + hash(name)) & 0x7FFFFFFF)
+                         seed=(seed + zlib.crc32(name.encode())) & 0x7FFFFFFF)  # crc, not hash(): equal in every process
         # replicated halves must be identical across the TP group
         ad.lora_A.tp_mode = "row" if mod.mode == "row" else "none"
         for b in ad.lora_B:

@@ -184,3 +184,38 @@ def test_mla_moe_model_serves_from_latent_cache():
             r = reqs[i * 2 + j]
             assert r.out_tokens == ref_t, (i, j, r.out_tokens, ref_t)
             assert max(abs(x - y) for x, y in zip(r.out_logprobs, ref_lp)) < 1e-3
+
+
+def test_mla_rollout_with_lora_adapters_on_the_latent_projections():
+    """LoRA on the q / kv up-projections and the output projection of an MLA model (non-zero B): the decoder's
+    absorbed attention folds the adapter of the kv up-projection into its matrices and must still equal the model."""
+    from gcore_b200.configs.config import LoRAConfig
+    from gcore_b200.models.config import ModelConfig
+    from gcore_b200.models.lora import apply_lora
+    cfg = ModelConfig(arch="deepseek_v3", num_layers=2, hidden_size=64, num_attention_heads=4, num_kv_heads=4,
+                      ffn_hidden_size=128, vocab_size=256, use_mla=True, q_lora_rank=32, kv_lora_rank=32,
+                      qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16, head_dim=24, rope_interleaved=True,
+                      dtype="float32")
+    torch.manual_seed(0)
+    model = GPTModel(cfg, recompute="none")
+    ads = apply_lora(model, LoRAConfig(rank=4, alpha=8, type="lora", lora_B_init_method="normal",
+                                       target_modules=["linear_q_up_proj", "linear_kv_up_proj", "linear_proj"]), seed=1)
+    assert len(ads) == 6
+    with torch.no_grad():
+        for a in ads.values():
+            for b in a.lora_B:
+                b.mul_(20.0)   # make the adapters matter
+    model.eval()
+    eng = InferEngine(cfg, RolloutWeights.from_model(model), max_running_requests=4, max_model_len=48,
+                      kv_block_size=4, sync_interval=3, use_cuda_graph=False)
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(3, 256, (l,), generator=g).tolist() for l in (6, 9)]
+    reqs = eng.generate(prompts, SamplingParams(max_new_tokens=6, greedy=True))
+    for p, r in zip(prompts, reqs):
+        ref_t, ref_lp = naive_greedy(model, p, 6)
+        assert r.out_tokens == ref_t and max(abs(x - y) for x, y in zip(r.out_logprobs, ref_lp)) < 1e-3
+    # and the adapters do change the outputs
+    for m in model.modules():
+        if getattr(m, "lora", None) is not None:
+            m.lora = None
+    assert naive_greedy(model, prompts[0], 6)[1] != [round(x, 9) for x in reqs[0].out_logprobs]

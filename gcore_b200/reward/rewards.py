@@ -145,3 +145,69 @@ def build_reward(cfg, tokenizer=None, rm_engines: Optional[Dict[str, object]] = 
         return MixReward(rms)
     parts = ([("rule", rule, 1.0)] if rule is not None else []) + rms
     return MixReward(parts)
+
+
+class ExternalAsyncReward:
+    """Base class of rewards computed by an outside service (a sandbox, a judge behind HTTP, a verifier cluster):
+    ``score_one(sample) -> float | (float, dict)`` is the only method a subclass has to write.  Samples are submitted
+    in micro-batches to a thread pool as soon as they exist (``submit``), results stream back while the caller does
+    other work, and ``__call__`` / ``collect`` hands them out in submission order.  A request that raises or exceeds
+    ``timeout_s`` is retried ``retries`` times and then gets ``fallback`` (the reference's external async reward
+    base with per-micro-batch streaming: gpatch_v4/reward/base_external_reward.py)."""
+
+    def __init__(self, max_workers: int = 8, micro_batch: int = 8, timeout_s: float = 60.0, retries: int = 1,
+                 fallback: float = 0.0):
+        from concurrent.futures import ThreadPoolExecutor
+        self.pool = ThreadPoolExecutor(max_workers=max_workers)
+        self.micro_batch, self.timeout_s, self.retries, self.fallback = micro_batch, timeout_s, retries, fallback
+        self._pending: List[tuple] = []
+        self.stats = {"requests": 0, "failures": 0, "retries": 0}
+
+    def score_one(self, sample: dict):
+        raise NotImplementedError
+
+    def score_batch(self, samples: List[dict]) -> List:
+        """One micro-batch; override when the service takes batches."""
+        return [self.score_one(s) for s in samples]
+
+    def _guarded(self, samples: List[dict]) -> List:
+        for attempt in range(self.retries + 1):
+            try:
+                return self.score_batch(samples)
+            except Exception:  # noqa: BLE001 - a failing service must not kill the training step
+                self.stats["retries" if attempt < self.retries else "failures"] += 1
+        return [self.fallback] * len(samples)
+
+    def submit(self, samples: List[dict]) -> None:
+        for i in range(0, len(samples), self.micro_batch):
+            mb = samples[i:i + self.micro_batch]
+            self.stats["requests"] += 1
+            self._pending.append((mb, self.pool.submit(self._guarded, mb)))
+
+    def collect(self):
+        """Rewards of everything submitted so far, in submission order."""
+        from concurrent.futures import TimeoutError as FutTimeout
+        rewards, extra = [], {}
+        for mb, fut in self._pending:
+            try:
+                res = fut.result(timeout=self.timeout_s)
+            except FutTimeout:
+                self.stats["failures"] += 1
+                res = [self.fallback] * len(mb)
+            for s, r in zip(mb, res):
+                if isinstance(r, tuple):
+                    r, info = r
+                    for k, v in info.items():
+                        extra.setdefault(k, []).append(float(v))
+                rewards.append(float(r))
+        self._pending = []
+        n = len(rewards)
+        return torch.tensor(rewards, dtype=torch.float32), None, {k: torch.tensor(v) for k, v in extra.items()
+                                                                  if len(v) == n}
+
+    def __call__(self, samples):
+        self.submit(list(samples))
+        return self.collect()
+
+    def close(self):
+        self.pool.shutdown(wait=False, cancel_futures=True)

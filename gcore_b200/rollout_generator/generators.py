@@ -134,3 +134,113 @@ class StaleRolloutQueue:
 
     def pop(self) -> List[dict]:
         return self.q.popleft()
+
+
+# ------------------------------------------------------------------------------------------------ record / replay
+def _to_jsonable(s: dict) -> dict:
+    out = {}
+    for k, v in s.items():
+        if isinstance(v, torch.Tensor):
+            out[k] = {"__tensor__": v.tolist(), "dtype": str(v.dtype).replace("torch.", "")}
+        elif isinstance(v, tuple):
+            out[k] = {"__tuple__": list(v)}
+        elif isinstance(v, (int, float, str, bool, list, dict)) or v is None:
+            out[k] = v
+    return out
+
+
+def _from_jsonable(d: dict) -> dict:
+    out = {}
+    for k, v in d.items():
+        if isinstance(v, dict) and "__tensor__" in v:
+            out[k] = torch.tensor(v["__tensor__"], dtype=getattr(torch, v["dtype"]))
+        elif isinstance(v, dict) and "__tuple__" in v:
+            out[k] = tuple(v["__tuple__"])
+        else:
+            out[k] = v
+    return out
+
+
+class RecordingGenerator(BaseRolloutGenerator):
+    """Wraps another generator and appends every batch it returns to a jsonl file (one line per step)."""
+
+    def __init__(self, trainer, config, inner: BaseRolloutGenerator, path: str):
+        super().__init__(trainer, config)
+        self.inner, self.path = inner, path
+
+    def __call__(self, prompt_iter, step: int) -> List[dict]:
+        import json
+        samples = self.inner(prompt_iter, step)
+        with open(self.path, "a") as f:
+            f.write(json.dumps({"step": step, "samples": [_to_jsonable(s) for s in samples]}) + "\n")
+        return samples
+
+    def state_dict(self):
+        return self.inner.state_dict()
+
+    def load_state_dict(self, sd):
+        self.inner.load_state_dict(sd)
+
+
+class ReplayRolloutGenerator(BaseRolloutGenerator):
+    """Feeds recorded rollouts (tokens, masks, rollout log-probs, rewards) back to the trainer instead of sampling:
+    reproduces a run's training phases without the rollout engine, or trains on rollouts made elsewhere
+    (the reference's replay generator under ``gpatch_v4/rollout_generator/``).  Resumes at the recorded position."""
+
+    def __init__(self, trainer, config, path: str, loop: bool = False):
+        super().__init__(trainer, config)
+        self.path, self.loop, self.pos = path, loop, 0
+        from ..data.datasets import IndexedJsonlDataset
+        self.rows = IndexedJsonlDataset(path)
+
+    def __call__(self, prompt_iter, step: int) -> List[dict]:
+        if self.pos >= len(self.rows):
+            if not self.loop:
+                raise StopIteration(f"replay file {self.path} has {len(self.rows)} steps")
+            self.pos = 0
+        row = self.rows[self.pos]
+        self.pos += 1
+        return [_from_jsonable(s) for s in row["samples"]]
+
+    def state_dict(self):
+        return {"pos": self.pos}
+
+    def load_state_dict(self, sd):
+        self.pos = int(sd.get("pos", 0))
+
+
+class ExternalRolloutGenerator(BaseRolloutGenerator):
+    """Rollouts come from a user function ``fn(prompts, step, trainer) -> samples`` (another serving stack, a tool
+    loop, an agentic environment); the samples are scored and filtered like the engine's own
+    (``policy.rollout_gen_py_path`` / ``policy.rollout_gen_cls`` name the function)."""
+
+    def __init__(self, trainer, config, fn: Optional[Callable] = None):
+        super().__init__(trainer, config)
+        p = config.policy
+        self.fn = fn or import_from_path(p.rollout_gen_py_path, p.rollout_gen_cls or "generate")
+
+    def __call__(self, prompt_iter, step: int) -> List[dict]:
+        t = self.cfg.training
+        samples = self.fn(next(prompt_iter), step, self.tr)
+        if samples and "rewards" not in samples[0]:
+            samples = self.tr.score(samples)
+        return keep_n_of_group(samples, t.sampling_repeat_n, t.sampling_keep_n, t.sampling_keeping_strategy)
+
+
+def build_generator(trainer, config) -> BaseRolloutGenerator:
+    """``policy.rollout_gen_type``: base | dynamic | replay | external; ``training.dynamic_sampling.enable`` selects
+    dynamic as before.  ``task.rollout.{replay_path, record_path, replay_loop}`` configure replay and recording."""
+    kind = config.policy.rollout_gen_type or "base"
+    opt = dict((config.task or {}).get("rollout", {}) or {})
+    if kind == "replay":
+        gen: BaseRolloutGenerator = ReplayRolloutGenerator(trainer, config, opt["replay_path"],
+                                                           bool(opt.get("replay_loop", False)))
+    elif kind == "external":
+        gen = ExternalRolloutGenerator(trainer, config)
+    elif kind == "dynamic" or config.training.dynamic_sampling.enable:
+        gen = DynamicSamplingGenerator(trainer, config)
+    else:
+        gen = BaseRolloutGenerator(trainer, config)
+    if opt.get("record_path"):
+        gen = RecordingGenerator(trainer, config, gen, opt["record_path"])
+    return gen

@@ -16,7 +16,7 @@ from ..core import parallel_state as ps
 from ..core.advantage import compute_advantages
 from ..data.datasets import default_dataset_fn
 from ..orches.failure import FaultInjector, Heartbeat
-from ..rollout_generator.generators import BaseRolloutGenerator, DynamicSamplingGenerator, StaleRolloutQueue
+from ..rollout_generator.generators import StaleRolloutQueue, build_generator
 from ..utils.logging_utils import get_logger
 from ..utils.report import Reporter
 from .grpo_trainer import GrpoTrainer
@@ -55,8 +55,7 @@ class RlLoop:
             fn = import_from_path(cfg.data.py_path, cfg.data.fn_name or "build_dataset")
         self.data = fn(cfg, self.tokenizer, ps.get_data_parallel_rank(), ps.get_data_parallel_world_size(), meta)
         self.prompt_iter = self._prompts()
-        gen_cls = DynamicSamplingGenerator if cfg.training.dynamic_sampling.enable else BaseRolloutGenerator
-        self.generator = gen_cls(tr, cfg)
+        self.generator = build_generator(tr, cfg)
         if meta and "rollout_generator" in tr.policy.loaded_extra_state:
             self.generator.load_state_dict(tr.policy.loaded_extra_state["rollout_generator"])
         self.queue = StaleRolloutQueue(cfg.training.rollout_max_staleness)

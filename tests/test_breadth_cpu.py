@@ -396,3 +396,39 @@ def test_streaming_dataset_shards_shuffles_and_resumes(tmp_path):
     dl = torch.utils.data.DataLoader(StreamingJsonlDataset(paths, 0, 1, transform=lambda r: r["id"]), batch_size=None,
                                      num_workers=2)
     assert sorted(int(x) for x in dl) == sorted(s * 100 + i for s in range(3) for i in range(17 + s))
+
+
+def test_external_async_reward_streams_retries_and_falls_back():
+    import threading
+    import time
+    from gcore_b200.reward.rewards import ExternalAsyncReward
+
+    class Judge(ExternalAsyncReward):
+        def __init__(self):
+            super().__init__(max_workers=4, micro_batch=2, timeout_s=5.0, retries=1, fallback=-1.0)
+            self.seen, self.lock, self.flaky = [], threading.Lock(), set()
+
+        def score_one(self, s):
+            with self.lock:
+                self.seen.append(s["id"])
+            time.sleep(0.02)
+            if s["id"] == 3 and s["id"] not in self.flaky:   # fails once, succeeds on the retry
+                self.flaky.add(3)
+                raise RuntimeError("service hiccup")
+            if s["id"] == 6:
+                raise RuntimeError("always down")
+            return float(s["id"]) * 0.5, {"latency": 0.02}
+
+    j = Judge()
+    first, second = [{"id": i} for i in range(4)], [{"id": i} for i in range(4, 8)]
+    j.submit(first)            # scoring starts while the caller produces the next samples
+    time.sleep(0.05)
+    assert len(j.seen) > 0
+    j.submit(second)
+    r, per_tok, extra = j.collect()
+    exp = [0.0, 0.5, 1.0, 1.5, 2.0, 2.5, -1.0, -1.0]   # ids 6 and 7 share the failing micro-batch: fallback for both
+    assert r.tolist() == exp and per_tok is None
+    assert j.stats["retries"] >= 1 and j.stats["failures"] == 1 and j.stats["requests"] == 4
+    r2, _, _ = j([{"id": 1}, {"id": 2}])
+    assert r2.tolist() == [0.5, 1.0]
+    j.close()

@@ -432,3 +432,40 @@ def test_external_async_reward_streams_retries_and_falls_back():
     r2, _, _ = j([{"id": 1}, {"id": 2}])
     assert r2.tolist() == [0.5, 1.0]
     j.close()
+
+
+def test_reward_redistribution_by_lcs_alignment():
+    import random
+    from gcore_b200.utils.reward_redist import (_lcs_python, lcs_match, redistribute_rewards,
+                                                redistribute_rewards_batch)
+    rng = random.Random(0)
+    # native Myers alignment = quadratic oracle (same LCS length, valid strictly increasing matches)
+    for trial in range(40):
+        a = [rng.randrange(12) for _ in range(rng.randrange(0, 60))]
+        b = list(a)
+        for _ in range(rng.randrange(0, 8)):       # a few edits, like tokenizer drift
+            if b and rng.random() < 0.5:
+                del b[rng.randrange(len(b))]
+            else:
+                b.insert(rng.randrange(len(b) + 1), rng.randrange(12))
+        ia, ib = lcs_match(a, b)
+        ref = _lcs_python(a, b)
+        assert len(ia) == len(ref[0])
+        assert all(a[i] == b[j] for i, j in zip(ia, ib))
+        assert all(x < y for x, y in zip(ia, ia[1:])) and all(x < y for x, y in zip(ib, ib[1:]))
+    assert lcs_match([1, 2, 3, 4], [9, 8, 7, 6], max_d=2) is None
+    # identical sequences: rewards pass through
+    r = redistribute_rewards([5, 6, 7], [5, 6, 7], [0.1, 0.2, 0.3])
+    assert torch.allclose(r, torch.tensor([0.1, 0.2, 0.3]))
+    # one original token re-encoded as two: it gets the mean of their rewards; neighbours keep theirs
+    r = redistribute_rewards([5, 60, 7], [5, 61, 62, 7], [1.0, 2.0, 4.0, 8.0])
+    assert torch.allclose(r, torch.tensor([1.0, 3.0, 8.0]))
+    # two original tokens merged into nothing on the other side: the gap takes the mean of its neighbours
+    r = redistribute_rewards([5, 60, 61, 7], [5, 7], [1.0, 3.0])
+    assert torch.allclose(r, torch.tensor([1.0, 2.0, 2.0, 3.0]))
+    # python fallback gives the same answer; the batch version equals the loop
+    a, b = [3, 4, 5, 9, 9, 6], [3, 5, 8, 6]
+    rw = [0.5, 1.0, 2.0, 4.0]
+    assert torch.allclose(redistribute_rewards(a, b, rw), redistribute_rewards(a, b, rw, native=False))
+    outs = redistribute_rewards_batch([a, [1, 2]], [b, [1, 2]], [rw, [0.0, 1.0]], workers=2)
+    assert torch.allclose(outs[0], redistribute_rewards(a, b, rw)) and outs[1].tolist() == [0.0, 1.0]

@@ -1,0 +1,81 @@
+"""Data converters (the reference's data-conversion tools): bring text / chat records into the indexed-jsonl formats
+the datasets read, tokenising once offline.
+
+    python -m gcore_b200.tools.data_convert sft      --src chat.jsonl --dst sft.jsonl --tokenizer tok_dir
+    python -m gcore_b200.tools.data_convert prompts  --src q.jsonl    --dst prompts.jsonl --tokenizer tok_dir
+    python -m gcore_b200.tools.data_convert pretrain --src text.jsonl --dst tokens.jsonl --tokenizer tok_dir
+
+``sft``: ``{"messages": [{"role", "content"}, ...]}`` or ``{"prompt", "response"}`` -> ``{"prompt": ids, "response":
+ids}``; ``prompts``: ``{"prompt" | "question", "answer"}`` -> ``{"prompt": ids, "answer": ...}``; ``pretrain``:
+``{"text"}`` -> ``{"tokens": ids}``.  Without ``--tokenizer`` a byte-level encoding (id = byte + 3) is used, which
+keeps the tools usable in tests and for smoke runs.  The offset index (``.idx``) is written next to the output."""
+from __future__ import annotations
+
+import argparse
+import json
+from typing import Callable, List
+
+
+def byte_tokenizer(text: str) -> List[int]:
+    return [b + 3 for b in text.encode("utf-8")]
+
+
+def load_tokenizer(path: str | None) -> Callable[[str], List[int]]:
+    if not path:
+        return byte_tokenizer
+    from transformers import AutoTokenizer
+    tok = AutoTokenizer.from_pretrained(path)
+    return lambda s: tok.encode(s, add_special_tokens=False)
+
+
+def _chat_to_pair(rec: dict) -> tuple:
+    if "messages" in rec:
+        msgs = rec["messages"]
+        last = max(i for i, m in enumerate(msgs) if m["role"] == "assistant")
+        prompt = "".join(f"<|{m['role']}|>\n{m['content']}\n" for m in msgs[:last]) + "<|assistant|>\n"
+        return prompt, msgs[last]["content"]
+    return rec["prompt"], rec["response"]
+
+
+def convert(kind: str, src: str, dst: str, encode: Callable[[str], List[int]], max_len: int | None = None) -> int:
+    n = 0
+    with open(src) as fi, open(dst, "w") as fo:
+        for line in fi:
+            if not line.strip():
+                continue
+            rec = json.loads(line)
+            if kind == "sft":
+                p, r = _chat_to_pair(rec)
+                out = {"prompt": encode(p), "response": encode(r)}
+                if max_len and len(out["prompt"]) + len(out["response"]) > max_len:
+                    continue
+            elif kind == "prompts":
+                out = {"prompt": encode(rec.get("prompt") or rec["question"]), "answer": rec.get("answer")}
+                if max_len and len(out["prompt"]) > max_len:
+                    continue
+            elif kind == "pretrain":
+                out = {"tokens": encode(rec["text"])}
+            else:
+                raise ValueError(f"unknown conversion {kind}")
+            fo.write(json.dumps(out) + "\n")
+            n += 1
+    from ..data.datasets import IndexedJsonlDataset
+    IndexedJsonlDataset.build_index(dst, dst + ".idx")
+    return n
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kind", choices=["sft", "prompts", "pretrain"])
+    ap.add_argument("--src", required=True)
+    ap.add_argument("--dst", required=True)
+    ap.add_argument("--tokenizer", default=None)
+    ap.add_argument("--max-len", type=int, default=None)
+    a = ap.parse_args(argv)
+    n = convert(a.kind, a.src, a.dst, load_tokenizer(a.tokenizer), a.max_len)
+    print(f"wrote {n} records to {a.dst}")
+    return n
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,45 @@
+"""Handing a tensor to another process on the same machine without copying it: ``export_handle`` turns a tensor into
+a small picklable handle (CUDA IPC memory handle for device tensors, shared-memory file descriptor for host tensors),
+``import_handle`` maps the same storage in the receiving process.  Used when a weight or KV buffer has to be visible
+to a separate serving process; inside one job the trainer and the rollout engine share storage directly
+(the reference's ``gpatch_v4/utils/tensor_ipc.py`` in front of its engines' IPC weight update)."""
+from __future__ import annotations
+
+import pickle
+from typing import Any, Tuple
+
+import torch
+from torch.multiprocessing.reductions import reduce_tensor
+
+
+def export_handle(t: torch.Tensor) -> bytes:
+    """The tensor must stay alive in the exporting process for as long as importers use it."""
+    if not t.is_cuda and not t.is_shared():
+        t.share_memory_()
+    fn, args = reduce_tensor(t)
+    from multiprocessing.reduction import ForkingPickler
+    import io
+    buf = io.BytesIO()
+    ForkingPickler(buf, pickle.HIGHEST_PROTOCOL).dump((fn, args))
+    return buf.getvalue()
+
+
+def import_handle(handle: bytes) -> torch.Tensor:
+    fn, args = pickle.loads(handle)
+    return fn(*args)
+
+
+def export_state(tensors: dict) -> dict:
+    return {k: export_handle(v) for k, v in tensors.items()}
+
+
+def import_state(handles: dict) -> dict:
+    return {k: import_handle(v) for k, v in handles.items()}
+
+
+def _child(conn):   # used by the self-test and as a usage example
+    h = conn.recv()
+    t = import_handle(h)
+    t.add_(1)
+    conn.send(float(t.sum()))
+    conn.close()

@@ -469,3 +469,64 @@ def test_reward_redistribution_by_lcs_alignment():
     assert torch.allclose(redistribute_rewards(a, b, rw), redistribute_rewards(a, b, rw, native=False))
     outs = redistribute_rewards_batch([a, [1, 2]], [b, [1, 2]], [rw, [0.0, 1.0]], workers=2)
     assert torch.allclose(outs[0], redistribute_rewards(a, b, rw)) and outs[1].tolist() == [0.0, 1.0]
+
+
+def test_moe_load_recorder_and_tensor_ipc(tmp_path):
+    import json
+    from gcore_b200.models.config import ModelConfig
+    from gcore_b200.models.gpt import GPTModel
+    from gcore_b200.utils.debug_moe import MoeLoadRecorder
+    cfg = ModelConfig(arch="qwen3_moe", num_layers=2, hidden_size=64, num_attention_heads=2, num_kv_heads=2,
+                      ffn_hidden_size=128, vocab_size=128, num_experts=4, moe_top_k=2, moe_ffn_hidden_size=32,
+                      dtype="float32")
+    torch.manual_seed(0)
+    model = GPTModel(cfg, recompute="none")
+    rec = MoeLoadRecorder(model)
+    t = torch.randint(3, 128, (10,))
+    with torch.no_grad():
+        model(t, torch.arange(10, dtype=torch.int32), torch.tensor([0, 10], dtype=torch.int32), 10)
+    s = rec.summary()
+    assert sorted(s) == [0, 1] and all(v["tokens"] == 20 and sum(v["counts"]) == 20 for v in s.values())
+    assert all(0 < v["entropy_frac"] <= 1.0 and v["max_over_mean"] >= 1.0 for v in s.values())
+    rec.dump(str(tmp_path / "moe.jsonl"), step=3)
+    row = json.loads(open(tmp_path / "moe.jsonl").read())
+    assert row["step"] == 3 and set(row["layers"]) == {"0", "1"} and rec.summary() == {}
+    rec.close()
+    # a host tensor handed to another process by handle: the child's in-place update is visible here
+    import torch.multiprocessing as mp
+    from gcore_b200.utils.tensor_ipc import _child, export_handle
+    x = torch.arange(6, dtype=torch.float32)
+    ctx = mp.get_context("spawn")
+    a, b = ctx.Pipe()
+    p = ctx.Process(target=_child, args=(b,))
+    p.start()
+    a.send(export_handle(x))
+    assert a.recv() == 21.0
+    p.join(30)
+    assert x.tolist() == [1.0, 2.0, 3.0, 4.0, 5.0, 6.0]
+
+
+def test_data_convert_tools(tmp_path):
+    import json
+    from gcore_b200.data.datasets import IndexedJsonlDataset, PretrainTokenDataset, SftDataset
+    from gcore_b200.tools import data_convert, gpu_check
+    chat = tmp_path / "chat.jsonl"
+    chat.write_text(json.dumps({"messages": [{"role": "user", "content": "2+2?"},
+                                             {"role": "assistant", "content": "4"}]}) + "\n" +
+                    json.dumps({"prompt": "hi", "response": "there"}) + "\n")
+    assert data_convert.main(["sft", "--src", str(chat), "--dst", str(tmp_path / "sft.jsonl")]) == 2
+    ds = IndexedJsonlDataset(str(tmp_path / "sft.jsonl"))
+    assert ds[1]["prompt"] == [ord(c) + 3 for c in "hi"] and bytes(t - 3 for t in ds[0]["response"]) == b"4"
+    item = SftDataset(ds, None, 64, "prompt", "response")[0]
+    assert item["prompt_length"] == len(ds[0]["prompt"]) and item["sequence_length"] == len(ds[0]["prompt"]) + 1
+    text = tmp_path / "text.jsonl"
+    text.write_text("\n".join(json.dumps({"text": "abcdefgh" * (i + 1)}) for i in range(5)) + "\n")
+    assert data_convert.main(["pretrain", "--src", str(text), "--dst", str(tmp_path / "tok.jsonl")]) == 5
+    rows = PretrainTokenDataset(IndexedJsonlDataset(str(tmp_path / "tok.jsonl")), None, 16)
+    assert len(rows) == (8 * 15) // 16 and rows[0]["tokens"].tolist() == [ord(c) + 3 for c in "abcdefgh" * 2]
+    q = tmp_path / "q.jsonl"
+    q.write_text(json.dumps({"question": "1+1", "answer": "2"}) + "\n")
+    assert data_convert.main(["prompts", "--src", str(q), "--dst", str(tmp_path / "p.jsonl")]) == 1
+    assert IndexedJsonlDataset(str(tmp_path / "p.jsonl"))[0]["answer"] == "2"
+    rep = gpu_check.main([])       # no GPU here: the report says so instead of failing
+    assert rep["cuda_available"] is False and rep["ok"] is False

@@ -388,8 +388,24 @@ class PpoConfig(MappingMixin):
     clip_cov_ratio: float = 0.0
     kl_cov_ratio: float = 0.0
     kl_cov_coef: float = 1.0
+    # steer: token weights in [steer_token_weight_min, 1] from the estimated entropy change, on top of a base loss
+    steer_token_weight_min: float = 0.8
+    steer_policy_method: str = "grpo"
+    # fipo: advantages weighted by exp(discounted future log-ratio), gamma = 2^(-1/decay_rate)
+    fipo_decay_rate: float = 32.0
+    fipo_chunk_size: int = 512
+    fipo_clip_ratio: float = 0.2
+    fipo_clip_high_only: bool = False
+    fipo_safety_thresh: float = 3.0
 
     def __post_init__(self):
+        if self.loss_func == "steer":
+            if self.skip_prev_logps:
+                raise ConfigError("loss_func=steer needs the previous log-probs (skip_prev_logps=false)")
+            if not 0.0 < self.steer_token_weight_min <= 1.0:
+                raise ConfigError("steer_token_weight_min must be in (0, 1]")
+            if self.steer_policy_method not in ("grpo", "cispo", "gspo", "sapo"):
+                raise ConfigError(f"steer_policy_method must be grpo|cispo|gspo|sapo, got {self.steer_policy_method}")
         if self.advantage_type not in ("grpo", "gdpo", "ppo", "reinforce", "on_policy_distill", "g_opd",
                                        "identity", "custom"):
             raise ConfigError(f"unknown advantage_type {self.advantage_type}")

@@ -450,7 +450,7 @@ class TrainingEngine:
             keys.append("ref_logprobs")
         if has_roll or cfg.loss_func == "vespo":
             keys.append("rollout_log_probs")
-        want_ent = cfg.ppo_entropy_bonus != 0
+        want_ent = cfg.ppo_entropy_bonus != 0 or cfg.loss_func == "steer"
         fast = (cfg.loss_func == "grpo" and not has_roll and not want_ent and cfg.kl_estimator == "k3"
                 and cfg.loss_func_py_path is None)
         loss_fn = None if fast else self._resolve_loss()

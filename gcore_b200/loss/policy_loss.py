@@ -11,6 +11,7 @@ sequence-level variants (packing-safe, unlike a ``[B, S]`` reduction over the la
 """
 from __future__ import annotations
 
+import math
 from dataclasses import dataclass, field
 from typing import Callable, Dict, Optional
 
@@ -174,6 +175,95 @@ def vespo_loss(cfg, li: LossInput) -> LossOutput:
         ratio = tlr.exp()
     tl = -phi[li.seq_ids.long()] * li.advantages * li.logp
     return LossOutput(tl, ratio, {"vespo/phi_mean": torch.stack([phi.sum(), phi.new_tensor(float(phi.numel()))])})
+
+
+@register_loss("steer")
+def steer_loss(cfg, li: LossInput) -> LossOutput:
+    """A base surrogate (``steer_policy_method``) whose tokens are down-weighted by how much their update is estimated
+    to move the policy entropy: ``metric = |A / p_old * p (1 - p) * (ln p + H)|``, weight ``exp(-k * metric)`` clipped
+    to ``[w_min, 1]`` with ``k`` chosen so that the largest metric of the batch gets ``w_min``
+    (gpatch_v4/training_backend/loss/ppo_loss.py:253-290, 872)."""
+    base = get_loss(cfg.steer_policy_method)(cfg, li)
+    H = li.old_entropy if li.old_entropy is not None else li.entropy
+    if H is None:
+        raise ValueError("loss_func=steer needs per-token entropies (they are computed when it is selected)")
+    w_min = float(cfg.steer_token_weight_min)
+    with torch.no_grad():
+        old = li.logp.detach() if li.old_logp is None else li.old_logp
+        p = li.logp.detach().float().exp().clamp(1e-8, 1.0 - 1e-8)
+        metric = (li.advantages.float() / old.float().exp().clamp(1e-8, 1.0) * p * (1.0 - p) *
+                  (p.log() + H.detach().float())).abs()
+        valid = li.mask > 0
+        top = metric[valid].max() if bool(valid.any()) else metric.new_zeros(())
+        k = -math.log(w_min) / torch.clamp(top, min=0.02) if w_min < 1.0 else metric.new_zeros(())
+        w = torch.exp(-k * metric).clamp(w_min, 1.0) * li.mask
+    m = dict(base.metrics)
+    m["steer/token_weight_mean"] = torch.stack([w.sum(), li.mask.sum()])
+    m["steer/token_weight_lt_0_95_frac"] = _frac((w < 0.95) & valid, li.mask)
+    return LossOutput(base.token_loss * w, base.ratios, m)
+
+
+def discounted_future_sum(x: torch.Tensor, seq_ids: torch.Tensor, gamma: float, chunk: int = 512) -> torch.Tensor:
+    """``out[t] = sum_{j >= t, same sequence} gamma^(j - t) x[j]`` over packed sequences.  Every sequence is walked
+    from its end in chunks; inside a chunk the sum is a reversed cumulative sum of ``x * gamma^k`` divided by
+    ``gamma^k`` in fp64 (exact for chunk lengths whose ``gamma^-k`` stays finite), the tail enters as a carry."""
+    out = torch.zeros_like(x, dtype=torch.float64)
+    ids = seq_ids.long()
+    T = x.numel()
+    if T == 0:
+        return out.to(x.dtype)
+    change = torch.nonzero(ids[1:] != ids[:-1]).flatten() + 1
+    bounds = [0] + change.tolist() + [T]
+    xd = x.double()
+    for s0, s1 in zip(bounds[:-1], bounds[1:]):
+        carry = xd.new_zeros(())
+        for b in range(s1, s0, -chunk):
+            a = max(s0, b - chunk)
+            k = torch.arange(b - a, device=x.device, dtype=torch.float64)
+            w = torch.pow(xd.new_tensor(gamma), k)
+            local = torch.flip(torch.cumsum(torch.flip(xd[a:b] * w, [0]), 0), [0]) / w
+            out[a:b] = local + carry * torch.pow(xd.new_tensor(gamma), (b - a) - k)
+            carry = out[a]
+    return out.to(x.dtype)
+
+
+@register_loss("fipo")
+def fipo_loss(cfg, li: LossInput) -> LossOutput:
+    """Clipped surrogate whose advantages are scaled by an influence weight: the exponential of the discounted sum of
+    the later tokens' log-ratios (``gamma = 2^(-1 / fipo_decay_rate)``), clipped to ``1 +- fipo_clip_ratio`` (or
+    ``[1, 1 + ratio]``); tokens with a negative advantage and a ratio above ``fipo_safety_thresh`` keep at most weight 1;
+    sequences with more than one dual-clipped token are dropped
+    (gpatch_v4/training_backend/loss_factory.py:1966-2240)."""
+    old = li.logp.detach() if li.old_logp is None else li.old_logp
+    ratio = _token_ratio(cfg, li.logp, old)
+    with torch.no_grad():
+        gamma = 2.0 ** (-1.0 / float(cfg.fipo_decay_rate))
+        fut = discounted_future_sum((li.logp.detach() - old) * li.mask, li.seq_ids, gamma, int(cfg.fipo_chunk_size))
+        hi = 1.0 + cfg.fipo_clip_ratio
+        lo = 1.0 if cfg.fipo_clip_high_only else 1.0 - cfg.fipo_clip_ratio
+        raw = torch.exp(fut.clamp(max=20.0))
+        iw = raw.clamp(lo, hi)
+        risky = (li.advantages < 0) & (ratio.detach() > cfg.fipo_safety_thresh)
+        iw = torch.where(risky, iw.clamp(0.8, 1.0), iw)
+    adv = li.advantages * iw
+    l1 = -adv * ratio
+    l2 = -adv * ratio.clamp(1 - cfg.clip_low, 1 + cfg.clip_high)
+    clip_max = torch.maximum(l1, l2)
+    tl = clip_max
+    metrics = {"ppo_ratio_clamped_frac": _frac(l2 > l1, li.mask),
+               "fipo/influence_weights_mean": torch.stack([(iw * li.mask).sum(), li.mask.sum()]),
+               "fipo/clip_frac_total": _frac((raw > hi) | (raw < lo), li.mask)}
+    c = cfg.ppo_dual_clip_ratio_c
+    if c:
+        l3 = -adv * c
+        dual = (adv < 0) & (l3 < clip_max)
+        tl = torch.where(adv < 0, torch.minimum(l3, clip_max), clip_max)
+        n_dual = _seg_sum((dual.float() * li.mask).detach(), li.seq_ids, li.num_seqs)
+        keep = (n_dual <= 1).to(tl.dtype)[li.seq_ids.long()]
+        tl = tl * keep
+        metrics["fipo/dropped_seq_frac"] = torch.stack([(n_dual > 1).float().sum(),
+                                                        (_seg_sum(li.mask, li.seq_ids, li.num_seqs) > 0).float().sum()])
+    return LossOutput(tl, ratio.detach(), metrics)
 
 
 @register_loss("reinforce")

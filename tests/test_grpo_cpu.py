@@ -50,7 +50,9 @@ def test_grpo_steps_improve_reward_and_keep_engine_in_sync():
 
 
 def test_alternative_losses_run():
-    for loss, extra in (("gspo", {"per_token_loss": False}), ("cispo", {}), ("sapo", {})):
+    for loss, extra in (("gspo", {"per_token_loss": False}), ("cispo", {}), ("sapo", {}), ("steer", {}),
+                        ("steer", {"steer_policy_method": "cispo", "steer_token_weight_min": 0.5}),
+                        ("fipo", {"ppo_dual_clip_ratio_c": 3.0})):
         cfg = make_cfg(loss_func=loss, **extra)
         tr = GrpoTrainer(cfg, model_cfg=get_preset("tiny_llama", dtype="float32"),
                          reward_fn=reward_has_small_token).setup()

@@ -213,3 +213,66 @@ def test_rule_reward_and_datasets(tmp_path):
     s2 = ResumableDistributedSampler(len(ds), dp_rank=0, dp_size=2, shuffle=True, seed=3)
     s2.load_state_dict(sd)
     assert list(iter(s2)) == a
+
+
+def test_fipo_future_sum_and_influence_weights():
+    from gcore_b200.configs.config import PpoConfig
+    from gcore_b200.loss import policy_loss as PL
+    torch.manual_seed(0)
+    lens = [5, 1, 700, 33]
+    seq_ids = torch.cat([torch.full((n,), i) for i, n in enumerate(lens)])
+    x = torch.randn(sum(lens)) * 0.05
+    gamma = 2.0 ** (-1.0 / 8.0)
+    got = PL.discounted_future_sum(x, seq_ids, gamma, chunk=64)
+    ref = torch.zeros_like(x)
+    o = 0
+    for n in lens:
+        acc = 0.0
+        for t in range(n - 1, -1, -1):
+            acc = float(x[o + t]) + gamma * acc
+            ref[o + t] = acc
+        o += n
+    assert torch.allclose(got, ref, atol=1e-5)
+    # loss: with logp == old every influence weight is 1 and fipo equals the clipped surrogate of grpo
+    cfg = PpoConfig(loss_func="fipo", fipo_decay_rate=8.0, fipo_chunk_size=64)
+    T = sum(lens)
+    lp = (torch.randn(T) * 0.1 - 2.0).requires_grad_(True)
+    adv = torch.randn(T)
+    mask = torch.ones(T)
+    li = PL.LossInput(lp, lp.detach().clone(), None, None, adv, mask, seq_ids, len(lens))
+    a, b = PL.get_loss("fipo")(cfg, li), PL.get_loss("grpo")(cfg, li)
+    assert torch.allclose(a.token_loss, b.token_loss, atol=1e-6)
+    # a later token whose probability rose lifts the weight of the earlier tokens of its sequence only
+    old = lp.detach().clone()
+    cur = lp.detach().clone()
+    cur[5 + 1 + 10] += 0.1                       # token 10 of the third sequence
+    li = PL.LossInput(cur.requires_grad_(True), old, None, None, torch.ones(T), mask, seq_ids, len(lens))
+    out = PL.get_loss("fipo")(cfg, li)
+    w = -out.token_loss.detach() / torch.exp(cur.detach() - old)     # = influence weight where nothing is clipped
+    s3 = 5 + 1
+    assert torch.allclose(w[:s3], torch.ones(s3), atol=1e-6) and torch.allclose(w[s3 + 11:], torch.ones(T - s3 - 11), atol=1e-6)
+    exp_w = torch.exp(0.1 * gamma ** torch.arange(10, -1, -1.0))
+    assert torch.allclose(w[s3:s3 + 11], exp_w.clamp(0.8, 1.2), atol=1e-5)
+
+
+def test_steer_token_weights():
+    from gcore_b200.configs.config import PpoConfig
+    from gcore_b200.loss import policy_loss as PL
+    torch.manual_seed(1)
+    T = 12
+    cfg = PpoConfig(loss_func="steer", steer_token_weight_min=0.6)
+    lp = (torch.randn(T) * 0.5 - 1.5).requires_grad_(True)
+    old = lp.detach() + torch.randn(T) * 0.01
+    adv = torch.randn(T)
+    ent = torch.rand(T) * 2
+    mask = torch.ones(T)
+    mask[-2:] = 0
+    seq_ids = torch.zeros(T, dtype=torch.long)
+    li = PL.LossInput(lp, old, None, None, adv, mask, seq_ids, 1, ent, None)
+    out, base = PL.get_loss("steer")(cfg, li), PL.get_loss("grpo")(cfg, li)
+    p = lp.detach().exp()
+    metric = (adv / old.exp() * p * (1 - p) * (p.log() + ent)).abs()
+    k = -torch.log(torch.tensor(0.6)) / torch.clamp(metric[:10].max(), min=0.02)
+    w = torch.exp(-k * metric).clamp(0.6, 1.0) * mask
+    assert torch.allclose(out.token_loss, base.token_loss * w, atol=1e-6)
+    assert abs(float(w[:10].min()) - 0.6) < 1e-5 and float(w[-1]) == 0.0   # the largest metric gets the floor

@@ -44,7 +44,8 @@ def main(argv=None):
     for step, (q, p) in enumerate(pair_batches(cfg, eng.model_cfg.vocab_size, cfg.training.seed)):
         if step >= total:
             break
-        m = embedding_step(eng, q, p, float(opt.get("temperature", 0.05)), opt.get("pooling", "last"))
+        m = embedding_step(eng, q, p, float(opt.get("temperature", 0.05)), opt.get("pooling", "last"),
+                           bool(opt.get("grad_cache", False)))
         history.append(m)
         log.info(f"step {step} " + " ".join(f"{k}={v:.4f}" for k, v in m.items()))
     finalize()

@@ -122,19 +122,40 @@ def _pooled(engine: TrainingEngine, samples: Sequence[dict], grad: bool, pooling
     return torch.stack(res)
 
 
+def _info_nce(vec: torch.Tensor, n: int, temperature: float):
+    sim = vec[:n] @ vec[n:].t() / temperature
+    tgt = torch.arange(n, device=sim.device)
+    loss = 0.5 * (torch.nn.functional.cross_entropy(sim, tgt) + torch.nn.functional.cross_entropy(sim.t(), tgt))
+    return loss, sim, tgt
+
+
 def embedding_step(engine: TrainingEngine, queries: List[dict], positives: List[dict], temperature: float = 0.05,
-                   pooling: str = "last") -> Dict[str, float]:
+                   pooling: str = "last", grad_cache: bool = False) -> Dict[str, float]:
     """Contrastive embedding training (the reference's embedding main): query ``i`` must pick ``positives[i]`` among
-    all positives of the batch (in-batch negatives, symmetric InfoNCE on cosine similarity / ``temperature``)."""
+    all positives of the batch (in-batch negatives, symmetric InfoNCE on cosine similarity / ``temperature``).
+
+    ``grad_cache``: the batch of negatives can be much larger than what fits in memory with activations kept.  All
+    vectors are first computed without a graph, the loss is differentiated with respect to the vectors only, and each
+    micro-batch is then run again with a graph and back-propagated through ``sum(vector * cached gradient)``; the
+    parameter gradients are the same as those of the direct computation."""
     assert len(queries) == len(positives)
     engine.model.train()
     engine.ddp.zero_grad_buffer()
     n = len(queries)
-    vec = _pooled(engine, list(queries) + list(positives), True, pooling)
-    sim = vec[:n] @ vec[n:].t() / temperature
-    tgt = torch.arange(n, device=sim.device)
-    loss = 0.5 * (torch.nn.functional.cross_entropy(sim, tgt) + torch.nn.functional.cross_entropy(sim.t(), tgt))
-    loss.backward()
+    allc = list(queries) + list(positives)
+    if grad_cache:
+        vec = _pooled(engine, allc, False, pooling).detach().requires_grad_(True)
+        loss, sim, tgt = _info_nce(vec, n, temperature)
+        loss.backward()
+        g = vec.grad
+        with backend_scope(engine.backend):
+            for idx in engine._microbatches(allc):
+                part = _pooled(engine, [allc[i] for i in idx], True, pooling)
+                (part * g[torch.tensor(idx, device=g.device)]).sum().backward()
+    else:
+        vec = _pooled(engine, allc, True, pooling)
+        loss, sim, tgt = _info_nce(vec, n, temperature)
+        loss.backward()
     engine.ddp.finish_grad_sync(extra_scale=1.0)
     lr = engine.optimizer.step()
     engine.step += 1

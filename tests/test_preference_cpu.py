@@ -62,3 +62,24 @@ def test_teacher_logprobs_are_attached_per_token():
     for s in out:
         key = [k for k in s if "teacher" in k][0]
         assert s[key].numel() == s["tokens"].numel() and bool((s[key][:-1] <= 0).all())
+
+
+def test_embedding_step_with_gradient_cache_equals_direct_step():
+    from gcore_b200.trainer.preference_trainers import embed, embedding_step
+    g = torch.Generator().manual_seed(2)
+    topics = torch.randint(3, 1000, (6, 5), generator=g)
+    mk = lambda t: {"tokens": torch.cat([t, torch.randint(3, 1000, (3,), generator=g)])}  # noqa: E731
+    q, p = [mk(t) for t in topics], [mk(t) for t in topics]
+    outs = []
+    for cached in (False, True):
+        e = _engine(seed=4)
+        e.train_cfg.train_mbs = 2          # several micro-batches, so the cache actually splits the work
+        m = embedding_step(e, q, p, temperature=0.1, grad_cache=cached)
+        outs.append((m, [b.grad_data.detach().clone() for b in e.ddp.buffers]))   # the reduced gradients
+    (ma, pa), (mb, pb) = outs
+    assert abs(ma["embedding/loss"] - mb["embedding/loss"]) < 1e-5
+    assert abs(ma["grad_norm"] - mb["grad_norm"]) < 1e-4 * max(1.0, ma["grad_norm"])
+    for a, b in zip(pa, pb):
+        assert float(a.abs().max()) > 0 and torch.allclose(a, b, atol=1e-5 * float(a.abs().max()))
+    v = embed(_engine(seed=4), q)
+    assert v.shape[0] == 6 and torch.allclose(v.norm(dim=-1), torch.ones(6), atol=1e-5)

@@ -30,11 +30,17 @@ class RolloutGroup:
 class RolloutController:
     def __init__(self, prompt_iter: Iterator[List[List[int]]], samplers: List[object], score_fn: Callable,
                  repeat_n: int, groups_per_batch: int, max_staleness: int = 1, max_inflight: Optional[int] = None,
-                 keep_stale: bool = False, tail_wait_s: float = 0.0, sampling_params=None):
+                 keep_stale: bool = False, tail_wait_s: float = 0.0, sampling_params=None,
+                 over_dispatch_ratio: float = 1.0, reuse_unused_prompts: bool = False):
         self.prompt_iter, self.samplers, self.score_fn = prompt_iter, samplers, score_fn
         self.repeat_n, self.groups_per_batch = repeat_n, groups_per_batch
         self.max_staleness, self.keep_stale, self.tail_wait_s = max_staleness, keep_stale, tail_wait_s
-        self.max_inflight = max_inflight or groups_per_batch * (max_staleness + 1)
+        # over-dispatch: more groups in flight than a batch needs, so a batch is made of the first to finish and
+        # stragglers do not hold it up; prompts of groups that went stale unused can be generated again
+        import math
+        self.max_inflight = max_inflight or math.ceil(groups_per_batch * (max_staleness + 1) *
+                                                      max(over_dispatch_ratio, 1.0))
+        self.reuse_unused_prompts = reuse_unused_prompts
         self.params = sampling_params
         self.version = 0
         self._pool = ThreadPoolExecutor(max_workers=max(len(samplers), 1))
@@ -43,7 +49,7 @@ class RolloutController:
         self._lock = threading.Lock()
         self._next_id = 0
         self._pending_prompts: List[List[int]] = []
-        self.stats = dict(fired=0, collected=0, dropped_stale=0, tail_batches=0)
+        self.stats = dict(fired=0, collected=0, dropped_stale=0, tail_batches=0, reused_prompts=0)
 
     # ---- weight versions
     def set_weight_version(self, v: int):
@@ -92,6 +98,9 @@ class RolloutController:
                 keep.append(g)
             else:
                 drop += 1
+                if self.reuse_unused_prompts:
+                    self._pending_prompts.append(g.prompt)
+                    self.stats["reused_prompts"] += 1
         self._done = keep
         self.stats["dropped_stale"] += drop
         return keep

@@ -11,7 +11,7 @@
 from __future__ import annotations
 
 from collections import deque
-from typing import Callable, List, Optional
+from typing import Callable, List, Optional, Sequence
 
 import torch
 
@@ -228,8 +228,8 @@ class ExternalRolloutGenerator(BaseRolloutGenerator):
 
 
 def build_generator(trainer, config) -> BaseRolloutGenerator:
-    """``policy.rollout_gen_type``: base | dynamic | replay | external; ``training.dynamic_sampling.enable`` selects
-    dynamic as before.  ``task.rollout.{replay_path, record_path, replay_loop}`` configure replay and recording."""
+    """``policy.rollout_gen_type``: base | dynamic | replay | external | two_turn_reflect; ``training.dynamic_sampling.enable`` selects
+    dynamic as before.  ``task.rollout.{replay_path, record_path, replay_loop, reflect_tokens, reflect_top_k}`` configure them."""
     kind = config.policy.rollout_gen_type or "base"
     opt = dict((config.task or {}).get("rollout", {}) or {})
     if kind == "replay":
@@ -237,6 +237,8 @@ def build_generator(trainer, config) -> BaseRolloutGenerator:
                                                            bool(opt.get("replay_loop", False)))
     elif kind == "external":
         gen = ExternalRolloutGenerator(trainer, config)
+    elif kind == "two_turn_reflect":
+        gen = TwoTurnReflectGenerator(trainer, config, opt.get("reflect_tokens", []), int(opt.get("reflect_top_k", 1)))
     elif kind == "dynamic" or config.training.dynamic_sampling.enable:
         gen = DynamicSamplingGenerator(trainer, config)
     else:
@@ -244,3 +246,41 @@ def build_generator(trainer, config) -> BaseRolloutGenerator:
     if opt.get("record_path"):
         gen = RecordingGenerator(trainer, config, gen, opt["record_path"])
     return gen
+
+
+class TwoTurnReflectGenerator(BaseRolloutGenerator):
+    """Second-turn reflection: after the first-turn samples of a prompt are scored, its ``top_k`` best and ``top_k``
+    worst responses each get a follow-up turn - the first-turn conversation plus ``reflect_tokens`` (a user message
+    asking the model to reconsider) - and the model answers again.  The batch then holds the first-turn samples and
+    the second-turn samples, ``1 + 2 * top_k`` rollout batches per prompt batch, each second-turn group normalised on
+    its own (the reference's two-turn reflect agent loop: ``reflect_prompt`` / ``reflect_top_k`` / ``rb_multiplier``,
+    gpatch_v4/configs/training_config.py:977-986).  The first turn is context, not a target, in the second turn."""
+
+    def __init__(self, trainer, config, reflect_tokens: Sequence[int], top_k: int = 1):
+        super().__init__(trainer, config)
+        self.reflect_tokens, self.top_k = list(reflect_tokens), max(int(top_k), 1)
+
+    @property
+    def rb_multiplier(self) -> int:
+        return 1 + 2 * self.top_k
+
+    def __call__(self, prompt_iter, step: int) -> List[dict]:
+        t = self.cfg.training
+        n = t.sampling_repeat_n
+        first = self.tr.score(self.tr.rollout(next(prompt_iter)))
+        groups = [first[i:i + n] for i in range(0, len(first), n)]
+        follow = []   # (origin sample, kind)
+        for g in groups:
+            srt = sorted(g, key=lambda s: float(torch.as_tensor(s["rewards"]).sum()))
+            k = min(self.top_k, len(srt) // 2 or 1)
+            follow += [(s, "worst") for s in srt[:k]] + [(s, "best") for s in srt[-k:]]
+        prompts2 = [torch.as_tensor(s["tokens"]).tolist() + self.reflect_tokens for s, _ in follow]
+        second = self.tr.score(self.tr.rollout(prompts2)) if prompts2 else []
+        base_gid = len(groups)
+        for j, (origin, kind) in enumerate(follow):
+            for s in second[j * n:(j + 1) * n]:
+                s["group_id"] = base_gid + j
+                s["turn"], s["reflect_of"], s["reflect_kind"] = 2, origin.get("unique_id"), kind
+        for s in first:
+            s["turn"] = 1
+        return first + second

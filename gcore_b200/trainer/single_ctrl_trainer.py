@@ -41,7 +41,9 @@ class GrpoSingleCtrlTrainer:
         groups = max(t.rollout_gbs // max(ps.get_data_parallel_world_size(), 1), 1)
         self.controller = RolloutController(self.prompt_iter, samplers, self.tr.score, t.sampling_repeat_n, groups,
                                             max_staleness=t.rollout_max_staleness,
-                                            keep_stale=self.cfg.ppo.offpolicy_correction != "none")
+                                            keep_stale=self.cfg.ppo.offpolicy_correction != "none",
+                                            over_dispatch_ratio=t.rollout_over_dispatch_ratio,
+                                            reuse_unused_prompts=t.rollout_reuse_unused_prompts)
         return self
 
     def step(self) -> Dict[str, float]:

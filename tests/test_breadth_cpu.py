@@ -530,3 +530,78 @@ def test_data_convert_tools(tmp_path):
     assert IndexedJsonlDataset(str(tmp_path / "p.jsonl"))[0]["answer"] == "2"
     rep = gpu_check.main([])       # no GPU here: the report says so instead of failing
     assert rep["cuda_available"] is False and rep["ok"] is False
+
+
+def test_over_dispatch_prompt_reuse_and_two_turn_reflect():
+    import time
+    from gcore_b200.rollout_generator.async_rollout import RolloutController
+    from gcore_b200.rollout_generator.generators import TwoTurnReflectGenerator
+
+    class Sampler:
+        def generate(self, prompts, params=None):
+            time.sleep(0.001)
+            return [{"tokens": list(p) + [7]} for p in prompts]
+
+    def prompts():
+        i = 0
+        while True:
+            yield [[i * 10 + j] for j in range(4)]
+            i += 1
+
+    def score(samples):
+        for s in samples:
+            s["rewards"] = 1.0
+        return samples
+
+    c = RolloutController(prompts(), [Sampler()], score, repeat_n=2, groups_per_batch=2, max_staleness=0,
+                          over_dispatch_ratio=3.0, reuse_unused_prompts=True)
+    assert c.max_inflight == 6                      # 3x more groups in flight than one batch needs
+    c.set_weight_version(0)
+    b0 = c.collect(timeout_s=30)
+    used = {tuple(s["tokens"][:1]) for s in b0}
+    time.sleep(0.05)                                # the over-dispatched groups finish with version-0 weights
+    c.set_weight_version(1)
+    b1 = c.collect(timeout_s=30)
+    assert c.stats["dropped_stale"] >= 1 and c.stats["reused_prompts"] == c.stats["dropped_stale"]
+    assert all(s["weight_version"] == 1 for s in b1)
+    # a prompt whose stale group was dropped is generated again instead of being lost
+    time.sleep(0.05)
+    c.set_weight_version(1)
+    seen = {tuple(s["tokens"][:1]) for s in b1} | used
+    b2 = c.collect(timeout_s=30)
+    assert {tuple(s["tokens"][:1]) for s in b2} <= {(i,) for i in range(100)} and len(seen) >= 3
+    c.shutdown()
+
+    class FakeTrainer:
+        def __init__(self):
+            self.calls = []
+
+        def rollout(self, prompts):
+            self.calls.append([list(p) for p in prompts])
+            out = []
+            for gi, p in enumerate(prompts):
+                for j in range(3):
+                    out.append({"tokens": torch.tensor(list(p) + [100 + j]), "prompt_length": len(p),
+                                "group_id": gi, "unique_id": (len(self.calls), gi, j)})
+            return out
+
+        def score(self, samples):
+            for s in samples:
+                s["rewards"] = torch.tensor(float(s["tokens"][-1]))     # last token = quality
+            return samples
+
+    class Cfg:
+        class training:
+            sampling_repeat_n, sampling_keep_n, sampling_keeping_strategy = 3, 3, "all"
+            filter_sampling_py_path = None
+
+    tr = FakeTrainer()
+    gen = TwoTurnReflectGenerator(tr, Cfg, reflect_tokens=[9, 9], top_k=1)
+    assert gen.rb_multiplier == 3
+    batch = gen(iter([[[1, 2], [3]]]), 0)
+    assert len(batch) == 2 * 3 + 4 * 3 and len(tr.calls) == 2
+    # second-turn prompts: worst (…100) and best (…102) first-turn conversation of every prompt + the reflect message
+    assert tr.calls[1] == [[1, 2, 100, 9, 9], [1, 2, 102, 9, 9], [3, 100, 9, 9], [3, 102, 9, 9]]
+    second = [s for s in batch if s["turn"] == 2]
+    assert sorted({s["group_id"] for s in second}) == [2, 3, 4, 5] and second[0]["reflect_kind"] == "worst"
+    assert second[0]["prompt_length"] == 5      # the first turn is context in the second turn

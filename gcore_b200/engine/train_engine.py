@@ -251,10 +251,31 @@ class TrainingEngine:
         from ..parallel.pp import broadcast_from_last_stage
         return broadcast_from_last_stage(t, shape, dtype, self.device, ps.get_pipeline_model_parallel_group())
 
-    def _logprob_entropy(self, model: GPTModel, hidden, targets, want_entropy=True):
+    def _logprob_entropy(self, model: GPTModel, hidden, targets, want_entropy=True, mask=None):
+        """Log-prob of ``targets`` (and entropy) per position.  With ``mask`` (and ``policy.ce_token_compaction``) only
+        the positions inside the loss mask go through the vocabulary projection - prompt and padding positions never
+        contribute to a loss or a metric - and the other positions read 0 (the reference's CE token compaction)."""
         w = model.output_weight()
         tp_group = ps.get_tensor_model_parallel_group() if model.tp_size > 1 else None
         mg = getattr(w, "main_grad", None) if (w.requires_grad and torch.is_grad_enabled()) else None
+        T = hidden.shape[0]
+        if mask is not None and getattr(self.policy_cfg, "ce_token_compaction", False) and mask.numel() == T:
+            idx = torch.nonzero(mask > 0).flatten()
+            n = int(idx.numel())
+            if 0 < n <= (T * 7) // 8:   # a sparse enough mask pays for the gather
+                lp_c, ent_c = linear_logprob_entropy(hidden.index_select(0, idx), w, targets.index_select(0, idx),
+                                                     self.temperature, tp_group, model.vocab_start(), mg, want_entropy)
+                lp = torch.zeros(T, dtype=lp_c.dtype, device=lp_c.device).index_copy(0, idx, lp_c)
+                ent = None
+                if ent_c is not None:
+                    ent = torch.zeros(T, dtype=ent_c.dtype, device=ent_c.device).index_copy(0, idx, ent_c)
+                return lp, ent
+            # dense mask: full projection, same convention (zeros outside the mask) so results do not depend on
+            # how a batch happens to be sharded or packed
+            lp, ent = linear_logprob_entropy(hidden, w, targets, self.temperature, tp_group, model.vocab_start(), mg,
+                                             want_entropy)
+            keep = (mask > 0).to(lp.dtype)
+            return lp * keep, (ent * keep if ent is not None else None)
         return linear_logprob_entropy(hidden, w, targets, self.temperature, tp_group, model.vocab_start(), mg,
                                       want_entropy)
 
@@ -306,7 +327,7 @@ class TrainingEngine:
             batches = self._microbatches(samples, forward_only=True)
 
             def step(mb, hidden, aux):
-                lp, ent = self._logprob_entropy(model, hidden, mb.targets, with_entropy)
+                lp, ent = self._logprob_entropy(model, hidden, mb.targets, with_entropy, mb.loss_mask)
                 return self._gather_cp(lp.float()), self._gather_cp(ent.float()) if ent is not None else None
 
             results = self._for_each_microbatch(model, samples, batches, (), step, forward_only=True)
@@ -414,7 +435,7 @@ class TrainingEngine:
             batches = self._microbatches(samples)
 
             def step(mb, hidden, aux):
-                lp, _ = self._logprob_entropy(self.model, hidden, mb.targets, want_entropy=False)
+                lp, _ = self._logprob_entropy(self.model, hidden, mb.targets, False, mb.loss_mask)
                 w = PL.aggregation_weights(mb.loss_mask, mb.seq_ids, mb.num_seqs + 1, per_token, denom)
                 loss = -(lp * w).sum()
                 if aux is not None:
@@ -463,7 +484,7 @@ class TrainingEngine:
             s.setdefault("loss_mask", s["mask"])
         with backend_scope(self.backend):
             def step(mb, hidden, aux):
-                lp, ent = self._logprob_entropy(self.model, hidden, mb.targets, want_ent)
+                lp, ent = self._logprob_entropy(self.model, hidden, mb.targets, want_ent, mb.loss_mask)
                 f = mb.fields
                 w = PL.aggregation_weights(mb.loss_mask, mb.seq_ids, mb.num_seqs + 1, per_token, denom)
                 old = f.get("logprobs") if has_old else None

@@ -27,7 +27,7 @@ def _seq_logps(engine: TrainingEngine, model, samples: Sequence[dict], grad: boo
         for idx in engine._microbatches(samples, forward_only=not grad):
             mb = engine._pack(samples, idx)
             hidden, _ = engine._hidden(model, mb)
-            lp, _ = engine._logprob_entropy(model, hidden, mb.targets, False)
+            lp, _ = engine._logprob_entropy(model, hidden, mb.targets, False, mb.loss_mask)
             seg = torch.zeros(mb.num_seqs + 1, dtype=lp.dtype, device=lp.device).index_add(0, mb.seq_ids.long(),
                                                                                            lp * mb.loss_mask)
             out.append((idx, seg[:len(idx)]))

@@ -276,3 +276,37 @@ def test_steer_token_weights():
     w = torch.exp(-k * metric).clamp(0.6, 1.0) * mask
     assert torch.allclose(out.token_loss, base.token_loss * w, atol=1e-6)
     assert abs(float(w[:10].min()) - 0.6) < 1e-5 and float(w[-1]) == 0.0   # the largest metric gets the floor
+
+
+def test_ce_token_compaction_is_exact_and_skips_prompt_rows(monkeypatch):
+    """Only positions inside the loss mask go through the vocabulary projection; losses, gradient norms and the
+    masked log-probs are those of the full computation."""
+    import sys
+    import os
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "workers"))
+    import parallel_worker as pw
+    from gcore_b200.engine import train_engine as te
+    from gcore_b200.models.config import get_preset
+    rows = []
+    real = te.linear_logprob_entropy
+
+    def spy(hidden, *a, **k):
+        rows.append(hidden.shape[0])
+        return real(hidden, *a, **k)
+
+    monkeypatch.setattr(te, "linear_logprob_entropy", spy)
+    res = {}
+    for on in (True, False):
+        e = pw.engine(get_preset("tiny_llama", dtype="float32", qkv_bias=True), 1)
+        e.policy_cfg.ce_token_compaction = on
+        rows.clear()
+        samples = pw.samples(8, 7)        # the loss mask covers about two thirds of every sequence
+        m = e.finetune_step(samples)
+        lp = e.compute_log_probs([{"tokens": s["tokens"], "prompt_length": 10} for s in pw.samples(2, 9)])
+        res[on] = (m["lm_loss"], float(e.optimizer.last_grad_norm), lp, list(rows))
+    assert abs(res[True][0] - res[False][0]) < 1e-6 and abs(res[True][1] - res[False][1]) < 1e-5
+    for a, b in zip(res[True][2], res[False][2]):
+        n = a["tokens"].numel()
+        assert torch.allclose(a["logprobs"][9:n - 1], b["logprobs"][9:n - 1], atol=1e-6)
+        assert float(a["logprobs"][:9].abs().sum()) == 0.0 and float(b["logprobs"][:9].abs().sum()) > 0.0
+    assert sum(res[True][3]) < 0.8 * sum(res[False][3])

@@ -179,9 +179,55 @@ def _optimizer_chunks(engine) -> List[Chunk]:
     return out
 
 
+_PENDING: List[dict] = []   # at most one asynchronous save in flight per process
+
+
+def _finish_save(h: dict):
+    """Second half of a save: every rank has written its shard and left its part file; rank 0 merges the metadata,
+    writes the sidecars and moves ``latest`` forward (only now does the checkpoint exist for a reader)."""
+    path, root, step, rank, world = h["path"], h["root"], h["step"], h["rank"], h["world"]
+    if h.get("thread") is not None:
+        h["thread"].join()
+        if h.get("error"):
+            raise RuntimeError(f"asynchronous checkpoint write failed: {h['error']}")
+    if world > 1:
+        ps.cpu_barrier()
+    if rank == 0:
+        parts = []
+        for r in range(world):
+            with open(os.path.join(path, f".part_{r}.pkl"), "rb") as f:
+                parts.append(pickle.load(f))
+        md = _merge_metadata(parts)
+        tmp = os.path.join(path, ".metadata.tmp")
+        with open(tmp, "wb") as f:
+            pickle.dump(md, f)
+        os.replace(tmp, os.path.join(path, ".metadata"))
+        torch.save(h["common"], os.path.join(path, "common.pt"))
+        with open(os.path.join(path, "metadata.json"), "w") as f:
+            json.dump({"sharded_backend": "torch_dist", "sharded_backend_version": 1, "common_backend": "torch",
+                       "common_backend_version": 1}, f)
+        for r in range(world):
+            os.remove(os.path.join(path, f".part_{r}.pkl"))
+        with open(os.path.join(root, LATEST), "w") as f:
+            f.write(str(step))
+        _rotate(root, *h["rotate"])
+    if world > 1:
+        ps.cpu_barrier()
+
+
+def wait_for_async_save():
+    """Completes the asynchronous save in flight, if any (collective: every rank calls it)."""
+    while _PENDING:
+        _finish_save(_PENDING.pop(0))
+
+
 def save_checkpoint(engine, root: str, step: int, extra_state: Optional[dict] = None, save_optim: bool = True,
                     save_total_limit: Optional[int] = None, save_retain_interval: Optional[int] = None,
-                    async_delete: bool = True) -> str:
+                    async_delete: bool = True, async_save: bool = False) -> str:
+    """``async_save``: tensors are copied to host memory before the call returns (a consistent snapshot of this
+    step), the shard file is written by a background thread while training goes on, and the checkpoint is published
+    (metadata, ``latest``) by the next ``save_checkpoint`` / ``wait_for_async_save`` call."""
+    wait_for_async_save()
     path = iter_dir(root, step)
     rank = dist.get_rank() if dist.is_initialized() else 0
     world = dist.get_world_size() if dist.is_initialized() else 1
@@ -189,42 +235,47 @@ def save_checkpoint(engine, root: str, step: int, extra_state: Optional[dict] = 
         os.makedirs(path, exist_ok=True)
     if world > 1:
         ps.cpu_barrier()
-    w = _ShardWriter(path, rank)
-    for c in _model_chunks(engine):
-        w.add_chunk(c)
+    chunks = _model_chunks(engine)
     if save_optim and engine.optimizer is not None:
-        for c in _optimizer_chunks(engine):
-            w.add_chunk(c)
+        chunks += _optimizer_chunks(engine)
+    if async_save:
+        for c in chunks:   # snapshot: training may overwrite the device tensors while the file is being written
+            c.tensor = c.tensor.detach().to("cpu", copy=True)
     pp, tp = ps.get_pipeline_model_parallel_rank(), ps.get_tensor_model_parallel_rank()
     dp = ps.get_data_parallel_rank(with_context_parallel=True)
-    w.add_object(f"rng_state/shard_{pp}_{tp}_{dp}", get_rng_state())
-    part = w.close()
-    parts = [part]
-    if world > 1:
-        gathered = [None] * world
-        dist.all_gather_object(gathered, part, group=ps.get_gloo_group("world"))
-        parts = gathered
-    if rank == 0:
-        md = _merge_metadata(parts)
-        tmp = os.path.join(path, ".metadata.tmp")
-        with open(tmp, "wb") as f:
-            pickle.dump(md, f)
-        os.replace(tmp, os.path.join(path, ".metadata"))
-        common = {"iteration": step, "checkpoint_version": 3.0,
-                  "optimizer_step": engine.optimizer.step_count if engine.optimizer is not None else 0,
-                  "engine_step": engine.step, "model_config": engine.model_cfg.to_dict(),
-                  "topology": dict(tp=engine.model.tp_size, ep=engine.model.ep_size,
-                                   pp=ps.get_pipeline_model_parallel_world_size(), world=world),
-                  "extra_state": extra_state or {}}
-        torch.save(common, os.path.join(path, "common.pt"))
-        with open(os.path.join(path, "metadata.json"), "w") as f:
-            json.dump({"sharded_backend": "torch_dist", "sharded_backend_version": 1, "common_backend": "torch",
-                       "common_backend_version": 1}, f)
-        with open(os.path.join(root, LATEST), "w") as f:
-            f.write(str(step))
-        _rotate(root, save_total_limit, save_retain_interval, async_delete)
-    if world > 1:
-        ps.cpu_barrier()
+    rng_key, rng_state = f"rng_state/shard_{pp}_{tp}_{dp}", get_rng_state()
+    common = {"iteration": step, "checkpoint_version": 3.0,
+              "optimizer_step": engine.optimizer.step_count if engine.optimizer is not None else 0,
+              "engine_step": engine.step, "model_config": engine.model_cfg.to_dict(),
+              "topology": dict(tp=engine.model.tp_size, ep=engine.model.ep_size,
+                               pp=ps.get_pipeline_model_parallel_world_size(), world=world),
+              "extra_state": extra_state or {}}
+    h = dict(path=path, root=root, step=step, rank=rank, world=world, common=common, thread=None, error=None,
+             rotate=(save_total_limit, save_retain_interval, async_delete))
+
+    def write():
+        try:
+            w = _ShardWriter(path, rank)
+            for c in chunks:
+                w.add_chunk(c)
+            w.add_object(rng_key, rng_state)
+            part = w.close()
+            tmp = os.path.join(path, f".part_{rank}.pkl.tmp")
+            with open(tmp, "wb") as f:
+                pickle.dump(part, f)
+            os.replace(tmp, os.path.join(path, f".part_{rank}.pkl"))
+        except Exception as e:  # noqa: BLE001 - reported by the thread's owner
+            h["error"] = repr(e)
+            if not async_save:
+                raise
+
+    if async_save:
+        h["thread"] = threading.Thread(target=write, daemon=True)
+        h["thread"].start()
+        _PENDING.append(h)
+    else:
+        write()
+        _finish_save(h)
     return path
 
 

@@ -11,7 +11,7 @@ from typing import Dict, Optional
 import torch
 import torch.distributed as dist
 
-from ..checkpoint.torch_dist import load_checkpoint, read_latest_step, save_checkpoint
+from ..checkpoint.torch_dist import load_checkpoint, read_latest_step, save_checkpoint, wait_for_async_save
 from ..configs.base import import_from_path
 from ..core import parallel_state as ps
 from ..data.datasets import default_dataset_fn
@@ -109,7 +109,7 @@ class FinetuneTrainer:
             return None
         return save_checkpoint(self.engine, ck.save_ckpt_path, self.step, extra_state={"consumed_batches": self.step},
                                save_optim=not ck.no_save_optim, save_total_limit=ck.save_total_limit,
-                               save_retain_interval=ck.save_retain_interval)
+                               save_retain_interval=ck.save_retain_interval, async_save=ck.async_save)
 
     def train_loop(self):
         t = self.cfg.training
@@ -123,4 +123,5 @@ class FinetuneTrainer:
                 self.save()
         if self.reporter:
             self.reporter.close()
+        wait_for_async_save()
         return self.history

@@ -10,7 +10,7 @@ from typing import Dict, Iterator, List, Optional
 import torch
 import torch.distributed as dist
 
-from ..checkpoint.torch_dist import load_checkpoint, read_latest_step, save_checkpoint
+from ..checkpoint.torch_dist import load_checkpoint, read_latest_step, save_checkpoint, wait_for_async_save
 from ..configs.base import import_from_path
 from ..core import parallel_state as ps
 from ..core.advantage import compute_advantages
@@ -99,7 +99,7 @@ class RlLoop:
         extra = {"consumed_batches": self.consumed_batches, "rollout_generator": self.generator.state_dict()}
         return save_checkpoint(self.trainer.policy, ck.save_ckpt_path, self.trainer.ppo_step, extra_state=extra,
                                save_optim=not ck.no_save_optim, save_total_limit=ck.save_total_limit,
-                               save_retain_interval=ck.save_retain_interval)
+                               save_retain_interval=ck.save_retain_interval, async_save=ck.async_save)
 
     def run(self):
         t = self.cfg.training
@@ -113,4 +113,5 @@ class RlLoop:
                 self.save()
         if self.reporter:
             self.reporter.close()
+        wait_for_async_save()
         return self.history

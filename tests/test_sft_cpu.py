@@ -67,3 +67,35 @@ def test_world2_gloo_matches_single_process(tmp_path):
         assert abs(a - b) < 2e-4, (ref, got)
     # the reloaded checkpoint reproduces the parameters bit for bit
     assert torch.load(out / "reload_ok_0.pt") is True
+
+
+def test_async_checkpoint_save_snapshots_the_step_and_publishes_later(tmp_path):
+    """An asynchronous save copies the tensors before returning (training continues and changes the weights), the
+    checkpoint appears under ``latest`` only once it is complete, and it holds the weights of its own step."""
+    import sys
+    import os
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "workers"))
+    import parallel_worker as pw
+    from gcore_b200.checkpoint import torch_dist as td
+    from gcore_b200.models.config import get_preset
+    mcfg = get_preset("tiny_llama", dtype="float32", qkv_bias=True)
+    e = pw.engine(mcfg, 1)
+    e.finetune_step(pw.samples(8, 1))
+    at_save = [p.detach().clone() for p in e.model.parameters()]
+    root = str(tmp_path / "ck")
+    td.save_checkpoint(e, root, 1, async_save=True)
+    assert td.read_latest_step(root) is None and len(td._PENDING) == 1     # not published yet
+    e.finetune_step(pw.samples(8, 2))                                      # weights move on while the file is written
+    td.save_checkpoint(e, root, 2, async_save=True)                        # publishes step 1, starts step 2
+    assert td.read_latest_step(root) == 1
+    td.wait_for_async_save()
+    assert td.read_latest_step(root) == 2 and not td._PENDING
+    assert not [f for f in os.listdir(os.path.join(root, "iter_0000001")) if f.startswith(".part_")]
+    e2 = pw.engine(mcfg, 1)
+    e2.setup_model_and_get_optimizer(seed=3)
+    assert td.load_checkpoint(e2, root, step=1) == 1
+    for a, b in zip(at_save, e2.model.parameters()):
+        assert torch.equal(a, b)
+    assert td.load_checkpoint(e2, root) == 2
+    for a, b in zip(e.model.parameters(), e2.model.parameters()):
+        assert torch.equal(a, b)

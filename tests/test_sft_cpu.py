@@ -99,3 +99,40 @@ def test_async_checkpoint_save_snapshots_the_step_and_publishes_later(tmp_path):
     assert td.load_checkpoint(e2, root) == 2
     for a, b in zip(e.model.parameters(), e2.model.parameters()):
         assert torch.equal(a, b)
+
+
+def test_checkpoint_stage_converters(tmp_path):
+    """hf <-> torch_dist round trip, policy -> critic (decoder copied, value head new, no vocabulary projection) and
+    strip (weights only) with the conversion tool."""
+    import json
+    import os
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "workers"))
+    import parallel_worker as pw
+    from gcore_b200.checkpoint.torch_dist import CheckpointReader, save_checkpoint
+    from gcore_b200.models.config import get_preset
+    from gcore_b200.tools import ckpt_convert as cc
+    mcfg = get_preset("tiny_llama", dtype="float32", qkv_bias=True)
+    cfg_json = tmp_path / "model.json"
+    cfg_json.write_text(json.dumps(mcfg.to_dict()))
+    e = pw.engine(mcfg, 1)
+    e.finetune_step(pw.samples(8, 1))
+    save_checkpoint(e, str(tmp_path / "rl"), 7, extra_state={"consumed_batches": 7})
+    cc.main(["strip", "--model", str(cfg_json), "--src", str(tmp_path / "rl"), "--dst", str(tmp_path / "pol"),
+             "--dtype", "float32"])
+    keys = set(CheckpointReader(str(tmp_path / "pol" / "iter_0000000")).keys())
+    assert not any(k.startswith("optimizer.") for k in keys) and "model.output_layer.weight" in keys
+    cc.main(["policy2critic", "--model", str(cfg_json), "--src", str(tmp_path / "pol"), "--dst", str(tmp_path / "crit"),
+             "--dtype", "float32"])
+    rd = CheckpointReader(str(tmp_path / "crit" / "iter_0000000"))
+    assert tuple(rd.full_tensor("model.output_layer.weight").shape) == (1, mcfg.hidden_size)
+    src = CheckpointReader(str(tmp_path / "pol" / "iter_0000000"))
+    k = "model.decoder.layers.mlp.linear_fc2.weight"
+    assert torch.equal(rd.full_tensor(k), src.full_tensor(k))
+    cc.main(["mcore2hf", "--model", str(cfg_json), "--src", str(tmp_path / "pol"), "--dst", str(tmp_path / "hf"),
+             "--dtype", "float32"])
+    cc.main(["hf2mcore", "--model", str(cfg_json), "--src", str(tmp_path / "hf"), "--dst", str(tmp_path / "back"),
+             "--dtype", "float32"])
+    back = CheckpointReader(str(tmp_path / "back" / "iter_0000000"))
+    for key in ("model.embedding.word_embeddings.weight", "model.decoder.layers.self_attention.linear_qkv.weight", k):
+        assert torch.equal(back.full_tensor(key), src.full_tensor(key)), key

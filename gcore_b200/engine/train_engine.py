@@ -135,6 +135,7 @@ class TrainingEngine:
                 assert verify_lora_weight_consistency(self.adapters, ps.get_tensor_model_parallel_group()), \
                     "LoRA replicated halves differ across the TP group"
         self._apply_freeze()
+        self._apply_precision()
         self._maybe_enable_fused_tp()
         if not self.policy_cfg.without_optim:
             oc = self.opt_cfg
@@ -143,13 +144,28 @@ class TrainingEngine:
             self.optimizer = DistributedOptimizer(self.ddp, oc, self.total_steps)
         return self.model, self.optimizer
 
+    def _apply_precision(self):
+        """``policy.fp8`` / ``fp8_qat`` / ``fp4_qat``: the decoder's projections whose contraction length is a multiple
+        of 128 switch to the block-fp8 GEMM or to quantisation-aware training (router, embedding and head stay bf16)."""
+        pc = self.policy_cfg
+        kind = "fp8" if pc.fp8 else ("fp8_qat" if pc.fp8_qat else ("fp4_qat" if pc.fp4_qat else None))
+        self.lowp_modules = []
+        if kind is None:
+            return
+        from ..models.gpt import ParallelLinear
+        for name, mod in self.model.named_modules():
+            if isinstance(mod, ParallelLinear) and "decoder.layers" in name and mod.in_local % 128 == 0 \
+                    and mod.out_local > 1:
+                mod.precision = kind
+                self.lowp_modules.append(name)
+
     def _maybe_enable_fused_tp(self):
         """TP > 1 on GPUs: the sequence-parallel collectives of every layer run inside the GEMM kernels over NVLink
         peer memory (``GCORE_FUSED_TP=0`` keeps the NCCL twins)."""
         from ..models import gpt as gpt_mod
         if (self.model.tp_size == 1 or not self.model.sequence_parallel or self.device.type != "cuda"
                 or self.backend != "native" or os.environ.get("GCORE_FUSED_TP", "1") == "0"
-                or self.policy_cfg.lora.enabled):
+                or self.policy_cfg.lora.enabled or getattr(self, "lowp_modules", None)):
             return
         from ..parallel.symm import get_fused_tp
         tp = self.model.tp_size

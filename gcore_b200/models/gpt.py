@@ -61,9 +61,19 @@ class ParallelLinear(nn.Module):
         if self.bias is not None:
             self.bias.tp_mode = "column" if mode == "column" else "none"
         self.lora: Optional[LoRAAdapter] = None
+        self.precision: Optional[str] = None   # None (bf16) | "fp8" | "fp8_qat" | "fp4_qat" (ops/lowp_linear.py)
+        self._fp8_cache: dict = {}
 
     def forward(self, x):
         w = self.weight
+        if self.precision is not None:
+            from ..ops import lowp_linear
+            mg = getattr(w, "main_grad", None) if w.requires_grad else None
+            if self.precision == "fp8":
+                y = lowp_linear.fp8_linear(x, w, self.bias, mg, self._fp8_cache)
+            else:
+                y = lowp_linear.qat_linear(x, w, self.bias, mg, self.precision)
+            return y + self.lora(x) if self.lora is not None else y
         ftp = FUSED_TP["ftp"] if FUSED_TP["active"] else None
         if ftp is not None and self.lora is None and self.tp_size > 1 and self.mode in ("column", "row"):
             # sequence-parallel layer with its collective fused into the GEMM (x is the local token shard for a

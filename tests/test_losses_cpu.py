@@ -310,3 +310,50 @@ def test_ce_token_compaction_is_exact_and_skips_prompt_rows(monkeypatch):
         assert torch.allclose(a["logprobs"][9:n - 1], b["logprobs"][9:n - 1], atol=1e-6)
         assert float(a["logprobs"][:9].abs().sum()) == 0.0 and float(b["logprobs"][:9].abs().sum()) > 0.0
     assert sum(res[True][3]) < 0.8 * sum(res[False][3])
+
+
+def test_low_precision_linear_modes_train(tmp_path):
+    """policy.fp8 / fp8_qat / fp4_qat switch the decoder projections: fp8 compute stays close to bf16 / fp32 training,
+    QAT sees fake-quantised weights with straight-through gradients, a frozen fp8 base trains under LoRA."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "workers"))
+    import parallel_worker as pw
+    from gcore_b200.configs.config import OptimizerConfig, PolicyConfig, TrainingConfig
+    from gcore_b200.engine.train_engine import TrainingEngine
+    from gcore_b200.models.config import get_preset
+    from gcore_b200.ops import lowp_linear, quant
+    mcfg = get_preset("tiny_llama", dtype="float32", qkv_bias=True, ffn_hidden_size=512)
+
+    def run(steps=4, **flags):
+        pc = PolicyConfig(recompute="none", without_ref=True, **flags)
+        e = TrainingEngine(pc, OptimizerConfig(lr=1e-3, lr_decay_style="constant", weight_decay=0.0, max_grad_norm=1.0),
+                           TrainingConfig(train_mbs=2, train_gbs=8), model_cfg=mcfg)
+        e.setup_model_and_get_optimizer(seed=11)
+        return e, [e.finetune_step(pw.samples(8, 50 + s))["lm_loss"] for s in range(steps)]
+
+    base_e, base = run()
+    assert base_e.lowp_modules == []
+    for flags, tol in (({"fp8": True}, 0.02), ({"fp8_qat": True}, 0.02), ({"fp4_qat": True}, 0.08)):
+        e, losses = run(**flags)
+        assert len(e.lowp_modules) == 4 * mcfg.num_layers            # qkv, proj, fc1, fc2 of every layer
+        assert all(abs(a - b) < tol for a, b in zip(base, losses)), (flags, base, losses)
+        assert losses != base                                         # the low-precision path really ran
+    # the QAT forward equals a plain linear on the fake-quantised weight, its gradient reaches the bf16 weight
+    w = torch.randn(256, 256, requires_grad=True)
+    x = torch.randn(5, 256)
+    y = lowp_linear.qat_linear(x, w, None, None, "fp8_qat")
+    q, s = quant.weight_quant_128x128_ref(w.detach(), pow2=True)
+    assert torch.allclose(y, x @ quant.dequant_128x128(q, s).t(), atol=1e-4)
+    y.sum().backward()
+    assert torch.allclose(w.grad, x.sum(0)[None, :].expand(256, 256), atol=1e-5)
+    # frozen block-fp8 base under LoRA: only the adapters train, the loss falls
+    pc = PolicyConfig(recompute="none", without_ref=True, fp8=True)
+    pc.lora.rank, pc.lora.alpha = 8, 16
+    e = TrainingEngine(pc, OptimizerConfig(lr=5e-3, lr_decay_style="constant", weight_decay=0.0),
+                       TrainingConfig(train_mbs=2, train_gbs=8), model_cfg=mcfg)
+    e.setup_model_and_get_optimizer(seed=11)
+    w0 = e.model.decoder.layers[0].self_attention.linear_qkv.weight.detach().clone()
+    batch = pw.samples(8, 77)
+    ls = [e.finetune_step(batch)["lm_loss"] for _ in range(8)]
+    assert ls[-1] < ls[0] - 0.05 and torch.equal(w0, e.model.decoder.layers[0].self_attention.linear_qkv.weight)

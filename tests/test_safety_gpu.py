@@ -129,3 +129,29 @@ def test_training_steps_match_the_eager_backend(kind, dtype, tol, monkeypatch):
     native, eager = run(False), run(True)
     for (l0, n0), (l1, n1) in zip(native, eager):
         assert abs(l0 - l1) < tol and abs(n0 - n1) < 10 * tol * max(1.0, n1), (native, eager)
+
+
+@pytest.mark.parametrize("flag", ["fp8", "fp8_qat", "fp4_qat"])
+def test_low_precision_training_matches_the_eager_backend(flag, monkeypatch):
+    """policy.fp8 (block-scaled e4m3 GEMM with on-the-fly activation quantisation) and the QAT modes through the
+    engine on the GPU: native quantisers / fp8 GEMM against their PyTorch definitions."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "workers"))
+    import parallel_worker as pw
+    from gcore_b200.configs.config import OptimizerConfig, PolicyConfig, TrainingConfig
+    from gcore_b200.engine.train_engine import TrainingEngine
+    from gcore_b200.models.config import get_preset
+    mcfg = get_preset("tiny_llama", dtype="bfloat16", qkv_bias=True, ffn_hidden_size=512)
+
+    def run(eager):
+        monkeypatch.setenv("GCORE_B200_FORCE_EAGER", "1" if eager else "0")
+        pc = PolicyConfig(recompute="none", without_ref=True, **{flag: True})
+        e = TrainingEngine(pc, OptimizerConfig(lr=1e-3, lr_decay_style="constant", weight_decay=0.0, max_grad_norm=1.0),
+                           TrainingConfig(train_mbs=2, train_gbs=8), model_cfg=mcfg)
+        e.setup_model_and_get_optimizer(seed=11)
+        assert len(e.lowp_modules) == 4 * mcfg.num_layers
+        return [float(e.finetune_step(pw.samples(8, 50 + s))["lm_loss"]) for s in range(3)]
+
+    native, eager = run(False), run(True)
+    assert all(abs(a - b) < 8e-3 for a, b in zip(native, eager)), (native, eager)

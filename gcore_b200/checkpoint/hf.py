@@ -22,7 +22,8 @@ from .layout import export_full_weights, load_hf_weights
 def hf_config_dict(cfg) -> dict:
     arch = {"llama": "LlamaForCausalLM", "qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
             "qwen3_moe": "Qwen3MoeForCausalLM", "deepseek_v3": "DeepseekV3ForCausalLM",
-            "mistral": "MistralForCausalLM", "gpt_oss": "GptOssForCausalLM"}.get(cfg.arch, "LlamaForCausalLM")
+            "mistral": "MistralForCausalLM", "gpt_oss": "GptOssForCausalLM",
+            "seed_oss": "SeedOssForCausalLM"}.get(cfg.arch, "LlamaForCausalLM")
     d = {"architectures": [arch], "model_type": cfg.arch if cfg.arch != "llama" else "llama",
          "hidden_size": cfg.hidden_size, "num_hidden_layers": cfg.num_layers,
          "num_attention_heads": cfg.num_attention_heads, "num_key_value_heads": cfg.num_kv_heads,

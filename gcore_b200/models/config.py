@@ -174,7 +174,7 @@ def from_hf_config(hf: Dict[str, Any]) -> ModelConfig:
     mt = hf.get("model_type", "llama")
     kw: Dict[str, Any] = dict(
         arch={"qwen2": "qwen2", "qwen3": "qwen3", "qwen3_moe": "qwen3_moe", "deepseek_v3": "deepseek_v3",
-              "mistral": "mistral", "gpt_oss": "gpt_oss"}.get(mt, "llama"),
+              "mistral": "mistral", "gpt_oss": "gpt_oss", "seed_oss": "seed_oss"}.get(mt, "llama"),
         num_layers=hf["num_hidden_layers"], hidden_size=hf["hidden_size"],
         num_attention_heads=hf["num_attention_heads"],
         num_kv_heads=hf.get("num_key_value_heads", hf["num_attention_heads"]),
@@ -183,7 +183,7 @@ def from_hf_config(hf: Dict[str, Any]) -> ModelConfig:
         tie_word_embeddings=hf.get("tie_word_embeddings", False),
         max_position_embeddings=hf.get("max_position_embeddings", 131072),
     )
-    if mt == "qwen2":
+    if mt == "qwen2" or hf.get("attention_bias"):   # seed_oss and other llama-style configs with biased projections
         kw["qkv_bias"] = True
     if mt in ("qwen3", "qwen3_moe"):
         kw["qk_layernorm"] = True

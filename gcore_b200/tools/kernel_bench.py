@@ -91,6 +91,19 @@ def main():
             xd = torch.randn(Td, K, device="cuda").bfloat16()
             rec(f"gemm_decode_{name}_T{Td}", time_fn(lambda: linear_forward(xd, w)), bytes_=2.0 * N * K,
                 base_ms=time_fn(lambda: xd @ w.t()))
+    # block-scaled fp8 GEMM (1x128 activation scales, 128x128 weight scales) and its quantisers
+    from gcore_b200.ops import quant
+    for name, N, K in shapes[:3:2] if not args.quick else shapes[:1]:
+        x = torch.randn(T, K, device="cuda").bfloat16()
+        w = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()
+        aq, as_ = quant.quant_act_1x128(x)
+        wq, ws = quant.quant_weight_128x128(w)
+        fl = 2.0 * T * N * K
+        rec(f"gemm_fp8_blockscaled_{name}_T{T}", time_fn(lambda: quant.gemm_fp8_blockscaled(aq, as_, wq, ws)), fl,
+            base_ms=time_fn(lambda: x @ w.t()))
+        rec(f"act_quant_1x128_{name}_T{T}", time_fn(lambda: quant.quant_act_1x128(x)), bytes_=3.0 * T * K)
+        rec(f"fp8_linear_incl_act_quant_{name}_T{T}",
+            time_fn(lambda: quant.gemm_fp8_blockscaled(*quant.quant_act_1x128(x), wq, ws)), fl)
     # attention forward: 8 sequences of 4096, 28 q heads / 4 kv heads, D=128, causal
     Hq, Hk, D, L, B = 28, 4, 128, 4096, 4
     q = torch.randn(B * L, Hq, D, device="cuda").bfloat16()

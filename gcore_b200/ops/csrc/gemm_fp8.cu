@@ -3,8 +3,10 @@
 // (the DeepSeek-V3 recipe; the reference's TileLang version is gfused/mygemm_fp8.py:45-97).
 //
 // Two-level accumulation: every 128-deep K block is multiplied on the tensor core into a fresh TMEM accumulator
-// (two buffers, ping-pong); the four epilogue warps pull that partial product out of TMEM, apply sA * sB and add it
-// into fp32 register accumulators while the tensor core already works on the next block.  bf16 or fp32 output.
+// (four buffers in rotation); eight promotion warps (two per TMEM lane quarter, 64 columns each) pull that partial
+// product out of TMEM, apply sA * sB and add it into fp32 register accumulators while the tensor core already works
+// on the next block.  The promotion has to keep up with ~270 tensor-core cycles per block, hence the eight warps,
+// both TMEM loads of a thread in flight at once and the scales fetched one block ahead.  bf16 or fp32 output.
 #include "ptx.cuh"
 #include "host_utils.h"
 
@@ -14,7 +16,10 @@ using namespace gk;
 constexpr int BM = 128, BN = 128, BK = 128;  // BK bytes = 128 = one swizzle row of e4m3
 constexpr int UMMA_K = 32;
 constexpr int STAGES = 5;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;          // TMA warp, MMA warp, 8 promotion warps
+constexpr int PROMO_THREADS = 256;
+constexpr int HALF = BN / 2;           // columns per promotion warp
+constexpr int NBUF = 4;                // TMEM accumulators in flight (4 x 128 columns = all of TMEM)
 constexpr int STAGE_BYTES = (BM + BN) * BK;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 
@@ -34,22 +39,25 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
   uint64_t* empty = full + STAGES;
-  uint64_t* tfull = empty + STAGES;   // 2
-  uint64_t* tempty = tfull + 2;       // 2 (128 arrivals)
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tempty + 2);
+  uint64_t* tfull = empty + STAGES;   // NBUF
+  uint64_t* tempty = tfull + NBUF;    // NBUF (one arrival per promotion thread)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tempty + NBUF);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int mt = (p.M + BM - 1) / BM;
-  const int m0 = (blockIdx.x % mt) * BM, n0 = (blockIdx.x / mt) * BN;
+  const int ntiles = mt * ((p.N + BN - 1) / BN);
   const int KB = (p.K + BK - 1) / BK;
+  // persistent: CTA c works on tiles c, c + grid, ...; the three roles walk the same sequence, and the pipeline
+  // (shared-memory stages, the two TMEM buffers) keeps running across tile boundaries, so the loads and MMAs of the
+  // next tile overlap the promotion and the store of the current one
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 128); }
+    for (int a = 0; a < NBUF; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], PROMO_THREADS); }
     fence_barrier_init();
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
   }
-  if (warp == 2) { tmem_alloc(tmem_holder, 256); tmem_relinquish(); }
+  if (warp == 2) { tmem_alloc(tmem_holder, NBUF * BN); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -57,27 +65,33 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
   if (warp == 0) {
     bool ok = true;
-    for (int kb = 0; kb < KB && ok; ++kb) {
-      const int s = kb % STAGES;
-      const uint32_t ph = (kb / STAGES) & 1;
-      ok = mbar_wait(&empty[s], ph ^ 1, p.err, ERR_WAIT_EMPTY);
-      if (!ok) break;
-      if (lane == 0) {
-        uint8_t* sa = smem + s * STAGE_BYTES;
-        mbar_expect_tx(&full[s], STAGE_BYTES);
-        tma_load_2d(sa, &tmA, &full[s], kb * BK, m0);
-        tma_load_2d(sa + BM * BK, &tmB, &full[s], kb * BK, n0);
+    long long it = 0;
+    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+      const int m0 = (tile % mt) * BM, n0 = (tile / mt) * BN;
+      for (int kb = 0; kb < KB && ok; ++kb, ++it) {
+        const int s = static_cast<int>(it % STAGES);
+        const uint32_t ph = static_cast<uint32_t>(it / STAGES) & 1;
+        ok = mbar_wait(&empty[s], ph ^ 1, p.err, ERR_WAIT_EMPTY);
+        if (!ok) break;
+        if (lane == 0) {
+          uint8_t* sa = smem + s * STAGE_BYTES;
+          mbar_expect_tx(&full[s], STAGE_BYTES);
+          tma_load_2d(sa, &tmA, &full[s], kb * BK, m0);
+          tma_load_2d(sa + BM * BK, &tmB, &full[s], kb * BK, n0);
+        }
+        __syncwarp();
       }
-      __syncwarp();
     }
   } else if (warp == 1) {
     constexpr uint32_t idesc = make_idesc(BM, BN, 0, 0, 0, 0);  // e4m3 x e4m3 -> f32
     bool ok = true;
-    for (int kb = 0; kb < KB && ok; ++kb) {
-      const int s = kb % STAGES, a = kb & 1;
-      ok = mbar_wait(&tempty[a], ((kb >> 1) & 1) ^ 1, p.err, ERR_WAIT_TMEM_EMPTY);
+    const long long total = static_cast<long long>((ntiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                                                   static_cast<int>(gridDim.x)) * KB;
+    for (long long it = 0; it < total && ok; ++it) {
+      const int s = static_cast<int>(it % STAGES), a = static_cast<int>(it % NBUF);
+      ok = mbar_wait(&tempty[a], (static_cast<uint32_t>(it / NBUF) & 1) ^ 1, p.err, ERR_WAIT_TMEM_EMPTY);
       if (!ok) break;
-      ok = mbar_wait(&full[s], (kb / STAGES) & 1, p.err, ERR_WAIT_FULL);
+      ok = mbar_wait(&full[s], static_cast<uint32_t>(it / STAGES) & 1, p.err, ERR_WAIT_FULL);
       if (!ok) break;
       tc_fence_after();
       if (lane == 0) {
@@ -93,35 +107,43 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       __syncwarp();
     }
   } else {
-    const int quad = warp & 3;
-    const int row = m0 + quad * 32 + lane;
-    float acc[BN];
-#pragma unroll
-    for (int j = 0; j < BN; ++j) acc[j] = 0.f;
+    const int quad = warp & 3;                 // TMEM lane quarter this warp may read
+    const int half = (warp - 2) >> 2;          // which 64 columns of the tile
     bool ok = true;
+    long long it = 0;
+    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+    const int m0 = (tile % mt) * BM, n0 = (tile / mt) * BN;
+    const int row = m0 + quad * 32 + lane;
+    float acc[HALF];
+#pragma unroll
+    for (int j = 0; j < HALF; ++j) acc[j] = 0.f;
     const int nb = n0 / 128;
-    for (int kb = 0; kb < KB && ok; ++kb) {
-      const int a = kb & 1;
-      ok = mbar_wait(&tfull[a], (kb >> 1) & 1, p.err, ERR_WAIT_TMEM_FULL);
+    const float* sa_row = p.sA + static_cast<long long>(row < p.M ? row : 0) * KB;
+    const float* sb_row = p.sB + static_cast<long long>(nb) * KB;
+    float sc_next = (row < p.M ? sa_row[0] : 0.f) * sb_row[0];
+    for (int kb = 0; kb < KB && ok; ++kb, ++it) {
+      const int a = static_cast<int>(it % NBUF);
+      const float sc = sc_next;
+      if (kb + 1 < KB) sc_next = (row < p.M ? sa_row[kb + 1] : 0.f) * sb_row[kb + 1];  // in flight during the wait
+      ok = mbar_wait(&tfull[a], static_cast<uint32_t>(it / NBUF) & 1, p.err, ERR_WAIT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
-      const float sc = (row < p.M ? p.sA[static_cast<long long>(row) * KB + kb] : 0.f) * p.sB[static_cast<long long>(nb) * KB + kb];
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + a * BN;
-#pragma unroll
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(taddr + c * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc[c * 32 + j] += sc * __uint_as_float(r[j]);
-      }
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + a * BN + half * HALF;
+      uint32_t r0[32], r1[32];
+      tmem_ld32(taddr, r0);
+      tmem_ld32(taddr + 32, r1);
+      tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(&tempty[a]);
+      mbar_arrive(&tempty[a]);                 // the values are in registers: the buffer can take the next block
+#pragma unroll
+      for (int j = 0; j < 32; ++j) acc[j] = fmaf(sc, __uint_as_float(r0[j]), acc[j]);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) acc[32 + j] = fmaf(sc, __uint_as_float(r1[j]), acc[32 + j]);
     }
     if (ok && row < p.M) {
 #pragma unroll
-      for (int c = 0; c < BN / 8; ++c) {
-        const int col = n0 + c * 8;
+      for (int c = 0; c < HALF / 8; ++c) {
+        const int col = n0 + half * HALF + c * 8;
         if (col + 8 <= p.N && (p.ldc & 7) == 0) {
           if (p.out_fp32) {
             float4* d = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col);
@@ -145,10 +167,11 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
       }
     }
+    }  // tiles
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 2) { tc_fence_after(); tmem_dealloc(tmem_base, 256); }
+  if (warp == 2) { tc_fence_after(); tmem_dealloc(tmem_base, NBUF * BN); }
 }
 
 }  // namespace gk8
@@ -173,6 +196,13 @@ GK_EXPORT int gk_gemm_fp8_blockscaled(const void* A, long long lda, const void* 
   P8 p;
   p.M = M; p.N = N; p.K = K; p.sA = sA; p.sB = sB; p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32; p.err = err;
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  gemm_fp8_kernel<<<tiles, THREADS, SMEM_BYTES, reinterpret_cast<cudaStream_t>(stream)>>>(tmA, tmB, p);
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  gemm_fp8_kernel<<<tiles < sms ? tiles : sms, THREADS, SMEM_BYTES, reinterpret_cast<cudaStream_t>(stream)>>>(tmA, tmB, p);
   return gk::launch_status();
 }

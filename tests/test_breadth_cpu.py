@@ -605,3 +605,22 @@ def test_over_dispatch_prompt_reuse_and_two_turn_reflect():
     second = [s for s in batch if s["turn"] == 2]
     assert sorted({s["group_id"] for s in second}) == [2, 3, 4, 5] and second[0]["reflect_kind"] == "worst"
     assert second[0]["prompt_length"] == 5      # the first turn is context in the second turn
+
+
+def test_eval_server_and_client_over_http():
+    from gcore_b200.client.rpc import serve
+    from gcore_b200.tools.eval_server import EvalClient, EvalService
+
+    def reward(samples):
+        return torch.tensor([1.0 if int(s["tokens"][-1]) % 2 == 0 else 0.0 for s in samples])
+
+    srv, url = serve(EvalService(reward), allowed=["score", "evaluate", "health"])
+    try:
+        c = EvalClient([url])
+        samples = [{"tokens": torch.tensor([5, 6, t]), "prompt_length": 2} for t in (2, 3, 4, 5, 7, 9)]
+        assert c.score(samples) == [1.0, 0.0, 1.0, 0.0, 0.0, 0.0]
+        m = c.evaluate(samples, n=3, ks=(1, 3))      # prompt 0: 2 of 3 correct, prompt 1: none
+        assert abs(m["eval/pass@1"] - (2 / 3) / 2) < 1e-6 and abs(m["eval/pass@3"] - 0.5) < 1e-6
+        assert c.health()[0]["samples"] == 12
+    finally:
+        srv.shutdown()

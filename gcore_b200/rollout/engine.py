@@ -425,7 +425,8 @@ class InferEngine:
                 q_nope, q_rope, c_kv, k_rope = lw.mla.project(h, pos)
                 sink = (self.k_cache[li].shape[0] - 1) * self.bs  # rows without a slot land in the spare block
                 self.k_cache[li].view(-1, self.mla_dim).index_copy_(
-                    0, torch.where(slots >= 0, slots, torch.full_like(slots, sink)).long(), torch.cat([c_kv, k_rope], -1))
+                    0, torch.where(slots >= 0, slots, torch.full_like(slots, sink)).long(),
+                    torch.cat([self._mla_cached_latent(lw.mla, c_kv), k_rope], -1))
                 a = self._allreduce(lw.mla.linear_proj(lw.mla.attend(q_nope, q_rope, c_kv, k_rope, cu)))
                 h, res = fused.rmsnorm(a, lw.ln2, cfg.rms_norm_eps, res)
                 x = self._mlp(lw, h)
@@ -507,6 +508,28 @@ class InferEngine:
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.ep_group)
         return [bool(x) for x in t.tolist()]
 
+    @staticmethod
+    def _mla_cached_latent(mla, c_kv):
+        """What the cache keeps of the latent.  When the kv up-projection computes in block fp8 the trainer multiplies
+        the 1x128-quantised latent with the 128x128-quantised weight; the absorbed decode reproduces that product
+        exactly by caching the quantise -> dequantise image of the latent (and absorbing the dequantised weight)."""
+        up = mla.linear_kv_up_proj
+        if getattr(up, "precision", None) == "fp8" and c_kv.shape[-1] % 128 == 0:
+            from ..ops import quant
+            q, sc = quant.quant_act_1x128(c_kv.to(torch.bfloat16).contiguous())
+            return quant.dequant_1x128(q, sc).to(c_kv.dtype)
+        return c_kv
+
+    @staticmethod
+    def _mla_up_weight(mla):
+        up = mla.linear_kv_up_proj
+        w = up.weight
+        if getattr(up, "precision", None) == "fp8" and w.shape[1] % 128 == 0:
+            from ..ops import quant
+            q, sc = quant.quant_weight_128x128(w.detach().to(torch.bfloat16).contiguous())
+            w = quant.dequant_128x128(q, sc)[:w.shape[0], :w.shape[1]].to(up.weight.dtype)
+        return w
+
     def _mla_decode(self, mla, h, pos, cache, slots, lat_idx, lat_mask):
         """One token per request of multi-head latent attention on the latent cache, in the absorbed form: the key
         up-projection is folded into the query and the value up-projection is applied after the weighted sum, so a
@@ -517,9 +540,9 @@ class InferEngine:
         B = h.shape[0]
         q_nope, q_rope, c_kv, k_rope = mla.project(h, pos)
         flat = cache.view(-1, self.mla_dim)
-        flat.index_copy_(0, slots, torch.cat([c_kv, k_rope], -1))
+        flat.index_copy_(0, slots, torch.cat([self._mla_cached_latent(mla, c_kv), k_rope], -1))
         lat = flat[lat_idx]                                            # [B, Lmax, C + dr]
-        w_up = mla.linear_kv_up_proj.weight.view(mla.h, dn + dv, C)
+        w_up = self._mla_up_weight(mla).view(mla.h, dn + dv, C)
         up_lora = getattr(mla.linear_kv_up_proj, "lora", None)
         if up_lora is not None:  # adapters on the up-projection: fold their delta into the absorbed matrices
             w_up = w_up + up_lora.delta_weight().view(mla.h, dn + dv, C).to(w_up.dtype)

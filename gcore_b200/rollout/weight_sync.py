@@ -262,10 +262,11 @@ def detach_lora_targets(policy_engine, weights) -> List[str]:
             "mlp.linear_fc1.weight": "fc1_w", "mlp.linear_fc2.weight": "fc2_w"}
     done = []
     for name in targets:
-        if name not in tmap:
+        suffix = name.split(".", 3)[3] if name.count(".") >= 3 else name
+        # multi-head-latent-attention layers are served by their module, adapters included: nothing to detach
+        if name not in tmap or tmap[name] is None or suffix not in attr:
             continue
         layer = int(name.split(".")[2])
-        suffix = name.split(".", 3)[3]
         setattr(weights.layers[layer], attr[suffix], tmap[name].clone())
         done.append(name)
     return done
@@ -283,7 +284,7 @@ def sync_lora_deltas(policy_engine, infer_engine) -> Dict[str, float]:
     moved = factors = 0
     with torch.no_grad():
         for name, lora in targets.items():
-            if name not in dst:
+            if name not in dst or dst[name] is None:
                 continue
             d = dst[name]
             assert d.data_ptr() != params[name].data_ptr(), "LoRA target still shares the frozen base storage"

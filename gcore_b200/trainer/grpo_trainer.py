@@ -107,6 +107,11 @@ class GrpoTrainer:
         self.sampling = SamplingParams(temperature=ie.temperature, top_k=ie.top_k, top_p=ie.top_p, min_p=ie.min_p,
                                        max_new_tokens=ie.generate_max_tokens, seed=ie.seed,
                                        stop_token_ids=tuple(ie.generate_params.get("stop_token_ids", ())))
+        # fp8 serving: asked for by the engine config, and implied by an fp8 policy so that trainer and rollout
+        # compute the same quantised products
+        self.serve_fp8 = bool(getattr(ie, "fp8_weights", False) or cfg.policy.fp8)
+        if self.serve_fp8:
+            self.engine.quantize_weights_fp8()
         # gradient buffers are only needed inside the update phase
         self.policy.release_grad_buffers()
         return self
@@ -231,6 +236,9 @@ class GrpoTrainer:
         else:
             from ..rollout.weight_sync import sync_weights
             sync_weights(self.policy, self.engine)
+        if self.serve_fp8:
+            # the engine's dense projections are re-quantised (e4m3, 128x128 scales) from the weights just handed over
+            self.engine.quantize_weights_fp8()
 
     def _rollout_metrics(self, samples):
         r = torch.stack([torch.as_tensor(s["rewards"]).float().sum() for s in samples])

@@ -124,3 +124,20 @@ def test_crash_is_detected_and_job_resumes_from_checkpoint(tmp_path):
     from gcore_b200.checkpoint.torch_dist import read_latest_step
     assert read_latest_step(str(ckpt)) == 5
     assert sorted(os.listdir(ckpt))[:3] == ["iter_0000002", "iter_0000004", "iter_0000005"]
+
+
+def test_every_recipe_yaml_loads_and_names_a_known_model():
+    import glob
+    from gcore_b200.configs.base import load_config
+    from gcore_b200.configs.config import FinetuneConfig, RlConfig
+    from gcore_b200.models.config import PRESETS
+    files = sorted(glob.glob(os.path.join(ROOT, "tasks", "math_rl", "yaml", "*.yaml")))
+    assert len(files) >= 7
+    for f in files:
+        raw = yaml.safe_load(open(f))
+        cfg = load_config(RlConfig if "sampler" in raw else FinetuneConfig, f, [])
+        assert cfg.policy.model_arch in PRESETS, f
+        if "teacher" in raw:
+            assert cfg.teacher.model_arch in PRESETS and cfg.ppo.advantage_type == "on_policy_distill"
+        if raw["policy"].get("fp8"):
+            assert cfg.policy.fp8 and cfg.policy.lora.enabled and "linear_kv_up_proj" in cfg.policy.lora.target_modules

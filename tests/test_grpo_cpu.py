@@ -154,3 +154,34 @@ def test_generative_and_bt_reward_models_drive_a_grpo_step():
     assert -1.0 <= s["reward_dict"]["gen_rm"] <= 1.0
     total = s["reward_dict"]["rule"] + 0.5 * s["reward_dict"]["gen_rm"] + 0.25 * s["reward_dict"]["bt_rm"]
     assert abs(float(s["rewards"]) - total) < 1e-5
+
+
+def test_grpo_with_fp8_base_lora_and_mla_moe_policy():
+    """The shape of the fp8 + LoRA recipe in miniature: DeepSeek-V3-style model (MLA, sigmoid-group MoE, dense first
+    layer), frozen block-fp8 projections, adapters on the MLA projections; the rollout engine serves the latent cache
+    with the fp8 products of the trainer, so its log-probs stay close to the trainer's."""
+    from gcore_b200.models.config import ModelConfig
+    mcfg = ModelConfig(arch="deepseek_v3", num_layers=3, hidden_size=128, num_attention_heads=4, num_kv_heads=4,
+                       ffn_hidden_size=256, vocab_size=512, use_mla=True, q_lora_rank=128, kv_lora_rank=128,
+                       qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32, head_dim=48, num_experts=8, moe_top_k=2,
+                       moe_ffn_hidden_size=64, moe_shared_expert_ffn=128, moe_router_type="sigmoid_group",
+                       moe_n_group=4, moe_topk_group=2, first_k_dense=1, moe_routed_scaling_factor=2.5,
+                       moe_router_bias=True, rope_interleaved=True, dtype="float32")
+    cfg = make_cfg()
+    cfg.policy.fp8 = True
+    cfg.policy.lora.rank, cfg.policy.lora.alpha, cfg.policy.lora.type = 8, 16, "lora"
+    cfg.policy.lora.target_modules = ["linear_q_down_proj", "linear_q_up_proj", "linear_kv_down_proj",
+                                      "linear_kv_up_proj", "linear_proj"]
+    torch.manual_seed(0)
+    tr = GrpoTrainer(cfg, model_cfg=mcfg, reward_fn=reward_has_small_token).setup()
+    assert tr.serve_fp8 and len(tr.policy.adapters) == 15 and len(tr.policy.lowp_modules) > 15
+    base = tr.policy.model.decoder.layers[1].self_attention.linear_kv_up_proj.weight.detach().clone()
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(3, 512, (8,), generator=g).tolist() for _ in range(4)]
+    m = tr.step(prompts)
+    s = tr.last_samples[0]
+    P, S = s["prompt_length"], s["sequence_length"]
+    assert float((s["logprobs"][P - 1:S - 1] - s["rollout_log_probs"][P - 1:S - 1]).abs().max()) < 0.03
+    assert m["policy/grad_norm"] > 0 and abs(m["ppo-metrics/ratio"] - 1.0) < 1e-3
+    tr.step(prompts)
+    assert torch.equal(base, tr.policy.model.decoder.layers[1].self_attention.linear_kv_up_proj.weight)  # frozen base

@@ -236,8 +236,24 @@ class MLAttention(nn.Module):
         kf = torch.cat([k_nope, k_rope.reshape(T, 1, dr).expand(T, h, dr)], -1)
         # pad v to the qk head dim so one attention call serves both (extra columns are zero and sliced away)
         vpad = torch.nn.functional.pad(v, (0, dn + dr - dv))
-        from ..ops.attention import attn_varlen_ref
-        o = attn_varlen_ref(qf, kf, vpad, cu_seqlens, cu_seqlens, True, 0, None, 1.0 / math.sqrt(dn + dr))
+        scale = 1.0 / math.sqrt(dn + dr)
+        from ..ops import _lib
+        if qf.is_cuda and qf.dtype in (torch.bfloat16, torch.float16) and not _lib.force_eager():
+            # 192-wide keys / 128-wide values do not fit the tcgen05 flash kernel (128 x 128 head dims); until it does,
+            # the library's fused attention runs one sequence at a time (memory linear in the sequence length)
+            bounds = cu_seqlens.tolist()
+            outs = []
+            for a, b in zip(bounds[:-1], bounds[1:]):
+                if b > a:
+                    outs.append(torch.nn.functional.scaled_dot_product_attention(
+                        qf[a:b].transpose(0, 1)[None], kf[a:b].transpose(0, 1)[None], vpad[a:b].transpose(0, 1)[None],
+                        is_causal=True, scale=scale)[0].transpose(0, 1))
+            if bounds[-1] < T:   # padding rows behind the last sequence
+                outs.append(qf.new_zeros(T - bounds[-1], h, dn + dr))
+            o = torch.cat(outs, 0)
+        else:
+            from ..ops.attention import attn_varlen_ref
+            o = attn_varlen_ref(qf, kf, vpad, cu_seqlens, cu_seqlens, True, 0, None, scale)
         return o[..., :dv].reshape(T, h * dv)
 
     def forward(self, x, pos, cu_seqlens, max_seqlen):

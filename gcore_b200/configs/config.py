@@ -407,8 +407,8 @@ class PpoConfig(MappingMixin):
                 raise ConfigError("steer_token_weight_min must be in (0, 1]")
             if self.steer_policy_method not in ("grpo", "cispo", "gspo", "sapo"):
                 raise ConfigError(f"steer_policy_method must be grpo|cispo|gspo|sapo, got {self.steer_policy_method}")
-        if self.advantage_type not in ("grpo", "gdpo", "ppo", "reinforce", "on_policy_distill", "g_opd",
-                                       "identity", "custom"):
+        if self.advantage_type not in ("grpo", "gdpo", "gdpo_sample_bn", "group_gdpo", "group_gdpo_sample_bn", "ppo",
+                                       "reinforce", "on_policy_distill", "g_opd", "identity", "custom"):
             raise ConfigError(f"unknown advantage_type {self.advantage_type}")
         if self.loss_func == "gspo" and self.per_token_loss:
             # sequence-level ratios are aggregated per sequence (gpatch_v4/configs/config.py:273-276)

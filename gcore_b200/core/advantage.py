@@ -12,6 +12,7 @@ plus global whitening, clipping and a KL-to-reference penalty folded into per-to
 """
 from __future__ import annotations
 
+import math
 from typing import Callable, Dict, List, Optional
 
 import torch
@@ -97,6 +98,73 @@ def gdpo_advantage(samples: List[dict], cfg, **_):
         s["pre_bn_advantages"] = a
     _broadcast_over_tokens(samples, total)
     return samples
+
+
+def _gdpo_combined(samples: List[dict], cfg):
+    """Sum over reward heads of weight x (group-normalised head reward); None without per-head rewards."""
+    heads = sorted({k for s in samples for k in (s.get("reward_dict") or {})})
+    if not heads:
+        return None
+    gid = torch.tensor([int(s["group_id"]) for s in samples])
+    sm = torch.tensor([bool(s.get("sample_mask", True)) for s in samples])
+    total = torch.zeros(len(samples))
+    for h in heads:
+        r = torch.tensor([float(s["reward_dict"].get(h, 0.0)) for s in samples])
+        total += cfg.gdpo_reward_weights.get(h, 1.0) * group_normalize(r, gid, sm, cfg.grpo_advantage_epsilon, True)
+    return total, sm
+
+
+def _sample_bn(total, sm, eps, group=None):
+    """(x - mean) / (std + eps) over the valid samples - of all data-parallel ranks when ``group`` is given - with the
+    unbiased standard deviation (1 for a single sample)."""
+    valid = sm.float()
+    st = torch.stack([(total * valid).sum(), (total * total * valid).sum(), valid.sum()]).double()
+    if group is not None:
+        import torch.distributed as dist
+        if dist.is_initialized() and dist.get_world_size(group) > 1:
+            dev = "cuda" if dist.get_backend(group) == "nccl" else "cpu"
+            t = st.to(dev)
+            dist.all_reduce(t, group=group)
+            st = t.cpu()
+    n = float(st[2])
+    mean = float(st[0]) / max(n, 1.0)
+    std = math.sqrt(max(float(st[1]) - n * mean * mean, 0.0) / (n - 1.0)) if n > 1 else 1.0
+    return (total - mean) / (std + eps) * valid, {"gdpo/bn_mean": mean, "gdpo/bn_std": std}
+
+
+def _gdpo_variant(samples, cfg, bn: bool, dp_group):
+    got = _gdpo_combined(samples, cfg)
+    if got is None:
+        return grpo_advantage(samples, cfg)
+    total, sm = got
+    for s, a in zip(samples, total.tolist()):
+        s["pre_bn_advantages"] = a
+    if bn:
+        total, stats = _sample_bn(total, sm, cfg.grpo_advantage_epsilon, dp_group)
+        for s in samples:
+            s["advantage_stats"] = stats
+    else:
+        total = total * sm.float()
+    _broadcast_over_tokens(samples, total)
+    return samples
+
+
+@register_advantage("gdpo_sample_bn")
+def gdpo_sample_bn_advantage(samples: List[dict], cfg, dp_group=None, **_):
+    """gdpo followed by a batch norm over the valid samples of the whole data-parallel batch."""
+    return _gdpo_variant(samples, cfg, True, dp_group)
+
+
+@register_advantage("group_gdpo")
+def group_gdpo_advantage(samples: List[dict], cfg, **_):
+    """Per-head group normalisation and mixing only (no batch statistics)."""
+    return _gdpo_variant(samples, cfg, False, None)
+
+
+@register_advantage("group_gdpo_sample_bn")
+def group_gdpo_sample_bn_advantage(samples: List[dict], cfg, **_):
+    """The batch norm uses this rank's samples only."""
+    return _gdpo_variant(samples, cfg, True, None)
 
 
 @register_advantage("reinforce")
@@ -189,7 +257,10 @@ def compute_advantages(samples: List[dict], ppo_cfg, dp_group=None, custom_fn: O
             from .packing import response_mask
             s["mask"] = response_mask(int(s["prompt_length"]), len(s["tokens"]))
     fn = custom_fn if custom_fn is not None else get_advantage_fn(ppo_cfg.advantage_type)
-    samples = fn(samples, ppo_cfg)
+    try:
+        samples = fn(samples, ppo_cfg, dp_group=dp_group)
+    except TypeError:   # plug-in functions with the two-argument signature
+        samples = fn(samples, ppo_cfg)
     if ppo_cfg.whiten_advantages:
         samples = whiten_advantages(samples, dp_group)
     if ppo_cfg.advantage_clip:

@@ -357,3 +357,34 @@ def test_low_precision_linear_modes_train(tmp_path):
     batch = pw.samples(8, 77)
     ls = [e.finetune_step(batch)["lm_loss"] for _ in range(8)]
     assert ls[-1] < ls[0] - 0.05 and torch.equal(w0, e.model.decoder.layers[0].self_attention.linear_qkv.weight)
+
+
+def test_gdpo_advantage_variants():
+    from gcore_b200.configs.config import PpoConfig
+    from gcore_b200.core.advantage import get_advantage_fn
+    torch.manual_seed(0)
+
+    def batch():
+        out = []
+        for g in range(3):
+            for j in range(4):
+                out.append({"group_id": g, "mask": torch.tensor([0.0, 1.0, 1.0]), "rewards": torch.tensor(0.0),
+                            "reward_dict": {"acc": float((g + j) % 2), "fmt": float(j % 3 == 0) * 0.5}})
+        return out
+
+    cfg = PpoConfig(advantage_type="group_gdpo", gdpo_reward_weights={"acc": 1.0, "fmt": 0.5})
+    plain = get_advantage_fn("group_gdpo")(batch(), cfg)
+    comb = torch.tensor([float(s["advantages"][1]) for s in plain])
+    for g in range(3):       # every head is group-normalised, so the mix has zero mean inside each group
+        assert abs(float(comb[g * 4:(g + 1) * 4].mean())) < 1e-5
+    bn = get_advantage_fn("group_gdpo_sample_bn")(batch(), cfg)
+    a = torch.tensor([float(s["advantages"][1]) for s in bn])
+    assert abs(float(a.mean())) < 1e-5 and abs(float(a.std()) - 1.0) < 1e-3      # unbiased std of the batch is 1
+    assert torch.allclose(a, (comb - comb.mean()) / (comb.std() + cfg.grpo_advantage_epsilon), atol=1e-5)
+    assert bn[0]["advantages"][0] == 0 and abs(bn[0]["pre_bn_advantages"] - float(comb[0])) < 1e-6
+    # without a process group the cross-rank form equals the local one; masked samples get no advantage
+    b = batch()
+    b[5]["sample_mask"] = False
+    g1 = get_advantage_fn("gdpo_sample_bn")(b, cfg, dp_group=None)
+    assert float(g1[5]["advantages"].abs().sum()) == 0.0 and "gdpo/bn_std" in g1[0]["advantage_stats"]
+    PpoConfig(advantage_type="gdpo_sample_bn")      # accepted by the configuration

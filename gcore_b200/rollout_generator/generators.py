@@ -284,3 +284,56 @@ class TwoTurnReflectGenerator(BaseRolloutGenerator):
         for s in first:
             s["turn"] = 1
         return first + second
+
+
+class AgenticRolloutGenerator(BaseRolloutGenerator):
+    """Multi-turn environment rollouts instead of single-turn prompts: every group runs ``sampling_repeat_n``
+    trajectories of one environment seed through ``agentic.TrajEnvManager`` (the policy is the trainer's rollout
+    engine, one generate call per turn), and the trajectory's tokens / assistant-token mask / rollout log-probs /
+    episode reward become one training sample.  With a ``teacher:`` section and
+    ``advantage_type=on_policy_distill`` this is agentic distillation: the teacher scores the student's trajectories
+    token by token (the reference's agent loop actors and agentic distill trainer)."""
+
+    def __init__(self, trainer, config, env_factory: Callable, tokenizer, max_turns: int = 4,
+                 max_new_tokens: Optional[int] = None):
+        super().__init__(trainer, config)
+        self.env_factory, self.tok, self.max_turns, self.max_new = env_factory, tokenizer, max_turns, max_new_tokens
+        self.seed = 0
+
+    def _generate(self, ctx: List[int]) -> dict:
+        from ..rollout.engine import SamplingParams
+        tr = self.tr
+        sp = SamplingParams(**{**tr.sampling.__dict__, "seed": tr.sampling.seed + self.seed * 7919 + len(ctx),
+                               "max_new_tokens": self.max_new or tr.sampling.max_new_tokens})
+        r = tr.engine.generate([ctx], sp, n=1)[0]
+        return {"token_ids": r.out_tokens, "logprobs": r.out_logprobs}
+
+    def __call__(self, prompt_iter, step: int) -> List[dict]:
+        from ..agentic import TrajEnvManager
+        t = self.cfg.training
+        groups = max(t.rollout_gbs, 1)
+        self.tr.engine.wake_up(("kv_cache",))
+        samples = []
+        for g in range(groups):
+            env_seed = step * 100003 + g
+            for j in range(t.sampling_repeat_n):
+                self.seed += 1
+                mgr = TrajEnvManager(self.env_factory(), self.tok, self._generate, max_turns=self.max_turns,
+                                     max_context_tokens=self.tr.engine.max_model_len - (self.max_new or
+                                                                                        self.tr.sampling.max_new_tokens),
+                                     group_id=g, traj_id=j)
+                s = mgr.run(env_seed, step)
+                toks = torch.as_tensor(s["tokens"], dtype=torch.int64)
+                s.update(tokens=toks, sequence_length=int(toks.numel()), rewards=torch.tensor(float(s["reward"])),
+                         unique_id=(step, g, j), finish_reason="env")
+                if "rollout_log_probs" in s:
+                    s["rollout_log_probs"] = torch.as_tensor(s["rollout_log_probs"], dtype=torch.float32)
+                samples.append(s)
+        self.tr.engine.sleep(("kv_cache",))
+        return samples
+
+    def state_dict(self):
+        return {"seed": self.seed}
+
+    def load_state_dict(self, sd):
+        self.seed = int(sd.get("seed", 0))

@@ -159,3 +159,48 @@ def test_record_replay_and_external_rollout_generators(tmp_path):
     hc = c.run()
     assert len(hc) == 2 and c.generator.fn.__module__.startswith("_gcore_plugin_")
     assert abs(hc[0]["policy/grad_norm"] - ha[0]["policy/grad_norm"]) < 1e-5
+
+
+def test_agentic_rollouts_train_with_grpo_and_with_a_teacher():
+    """Multi-turn FrozenLake trajectories produced by the trainer's own engine (one generate call per turn): the
+    assistant tokens of all turns are the training targets, rollout log-probs line up with the trainer's, and the
+    same generator feeds on-policy distillation (teacher scores on the student's trajectories)."""
+    from test_grpo_cpu import make_cfg
+    from gcore_b200.agentic import FrozenLakeEnv
+    from gcore_b200.configs.config import PolicyConfig
+    from gcore_b200.models.config import get_preset
+    from gcore_b200.rollout_generator.generators import AgenticRolloutGenerator
+    from gcore_b200.trainer.grpo_trainer import GrpoTrainer
+
+    class Tok:   # byte-ish tokenizer inside the tiny vocabulary
+        def encode(self, t):
+            return [ord(c) % 250 + 3 for c in t]
+
+        def decode(self, ids):
+            return "".join(chr((i - 3) % 250) for i in ids)
+
+    for distill in (False, True):
+        torch.manual_seed(0)
+        cfg = make_cfg()
+        cfg.training.rollout_gbs, cfg.training.sampling_repeat_n, cfg.training.train_gbs = 2, 2, 4
+        cfg.sampler.infer_engine_configs[0].generate_max_tokens = 6
+        cfg.sampler.infer_engine_configs[0].max_model_len = 640
+        if distill:
+            cfg.teacher = PolicyConfig(recompute="none", without_ref=True)
+            cfg.ppo.advantage_type, cfg.ppo.loss_func = "on_policy_distill", "opd"
+        tr = GrpoTrainer(cfg, model_cfg=get_preset("tiny_llama", dtype="float32")).setup()
+        gen = AgenticRolloutGenerator(tr, cfg, lambda: FrozenLakeEnv(size=3), Tok(), max_turns=2, max_new_tokens=6)
+        samples = gen(iter([]), 0)
+        assert len(samples) == 4 and all(1 <= s["num_turns"] <= 2 for s in samples)
+        s = samples[0]
+        n_assist = int(s["mask"].sum())
+        assert n_assist == 6 * s["num_turns"] and s["tokens"].numel() > s["prompt_length"] + n_assist - 1
+        if not distill:
+            for x in samples:
+                x["rewards"] = torch.tensor(float(x["num_turns"]))   # any signal: longer episodes score higher
+        m = tr.train_on_samples(samples)
+        assert m["policy/grad_norm"] >= 0 and "ppo-metrics/pg_loss" in m
+        keep = s["mask"] > 0
+        assert torch.allclose(s["logprobs"][keep], s["rollout_log_probs"][keep], atol=2e-3)
+        if distill:
+            assert "teacher_logprobs" in s and float(s["advantages"][~keep].abs().sum()) == 0.0

@@ -228,7 +228,7 @@ class ExternalRolloutGenerator(BaseRolloutGenerator):
 
 
 def build_generator(trainer, config) -> BaseRolloutGenerator:
-    """``policy.rollout_gen_type``: base | dynamic | replay | external | two_turn_reflect; ``training.dynamic_sampling.enable`` selects
+    """``policy.rollout_gen_type``: base | dynamic | replay | external | two_turn_reflect | agentic; ``training.dynamic_sampling.enable`` selects
     dynamic as before.  ``task.rollout.{replay_path, record_path, replay_loop, reflect_tokens, reflect_top_k}`` configure them."""
     kind = config.policy.rollout_gen_type or "base"
     opt = dict((config.task or {}).get("rollout", {}) or {})
@@ -237,6 +237,20 @@ def build_generator(trainer, config) -> BaseRolloutGenerator:
                                                            bool(opt.get("replay_loop", False)))
     elif kind == "external":
         gen = ExternalRolloutGenerator(trainer, config)
+    elif kind == "agentic":
+        from ..agentic import make_env
+
+        class _ByteTok:   # stands in when the job has no tokenizer (synthetic runs)
+            def encode(self, t):
+                return [b % 250 + 3 for b in t.encode("utf-8")]
+
+            def decode(self, ids):
+                return bytes((i - 3) % 250 for i in ids).decode("latin-1")
+
+        env_name, env_kw = opt.get("env", "frozen_lake"), dict(opt.get("env_kwargs", {}) or {})
+        gen = AgenticRolloutGenerator(trainer, config, lambda: make_env(env_name, **env_kw),
+                                      getattr(trainer, "tokenizer", None) or _ByteTok(),
+                                      int(opt.get("max_turns", 4)), opt.get("max_new_tokens"))
     elif kind == "two_turn_reflect":
         gen = TwoTurnReflectGenerator(trainer, config, opt.get("reflect_tokens", []), int(opt.get("reflect_top_k", 1)))
     elif kind == "dynamic" or config.training.dynamic_sampling.enable:

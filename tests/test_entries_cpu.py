@@ -204,3 +204,19 @@ def test_agentic_rollouts_train_with_grpo_and_with_a_teacher():
         assert torch.allclose(s["logprobs"][keep], s["rollout_log_probs"][keep], atol=2e-3)
         if distill:
             assert "teacher_logprobs" in s and float(s["advantages"][~keep].abs().sum()) == 0.0
+
+
+def test_agentic_generator_from_config(tmp_path):
+    from gcore_b200.configs.base import load_config
+    from gcore_b200.configs.config import RlConfig
+    from gcore_b200.rollout_generator.generators import AgenticRolloutGenerator
+    from gcore_b200.trainer.rl_loop import RlLoop
+    y = _rl_yaml(tmp_path)
+    loop = RlLoop(load_config(RlConfig, y, [
+        "policy.rollout_gen_type=agentic", "+task.rollout.env=frozen_lake", "+task.rollout.env_kwargs.size=3",
+        "+task.rollout.max_turns=2", "+task.rollout.max_new_tokens=4", "training.rollout_gbs=2",
+        "training.sampling_repeat_n=2", "training.train_gbs=4", "training.total_ppo_step=1",
+        "sampler.infer_engine_configs.0.max_model_len=640"])).setup()
+    assert isinstance(loop.generator, AgenticRolloutGenerator)
+    hist = loop.run()
+    assert len(hist) == 1 and "rollout-rewards/mean" in hist[0]

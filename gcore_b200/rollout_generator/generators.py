@@ -232,6 +232,11 @@ def build_generator(trainer, config) -> BaseRolloutGenerator:
     dynamic as before.  ``task.rollout.{replay_path, record_path, replay_loop, reflect_tokens, reflect_top_k}`` configure them."""
     kind = config.policy.rollout_gen_type or "base"
     opt = dict((config.task or {}).get("rollout", {}) or {})
+    dbg = config.debug
+    if getattr(dbg, "replay_rollout_path", None):      # debug.replay_rollout_path / dump_rollout_path: same machinery
+        kind, opt["replay_path"] = "replay", dbg.replay_rollout_path
+    if getattr(dbg, "dump_rollout_path", None):
+        opt.setdefault("record_path", dbg.dump_rollout_path)
     if kind == "replay":
         gen: BaseRolloutGenerator = ReplayRolloutGenerator(trainer, config, opt["replay_path"],
                                                            bool(opt.get("replay_loop", False)))

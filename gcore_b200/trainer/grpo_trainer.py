@@ -221,10 +221,38 @@ class GrpoTrainer:
         metrics.update(self._rollout_metrics(samples))
         for k in ("compute_logps", "generate_ppo_data", "train_step", "update_weights"):
             metrics[f"time_perf/{k}"] = tm.last(k)
+        self._maybe_dump_tokens(samples)
         self.ppo_step += 1
         self.last_metrics = metrics
         self.last_samples = samples
         return metrics
+
+    def _maybe_dump_tokens(self, samples: List[dict]):
+        """Per-token dump of what was trained on (tokens, mask, trainer / reference / rollout log-probs, advantages,
+        rewards), one jsonl file per step and rank, every ``training.ppo_dump_metrics_interval`` steps
+        (the reference's offline per-token dumps: gpatch_v4/actor/grpo_train_actor.py:167-216)."""
+        t = self.cfg.training
+        every = getattr(t, "ppo_dump_metrics_interval", 0)
+        if not every or self.ppo_step % every:
+            return
+        import json
+        import os
+        d = getattr(t, "ppo_dump_metrics_dir", None) or os.path.join(self.cfg.report.log_dir or ".", "token_dumps")
+        os.makedirs(d, exist_ok=True)
+        rank = torch.distributed.get_rank() if torch.distributed.is_initialized() else 0
+        tok = getattr(self, "tokenizer", None)
+        with open(os.path.join(d, f"step{self.ppo_step:07d}_rank{rank}.jsonl"), "w") as f:
+            for s in samples:
+                row = {"prompt_length": int(s["prompt_length"]), "group_id": int(s.get("group_id", 0)),
+                       "reward": float(torch.as_tensor(s["rewards"]).sum())}
+                for k in ("tokens", "mask", "logprobs", "ref_logprobs", "rollout_log_probs", "teacher_logprobs",
+                          "advantages", "values"):
+                    if k in s and s[k] is not None:
+                        v = torch.as_tensor(s[k])
+                        row[k] = v.tolist() if k == "tokens" else [round(float(x), 6) for x in v.tolist()]
+                if tok is not None:
+                    row["text"] = tok.decode(torch.as_tensor(s["tokens"]).tolist())
+                f.write(json.dumps(row) + "\n")
 
     def update_weights(self):
         """Hands the updated weights to the rollout engine (zero-copy when storage is shared)."""

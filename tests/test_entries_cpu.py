@@ -1,5 +1,6 @@
 """Every entry point runs in-process on a tiny CPU model from a YAML file plus dotted overrides."""
 import json
+import os
 
 import pytest
 import torch
@@ -220,3 +221,27 @@ def test_agentic_generator_from_config(tmp_path):
     assert isinstance(loop.generator, AgenticRolloutGenerator)
     hist = loop.run()
     assert len(hist) == 1 and "rollout-rewards/mean" in hist[0]
+
+
+def test_per_token_dumps_and_debug_rollout_paths(tmp_path):
+    from gcore_b200.configs.base import load_config
+    from gcore_b200.configs.config import RlConfig
+    from gcore_b200.trainer.rl_loop import RlLoop
+    y = _rl_yaml(tmp_path)
+    rec = tmp_path / "dbg_rollouts.jsonl"
+    loop = RlLoop(load_config(RlConfig, y, ["training.ppo_dump_metrics_interval=1",
+                                            f"debug.dump_rollout_path={rec}"])).setup()
+    loop.run()
+    d = tmp_path / "logs" / "token_dumps"
+    files = sorted(os.listdir(d))
+    assert files == ["step0000000_rank0.jsonl", "step0000001_rank0.jsonl"]
+    rows = [json.loads(l) for l in open(d / files[0])]
+    assert len(rows) == 8
+    r = rows[0]
+    n = len(r["tokens"])
+    assert len(r["logprobs"]) == n and len(r["advantages"]) == n and len(r["mask"]) == n and "reward" in r
+    assert all(a == 0.0 for a in r["advantages"][:r["prompt_length"] - 1])       # nothing to learn on the prompt
+    assert len(open(rec).read().splitlines()) == 2
+    replay = RlLoop(load_config(RlConfig, y, [f"debug.replay_rollout_path={rec}"])).setup()
+    replay.trainer.rollout = None      # would raise if the engine were asked
+    assert len(replay.run()) == 2

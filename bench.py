@@ -50,20 +50,61 @@ def reference_arm(args):
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples the SM clock and the throttle reasons while the timed region runs: one NVML query per second from a
+    thread of this process (three calls per sample).  A polling ``nvidia-smi -lms 200`` per rank, the obvious way,
+    slowed the timed steps by 5-10 % against the warm-up steps (driver contention with the launch path), so it is
+    only the fallback when the NVML bindings are missing."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
+    REASONS = (("hw_slowdown", "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+               ("hw_thermal_slowdown", "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+               ("sw_thermal_slowdown", "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+               ("sw_power_cap", "nvmlClocksThrottleReasonSwPowerCap", 0x4))
 
-    def __init__(self, gpu_index: int):
-        self.idx = gpu_index
-        self.rows = []
-        self.proc = None
+    def __init__(self, gpu_index: int, period_s: float = 1.0):
+        self.idx, self.period = gpu_index, period_s
+        self.rows = []          # nvidia-smi fallback: csv rows
+        self.samples = []       # NVML: (sm_mhz, max_mhz, reasons bitmask)
+        self.proc = self.thread = self.nvml = self.handle = None
+        self._stop = threading.Event()
+
+    def _open_nvml(self):
+        import pynvml
+        import torch
+        pynvml.nvmlInit()
+        h = None
+        try:   # the CUDA device of this rank by UUID (CUDA_VISIBLE_DEVICES may renumber the devices)
+            uuid = str(torch.cuda.get_device_properties(self.idx).uuid)
+            h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+        except Exception:  # noqa: BLE001
+            h = pynvml.nvmlDeviceGetHandleByIndex(self.idx)
+        self.nvml, self.handle = pynvml, h
+
+    def _poll(self):
+        n = self.nvml
+        get_reasons = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            getattr(n, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        mx = n.nvmlDeviceGetMaxClockInfo(self.handle, n.NVML_CLOCK_SM)
+        while not self._stop.is_set():
+            try:
+                self.samples.append((n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM), mx,
+                                     int(get_reasons(self.handle))))
+            except Exception:  # noqa: BLE001
+                pass
+            self._stop.wait(self.period)
 
     def start(self):
         try:
+            self._open_nvml()
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:  # noqa: BLE001 - no NVML bindings: fall back to the command-line tool, at a slow rate
+            self.nvml = None
+        try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.idx)], stdout=subprocess.PIPE,
+                                          "-lms", "1000", "-i", str(self.idx)], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -75,6 +116,18 @@ class ClockSampler:
             self.rows.append([x.strip() for x in line.split(",")])
 
     def stop(self):
+        if self.nvml is not None:
+            self._stop.set()
+            self.thread.join(timeout=5)
+            sm = [s[0] for s in self.samples]
+            reasons = set()
+            for _, _, bits in self.samples:
+                for name, const, default in self.REASONS:
+                    if bits & int(getattr(self.nvml, const, default)):
+                        reasons.add(name)
+            return {"sm_mhz": statistics.median(sm) if sm else None,
+                    "sm_max_mhz": float(self.samples[0][1]) if self.samples else None, "reasons": sorted(reasons),
+                    "samples": len(sm), "source": "nvml"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -93,7 +146,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "source": "nvidia-smi"}
 
 
 def build_config(args, world):

@@ -10,7 +10,6 @@ that raises; it is not provided here.
 from __future__ import annotations
 
 import io
-import json
 import threading
 import urllib.request
 from typing import Any, Callable, Dict, List, Optional

@@ -10,7 +10,7 @@ from __future__ import annotations
 import copy
 import dataclasses
 import typing
-from dataclasses import MISSING, dataclass, field, fields, is_dataclass
+from dataclasses import dataclass, field, fields, is_dataclass
 from typing import Any, get_args, get_origin, get_type_hints
 
 import yaml

@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import io
 import pickle
-from typing import Dict, List, Sequence, Tuple
+from typing import List, Sequence, Tuple
 
 import torch
 import torch.distributed as dist

@@ -25,7 +25,6 @@ from ..loss import policy_loss as PL
 from ..models.config import ModelConfig, build_model_config
 from ..models.gpt import GPTModel
 from ..models.lora import apply_lora, verify_lora_weight_consistency
-from ..ops import _lib
 from ..ops.rl import grpo_loss as fused_grpo_loss
 from ..ops.vocab import linear_logprob_entropy
 from ..utils import io_counters

@@ -9,8 +9,6 @@ Dispatch semantics follow ``DeepseekV4Experts._forward_eager`` (gpatch_v4/models
 """
 from __future__ import annotations
 
-import math
-from typing import Optional
 
 import torch
 import torch.nn as nn

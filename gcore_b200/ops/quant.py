@@ -6,7 +6,6 @@ fp32 or power-of-two scales, e2m1 1x32 with e8m0 scales, and quantise->dequantis
 """
 from __future__ import annotations
 
-import math
 
 import torch
 

@@ -13,7 +13,6 @@ import torch.distributed as dist
 from ..checkpoint.torch_dist import load_checkpoint, read_latest_step, save_checkpoint, wait_for_async_save
 from ..configs.base import import_from_path
 from ..core import parallel_state as ps
-from ..core.advantage import compute_advantages
 from ..data.datasets import default_dataset_fn
 from ..orches.failure import FaultInjector, Heartbeat
 from ..rollout_generator.generators import StaleRolloutQueue, build_generator

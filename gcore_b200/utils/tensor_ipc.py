@@ -6,7 +6,6 @@ to a separate serving process; inside one job the trainer and the rollout engine
 from __future__ import annotations
 
 import pickle
-from typing import Any, Tuple
 
 import torch
 from torch.multiprocessing.reductions import reduce_tensor

@@ -36,6 +36,9 @@ def all_to_all_uneven(x, out_splits, in_splits, group):
     return _AllToAll.apply(x, out_splits, in_splits, group)
 
 
+CHECK_A2A = {"enabled": False}   # switched on by ``debug.check_a2a_legality``: every exchange is validated first
+
+
 def check_a2a_legality(in_splits, out_splits, group):
     """Debug check: every rank's send sizes must equal its peers' receive sizes
     (gpatch_v4/utils/dynamic_cp_utils.py:441-555 does the same before a fused reroute)."""
@@ -74,6 +77,8 @@ def ep_moe_forward(layer, x, idx, w):
     dist.all_to_all_single(recv_cnt, cnt, group=group)
     in_splits = cnt.sum(1).tolist()       # rows this rank sends to each peer (host sync, like the reference)
     out_splits = recv_cnt.sum(1).tolist()  # rows this rank receives from each peer
+    if CHECK_A2A["enabled"]:               # debug.check_a2a_legality
+        check_a2a_legality(in_splits, out_splits, group)
     recv_rows = all_to_all_uneven(send_rows, out_splits, in_splits, group)
     recv_e = torch.empty(sum(out_splits), dtype=send_e.dtype, device=x.device)
     dist.all_to_all_single(recv_e, send_e.contiguous(), out_splits, in_splits, group=group)

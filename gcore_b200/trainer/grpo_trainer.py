@@ -85,6 +85,9 @@ class GrpoTrainer:
             if cfg.teacher.hf_model_path:
                 from ..checkpoint.hf import load_hf
                 load_hf(self.teacher, cfg.teacher.hf_model_path)
+        if cfg.debug.check_a2a_legality:
+            from ..parallel import ep as ep_mod
+            ep_mod.CHECK_A2A["enabled"] = True
         model = self.policy.model
         # with LoRA only the adapted projections differ from the frozen base: the rollout engine then owns copies of
         # those tensors (base + delta, rewritten at every resync) and shares the storage of all the others
@@ -190,6 +193,9 @@ class GrpoTrainer:
         """Everything after rollout + reward: prev / ref log-probs, advantages, policy (and critic) update, weight
         hand-over.  ``samples`` may come from an earlier weight version (stale rollouts)."""
         cfg, t, tm = self.cfg, self.cfg.training, self.timers
+        if cfg.debug.check_rollout_batches:
+            from ..gdebug import check_rollout_batches
+            check_rollout_batches(samples)
         tm.start("compute_logps")
         if not cfg.ppo.skip_prev_logps:
             self.policy.compute_log_probs(samples, use_ref=False)
@@ -264,6 +270,11 @@ class GrpoTrainer:
         else:
             from ..rollout.weight_sync import sync_weights
             sync_weights(self.policy, self.engine)
+        if self.cfg.debug.debug_update_weight and not self.lora and not self.serve_fp8:
+            from ..rollout.weight_sync import verify
+            bad = verify(self.policy, self.engine)
+            if bad:
+                raise RuntimeError(f"rollout weights differ from the trainer's after the hand-over: {bad[:6]}")
         if self.serve_fp8:
             # the engine's dense projections are re-quantised (e4m3, 128x128 scales) from the weights just handed over
             self.engine.quantize_weights_fp8()

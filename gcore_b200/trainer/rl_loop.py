@@ -103,6 +103,14 @@ class RlLoop:
     def run(self):
         t = self.cfg.training
         total = t.exit_step or t.total_ppo_step or 0
+        tracer = None
+        if self.cfg.debug.trace_python_calls:
+            from ..utils.python_call_tracer import PythonCallTracer
+            roots = self.cfg.debug.trace_roots or [os.path.dirname(os.path.dirname(os.path.abspath(__file__)))]
+            out = os.path.join(self.cfg.report.log_dir or ".", f"python_calls_rank{self.rank}.log")
+            os.makedirs(os.path.dirname(out), exist_ok=True)
+            tracer = PythonCallTracer(roots, out)
+            tracer.__enter__()
         while self.trainer.ppo_step < total:
             m = self.one_step()
             if self.rank == 0:
@@ -110,6 +118,8 @@ class RlLoop:
                               f"step {m['time_perf/step']:.2f}s")
             if t.save_interval and self.trainer.ppo_step % t.save_interval == 0:
                 self.save()
+        if tracer is not None:
+            tracer.__exit__(None, None, None)
         if self.reporter:
             self.reporter.close()
         wait_for_async_save()

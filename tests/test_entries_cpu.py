@@ -245,3 +245,26 @@ def test_per_token_dumps_and_debug_rollout_paths(tmp_path):
     replay = RlLoop(load_config(RlConfig, y, [f"debug.replay_rollout_path={rec}"])).setup()
     replay.trainer.rollout = None      # would raise if the engine were asked
     assert len(replay.run()) == 2
+
+
+def test_debug_flags_are_honoured(tmp_path):
+    """debug.debug_update_weight verifies the hand-over, check_rollout_batches validates the samples, and
+    trace_python_calls writes a call trace of the package."""
+    from gcore_b200.configs.base import load_config
+    from gcore_b200.configs.config import RlConfig
+    from gcore_b200.trainer.rl_loop import RlLoop
+    y = _rl_yaml(tmp_path)
+    loop = RlLoop(load_config(RlConfig, y, ["debug.debug_update_weight=true", "debug.trace_python_calls=true",
+                                            "training.total_ppo_step=1", "policy.share_rollout_weights=false"])).setup()
+    loop.run()     # separate rollout copy: the verification really compares two sets of tensors
+    trace = open(tmp_path / "logs" / "python_calls_rank0.log").read()
+    assert "train_on_samples" in trace and "rollout" in trace
+    # a malformed sample is caught before any compute
+    bad = [{"tokens": torch.tensor([1, 2, 3]), "prompt_length": 5, "rewards": torch.tensor(0.0), "group_id": 0}]
+    with pytest.raises(AssertionError, match="prompt_length"):
+        loop.trainer.train_on_samples(bad)
+    # a rollout copy that went out of sync is reported
+    with torch.no_grad():
+        loop.trainer.engine.w.layers[0].o_w.add_(1.0)
+    from gcore_b200.rollout.weight_sync import verify
+    assert verify(loop.trainer.policy, loop.trainer.engine)

@@ -608,7 +608,7 @@ class TrainingEngine:
         lora_of = {}
         if merged_lora:
             for n, m in self.model.named_modules():
-                if isinstance(m, ParallelLinear) and m.lora is not None:
+                if (isinstance(m, ParallelLinear) or type(m).__name__ == "Router") and getattr(m, "lora", None) is not None:
                     lora_of[n + ".weight"] = m.lora
         for n, p in self.model.named_parameters():
             if getattr(p, "is_lora", False):

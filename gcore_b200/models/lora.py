@@ -104,6 +104,20 @@ def apply_lora(model: nn.Module, lora_cfg, seed: int = 0) -> Dict[str, LoRAAdapt
             b.tp_mode = "column" if mod.mode == "column" else "none"
         mod.lora = ad
         adapters[name] = ad
+    if "router" in lora_cfg.target_modules:
+        # the routing matrix [experts, hidden] is a plain fp32 parameter: its adapter is replicated over TP like it
+        from .moe import Router
+        for name, mod in model.named_modules():
+            if isinstance(mod, Router) and not any(e in name for e in lora_cfg.exclude_modules):
+                w = mod.weight
+                ad = LoRAAdapter(w.shape[1], [w.shape[0]], lora_cfg.rank, lora_cfg.alpha, lora_cfg.dropout, w.dtype,
+                                 w.device, lora_cfg.lora_A_init_method, lora_cfg.lora_B_init_method,
+                                 seed=(seed + zlib.crc32(name.encode())) & 0x7FFFFFFF)
+                ad.lora_A.tp_mode = "none"
+                for b in ad.lora_B:
+                    b.tp_mode = "none"
+                mod.lora = ad
+                adapters[name] = ad
     if lora_cfg.check_lora_all_coverage:
         missing = [n for n, m in model.named_modules() if isinstance(m, ParallelLinear) and m.lora is None
                    and n.split(".")[-1] in lora_cfg.target_modules]
@@ -144,6 +158,8 @@ def merge_lora_(model) -> None:
     with torch.no_grad():
         for m in model.modules():
             if isinstance(m, ParallelLinear) and m.lora is not None:
+                m.weight.add_(m.lora.delta_weight().to(m.weight.dtype))
+            elif type(m).__name__ == "Router" and getattr(m, "lora", None) is not None:
                 m.weight.add_(m.lora.delta_weight().to(m.weight.dtype))
 
 

@@ -52,11 +52,14 @@ class Router(nn.Module):
             self.register_buffer("expert_bias", torch.zeros(cfg.num_experts, dtype=torch.float32, device=device))
         else:
             self.expert_bias = None
+        self.lora = None   # optional low-rank adapter on the routing matrix ("router" in lora.target_modules)
 
     def forward(self, x):
         cfg = self.cfg
         E, K = cfg.num_experts, cfg.moe_top_k
         logits = torch.nn.functional.linear(x.float(), self.weight)  # [T, E]
+        if self.lora is not None:
+            logits = logits + self.lora(x.float())
         replay = RouterReplay.get(self.layer_idx) if RouterReplay.mode == "replay" else None
         if cfg.moe_router_type == "softmax":
             probs = torch.softmax(logits, dim=-1)

@@ -185,3 +185,29 @@ def test_grpo_with_fp8_base_lora_and_mla_moe_policy():
     assert m["policy/grad_norm"] > 0 and abs(m["ppo-metrics/ratio"] - 1.0) < 1e-3
     tr.step(prompts)
     assert torch.equal(base, tr.policy.model.decoder.layers[1].self_attention.linear_kv_up_proj.weight)  # frozen base
+
+
+def test_lora_on_the_router_trains_and_reaches_the_rollout_engine():
+    """"router" in lora.target_modules: the routing matrix gets an adapter (replicated), it trains with the base frozen,
+    and the rollout engine (which runs the shared MoE module) routes with it."""
+    from gcore_b200.models.config import ModelConfig
+    mcfg = ModelConfig(arch="qwen3_moe", num_layers=2, hidden_size=128, num_attention_heads=4, num_kv_heads=2,
+                       ffn_hidden_size=256, vocab_size=512, num_experts=8, moe_top_k=2, moe_ffn_hidden_size=64,
+                       moe_aux_loss_coef=1e-3, dtype="float32", qk_layernorm=True)
+    cfg = make_cfg()
+    cfg.policy.lora.rank, cfg.policy.lora.alpha = 4, 8
+    cfg.policy.lora.target_modules = ["linear_qkv", "router"]
+    torch.manual_seed(1)
+    tr = GrpoTrainer(cfg, model_cfg=mcfg, reward_fn=reward_has_small_token).setup()
+    routers = [n for n in tr.policy.adapters if n.endswith("router")]
+    assert len(routers) == 2
+    r0 = tr.policy.model.decoder.layers[0].mlp.router
+    base = r0.weight.detach().clone()
+    g = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(3, 512, (8,), generator=g).tolist() for _ in range(4)]
+    for _ in range(3):
+        m = tr.step(prompts)
+    assert torch.equal(base, r0.weight) and float(r0.lora.lora_B[0].detach().abs().sum()) > 0   # only the adapter moved
+    s = tr.last_samples[0]
+    P, S = s["prompt_length"], s["sequence_length"]
+    assert torch.allclose(s["logprobs"][P - 1:S - 1], s["rollout_log_probs"][P - 1:S - 1], atol=2e-3)

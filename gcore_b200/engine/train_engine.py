@@ -610,6 +610,10 @@ class TrainingEngine:
             for n, m in self.model.named_modules():
                 if (isinstance(m, ParallelLinear) or type(m).__name__ == "Router") and getattr(m, "lora", None) is not None:
                     lora_of[n + ".weight"] = m.lora
+                elif type(m).__name__ == "Experts":
+                    for leaf in ("fc1", "fc2"):
+                        if getattr(m, "lora_" + leaf, None) is not None:
+                            lora_of[f"{n}.linear_{leaf}.weight"] = getattr(m, "lora_" + leaf)
         for n, p in self.model.named_parameters():
             if getattr(p, "is_lora", False):
                 continue

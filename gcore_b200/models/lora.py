@@ -64,6 +64,46 @@ class LoRAAdapter(nn.Module):
         return torch.cat(parts, 0) * self.scale
 
 
+class ExpertLoRA(nn.Module):
+    """Adapter of a grouped expert projection ``[E, out, in]`` applied to the expert-sorted token rows: one A / B pair
+    shared by all local experts (``shared=True``: two dense products over all rows) or a pair per expert (rows are
+    taken expert by expert from the offsets of the dispatch plan)."""
+
+    def __init__(self, num_experts: int, in_features: int, out_features: int, rank: int, alpha: float, shared: bool,
+                 dtype, device, seed: int = 0):
+        super().__init__()
+        self.scale, self.rank, self.shared, self.num_experts = alpha / rank, rank, shared, num_experts
+        n = 1 if shared else num_experts
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        bound = math.sqrt(6.0 / (in_features + rank))
+        self.lora_A = nn.Parameter(((torch.rand(n, rank, in_features, generator=g) * 2 - 1) * bound).to(dtype).to(device))
+        self.lora_B = nn.Parameter(torch.zeros(n, out_features, rank, dtype=dtype, device=device))
+        for p in (self.lora_A, self.lora_B):
+            p.is_lora = True
+            # a shared adapter is replicated like a dense parameter; per-expert adapters live with their experts
+            p.tp_mode = "none" if shared else "expert"
+            if not shared:
+                p.is_expert = True
+
+    def forward(self, x_perm, offsets):
+        x_perm = x_perm.to(self.lora_A.dtype)
+        if self.shared:
+            return torch.nn.functional.linear(torch.nn.functional.linear(x_perm, self.lora_A[0]), self.lora_B[0]) * self.scale
+        out = x_perm.new_zeros(x_perm.shape[0], self.lora_B.shape[1])
+        bounds = offsets.tolist()
+        for e in range(self.num_experts):
+            a, b = bounds[e], bounds[e + 1]
+            if b > a:
+                out[a:b] = torch.nn.functional.linear(torch.nn.functional.linear(x_perm[a:b], self.lora_A[e]),
+                                                      self.lora_B[e]) * self.scale
+        return out
+
+    def delta_weight(self) -> torch.Tensor:
+        """``[E, out, in]`` dense update."""
+        d = torch.matmul(self.lora_B.float(), self.lora_A.float()) * self.scale
+        return d.expand(self.num_experts, -1, -1) if self.shared else d
+
+
 def _splits_for(name: str, module, cfg, tp_size: int, canonical: bool) -> List[int]:
     if not canonical:
         return [module.out_local]
@@ -104,6 +144,21 @@ def apply_lora(model: nn.Module, lora_cfg, seed: int = 0) -> Dict[str, LoRAAdapt
             b.tp_mode = "column" if mod.mode == "column" else "none"
         mod.lora = ad
         adapters[name] = ad
+    # grouped expert projections: `linear_fc1` / `linear_fc2` among the targets also adapt the experts, with one
+    # adapter per layer (`share_expert_adapters`) or one per expert
+    from .moe import Experts
+    for name, mod in model.named_modules():
+        if not isinstance(mod, Experts) or any(e in name for e in lora_cfg.exclude_modules):
+            continue
+        for leaf in ("linear_fc1", "linear_fc2"):
+            if leaf not in lora_cfg.target_modules:
+                continue
+            w = getattr(mod, leaf).weight
+            ad = ExpertLoRA(w.shape[0], w.shape[2], w.shape[1], lora_cfg.rank, lora_cfg.alpha,
+                            lora_cfg.share_expert_adapters, dtype or w.dtype, w.device,
+                            seed=(seed + zlib.crc32(f"{name}.{leaf}".encode())) & 0x7FFFFFFF)
+            setattr(mod, "lora_" + leaf[len("linear_"):], ad)
+            adapters[f"{name}.{leaf}"] = ad
     if "router" in lora_cfg.target_modules:
         # the routing matrix [experts, hidden] is a plain fp32 parameter: its adapter is replicated over TP like it
         from .moe import Router
@@ -161,6 +216,12 @@ def merge_lora_(model) -> None:
                 m.weight.add_(m.lora.delta_weight().to(m.weight.dtype))
             elif type(m).__name__ == "Router" and getattr(m, "lora", None) is not None:
                 m.weight.add_(m.lora.delta_weight().to(m.weight.dtype))
+            elif type(m).__name__ == "Experts":
+                for leaf in ("fc1", "fc2"):
+                    ad = getattr(m, "lora_" + leaf, None)
+                    if ad is not None:
+                        w = getattr(m, "linear_" + leaf).weight
+                        w.add_(ad.delta_weight().to(w.dtype))
 
 
 def lora_state_dict(model) -> Dict[str, torch.Tensor]:

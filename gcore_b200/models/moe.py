@@ -170,11 +170,17 @@ class Experts(nn.Module):
         self.linear_fc2.weight.tp_mode = "expert"
         self.linear_fc1.weight.is_expert = True
         self.linear_fc2.weight.is_expert = True
+        self.lora_fc1 = self.lora_fc2 = None   # models/lora.py::ExpertLoRA when the experts are adapted
 
     def forward(self, x_perm, offsets):
         h = grouped_linear(x_perm, self.linear_fc1.weight, offsets)
+        if self.lora_fc1 is not None:
+            h = h + self.lora_fc1(x_perm, offsets).to(h.dtype)
         h = fused.swiglu(h)
-        return grouped_linear(h, self.linear_fc2.weight, offsets)
+        y = grouped_linear(h, self.linear_fc2.weight, offsets)
+        if self.lora_fc2 is not None:
+            y = y + self.lora_fc2(h, offsets).to(y.dtype)
+        return y
 
 
 class MoELayer(nn.Module):

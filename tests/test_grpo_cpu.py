@@ -211,3 +211,51 @@ def test_lora_on_the_router_trains_and_reaches_the_rollout_engine():
     s = tr.last_samples[0]
     P, S = s["prompt_length"], s["sequence_length"]
     assert torch.allclose(s["logprobs"][P - 1:S - 1], s["rollout_log_probs"][P - 1:S - 1], atol=2e-3)
+
+
+def test_lora_on_grouped_experts_shared_and_per_expert():
+    """`linear_fc1` / `linear_fc2` among the LoRA targets also adapt the grouped expert projections: one adapter per
+    layer or one per expert; the adapted forward equals the forward with the deltas merged into the expert weights."""
+    from gcore_b200.configs.config import LoRAConfig
+    from gcore_b200.models.config import ModelConfig
+    from gcore_b200.models.gpt import GPTModel
+    from gcore_b200.models.lora import ExpertLoRA, apply_lora, merge_lora_
+    mcfg = ModelConfig(arch="qwen3_moe", num_layers=2, hidden_size=64, num_attention_heads=2, num_kv_heads=2,
+                       ffn_hidden_size=128, vocab_size=128, num_experts=4, moe_top_k=2, moe_ffn_hidden_size=32,
+                       dtype="float32")
+    t = torch.randint(3, 128, (14,))
+    pos, cu = torch.arange(14, dtype=torch.int32), torch.tensor([0, 14], dtype=torch.int32)
+    for shared in (True, False):
+        torch.manual_seed(0)
+        model = GPTModel(mcfg, recompute="none")
+        ads = apply_lora(model, LoRAConfig(rank=4, alpha=8, target_modules=["linear_fc1", "linear_fc2"],
+                                           share_expert_adapters=shared), seed=3)
+        ex = [a for a in ads.values() if isinstance(a, ExpertLoRA)]
+        assert len(ex) == 4 and ex[0].lora_A.shape[0] == (1 if shared else 4)
+        assert not model.decoder.layers[0].mlp.experts.linear_fc1.weight.requires_grad and ex[0].lora_A.requires_grad
+        # gradients reach the adapters through the whole model
+        with torch.no_grad():
+            for a in ex:
+                a.lora_B.normal_(0, 0.3)
+        h, _ = model(t, pos, cu, 14)
+        h.float().pow(2).sum().backward()
+        assert all(a.lora_A.grad is not None and a.lora_B.grad.abs().sum() > 0 for a in ex)
+        # adapted experts == experts with the deltas merged (fixed routing: the expert module is called directly)
+        experts = model.decoder.layers[0].mlp.experts
+        offsets = torch.tensor([0, 5, 5, 12, 16], dtype=torch.int32)
+        x_perm = torch.randn(16, 64)
+        with torch.no_grad():
+            ref = experts(x_perm, offsets)
+            saved = [(a, a.lora_B.detach().clone()) for a in ex]
+            for a in ex:
+                a.lora_B.zero_()
+            plain = experts(x_perm, offsets)
+            for a, b in saved:
+                a.lora_B.copy_(b)
+            merge_lora_(model)
+            for a in ex:
+                a.lora_B.zero_()
+            merged = experts(x_perm, offsets)
+        # expert GEMM outputs are rounded to bf16, so "equal" is to bf16 resolution - far below what the adapters change
+        err, effect = float((ref - merged).abs().max()), float((ref - plain).abs().max())
+        assert err < 0.03 * max(1.0, float(ref.abs().max())) and effect > 5 * err, (err, effect)

@@ -253,6 +253,11 @@ def main():
                   f"logps {m['time_perf/compute_logps']:.2f}s train {m['time_perf/train_step']:.2f}s "
                   f"tokens {m['rollout-metrics/total_tokens']:.0f}", file=sys.stderr, flush=True)
     _lib.check_device_errors()
+    # the model, engine and optimizer objects built so far are permanent: keep the cyclic collector from walking them
+    # every time the per-token Python objects of a rollout trigger a full collection
+    import gc
+    gc.collect()
+    gc.freeze()
     io_counters.reset()
     launches0 = trainer_launches(trainer)
     sampler = ClockSampler(local)

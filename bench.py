@@ -68,6 +68,11 @@ class ClockSampler:
         self.samples = []       # NVML: (sm_mhz, max_mhz, reasons bitmask)
         self.proc = self.thread = self.nvml = self.handle = None
         self._stop = threading.Event()
+        self.t_mark = 0.0       # samples older than this (taken while the sampler was starting up) are dropped
+
+    def mark(self):
+        """Start of the timed region: only samples from here on are reported."""
+        self.t_mark = time.time()
 
     def _open_nvml(self):
         import pynvml
@@ -89,7 +94,7 @@ class ClockSampler:
         while not self._stop.is_set():
             try:
                 self.samples.append((n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM), mx,
-                                     int(get_reasons(self.handle))))
+                                     int(get_reasons(self.handle)), time.time()))
             except Exception:  # noqa: BLE001
                 pass
             self._stop.wait(self.period)
@@ -113,15 +118,16 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
+            self.rows.append([x.strip() for x in line.split(",")] + [time.time()])
 
     def stop(self):
         if self.nvml is not None:
             self._stop.set()
             self.thread.join(timeout=5)
+            self.samples = [x for x in self.samples if x[3] >= self.t_mark]
             sm = [s[0] for s in self.samples]
             reasons = set()
-            for _, _, bits in self.samples:
+            for _, _, bits, _ in self.samples:
                 for name, const, default in self.REASONS:
                     if bits & int(getattr(self.nvml, const, default)):
                         reasons.add(name)
@@ -137,6 +143,8 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         for r in self.rows:
+            if r[-1] < self.t_mark:
+                continue
             try:
                 sm.append(float(r[1]))
                 mx.append(float(r[2]))
@@ -246,7 +254,12 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local)
     for i in range(args.warmup):
+        if i == args.warmup - 1:
+            # the sampler comes up during the last untimed step, so that whatever its start costs (NVML attach, or the
+            # fork of the fallback tool) is not inside the timed region; only samples taken after `mark()` are reported
+            sampler.start()
         m = run_step(i)
         if rank == 0:
             print(f"[warmup {i}] step {m['time_perf/step']:.2f}s rollout {m['time_perf/rollout']:.2f}s "
@@ -260,9 +273,10 @@ def main():
     gc.freeze()
     io_counters.reset()
     launches0 = trainer_launches(trainer)
-    sampler = ClockSampler(local)
+    if args.warmup == 0:
+        sampler.start()
     barrier()
-    sampler.start()
+    sampler.mark()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
     ev0.record()

@@ -21,7 +21,7 @@ from .layout import export_full_weights, load_hf_weights
 
 def hf_config_dict(cfg) -> dict:
     arch = {"llama": "LlamaForCausalLM", "qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
-            "qwen3_moe": "Qwen3MoeForCausalLM", "deepseek_v3": "DeepseekV3ForCausalLM",
+            "qwen3_moe": "Qwen3MoeForCausalLM", "qwen2_moe": "Qwen2MoeForCausalLM", "deepseek_v3": "DeepseekV3ForCausalLM",
             "mistral": "MistralForCausalLM", "gpt_oss": "GptOssForCausalLM",
             "seed_oss": "SeedOssForCausalLM"}.get(cfg.arch, "LlamaForCausalLM")
     d = {"architectures": [arch], "model_type": cfg.arch if cfg.arch != "llama" else "llama",
@@ -35,6 +35,8 @@ def hf_config_dict(cfg) -> dict:
         d.update(num_experts=cfg.num_experts, n_routed_experts=cfg.num_experts, num_experts_per_tok=cfg.moe_top_k,
                  moe_intermediate_size=cfg.moe_ffn_hidden_size, norm_topk_prob=cfg.moe_norm_topk_prob,
                  router_aux_loss_coef=cfg.moe_aux_loss_coef)
+        if getattr(cfg, "moe_shared_expert_gate", False):
+            d["shared_expert_intermediate_size"] = cfg.moe_shared_expert_ffn
     if cfg.use_mla:
         d.update(q_lora_rank=cfg.q_lora_rank or None, kv_lora_rank=cfg.kv_lora_rank,
                  qk_nope_head_dim=cfg.qk_nope_head_dim, qk_rope_head_dim=cfg.qk_rope_head_dim,

@@ -136,6 +136,11 @@ def assign_from_chunks(name: str, param: torch.Tensor, cfg, tp_rank, tp_size, ep
 
 
 # ------------------------------------------------------------------------------------------------ HF names
+def _hf_shared(cfg) -> str:
+    """HF prefix of the shared expert: ``shared_expert.`` for qwen2_moe, ``shared_experts.`` otherwise."""
+    return "shared_expert." if getattr(cfg, "arch", "") == "qwen2_moe" else "shared_experts."
+
+
 def hf_name_map(cfg) -> Dict[str, str]:
     """internal parameter name pattern -> HF name (``{i}`` layer index, ``{e}`` expert index)."""
     m = {
@@ -150,7 +155,9 @@ def hf_name_map(cfg) -> Dict[str, str]:
         "decoder.layers.{i}.self_attention.sinks": "model.layers.{i}.self_attn.sinks",
         "decoder.layers.{i}.mlp.linear_fc2.weight": "model.layers.{i}.mlp.down_proj.weight",
         "decoder.layers.{i}.mlp.router.weight": "model.layers.{i}.mlp.gate.weight",
-        "decoder.layers.{i}.mlp.shared_experts.linear_fc2.weight": "model.layers.{i}.mlp.shared_experts.down_proj.weight",
+        "decoder.layers.{i}.mlp.shared_experts.linear_fc2.weight":
+            "model.layers.{i}.mlp." + _hf_shared(cfg) + "down_proj.weight",
+        "decoder.layers.{i}.mlp.shared_expert_gate.weight": "model.layers.{i}.mlp.shared_expert_gate.weight",
         # MLA
         "decoder.layers.{i}.self_attention.linear_q_down_proj.weight": "model.layers.{i}.self_attn.q_a_proj.weight",
         "decoder.layers.{i}.self_attention.linear_q_up_proj.weight": "model.layers.{i}.self_attn.q_b_proj.weight",
@@ -199,7 +206,7 @@ def full_hf_tensors(name: str, t: torch.Tensor, cfg, tp_mode: str, tp_group, ep_
     if rest in ("mlp.linear_fc1.weight", "mlp.shared_experts.linear_fc1.weight"):
         shared = "shared_experts" in rest
         g, u = t.chunk(2, 0)
-        pre = f"model.layers.{li}.mlp." + ("shared_experts." if shared else "")
+        pre = f"model.layers.{li}.mlp." + (_hf_shared(cfg) if shared else "")
         grp = None if shared else tp_group
         yield pre + "gate_proj.weight", _gather_tp(g, 0, grp)
         yield pre + "up_proj.weight", _gather_tp(u, 0, grp)
@@ -263,7 +270,7 @@ def load_hf_weights(model, hf_tensors: Dict[str, torch.Tensor], tp_rank: int = 0
                 p.copy_(torch.cat(parts, 0))
             elif rest in ("mlp.linear_fc1.weight", "mlp.shared_experts.linear_fc1.weight"):
                 shared = "shared_experts" in rest
-                pre = f"model.layers.{li}.mlp." + ("shared_experts." if shared else "")
+                pre = f"model.layers.{li}.mlp." + (_hf_shared(cfg) if shared else "")
                 n, r = (1, 0) if shared else (tp, tp_rank)
                 p.copy_(torch.cat([hf_tensors[pre + "gate_proj.weight"].chunk(n, 0)[r],
                                    hf_tensors[pre + "up_proj.weight"].chunk(n, 0)[r]], 0))

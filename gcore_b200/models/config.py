@@ -35,6 +35,7 @@ class ModelConfig:
     moe_top_k: int = 0
     moe_ffn_hidden_size: int = 0
     moe_shared_expert_ffn: int = 0
+    moe_shared_expert_gate: bool = False   # qwen2_moe: the shared expert's output is scaled by sigmoid(x . g)
     moe_router_type: str = "softmax"  # softmax | sigmoid_group
     moe_n_group: int = 1
     moe_topk_group: int = 1
@@ -195,6 +196,13 @@ def from_hf_config(hf: Dict[str, Any]) -> ModelConfig:
     if mt == "qwen3_moe":
         kw.update(num_experts=hf["num_experts"], moe_top_k=hf["num_experts_per_tok"],
                   moe_ffn_hidden_size=hf["moe_intermediate_size"], moe_norm_topk_prob=hf.get("norm_topk_prob", True),
+                  moe_aux_loss_coef=hf.get("router_aux_loss_coef", 0.0))
+    if mt == "qwen2_moe":
+        kw.update(arch="qwen2_moe", qkv_bias=True, num_experts=hf["num_experts"], moe_top_k=hf["num_experts_per_tok"],
+                  moe_ffn_hidden_size=hf["moe_intermediate_size"],
+                  moe_shared_expert_ffn=hf.get("shared_expert_intermediate_size", 0),
+                  moe_shared_expert_gate=bool(hf.get("shared_expert_intermediate_size", 0)),
+                  moe_norm_topk_prob=hf.get("norm_topk_prob", False),
                   moe_aux_loss_coef=hf.get("router_aux_loss_coef", 0.0))
     if mt == "deepseek_v3":
         kw.update(use_mla=True, q_lora_rank=hf.get("q_lora_rank") or 0, kv_lora_rank=hf["kv_lora_rank"],

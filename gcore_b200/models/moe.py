@@ -197,6 +197,13 @@ class MoELayer(nn.Module):
             self.shared_experts = MLP(cfg, cfg.moe_shared_expert_ffn, 1, device)
         else:
             self.shared_experts = None
+        self.shared_expert_gate = None
+        if self.shared_experts is not None and getattr(cfg, "moe_shared_expert_gate", False):
+            dt = {"bfloat16": torch.bfloat16, "float32": torch.float32}[cfg.dtype]
+            self.shared_expert_gate = nn.Module()
+            self.shared_expert_gate.weight = nn.Parameter(torch.zeros(1, cfg.hidden_size, dtype=dt, device=device))
+            self.shared_expert_gate.weight.tp_mode = "none"
+            self.shared_expert_gate.weight.sequence_parallel = True
 
     def forward(self, x):
         cfg = self.cfg
@@ -216,5 +223,8 @@ class MoELayer(nn.Module):
             y_perm = self.experts(x_perm, offsets)
             y = (y_perm[dest].view(T, K, H) * w.to(x.dtype)[:, :, None]).sum(1)
         if self.shared_experts is not None:
-            y = y + self.shared_experts(x)
+            ys = self.shared_experts(x)
+            if self.shared_expert_gate is not None:
+                ys = ys * torch.sigmoid(torch.nn.functional.linear(x, self.shared_expert_gate.weight))
+            y = y + ys
         return y, aux

@@ -624,3 +624,48 @@ def test_eval_server_and_client_over_http():
         assert c.health()[0]["samples"] == 12
     finally:
         srv.shutdown()
+
+
+def test_qwen2_moe_shared_expert_gate_and_hf_round_trip(tmp_path):
+    """qwen2_moe: the shared expert's output is scaled by sigmoid(x . g); HF import / export use the family's names
+    (``shared_expert.*``, ``shared_expert_gate``) and round-trip the weights."""
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "workers"))
+    from gcore_b200.checkpoint.hf import load_hf, read_hf_dir, save_hf
+    from gcore_b200.configs.config import OptimizerConfig, PolicyConfig, TrainingConfig
+    from gcore_b200.engine.train_engine import TrainingEngine
+    from gcore_b200.models.config import from_hf_config
+    hf = {"model_type": "qwen2_moe", "num_hidden_layers": 2, "hidden_size": 64, "num_attention_heads": 2,
+          "num_key_value_heads": 2, "intermediate_size": 128, "vocab_size": 128, "num_experts": 4,
+          "num_experts_per_tok": 2, "moe_intermediate_size": 32, "shared_expert_intermediate_size": 48,
+          "norm_topk_prob": False, "torch_dtype": "float32"}
+    cfg = from_hf_config(hf)
+    cfg.dtype = "float32"
+    assert cfg.arch == "qwen2_moe" and cfg.moe_shared_expert_gate and cfg.qkv_bias and cfg.moe_shared_expert_ffn == 48
+
+    def engine(seed):
+        e = TrainingEngine(PolicyConfig(recompute="none", without_ref=True), OptimizerConfig(lr=1e-3),
+                           TrainingConfig(train_mbs=2, train_gbs=2), model_cfg=cfg)
+        e.setup_model_and_get_optimizer(seed=seed)
+        return e
+
+    a = engine(1)
+    layer = a.model.decoder.layers[0].mlp
+    with torch.no_grad():
+        layer.shared_expert_gate.weight.normal_(0, 0.5)
+    x = torch.randn(6, 64)
+    with torch.no_grad():
+        y, _ = layer(x)
+        w = layer.shared_expert_gate.weight.clone()
+        shared = layer.shared_experts(x) * torch.sigmoid(x @ w.t())
+        layer.shared_experts.linear_fc2.weight.zero_()
+        y_routed, _ = layer(x)
+    assert torch.allclose(y - y_routed, shared, atol=2e-2)     # bf16-rounded expert outputs
+    save_hf(a, str(tmp_path / "hf"))
+    names = set(read_hf_dir(str(tmp_path / "hf")))
+    assert "model.layers.0.mlp.shared_expert_gate.weight" in names
+    assert "model.layers.1.mlp.shared_expert.up_proj.weight" in names and "model.layers.0.mlp.experts.3.down_proj.weight" in names
+    b = engine(2)
+    load_hf(b, str(tmp_path / "hf"))
+    for (n, p), (_, q) in zip(a.model.named_parameters(), b.model.named_parameters()):
+        assert torch.equal(p, q), n

@@ -669,3 +669,37 @@ def test_qwen2_moe_shared_expert_gate_and_hf_round_trip(tmp_path):
     load_hf(b, str(tmp_path / "hf"))
     for (n, p), (_, q) in zip(a.model.named_parameters(), b.model.named_parameters()):
         assert torch.equal(p, q), n
+
+
+def test_native_planners_properties():
+    """The C++ planners of the runtime library on random inputs: every index placed once, bins within capacity and no
+    more of them than first-fit-decreasing in Python, k-way partitions balanced (and of equal size when asked)."""
+    import random
+    from gcore_b200.core.packing import ffd_pack, kk_partition
+    rng = random.Random(7)
+    for trial in range(60):
+        n = rng.randrange(1, 120)
+        cap = rng.choice([512, 2048, 8192])
+        lens = [rng.randrange(1, cap + 1) for _ in range(n)]
+        bins = ffd_pack(lens, cap)
+        assert sorted(i for b in bins for i in b) == list(range(n))
+        assert all(sum(lens[i] for i in b) <= cap for b in bins)
+        # python first-fit-decreasing as the yardstick
+        loads = []
+        for i in sorted(range(n), key=lambda i: -lens[i]):
+            for j in range(len(loads)):
+                if loads[j] + lens[i] <= cap:
+                    loads[j] += lens[i]
+                    break
+            else:
+                loads.append(lens[i])
+        assert len(bins) <= len(loads)
+        assert len(bins) >= -(-sum(lens) // cap)          # and never fewer than the volume bound
+        k = rng.randrange(1, min(n, 8) + 1)
+        parts = kk_partition(lens, k)
+        assert sorted(i for p in parts for i in p) == list(range(n)) and len(parts) == k
+        sums = [sum(lens[i] for i in p) for p in parts]
+        assert max(sums) - min(sums) <= 2 * max(lens)
+        if n % k == 0:
+            eq = kk_partition(lens, k, equal_size=True)
+            assert all(len(p) == n // k for p in eq) and sorted(i for p in eq for i in p) == list(range(n))

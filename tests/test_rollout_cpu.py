@@ -219,3 +219,45 @@ def test_mla_rollout_with_lora_adapters_on_the_latent_projections():
         if getattr(m, "lora", None) is not None:
             m.lora = None
     assert naive_greedy(model, prompts[0], 6)[1] != [round(x, 9) for x in reqs[0].out_logprobs]
+
+
+def test_block_manager_accounting_fork_and_exhaustion():
+    """The C++ scheduler / block manager on its own: admission order, block accounting across reserve / advance /
+    finish, copy-on-write fork of a prompt's blocks (shared full blocks, one private copy of the partial block), and
+    refusal instead of over-commitment when the cache is exhausted."""
+    from gcore_b200.rollout.engine import _Sched
+    bs = 4
+    s = _Sched(num_blocks=12, block_size=bs, max_running=8, max_prefill_tokens=64)
+    assert s.stats()["free_blocks"] == 12
+    assert s.add(1, 10, 6) == 0 and s.add(2, 5, 4) == 0          # prompts of 10 and 5 tokens
+    pre, dec = s.step(8, 0)
+    assert pre == [1, 2] and dec == []
+    for rid in pre:
+        s.commit(rid, True)
+    used = 12 - s.stats()["free_blocks"]
+    assert used >= 3 + 2                                            # ceil(10/4) + ceil(5/4) blocks hold the prompts
+    tabs, _ = s.tables([1, 2], 8)
+    assert len(set(tabs[0, :3].tolist())) == 3 and not set(tabs[0, :3].tolist()) & set(tabs[1, :2].tolist())
+    # fork request 1: full blocks are shared, the partial last block (10 % 4 = 2 tokens) is copied
+    rc, src, dst = s.fork(1, 3, 6)
+    assert rc == 0 and src >= 0 and dst >= 0 and src != dst
+    t3, _ = s.tables([3], 8)
+    assert t3[0, :2].tolist() == tabs[0, :2].tolist() and int(t3[0, 2]) == dst and int(tabs[0, 2]) == src
+    free_after_fork = s.stats()["free_blocks"]
+    # decode: reservations take blocks only when a block boundary is crossed
+    assert s.reserve(1, 3) == 0
+    s.advance(1, 2)
+    assert s.reserve(3, 3) == 0
+    s.advance(3, 2)
+    assert s.stats()["free_blocks"] <= free_after_fork
+    # finishing the parent keeps the shared blocks alive for the child; finishing both returns everything
+    s.finish(1)
+    t3b, _ = s.tables([3], 8)
+    assert t3b[0, :3].tolist() == t3[0, :3].tolist()
+    s.finish(3)
+    s.finish(2)
+    st = s.stats()
+    assert st["free_blocks"] == st["num_blocks"] == 12 and st["running"] == 0
+    # exhaustion: a request that cannot fit is refused at add time, the cache stays consistent
+    assert s.add(9, 100, 50) != 0
+    assert s.stats()["free_blocks"] == 12 and s.stats()["waiting"] == 0

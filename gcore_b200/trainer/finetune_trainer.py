@@ -84,6 +84,13 @@ class FinetuneTrainer:
         return out
 
     def train_one_step(self) -> Dict[str, float]:
+        if getattr(self, "profiler", None) is None:
+            from ..utils.profiler import StepProfiler
+            pc = self.cfg.report.profile
+            self.profiler = StepProfiler(pc, self.rank, pc.export_dir or os.path.join(self.cfg.report.log_dir or ".",
+                                                                                      "profile"))
+        step_id = self.step
+        self.profiler.step_begin(step_id)
         self.injector.at_step(self.step)
         self.timers.start("train_step")
         samples = self._to_samples(self._next_batch())
@@ -100,6 +107,9 @@ class FinetuneTrainer:
             self.heartbeat.stamp(self.step)
         if self.reporter:
             self.reporter.log(m, self.step)
+        summ = self.profiler.step_end(step_id)
+        if summ:
+            m.update({f"profile/{k}": v for k, v in summ.items()})
         self.history.append(m)
         return m
 

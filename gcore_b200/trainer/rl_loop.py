@@ -72,6 +72,12 @@ class RlLoop:
 
     def one_step(self) -> Dict[str, float]:
         cfg, tr = self.cfg, self.trainer
+        if getattr(self, "profiler", None) is None:
+            from ..utils.profiler import StepProfiler
+            self.profiler = StepProfiler(cfg.report.profile, self.rank,
+                                         cfg.report.profile.export_dir or os.path.join(cfg.report.log_dir or ".", "profile"))
+        step_id = tr.ppo_step
+        self.profiler.step_begin(step_id)
         self.injector.at_step(tr.ppo_step)
         tm = tr.timers
         tm.start("step")
@@ -88,6 +94,9 @@ class RlLoop:
             self.heartbeat.stamp(tr.ppo_step)
         if self.reporter:
             self.reporter.log(metrics, tr.ppo_step)
+        summ = self.profiler.step_end(step_id)
+        if summ:
+            metrics.update({f"profile/{k}": v for k, v in summ.items()})
         self.history.append(metrics)
         return metrics
 

@@ -24,9 +24,9 @@ class StepProfiler:
         self.start_step, self.end_step = int(g("profile_start_step", 2)), int(g("profile_end_step", 3))
         ranks = g("export_ranks", None)
         self.export = ranks is None or rank in list(ranks)
-        self.gzip = bool(g("gzip_trace", False))
+        self.gzip = bool(g("gzip_trace", False) or g("gzip", False))
         self.rank = rank
-        self.out_dir = out_dir or g("profile_dir", "./profile")
+        self.out_dir = out_dir or g("export_dir", None) or g("profile_dir", "./profile")
         self._prof = None
         self.summary: Dict[str, float] = {}
 

@@ -268,3 +268,21 @@ def test_debug_flags_are_honoured(tmp_path):
         loop.trainer.engine.w.layers[0].o_w.add_(1.0)
     from gcore_b200.rollout.weight_sync import verify
     assert verify(loop.trainer.policy, loop.trainer.engine)
+
+
+def test_step_profiler_from_config(tmp_path):
+    """report.profile.enable: the configured steps are traced with torch.profiler, a Chrome trace lands in the export
+    directory and the communication / compute split joins the step's metrics."""
+    from gcore_b200.entry import train_lm_finetune
+    from gcore_b200.configs.base import load_config
+    from gcore_b200.configs.config import FinetuneConfig
+    from gcore_b200.trainer.finetune_trainer import FinetuneTrainer
+    y = _sft_yaml(tmp_path)
+    cfg = load_config(FinetuneConfig, y, ["report.profile.enable=true", "report.profile.profile_start_step=1",
+                                          "report.profile.profile_end_step=1",
+                                          f"report.profile.export_dir={tmp_path / 'prof'}"])
+    tr = FinetuneTrainer(cfg).setup()
+    hist = tr.train_loop()
+    assert len(hist) == 3 and "profile/comm_frac" in hist[1] and "profile/comm_frac" not in hist[0]
+    files = os.listdir(tmp_path / "prof")
+    assert files == ["trace_rank0_step1-1.json"] and os.path.getsize(tmp_path / "prof" / files[0]) > 1000

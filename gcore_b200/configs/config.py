@@ -382,13 +382,16 @@ class PpoConfig(MappingMixin):
     skip_prev_logps: bool = False
     use_original_logprob: bool = False
     feature_store_enable: bool = False
-    cispo_eps_high: float = 5.0
-    cispo_eps_low: float = 1.0
     sapo_tau_pos: float = 1.0
     sapo_tau_neg: float = 1.05
-    clip_cov_ratio: float = 0.0
-    kl_cov_ratio: float = 0.0
-    kl_cov_coef: float = 1.0
+    # entropy regularisation on the clipped surrogate: clip-cov | kl-cov | None (loss_func clip_cov / kl_cov select
+    # the same losses directly)
+    entropy_regularization_type: Optional[str] = None
+    clip_cov_ratio: float = 2e-4
+    clip_cov_ub: float = 5.0
+    clip_cov_lb: float = 1.0
+    kl_cov_ratio: float = 2e-4
+    kl_cov_coef: float = 0.1
     # steer: token weights in [steer_token_weight_min, 1] from the estimated entropy change, on top of a base loss
     steer_token_weight_min: float = 0.8
     steer_policy_method: str = "grpo"
@@ -407,6 +410,11 @@ class PpoConfig(MappingMixin):
                 raise ConfigError("steer_token_weight_min must be in (0, 1]")
             if self.steer_policy_method not in ("grpo", "cispo", "gspo", "sapo"):
                 raise ConfigError(f"steer_policy_method must be grpo|cispo|gspo|sapo, got {self.steer_policy_method}")
+        if self.entropy_regularization_type not in (None, "clip-cov", "kl-cov"):
+            raise ConfigError(f"entropy_regularization_type must be clip-cov|kl-cov, got "
+                              f"{self.entropy_regularization_type}")
+        if self.entropy_regularization_type and self.loss_func != "grpo":
+            raise ConfigError("entropy_regularization_type applies to loss_func=grpo")
         if self.advantage_type not in ("grpo", "gdpo", "gdpo_sample_bn", "group_gdpo", "group_gdpo_sample_bn", "ppo",
                                        "reinforce", "on_policy_distill", "g_opd", "identity", "custom"):
             raise ConfigError(f"unknown advantage_type {self.advantage_type}")

@@ -488,7 +488,7 @@ class TrainingEngine:
             keys.append("rollout_log_probs")
         want_ent = cfg.ppo_entropy_bonus != 0 or cfg.loss_func == "steer"
         fast = (cfg.loss_func == "grpo" and not has_roll and not want_ent and cfg.kl_estimator == "k3"
-                and cfg.loss_func_py_path is None)
+                and cfg.loss_func_py_path is None and not cfg.entropy_regularization_type)
         loss_fn = None if fast else self._resolve_loss()
         acc: Dict[str, torch.Tensor] = {}
 
@@ -557,6 +557,8 @@ class TrainingEngine:
         if cfg.loss_func_py_path:
             from ..configs.base import import_from_path
             return import_from_path(cfg.loss_func_py_path, cfg.loss_func_fn_name or "loss_func")
+        if cfg.entropy_regularization_type:
+            return PL.get_loss(cfg.entropy_regularization_type.replace("-", "_"))
         return PL.get_loss(cfg.loss_func)
 
     # ------------------------------------------------------------------ critic

@@ -266,6 +266,68 @@ def fipo_loss(cfg, li: LossInput) -> LossOutput:
     return LossOutput(tl, ratio.detach(), metrics)
 
 
+def _centered_cov(cfg, li: LossInput):
+    """Per-token ``(A - mean A) * (log p - mean log p)`` over the valid tokens of the micro-batch (detached)."""
+    valid = li.mask > 0
+    n = li.mask.sum().clamp_min(1.0)
+    a = li.advantages.detach().float()
+    lp = li.logp.detach().float()
+    cov = (a - (a * li.mask).sum() / n) * (lp - (lp * li.mask).sum() / n)
+    return cov, valid
+
+
+@register_loss("clip_cov")
+def clip_cov_loss(cfg, li: LossInput) -> LossOutput:
+    """Clipped surrogate in which a random ``clip_cov_ratio`` share of the valid tokens whose advantage / log-prob
+    covariance lies in ``(clip_cov_lb, clip_cov_ub)`` (and which the ratio clip left alone) gets no gradient: the
+    high-covariance tokens are the ones that collapse the entropy (gpatch_v4/training_backend/loss/ppo_loss.py:142-167)."""
+    old = li.logp.detach() if li.old_logp is None else li.old_logp
+    ratio = _token_ratio(cfg, li.logp, old)
+    l1 = -li.advantages * ratio
+    l2 = -li.advantages * ratio.clamp(1 - cfg.clip_low, 1 + cfg.clip_high)
+    with torch.no_grad():
+        cov, valid = _centered_cov(cfg, li)
+        cand = valid & ~(l2 > l1) & (cov < cfg.clip_cov_ub) & (cov > cfg.clip_cov_lb)
+        idx = torch.nonzero(cand).flatten()
+        n_drop = max(int(cfg.clip_cov_ratio * float(li.mask.sum())), 1)
+        keep = torch.ones_like(li.mask)
+        if idx.numel() > 0:
+            pick = idx[torch.randperm(idx.numel(), device=idx.device)[:min(n_drop, idx.numel())]]
+            keep[pick] = 0
+    tl = torch.maximum(l1, l2) * keep
+    return LossOutput(tl, ratio.detach(), {"ppo_ratio_clamped_frac": _frac(l2 > l1, li.mask),
+                                           "clip_cov_frac": _frac(keep == 0, li.mask),
+                                           "cov_mean": torch.stack([(cov * li.mask).sum(), li.mask.sum()])})
+
+
+@register_loss("kl_cov")
+def kl_cov_loss(cfg, li: LossInput) -> LossOutput:
+    """Clipped surrogate plus ``kl_cov_coef * |log p - log p_old|`` on the ``kl_cov_ratio`` share of valid tokens
+    with the largest advantage / log-prob covariance (gpatch_v4/training_backend/loss/ppo_loss.py:169-210)."""
+    old = li.logp.detach() if li.old_logp is None else li.old_logp
+    ratio = _token_ratio(cfg, li.logp, old)
+    l1 = -li.advantages * ratio
+    l2 = -li.advantages * ratio.clamp(1 - cfg.clip_low, 1 + cfg.clip_high)
+    d = li.logp - old
+    if cfg.ppo_logps_ratio_clamp is not None:
+        d = d.clamp(-cfg.ppo_logps_ratio_clamp, cfg.ppo_logps_ratio_clamp)
+    abs_kl = d.abs()
+    tl = torch.maximum(l1, l2)
+    with torch.no_grad():
+        cov, valid = _centered_cov(cfg, li)
+        sel = torch.zeros_like(valid)
+        n_valid = int(valid.sum())
+        if n_valid > 0 and cfg.kl_cov_ratio > 0:
+            k = max(1, int(n_valid * cfg.kl_cov_ratio))
+            top = torch.topk(cov.masked_fill(~valid, float("-inf")), k).indices
+            sel[top] = True
+    tl = torch.where(sel, tl + cfg.kl_cov_coef * abs_kl, tl)
+    return LossOutput(tl, ratio.detach(), {"ppo_ratio_clamped_frac": _frac(l2 > l1, li.mask),
+                                           "ppo_abs_kl": torch.stack([(abs_kl.detach() * li.mask).sum(), li.mask.sum()]),
+                                           "kl_cov_frac": _frac(sel, li.mask),
+                                           "cov_mean": torch.stack([(cov * li.mask).sum(), li.mask.sum()])})
+
+
 @register_loss("reinforce")
 def reinforce_loss(cfg, li: LossInput) -> LossOutput:
     return LossOutput(-li.advantages * li.logp, torch.ones_like(li.logp), {})

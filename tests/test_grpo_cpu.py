@@ -52,12 +52,16 @@ def test_grpo_steps_improve_reward_and_keep_engine_in_sync():
 def test_alternative_losses_run():
     for loss, extra in (("gspo", {"per_token_loss": False}), ("cispo", {}), ("sapo", {}), ("steer", {}),
                         ("steer", {"steer_policy_method": "cispo", "steer_token_weight_min": 0.5}),
-                        ("fipo", {"ppo_dual_clip_ratio_c": 3.0})):
+                        ("fipo", {"ppo_dual_clip_ratio_c": 3.0}),
+                        ("grpo", {"entropy_regularization_type": "kl-cov", "kl_cov_ratio": 0.1}),
+                        ("grpo", {"entropy_regularization_type": "clip-cov", "clip_cov_lb": 0.0})):
         cfg = make_cfg(loss_func=loss, **extra)
         tr = GrpoTrainer(cfg, model_cfg=get_preset("tiny_llama", dtype="float32"),
                          reward_fn=reward_has_small_token).setup()
         m = tr.step([[5, 6, 7, 8, 9], [10, 11, 12], [13, 14, 15, 16], [20, 21]])
         assert m["policy/grad_norm"] >= 0 and "ppo-metrics/pg_loss" in m
+        if extra.get("entropy_regularization_type") == "kl-cov":
+            assert m["ppo-metrics/kl_cov_frac"] > 0
 
 
 def test_grpo_step_with_moe_policy_and_ppo_critic_value_path():

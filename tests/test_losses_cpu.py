@@ -388,3 +388,47 @@ def test_gdpo_advantage_variants():
     g1 = get_advantage_fn("gdpo_sample_bn")(b, cfg, dp_group=None)
     assert float(g1[5]["advantages"].abs().sum()) == 0.0 and "gdpo/bn_std" in g1[0]["advantage_stats"]
     PpoConfig(advantage_type="gdpo_sample_bn")      # accepted by the configuration
+
+
+def test_entropy_regularisation_clip_cov_and_kl_cov():
+    """kl-cov adds coef * |log-ratio| on exactly the top share of tokens by covariance; clip-cov removes the gradient
+    of a bounded number of tokens inside the covariance window; both reduce to the clipped surrogate elsewhere."""
+    from gcore_b200.configs.config import PpoConfig, ConfigError
+    T = 200
+    g = torch.Generator().manual_seed(3)
+    lp = (torch.randn(T, generator=g) * 0.5 - 1.5).requires_grad_(True)
+    old = lp.detach() + torch.randn(T, generator=g) * 0.05
+    adv = torch.randn(T, generator=g) * 2
+    mask = torch.ones(T)
+    mask[:20] = 0
+    li = PL.LossInput(lp, old, None, None, adv, mask, torch.zeros(T, dtype=torch.int32), 1)
+    base = PL.get_loss("grpo")(PpoConfig(), li).token_loss
+
+    cfg = PpoConfig(entropy_regularization_type="kl-cov", kl_cov_ratio=0.05, kl_cov_coef=0.5)
+    out = PL.get_loss("kl_cov")(cfg, li)
+    a, l = adv[20:], lp.detach()[20:]
+    cov = (a - a.mean()) * (l - l.mean())
+    top = torch.topk(cov, int(180 * 0.05)).indices + 20
+    want = base.clone()
+    want[top] = want[top] + 0.5 * (lp - old).abs()[top]
+    assert torch.allclose(out.token_loss, want, atol=1e-6)
+    assert float(out.metrics["kl_cov_frac"][0]) == 9.0
+
+    cfg = PpoConfig(entropy_regularization_type="clip-cov", clip_cov_ratio=0.02, clip_cov_lb=0.2, clip_cov_ub=50.0)
+    torch.manual_seed(0)
+    out = PL.get_loss("clip_cov")(cfg, li)
+    dropped = torch.nonzero((out.token_loss == 0) & (base != 0)).flatten()
+    assert 1 <= dropped.numel() <= int(0.02 * 180)
+    full_cov = torch.zeros(T)
+    full_cov[20:] = cov
+    assert bool(((full_cov[dropped] > 0.2) & (full_cov[dropped] < 50.0)).all()) and bool((dropped >= 20).all())
+    kept = torch.ones(T, dtype=torch.bool)
+    kept[dropped] = False
+    assert torch.allclose(out.token_loss[kept], base[kept], atol=1e-6)
+    out.token_loss.sum().backward()
+    assert bool((lp.grad[dropped] == 0).all())
+
+    with pytest.raises(ConfigError):
+        PpoConfig(entropy_regularization_type="cov")
+    with pytest.raises(ConfigError):
+        PpoConfig(entropy_regularization_type="kl-cov", loss_func="cispo")

@@ -604,7 +604,8 @@ class RlConfig(BaseTopConfig):
 
 
 @dataclass
-class DpoConfig(BaseTopConfig):
+class DpoConfig(RlConfig):
+    """``train_lm_dpo``: the sections of the RL configuration plus the preference-loss options at the top level."""
     dpo_beta: float = 0.1
     dpo_label_smoothing: float = 0.0
     dpo_sft_loss_coef: float = 0.0
@@ -612,9 +613,15 @@ class DpoConfig(BaseTopConfig):
 
 
 @dataclass
-class RewardTrainConfig(BaseTopConfig):
+class RewardTrainConfig(RlConfig):
+    """``train_lm_reward_model``: ``rm_margin`` is subtracted from the chosen - rejected score gap."""
     rm_loss: str = "bt"  # Bradley-Terry pairwise
     rm_margin: float = 0.0
+
+    def __post_init__(self):
+        super().__post_init__() if hasattr(super(), "__post_init__") else None
+        if self.rm_loss != "bt":
+            raise ConfigError(f"rm_loss must be bt (Bradley-Terry), got {self.rm_loss}")
 
 
 @dataclass

@@ -4,7 +4,7 @@ import sys
 
 import torch
 
-from ..configs.config import RlConfig
+from ..configs.config import DpoConfig
 from ..data.datasets import IndexedJsonlDataset
 from ..engine.train_engine import TrainingEngine
 from ..trainer.preference_trainers import dpo_step
@@ -29,16 +29,17 @@ def pair_batches(cfg, vocab: int, seed: int = 0):
 
 
 def main(argv=None):
-    cfg = load(RlConfig, argv)
+    cfg = load(DpoConfig, argv)
     init_runtime(cfg)
     eng = TrainingEngine(cfg.policy, cfg.optimizer, cfg.training, cfg.ppo)
-    eng.setup_model_and_get_optimizer(seed=cfg.training.seed, with_ref=True)
+    eng.setup_model_and_get_optimizer(seed=cfg.training.seed, with_ref=not cfg.reference_free)
     log = get_logger("dpo")
     total = cfg.training.exit_step or cfg.training.total_ppo_step or 0
     for step, (chosen, rejected) in enumerate(pair_batches(cfg, eng.model_cfg.vocab_size, cfg.training.seed)):
         if step >= total:
             break
-        m = dpo_step(eng, chosen, rejected, beta=getattr(cfg.ppo, "dpo_beta", 0.1))
+        m = dpo_step(eng, chosen, rejected, beta=cfg.dpo_beta, label_smoothing=cfg.dpo_label_smoothing,
+                     reference_free=cfg.reference_free, sft_coef=cfg.dpo_sft_loss_coef)
         log.info(f"step {step} " + " ".join(f"{k}={v:.4f}" for k, v in m.items()))
     finalize()
     return 0

@@ -1,7 +1,7 @@
 """Bradley-Terry reward-model training entry point (``gpatch_v4/entry/train_lm_reward_model.py``)."""
 import sys
 
-from ..configs.config import RlConfig
+from ..configs.config import RewardTrainConfig
 from ..engine.train_engine import TrainingEngine
 from ..trainer.preference_trainers import rm_step
 from ..utils.logging_utils import get_logger
@@ -10,7 +10,7 @@ from .train_lm_dpo import pair_batches
 
 
 def main(argv=None):
-    cfg = load(RlConfig, argv)
+    cfg = load(RewardTrainConfig, argv)
     init_runtime(cfg)
     eng = TrainingEngine(cfg.policy, cfg.optimizer, cfg.training, cfg.ppo, value_head=True)
     eng.setup_model_and_get_optimizer(seed=cfg.training.seed, with_ref=False)
@@ -19,7 +19,7 @@ def main(argv=None):
     for step, (chosen, rejected) in enumerate(pair_batches(cfg, eng.model_cfg.vocab_size, cfg.training.seed)):
         if step >= total:
             break
-        m = rm_step(eng, chosen, rejected)
+        m = rm_step(eng, chosen, rejected, margin=cfg.rm_margin)
         log.info(f"step {step} " + " ".join(f"{k}={v:.4f}" for k, v in m.items()))
     finalize()
     return 0

@@ -52,7 +52,12 @@ def dpo_step(engine: TrainingEngine, chosen: List[dict], rejected: List[dict], b
     n = len(chosen)
     loss, m = PL.dpo_loss(pol[:n], pol[n:], ref[:n], ref[n:], beta, label_smoothing, reference_free)
     if sft_coef:
-        ntok = sum(float(torch.as_tensor(s.get("loss_mask", s.get("mask"))).sum()) for s in chosen)
+        def resp_tokens(s):
+            m = s.get("loss_mask", s.get("mask"))
+            if m is not None:
+                return float(torch.as_tensor(m).sum())
+            return float(len(s["tokens"]) - int(s.get("prompt_length", 0)))
+        ntok = sum(resp_tokens(s) for s in chosen)
         loss = loss - sft_coef * pol[:n].sum() / max(ntok, 1.0)
     dp = ps.get_data_parallel_world_size(with_context_parallel=True)
     (loss / 1.0).backward()

@@ -40,7 +40,9 @@ def test_rl_and_preference_entries(tmp_path):
     assert train_lm_grpo_single_ctrl.main(["--config", y, "training.single_controller=true"]) == 0
     small = ["training.train_gbs=4", "training.rollout_gbs=4"]
     assert train_lm_dpo.main(["--config", y] + small) == 0
-    assert train_lm_reward_model.main(["--config", y] + small) == 0
+    assert train_lm_dpo.main(["--config", y, "dpo_beta=0.3", "dpo_label_smoothing=0.1", "dpo_sft_loss_coef=0.5",
+                              "reference_free=true"] + small) == 0
+    assert train_lm_reward_model.main(["--config", y, "rm_margin=0.5"] + small) == 0
 
 
 def test_distillation_entry_on_and_off_policy(tmp_path):

@@ -58,6 +58,12 @@ class GrpoTrainer:
         if config.ppo.advantage_py_path:
             self.advantage_fn = import_from_path(config.ppo.advantage_py_path,
                                                  config.ppo.advantage_fn_name or "advantage_fn")
+        # optional user step after the advantages exist: fn(samples, ppo_cfg, dp_group) -> samples or
+        # (samples, metrics); the hook point of gpatch_v4/actor/mixin.py:821-832
+        self.post_advantage_fn = None
+        if config.ppo.post_advantage_py_path:
+            self.post_advantage_fn = import_from_path(config.ppo.post_advantage_py_path,
+                                                      config.ppo.post_advantage_fn_name or "post_advantage_fn")
 
     def _load_reward_fn(self):
         b = self.cfg.bt_rm
@@ -208,9 +214,13 @@ class GrpoTrainer:
         tm.stop("compute_logps")
         tm.start("generate_ppo_data")
         samples = compute_advantages(samples, cfg.ppo, ps.get_data_parallel_group(), self.advantage_fn)
+        post_metrics: Dict[str, float] = {}
+        if self.post_advantage_fn is not None:
+            res = self.post_advantage_fn(samples, cfg.ppo, ps.get_data_parallel_group())
+            samples, post_metrics = res if isinstance(res, tuple) else (res, {})
         tm.stop("generate_ppo_data")
         tm.start("train_step")
-        metrics: Dict[str, float] = {}
+        metrics: Dict[str, float] = {k: float(v) for k, v in post_metrics.items()}
         self.policy.allocate_grad_buffers()
         per_update = max(t.train_gbs // max(ps.get_data_parallel_world_size(), 1), 1)
         for _ in range(t.ppo_max_epochs_2):

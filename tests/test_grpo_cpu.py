@@ -263,3 +263,22 @@ def test_lora_on_grouped_experts_shared_and_per_expert():
         # expert GEMM outputs are rounded to bf16, so "equal" is to bf16 resolution - far below what the adapters change
         err, effect = float((ref - merged).abs().max()), float((ref - plain).abs().max())
         assert err < 0.03 * max(1.0, float(ref.abs().max())) and effect > 5 * err, (err, effect)
+
+
+def test_user_post_advantage_hook_edits_samples_and_reports_metrics(tmp_path):
+    """``ppo.post_advantage_py_path``: a user function sees the samples once the advantages exist, may change them and
+    returns metrics that land in the step's metrics."""
+    hook = tmp_path / "post_adv.py"
+    hook.write_text(
+        "def halve(samples, ppo_cfg, dp_group):\n"
+        "    tot = 0.0\n"
+        "    for s in samples:\n"
+        "        tot += float(s['advantages'].abs().sum())\n"
+        "        s['advantages'] = s['advantages'] * 0.0\n"
+        "    return samples, {'post-adv/abs_sum': tot}\n")
+    cfg = make_cfg(post_advantage_py_path=str(hook), post_advantage_fn_name="halve", grpo_kl_loss_beta=0.0)
+    tr = GrpoTrainer(cfg, model_cfg=get_preset("tiny_llama", dtype="float32"), reward_fn=reward_has_small_token).setup()
+    m = tr.step([[5, 6, 7, 8, 9], [10, 11, 12], [13, 14, 15, 16], [20, 21]])
+    assert m["post-adv/abs_sum"] > 0
+    assert m["policy/grad_norm"] < 1e-7     # zeroed advantages and no KL term: nothing to learn from
+    assert all(float(s["advantages"].abs().sum()) == 0.0 for s in tr.last_samples)

@@ -356,5 +356,16 @@ def default_dataset_fn(config, tokenizer, dp_rank: int, dp_size: int, meta_info:
         sampler.set_epoch(meta_info["consumed_batches"] // per_epoch)
         sampler.set_start_index((meta_info["consumed_batches"] % per_epoch) * bs)
     dl = build_dataloader(ds, sampler, bs, prompt_collate if rl else sft_collate, d.num_workers)
-    return {"train_dataset": ds, "train_sampler": sampler, "train_dataloader": dl, "eval_dataset": None,
-            "eval_dataloader": None}
+    eval_ds = eval_dl = None
+    if rl and (d.eval_data_path or syn.get("eval_num_samples")):
+        # held-out prompts for the periodic evaluation: fixed order, sharded over the data-parallel ranks
+        if d.eval_data_path:
+            eval_ds = PromptDataset(IndexedJsonlDataset(d.eval_data_path), tokenizer, d.max_prompt_length,
+                                    d.prompt_key, d.label_key)
+        else:
+            eval_ds = SyntheticPromptDataset(int(syn["eval_num_samples"]), syn.get("prompt_len", 256),
+                                             syn.get("lo", 100), syn.get("hi", 150000), seed=d.seed + 7919)
+        eval_sampler = ResumableDistributedSampler(len(eval_ds), dp_rank, dp_size, False, d.seed)
+        eval_dl = build_dataloader(eval_ds, eval_sampler, bs, prompt_collate, 0)
+    return {"train_dataset": ds, "train_sampler": sampler, "train_dataloader": dl, "eval_dataset": eval_ds,
+            "eval_dataloader": eval_dl}

@@ -126,12 +126,16 @@ class GrpoTrainer:
         return self
 
     # ------------------------------------------------------------------ phases
-    def rollout(self, prompts: Sequence) -> List[dict]:
+    def rollout(self, prompts: Sequence, n: Optional[int] = None, sampling: Optional[dict] = None) -> List[dict]:
         """``prompts``: token-id lists, or for a vision-language policy dicts with ``tokens``, ``pixel_patches`` and
-        ``image_grid`` (the vision tower runs here, once per prompt; the engine only sees feature rows)."""
+        ``image_grid`` (the vision tower runs here, once per prompt; the engine only sees feature rows).  ``n`` samples
+        per prompt (default ``training.sampling_repeat_n``); ``sampling`` overrides fields of the job's sampling
+        parameters for this call (evaluation passes its own temperature / length)."""
         t = self.cfg.training
+        n = int(n or t.sampling_repeat_n)
         self.engine.wake_up(("kv_cache",))
-        sp = SamplingParams(**{**self.sampling.__dict__, "seed": self.sampling.seed + self.ppo_step * 1000003})
+        sp = SamplingParams(**{**self.sampling.__dict__, **(sampling or {}),
+                               "seed": self.sampling.seed + self.ppo_step * 1000003})
         images = [p if isinstance(p, dict) and "pixel_patches" in p else None for p in prompts]
         prompts = [list(p["tokens"]) if isinstance(p, dict) else p for p in prompts]
         vl_kw = {}
@@ -149,7 +153,7 @@ class GrpoTrainer:
                     patches = torch.as_tensor(im["pixel_patches"], dtype=torch.float32).to(self.policy.device)
                     embeds.append(model.vision(patches.to(next(model.vision.parameters()).dtype), grids))
             vl_kw = dict(image_embeds=embeds, image_token_id=model.image_token_id)
-        reqs = self.engine.generate(prompts, sp, n=t.sampling_repeat_n, **vl_kw)
+        reqs = self.engine.generate(prompts, sp, n=n, **vl_kw)
         self.engine.sleep(("kv_cache",))
         samples = []
         dp_rank = ps.get_data_parallel_rank()
@@ -159,9 +163,9 @@ class GrpoTrainer:
             lp = torch.zeros(S, dtype=torch.float32)
             lp[P - 1:S - 1] = torch.tensor(r.out_logprobs, dtype=torch.float32)
             samples.append(dict(tokens=toks, prompt_length=P, sequence_length=S, rollout_log_probs=lp,
-                                group_id=k // t.sampling_repeat_n, unique_id=(self.ppo_step, dp_rank, k),
+                                group_id=k // n, unique_id=(self.ppo_step, dp_rank, k),
                                 mask=response_mask(P, S), finish_reason=r.finish_reason))
-            im = images[k // t.sampling_repeat_n]
+            im = images[k // n]
             if im is not None:  # the training passes re-run the vision tower on the same pixels
                 samples[-1]["pixel_patches"], samples[-1]["image_grid"] = im["pixel_patches"], im["image_grid"]
         return samples

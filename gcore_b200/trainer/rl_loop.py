@@ -33,6 +33,7 @@ class RlLoop:
         self.reporter: Optional[Reporter] = None
         self.history: List[Dict[str, float]] = []
         self.consumed_batches = 0
+        self.eval_history: List[Dict[str, float]] = []
 
     def setup(self):
         cfg, tr = self.cfg, self.trainer
@@ -100,6 +101,38 @@ class RlLoop:
         self.history.append(metrics)
         return metrics
 
+    def evaluate(self) -> Dict[str, float]:
+        """Held-out evaluation with the current weights (``data.eval_data_path``; every ``training.eval_interval``
+        steps from ``run``): ``task.eval.repeat_n`` samples per prompt (default ``sampling_repeat_n``) drawn with
+        the sampler's ``eval_generate_params`` on top of the training sampling parameters, scored by the job's
+        reward function; mean reward, pass@k and response length over the data-parallel ranks
+        (the in-training evaluation of gpatch_v4/actor/grpo_train_actor.py; runner in evaluate/runner.py)."""
+        dl = self.data.get("eval_dataloader")
+        if dl is None:
+            return {}
+        from ..evaluate.runner import EvaluateRunner
+        tr = self.trainer
+        ev = dict((self.cfg.task or {}).get("eval", {}) or {})
+        ie = self.cfg.sampler.infer_engine_configs[0]
+        names = {"max_tokens": "max_new_tokens", "generate_max_tokens": "max_new_tokens"}
+        override = {names.get(k, k): v for k, v in dict(ie.eval_generate_params or {}).items()
+                    if names.get(k, k) in tr.sampling.__dict__}
+        n = int(ev.get("repeat_n", self.cfg.training.sampling_repeat_n))
+        runner = EvaluateRunner(lambda p: tr.rollout(p, n=n, sampling=override),
+                                lambda s: [float(x["rewards"]) for x in tr.score(s)], n,
+                                ks=tuple(ev.get("ks", (1,))), threshold=float(ev.get("threshold", 0.5)),
+                                dp_group=ps.get_data_parallel_group())
+        prompts, limit = [], int(ev.get("batches", 0))
+        for i, batch in enumerate(dl):
+            if limit and i >= limit:
+                break
+            prompts += [p["prompt_token_ids"] for p in batch["prompt_token_ids"]]
+        metrics = runner.run(prompts)
+        if self.reporter:
+            self.reporter.log(metrics, tr.ppo_step)
+        self.eval_history.append({"step": tr.ppo_step, **metrics})
+        return metrics
+
     def save(self):
         ck = self.cfg.checkpoint
         if not ck.save_ckpt_path:
@@ -125,6 +158,10 @@ class RlLoop:
             if self.rank == 0:
                 self.log.info(f"ppo_step {self.trainer.ppo_step} reward {m['rollout-rewards/mean']:.4f} "
                               f"step {m['time_perf/step']:.2f}s")
+            if t.eval_interval and self.trainer.ppo_step % t.eval_interval == 0:
+                em = self.evaluate()
+                if em and self.rank == 0:
+                    self.log.info(f"ppo_step {self.trainer.ppo_step} " + " ".join(f"{k}={v:.4f}" for k, v in em.items()))
             if t.save_interval and self.trainer.ppo_step % t.save_interval == 0:
                 self.save()
         if tracer is not None:

@@ -288,3 +288,34 @@ def test_step_profiler_from_config(tmp_path):
     assert len(hist) == 3 and "profile/comm_frac" in hist[1] and "profile/comm_frac" not in hist[0]
     files = os.listdir(tmp_path / "prof")
     assert files == ["trace_rank0_step1-1.json"] and os.path.getsize(tmp_path / "prof" / files[0]) > 1000
+
+
+def test_periodic_evaluation_inside_the_rl_loop(tmp_path):
+    """``training.eval_interval`` with a held-out prompt set: the loop evaluates with the evaluation sampling
+    parameters (greedy, shorter) and its own samples-per-prompt, and keeps training afterwards."""
+    from gcore_b200.configs.base import load_config
+    from gcore_b200.configs.config import RlConfig
+    from gcore_b200.trainer.rl_loop import RlLoop
+    y = _rl_yaml(tmp_path)
+    cfg = load_config(RlConfig, y, ["training.eval_interval=2", "training.total_ppo_step=4",
+                                    "+data.synthetic.eval_num_samples=8", "+task.eval.repeat_n=1",
+                                    "+task.eval.ks=[1]", "+task.eval.threshold=-1.0",
+                                    "+sampler.infer_engine_configs.0.eval_generate_params.greedy=true",
+                                    "+sampler.infer_engine_configs.0.eval_generate_params.max_tokens=4"])
+    loop = RlLoop(cfg).setup()
+    seen = []
+    orig = loop.trainer.rollout
+
+    def spy(prompts, n=None, sampling=None):
+        out = orig(prompts, n=n, sampling=sampling)
+        if sampling is not None:
+            seen.append((len(prompts), n, dict(sampling), max(s["sequence_length"] - s["prompt_length"] for s in out)))
+        return out
+    loop.trainer.rollout = spy
+    hist = loop.run()
+    assert len(hist) == 4 and [e["step"] for e in loop.eval_history] == [2, 4]
+    e = loop.eval_history[0]
+    assert e["eval/num_samples"] == 8.0 and e["eval/pass@1"] == 1.0 and e["eval/response_length"] <= 4.0
+    assert seen[0][:2] == (8, 1) and seen[0][2] == {"greedy": True, "max_new_tokens": 4} and seen[0][3] <= 4
+    # greedy decoding of a fixed prompt set: the two evaluations differ only through the weight updates in between
+    assert loop.eval_history[0].keys() == loop.eval_history[1].keys()

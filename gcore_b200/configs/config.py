@@ -481,6 +481,7 @@ class TrainingConfig(MappingMixin):
     per_token_loss: bool = True
     sort_batched: bool = False
     manual_gc: bool = False
+    manual_gc_interval: int = 1
     # RL-only
     total_ppo_step: Optional[int] = None
     ppo_step_per_epoch: Optional[int] = None

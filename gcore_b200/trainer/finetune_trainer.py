@@ -4,6 +4,8 @@ state; resumes automatically from the newest checkpoint; stamps a heartbeat and 
 every step boundary."""
 from __future__ import annotations
 
+import gc
+import math
 import os
 import time
 from typing import Dict, Optional
@@ -61,6 +63,18 @@ class FinetuneTrainer:
         dp_rank, dp_size = ps.get_data_parallel_rank(), ps.get_data_parallel_world_size()
         self.data = fn(cfg, self.tokenizer, dp_rank, dp_size, meta)
         self.loader_iter = iter(self.data["train_dataloader"])
+        t = cfg.training
+        self.total_steps = t.exit_step or t.total_training_step
+        if not t.total_training_step:
+            # no explicit length: training.num_train_epoches passes over this rank's share of the data
+            # (gpatch_v4/actor/pretrain_actor.py:66); the learning-rate schedule decays over the same span
+            s = self.data["train_sampler"]
+            per_epoch = max(getattr(s, "per_rank", len(self.data["train_dataloader"])) //
+                            max(t.train_gbs // max(dp_size, 1), 1), 1)
+            span = int(math.ceil(per_epoch * max(t.num_train_epoches, 1)))
+            self.total_steps = self.total_steps or span
+            if self.engine.optimizer is not None and self.engine.optimizer.total_steps is None:
+                self.engine.optimizer.total_steps = span
         if ps.is_last_rank():
             self.reporter = Reporter(cfg.report, os.path.join(cfg.report.log_dir, cfg.report.run_name or "finetune"))
         return self
@@ -123,14 +137,23 @@ class FinetuneTrainer:
 
     def train_loop(self):
         t = self.cfg.training
-        total = t.exit_step or t.total_training_step or 0
+        total = self.total_steps or 0
+        if t.manual_gc:
+            # the collector runs between steps only, so that no rank stalls inside a step while the others wait in a
+            # collective (gpatch_v4/actor/finetune_actor.py:346-357)
+            gc.disable()
+            gc.collect()
         while self.step < total:
             m = self.train_one_step()
+            if t.manual_gc and self.step % max(t.manual_gc_interval, 1) == 0:
+                gc.collect()
             if self.rank == 0 and self.step % max(self.cfg.report.log_interval, 1) == 0:
                 self.log.info(f"step {self.step} lm_loss {m['lm_loss']:.4f} grad_norm {m['grad_norm']:.3f} "
                               f"{m['time_perf/train_step']:.3f}s")
             if t.save_interval and self.step % t.save_interval == 0:
                 self.save()
+        if t.manual_gc:
+            gc.enable()
         if self.reporter:
             self.reporter.close()
         wait_for_async_save()

@@ -4,6 +4,7 @@ gpatch_v4/trainer/grpo_trainer.py:66-98, actor/grpo_train_actor.py:1466-1571) an
 ``rollout_max_staleness`` (gpatch_v4/trainer/grpo_single_ctrl_trainer.py:72-...)."""
 from __future__ import annotations
 
+import gc
 import os
 from typing import Dict, Iterator, List, Optional
 
@@ -153,8 +154,13 @@ class RlLoop:
             os.makedirs(os.path.dirname(out), exist_ok=True)
             tracer = PythonCallTracer(roots, out)
             tracer.__enter__()
+        if t.manual_gc:
+            gc.disable()
+            gc.collect()
         while self.trainer.ppo_step < total:
             m = self.one_step()
+            if t.manual_gc and self.trainer.ppo_step % max(t.manual_gc_interval, 1) == 0:
+                gc.collect()
             if self.rank == 0:
                 self.log.info(f"ppo_step {self.trainer.ppo_step} reward {m['rollout-rewards/mean']:.4f} "
                               f"step {m['time_perf/step']:.2f}s")
@@ -164,6 +170,8 @@ class RlLoop:
                     self.log.info(f"ppo_step {self.trainer.ppo_step} " + " ".join(f"{k}={v:.4f}" for k, v in em.items()))
             if t.save_interval and self.trainer.ppo_step % t.save_interval == 0:
                 self.save()
+        if t.manual_gc:
+            gc.enable()
         if tracer is not None:
             tracer.__exit__(None, None, None)
         if self.reporter:

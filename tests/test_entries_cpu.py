@@ -319,3 +319,29 @@ def test_periodic_evaluation_inside_the_rl_loop(tmp_path):
     assert seen[0][:2] == (8, 1) and seen[0][2] == {"greedy": True, "max_new_tokens": 4} and seen[0][3] <= 4
     # greedy decoding of a fixed prompt set: the two evaluations differ only through the weight updates in between
     assert loop.eval_history[0].keys() == loop.eval_history[1].keys()
+
+
+def test_finetune_length_from_epochs_and_manual_gc(tmp_path):
+    """Without a step count the job runs ``num_train_epoches`` passes over the data, the decay of the learning rate
+    spans the same steps, and ``manual_gc`` keeps the collector off inside the loop and restores it afterwards."""
+    import gc
+    from gcore_b200.configs.base import load_config
+    from gcore_b200.configs.config import FinetuneConfig
+    from gcore_b200.trainer.finetune_trainer import FinetuneTrainer
+    y = _sft_yaml(tmp_path)
+    cfg = load_config(FinetuneConfig, y, ["~training.exit_step", "training.num_train_epoches=2",
+                                          "data.synthetic.num_samples=16", "training.manual_gc=true",
+                                          "optimizer.lr_decay_style=linear", "optimizer.min_lr=0.0"])
+    tr = FinetuneTrainer(cfg).setup()
+    assert tr.total_steps == 8 and tr.engine.optimizer.total_steps == 8     # 16 samples / batch 4 x 2 epochs
+    state = []
+    orig = tr.train_one_step
+
+    def spy():
+        state.append(gc.isenabled())
+        return orig()
+    tr.train_one_step = spy
+    hist = tr.train_loop()
+    assert len(hist) == 8 and state == [False] * 8 and gc.isenabled()
+    lrs = [m["lr"] for m in hist]
+    assert lrs[0] > lrs[-1] and lrs[-1] <= 0.3 * lrs[0]

@@ -136,8 +136,15 @@ def _build(tp, value, path):
 
 def from_dict(cls, data: dict, path: str = ""):
     """Instantiates dataclass ``cls`` from a nested dict.  Unknown keys are an error unless the class defines
-    ``_allow_extra = True`` (then they land in ``extra``)."""
+    ``_allow_extra = True`` (then they land in ``extra``).  A class attribute ``_aliases = {other_name: field}``
+    accepts a second spelling of a field (the reference's name where this package shortened it); giving both is an
+    error."""
     data = dict(data or {})
+    for other, name in (getattr(cls, "_aliases", None) or {}).items():
+        if other in data:
+            if name in data:
+                raise ConfigError(f"{path or cls.__name__}: both '{other}' and its alias '{name}' are set")
+            data[name] = data.pop(other)
     hints = get_type_hints(cls)
     kwargs = {}
     names = {f.name for f in fields(cls)}

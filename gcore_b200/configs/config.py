@@ -401,6 +401,25 @@ class PpoConfig(MappingMixin):
     fipo_clip_ratio: float = 0.2
     fipo_clip_high_only: bool = False
     fipo_safety_thresh: float = 3.0
+    # vespo: phi(W) = W^c1 * exp(c2 * (1 - W)), separate shapes for sequences with positive / negative advantage
+    vespo_c1_pos: float = 1.0
+    vespo_c2_pos: float = 1.0
+    vespo_c1_neg: float = 1.0
+    vespo_c2_neg: float = 1.0
+
+    # the spellings of gpatch_v4/configs/ppo_config.py for the fields this package names differently
+    _aliases = {
+        "ppo_entropy_regularization_type": "entropy_regularization_type",
+        "ppo_clip_cov_ratio": "clip_cov_ratio", "ppo_clip_cov_ub": "clip_cov_ub", "ppo_clip_cov_lb": "clip_cov_lb",
+        "ppo_kl_cov_ratio": "kl_cov_ratio", "ppo_kl_cov_coef": "kl_cov_coef",
+        "off_policy_correction_mode": "offpolicy_correction", "off_policy_correction_level": "offpolicy_correction_level",
+        "off_policy_correction_upper_bound": "offpolicy_correction_upper",
+        "off_policy_correction_lower_bound": "offpolicy_correction_lower",
+        "off_policy_correction_veto_threshold": "offpolicy_correction_veto",
+        "custom_advantage_py_path": "advantage_py_path", "custom_advantage_py_name": "advantage_fn_name",
+        "custom_post_advantage_py_name": "post_advantage_fn_name", "loss_func_py_name": "loss_func_fn_name",
+        "advantage_clip_lower_bound": "advantage_clip_low", "advantage_clip_upper_bound": "advantage_clip_high",
+    }
 
     def __post_init__(self):
         if self.loss_func == "steer":
@@ -482,6 +501,16 @@ class TrainingConfig(MappingMixin):
     sort_batched: bool = False
     manual_gc: bool = False
     manual_gc_interval: int = 1
+    # parameter groups kept out of training (on top of policy.freeze_patterns); the vision ones apply to
+    # vision-language policies
+    freeze_moe_router: bool = False
+    freeze_moe_shared_experts: bool = False
+    freeze_llm: bool = False
+    freeze_vit: bool = False
+    freeze_projector: bool = False
+    # held-out evaluation inside the RL loop: also once before the first step; its own samples per prompt
+    eval_before_train: bool = False
+    eval_sampling_repeat_n: Optional[int] = None
     # RL-only
     total_ppo_step: Optional[int] = None
     ppo_step_per_epoch: Optional[int] = None

@@ -175,7 +175,12 @@ class TrainingEngine:
 
     def _apply_freeze(self):
         import re
-        for pat in self.policy_cfg.freeze_patterns:
+        t = self.train_cfg
+        named = {"freeze_moe_router": r"\.router\.", "freeze_moe_shared_experts": r"\.shared_expert(s|_gate)\.",
+                 "freeze_vit": r"^vision\.(?!merge_fc)", "freeze_projector": r"^vision\.merge_fc",
+                 "freeze_llm": r"^(?!vision\.)"}
+        flags = [pat for k, pat in named.items() if getattr(t, k, False)]
+        for pat in flags + list(self.policy_cfg.freeze_patterns):
             for n, p in self.model.named_parameters():
                 if re.search(pat, n):
                     p.requires_grad_(False)

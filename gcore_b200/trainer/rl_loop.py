@@ -118,7 +118,8 @@ class RlLoop:
         names = {"max_tokens": "max_new_tokens", "generate_max_tokens": "max_new_tokens"}
         override = {names.get(k, k): v for k, v in dict(ie.eval_generate_params or {}).items()
                     if names.get(k, k) in tr.sampling.__dict__}
-        n = int(ev.get("repeat_n", self.cfg.training.sampling_repeat_n))
+        t = self.cfg.training
+        n = int(ev.get("repeat_n", t.eval_sampling_repeat_n or t.sampling_repeat_n))
         runner = EvaluateRunner(lambda p: tr.rollout(p, n=n, sampling=override),
                                 lambda s: [float(x["rewards"]) for x in tr.score(s)], n,
                                 ks=tuple(ev.get("ks", (1,))), threshold=float(ev.get("threshold", 0.5)),
@@ -157,6 +158,8 @@ class RlLoop:
         if t.manual_gc:
             gc.disable()
             gc.collect()
+        if t.eval_before_train and t.eval_interval and self.trainer.ppo_step < total:
+            self.evaluate()
         while self.trainer.ppo_step < total:
             m = self.one_step()
             if t.manual_gc and self.trainer.ppo_step % max(t.manual_gc_interval, 1) == 0:

@@ -141,3 +141,18 @@ def test_every_recipe_yaml_loads_and_names_a_known_model():
             assert cfg.teacher.model_arch in PRESETS and cfg.ppo.advantage_type == "on_policy_distill"
         if raw["policy"].get("fp8"):
             assert cfg.policy.fp8 and cfg.policy.lora.enabled and "linear_kv_up_proj" in cfg.policy.lora.target_modules
+
+
+def test_reference_spellings_of_ppo_fields_are_accepted():
+    from gcore_b200.configs.base import ConfigError, from_dict
+    from gcore_b200.configs.config import PpoConfig
+    c = from_dict(PpoConfig, {"ppo_entropy_regularization_type": "kl-cov", "ppo_kl_cov_ratio": 0.01,
+                              "off_policy_correction_mode": "icepop", "off_policy_correction_upper_bound": 3.0,
+                              "custom_advantage_py_path": "/x/adv.py", "custom_advantage_py_name": "fn",
+                              "vespo_c1_neg": 2.0})
+    assert c.entropy_regularization_type == "kl-cov" and c.kl_cov_ratio == 0.01 and c.offpolicy_correction == "icepop"
+    assert c.offpolicy_correction_upper == 3.0 and c.advantage_py_path == "/x/adv.py" and c.advantage_fn_name == "fn"
+    assert c.vespo_c1_neg == 2.0
+    import pytest
+    with pytest.raises(ConfigError):
+        from_dict(PpoConfig, {"ppo_kl_cov_ratio": 0.01, "kl_cov_ratio": 0.02})

@@ -129,3 +129,35 @@ def test_vision_policy_from_config():
                        model_cfg=get_preset("tiny_llama", dtype="float32"))
     e.setup_model_and_get_optimizer(seed=1)
     assert isinstance(e.model, VLModel) and e.model.image_token_id == 5 and e.model.vc.num_layers == 1
+
+
+def test_freeze_flags_select_tower_projector_decoder_router_and_shared_experts():
+    """``training.freeze_*``: each flag takes exactly its parameter group out of training."""
+    from gcore_b200.configs.base import from_dict
+    from gcore_b200.configs.config import OptimizerConfig, PolicyConfig, TrainingConfig
+    from gcore_b200.engine.train_engine import TrainingEngine
+    from gcore_b200.models.config import ModelConfig
+    mc = ModelConfig(arch="qwen3_moe", num_layers=2, hidden_size=64, num_attention_heads=2, num_kv_heads=2,
+                     ffn_hidden_size=128, vocab_size=128, num_experts=4, moe_top_k=2, moe_ffn_hidden_size=32,
+                     moe_shared_expert_ffn=32, dtype="float32")
+
+    def frozen(**flags):
+        pc = from_dict(PolicyConfig, {"recompute": "none", "without_ref": True, "image_token_id": 5,
+                                      "vision_config": {"patch_size": 2, "hidden_size": 64, "num_layers": 1,
+                                                        "num_heads": 2, "ffn_hidden_size": 128, "max_grid": 8}})
+        e = TrainingEngine(pc, OptimizerConfig(lr=1e-3), TrainingConfig(train_mbs=2, train_gbs=2, **flags), model_cfg=mc)
+        e.setup_model_and_get_optimizer(seed=1)
+        names = [n for n, _ in e.model.named_parameters()]
+        return names, {n for n, p in e.model.named_parameters() if not p.requires_grad}
+
+    names, f = frozen()
+    assert not f
+    names, f = frozen(freeze_vit=True)
+    assert f == {n for n in names if n.startswith("vision.") and "merge_fc" not in n} and f
+    names, f = frozen(freeze_projector=True)
+    assert f == {n for n in names if n.startswith("vision.merge_fc")} and len(f) >= 2
+    names, f = frozen(freeze_llm=True)
+    assert f == {n for n in names if not n.startswith("vision.")}
+    names, f = frozen(freeze_moe_router=True, freeze_moe_shared_experts=True)
+    assert f == {n for n in names if ".router." in n or ".shared_experts." in n} and \
+        any(".router." in n for n in f) and any(".shared_experts." in n for n in f)

@@ -508,6 +508,11 @@ class TrainingConfig(MappingMixin):
     freeze_llm: bool = False
     freeze_vit: bool = False
     freeze_projector: bool = False
+    # selection bias of sigmoid routers (loss-free load balancing): frozen by default; when released it moves by
+    # update_speed per step towards the mean expert load (sign update, or the log-ratio update)
+    freeze_router_correction_bias: bool = True
+    router_correction_bias_update_speed: float = 1e-3
+    router_correction_bias_use_abs_update: bool = True
     # held-out evaluation inside the RL loop: also once before the first step; its own samples per prompt
     eval_before_train: bool = False
     eval_sampling_repeat_n: Optional[int] = None

@@ -53,6 +53,8 @@ def backend_scope(backend: str):
 
 
 class TrainingEngine:
+    router_bias_violation = None   # (max, mean) load violation of the last router-bias update, when it is on
+
     def __init__(self, policy_cfg, optimizer_cfg, training_cfg, ppo_cfg=None, model_cfg: Optional[ModelConfig] = None,
                  role: str = "policy", value_head: bool = False, total_steps: Optional[int] = None,
                  vision_cfg=None, image_token_id: Optional[int] = None):
@@ -409,6 +411,15 @@ class TrainingEngine:
         self.ddp.finish_grad_sync(extra_scale=float(dp))
         lr = self.optimizer.step(lr)
         self.step += 1
+        self.router_bias_violation = None
+        t = self.train_cfg
+        if not getattr(t, "freeze_router_correction_bias", True) and getattr(self.model_cfg, "moe_router_bias", False):
+            from ..models.moe import update_router_bias
+            groups = [ps.get_data_parallel_group(with_context_parallel=True)]
+            if ps.get_tensor_model_parallel_world_size() > 1:
+                groups.append(ps.get_tensor_model_parallel_group())
+            self.router_bias_violation = update_router_bias(self.model, t.router_correction_bias_update_speed,
+                                                            t.router_correction_bias_use_abs_update, groups)
         return lr, float(self.optimizer.last_grad_norm.item())
 
     def _reduce_metrics(self, acc: Dict[str, torch.Tensor]) -> Dict[str, float]:
@@ -468,6 +479,8 @@ class TrainingEngine:
             lr, gn = self._finish_step()
         out = self._reduce_metrics(acc)
         out.update(lr=lr, grad_norm=gn)
+        if self.router_bias_violation is not None:
+            out["moe/max_violation"], out["moe/mean_violation"] = self.router_bias_violation
         return out
 
     pretrain_step = finetune_step
@@ -555,6 +568,8 @@ class TrainingEngine:
             lr, gn = self._finish_step()
         out = self._reduce_metrics(acc)
         out.update({"policy/lr": lr, "policy/grad_norm": gn})
+        if self.router_bias_violation is not None:
+            out["moe/max_violation"], out["moe/mean_violation"] = self.router_bias_violation
         return out
 
     def _resolve_loss(self):

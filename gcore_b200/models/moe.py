@@ -50,8 +50,12 @@ class Router(nn.Module):
         if cfg.moe_router_bias:
             # selection-only bias updated outside autograd (aux-loss-free balancing)
             self.register_buffer("expert_bias", torch.zeros(cfg.num_experts, dtype=torch.float32, device=device))
+            # tokens routed to each expert since the last bias update (training passes only)
+            self.register_buffer("tokens_per_expert", torch.zeros(cfg.num_experts, dtype=torch.float32, device=device),
+                                 persistent=False)
         else:
             self.expert_bias = None
+            self.tokens_per_expert = None
         self.lora = None   # optional low-rank adapter on the routing matrix ("router" in lora.target_modules)
 
     def forward(self, x):
@@ -91,6 +95,11 @@ class Router(nn.Module):
             scores_for_aux = scores / scores.sum(-1, keepdim=True).clamp_min(1e-20)
         if RouterReplay.mode == "record":
             RouterReplay.put(self.layer_idx, idx.detach())
+        if self.tokens_per_expert is not None and self.training and torch.is_grad_enabled():
+            # with activation recomputation the first pass runs without grad, so every token is counted once
+            with torch.no_grad():
+                flat = idx.reshape(-1)
+                self.tokens_per_expert.scatter_add_(0, flat, torch.ones_like(flat, dtype=torch.float32))
         aux = None
         if self.training and (cfg.moe_aux_loss_coef > 0 or cfg.moe_z_loss_coef > 0):
             aux = x.new_zeros((), dtype=torch.float32)
@@ -104,6 +113,33 @@ class Router(nn.Module):
             if cfg.moe_z_loss_coef > 0:
                 aux = aux + cfg.moe_z_loss_coef * torch.logsumexp(logits, -1).pow(2).mean()
         return idx, w, aux
+
+
+@torch.no_grad()
+def update_router_bias(model: nn.Module, speed: float, use_abs: bool = True, groups=()):
+    """Loss-free load balancing (arXiv 2408.15664): after an optimizer step the selection bias of every expert moves by
+    ``speed`` towards the mean load, ``sign(mean - count)`` (``use_abs``) or ``log((mean + 1) / (count + 1))``; counts
+    are summed over ``groups`` (the groups that shard tokens: data / context parallel and the sequence-parallel tensor
+    group).  Returns (max, mean) over layers of the maximal violation ``(max_e count - mean) / mean``, or None when no
+    router carries a bias (gpatch_v4/models/deepseek_v4/freeze_update_router.py:120-178)."""
+    import torch.distributed as dist
+    routers = [m for m in model.modules() if isinstance(m, Router) and m.tokens_per_expert is not None]
+    if not routers:
+        return None
+    counts = torch.stack([r.tokens_per_expert for r in routers]).double()
+    for g in groups:
+        if g is not None and dist.is_initialized() and dist.get_world_size(g) > 1:
+            dist.all_reduce(counts, group=g)
+    avg = counts.mean(-1, keepdim=True)
+    if use_abs:
+        delta = torch.sign(avg - counts) * speed
+    else:
+        delta = torch.log((avg + 1.0) / (counts + 1.0)) * speed
+    for i, r in enumerate(routers):
+        r.expert_bias.add_(delta[i].to(r.expert_bias.dtype))
+        r.tokens_per_expert.zero_()
+    vio = (counts.max(-1).values - avg[:, 0]) / avg[:, 0].clamp_min(1e-12)
+    return float(vio.max()), float(vio.mean())
 
 
 def build_dispatch_plan(expert_ids: torch.Tensor, num_experts: int):

@@ -703,3 +703,57 @@ def test_native_planners_properties():
         if n % k == 0:
             eq = kk_partition(lens, k, equal_size=True)
             assert all(len(p) == n // k for p in eq) and sorted(i for p in eq for i in p) == list(range(n))
+
+
+def test_loss_free_load_balancing_moves_the_router_bias_towards_even_load():
+    """A sigmoid router with a selection bias, released by ``freeze_router_correction_bias=false``: every step the bias
+    of over-loaded experts drops and that of under-loaded ones rises by the update speed, the counts are reset, and
+    over the steps the load violation shrinks; the frozen default leaves the bias alone."""
+    from gcore_b200.configs.config import OptimizerConfig, PolicyConfig, TrainingConfig
+    from gcore_b200.engine.train_engine import TrainingEngine
+    from gcore_b200.models.config import ModelConfig
+    from gcore_b200.models.moe import Router, update_router_bias
+    mc = ModelConfig(arch="deepseek_v3", num_layers=2, hidden_size=64, num_attention_heads=2, num_kv_heads=2,
+                     ffn_hidden_size=128, vocab_size=128, num_experts=8, moe_top_k=2, moe_ffn_hidden_size=32,
+                     moe_router_type="sigmoid_group", moe_router_bias=True, moe_n_group=1, moe_topk_group=1,
+                     dtype="float32")
+
+    def engine(**tk):
+        e = TrainingEngine(PolicyConfig(recompute="none", without_ref=True),
+                           OptimizerConfig(lr=0.0, lr_decay_style="constant", weight_decay=0.0),
+                           TrainingConfig(train_mbs=4, train_gbs=4, **tk), model_cfg=mc)
+        e.setup_model_and_get_optimizer(seed=3)
+        return e
+
+    g = torch.Generator().manual_seed(0)
+    batch = [{"tokens": torch.randint(3, 128, (64,), generator=g), "loss_mask": torch.ones(64)} for _ in range(4)]
+    e = engine()
+    e.finetune_step(batch)
+    routers = [m for m in e.model.modules() if isinstance(m, Router)]
+    assert routers and all(float(r.expert_bias.abs().sum()) == 0.0 for r in routers)
+
+    e = engine(freeze_router_correction_bias=False, router_correction_bias_update_speed=0.01)
+    routers = [m for m in e.model.modules() if isinstance(m, Router)]
+    # make the first expert of the first MoE layer the favourite, so that the start is clearly unbalanced
+    with torch.no_grad():
+        routers[0].weight[0] += 0.5 * routers[0].weight[0].sign()
+    first = e.finetune_step(batch)
+    r = routers[0]
+    assert float(r.tokens_per_expert.sum()) == 0.0                       # reset after the update
+    assert all(min(abs(v), abs(v - 0.01)) < 1e-6 for v in r.expert_bias.abs().tolist())
+    assert "moe/max_violation" in first
+    vio = [first["moe/max_violation"]] + [e.finetune_step(batch)["moe/max_violation"] for _ in range(30)]
+    assert min(vio[-5:]) < vio[0], vio
+    # counts: one per routed (token, k) pair of the step, each layer
+    e.model.train()
+    hidden = torch.randn(10, 64)
+    routers[0](hidden)
+    assert float(routers[0].tokens_per_expert.sum()) == 20.0
+    with torch.no_grad():
+        routers[0](hidden)                                               # passes without grad are not counted
+    assert float(routers[0].tokens_per_expert.sum()) == 20.0
+    before = routers[0].expert_bias.clone()
+    c = routers[0].tokens_per_expert.clone()
+    update_router_bias(e.model, 0.1, use_abs=False)
+    want = before + 0.1 * torch.log((c.mean() + 1) / (c + 1))
+    assert torch.allclose(routers[0].expert_bias, want, atol=1e-6)

@@ -642,9 +642,19 @@ class RlConfig(BaseTopConfig):
 class DpoConfig(RlConfig):
     """``train_lm_dpo``: the sections of the RL configuration plus the preference-loss options at the top level."""
     dpo_beta: float = 0.1
+    dpo_loss_type: str = "sigmoid"
     dpo_label_smoothing: float = 0.0
-    dpo_sft_loss_coef: float = 0.0
+    dpo_sft_loss_coef: float = 0.0      # weight of the cross-entropy term on the chosen responses
     reference_free: bool = False
+
+    _aliases = {"dpo_ftx_gamma": "dpo_sft_loss_coef"}
+
+    def __post_init__(self):
+        sup = getattr(super(), "__post_init__", None)
+        if sup is not None:
+            sup()
+        if self.dpo_loss_type != "sigmoid":
+            raise ConfigError(f"dpo_loss_type must be sigmoid, got {self.dpo_loss_type}")
 
 
 @dataclass

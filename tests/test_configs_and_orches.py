@@ -156,3 +156,13 @@ def test_reference_spellings_of_ppo_fields_are_accepted():
     import pytest
     with pytest.raises(ConfigError):
         from_dict(PpoConfig, {"ppo_kl_cov_ratio": 0.01, "kl_cov_ratio": 0.02})
+
+
+def test_dpo_config_options_and_alias():
+    import pytest
+    from gcore_b200.configs.base import ConfigError, from_dict
+    from gcore_b200.configs.config import DpoConfig
+    c = from_dict(DpoConfig, {"dpo_beta": 0.2, "dpo_ftx_gamma": 0.3})
+    assert c.dpo_beta == 0.2 and c.dpo_sft_loss_coef == 0.3 and c.dpo_loss_type == "sigmoid"
+    with pytest.raises(ConfigError):
+        from_dict(DpoConfig, {"dpo_loss_type": "ipo"})

@@ -306,6 +306,7 @@ class PolicyConfig(MappingMixin):
     forward_only_mbs: int = 1
     dynamic_mbs_target_seqlen: Optional[int] = None
     dynamic_mbs_limit: Optional[int] = None
+    dynamic_mbs_target_seqlen_fwd_only: Optional[int] = None  # token budget of forward-only micro-batches
     ppo_pack_seq: bool = True
     without_ref: bool = False
     without_optim: bool = False

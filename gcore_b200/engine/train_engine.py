@@ -35,6 +35,13 @@ def _device():
     return torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
 
 
+class FillerBatch(list):
+    """Sample indices of a micro-batch that exists only so that every rank of a group runs the same number of
+    micro-batches (each one carries the group's per-layer collectives).  It is packed like any other micro-batch,
+    with its loss mask zeroed: it adds nothing to the loss, the gradients or the metrics, and its forward-only
+    results are dropped."""
+
+
 @contextlib.contextmanager
 def backend_scope(backend: str):
     """``nccl_eager`` forces the eager implementation of every op for the duration of the call."""
@@ -319,6 +326,8 @@ class TrainingEngine:
         pad = self._pad_multiple()
         cpg = self._cp_group()
         mb = pack_samples(samples, idx, keys, pad_to_multiple=pad, pin=self.device.type == "cuda")
+        if isinstance(idx, FillerBatch):
+            mb.loss_mask.zero_()
         if cpg is not None:
             from ..parallel.cp import shard_packed_batch
             PL.set_context_parallel_group(cpg)
@@ -332,7 +341,36 @@ class TrainingEngine:
         pc = self.policy_cfg
         max_tok = pc.dynamic_mbs_target_seqlen
         mbs = pc.forward_only_mbs if forward_only else self.train_cfg.train_mbs
-        return make_microbatches(lens, mbs=mbs, max_tokens=max_tok)
+        if forward_only and getattr(pc, "dynamic_mbs_target_seqlen_fwd_only", None):
+            max_tok = pc.dynamic_mbs_target_seqlen_fwd_only
+        batches = make_microbatches(lens, mbs=mbs, max_tokens=max_tok)
+        return self._equalize_microbatch_count(batches, lens)
+
+    def _equalize_microbatch_count(self, batches, lens):
+        """Expert-parallel ranks are data-parallel ranks with their own samples, and every MoE layer runs one
+        all-to-all per micro-batch: all of them must run the same number of micro-batches, whatever their local
+        lengths pack into (the reference derives one micro-batch size from the group-max sequence length,
+        gpatch_v4/training_backend/megatron_backend/mixin.py:2743-2765).  Ranks with fewer micro-batches first split
+        their largest ones, then append filler micro-batches (see ``FillerBatch``)."""
+        if ps.get_expert_model_parallel_world_size() <= 1 or not dist.is_initialized():
+            return batches
+        g = ps.get_data_parallel_group(with_context_parallel=True)
+        if g is None or dist.get_world_size(g) <= 1:
+            return batches
+        t = torch.tensor([len(batches)], dtype=torch.int64,
+                         device=self.device if dist.get_backend(g) == "nccl" else "cpu")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=g)
+        want = int(t.item())
+        batches = [list(b) for b in batches]
+        while len(batches) < want:
+            k = max(range(len(batches)), key=lambda i: len(batches[i])) if batches else -1
+            if k >= 0 and len(batches[k]) > 1:
+                b = batches.pop(k)
+                batches += [b[:len(b) // 2], b[len(b) // 2:]]
+            else:
+                shortest = min(range(len(lens)), key=lambda i: lens[i])
+                batches.append(FillerBatch([shortest]))
+        return batches
 
     # ------------------------------------------------------------------ log-probs (forward only)
     @torch.no_grad()
@@ -354,6 +392,8 @@ class TrainingEngine:
 
             results = self._for_each_microbatch(model, samples, batches, (), step, forward_only=True)
             for bi, idx in enumerate(batches):
+                if isinstance(idx, FillerBatch):
+                    continue
                 lens = [len(samples[i]["tokens"]) for i in idx]
                 total = sum(lens)
                 pad_mult = self._pad_multiple()
@@ -384,6 +424,8 @@ class TrainingEngine:
             for idx in self._microbatches(samples, forward_only=True):
                 mb = self._pack(samples, idx)
                 v, _ = self._hidden(self.model, mb)
+                if isinstance(idx, FillerBatch):
+                    continue
                 vc = self._gather_cp(v.float()).cpu()
                 cu = mb.cu_seqlens.tolist()
                 for j, i in enumerate(idx):
@@ -404,6 +446,14 @@ class TrainingEngine:
             dist.all_reduce(tt, group=g)
             n = float(tt.item())
         return max(n, 1.0)
+
+    def _aux_scale(self, n_microbatches: int) -> float:
+        """Weight of one micro-batch's MoE auxiliary (load-balance / z) loss.  Gradients are *summed* over the
+        micro-batches and over data-parallel ranks (``_finish_step``), so the auxiliary term is divided by both counts:
+        the effective ``moe_aux_loss_coef`` is then the configured one whatever the parallel layout or the packing
+        (Megatron scales by 1 / num_microbatches and averages over data parallel)."""
+        dp = ps.get_data_parallel_world_size(with_context_parallel=True)
+        return 1.0 / (max(n_microbatches, 1) * max(dp, 1))
 
     def _finish_step(self, lr=None):
         dp = ps.get_data_parallel_world_size(with_context_parallel=True)
@@ -464,13 +514,14 @@ class TrainingEngine:
         acc = {"lm_loss": torch.zeros(2, device=self.device)}
         with backend_scope(self.backend):
             batches = self._microbatches(samples)
+            aux_scale = self._aux_scale(len(batches))
 
             def step(mb, hidden, aux):
                 lp, _ = self._logprob_entropy(self.model, hidden, mb.targets, False, mb.loss_mask)
                 w = PL.aggregation_weights(mb.loss_mask, mb.seq_ids, mb.num_seqs + 1, per_token, denom)
                 loss = -(lp * w).sum()
                 if aux is not None:
-                    loss = loss + aux / max(len(batches), 1)
+                    loss = loss + aux * aux_scale
                 with torch.no_grad():
                     acc["lm_loss"] += torch.stack([-(lp.detach() * mb.loss_mask).sum(), mb.loss_mask.sum()])
                 return loss
@@ -505,6 +556,14 @@ class TrainingEngine:
         if has_roll or cfg.loss_func == "vespo":
             keys.append("rollout_log_probs")
         want_ent = cfg.ppo_entropy_bonus != 0 or cfg.loss_func == "steer"
+        has_old_ent = False
+        if cfg.loss_func == "steer":
+            # STEER weights tokens by the entropy of the policy that generated the batch, not the current one
+            # (gpatch_v4/training_backend/loss/ppo_loss.py:387,409-416)
+            assert not cfg.skip_prev_logps, "the steer loss needs the previous-policy pass (skip_prev_logps must be off)"
+            has_old_ent = all("prev_per_token_entropies" in s for s in samples)
+            if has_old_ent:
+                keys.append("prev_per_token_entropies")
         fast = (cfg.loss_func == "grpo" and not has_roll and not want_ent and cfg.kl_estimator == "k3"
                 and cfg.loss_func_py_path is None and not cfg.entropy_regularization_type)
         loss_fn = None if fast else self._resolve_loss()
@@ -536,7 +595,8 @@ class TrainingEngine:
                     add("ppo-metrics/approx_kl", torch.stack([st[5], st[2]]))
                 else:
                     li = PL.LossInput(lp, old, ref, f.get("rollout_log_probs"), f["advantages"], mb.loss_mask,
-                                      mb.seq_ids, mb.num_seqs + 1, ent, None)
+                                      mb.seq_ids, mb.num_seqs + 1, ent,
+                                      f.get("prev_per_token_entropies") if has_old_ent else None)
                     lo = loss_fn(cfg, li)
                     tl = lo.token_loss
                     if has_roll and cfg.loss_func != "vespo":
@@ -561,10 +621,12 @@ class TrainingEngine:
                     if ent is not None:
                         add("policy/entropy", torch.stack([(ent.detach() * mb.loss_mask).sum(), mb.loss_mask.sum()]))
                 if aux is not None:
-                    loss = loss + aux
+                    loss = loss + aux * aux_scale
                 return loss
 
-            self._for_each_microbatch(self.model, samples, self._microbatches(samples), keys, step)
+            batches = self._microbatches(samples)
+            aux_scale = self._aux_scale(len(batches))
+            self._for_each_microbatch(self.model, samples, batches, keys, step)
             lr, gn = self._finish_step()
         out = self._reduce_metrics(acc)
         out.update({"policy/lr": lr, "policy/grad_norm": gn})

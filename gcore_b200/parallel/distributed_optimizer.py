@@ -350,6 +350,8 @@ class DistributedOptimizer:
             buf, s, e = sh["buf"], sh["s"], sh["e"]
             if skip_peer and buf.peer:
                 continue
+            if not buf.use_distributed_optimizer and buf.dp > 1 and buf.dp_rank != 0:
+                continue  # every rank of the reduction group holds the whole bucket: count it once
             g = buf.grad_data[s:e]
             if tp_rank == 0 or ps.get_tensor_model_parallel_world_size() == 1:
                 optim_ops.sumsq(g, total)

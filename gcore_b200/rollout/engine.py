@@ -560,9 +560,18 @@ class InferEngine:
         logits = linear_forward(hidden, self.w.head, out_dtype=torch.float32)
         sp = st["params"]
         if sp["filtered"]:
+            tp_group, vocab_start = (self.tp_group, self.vocab_start) if self.tp > 1 else (None, 0)
+            if self.tp > 1:
+                # top-k / top-p / min-p are properties of the whole distribution: the k-th value and the nucleus
+                # threshold of a vocabulary shard are not those of the vocabulary.  Gather the shards, filter the
+                # full row on every rank (same result everywhere: the sampler's random stream depends only on
+                # seed, step and token id), and sample without a cross-rank merge.
+                parts = [torch.empty_like(logits) for _ in range(self.tp)]
+                dist.all_gather(parts, logits.contiguous(), group=self.tp_group)
+                logits = torch.cat(parts, dim=1)
+                tp_group, vocab_start = None, 0
             logits = apply_top_k_top_p(logits / max(sp["temperature"], 1e-6), sp["top_k"], sp["top_p"], sp["min_p"])
-            tok, lp = sample(logits.contiguous(), 1.0, st["seeds"], st["steps"], sp["greedy"], self.tp_group
-                             if self.tp > 1 else None, self.vocab_start)
+            tok, lp = sample(logits.contiguous(), 1.0, st["seeds"], st["steps"], sp["greedy"], tp_group, vocab_start)
         else:
             tok, lp = sample(logits, sp["temperature"], st["seeds"], st["steps"], sp["greedy"],
                              self.tp_group if self.tp > 1 else None, self.vocab_start)

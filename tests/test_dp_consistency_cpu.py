@@ -1,0 +1,66 @@
+"""Properties that must not depend on how a batch is spread over data-parallel ranks or packed into micro-batches
+(gloo, world 2): equal micro-batch counts under expert parallelism with a token budget, the weight of the MoE
+auxiliary loss, the gradient norm without a sharded optimizer, and top-k / top-p / min-p sampling with a
+vocabulary-sharded head."""
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, os.path.join(ROOT, "tests", "workers"))
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+from test_parallel_cpu import _spawn  # noqa: E402
+
+
+def test_ep_ranks_run_equal_microbatch_counts_under_a_token_budget(tmp_path):
+    out = tmp_path / "dyn.json"
+    _spawn("ep_dynmbs", out, port="29561")
+    got = json.load(open(out))
+    for step in range(2):
+        assert got["counts"][0][step] == got["counts"][1][step] > 1, got["counts"]
+    assert all(l == l and l > 0 for l in got["losses"])
+    assert got["n_logprobs"] == 3
+
+
+def test_moe_aux_loss_weight_is_independent_of_dp_and_microbatching(tmp_path):
+    import parallel_worker as pw
+    out = tmp_path / "aux.json"
+    _spawn("aux_dp", out, port="29563")
+    got = json.load(open(out))
+    e = pw.engine(pw.MOE_CFG, 1)
+    batch = pw.samples(8, 190, vocab=512)
+    for b in batch:
+        b["loss_mask"] = torch.zeros_like(b["loss_mask"])
+    ref = e.finetune_step(batch)["grad_norm"]   # one rank, the same four micro-batches of two samples
+    assert ref > 0
+    assert abs(ref - got["grad_norm"]) < 1e-5 * max(ref, 1.0) + 1e-7, (ref, got)
+
+
+def test_grad_norm_without_sharded_optimizer_counts_each_bucket_once(tmp_path):
+    out = tmp_path / "norm.json"
+    _spawn("nodistopt", out, port="29565")
+    a, b = json.load(open(out))["norms"]
+    assert abs(a - b) < 1e-4 * max(a, 1.0), (a, b)
+
+
+def test_tp2_filtered_sampling_equals_single_rank(tmp_path):
+    from gcore_b200.models.config import get_preset
+    from gcore_b200.models.gpt import GPTModel
+    from gcore_b200.rollout.engine import InferEngine, RolloutWeights, SamplingParams
+    out = tmp_path / "topk.json"
+    _spawn("tp_topk", out, port="29567")
+    got = json.load(open(out))
+    mcfg = get_preset("tiny_llama", dtype="float32", qkv_bias=True)
+    model = GPTModel(mcfg, recompute="none")
+    model.reset_parameters(21)
+    model.eval()
+    eng = InferEngine(mcfg, RolloutWeights.from_model(model), max_running_requests=4, max_model_len=48,
+                      kv_block_size=4, sync_interval=2, use_cuda_graph=False)
+    for name, kw in (("top_k", dict(top_k=3)), ("top_p", dict(top_p=0.3)), ("min_p", dict(min_p=0.2))):
+        reqs = eng.generate(got["prompts"], SamplingParams(max_new_tokens=6, temperature=1.5, seed=5, **kw), n=2)
+        assert [r.out_tokens for r in reqs] == got["out"][name]["tokens"], name
+        for a, b in zip(reqs, got["out"][name]["logprobs"]):
+            assert max(abs(x - y) for x, y in zip(a.out_logprobs, b)) < 1e-4, name

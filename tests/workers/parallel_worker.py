@@ -1,4 +1,5 @@
-"""gloo worker for the parallelism parity tests: mode = tp | ep | ep_rollout | ep_grpo | cp | pp | vpp | fsdp."""
+"""gloo worker for the parallelism parity tests: mode = tp | ep | ep_rollout | ep_grpo | cp | pp | vpp | fsdp |
+ep_dynmbs | aux_dp | tp_topk | nodistopt."""
 import json
 import os
 import sys
@@ -24,6 +25,11 @@ def samples(n, seed, L=48, vocab=1024):
         m[ln // 3:ln - 1] = 1
         out.append({"tokens": t, "loss_mask": m})
     return out
+
+
+MOE_CFG = ModelConfig(arch="qwen3_moe", num_layers=2, hidden_size=128, num_attention_heads=4, num_kv_heads=2,
+                      ffn_hidden_size=256, vocab_size=512, num_experts=8, moe_top_k=2, moe_ffn_hidden_size=64,
+                      moe_aux_loss_coef=1e-2, dtype="float32", qk_layernorm=True)
 
 
 def engine(mcfg, tp, sp=True, lr=1e-3, vpp=None):
@@ -171,6 +177,64 @@ def main():
             e2.setup_model_and_get_optimizer(seed=99)
             assert e2.load_checkpoint(sys.argv[3]) == 4
             res["next_loss"] = [x.finetune_step(samples(8, 160)[rank::world])["lm_loss"] for x in (e, e2)]
+    elif mode == "ep_dynmbs":
+        # expert-parallel ranks whose samples pack into different numbers of micro-batches (rank 0: six long samples,
+        # rank 1: two short ones) under a token budget: every rank must still run the same number of all-to-alls
+        ps.initialize_model_parallel(tp=1, ep=2)
+        e = engine(MOE_CFG, 1)
+        e.policy_cfg.dynamic_mbs_target_seqlen = 64
+        losses, counts = [], []
+        for s in range(2):
+            batch = samples(8, 170 + s, vocab=512)
+            batch.sort(key=lambda x: -len(x["tokens"]))
+            mine = batch[:6] if rank == 0 else batch[6:]
+            counts.append(len(e._microbatches(mine)))
+            losses.append(e.finetune_step(mine)["lm_loss"])
+        lp = e.compute_log_probs(samples(3 if rank == 0 else 1, 180 + rank, vocab=512))
+        allc = [None, None]
+        dist.all_gather_object(allc, counts)
+        res = {"losses": losses, "counts": allc, "n_logprobs": len(lp)}
+    elif mode == "aux_dp":
+        # only the MoE auxiliary loss has a gradient (loss masks are zero): two data-parallel ranks with two
+        # micro-batches each must produce the gradient of one rank running the same four micro-batches
+        ps.initialize_model_parallel(tp=1)
+        e = engine(MOE_CFG, 1)
+        batch = samples(8, 190, vocab=512)
+        for b in batch:
+            b["loss_mask"] = torch.zeros_like(b["loss_mask"])
+        m = e.finetune_step(batch[rank * 4:(rank + 1) * 4])
+        res = {"grad_norm": m["grad_norm"]}
+    elif mode == "nodistopt":
+        ps.initialize_model_parallel(tp=1)
+        mcfg = get_preset("tiny_llama", dtype="float32", qkv_bias=True)
+        norms = []
+        for dist_opt in (True, False):
+            pc = PolicyConfig(recompute="none", without_ref=True)
+            oc = OptimizerConfig(lr=1e-3, lr_decay_style="constant", weight_decay=0.0, max_grad_norm=1.0,
+                                 use_distributed_optimizer=dist_opt)
+            e = TrainingEngine(pc, oc, TrainingConfig(train_mbs=2, train_gbs=8), model_cfg=mcfg)
+            e.setup_model_and_get_optimizer(seed=11)
+            norms.append(e.finetune_step(samples(8, 200)[rank::world])["grad_norm"])
+        res = {"norms": norms}
+    elif mode == "tp_topk":
+        # vocabulary-sharded head with top-k / top-p / min-p: the filter must act on the whole vocabulary
+        from gcore_b200.models.gpt import GPTModel
+        from gcore_b200.rollout.engine import InferEngine, RolloutWeights, SamplingParams
+        ps.initialize_model_parallel(tp=2)
+        mcfg = get_preset("tiny_llama", dtype="float32", qkv_bias=True)
+        model = GPTModel(mcfg, tp_size=2, recompute="none")
+        model.reset_parameters(21)
+        model.eval()
+        eng = InferEngine(mcfg, RolloutWeights.from_model(model), tp_size=2,
+                          tp_group=ps.get_tensor_model_parallel_group(), max_running_requests=4, max_model_len=48,
+                          kv_block_size=4, sync_interval=2, use_cuda_graph=False)
+        g = torch.Generator().manual_seed(100)
+        prompts = [torch.randint(3, 1024, (5 + 2 * i,), generator=g).tolist() for i in range(2)]
+        out_all = {}
+        for name, kw in (("top_k", dict(top_k=3)), ("top_p", dict(top_p=0.3)), ("min_p", dict(min_p=0.2))):
+            reqs = eng.generate(prompts, SamplingParams(max_new_tokens=6, temperature=1.5, seed=5, **kw), n=2)
+            out_all[name] = {"tokens": [r.out_tokens for r in reqs], "logprobs": [r.out_logprobs for r in reqs]}
+        res = {"prompts": prompts, "out": out_all}
     if rank == 0:
         json.dump(res, open(out, "w"))
     dist.barrier()

@@ -1,7 +1,16 @@
-"""Per-kernel timing on one GPU with CUDA events (warm-up, L2 flush between iterations), reported against the
-measured roofline denominators in ``MEASURED_PEAKS.json`` when present.
+"""Kernel and phase timing on one GPU with CUDA events (warm-up, inputs or L2 flush larger than L2), reported
+against the measured roofline denominators in ``MEASURED_PEAKS.json`` when present.
 
-``python -m gcore_b200.tools.kernel_bench [--out file.json] [--quick]``
+``python -m gcore_b200.tools.kernel_bench [--out file.json] [--quick]``      the training / decode shape table
+``python -m gcore_b200.tools.kernel_bench gemm --tokens 64 --n 37888 --k 3584 [--iters 5] [--layout fwd|dgrad|wgrad]``
+``python -m gcore_b200.tools.kernel_bench attn --batch 2 --seq 2048 --heads 8 --kv-heads 2 [--bwd] [--sdpa]``
+``python -m gcore_b200.tools.kernel_bench paged --tokens 64 --heads 28 --kv-heads 4 --ctx 768 --max-ctx 1280 [--graph]``
+``python -m gcore_b200.tools.kernel_bench decode_chain [--tokens 64] [--tp 1] [--json out.json]``   per-kernel cost
+                                                                 of one decoder layer under CUDA-graph replay
+``python -m gcore_b200.tools.kernel_bench train_step --model qwen2.5-7b --layers 8 --tokens 8192 --seqlen 1280``
+
+The single-shape sub-commands launch one kernel a few times, which also makes them the small cases profilers are
+pointed at.
 """
 from __future__ import annotations
 
@@ -9,6 +18,7 @@ import argparse
 import json
 import os
 import sys
+import time
 
 import torch
 
@@ -49,11 +59,12 @@ def time_fn(fn, iters=10, warmup=3):
     return ts[len(ts) // 2]
 
 
-def main():
+def cmd_table(argv=None):
+    """Training and decode shapes of the 7B recipe against the library twin of each kernel."""
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default=None)
     ap.add_argument("--quick", action="store_true")
-    args = ap.parse_args()
+    args = ap.parse_args(argv)
     from gcore_b200.ops import _lib
     from gcore_b200.ops.attention import flash_attn_varlen, paged_decode
     from gcore_b200.ops.gemm import gemm, linear_forward
@@ -133,6 +144,325 @@ def main():
     if args.out:
         os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
         json.dump(res, open(args.out, "w"), indent=1)
+
+
+def cmd_gemm(argv=None):
+    """Runs one GEMM shape a few times (for ncu captures and quick timing)."""
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", "--T", type=int, default=64)
+    ap.add_argument("--n", "--N", type=int, default=37888)
+    ap.add_argument("--k", "--K", type=int, default=3584)
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--layout", default="fwd")
+    args = ap.parse_args(argv)
+    from gcore_b200.ops import _lib
+    from gcore_b200.ops.gemm import linear_dgrad, linear_forward, linear_wgrad
+    T, N, K = args.tokens, args.n, args.k
+    x = torch.randn(T, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()
+    dy = torch.randn(T, N, device="cuda").bfloat16()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    fn = {"fwd": lambda: linear_forward(x, w), "dgrad": lambda: linear_dgrad(dy, w),
+          "wgrad": lambda: linear_wgrad(dy, x)}[args.layout]
+    ts = []
+    for _ in range(args.iters):
+        flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    _lib.check_device_errors()
+    print(f"{args.layout} T={T} N={N} K={K}: ms per call {[round(t, 4) for t in ts]}")
+
+
+def cmd_attn(argv=None):
+    """Runs one flash-attention shape a few times (for ncu captures and quick timing)."""
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=2)
+    ap.add_argument("--seq", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=8)
+    ap.add_argument("--kv-heads", type=int, default=2)
+    ap.add_argument("--dim", type=int, default=128)
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--bwd", action="store_true")
+    ap.add_argument("--sdpa", action="store_true", help="time torch SDPA on the same shape instead")
+    a = ap.parse_args(argv)
+    from gcore_b200.ops import _lib
+    from gcore_b200.ops.attention import flash_attn_varlen
+    B, L, H, Hk, D = a.batch, a.seq, a.heads, a.kv_heads, a.dim
+    T = B * L
+    q = torch.randn(T, H, D, device="cuda").bfloat16().requires_grad_(a.bwd)
+    k = torch.randn(T, Hk, D, device="cuda").bfloat16().requires_grad_(a.bwd)
+    v = torch.randn(T, Hk, D, device="cuda").bfloat16().requires_grad_(a.bwd)
+    do = torch.randn(T, H, D, device="cuda").bfloat16()
+    cu = torch.arange(0, T + 1, L, dtype=torch.int32, device="cuda")
+    flops = 4.0 * B * H * L * L * D / 2 * (3.5 if a.bwd else 1.0)
+
+    def run():
+        if a.sdpa:
+            qq = q.view(B, L, H, D).transpose(1, 2)
+            kk = k.view(B, L, Hk, D).transpose(1, 2).repeat_interleave(H // Hk, 1)
+            vv = v.view(B, L, Hk, D).transpose(1, 2).repeat_interleave(H // Hk, 1)
+            o = torch.nn.functional.scaled_dot_product_attention(qq, kk, vv, is_causal=True)
+            if a.bwd:
+                o.backward(do.view(B, L, H, D).transpose(1, 2))
+            return
+        o = flash_attn_varlen(q, k, v, cu, cu, L, L, causal=True)
+        if a.bwd:
+            o.backward(do)
+
+    ts = []
+    for _ in range(a.iters):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        run()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    _lib.check_device_errors()
+    best = min(ts[1:]) if len(ts) > 1 else ts[0]
+    print(f"attn B={B} L={L} H={H}/{Hk} D={D} bwd={a.bwd} sdpa={a.sdpa}: ms {[round(t, 4) for t in ts]} "
+          f"-> {flops / best / 1e9:.0f} TFLOP/s (causal FLOPs)")
+
+
+def cmd_paged(argv=None):
+    """Runs the paged decode-attention kernel on one shape (for ncu captures and quick timing)."""
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=64)
+    ap.add_argument("--heads", type=int, default=28)
+    ap.add_argument("--kv-heads", type=int, default=4)
+    ap.add_argument("--ctx", type=int, default=768)
+    ap.add_argument("--max-ctx", type=int, default=1280)
+    ap.add_argument("--block-size", type=int, default=16)
+    ap.add_argument("--iters", type=int, default=8)
+    ap.add_argument("--graph", action="store_true")
+    a = ap.parse_args(argv)
+    from gcore_b200.ops import _lib
+    from gcore_b200.ops.attention import paged_decode
+    dev = torch.device("cuda")
+    T, hq, hk, D, bs = a.tokens, a.heads, a.kv_heads, 128, a.block_size
+    nblk = T * ((a.max_ctx + bs - 1) // bs)
+    copies = 4
+    kc = [torch.randn(nblk, bs, hk, D, device=dev).bfloat16() for _ in range(copies)]
+    vc = [torch.randn(nblk, bs, hk, D, device=dev).bfloat16() for _ in range(copies)]
+    bt = torch.arange(nblk, device=dev, dtype=torch.int32).view(T, -1)
+    ctx = torch.full((T,), a.ctx, dtype=torch.int32, device=dev)
+    qkv = torch.randn(T, (hq + 2 * hk) * D, device=dev).bfloat16()
+    q = qkv.view(T, hq + 2 * hk, D)[:, :hq]
+    mb = T * a.ctx * 2 * hk * D * 2 / 1e6
+    if a.graph:
+                us = graph_time([lambda i=i: paged_decode(q, kc[i % copies], vc[i % copies], bt, ctx, a.max_ctx)
+                         for i in range(24)])
+    else:
+        ts = []
+        for i in range(a.iters):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            paged_decode(q, kc[i % copies], vc[i % copies], bt, ctx, a.max_ctx)
+            e.record()
+            torch.cuda.synchronize()
+            ts.append(s.elapsed_time(e) * 1e3)
+        us = min(ts[1:]) if len(ts) > 1 else ts[0]
+    _lib.check_device_errors()
+    print(f"paged decode T={T} H={hq}/{hk} ctx={a.ctx} max={a.max_ctx}: {us:.2f} us per call, {mb:.0f} MB of K/V "
+          f"-> {mb / us:.2f} TB/s")
+
+
+def graph_time(fn_list, reps=5):
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for f in fn_list[:2]:
+            f()
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for f in fn_list:
+            f()
+    g.replay()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b) / len(fn_list))
+    return sorted(ts)[len(ts) // 2] * 1e3  # us
+
+
+def cmd_decode_chain(argv=None):
+    """Per-kernel cost of the decode chain under CUDA-graph replay (what a rollout step actually pays per kernel)."""
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=64)
+    ap.add_argument("--tp", type=int, default=1)
+    ap.add_argument("--json", default=None)
+    ap.add_argument("--pdl", type=int, default=0, help="launch the native kernels with programmatic dependent launch")
+    args = ap.parse_args(argv)
+    from gcore_b200.ops import _lib, fused
+    from gcore_b200.ops.attention import kv_append_rope, paged_decode
+    from gcore_b200.ops.gemm import gemm, linear_forward
+    dev = torch.device("cuda")
+    if args.pdl:
+        _lib.kernels().gk_set_pdl(1)
+    T, tp = args.tokens, args.tp
+    H, F, hq, hk, D = 3584, 18944 // tp, 28 // tp, 4 // tp, 128
+    res = {}
+    copies = 12
+    shapes = {"qkv": ((hq + 2 * hk) * D, H), "o": (H, hq * D), "fc1": (2 * F, H), "fc2": (H, F)}
+    for name, (N, K) in shapes.items():
+        ws = [(torch.randn(N, K, device=dev) * 0.02).bfloat16() for _ in range(copies)]
+        x = torch.randn(T, K, device=dev).bfloat16()
+        res[name + "_default"] = round(graph_time([lambda w=ws[i % copies]: linear_forward(x, w) for i in range(24)]), 2)
+        from gcore_b200.ops import gemm as gemm_mod
+        gemm_mod._SKINNY[0] = False
+        res[name + "_general_kernel"] = round(
+            graph_time([lambda w=ws[i % copies]: linear_forward(x, w) for i in range(24)]), 2)
+        gemm_mod._SKINNY[0] = True
+        bn = 32 if T <= 32 else (64 if T <= 64 else 128)
+        for ks in (2, 4):
+            if (K // 64) // ks < 2:
+                continue
+            res[f"{name}_ksplit{ks}"] = round(graph_time(
+                [lambda w=ws[i % copies]: gemm(w, x, transposed=True, bn=bn, ksplit=ks) for i in range(24)]), 2)
+        res[name + "_torch"] = round(graph_time([lambda w=ws[i % copies]: torch.matmul(x, w.t()) for i in range(24)]), 2)
+        res[name + "_MB"] = round(N * K * 2 / 1e6, 1)
+        del ws
+    # small kernels
+    x = torch.randn(T, H, device=dev).bfloat16()
+    r = torch.randn(T, H, device=dev).bfloat16()
+    g = torch.ones(H, device=dev).bfloat16()
+    res["rmsnorm_residual"] = round(graph_time([lambda: fused.rmsnorm(x, g, 1e-6, r) for _ in range(24)]), 2)
+    gu = torch.randn(T, 2 * F, device=dev).bfloat16()
+    res["swiglu"] = round(graph_time([lambda: fused.swiglu(gu) for _ in range(24)]), 2)
+    bs, ctx_len, max_len = 16, 768, 1280
+    nblk = T * (max_len // bs)
+    kc = [torch.randn(nblk, bs, hk, D, device=dev).bfloat16() for _ in range(4)]
+    vc = [torch.randn(nblk, bs, hk, D, device=dev).bfloat16() for _ in range(4)]
+    bt = torch.arange(nblk, device=dev, dtype=torch.int32).view(T, -1)
+    ctx = torch.full((T,), ctx_len, dtype=torch.int32, device=dev)
+    qkv = torch.randn(T, (hq + 2 * hk) * D, device=dev).bfloat16()
+    q = qkv.view(T, hq + 2 * hk, D)[:, :hq]
+    res["paged_decode_ctx768"] = round(graph_time(
+        [lambda i=i: paged_decode(q, kc[i % 4], vc[i % 4], bt, ctx, max_len) for i in range(24)]), 2)
+    res["paged_decode_kv_MB"] = round(T * ctx_len * 2 * hk * D * 2 / 1e6, 1)
+    pos = torch.full((T,), ctx_len - 1, dtype=torch.int32, device=dev)
+    slots = (bt[:, (ctx_len - 1) // bs] * bs + (ctx_len - 1) % bs).to(torch.int32)
+    res["kv_append_rope"] = round(graph_time(
+        [lambda: kv_append_rope(qkv, pos, slots, kc[0], vc[0], hq, hk, D, 1e6) for _ in range(24)]), 2)
+    # one decoder layer as the rollout engine chains it (without the all-reduces)
+    Hd = H
+    wq = (torch.randn((hq + 2 * hk) * D, Hd, device=dev) * 0.02).bfloat16()
+    wo = (torch.randn(Hd, hq * D, device=dev) * 0.02).bfloat16()
+    w1 = (torch.randn(2 * F, Hd, device=dev) * 0.02).bfloat16()
+    w2 = (torch.randn(Hd, F, device=dev) * 0.02).bfloat16()
+    layers = [[t.clone() for t in (wq, wo, w1, w2)] for _ in range(6)]
+
+    def layer(i):
+        a, b, c, d2 = layers[i % 6]
+        h, r2 = fused.rmsnorm(x, g, 1e-6, r)
+        qkv2 = linear_forward(h, a)
+        kv_append_rope(qkv2, pos, slots, kc[i % 4], vc[i % 4], hq, hk, D, 1e6)
+        o = paged_decode(qkv2.view(T, hq + 2 * hk, D)[:, :hq], kc[i % 4], vc[i % 4], bt, ctx, max_len)
+        y = linear_forward(o.view(T, hq * D), b)
+        h2, _ = fused.rmsnorm(y, g, 1e-6, r2)
+        return linear_forward(fused.swiglu(linear_forward(h2, c)), d2)
+
+    res["layer_chain_us"] = round(graph_time([lambda i=i: layer(i) for i in range(12)]), 2)
+    _lib.check_device_errors()
+    print(json.dumps(res, indent=1))
+    if args.json:
+        json.dump(res, open(args.json, "w"), indent=1)
+
+
+def cmd_train_step(argv=None):
+    """Where does a training micro-batch spend its time?  Builds one model shard, runs forward / backward / optimizer on a"""
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="qwen2.5-7b")
+    ap.add_argument("--layers", type=int, default=8)
+    ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--seqlen", type=int, default=1280)
+    ap.add_argument("--recompute", default="full")
+    ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--profile", action="store_true")
+    args = ap.parse_args(argv)
+    from gcore_b200.configs.config import OptimizerConfig, PolicyConfig, TrainingConfig
+    from gcore_b200.engine.train_engine import TrainingEngine
+    from gcore_b200.models.config import get_preset
+    from gcore_b200.ops import _lib
+    torch.cuda.set_device(0)
+    mcfg = get_preset(args.model, num_layers=args.layers)
+    eng = TrainingEngine(PolicyConfig(recompute=args.recompute, without_ref=True), OptimizerConfig(),
+                         TrainingConfig(), model_cfg=mcfg)
+    eng.setup_model_and_get_optimizer(seed=1)
+    nseq = max(args.tokens // args.seqlen, 1)
+    g = torch.Generator().manual_seed(0)
+    samples = [{"tokens": torch.randint(100, 150000, (args.seqlen,), generator=g), "prompt_length": 256}
+               for _ in range(nseq)]
+    from gcore_b200.core.packing import response_mask
+    for s in samples:
+        s["mask"] = response_mask(256, args.seqlen)
+    mb = eng._pack(samples, list(range(nseq)))
+
+    def ev():
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        return e
+
+    def one(record=None):
+        eng.ddp.zero_grad_buffer()
+        t0 = ev()
+        hidden, _ = eng._hidden(eng.model, mb)
+        t1 = ev()
+        lp, _ = eng._logprob_entropy(eng.model, hidden, mb.targets, False)
+        loss = -(lp * mb.loss_mask).sum() / mb.loss_mask.sum()
+        t2 = ev()
+        loss.backward()
+        t3 = ev()
+        eng.ddp.finish_grad_sync()
+        eng.optimizer.step(1e-6)
+        t4 = ev()
+        torch.cuda.synchronize()
+        if record is not None:
+            record.append(dict(fwd_layers_ms=t0.elapsed_time(t1), head_fwd_ms=t1.elapsed_time(t2),
+                               bwd_ms=t2.elapsed_time(t3), opt_ms=t3.elapsed_time(t4)))
+
+    eng.model.train()
+    for _ in range(2):
+        one()
+    rec = []
+    for _ in range(args.iters):
+        one(rec)
+    mean = {k: round(sum(r[k] for r in rec) / len(rec), 2) for k in rec[0]}
+    L, T = args.layers, mb.tokens.numel()
+    per_layer = mcfg.num_parameters(include_embedding=False) / mcfg.num_layers * 2 * T
+    head = 2 * T * mcfg.hidden_size * mcfg.vocab_size
+    mean["fwd_layers_tflops"] = round(per_layer * L / mean["fwd_layers_ms"] / 1e9, 1)
+    mean["head_fwd_tflops"] = round(head / mean["head_fwd_ms"] / 1e9, 1)
+    passes = 3 if args.recompute == "full" else 2
+    mean["bwd_tflops"] = round((per_layer * L * passes + head * 3) / mean["bwd_ms"] / 1e9, 1)
+    print(json.dumps(mean))
+    if args.profile:
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+            one()
+        print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=25, max_name_column_width=60))
+    _lib.check_device_errors()
+
+
+COMMANDS = {"table": cmd_table, "gemm": cmd_gemm, "attn": cmd_attn, "paged": cmd_paged,
+            "decode_chain": cmd_decode_chain, "train_step": cmd_train_step}
+
+
+def main(argv=None):
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if argv and argv[0] in COMMANDS:
+        return COMMANDS[argv[0]](argv[1:])
+    return cmd_table(argv)
 
 
 if __name__ == "__main__":

@@ -14,12 +14,21 @@ def _rand(*shape, scale=1.0, dtype=torch.bfloat16):
 
 
 def _close(a, b, rtol=2e-2, atol=2e-2):
+    """Three criteria: (1) the largest error against the largest reference magnitude, (2) element by element,
+    ``|a - b| <= atol + rtol * |b|`` with at most one element in 10^4 beyond it (a kernel that is wrong on the small
+    elements only passes (1) but not this one), (3) the relative RMS error of the whole tensor."""
     a, b = a.float(), b.float()
     if a.numel() == 0:
         return
-    err = (a - b).abs().max().item()
+    diff = (a - b).abs()
+    err = diff.max().item()
     ref = b.abs().max().item()
     assert err <= atol + rtol * ref, f"max err {err} vs ref magnitude {ref}"
+    bad = (diff > atol + rtol * b.abs()).float().mean().item()
+    assert bad <= 1e-4, f"{bad:.2e} of the elements are outside atol {atol} + rtol {rtol} * |ref|"
+    rms = (diff.norm() / b.norm().clamp_min(1e-20)).item()
+    assert rms <= max(4 * rtol, 2e-2) or diff.norm().item() <= atol * math.sqrt(a.numel()), \
+        f"relative RMS error {rms:.3e}"
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 512), (300, 200, 136), (1000, 3584, 1024), (64, 96, 64)])

@@ -466,7 +466,7 @@ class DynamicSamplingConfig(MappingMixin):
 
 @dataclass
 class TrainingConfig(MappingMixin):
-    training_backend: str = "native"  # native (fused sm_100a kernels) | nccl_eager (library baseline)
+    training_backend: str = "native"  # native (fused sm_100a kernels) | nccl_eager (library baseline) | fsdp2 (ZeRO-3)
     train_gbs: int = 8
     train_mbs: int = 1
     gradient_accumulation_steps: Optional[int] = None
@@ -548,9 +548,9 @@ class TrainingConfig(MappingMixin):
     custom_actors: Dict[str, Any] = field(default_factory=dict)
 
     def __post_init__(self):
-        if self.training_backend in ("mcore", "fsdp2", "mlite"):
-            self.training_backend = "native"
-        if self.training_backend not in ("native", "nccl_eager"):
+        if self.training_backend in ("mcore", "mlite"):
+            self.training_backend = "native"   # the Megatron-style ZeRO-1 / TP / PP / CP / EP engine of this package
+        if self.training_backend not in ("native", "nccl_eager", "fsdp2"):
             raise ConfigError(f"unknown training_backend {self.training_backend}")
         if self.sampling_keep_n is None:
             self.sampling_keep_n = self.sampling_repeat_n

@@ -39,9 +39,21 @@ class _GradShim:
 
 
 class _OptShim:
-    def __init__(self):
+    """The attributes of ``DistributedOptimizer`` that trainers read; ``total_steps`` feeds the learning-rate decay."""
+
+    def __init__(self, engine=None):
         self.last_grad_norm = torch.zeros(())
         self.step_count = 0
+        self._engine = engine
+
+    @property
+    def total_steps(self):
+        return self._engine.total_steps if self._engine is not None else None
+
+    @total_steps.setter
+    def total_steps(self, v):
+        if self._engine is not None:
+            self._engine.total_steps = v
 
 
 class Fsdp2Engine(TrainingEngine):
@@ -87,7 +99,7 @@ class Fsdp2Engine(TrainingEngine):
             self.torch_opt = torch.optim.AdamW(params, lr=cfg.lr, betas=(cfg.adam_beta1, cfg.adam_beta2),
                                                eps=cfg.adam_eps, weight_decay=cfg.weight_decay)
         self.ddp = _GradShim(self.model)
-        self.optimizer = _OptShim()
+        self.optimizer = _OptShim(self)
         return self
 
     def _finish_step(self, lr=None):

@@ -59,8 +59,16 @@ def backend_scope(backend: str):
             os.environ["GCORE_B200_FORCE_EAGER"] = old
 
 
+class CPBatch(list):
+    """Sample indices of a micro-batch that runs on its own context-parallel group (dynamic context parallelism:
+    the group is the block of pool ranks its sequences were scheduled on; ``None`` = this rank alone)."""
+    cp_group = None
+
+
 class TrainingEngine:
-    router_bias_violation = None   # (max, mean) load violation of the last router-bias update, when it is on
+    router_bias_violation = None
+    _dcp = None       # dynamic context parallelism: {"pool": group, "groups": {(start, size): group}}
+    _cur_cpg = None   # context-parallel group of the micro-batch packed last (dynamic context parallelism)   # (max, mean) load violation of the last router-bias update, when it is on
 
     def __init__(self, policy_cfg, optimizer_cfg, training_cfg, ppo_cfg=None, model_cfg: Optional[ModelConfig] = None,
                  role: str = "policy", value_head: bool = False, total_steps: Optional[int] = None,
@@ -145,12 +153,55 @@ class TrainingEngine:
         self._apply_freeze()
         self._apply_precision()
         self._maybe_enable_fused_tp()
+        self._setup_dynamic_cp()
         if not self.policy_cfg.without_optim:
             oc = self.opt_cfg
             self.ddp = DistributedDataParallel(self.model, oc.grad_reduce_in_fp32, oc.bucket_size,
                                                oc.use_distributed_optimizer, oc.overlap_grad_reduce)
             self.optimizer = DistributedOptimizer(self.ddp, oc, self.total_steps)
         return self.model, self.optimizer
+
+    def _setup_dynamic_cp(self):
+        """``dist_config.dynamic_context_parallel``: the data-parallel ranks form a pool; every step each sequence is
+        given a block of 1, 2, 4, ... pool ranks by its length (``max_seqlen_per_dp_cp_rank`` tokens per rank), the
+        samples travel to their blocks in one byte all-to-all, and results travel back
+        (gpatch_v4/extended_model/llm.py:1056-1430, utils/dynamic_cp_utils.py:1109,1471,1898).  Collective: builds one
+        process group per aligned power-of-two block of the pool."""
+        d = self.policy_cfg.dist_config
+        if not d.dynamic_context_parallel or not dist.is_initialized():
+            return
+        pool = ps.get_data_parallel_group(with_context_parallel=True)
+        if pool is None or dist.get_world_size(pool) <= 1:
+            return
+        assert ps.get_context_parallel_world_size() == 1, \
+            "dynamic context parallelism sizes its own groups: set context_parallel_size to 1"
+        assert ps.get_pipeline_model_parallel_world_size() == 1 and not self.model_cfg.is_moe, \
+            "dynamic context parallelism is built for dense models without pipeline stages"
+        from ..parallel.dynamic_cp import build_block_groups
+        self._dcp = {"pool": pool, "groups": build_block_groups(pool)}
+
+    def _dynamic_cp_plan(self, samples, forward_only: bool):
+        """-> (this rank's share of the rerouted samples, micro-batches over them).  Micro-batches are ordered by
+        (micro-step, block size descending): blocks are aligned power-of-two ranges, so every rank meets the groups it
+        belongs to in the same order."""
+        from ..parallel import dynamic_cp as D
+        d = self.policy_cfg.dist_config
+        pool = self._dcp["pool"]
+        budget = (d.max_seqlen_per_dp_cp_rank_fwd_only if forward_only else None) or d.max_seqlen_per_dp_cp_rank
+        lens, offsets = D.gather_lengths(samples, pool)
+        plan = D.schedule(lens, dist.get_world_size(pool), budget, d.min_dynamic_context_parallel_size)
+        steps = D.reroute_samples(list(samples), plan, offsets, pool)
+        flat, batches = [], []
+        for st in steps:
+            by_block: Dict[tuple, list] = {}
+            for smp in st:
+                by_block.setdefault(tuple(smp["_block"]), []).append(smp)
+            for blk in sorted(by_block, key=lambda b: (-b[1], b[0])):
+                b = CPBatch(range(len(flat), len(flat) + len(by_block[blk])))
+                b.cp_group = self._dcp["groups"][blk] if blk[1] > 1 else None
+                flat += by_block[blk]
+                batches.append(b)
+        return flat, batches
 
     def _apply_precision(self):
         """``policy.fp8`` / ``fp8_qat`` / ``fp4_qat``: the decoder's projections whose contraction length is a multiple
@@ -215,7 +266,7 @@ class TrainingEngine:
 
     def _gather_cp(self, x: torch.Tensor) -> torch.Tensor:
         """Token-axis tensors of a context-parallel shard -> the whole packed micro-batch (forward-only results)."""
-        g = self._cp_group()
+        g = self._cur_cpg if self._dcp is not None else self._cp_group()
         if g is None:
             return x
         parts = [torch.empty_like(x) for _ in range(dist.get_world_size(g))]
@@ -312,19 +363,23 @@ class TrainingEngine:
         return ps.get_tensor_model_parallel_world_size() if (self.model is not None and self.model.sequence_parallel) \
             else 1
 
-    def _pad_multiple(self) -> int:
+    def _pad_multiple(self, cpg="static") -> int:
         pad = max(self._tp_pad(), 1)
         if self.device.type == "cuda":
             from ..models import gpt as gpt_mod
             pad = pad * (128 if gpt_mod.FUSED_TP["ftp"] is not None else 8) if pad > 1 else 8
-        cpg = self._cp_group()
+        if isinstance(cpg, str):
+            cpg = self._cp_group()
         if cpg is not None:
             pad *= dist.get_world_size(cpg)
         return pad
 
     def _pack(self, samples, idx, keys=()):
-        pad = self._pad_multiple()
-        cpg = self._cp_group()
+        cpg = idx.cp_group if isinstance(idx, CPBatch) else self._cp_group()
+        pad = self._pad_multiple(cpg)
+        if self._dcp is not None:
+            self._cur_cpg = cpg
+            PL.set_context_parallel_group(cpg)
         mb = pack_samples(samples, idx, keys, pad_to_multiple=pad, pin=self.device.type == "cuda")
         if isinstance(idx, FillerBatch):
             mb.loss_mask.zero_()
@@ -343,7 +398,15 @@ class TrainingEngine:
         mbs = pc.forward_only_mbs if forward_only else self.train_cfg.train_mbs
         if forward_only and getattr(pc, "dynamic_mbs_target_seqlen_fwd_only", None):
             max_tok = pc.dynamic_mbs_target_seqlen_fwd_only
-        batches = make_microbatches(lens, mbs=mbs, max_tokens=max_tok)
+        smart = pc.smart_pad_infer if forward_only else pc.smart_pad_train
+        if smart and not max_tok:
+            # samples of similar length share a micro-batch (gpatch_v4/core/smart_pad_helper.py:300-1044): with a fixed
+            # number of samples per micro-batch this evens out the work of a micro-batch's sequences and, under
+            # pipeline parallelism, the per-micro-batch activation shapes
+            from ..core.dp_balancing import smart_pad_buckets
+            batches, _ = smart_pad_buckets(lens, mbs or 1)
+        else:
+            batches = make_microbatches(lens, mbs=mbs, max_tokens=max_tok)
         return self._equalize_microbatch_count(batches, lens)
 
     def _equalize_microbatch_count(self, batches, lens):
@@ -383,8 +446,12 @@ class TrainingEngine:
         was_training = model.training
         model.eval()
         key = out_key or ("ref_logprobs" if use_ref else "logprobs")
+        originals = None
+        if self._dcp is not None:
+            originals = samples
+            samples, dcp_batches = self._dynamic_cp_plan(samples, forward_only=True)
         with backend_scope(self.backend):
-            batches = self._microbatches(samples, forward_only=True)
+            batches = dcp_batches if originals is not None else self._microbatches(samples, forward_only=True)
 
             def step(mb, hidden, aux):
                 lp, ent = self._logprob_entropy(model, hidden, mb.targets, with_entropy, mb.loss_mask)
@@ -396,7 +463,7 @@ class TrainingEngine:
                     continue
                 lens = [len(samples[i]["tokens"]) for i in idx]
                 total = sum(lens)
-                pad_mult = self._pad_multiple()
+                pad_mult = self._pad_multiple(idx.cp_group if isinstance(idx, CPBatch) else "static")
                 total_padded = (total + pad_mult - 1) // pad_mult * pad_mult
                 lp, ent = results[bi] if results else (None, None)
                 lp = self._from_last_stage(lp, (total_padded,), torch.float32)
@@ -412,6 +479,12 @@ class TrainingEngine:
                     if ent_c is not None:
                         samples[i]["prev_per_token_entropies"] = ent_c[o:o + ln].clone()
                     o += ln
+        if originals is not None:
+            from ..parallel.dynamic_cp import reverse_reroute
+            back = reverse_reroute(samples, len(originals), self._dcp["pool"], keys=(key, "prev_per_token_entropies"))
+            for smp, res in zip(originals, back):
+                smp.update(res)
+            samples = originals
         if was_training:
             model.train()
         return samples
@@ -513,7 +586,10 @@ class TrainingEngine:
         denom = self._global_counts(samples, per_token)
         acc = {"lm_loss": torch.zeros(2, device=self.device)}
         with backend_scope(self.backend):
-            batches = self._microbatches(samples)
+            if self._dcp is not None:
+                samples, batches = self._dynamic_cp_plan(samples, forward_only=False)
+            else:
+                batches = self._microbatches(samples)
             aux_scale = self._aux_scale(len(batches))
 
             def step(mb, hidden, aux):
@@ -624,7 +700,10 @@ class TrainingEngine:
                     loss = loss + aux * aux_scale
                 return loss
 
-            batches = self._microbatches(samples)
+            if self._dcp is not None:
+                samples, batches = self._dynamic_cp_plan(samples, forward_only=False)
+            else:
+                batches = self._microbatches(samples)
             aux_scale = self._aux_scale(len(batches))
             self._for_each_microbatch(self.model, samples, batches, keys, step)
             lr, gn = self._finish_step()

@@ -6,7 +6,7 @@ import torch
 
 from ..configs.config import DpoConfig
 from ..data.datasets import IndexedJsonlDataset
-from ..engine.train_engine import TrainingEngine
+from ..engine import get_training_engine
 from ..trainer.preference_trainers import dpo_step
 from ..utils.logging_utils import get_logger
 from .common import finalize, init_runtime, load
@@ -31,7 +31,7 @@ def pair_batches(cfg, vocab: int, seed: int = 0):
 def main(argv=None):
     cfg = load(DpoConfig, argv)
     init_runtime(cfg)
-    eng = TrainingEngine(cfg.policy, cfg.optimizer, cfg.training, cfg.ppo)
+    eng = get_training_engine(cfg.policy, cfg.optimizer, cfg.training, cfg.ppo)
     eng.setup_model_and_get_optimizer(seed=cfg.training.seed, with_ref=not cfg.reference_free)
     log = get_logger("dpo")
     total = cfg.training.exit_step or cfg.training.total_ppo_step or 0

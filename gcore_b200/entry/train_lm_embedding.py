@@ -9,7 +9,7 @@ import torch
 
 from ..configs.config import FinetuneConfig
 from ..data.datasets import IndexedJsonlDataset
-from ..engine.train_engine import TrainingEngine
+from ..engine import get_training_engine
 from ..trainer.preference_trainers import embedding_step
 from ..utils.logging_utils import get_logger
 from .common import finalize, init_runtime, load
@@ -35,7 +35,7 @@ def main(argv=None):
     cfg = load(FinetuneConfig, argv)
     init_runtime(cfg)
     cfg.policy.without_ref = True
-    eng = TrainingEngine(cfg.policy, cfg.optimizer, cfg.training, None)
+    eng = get_training_engine(cfg.policy, cfg.optimizer, cfg.training, None)
     eng.setup_model_and_get_optimizer(seed=cfg.training.seed)
     opt = dict((cfg.task or {}).get("embedding", {}) or {})
     log = get_logger("embedding")

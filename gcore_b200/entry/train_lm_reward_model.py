@@ -2,7 +2,7 @@
 import sys
 
 from ..configs.config import RewardTrainConfig
-from ..engine.train_engine import TrainingEngine
+from ..engine import get_training_engine
 from ..trainer.preference_trainers import rm_step
 from ..utils.logging_utils import get_logger
 from .common import finalize, init_runtime, load
@@ -12,7 +12,7 @@ from .train_lm_dpo import pair_batches
 def main(argv=None):
     cfg = load(RewardTrainConfig, argv)
     init_runtime(cfg)
-    eng = TrainingEngine(cfg.policy, cfg.optimizer, cfg.training, cfg.ppo, value_head=True)
+    eng = get_training_engine(cfg.policy, cfg.optimizer, cfg.training, cfg.ppo, value_head=True)
     eng.setup_model_and_get_optimizer(seed=cfg.training.seed, with_ref=False)
     log = get_logger("rm")
     total = cfg.training.exit_step or cfg.training.total_ppo_step or 0

@@ -14,7 +14,7 @@ import torch
 
 from ..configs.config import RlConfig
 from ..data.datasets import IndexedJsonlDataset
-from ..engine.train_engine import TrainingEngine
+from ..engine import get_training_engine
 from ..trainer.grpo_trainer import GrpoTrainer
 from ..utils.logging_utils import get_logger
 from .common import finalize, init_runtime, load
@@ -59,7 +59,7 @@ def main(argv=None):
     history = []
     if mode == "sft":
         cfg.policy.without_ref = True
-        eng = TrainingEngine(cfg.policy, cfg.optimizer, cfg.training, None)
+        eng = get_training_engine(cfg.policy, cfg.optimizer, cfg.training, None)
         eng.setup_model_and_get_optimizer(seed=cfg.training.seed)
         assert hasattr(eng.model, "vision"), "policy.vision_config is empty: not a vision-language policy"
         rows = vlm_rows(cfg, eng.model.vc, eng.model.image_token_id, eng.model_cfg.vocab_size,

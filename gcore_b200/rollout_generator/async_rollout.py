@@ -73,23 +73,56 @@ class RolloutController:
         g.finished_at = time.time()
         return g
 
+    def _run_groups(self, groups: List[RolloutGroup], sampler) -> List[RolloutGroup]:
+        """All groups handed to one sampler in this round, as ONE engine call: a continuous-batching engine decodes
+        ``len(groups) * repeat_n`` sequences per step instead of ``repeat_n``."""
+        outs = sampler.generate_groups([g.prompt for g in groups], self.repeat_n, self.params)
+        assert len(outs) == len(groups) * self.repeat_n, "a batched sampler returns repeat_n samples per prompt, in order"
+        now = time.time()
+        for k, g in enumerate(groups):
+            samples = []
+            for o in outs[k * self.repeat_n:(k + 1) * self.repeat_n]:
+                s = dict(o) if isinstance(o, dict) else {"tokens": o}
+                s.update(prompt_id=g.prompt_id, group_id=g.prompt_id, weight_version=g.weight_version,
+                         prompt_length=len(g.prompt))
+                samples.append(s)
+            g.samples = self.score_fn(samples)
+            g.finished_at = now
+        return groups
+
     def fire(self):
-        """Tops the in-flight set up to ``max_inflight`` groups."""
+        """Tops the in-flight set up to ``max_inflight`` groups.  Samplers that offer ``generate_groups`` receive all
+        of their new groups in one call; the others one call per group."""
         with self._lock:
+            new: Dict[int, List[RolloutGroup]] = {}
             while len(self._inflight) + len(self._done) < self.max_inflight:
                 g = RolloutGroup(self._next_id, self._take_prompt(), self.version)
-                sampler = self.samplers[self._next_id % len(self.samplers)]
-                self._inflight[g.prompt_id] = self._pool.submit(self._run_group, g, sampler)
+                si = self._next_id % len(self.samplers)
+                sampler = self.samplers[si]
+                if hasattr(sampler, "generate_groups"):
+                    new.setdefault(si, []).append(g)
+                    self._inflight[g.prompt_id] = None  # filled below, once the sampler's round is complete
+                else:
+                    self._inflight[g.prompt_id] = self._pool.submit(self._run_group, g, sampler)
                 self._next_id += 1
                 self.stats["fired"] += 1
+            for si, groups in new.items():
+                fut = self._pool.submit(self._run_groups, groups, self.samplers[si])
+                for g in groups:
+                    self._inflight[g.prompt_id] = fut
+                self.stats["batched_calls"] = self.stats.get("batched_calls", 0) + 1
 
     # ---- collect
     def _harvest(self):
         with self._lock:
-            for pid in [p for p, f in self._inflight.items() if f.done()]:
-                g = self._inflight.pop(pid).result()
-                self._done.append(g)
-                self.stats["collected"] += 1
+            for pid in [p for p, f in self._inflight.items() if f is not None and f.done()]:
+                if pid not in self._inflight:
+                    continue  # finished together with an earlier group of the same batched call
+                res = self._inflight.pop(pid).result()
+                for g in (res if isinstance(res, list) else [res]):
+                    self._inflight.pop(g.prompt_id, None)
+                    self._done.append(g)
+                    self.stats["collected"] += 1
 
     def _fresh(self) -> List[RolloutGroup]:
         keep, drop = [], 0

@@ -17,6 +17,7 @@ from ..checkpoint.torch_dist import load_checkpoint, read_latest_step, save_chec
 from ..configs.base import import_from_path
 from ..core import parallel_state as ps
 from ..data.datasets import default_dataset_fn
+from ..engine import get_training_engine
 from ..engine.train_engine import TrainingEngine
 from ..orches.failure import FaultInjector, Heartbeat
 from ..utils.flops_counter import mfu, train_flops
@@ -29,7 +30,7 @@ class FinetuneTrainer:
     def __init__(self, config, model_cfg=None, tokenizer=None, dataset_fn=None):
         self.cfg, self.tokenizer, self.dataset_fn = config, tokenizer, dataset_fn
         t = config.training
-        self.engine = TrainingEngine(config.policy, config.optimizer, t, None, model_cfg=model_cfg,
+        self.engine = get_training_engine(config.policy, config.optimizer, t, None, model_cfg=model_cfg,
                                      total_steps=t.total_training_step)
         self.step = 0
         self.log = get_logger("finetune")
@@ -52,8 +53,12 @@ class FinetuneTrainer:
             resume_from = ck.save_ckpt_path
         meta = None
         if resume_from and read_latest_step(resume_from) is not None:
-            self.step = load_checkpoint(self.engine, resume_from, load_optim=not ck.no_load_optim,
-                                        load_rng=not ck.no_load_rng)
+            if hasattr(self.engine, "torch_opt"):
+                self.step = self.engine.load_checkpoint(resume_from)
+                self.engine.loaded_extra_state = {}
+            else:
+                self.step = load_checkpoint(self.engine, resume_from, load_optim=not ck.no_load_optim,
+                                            load_rng=not ck.no_load_rng)
             meta = {"consumed_batches": self.engine.loaded_extra_state.get("consumed_batches", self.step),
                     "resume_step": self.step}
             self.log.info(f"resumed from {resume_from} at step {self.step}")
@@ -108,6 +113,11 @@ class FinetuneTrainer:
         self.injector.at_step(self.step)
         self.timers.start("train_step")
         samples = self._to_samples(self._next_batch())
+        if self.cfg.policy.balance_dp_seqlen and ps.get_data_parallel_world_size() > 1:
+            # the loss is normalised by the global token count, so samples may change ranks freely
+            # (gpatch_v4/actor/finetune_actor.py "[DP balance]", core/dp_balancing.py:369)
+            from ..core.dp_balancing import rebalance_across_dp_ranks
+            samples, _ = rebalance_across_dp_ranks(samples, ps.get_data_parallel_group())
         m = self.engine.finetune_step(samples)
         dt = self.timers.stop("train_step")
         self.step += 1
@@ -131,6 +141,8 @@ class FinetuneTrainer:
         ck = self.cfg.checkpoint
         if not ck.save_ckpt_path:
             return None
+        if hasattr(self.engine, "torch_opt"):   # ZeRO-3 engine: torch.distributed.checkpoint of the sharded state
+            return self.engine.save_checkpoint(ck.save_ckpt_path, self.step)
         return save_checkpoint(self.engine, ck.save_ckpt_path, self.step, extra_state={"consumed_batches": self.step},
                                save_optim=not ck.no_save_optim, save_total_limit=ck.save_total_limit,
                                save_retain_interval=ck.save_retain_interval, async_save=ck.async_save)

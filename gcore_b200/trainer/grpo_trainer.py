@@ -19,6 +19,7 @@ from ..configs.config import RlConfig
 from ..core import parallel_state as ps
 from ..core.advantage import compute_advantages
 from ..core.packing import response_mask
+from ..engine import get_training_engine
 from ..engine.train_engine import TrainingEngine
 from ..rollout.engine import InferEngine, RolloutWeights, SamplingParams
 from ..utils.timers import Timers
@@ -45,7 +46,7 @@ class GrpoTrainer:
         self.reward_fn = reward_fn or self._load_reward_fn() or synthetic_reward
         self.prompt_source = prompt_source
         t = config.training
-        self.policy = TrainingEngine(config.policy, config.optimizer, t, config.ppo, model_cfg=model_cfg,
+        self.policy = get_training_engine(config.policy, config.optimizer, t, config.ppo, model_cfg=model_cfg,
                                      total_steps=t.total_ppo_step, vision_cfg=vision_cfg,
                                      image_token_id=image_token_id)
         self.critic: Optional[TrainingEngine] = None
@@ -78,14 +79,14 @@ class GrpoTrainer:
         ie = cfg.sampler.infer_engine_configs[0]
         self.policy.temperature = ie.temperature
         if cfg.require_critic_model():
-            self.critic = TrainingEngine(cfg.critic, cfg.critic.optimizer, cfg.training, cfg.ppo,
+            self.critic = get_training_engine(cfg.critic, cfg.critic.optimizer, cfg.training, cfg.ppo,
                                          model_cfg=self.policy.model_cfg, role="critic", value_head=True)
             self.critic.setup_model_and_get_optimizer(with_ref=False)
         if cfg.teacher is not None:
             # on-policy distillation: a frozen teacher scores the student's rollouts (forward only, no optimizer;
             # gpatch_v4/trainer on-policy distill trainer + teacher client)
             cfg.teacher.without_optim = True
-            self.teacher = TrainingEngine(cfg.teacher, cfg.optimizer, cfg.training, cfg.ppo,
+            self.teacher = get_training_engine(cfg.teacher, cfg.optimizer, cfg.training, cfg.ppo,
                                           model_cfg=self.teacher_model_cfg or self.policy.model_cfg, role="teacher")
             self.teacher.setup_model_and_get_optimizer(with_ref=False, seed=cfg.training.seed + 7919)
             if cfg.teacher.hf_model_path:
@@ -225,6 +226,17 @@ class GrpoTrainer:
         tm.stop("generate_ppo_data")
         tm.start("train_step")
         metrics: Dict[str, float] = {k: float(v) for k, v in post_metrics.items()}
+        if cfg.policy.balance_dp_seqlen and ps.get_data_parallel_world_size() > 1:
+            # even out the token counts of the data-parallel ranks before the update: losses are normalised by global
+            # counts, so which rank trains which sample does not change the gradient
+            # (gpatch_v4/actor/grpo_train_actor.py:1344-1353, core/dp_balancing.py:369)
+            from ..core.dp_balancing import rebalance_across_dp_ranks
+            before = float(sum(s["sequence_length"] for s in samples))
+            samples, _ = rebalance_across_dp_ranks(samples, ps.get_data_parallel_group())
+            for s in samples:
+                s.pop("_origin", None)
+            metrics["rollout-metrics/dp_balance_tokens_before"] = before
+            metrics["rollout-metrics/dp_balance_tokens_after"] = float(sum(s["sequence_length"] for s in samples))
         self.policy.allocate_grad_buffers()
         per_update = max(t.train_gbs // max(ps.get_data_parallel_world_size(), 1), 1)
         for _ in range(t.ppo_max_epochs_2):

@@ -16,13 +16,17 @@ from .grpo_trainer import GrpoTrainer
 
 
 class _LocalSampler:
-    """Adapts ``GrpoTrainer.rollout`` (one prompt group at a time) to the controller's sampler interface."""
+    """Adapts ``GrpoTrainer.rollout`` to the controller's sampler interface.  The controller hands over every prompt
+    group it fires in a round at once, so the colocated engine decodes all of them in one continuous batch."""
 
     def __init__(self, trainer: GrpoTrainer):
         self.tr = trainer
 
+    def generate_groups(self, prompts, repeat_n, params=None):
+        return self.tr.rollout(list(prompts), n=repeat_n)
+
     def generate(self, prompts, params=None):
-        return self.tr.rollout([prompts[0]])  # one prompt group: sampling_repeat_n samples
+        return self.tr.rollout([prompts[0]], n=len(prompts))
 
 
 class GrpoSingleCtrlTrainer:

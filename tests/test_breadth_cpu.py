@@ -757,3 +757,33 @@ def test_loss_free_load_balancing_moves_the_router_bias_towards_even_load():
     update_router_bias(e.model, 0.1, use_abs=False)
     want = before + 0.1 * torch.log((c.mean() + 1) / (c + 1))
     assert torch.allclose(routers[0].expert_bias, want, atol=1e-6)
+
+
+def test_async_controller_hands_a_batched_sampler_all_groups_of_a_round_at_once():
+    """A sampler with ``generate_groups`` (the colocated engine) gets every prompt group fired in a round in one
+    call, so the engine decodes groups x samples sequences per step instead of one group at a time."""
+    from gcore_b200.rollout_generator.async_rollout import RolloutController
+    calls = []
+
+    class Batched:
+        def generate_groups(self, prompts, n, params=None):
+            calls.append(len(prompts))
+            return [{"tokens": list(p) + [j]} for p in prompts for j in range(n)]
+
+    def prompts():
+        k = 0
+        while True:
+            yield [[k, k + 1], [k + 2, k + 3]]
+            k += 4
+
+    def score(samples):
+        for s in samples:
+            s["rewards"] = float(s["tokens"][-1])
+        return samples
+
+    c = RolloutController(prompts(), [Batched()], score, repeat_n=3, groups_per_batch=4, max_staleness=0)
+    batch = c.collect(timeout_s=20)
+    assert calls[0] == 4 and len(batch) == 12 and c.stats["batched_calls"] >= 1
+    assert [s["group_id"] for s in batch] == [0] * 3 + [1] * 3 + [2] * 3 + [3] * 3
+    assert [s["tokens"][-1] for s in batch[:3]] == [0, 1, 2]
+    c.shutdown()

@@ -17,7 +17,7 @@ from test_parallel_cpu import _spawn  # noqa: E402
 
 def test_ep_ranks_run_equal_microbatch_counts_under_a_token_budget(tmp_path):
     out = tmp_path / "dyn.json"
-    _spawn("ep_dynmbs", out, port="29561")
+    _spawn("ep_dynmbs", out, port="29571")
     got = json.load(open(out))
     for step in range(2):
         assert got["counts"][0][step] == got["counts"][1][step] > 1, got["counts"]
@@ -64,3 +64,29 @@ def test_tp2_filtered_sampling_equals_single_rank(tmp_path):
         assert [r.out_tokens for r in reqs] == got["out"][name]["tokens"], name
         for a, b in zip(reqs, got["out"][name]["logprobs"]):
             assert max(abs(x - y) for x, y in zip(a.out_logprobs, b)) < 1e-4, name
+
+
+def test_dynamic_context_parallel_step_equals_single_process(tmp_path):
+    import parallel_worker as pw
+    from gcore_b200.models.config import get_preset
+    out = tmp_path / "dcp.json"
+    _spawn("dyncp", out, port="29569")
+    got = json.load(open(out))
+    e = pw.engine(get_preset("tiny_llama", dtype="float32", qkv_bias=True), 1)
+    ref = [e.finetune_step(pw.samples(8, 210 + s, L=72))["lm_loss"] for s in range(3)]
+    for a, b in zip(ref, got["losses"]):
+        assert abs(a - b) < 5e-4, (ref, got["losses"])
+    assert abs(float(e.optimizer.last_grad_norm) - got["grad_norm"]) < 5e-3
+    full = e.compute_log_probs(pw.samples(6, 219, L=72))
+    for r in range(2):
+        for mine, theirs in zip(full[r::2], got["logprobs"][r]):
+            assert torch.allclose(mine["logprobs"], torch.tensor(theirs), atol=2e-4)
+
+
+def test_grpo_update_runs_on_balanced_token_counts(tmp_path):
+    out = tmp_path / "bal.json"
+    _spawn("dp_grpo_balance", out, port="29573")
+    r0, r1 = json.load(open(out))["ranks"]
+    assert abs(r0["before"] - r1["before"]) > abs(r0["after"] - r1["after"]), (r0, r1)
+    assert r0["before"] + r1["before"] == r0["after"] + r1["after"]
+    assert r0["grad_norm"] == r1["grad_norm"] and r0["grad_norm"] > 0

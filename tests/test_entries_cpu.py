@@ -345,3 +345,25 @@ def test_finetune_length_from_epochs_and_manual_gc(tmp_path):
     assert len(hist) == 8 and state == [False] * 8 and gc.isenabled()
     lrs = [m["lr"] for m in hist]
     assert lrs[0] > lrs[-1] and lrs[-1] <= 0.3 * lrs[0]
+
+
+def test_fsdp2_backend_is_selected_from_config_and_resumes(tmp_path):
+    """``training.training_backend=fsdp2`` builds the ZeRO-3 engine, trains through the ordinary SFT trainer, saves a
+    torch.distributed.checkpoint tree at the save interval and resumes from it."""
+    from gcore_b200.configs.base import load_config
+    from gcore_b200.configs.config import FinetuneConfig
+    from gcore_b200.engine.fsdp2_engine import Fsdp2Engine
+    from gcore_b200.trainer.finetune_trainer import FinetuneTrainer
+    y = _sft_yaml(tmp_path)
+    over = ["training.training_backend=fsdp2", "training.save_interval=3",
+            f"checkpoint.save_ckpt_path={tmp_path / 'ck'}"]
+    tr = FinetuneTrainer(load_config(FinetuneConfig, y, over)).setup()
+    assert isinstance(tr.engine, Fsdp2Engine)
+    hist = tr.train_loop()
+    assert len(hist) == 3 and hist[-1]["lm_loss"] < hist[0]["lm_loss"] + 0.5
+    tr2 = FinetuneTrainer(load_config(FinetuneConfig, y, over + ["training.auto_load_from_save_ckpt=true",
+                                                                  "training.exit_step=4"])).setup()
+    assert tr2.step == 3
+    for (n, p), (_, q) in zip(tr.engine.model.named_parameters(), tr2.engine.model.named_parameters()):
+        assert torch.equal(p, q), n
+    assert len(tr2.train_loop()) == 1

@@ -1,5 +1,5 @@
 """gloo worker for the parallelism parity tests: mode = tp | ep | ep_rollout | ep_grpo | cp | pp | vpp | fsdp |
-ep_dynmbs | aux_dp | tp_topk | nodistopt."""
+ep_dynmbs | aux_dp | tp_topk | nodistopt | dyncp | dp_grpo_balance."""
 import json
 import os
 import sys
@@ -204,6 +204,47 @@ def main():
             b["loss_mask"] = torch.zeros_like(b["loss_mask"])
         m = e.finetune_step(batch[rank * 4:(rank + 1) * 4])
         res = {"grad_norm": m["grad_norm"]}
+    elif mode == "dyncp":
+        # data-parallel pool of two ranks; sequences longer than the per-rank budget run on both ranks (CP 2), the
+        # others on one: the step must equal a single process training on the union of the two ranks' samples
+        ps.initialize_model_parallel(tp=1)
+        mcfg = get_preset("tiny_llama", dtype="float32", qkv_bias=True)
+        pc = PolicyConfig(recompute="none", without_ref=True)
+        pc.dist_config.dynamic_context_parallel = True
+        pc.dist_config.max_seqlen_per_dp_cp_rank = 40
+        oc = OptimizerConfig(lr=1e-3, lr_decay_style="constant", weight_decay=0.0, max_grad_norm=1.0)
+        e = TrainingEngine(pc, oc, TrainingConfig(train_mbs=2, train_gbs=8), model_cfg=mcfg)
+        e.setup_model_and_get_optimizer(seed=11)
+        assert e._dcp is not None
+        losses = [e.finetune_step(samples(8, 210 + s, L=72)[rank::world])["lm_loss"] for s in range(3)]
+        mine = samples(6, 219, L=72)[rank::world]
+        lp = e.compute_log_probs(mine)
+        allp = [None, None]
+        dist.all_gather_object(allp, [x["logprobs"].tolist() for x in lp])
+        res = {"losses": losses, "grad_norm": float(e.optimizer.last_grad_norm), "logprobs": allp}
+    elif mode == "dp_grpo_balance":
+        # GRPO on two data-parallel ranks whose responses differ in length (different stop tokens): with
+        # policy.balance_dp_seqlen the update runs on evened-out token counts; smart-pad groups similar lengths
+        sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+        from test_grpo_cpu import make_cfg, reward_has_small_token
+        from gcore_b200.trainer.grpo_trainer import GrpoTrainer
+        ps.initialize_model_parallel(tp=1)
+        cfg = make_cfg()
+        cfg.policy.balance_dp_seqlen = True
+        cfg.policy.smart_pad_train = True
+        cfg.training.rollout_gbs, cfg.training.train_gbs = 8, 32   # 4 prompts x 4 samples per rank
+        cfg.sampler.infer_engine_configs[0].generate_max_tokens = 4 if rank == 0 else 24
+        torch.manual_seed(0)
+        tr = GrpoTrainer(cfg, model_cfg=get_preset("tiny_llama", dtype="float32", qkv_bias=True),
+                         reward_fn=reward_has_small_token).setup()
+        g = torch.Generator().manual_seed(5 + rank)
+        prompts = [torch.randint(3, 1024, (6 + i,), generator=g).tolist() for i in range(4)]
+        m = tr.step(prompts)
+        res = {"before": m["rollout-metrics/dp_balance_tokens_before"],
+               "after": m["rollout-metrics/dp_balance_tokens_after"], "grad_norm": m["policy/grad_norm"]}
+        allres = [None, None]
+        dist.all_gather_object(allres, res)
+        res = {"ranks": allres}
     elif mode == "nodistopt":
         ps.initialize_model_parallel(tp=1)
         mcfg = get_preset("tiny_llama", dtype="float32", qkv_bias=True)

@@ -231,8 +231,15 @@ def main():
     if world > 1:
         ps.initialize_model_parallel(tp=tp)
     if args.impl == "nccl_eager":
+        # library build of the same step: cuBLAS GEMMs, the library's fused attention, PyTorch elementwise ops, NCCL
+        # collectives at the call sites of the fused kernels, a CUDA-graph decode loop over library ops, and a weight
+        # resync that copies every tensor through a staging bucket into a separate rollout copy (freed after rollout)
         cfg.training.training_backend = "nccl_eager"
+        cfg.policy.share_rollout_weights = False
+        cfg.policy.release_rollout_weights = True
         os.environ["GCORE_B200_FORCE_EAGER"] = "1"
+        for k in ("GCORE_FUSED_TP", "GCORE_FUSED_DP", "GCORE_FUSED_EP", "GCORE_FUSED_CP", "GCORE_PEER_ALLREDUCE"):
+            os.environ[k] = "0"
     over = {"num_layers": args.layers} if args.layers else {}
     mcfg = get_preset(args.model, **over)
     trainer = GrpoTrainer(cfg, model_cfg=mcfg, reward_fn=synthetic_reward).setup()
@@ -305,14 +312,17 @@ def main():
         out = {
             "metric": "grpo_rollout_plus_train_tokens_per_s", "value": round(value, 1), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_s / args.steps * 1e3, 1),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": vs_baseline(args, world, value), "dtype": "bf16", "data": "synthetic",
             "impl": args.impl,
             "config": {"model": args.model + (f"-{args.layers}layers-DEBUG" if args.layers else ""),
                        "global_batch": int(cfg.training.rollout_gbs * args.samples),
                        "seq_len": args.prompt_len + args.max_response,
                        "parallelism": f"tp{tp}dp{dp}", "prompts": int(cfg.training.rollout_gbs),
                        "samples_per_prompt": args.samples, "weights": "random-init",
-                       "resync": "zero-copy shared parameter storage (trainer and rollout engine, same TP layout)",
+                       "resync": ("zero-copy shared parameter storage (trainer and rollout engine, same TP layout)"
+                                  if cfg.policy.share_rollout_weights else
+                                  "bucketed copy into a separate rollout copy (rebuilt every step, freed after rollout)"),
                        "l2": "inputs (15 GB of weights per pass) are larger than L2", "recompute": args.recompute, "recompute_layers": args.recompute_layers,
                        "micro_batch_tokens": args.mb_tokens},
             "clocks": clocks,
@@ -330,6 +340,20 @@ def main():
         dist.barrier()
         dist.destroy_process_group()
     return 0
+
+
+def vs_baseline(args, world, value):
+    """value / the library (``nccl_eager``) build's measured value of the same config at the same GPU count, from the
+    committed ``baseline/measured_baselines.json``; None when that row has not been measured.  (The reference
+    publishes no number for this metric, and cannot run here: the library build is its stand-in.)"""
+    if args.impl != "native" or args.layers:
+        return None
+    try:
+        rows = json.load(open(os.path.join(ROOT, "baseline", "measured_baselines.json")))["nccl_eager"]
+        base = rows[args.model][str(world)]["value"]
+        return round(value / base, 3) if base else None
+    except Exception:  # noqa: BLE001
+        return None
 
 
 def trainer_launches(trainer) -> int:

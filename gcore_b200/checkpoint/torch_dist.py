@@ -65,8 +65,13 @@ class _ShardWriter:
         self.storage[MetadataIndex(c.key, torch.Size(c.offset))] = _StorageInfo(self.rel, off, length)
 
     def add_object(self, key: str, obj):
+        # a sharded object travels as a BytesIO holding its torch.save image, and torch.distributed.checkpoint stores
+        # non-tensor items with torch.save again: readers unwrap twice (Megatron's ShardedObject convention)
+        inner = io.BytesIO()
+        torch.save(obj, inner)
+        inner.seek(0)
         buf = io.BytesIO()
-        torch.save(obj, buf)
+        torch.save(inner, buf)
         off = self.f.tell()
         self.f.write(buf.getvalue())
         self.bytes_items[key] = BytesStorageMetadata()
@@ -95,18 +100,43 @@ def _merge_metadata(parts: List[dict]) -> Metadata:
 
 
 def get_rng_state() -> dict:
-    st = {"random": random.getstate(), "numpy": np.random.get_state(), "torch": torch.get_rng_state()}
+    """Field names of Megatron's ``rng_state`` object (gpatch_v4/training_backend/megatron_backend/checkpoint.py:
+    753-797).  ``rng_tracker_states`` holds the named CUDA generators of a tensor-parallel RNG tracker; this package
+    draws its parallel randomness (initialisation, dropout-free training) from the default generators, so the entry
+    carries the default CUDA state under the tracker's default name."""
+    st = {"random_rng_state": random.getstate(), "np_rng_state": np.random.get_state(),
+          "torch_rng_state": torch.get_rng_state(), "rng_tracker_states": {}}
     if torch.cuda.is_available():
-        st["cuda"] = torch.cuda.get_rng_state()
+        st["cuda_rng_state"] = torch.cuda.get_rng_state()
+        st["rng_tracker_states"] = {"model-parallel-rng": st["cuda_rng_state"]}
     return st
 
 
-def set_rng_state(st: dict):
-    random.setstate(st["random"])
-    np.random.set_state(st["numpy"])
-    torch.set_rng_state(st["torch"])
-    if "cuda" in st and torch.cuda.is_available():
-        torch.cuda.set_rng_state(st["cuda"])
+def set_rng_state(st):
+    if isinstance(st, (list, tuple)):   # the object is a list with one entry per data-parallel random stream
+        st = st[0]
+    random.setstate(st.get("random_rng_state", st.get("random")))
+    np.random.set_state(st.get("np_rng_state", st.get("numpy")))
+    torch.set_rng_state(st.get("torch_rng_state", st.get("torch")))
+    cuda = st.get("cuda_rng_state", st.get("cuda"))
+    if cuda is not None and torch.cuda.is_available():
+        torch.cuda.set_rng_state(cuda)
+
+
+def rng_object_key(pp: int, tp: int, pp_size: int, tp_size: int, dp: int = 0) -> str:
+    """Storage key of the ``rng_state`` sharded object: global shape (pp_size, tp_size), offset (pp, tp); the object
+    of data-parallel replica 0 is the one Megatron stores, the other replicas' streams are kept under a sibling name
+    (they differ here because every data-parallel rank seeds its rollout sampler differently)."""
+    base = "rng_state" if dp == 0 else f"rng_state_dp{dp}"
+    return f"{base}/shard_{pp}_{tp}_{pp_size}_{tp_size}"
+
+
+def scheduler_state(opt_cfg, optimizer, total_steps) -> dict:
+    """``OptimizerParamScheduler.state_dict`` fields."""
+    return {"max_lr": opt_cfg.lr, "lr_warmup_steps": opt_cfg.lr_warmup_steps, "num_steps": optimizer.step_count,
+            "lr_decay_style": opt_cfg.lr_decay_style, "lr_decay_steps": opt_cfg.lr_decay_steps or total_steps,
+            "min_lr": opt_cfg.min_lr, "start_wd": opt_cfg.weight_decay, "end_wd": opt_cfg.weight_decay,
+            "wd_incr_style": "constant", "wd_incr_steps": opt_cfg.lr_decay_steps or total_steps}
 
 
 def _canonical(model, name: str) -> str:
@@ -138,8 +168,8 @@ def _model_chunks(engine) -> List[Chunk]:
                               mode):
             if c.replicated and tp_rank != 0:
                 continue
-            c.key = "model." + c.key
-            out.append(c)
+            out.append(c)   # the key is the parameter's path in the model, without a prefix (Megatron builds the
+            #                 model's sharded state dict with an empty prefix)
     return out
 
 
@@ -243,13 +273,21 @@ def save_checkpoint(engine, root: str, step: int, extra_state: Optional[dict] = 
             c.tensor = c.tensor.detach().to("cpu", copy=True)
     pp, tp = ps.get_pipeline_model_parallel_rank(), ps.get_tensor_model_parallel_rank()
     dp = ps.get_data_parallel_rank(with_context_parallel=True)
-    rng_key, rng_state = f"rng_state/shard_{pp}_{tp}_{dp}", get_rng_state()
+    rng_key = rng_object_key(pp, tp, ps.get_pipeline_model_parallel_world_size(),
+                             ps.get_tensor_model_parallel_world_size(), dp)
+    rng_state = [get_rng_state()]
     common = {"iteration": step, "checkpoint_version": 3.0,
               "optimizer_step": engine.optimizer.step_count if engine.optimizer is not None else 0,
               "engine_step": engine.step, "model_config": engine.model_cfg.to_dict(),
               "topology": dict(tp=engine.model.tp_size, ep=engine.model.ep_size,
                                pp=ps.get_pipeline_model_parallel_world_size(), world=world),
               "extra_state": extra_state or {}}
+    if engine.optimizer is not None and save_optim:
+        oc = engine.opt_cfg
+        common["optimizer"] = {"optimizer": {"param_groups": [
+            {"lr": oc.lr, "betas": (oc.adam_beta1, oc.adam_beta2), "eps": oc.adam_eps, "weight_decay": oc.weight_decay,
+             "step": engine.optimizer.step_count}]}, "param_state_sharding_type": "fully_sharded_model_space"}
+        common["lr_scheduler"] = scheduler_state(oc, engine.optimizer, engine.total_steps)
     h = dict(path=path, root=root, step=step, rank=rank, world=world, common=common, thread=None, error=None,
              rotate=(save_total_limit, save_retain_interval, async_delete))
 
@@ -316,7 +354,11 @@ class CheckpointReader:
         return torch.load(io.BytesIO(f.read(info.length)), map_location="cpu", weights_only=False)
 
     def read_object(self, key: str):
-        return self._read(self.md.storage_data[MetadataIndex(key)])
+        obj = self._read(self.md.storage_data[MetadataIndex(key)])
+        if isinstance(obj, io.BytesIO):   # the object's own torch.save image (see ``_ShardWriter.add_object``)
+            obj.seek(0)
+            obj = torch.load(obj, map_location="cpu", weights_only=False)
+        return obj
 
     def read_region(self, key: str, offset: Tuple[int, ...], shape: Tuple[int, ...]) -> torch.Tensor:
         """Assembles ``global[key][offset : offset + shape]`` from the stored chunks that overlap it."""
@@ -377,11 +419,13 @@ def load_checkpoint(engine, root: str, step: Optional[int] = None, load_optim: b
         name = _canonical(model, name)
         mode = getattr(p, "tp_mode", "none")
         probe = param_chunks(name, p.detach(), model.cfg, tp_rank if tp > 1 else 0, tp, ep_rank, ep, mode)
-        if any(("model." + c.key) not in have for c in probe):
+        # parameter paths carry no prefix; trees written by earlier versions of this package had "model." in front
+        prefix = next((pre for pre in ("", "model.") if all((pre + c.key) in have for c in probe)), None)
+        if prefix is None:
             missing.append(name)
             continue
         assign_from_chunks(name, p.data, model.cfg, tp_rank if tp > 1 else 0, tp, ep_rank, ep, mode,
-                           fetch_with("model."))
+                           fetch_with(prefix))
     if missing and strict:
         raise KeyError(f"checkpoint {path} lacks parameters: {missing[:8]}{'...' if len(missing) > 8 else ''}")
     common = torch.load(os.path.join(path, "common.pt"), map_location="cpu", weights_only=False)
@@ -404,16 +448,19 @@ def load_checkpoint(engine, root: str, step: Optional[int] = None, load_optim: b
                         assign_from_chunks(name, tmp, model.cfg, tp_rank if tp > 1 else 0, tp, ep_rank, ep, mode,
                                            fetch_with(f"optimizer.state.{label}."))
                         sh[k][lo - s:hi - s].copy_(tmp.reshape(-1)[lo - o:hi - o])
-            opt.step_count = common.get("optimizer_step", 0)
+            opt.step_count = common.get("optimizer_step", common.get("lr_scheduler", {}).get("num_steps", 0))
         else:
             opt.reload_master_from_params()
     engine.step = common.get("engine_step", step)
     if load_rng:
         pp = ps.get_pipeline_model_parallel_rank()
         dp = ps.get_data_parallel_rank(with_context_parallel=True)
-        key = f"rng_state/shard_{pp}_{tp_rank}_{dp}"
-        if key in have:
-            set_rng_state(rd.read_object(key))
+        sizes = (ps.get_pipeline_model_parallel_world_size(), ps.get_tensor_model_parallel_world_size())
+        for key in (rng_object_key(pp, tp_rank, *sizes, dp), rng_object_key(pp, tp_rank, *sizes, 0),
+                    f"rng_state/shard_{pp}_{tp_rank}_{dp}"):
+            if key in have:
+                set_rng_state(rd.read_object(key))
+                break
     rd.close()
     engine.loaded_extra_state = common.get("extra_state", {})
     return step

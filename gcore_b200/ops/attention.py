@@ -119,6 +119,22 @@ def flash_attn_varlen(q, k, v, cu_q, cu_k, max_q, max_k, causal=True, window=0, 
                                         (sinks is not None and sinks.requires_grad)):
             return _FlashAttnFn.apply(q, k, v, sinks, cu_q, cu_k, max_q, max_k, causal, window, scale)
         return _native_fwd(q, k, v, cu_q, cu_k, max_q, causal, window, sinks, scale)[0]
+    if q.is_cuda and q.dtype in (torch.bfloat16, torch.float16) and sinks is None and causal \
+            and q.shape[0] == k.shape[0]:
+        # eager baseline backend on a GPU: the library's fused variable-length attention (with autograd); grouped
+        # key / value heads are expanded because the library call takes one head count
+        try:
+            from torch.nn.attention.varlen import varlen_attn
+        except ImportError:
+            varlen_attn = None
+        if varlen_attn is not None:
+            g = q.shape[1] // k.shape[1]
+            kk = k.repeat_interleave(g, 1) if g > 1 else k
+            vv = v.repeat_interleave(g, 1) if g > 1 else v
+            cq = cu_q if cu_q.dtype == torch.int32 else cu_q.to(torch.int32)
+            ck = cu_k if cu_k.dtype == torch.int32 else cu_k.to(torch.int32)
+            return varlen_attn(q.contiguous(), kk.contiguous(), vv.contiguous(), cq, ck, int(max_q), int(max_k),
+                               scale=scale, window_size=(int(window) - 1 if window else -1, 0))
     return attn_varlen_ref(q, k, v, cu_q, cu_k, causal, window, sinks, scale)
 
 
@@ -141,6 +157,19 @@ def kv_append_rope(qkv, pos, slots, k_cache, v_cache, Hq, Hk, D, theta, rot=None
     kc = k_cache.view(-1, Hk, D)
     vc = v_cache.view(-1, Hk, D)
     valid = slots >= 0
+    if qkv.is_cuda:
+        # no boolean indexing on a GPU (it synchronises): rows without a slot rewrite the value a live row of the
+        # same call writes anyway (or, when the call has no live row, the first slot's current content)
+        sl = slots.long()
+        first = torch.argmax(valid.to(torch.int8))
+        sl = torch.where(valid, sl, sl[first].clamp_min(0))
+        src = torch.where(valid, torch.arange(T, device=qkv.device), first)
+        any_valid = valid.any()
+        knew = torch.where(any_valid, x[src, Hq:Hq + Hk], kc[sl])
+        vnew = torch.where(any_valid, x[src, Hq + Hk:], vc[sl])
+        kc.index_copy_(0, sl, knew)
+        vc.index_copy_(0, sl, vnew)
+        return
     kc[slots[valid].long()] = x[valid, Hq:Hq + Hk]
     vc[slots[valid].long()] = x[valid, Hq + Hk:]
 
@@ -174,6 +203,29 @@ def paged_decode(q, k_cache, v_cache, block_table, ctx_len, max_ctx, scale=None,
     g = Hq // Hk
     kc = k_cache.view(-1, Hk, D)
     vc = v_cache.view(-1, Hk, D)
+    if q.is_cuda:
+        # library path on a GPU (the eager baseline backend): one gather of every request's rows through the block
+        # table, then the library's fused attention with a length mask - no host synchronisation, static shapes
+        L = min(block_table.shape[1] * bs, (int(max_ctx) + bs - 1) // bs * bs)
+        p = torch.arange(L, device=q.device)
+        idx = block_table.long()[:, p // bs] * bs + (p % bs)[None, :]
+        n = ctx_len.long()[:, None]
+        mask = p[None, :] < n
+        if window and window > 0:
+            mask = mask & (p[None, :] >= n - window)
+        kk, vv = kc[idx], vc[idx]                                   # [B, L, Hk, D]
+        if sinks is None:
+            o = torch.nn.functional.scaled_dot_product_attention(
+                q.unsqueeze(2), kk.permute(0, 2, 1, 3), vv.permute(0, 2, 1, 3), attn_mask=mask[:, None, None, :],
+                scale=scale, enable_gqa=True)
+            out.copy_(torch.nan_to_num(o.squeeze(2)))
+            return out
+        sc = torch.einsum("bhd,blhd->bhl", q.float(), kk.float().repeat_interleave(g, 2)) * scale
+        sc = sc.masked_fill(~mask[:, None, :], float("-inf"))
+        lse = torch.logsumexp(torch.cat([sc, sinks.float()[None, :, None].expand(B, Hq, 1)], -1), -1)
+        pr = torch.exp(sc - lse[..., None])
+        out.copy_(torch.einsum("bhl,blhd->bhd", pr, vv.float().repeat_interleave(g, 2)).to(out.dtype))
+        return out
     for b in range(B):
         n = int(ctx_len[b])
         start = max(0, n - window) if window and window > 0 else 0

@@ -165,12 +165,38 @@ def sample_ref(logits, temperature, seeds, steps, greedy=False):
     return tok, lp
 
 
+_LIB_RNG = {"seeded": False}
+
+
+def _sample_library(logits, temperature, greedy, tp_group):
+    """Library sampling on a GPU (the eager baseline backend): vocabulary shards are gathered, then Gumbel-max from
+    the device's default generator (which CUDA graphs can capture), seeded alike on every rank at first use so that
+    tensor-parallel ranks draw the same tokens; per-request seeds are a property of the native sampler only."""
+    if tp_group is not None and dist.get_world_size(tp_group) > 1:
+        parts = [torch.empty_like(logits) for _ in range(dist.get_world_size(tp_group))]
+        dist.all_gather(parts, logits.contiguous(), group=tp_group)
+        logits = torch.cat(parts, dim=1)
+    z = logits.float() / max(float(temperature), 1e-6)
+    if greedy:
+        tok = z.argmax(-1)
+    else:
+        if not _LIB_RNG["seeded"] and not torch.cuda.is_current_stream_capturing():
+            torch.cuda.manual_seed(20240229)
+            _LIB_RNG["seeded"] = True
+        u = torch.rand(z.shape, device=z.device).clamp_min_(1e-20)
+        tok = (z - torch.log(-torch.log(u) + 1e-20)).argmax(-1)
+    lp = torch.log_softmax(z, -1).gather(-1, tok[:, None]).squeeze(-1)
+    return tok, lp
+
+
 def sample(logits, temperature, seeds, steps, greedy=False, tp_group=None, vocab_start=0):
     """Draws one token per row from ``softmax(logits / temperature)`` (Gumbel-max) and returns
     ``(tokens int64 [B], logp fp32 [B])``.  ``seeds`` int64 [B], ``steps`` int32 [B] select the random stream; the
     draw for a given (seed, step, token id) is independent of batching and of the vocabulary sharding."""
     B, V = logits.shape
     if not (_lib.use_native(logits) and logits.dtype in (torch.bfloat16, torch.float32)):
+        if logits.is_cuda:
+            return _sample_library(logits, temperature, greedy, tp_group)
         return sample_ref(logits, temperature, seeds, steps, greedy)
     inv_temp = 1.0 / max(float(temperature), 1e-6)
     tokens = torch.empty(B, dtype=torch.int64, device=logits.device)

@@ -245,7 +245,8 @@ class InferEngine:
         self.mla_dim = (cfg.kv_lora_rank + cfg.qk_rope_head_dim) if getattr(cfg, "use_mla", False) else 0
         self.vocab_local = weights.head.shape[0]
         self.vocab_start = self.vocab_local * (dist.get_rank(tp_group) if (tp_group is not None and tp_size > 1) else 0)
-        self.use_graph = use_cuda_graph and self.device.type == "cuda" and not _lib.force_eager()
+        # the library (eager) backend is captured too: its decode path is synchronisation-free on a GPU
+        self.use_graph = use_cuda_graph and self.device.type == "cuda"
         self.ep_group = None  # set when experts are parallel: engines of the group then run their passes in lockstep
         if any(getattr(lw.moe, "ep_size", 1) > 1 for lw in weights.layers if lw.moe is not None):
             # expert-parallel dispatch sizes its exchanges on the host (and the peer-memory path numbers its epochs
@@ -319,6 +320,48 @@ class InferEngine:
                 torch.cuda.empty_cache()
         if "weights" in tags:
             self.asleep["weights"] = True
+            if getattr(self, "owns_weights", False):
+                # a separate rollout copy is only needed while the engine serves: drop it, the next weight update
+                # rebuilds it (the reference's engines release their weights in sleep mode the same way)
+                self.w = None
+                self._graphs.clear()
+                if self.device.type == "cuda":
+                    torch.cuda.empty_cache()
+
+    def load_weights_from(self, model, bucket_mb: int = 512):
+        """Rebuilds an owned rollout copy from ``model`` through a staging bucket of ``bucket_mb``: every tensor is
+        copied into the bucket and from the bucket into the engine's own storage - the byte traffic of the reference's
+        export -> flattened bucket -> engine ``load_weights`` hand-over on one GPU
+        (gpatch_v4/client/update_weight_factory.py:271-379)."""
+        w = RolloutWeights.from_model(model, clone=False)
+        own = RolloutWeights.from_model(model, clone=False)
+        stage = torch.empty(bucket_mb << 20, dtype=torch.uint8, device=self.device)
+        moved = 0
+
+        def via_bucket(t):
+            nonlocal moved
+            if t is None or not isinstance(t, torch.Tensor):
+                return t
+            n = t.numel() * t.element_size()
+            moved += n
+            if n > stage.numel():
+                return t.detach().clone()
+            b = stage[:n].view(t.dtype).view(t.shape)
+            b.copy_(t)
+            return b.clone()
+
+        own.embed, own.final_ln, own.head = via_bucket(w.embed), via_bucket(w.final_ln), via_bucket(w.head)
+        for lo, lw in zip(own.layers, w.layers):
+            for k in ("ln1", "qkv_w", "qkv_b", "o_w", "ln2", "fc1_w", "fc2_w", "q_ln", "k_ln", "sinks"):
+                setattr(lo, k, via_bucket(getattr(lw, k)))
+        del stage
+        self.w = own
+        self.owns_weights = True
+        self.asleep["weights"] = False
+        self._graphs.clear()
+        if self.device.type == "cuda":
+            torch.cuda.current_stream().synchronize()
+        return moved
 
     def flush_cache(self):
         if self.sched is not None:

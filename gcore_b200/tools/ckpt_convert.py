@@ -70,7 +70,7 @@ def policy_to_critic(model: str, src: str, dst: str, step=None, dtype: str = "bf
     rd = CheckpointReader(iter_dir(src, step if step is not None else read_latest_step(src)))
     have = set(rd.keys())
     rd.close()
-    assert any(k.startswith("model.decoder.layers") for k in have), f"{src} holds no decoder weights"
+    assert any(k.startswith(("decoder.layers", "model.decoder.layers")) for k in have), f"{src} holds no decoder weights"
     assert head, "the critic model has no value head"
     eng.optimizer.reload_master_from_params()
     save_checkpoint(eng, dst, out_step, save_optim=False)

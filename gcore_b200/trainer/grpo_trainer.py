@@ -100,6 +100,9 @@ class GrpoTrainer:
         # those tensors (base + delta, rewritten at every resync) and shares the storage of all the others
         self.lora = bool(cfg.policy.lora.enabled)
         share = cfg.policy.share_rollout_weights
+        # a separate rollout copy that exists only while the engine serves (rebuilt by every weight update, dropped
+        # after every rollout): the memory behaviour of the reference's colocated engines in sleep mode
+        self.release_rollout_weights = bool(not share and getattr(cfg.policy, "release_rollout_weights", False))
         weights = RolloutWeights.from_model(model, clone=not share)
         if self.lora and share:
             from ..rollout.weight_sync import detach_lora_targets
@@ -122,6 +125,7 @@ class GrpoTrainer:
         self.serve_fp8 = bool(getattr(ie, "fp8_weights", False) or cfg.policy.fp8)
         if self.serve_fp8:
             self.engine.quantize_weights_fp8()
+        self.engine.owns_weights = not share
         # gradient buffers are only needed inside the update phase
         self.policy.release_grad_buffers()
         return self
@@ -155,7 +159,7 @@ class GrpoTrainer:
                     embeds.append(model.vision(patches.to(next(model.vision.parameters()).dtype), grids))
             vl_kw = dict(image_embeds=embeds, image_token_id=model.image_token_id)
         reqs = self.engine.generate(prompts, sp, n=n, **vl_kw)
-        self.engine.sleep(("kv_cache",))
+        self.engine.sleep(("kv_cache", "weights") if self.release_rollout_weights else ("kv_cache",))
         samples = []
         dp_rank = ps.get_data_parallel_rank()
         for k, r in enumerate(reqs):
@@ -293,6 +297,8 @@ class GrpoTrainer:
                 from ..rollout.weight_sync import sync_lora_deltas
                 sync_lora_deltas(self.policy, self.engine)
             self.engine.update_weights(None)
+        elif self.release_rollout_weights:
+            self.engine.load_weights_from(self.policy.model, self.cfg.policy.sampler_client.update_weight_max_size_mb)
         else:
             from ..rollout.weight_sync import sync_weights
             sync_weights(self.policy, self.engine)

@@ -282,3 +282,26 @@ def test_user_post_advantage_hook_edits_samples_and_reports_metrics(tmp_path):
     assert m["post-adv/abs_sum"] > 0
     assert m["policy/grad_norm"] < 1e-7     # zeroed advantages and no KL term: nothing to learn from
     assert all(float(s["advantages"].abs().sum()) == 0.0 for s in tr.last_samples)
+
+
+def test_separate_rollout_copy_is_freed_after_rollout_and_rebuilt_at_resync():
+    """``share_rollout_weights=false`` with ``release_rollout_weights``: the engine owns a copy only while it serves;
+    every resync rebuilds it through the staging bucket from the trained weights (the library baseline's hand-over)."""
+    torch.manual_seed(0)
+    cfg = make_cfg()
+    cfg.policy.share_rollout_weights = False
+    cfg.policy.release_rollout_weights = True
+    tr = GrpoTrainer(cfg, model_cfg=get_preset("tiny_llama", dtype="float32"), reward_fn=reward_has_small_token).setup()
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(3, 1024, (8,), generator=g).tolist() for _ in range(4)]
+    p = tr.policy.model.decoder.layers[0].self_attention.linear_qkv.weight
+    for _ in range(2):
+        m = tr.step(prompts)
+        assert m["policy/grad_norm"] > 0
+        w = tr.engine.w.layers[0].qkv_w           # rebuilt by the resync at the end of the step
+        assert w.data_ptr() != p.data_ptr() and torch.equal(w, p.detach())
+    tr.rollout(prompts)
+    assert tr.engine.w is None                    # dropped with the KV cache when the rollout ends
+    tr.update_weights()
+    s = tr.rollout(prompts)[0]
+    assert len(s["tokens"]) > s["prompt_length"]

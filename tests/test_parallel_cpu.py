@@ -46,18 +46,18 @@ def test_tp2_sp_matches_single_process_and_checkpoint_reshards(tmp_path):
     # Megatron-style keys: stacked layer axis, interleaved QKV, fc1 = [gate; up]
     rd = CheckpointReader(str(tmp_path / "ckpt" / "iter_0000004"))
     keys = set(rd.keys())
-    assert "model.decoder.layers.self_attention.linear_qkv.weight" in keys
-    assert "model.decoder.layers.self_attention.linear_qkv.layer_norm_weight" in keys
+    assert "decoder.layers.self_attention.linear_qkv.weight" in keys
+    assert "decoder.layers.self_attention.linear_qkv.layer_norm_weight" in keys
     assert "optimizer.state.exp_avg.decoder.layers.mlp.linear_fc1.weight" in keys
-    qkv = rd.full_tensor("model.decoder.layers.self_attention.linear_qkv.weight")
+    qkv = rd.full_tensor("decoder.layers.self_attention.linear_qkv.weight")
     assert tuple(qkv.shape) == (2, (4 + 2 * 2) * 64, 256)
     for f in ("common.pt", "metadata.json", ".metadata"):
         assert os.path.exists(tmp_path / "ckpt" / "iter_0000004" / f)
     # independent reader: torch.distributed.checkpoint itself
     import torch.distributed.checkpoint as dcp
-    sd = {"model.decoder.layers.self_attention.linear_qkv.weight": torch.zeros_like(qkv)}
+    sd = {"decoder.layers.self_attention.linear_qkv.weight": torch.zeros_like(qkv)}
     dcp.load(sd, checkpoint_id=str(tmp_path / "ckpt" / "iter_0000004"), no_dist=True)
-    assert torch.equal(sd["model.decoder.layers.self_attention.linear_qkv.weight"], qkv)
+    assert torch.equal(sd["decoder.layers.self_attention.linear_qkv.weight"], qkv)
     # HF export gathered over TP equals the single-process weights under HF names
     from gcore_b200.checkpoint.hf import read_hf_dir
     from gcore_b200.checkpoint.layout import export_full_weights
@@ -143,7 +143,7 @@ def test_pp2_1f1b_matches_single_process(tmp_path):
     # ... and loads into the unpartitioned model: layers are stored under their global index
     from gcore_b200.checkpoint.torch_dist import CheckpointReader, load_checkpoint
     rd = CheckpointReader(str(tmp_path / "ckpt" / "iter_0000004"))
-    assert tuple(rd.full_tensor("model.decoder.layers.mlp.linear_fc2.weight").shape)[0] == 4
+    assert tuple(rd.full_tensor("decoder.layers.mlp.linear_fc2.weight").shape)[0] == 4
     e2 = pw.engine(mcfg, 1)
     e2.setup_model_and_get_optimizer(seed=5)
     assert load_checkpoint(e2, str(tmp_path / "ckpt")) == 4

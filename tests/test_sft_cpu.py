@@ -121,18 +121,18 @@ def test_checkpoint_stage_converters(tmp_path):
     cc.main(["strip", "--model", str(cfg_json), "--src", str(tmp_path / "rl"), "--dst", str(tmp_path / "pol"),
              "--dtype", "float32"])
     keys = set(CheckpointReader(str(tmp_path / "pol" / "iter_0000000")).keys())
-    assert not any(k.startswith("optimizer.") for k in keys) and "model.output_layer.weight" in keys
+    assert not any(k.startswith("optimizer.") for k in keys) and "output_layer.weight" in keys
     cc.main(["policy2critic", "--model", str(cfg_json), "--src", str(tmp_path / "pol"), "--dst", str(tmp_path / "crit"),
              "--dtype", "float32"])
     rd = CheckpointReader(str(tmp_path / "crit" / "iter_0000000"))
-    assert tuple(rd.full_tensor("model.output_layer.weight").shape) == (1, mcfg.hidden_size)
+    assert tuple(rd.full_tensor("output_layer.weight").shape) == (1, mcfg.hidden_size)
     src = CheckpointReader(str(tmp_path / "pol" / "iter_0000000"))
-    k = "model.decoder.layers.mlp.linear_fc2.weight"
+    k = "decoder.layers.mlp.linear_fc2.weight"
     assert torch.equal(rd.full_tensor(k), src.full_tensor(k))
     cc.main(["mcore2hf", "--model", str(cfg_json), "--src", str(tmp_path / "pol"), "--dst", str(tmp_path / "hf"),
              "--dtype", "float32"])
     cc.main(["hf2mcore", "--model", str(cfg_json), "--src", str(tmp_path / "hf"), "--dst", str(tmp_path / "back"),
              "--dtype", "float32"])
     back = CheckpointReader(str(tmp_path / "back" / "iter_0000000"))
-    for key in ("model.embedding.word_embeddings.weight", "model.decoder.layers.self_attention.linear_qkv.weight", k):
+    for key in ("embedding.word_embeddings.weight", "decoder.layers.self_attention.linear_qkv.weight", k):
         assert torch.equal(back.full_tensor(key), src.full_tensor(key)), key

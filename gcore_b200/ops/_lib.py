@@ -52,6 +52,9 @@ def kernels() -> ctypes.CDLL:
                 "to eager PyTorch)")
         lib = ctypes.CDLL(str(path))
         _declare_kernels(lib)
+        cap = os.environ.get("GCORE_DECODE_SMEM_KB")   # shared-memory budget of decode GEMM CTAs (0 = full ring)
+        if cap is not None and hasattr(lib, "gk_gemm_set_decode_smem_cap"):
+            lib.gk_gemm_set_decode_smem_cap(int(cap) * 1024)
         _KERNELS = lib
     return _KERNELS
 

@@ -238,7 +238,9 @@ using namespace gks;
 static int skinny_smem_bytes(int Tp, int ks, int K, int* stages_out) {
   const int stage_bytes = A_BYTES + Tp * 128;
   const int red_bytes = ks > 1 ? Tp * BM * 4 : 0;
-  int stages = (200 * 1024 - red_bytes) / stage_bytes;
+  const int budget = gk::decode_smem_cap() > 0 ? gk::decode_smem_cap() : 200 * 1024;
+  int stages = (budget - red_bytes - 1024 - 256) / stage_bytes;
+  if (stages < 3) stages = 3;
   if (stages > MAX_STAGES) stages = MAX_STAGES;
   const int kb_per = ((K + BK - 1) / BK + ks - 1) / ks;
   if (stages > kb_per) stages = kb_per < 2 ? 2 : kb_per;

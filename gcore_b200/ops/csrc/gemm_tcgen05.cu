@@ -55,6 +55,9 @@ struct GemmParams {
   float* ws;
   int* counters;
   int* err;
+  int stages;   // shared-memory ring depth actually used (<= Cfg::STAGES)
+  int a_early;  // operand A does not depend on the kernel before this one (decode: A is the weight): its first
+                // tiles are requested before the programmatic-dependency wait, while the predecessor still runs
 };
 
 struct Tile {
@@ -242,16 +245,18 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const Tile& t, 
   }
 }
 
-template <int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+// MINB = 2 is the decode instantiation: registers are capped so that two CTAs (of this kernel, or this one and the
+// next GEMM of the chain) fit one SM's register file together.
+template <int BN, bool A_MN, bool B_MN, int MINB = 1>
+__global__ void __launch_bounds__(GEMM_THREADS, MINB)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
   using C = Cfg<BN>;
-  constexpr int STAGES = C::STAGES;
+  const int STAGES = p.stages;  // ring depth of this launch; the barrier arrays are sized for the maximum
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * C::STAGE_BYTES);
-  uint64_t* empty = full + STAGES;
-  uint64_t* tfull = empty + STAGES;
+  uint64_t* empty = full + C::STAGES;
+  uint64_t* tfull = empty + C::STAGES;
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tempty + 2);
   int* s_flag = reinterpret_cast<int*>(tmem_holder + 1);
@@ -261,6 +266,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int lane = threadIdx.x & 31;
   pdl_launch_dependents();
 
+  int pre = 0;  // k-blocks of this CTA's first tile whose A tiles were requested early (thread 0 only)
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
@@ -271,8 +277,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(&tempty[a], 128);
     }
     fence_barrier_init();
-    prefetch_tmap(&tmA);
+    if (p.a_early && p.group_mode == 0 && !A_MN) {
+      // the weight tiles of the first output tile start streaming now; the stage barriers are armed for the whole
+      // stage, the B halves follow after the dependency wait (producer loop below)
+      if (static_cast<int>(blockIdx.x) < total_tiles(p, nullptr, BN)) {
+        const Tile t = decode_tile(p, nullptr, BN, blockIdx.x);
+        pre = t.kblocks < STAGES ? t.kblocks : STAGES;
+        for (int kb = 0; kb < pre; ++kb) {
+          mbar_expect_tx(&full[kb], C::STAGE_BYTES);
+          tma_load_2d(smem + kb * C::STAGE_BYTES, &tmA, &full[kb], t.k0 + kb * BK, t.m0);
+        }
+      }
+    }
     prefetch_tmap(&tmB);
+    if (!p.a_early) prefetch_tmap(&tmA);
   }
   if (threadIdx.x == 32 && p.group_mode == 1) {
     pdl_wait();  // the group offsets come from the kernel before this one
@@ -299,17 +317,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int s = 0;
     uint32_t ph = 0;
     bool ok = true;
+    pre = __shfl_sync(0xffffffffu, pre, 0);
     for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
       const Tile t = decode_tile(p, s_prefix, BN, tile);
       for (int kb = 0; kb < t.kblocks; ++kb) {
         ok = mbar_wait(&empty[s], ph ^ 1, p.err, ERR_WAIT_EMPTY);
         if (!ok) break;
+        const bool a_done = (tile == static_cast<int>(blockIdx.x)) && (kb < pre);  // requested before the wait
         if (lane == 0) {
           uint8_t* sa = smem + s * C::STAGE_BYTES;
           uint8_t* sb = sa + C::A_BYTES;
           const int k = t.k0 + kb * BK;
-          mbar_expect_tx(&full[s], C::STAGE_BYTES);
-          if (A_MN) {
+          if (!a_done) mbar_expect_tx(&full[s], C::STAGE_BYTES);
+          if (a_done) {
+          } else if (A_MN) {
 #pragma unroll
             for (int i = 0; i < BM / 64; ++i) tma_load_2d(sa + i * 8192, &tmA, &full[s], t.m0 + i * 64, k);
           } else {
@@ -425,11 +446,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             float v[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = 0.f;
-            // four partials' loads are in flight together: the reduction costs ksplit / 4 trips to L2, not ksplit
-            for (int ks0 = 0; ks0 < p.ksplit; ks0 += 4) {
-              float part[4][32];
+            // several partials' loads are in flight together: the reduction costs ksplit / U trips to L2, not ksplit
+            constexpr int U = MINB > 1 ? 2 : 4;
+            for (int ks0 = 0; ks0 < p.ksplit; ks0 += U) {
+              float part[U][32];
 #pragma unroll
-              for (int u = 0; u < 4; ++u) {
+              for (int u = 0; u < U; ++u) {
                 const int ks = ks0 + u < p.ksplit ? ks0 + u : ks0;  // a repeated slice is loaded but not added
                 const float* w = p.ws + (static_cast<long long>(t.mn_index) * p.ksplit + ks) * (BM * BN) +
                                  static_cast<long long>(c * 32) * BM + row_in_tile;
@@ -437,7 +459,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 for (int j = 0; j < 32; ++j) part[u][j] = __ldcg(w + j * BM);
               }
 #pragma unroll
-              for (int u = 0; u < 4; ++u) {
+              for (int u = 0; u < U; ++u) {
                 if (ks0 + u < p.ksplit) {
 #pragma unroll
                   for (int j = 0; j < 32; ++j) v[j] += part[u][j];
@@ -461,23 +483,48 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
-template <int BN, bool A_MN, bool B_MN>
-int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid, cudaStream_t st) {
+template <int BN, bool A_MN, bool B_MN, int MINB>
+int launch_gemm_q(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& q, int grid, cudaStream_t st) {
   using C = Cfg<BN>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, A_MN, B_MN>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, A_MN, B_MN, MINB>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  launch_k(gemm_bf16_kernel<BN, A_MN, B_MN>, dim3(grid), dim3(GEMM_THREADS), C::SMEM_BYTES, st, tmA, tmB, p);
+  const int smem_bytes = q.stages * C::STAGE_BYTES + 1024 + 256 + (MAX_GROUPS + 1) * 4;
+  launch_k(gemm_bf16_kernel<BN, A_MN, B_MN, MINB>, dim3(grid), dim3(GEMM_THREADS), smem_bytes, st, tmA, tmB, q);
   return launch_status();
+}
+
+template <int BN, bool A_MN, bool B_MN>
+int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid, cudaStream_t st) {
+  using C = Cfg<BN>;
+  GemmParams q = p;
+  q.stages = C::STAGES;
+  q.a_early = 0;
+  if constexpr (!A_MN && !B_MN && BN <= 128) {
+    if (p.transposed && p.group_mode == 0 && decode_smem_cap() > 0) {
+      // decode (swap-AB): A is the weight.  A shallower ring and the register-capped instantiation leave room for
+      // the CTA of the next kernel of the chain on the same SM, which then streams its own weights while this
+      // kernel drains (programmatic dependent launch)
+      int nst = (decode_smem_cap() - 1024 - 256 - (MAX_GROUPS + 1) * 4) / C::STAGE_BYTES;
+      if (nst < 3) nst = 3;
+      if (nst < C::STAGES) q.stages = nst;
+      q.a_early = 1;
+      return launch_gemm_q<BN, A_MN, B_MN, 2>(tmA, tmB, q, grid, st);
+    }
+  }
+  return launch_gemm_q<BN, A_MN, B_MN, 1>(tmA, tmB, q, grid, st);
 }
 
 }  // namespace gk
 
 using namespace gk;
+
+// Shared-memory budget of decode-shaped (swap-AB) launches; 0 restores the full-depth ring and the late A loads.
+GK_EXPORT void gk_gemm_set_decode_smem_cap(int bytes) { gk::decode_smem_cap() = bytes; }
 
 // Scratch requirement of split-K for a given problem: floats of workspace and ints of counters.
 GK_EXPORT void gk_gemm_splitk_scratch(int M, int N, int bn, int ksplit, long long* ws_floats, long long* counters) {

@@ -96,6 +96,14 @@ inline int sm_count() {
   return n;
 }
 
+// Shared-memory budget of one CTA of a decode-shaped (swap-AB) GEMM launch, in bytes; 0 = as much as the kernel can
+// use.  With the budget at about half an SM, the CTA of the next GEMM of a decode chain becomes resident beside the
+// running one and streams its first weight tiles while the running kernel finishes.
+inline int& decode_smem_cap() {
+  static int cap = 104 * 1024;
+  return cap;
+}
+
 // ---- programmatic dependent launch: a kernel launched through launch_k may start its prologue while the previous
 // kernel of the stream is still draining; it must call pdl_wait() before it touches global memory, and it calls
 // pdl_launch_dependents() first so that its own successor may be scheduled early.  Both instructions are no-ops in a

@@ -231,7 +231,7 @@ class InferEngine:
                  max_running_requests: int = 64, max_model_len: int = 2048, kv_block_size: int = 16,
                  num_kv_blocks: Optional[int] = None, gpu_memory_utilization: float = 0.7,
                  max_prefill_tokens: int = 16384, use_cuda_graph: bool = True, sync_interval: int = 8,
-                 eos_token_id: Optional[int] = None, device=None):
+                 eos_token_id: Optional[int] = None, device=None, max_sync_interval: int = 64):
         self.cfg, self.w = cfg, weights
         self.tp, self.tp_group = tp_size, tp_group
         self.device = device or weights.embed.device
@@ -253,7 +253,11 @@ class InferEngine:
             # there), so a decode step cannot be replayed from a captured graph
             self.use_graph = False
             self.ep_group = ps.get_expert_model_parallel_group()
+        # decode steps between two host synchronisations: ``sync_interval`` while requests wait for a slot (a finished
+        # request should hand its slot over soon), up to ``max_sync_interval`` when nothing waits (then only the
+        # discarded tokens after an early stop are at stake, and every synchronisation costs the GPU an idle gap)
         self.sync_interval = max(1, sync_interval)
+        self.max_sync_interval = max(self.sync_interval, max_sync_interval)
         self.eos = eos_token_id
         self.gpu_memory_utilization = gpu_memory_utilization
         self._num_blocks_cfg = num_kv_blocks
@@ -626,7 +630,7 @@ class InferEngine:
     # ------------------------------------------------------------------ state / graphs
     def _new_state(self, B, params: SamplingParams):
         dev = self.device
-        R = self.sync_interval
+        R = self.max_sync_interval
         return dict(
             tokens=torch.zeros(B, dtype=torch.int64, device=dev), pos=torch.zeros(B, dtype=torch.int32, device=dev),
             active=torch.zeros(B, dtype=torch.bool, device=dev),
@@ -843,6 +847,10 @@ class InferEngine:
                 continue
             # ---- reserve KV for the next interval and push the batch state
             interval = self.sync_interval
+            if self.sched.stats()["waiting"] == 0 and self.ep_group is None:
+                # nobody waits for a slot: run until the first request reaches its length limit
+                left = min(params.max_new_tokens - len(r.out_tokens) for r in slot_req.values())
+                interval = max(interval, min(left, self.max_sync_interval))
             for s, r in list(slot_req.items()):
                 remaining = params.max_new_tokens - len(r.out_tokens)
                 self.sched.reserve(r.rid, min(interval, remaining) + 1)
@@ -862,28 +870,27 @@ class InferEngine:
             ring_tok = st["ring_tok"].cpu()
             ring_lp = st["ring_lp"].cpu()
             io_counters.add_d2h(io_counters.tensor_bytes(ring_tok, ring_lp))
-            # ---- harvest (plain lists: per-element tensor indexing would keep the GPU idle for milliseconds)
-            tok_cols = ring_tok.t().tolist()
-            lp_cols = ring_lp.t().tolist()
+            # ---- harvest: one column of the ring per request, cut at its first stop token or at its length limit
+            tok_np = ring_tok[:interval].t().contiguous().numpy()     # [B, interval]
+            lp_np = ring_lp[:interval].t().contiguous().numpy()
+            stop_hit = None
+            if stop_ids:
+                import numpy as np
+                stop_hit = np.isin(tok_np, np.fromiter(stop_ids, dtype=tok_np.dtype))
             for s in live:
                 r = slot_req[s]
-                done = False
-                took = 0
-                col_t, col_l = tok_cols[s], lp_cols[s]
-                for k in range(interval):
-                    t = col_t[k]
-                    r.out_tokens.append(t)
-                    r.out_logprobs.append(col_l[k])
-                    took += 1
-                    if t in stop_ids:
-                        done, r.finish_reason = True, "stop"
-                        break
-                    if len(r.out_tokens) >= params.max_new_tokens:
-                        done, r.finish_reason = True, "length"
-                        break
+                room = params.max_new_tokens - len(r.out_tokens)
+                took = min(interval, room)
+                reason = "length" if took == room else ""
+                if stop_hit is not None:
+                    hits = stop_hit[s, :took].nonzero()[0]
+                    if hits.size:
+                        took, reason = int(hits[0]) + 1, "stop"
+                r.out_tokens.extend(tok_np[s, :took].tolist())
+                r.out_logprobs.extend(lp_np[s, :took].tolist())
                 self.stats["generated_tokens"] += took
-                if done:
-                    r.finished = True
+                if reason:
+                    r.finished, r.finish_reason = True, reason
                     self.sched.finish(r.rid)
                     del slot_req[s]
                     slots_free.append(s)

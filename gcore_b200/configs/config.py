@@ -325,6 +325,7 @@ class PolicyConfig(MappingMixin):
     manual_clear_memory: bool = False
     export_weights_buffer_max_size_mb: int = 2048
     share_rollout_weights: bool = True  # colocated trainer and decoder read the same bf16 parameter storage
+    offload_ref_model: bool = False  # frozen reference policy in pinned host memory except during its forward pass
     release_rollout_weights: bool = False  # separate copy only: free it after each rollout, rebuild it at each resync
     ce_token_compaction: bool = True    # vocabulary projection / log-probs only at positions inside the loss mask
     # vision-language policy: fields of ``models.vlm.VisionConfig`` (empty = text-only) and the placeholder token id

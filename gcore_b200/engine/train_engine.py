@@ -746,6 +746,61 @@ class TrainingEngine:
         return out
 
     # ------------------------------------------------------------------ memory time-sharing
+    def _ref_swap(self):
+        if self.ref_model is None:
+            return None
+        if getattr(self, "_ref_swapper", None) is None:
+            from .swap import ModuleSwap
+            self._ref_swapper = ModuleSwap(self.ref_model, frozen=True)
+        return self._ref_swapper
+
+    def offload_ref_model(self):
+        """Frees the frozen reference policy's device memory (its pinned host image is written once)."""
+        sw = self._ref_swap()
+        if sw is not None:
+            sw.offload()
+
+    def prefetch_ref_model(self):
+        """Starts bringing the reference policy back on a side stream (hidden under whatever runs next)."""
+        sw = self._ref_swap()
+        if sw is not None:
+            sw.prefetch()
+
+    def onload_ref_model(self):
+        sw = self._ref_swap()
+        if sw is not None:
+            sw.onload()
+
+    def offload_model(self):
+        """Moves the trainable model's flat parameter buffers to pinned host memory (buffers that are mapped on
+        data-parallel peers stay: their addresses are part of the peers' kernels' arguments)."""
+        from .swap import BufferSwap
+        if getattr(self, "_model_swaps", None) is None:
+            self._model_swaps = []
+            for buf in (self.ddp.buffers if self.ddp is not None else []):
+                if buf.peer:
+                    continue
+
+                shapes = {id(p): (tuple(p.shape), p.numel()) for p in buf.params}
+
+                def rebind(t, buf=buf, shapes=shapes):
+                    for p in buf.params:
+                        o = buf.offsets[id(p)]
+                        shp, n = shapes[id(p)]
+                        p.data = t[o:o + n].view(shp) if t is not None else \
+                            torch.empty(0, dtype=p.dtype, device=p.device)
+
+                def set_buffer(t, buf=buf):
+                    buf.param_data = t
+
+                self._model_swaps.append(BufferSwap(lambda buf=buf: buf.param_data, set_buffer, rebind))
+        for sw in self._model_swaps:
+            sw.offload()
+
+    def onload_model(self):
+        for sw in getattr(self, "_model_swaps", None) or []:
+            sw.onload()
+
     def offload_optimizer(self):
         if self.optimizer is not None:
             self.optimizer.offload()

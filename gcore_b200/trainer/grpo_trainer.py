@@ -126,6 +126,8 @@ class GrpoTrainer:
         if self.serve_fp8:
             self.engine.quantize_weights_fp8()
         self.engine.owns_weights = not share
+        if getattr(cfg.policy, "offload_ref_model", False):
+            self.policy.offload_ref_model()
         # gradient buffers are only needed inside the update phase
         self.policy.release_grad_buffers()
         return self
@@ -212,10 +214,21 @@ class GrpoTrainer:
             from ..gdebug import check_rollout_batches
             check_rollout_batches(samples)
         tm.start("compute_logps")
+        need_ref = not cfg.policy.without_ref and cfg.ppo.grpo_kl_loss_beta != 0
+        swap_ref = need_ref and getattr(cfg.policy, "offload_ref_model", False)
+        if swap_ref:
+            # the frozen reference policy lives in pinned host memory between its forward passes; its upload runs on
+            # a side stream under the old-policy pass (gpatch_v4/training_backend/megatron_backend/mcore_engine.py:
+            # 373-531 swaps policy and reference around the two passes)
+            self.policy.prefetch_ref_model()
         if not cfg.ppo.skip_prev_logps:
             self.policy.compute_log_probs(samples, use_ref=False)
-        if not cfg.policy.without_ref and cfg.ppo.grpo_kl_loss_beta != 0:
+        if need_ref:
+            if swap_ref:
+                self.policy.onload_ref_model()
             self.policy.compute_log_probs(samples, use_ref=True)
+            if swap_ref:
+                self.policy.offload_ref_model()
         if self.critic is not None:
             self.critic.compute_values(samples)
         if self.teacher is not None:
@@ -310,6 +323,26 @@ class GrpoTrainer:
         if self.serve_fp8:
             # the engine's dense projections are re-quantised (e4m3, 128x128 scales) from the weights just handed over
             self.engine.quantize_weights_fp8()
+
+    def offload_model(self):
+        """Trainable weights to pinned host memory (early-swap mode of the reference's ``OffloadManager``,
+        gpatch_v4/actor/mixin.py:360-393).  A rollout engine that reads the trainer's storage drops its views first,
+        so the device memory is really returned."""
+        if self.cfg.policy.share_rollout_weights and self.engine is not None:
+            self.engine.w = None
+            self.engine._graphs.clear()
+        self.policy.offload_model()
+
+    def onload_model(self):
+        self.policy.onload_model()
+        if self.cfg.policy.share_rollout_weights and self.engine is not None:
+            w = RolloutWeights.from_model(self.policy.model, clone=False)
+            if self.lora:
+                from ..rollout.weight_sync import detach_lora_targets
+                detach_lora_targets(self.policy, w)
+            self.engine.w = w
+            self.engine._graphs.clear()
+            self.update_weights()
 
     def _rollout_metrics(self, samples):
         r = torch.stack([torch.as_tensor(s["rewards"]).float().sum() for s in samples])

@@ -305,3 +305,30 @@ def test_separate_rollout_copy_is_freed_after_rollout_and_rebuilt_at_resync():
     tr.update_weights()
     s = tr.rollout(prompts)[0]
     assert len(s["tokens"]) > s["prompt_length"]
+
+
+def test_reference_and_policy_weights_swap_to_host_and_back():
+    """``policy.offload_ref_model``: the reference policy holds no device storage outside its forward pass and the
+    step's numbers do not change; ``offload_model`` / ``onload_model`` round-trip the trainable weights."""
+    prompts = [torch.randint(3, 1024, (8,), generator=torch.Generator().manual_seed(5)).tolist() for _ in range(4)]
+    out = []
+    for swap in (False, True):
+        torch.manual_seed(0)
+        cfg = make_cfg(grpo_kl_loss_beta=0.05)
+        cfg.policy.offload_ref_model = swap
+        tr = GrpoTrainer(cfg, model_cfg=get_preset("tiny_llama", dtype="float32"),
+                         reward_fn=reward_has_small_token).setup()
+        ms = [tr.step(prompts) for _ in range(2)]
+        out.append([(m["policy/grad_norm"], m["ppo-metrics/kl_to_ref"]) for m in ms])
+        if swap:
+            assert all(p.numel() == 0 for p in tr.policy.ref_model.parameters())
+            before = [p.detach().clone() for p in tr.policy.model.parameters()]
+            tr.offload_model()
+            assert all(p.numel() == 0 for p in tr.policy.model.parameters()) and tr.engine.w is None
+            tr.onload_model()
+            assert tr.engine.w.layers[0].qkv_w.data_ptr() == \
+                tr.policy.model.decoder.layers[0].self_attention.linear_qkv.weight.data_ptr()
+            for a, p in zip(before, tr.policy.model.parameters()):
+                assert torch.equal(a, p)
+            assert tr.step(prompts)["policy/grad_norm"] > 0
+    assert out[0] == out[1] and out[0][1][1] > 0

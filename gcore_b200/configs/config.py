@@ -690,3 +690,97 @@ class EvaluateConfig(BaseTopConfig):
 @dataclass
 class InferenceConfig(EvaluateConfig):
     output_path: Optional[str] = None
+
+
+# ---------------------------------------------------------------------------------------------------- image generation
+@dataclass
+class T2iModelConfig(MappingMixin):
+    """Architecture of the diffusion transformer, its text encoder and its latent autoencoder (random init unless
+    ``state_dict_path`` is given); fields of ``models.dit.DiTConfig`` under ``transformer``."""
+    pipeline: str = "flux"   # flux | qwen_image_edit | flux_kontext | bagel
+    transformer: Dict[str, Any] = field(default_factory=dict)
+    text_layers: int = 2
+    text_max_length: int = 32
+    latent_channels: int = 16
+    vae_factor: int = 8
+    vae_base_channels: int = 16
+    state_dict_path: Optional[str] = None
+    freeze_text_encoder: bool = True
+    freeze_vae: bool = True
+    # bagel: width / depth of the unified decoder
+    lm_hidden_size: int = 128
+    lm_layers: int = 2
+    lm_heads: int = 4
+    lm_vocab_size: int = 258
+
+
+@dataclass
+class T2iTrainingConfig(MappingMixin):
+    """Names follow the reference's text-to-image training section (gpatch_v4/configs/config.py ``T2i*`` and the use
+    sites in extended_pipeline/pipeline_flux.py:232-535)."""
+    seed: int = 42
+    height: int = 64
+    width: int = 64
+    sampling_steps: int = 8
+    shift: float = 3.0
+    eta: float = 0.3
+    guidance_scale: float = 3.5
+    timestep_fraction: float = 0.5          # share of a trajectory's steps the update trains on
+    rollout_gbs: int = 4                    # prompts per rollout, whole job
+    rollout_mbs: int = 1
+    rollout_model_mbs: Optional[int] = None
+    sampling_repeat_n: int = 4
+    same_noise_for_same_prompt: bool = False
+    train_gbs_wo_timestep: int = 16         # trajectories per optimizer step, whole job
+    train_mbs: int = 1
+    train_gas_wo_timestep: int = 1
+    total_ppo_step: int = 2
+    total_training_step: int = 2
+    gradient_accumulation_steps: int = 1
+    train_method: str = "dpo"               # preference trainer: dpo | sft
+    use_torch_autocast: bool = False
+    use_bf16: bool = True
+    gradient_checkpointing: bool = False
+    ema_decay: float = 0.0
+    save_interval: int = 0
+    eval_interval: int = 0
+    noise_scheme: str = "logit_normal"
+    ce_loss_weight: float = 1.0             # bagel: weight of the text cross-entropy against the flow loss
+    mse_loss_weight: float = 1.0
+
+    def __post_init__(self):
+        if not 0 < self.timestep_fraction <= 1:
+            raise ConfigError("timestep_fraction must be in (0, 1]")
+        if self.train_method not in ("dpo", "sft"):
+            raise ConfigError("train_method must be dpo | sft")
+
+
+@dataclass
+class T2iPpoConfig(MappingMixin):
+    ppo_ratio_eps: float = 1e-4
+    ppo_clip_ratio_low: Optional[float] = None
+    ppo_clip_ratio_high: Optional[float] = None
+    adv_clip_min: float = -5.0
+    adv_clip_max: float = 5.0
+    grpo_advantage_epsilon: float = 1e-8
+    reward_weights: Dict[str, float] = field(default_factory=dict)
+
+
+@dataclass
+class T2iDpoSection(MappingMixin):
+    beta_dpo: float = 5000.0
+
+
+@dataclass
+class T2iConfig(MappingMixin):
+    model: T2iModelConfig = field(default_factory=T2iModelConfig)
+    training: T2iTrainingConfig = field(default_factory=T2iTrainingConfig)
+    ppo: T2iPpoConfig = field(default_factory=T2iPpoConfig)
+    dpo: T2iDpoSection = field(default_factory=T2iDpoSection)
+    optimizer: OptimizerConfig = field(default_factory=OptimizerConfig)
+    checkpoint: CheckpointConfig = field(default_factory=CheckpointConfig)
+    data: DataConfig = field(default_factory=DataConfig)
+    bt_rm: RewardConfig = field(default_factory=RewardConfig)
+    report: ReportConfig = field(default_factory=ReportConfig)
+    debug: DebugConfig = field(default_factory=DebugConfig)
+    task: Dict[str, Any] = field(default_factory=dict)

@@ -505,15 +505,17 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams
   q.stages = C::STAGES;
   q.a_early = 0;
   if constexpr (!A_MN && !B_MN && BN <= 128) {
-    if (p.transposed && p.group_mode == 0 && decode_smem_cap() > 0) {
-      // decode (swap-AB): A is the weight.  A shallower ring and the register-capped instantiation leave room for
-      // the CTA of the next kernel of the chain on the same SM, which then streams its own weights while this
-      // kernel drains (programmatic dependent launch)
-      int nst = (decode_smem_cap() - 1024 - 256 - (MAX_GROUPS + 1) * 4) / C::STAGE_BYTES;
-      if (nst < 3) nst = 3;
-      if (nst < C::STAGES) q.stages = nst;
+    if (p.transposed && p.group_mode == 0) {
+      // decode (swap-AB): A is the weight, which no earlier kernel of the chain writes: its first tiles are requested
+      // before the dependency wait.  With a shared-memory budget set, a shallower ring and the register-capped
+      // instantiation also leave room for the next kernel's CTA on the same SM.
       q.a_early = 1;
-      return launch_gemm_q<BN, A_MN, B_MN, 2>(tmA, tmB, q, grid, st);
+      if (decode_smem_cap() > 0) {
+        int nst = (decode_smem_cap() - 1024 - 256 - (MAX_GROUPS + 1) * 4) / C::STAGE_BYTES;
+        if (nst < 3) nst = 3;
+        if (nst < C::STAGES) q.stages = nst;
+        return launch_gemm_q<BN, A_MN, B_MN, 2>(tmA, tmB, q, grid, st);
+      }
     }
   }
   return launch_gemm_q<BN, A_MN, B_MN, 1>(tmA, tmB, q, grid, st);

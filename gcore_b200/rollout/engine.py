@@ -245,8 +245,9 @@ class InferEngine:
         self.mla_dim = (cfg.kv_lora_rank + cfg.qk_rope_head_dim) if getattr(cfg, "use_mla", False) else 0
         self.vocab_local = weights.head.shape[0]
         self.vocab_start = self.vocab_local * (dist.get_rank(tp_group) if (tp_group is not None and tp_size > 1) else 0)
-        # the library (eager) backend is captured too: its decode path is synchronisation-free on a GPU
-        self.use_graph = use_cuda_graph and self.device.type == "cuda"
+        # the library (eager) backend launches its decode ops one by one (its GPU path has no host synchronisation, so
+        # the launch queue stays ahead of the device)
+        self.use_graph = use_cuda_graph and self.device.type == "cuda" and not _lib.force_eager()
         self.ep_group = None  # set when experts are parallel: engines of the group then run their passes in lockstep
         if any(getattr(lw.moe, "ep_size", 1) > 1 for lw in weights.layers if lw.moe is not None):
             # expert-parallel dispatch sizes its exchanges on the host (and the peer-memory path numbers its epochs

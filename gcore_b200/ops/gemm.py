@@ -61,6 +61,17 @@ def _use_wide(M: int, N: int, K: int) -> bool:
     return eff_w * WIDE["gain"] > eff_g
 
 
+TWO_CTA = {"enabled": os.environ.get("GCORE_GEMM_2CTA", "1") != "0", "min_tiles": 37}
+
+
+def _use_two_cta(M: int, N: int, K: int) -> bool:
+    """The pair kernel works on 256 x 256 tiles over 74 SM pairs: problems with too few tiles to fill half of them
+    stay on the one-CTA kernels (which also split K)."""
+    if M < 256 or N < 256 or K < 128:
+        return False
+    return ((M + 255) // 256) * ((N + 255) // 256) >= TWO_CTA["min_tiles"]
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: torch.Tensor | None = None,
          out_dtype: torch.dtype | None = None, bias: torch.Tensor | None = None, bias_along_m: bool = False,
          alpha: float = 1.0, accumulate: bool = False, transposed: bool = False, bn: int | None = None,
@@ -102,6 +113,17 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
             out.zero_()
         return out
     lib = _lib.kernels()
+    if (TWO_CTA["enabled"] and bn is None and ksplit == 1 and not transposed and not bias_along_m
+            and (b_mn or not a_mn) and _use_two_cta(M, N, K) and out.dtype in (torch.bfloat16, torch.float32)
+            and hasattr(lib, "gk_gemm_2cta")):
+        # CTA pairs on 256 x 256 tiles (tcgen05.mma.cta_group::2): each SM stages half of the B tile
+        LAUNCHES["gemm"] += 1
+        rc = lib.gk_gemm_2cta(_lib.ptr(a), a.stride(0), a.shape[0], int(a_mn), _lib.ptr(b), b.stride(0), b.shape[0],
+                              int(b_mn), _lib.ptr(out), out.stride(0), int(out.dtype == torch.float32), int(accumulate),
+                              _lib.ptr(bias), int(bias is not None and bias.dtype == torch.float32), float(alpha),
+                              M, N, K, _lib.ptr(_lib.err_flag(a.device)), _lib.stream_ptr())
+        _lib.check(rc, "gk_gemm_2cta")
+        return out
     if (bn is None and ksplit == 1 and not transposed and not bias_along_m and _use_wide(M, N, K)
             and out.dtype in (torch.bfloat16, torch.float32) and hasattr(lib, "gk_gemm_wide")):
         LAUNCHES["gemm"] += 1

@@ -154,9 +154,12 @@ def cmd_gemm(argv=None):
     ap.add_argument("--k", "--K", type=int, default=3584)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--layout", default="fwd")
+    ap.add_argument("--two-cta", type=int, default=1, help="0: keep the one-CTA kernels (A/B comparison)")
     args = ap.parse_args(argv)
     from gcore_b200.ops import _lib
+    from gcore_b200.ops import gemm as gemm_mod
     from gcore_b200.ops.gemm import linear_dgrad, linear_forward, linear_wgrad
+    gemm_mod.TWO_CTA["enabled"] = bool(args.two_cta)
     T, N, K = args.tokens, args.n, args.k
     x = torch.randn(T, K, device="cuda").bfloat16()
     w = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()

@@ -497,3 +497,37 @@ def test_gemm_wide_tiles(M, N, K, a_mn, b_mn):
     _close(acc, 0.5 * ref + 2.0, rtol=1e-2, atol=1e-2 * max(1.0, K / 512) ** 0.5)
     # the dispatcher sends large well-quantised problems here and keeps the rest on the 128-row kernel
     assert G._use_wide(8192, 37888, 3584) and not G._use_wide(512, 4096, 4096)
+
+
+@pytest.mark.parametrize("M,N,K", [(2048, 2304, 512), (4096, 1024, 1088), (2000, 2100, 520), (8192, 4608, 3584)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
+def test_gemm_cta_pair_kernel(M, N, K, a_mn, b_mn):
+    """256 x 256 tiles on CTA pairs (tcgen05.mma.cta_group::2): forward / dgrad / wgrad layouts, ragged edges, bias,
+    fp32 accumulation into an existing buffer; bitwise repeatable."""
+    from gcore_b200.ops import gemm as G
+    if (a_mn and M % 8) or (b_mn and N % 8):
+        pytest.skip("MN-major operands need a 16-byte aligned leading dimension")
+    assert G.TWO_CTA["enabled"] and G._use_two_cta(M, N, K)
+    torch.manual_seed(3)
+    A, B = _rand(M, K, scale=0.5), _rand(N, K, scale=0.5)
+    a = A.t().contiguous() if a_mn else A
+    b = B.t().contiguous() if b_mn else B
+    ref = A.float() @ B.float().t()
+    before = G.LAUNCHES["gemm"]
+    out = G.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    assert G.LAUNCHES["gemm"] == before + 1
+    _close(out, ref, rtol=1e-2, atol=1e-2 * math.sqrt(K))
+    assert torch.equal(out, G.gemm(a, b, a_mn=a_mn, b_mn=b_mn))
+    bias = _rand(N)
+    C0 = torch.randn(M, N, device=DEV, dtype=torch.float32)
+    acc = C0.clone()
+    G.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=acc, bias=bias, alpha=0.5, accumulate=True)
+    _close(acc, C0 + 0.5 * ref + bias.float()[None], rtol=2e-3, atol=2e-3 * math.sqrt(K))
+    # the one-CTA kernels agree (same products, different tiling)
+    G.TWO_CTA["enabled"] = False
+    try:
+        one = G.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+    finally:
+        G.TWO_CTA["enabled"] = True
+    two = G.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+    _close(two, one, rtol=1e-4, atol=1e-3)

@@ -331,6 +331,8 @@ class PolicyConfig(MappingMixin):
     # vision-language policy: fields of ``models.vlm.VisionConfig`` (empty = text-only) and the placeholder token id
     vision_config: Dict[str, Any] = field(default_factory=dict)
     image_token_id: Optional[int] = None
+    # Qwen3-VL family (model_config.mrope_sections set): video_token_id, deepstack_layers, temporal_patch
+    vision_options: Dict[str, Any] = field(default_factory=dict)
     sampler_client: ClientConfig = field(default_factory=ClientConfig)
     bt_rm_client: ClientConfig = field(default_factory=ClientConfig)
     gen_rm_client: ClientConfig = field(default_factory=ClientConfig)

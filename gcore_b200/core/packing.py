@@ -31,7 +31,17 @@ class PackedBatch:
     fields: Dict[str, torch.Tensor] = field(default_factory=dict)  # extra per-token tensors on the log-prob axis
     pad_tokens: int = 0
     cp_ctx: Optional[object] = None  # parallel.cp.CPContext when the token axis is sharded over context-parallel ranks
-    vision: Optional[tuple] = None   # (patches [sum(h*w), patch_dim], [(h, w), ...]) for vision-language batches
+    # vision-language batches: (patches [sum(h*w), patch_dim], [(h, w), ...]), or with videos a dict of
+    # image_patches / image_grid / video_patches / video_grid
+    vision: Optional[object] = None
+
+    def _vision_to(self, kw):
+        v = self.vision
+        if v is None:
+            return None
+        if isinstance(v, dict):
+            return {k: (x.to(**kw) if isinstance(x, torch.Tensor) else x) for k, x in v.items()}
+        return (v[0].to(**kw), v[1])
 
     @property
     def num_seqs(self):
@@ -43,7 +53,7 @@ class PackedBatch:
                            self.max_seqlen, self.targets.to(**kw), self.loss_mask.to(**kw), self.seq_ids.to(**kw),
                            self.sample_index, {k: v.to(**kw) for k, v in self.fields.items()}, self.pad_tokens,
                            self.cp_ctx,
-                           None if self.vision is None else (self.vision[0].to(**kw), self.vision[1]))
+                           self._vision_to(kw))
 
 
 def response_mask(prompt_len: int, seq_len: int) -> torch.Tensor:
@@ -110,9 +120,16 @@ def pack_samples(samples: Sequence[Dict], indices: Sequence[int], per_token_keys
 
     vision = None
     imgs = [(samples[i]["pixel_patches"], samples[i]["image_grid"]) for i in indices if "pixel_patches" in samples[i]]
+    vids = [(samples[i]["video_patches"], samples[i]["video_grid"]) for i in indices if "video_patches" in samples[i]]
     if imgs:
         grids = [tuple(g) for _, gs in imgs for g in (gs if isinstance(gs[0], (list, tuple)) else [gs])]
         vision = (cat([torch.as_tensor(p, dtype=torch.float32) for p, _ in imgs]), grids)
+    if vids:
+        # videos ride in a dict next to the images (models that take videos read the dict form)
+        vgrids = [tuple(g) for _, gs in vids for g in (gs if isinstance(gs[0], (list, tuple)) else [gs])]
+        vision = {"image_patches": vision[0] if vision else None, "image_grid": vision[1] if vision else [],
+                  "video_patches": cat([torch.as_tensor(p, dtype=torch.float32) for p, _ in vids]),
+                  "video_grid": vgrids}
     return PackedBatch(cat(toks), cat(pos), torch.tensor(cu, dtype=torch.int32), max_len, cat(tgt), cat(mask),
                        cat(sid), list(indices), {k: cat(v) for k, v in extra.items()}, pad, None, vision)
 

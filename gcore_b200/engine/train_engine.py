@@ -123,9 +123,18 @@ class TrainingEngine:
         if self.vision_cfg is not None:
             from ..models.vlm import VLModel
             assert tp == 1 and pp == 1, "vision-language models run with TP = PP = 1"
-            m = VLModel(self.model_cfg, self.vision_cfg, self.image_token_id, device=self.device,
-                        recompute=recompute if recompute is not None else self.policy_cfg.recompute,
-                        value_head=value_head)
+            kw = dict(device=self.device, recompute=recompute if recompute is not None else self.policy_cfg.recompute,
+                      value_head=value_head)
+            if self.model_cfg.mrope_sections is not None:
+                # multi-axis rotary ids: the Qwen3-VL family (images + videos, deepstack features)
+                from ..models.qwen3_vl import Qwen3VLModel
+                vopt = dict(getattr(self.policy_cfg, "vision_options", None) or {})
+                m = Qwen3VLModel(self.model_cfg, self.vision_cfg, self.image_token_id,
+                                 video_token_id=vopt.get("video_token_id"),
+                                 deepstack_layers=tuple(vopt.get("deepstack_layers", (0,))),
+                                 temporal_patch=int(vopt.get("temporal_patch", 2)), **kw)
+            else:
+                m = VLModel(self.model_cfg, self.vision_cfg, self.image_token_id, **kw)
         else:
             m = GPTModel(self.model_cfg, tp_size=tp, ep_size=ep, sequence_parallel=d.sequence_parallel,
                          recompute=recompute if recompute is not None else self.policy_cfg.recompute,

@@ -4,7 +4,7 @@ of a HuggingFace ``config.json`` so real checkpoints and the random-init benchma
 from __future__ import annotations
 
 from dataclasses import dataclass, field, fields
-from typing import Any, Dict, List, Optional
+from typing import Tuple, Any, Dict, List, Optional
 
 
 @dataclass
@@ -55,6 +55,10 @@ class ModelConfig:
     v_head_dim: int = 0
     # vision tower stub for VLM families (patch embedding + merger feeding the decoder)
     vision: Dict[str, Any] = field(default_factory=dict)
+    # multi-axis rotary position ids (vision-language decoders): frequencies per (temporal, height, width) axis,
+    # summing to rotary_dim / 2; interleaved assignment (Qwen3-VL) or consecutive chunks (Qwen2-VL)
+    mrope_sections: Optional[Tuple[int, int, int]] = None
+    mrope_interleaved: bool = True
     dtype: str = "bfloat16"
     init_std: float = 0.02
     fp8_base_weights: bool = False  # frozen e4m3 base with 128x128 block scales

@@ -158,7 +158,7 @@ class _RopeQKInplace(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, qkv, pos, nrot_heads, theta, rot, interleaved):
-        ctx.save_for_backward(pos)
+        ctx.pos = pos   # position ids or (cos, sin) tables: never differentiated
         ctx.args = (nrot_heads, theta, rot, interleaved)
         fused.rope_inplace(qkv[:, :nrot_heads], pos, theta, rot, interleaved, False)
         ctx.mark_dirty(qkv)
@@ -166,7 +166,7 @@ class _RopeQKInplace(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, g):
-        (pos,) = ctx.saved_tensors
+        pos = ctx.pos
         n, theta, rot, interleaved = ctx.args
         g = g.contiguous() if not g.is_contiguous() else g
         fused.rope_inplace(g[:, :n], pos, theta, rot, interleaved, True)
@@ -464,7 +464,7 @@ class GPTModel(nn.Module):
         return self.vocab_local * (ps.get_tensor_model_parallel_rank() if self.tp_size > 1 else 0)
 
     def forward(self, input_ids=None, position_ids=None, cu_seqlens=None, max_seqlen=None, hidden_in=None,
-                inputs_embeds=None, chunk=None):
+                inputs_embeds=None, chunk=None, deepstack=None):
         """``input_ids`` [T] packed tokens (first stage) or ``hidden_in`` (later pipeline stages, sequence-parallel
         shard).  Returns ``(hidden, aux_loss)``: on the last stage ``hidden`` is the final-normed ``[T, H]`` (gathered
         over SP), otherwise the stage output to send downstream.  ``chunk`` selects one model chunk of an interleaved
@@ -487,7 +487,14 @@ class GPTModel(nn.Module):
             x = hidden_in
         residual = None
         aux_total = None
-        pos32 = position_ids.to(torch.int32) if position_ids.dtype != torch.int32 else position_ids
+        if position_ids.dim() == 2:
+            # [T, 3] (temporal, height, width) ids of a vision-language stream: rotary tables replace the ids
+            cfg = self.cfg
+            assert cfg.mrope_sections is not None, "multi-axis position ids need model_config.mrope_sections"
+            pos32 = fused.mrope_tables(position_ids, cfg.rope_theta, cfg.rotary_dim or cfg.head_dim,
+                                       tuple(cfg.mrope_sections), cfg.mrope_interleaved)
+        else:
+            pos32 = position_ids.to(torch.int32) if position_ids.dtype != torch.int32 else position_ids
         n_ckpt = getattr(self, "recompute_num_layers", None)
         for li in range(l0, l1):
             layer = self.decoder.layers[li]
@@ -499,6 +506,10 @@ class GPTModel(nn.Module):
                 x, residual, aux = layer(x, residual, pos32, cu_seqlens, max_seqlen, tp_group, sp)
             if aux is not None:
                 aux_total = aux if aux_total is None else aux_total + aux
+            if deepstack is not None and li < len(deepstack[1]):
+                # intermediate vision-tower features join the hidden state of the visual tokens behind each of the
+                # first decoder layers (Qwen3-VL "deepstack")
+                x = x.index_add(0, deepstack[0], deepstack[1][li].to(x.dtype))
         if not last:
             # carry the un-added residual forward as one tensor
             return (x + residual if residual is not None else x), aux_total

@@ -215,6 +215,30 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const int* __restrict
   }
 }
 
+// Same rotation with the angles given as tables cos / sin [T, rot / 2] (multi-axis rotary position ids of
+// vision-language models: every frequency takes its angle from the temporal, height or width index of the token).
+__global__ void rope_table_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ cs,
+                                  const float* __restrict__ sn, int T, int nheads, int D, int rot, long long stride_t,
+                                  float sign, int interleaved) {
+  const int half = rot >> 1;
+  const long long total = static_cast<long long>(T) * nheads * half;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int i = static_cast<int>(idx % half);
+    const long long th = idx / half;
+    const int h = static_cast<int>(th % nheads);
+    const int t = static_cast<int>(th / nheads);
+    const float c = cs[static_cast<long long>(t) * half + i];
+    const float s = sn[static_cast<long long>(t) * half + i] * sign;
+    __nv_bfloat16* p = x + t * stride_t + static_cast<long long>(h) * D;
+    const int i0 = interleaved ? 2 * i : i;
+    const int i1 = interleaved ? 2 * i + 1 : i + half;
+    const float a = __bfloat162float(p[i0]), b = __bfloat162float(p[i1]);
+    p[i0] = __float2bfloat16(a * c - b * s);
+    p[i1] = __float2bfloat16(b * c + a * s);
+  }
+}
+
 // ------------------------------------------------------------------------------------------ SwiGLU
 // in [T, 2F] = [gate | up]; out [T, F] = silu(gate) * up
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, long long T,
@@ -368,6 +392,16 @@ GK_EXPORT int gk_rope(void* x, const int* pos, int T, int nheads, int D, int rot
   rope_kernel<<<grid_for(total, 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<__nv_bfloat16*>(x), pos, T, nheads, D, rot, stride_t, theta, backward ? -1.f : 1.f,
       interleaved);
+  return launch_status();
+}
+
+GK_EXPORT int gk_rope_table(void* x, const float* cs, const float* sn, int T, int nheads, int D, int rot,
+                            long long stride_t, int backward, int interleaved, void* stream) {
+  if (rot % 2 || rot > D) return -1;
+  const long long total = static_cast<long long>(T) * nheads * (rot / 2);
+  if (total == 0) return 0;
+  rope_table_kernel<<<grid_for(total, 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<__nv_bfloat16*>(x), cs, sn, T, nheads, D, rot, stride_t, backward ? -1.f : 1.f, interleaved);
   return launch_status();
 }
 

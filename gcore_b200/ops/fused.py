@@ -76,14 +76,41 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-6, residual: torch
 
 
 # ------------------------------------------------------------------------------------------------ RoPE
+def mrope_tables(pos3: torch.Tensor, theta: float, rot: int, sections, interleaved_sections: bool = True):
+    """Multi-axis rotary tables.  ``pos3`` [T, 3] = (temporal, height, width) index of every token; frequency ``i``
+    of the ``rot / 2`` frequencies takes its angle from one of the three axes: chunked (``sections = (t, h, w)``
+    consecutive frequencies per axis, Qwen2-VL) or interleaved (frequency ``i`` uses axis ``i % 3`` while that axis
+    still has budget, the rest temporal, Qwen3-VL; gpatch_v4/extended_model/qwen3_vl.py).  Returns ``(cos, sin)``
+    fp32 ``[T, rot / 2]``, accepted wherever a rotary op takes position ids."""
+    half = rot // 2
+    assert sum(sections) == half, f"mrope sections {sections} must sum to {half}"
+    inv = theta ** (-torch.arange(0, half, device=pos3.device, dtype=torch.float32) * 2.0 / rot)
+    axis = torch.zeros(half, dtype=torch.long, device=pos3.device)
+    if interleaved_sections:
+        idx = torch.arange(half, device=pos3.device)
+        for a in (1, 2):
+            axis[(idx % 3 == a) & (idx < 3 * sections[a])] = a
+    else:
+        o = 0
+        for a, n in enumerate(sections):
+            axis[o:o + n] = a
+            o += n
+    ang = pos3.float()[:, axis] * inv[None, :]
+    return ang.cos().contiguous(), ang.sin().contiguous()
+
+
 def rope_ref(x, pos, theta, rot=None, interleaved=False, backward=False):
-    """x: [T, nheads, D]; rotate-half pairing (i, i + rot/2) unless ``interleaved``."""
+    """x: [T, nheads, D]; rotate-half pairing (i, i + rot/2) unless ``interleaved``.  ``pos``: position ids [T] or a
+    ``(cos, sin)`` pair of tables [T, rot / 2] (see ``mrope_tables``)."""
     D = x.shape[-1]
     rot = rot or D
     half = rot // 2
-    inv = theta ** (-torch.arange(0, half, device=x.device, dtype=torch.float32) * 2.0 / rot)
-    ang = pos.float()[:, None] * inv[None, :]
-    c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    if isinstance(pos, tuple):
+        c, s = pos[0][:, None, :], pos[1][:, None, :]
+    else:
+        inv = theta ** (-torch.arange(0, half, device=x.device, dtype=torch.float32) * 2.0 / rot)
+        ang = pos.float()[:, None] * inv[None, :]
+        c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]
     if backward:
         s = -s
     xf = x.float()
@@ -103,6 +130,12 @@ def rope_inplace(x: torch.Tensor, pos: torch.Tensor, theta: float, rot: int | No
     T, nh, D = x.shape
     rot = rot or D
     if x.dtype == torch.bfloat16 and _lib.use_native(x) and x.stride(2) == 1 and x.stride(1) == D:
+        if isinstance(pos, tuple):
+            LAUNCHES["elementwise"] += 1
+            _lib.check(_lib.kernels().gk_rope_table(_lib.ptr(x), _lib.ptr(pos[0]), _lib.ptr(pos[1]), T, nh, D, rot,
+                                                    x.stride(0), int(backward), int(interleaved), _lib.stream_ptr()),
+                       "rope_table")
+            return x
         p32 = pos if pos.dtype == torch.int32 else pos.to(torch.int32)
         LAUNCHES["elementwise"] += 1
         _lib.check(_lib.kernels().gk_rope(_lib.ptr(x), _lib.ptr(p32), T, nh, D, rot, x.stride(0), float(theta),
@@ -115,13 +148,13 @@ def rope_inplace(x: torch.Tensor, pos: torch.Tensor, theta: float, rot: int | No
 class _RopeFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, pos, theta, rot, interleaved):
-        ctx.save_for_backward(pos)
+        ctx.pos = pos   # position ids or (cos, sin) tables: never differentiated
         ctx.args = (theta, rot, interleaved)
         return rope_inplace(x.clone(), pos, theta, rot, interleaved, False)
 
     @staticmethod
     def backward(ctx, g):
-        (pos,) = ctx.saved_tensors
+        pos = ctx.pos
         theta, rot, interleaved = ctx.args
         return rope_inplace(g.clone(), pos, theta, rot, interleaved, True), None, None, None, None
 

@@ -161,3 +161,89 @@ def test_freeze_flags_select_tower_projector_decoder_router_and_shared_experts()
     names, f = frozen(freeze_moe_router=True, freeze_moe_shared_experts=True)
     assert f == {n for n in names if ".router." in n or ".shared_experts." in n} and \
         any(".router." in n for n in f) and any(".shared_experts." in n for n in f)
+
+
+def test_qwen3_vl_rope_index_video_frames_and_deepstack():
+    """Multi-axis position ids (text / image / video blocks), interleaved frequency assignment, per-frame attention
+    over video patch volumes and intermediate vision features joining the first decoder layers."""
+    from gcore_b200.models.config import ModelConfig
+    from gcore_b200.models.qwen3_vl import Qwen3VLModel, get_rope_index
+    from gcore_b200.models.vlm import VisionConfig
+    from gcore_b200.ops.fused import mrope_tables, rope_ref
+    IMG, VID = 500, 501
+    # text(2) image 4x4 -> 4 tokens, text(1), video (t=2, 4x2) -> 2 * 2 * 1 = 4 tokens, text(2)
+    toks = [5, 6] + [IMG] * 4 + [7] + [VID] * 4 + [8, 9]
+    pos, delta = get_rope_index(toks, [(1, 4, 4)], IMG, VID, 2, [(2, 4, 2)])
+    assert pos[:2].tolist() == [[0, 0, 0], [1, 1, 1]]
+    assert pos[2:6].tolist() == [[2, 2, 2], [2, 2, 3], [2, 3, 2], [2, 3, 3]]          # one frame, 2 x 2 merged grid
+    assert pos[6].tolist() == [4, 4, 4]                                                # text resumes after max + 1
+    assert pos[7:11].tolist() == [[5, 5, 5], [5, 6, 5], [6, 5, 5], [6, 6, 5]]          # two frames, 2 x 1 grid each
+    assert pos[11].tolist() == [7, 7, 7] and delta == 9 - len(toks)
+    # text-only streams rotate exactly like plain 1-D rotary embedding
+    p1 = torch.arange(6)
+    x = torch.randn(6, 2, 16)
+    tab = mrope_tables(p1[:, None].expand(6, 3), 10000.0, 16, (4, 2, 2), True)
+    assert torch.allclose(rope_ref(x, tab, 10000.0, 16), rope_ref(x, p1, 10000.0, 16), atol=1e-6)
+    # interleaved vs chunked assignment differ once the axes differ
+    p3 = torch.tensor([[3, 1, 2]])
+    ci, _ = mrope_tables(p3, 10000.0, 16, (4, 2, 2), True)
+    cc, _ = mrope_tables(p3, 10000.0, 16, (4, 2, 2), False)
+    inv = 10000.0 ** (-torch.arange(8) * 2.0 / 16)
+    assert torch.allclose(ci[0], torch.cos(torch.tensor([3., 1., 2., 3., 1., 2., 3., 3.]) * inv), atol=1e-6)
+    assert torch.allclose(cc[0], torch.cos(torch.tensor([3., 3., 3., 3., 1., 1., 2., 2.]) * inv), atol=1e-6)
+
+    mcfg = ModelConfig(arch="qwen3", num_layers=2, hidden_size=64, num_attention_heads=4, num_kv_heads=2, head_dim=16,
+                       ffn_hidden_size=128, vocab_size=512, dtype="float32", qk_layernorm=True, mrope_sections=(4, 2, 2))
+    vc = VisionConfig(patch_size=2, hidden_size=32, num_layers=2, num_heads=2, ffn_hidden_size=64, max_grid=8)
+    torch.manual_seed(0)
+    m = Qwen3VLModel(mcfg, vc, IMG, VID, deepstack_layers=(0,), temporal_patch=2, recompute="none")
+    m.reset_parameters(3)
+    ids = torch.tensor(toks + [11, 12, 13])          # a second, text-only sequence in the same packed batch
+    cu = torch.tensor([0, len(toks), len(toks) + 3], dtype=torch.int32)
+    vision = {"image_patches": torch.randn(16, vc.patch_dim), "image_grid": [(4, 4)],
+              "video_patches": torch.randn(16, vc.patch_dim * 2), "video_grid": [(2, 4, 2)]}
+    h, _ = m(ids, None, cu, len(toks), vision=vision)
+    assert h.shape == (ids.numel(), 64) and torch.isfinite(h).all()
+    h.sum().backward()
+    assert m.vision.deep_fc2[0].weight.grad.abs().sum() > 0 and m.vision.video_embed.weight.grad.abs().sum() > 0
+    # the text-only sequence is unaffected by the visual sequence in front of it
+    h2, _ = m(ids[len(toks):], None, torch.tensor([0, 3], dtype=torch.int32), 3)
+    assert torch.allclose(h[len(toks):], h2, atol=1e-5)
+
+
+def test_qwen3_vl_trains_through_the_engine_with_images_and_videos():
+    from gcore_b200.configs.config import OptimizerConfig, PolicyConfig, TrainingConfig
+    from gcore_b200.engine.train_engine import TrainingEngine
+    from gcore_b200.models.config import ModelConfig
+    from gcore_b200.models.qwen3_vl import Qwen3VLModel
+    IMG, VID = 500, 501
+    mcfg = ModelConfig(arch="qwen3", num_layers=2, hidden_size=64, num_attention_heads=4, num_kv_heads=2, head_dim=16,
+                       ffn_hidden_size=128, vocab_size=512, dtype="float32", qk_layernorm=True, mrope_sections=(4, 2, 2))
+    pc = PolicyConfig(recompute="none", without_ref=True, image_token_id=IMG,
+                      vision_config=dict(patch_size=2, hidden_size=32, num_layers=2, num_heads=2, ffn_hidden_size=64,
+                                         max_grid=8),
+                      vision_options={"video_token_id": VID, "deepstack_layers": [0, 1]})
+    e = TrainingEngine(pc, OptimizerConfig(lr=2e-3, lr_decay_style="constant", weight_decay=0.0),
+                       TrainingConfig(train_mbs=2, train_gbs=4), model_cfg=mcfg)
+    e.setup_model_and_get_optimizer(seed=5)
+    assert isinstance(e.model, Qwen3VLModel)
+    g = torch.Generator().manual_seed(1)
+
+    def sample(kind):
+        if kind == "image":
+            toks = [3, 4] + [IMG] * 4 + [9, 10, 11, 12]
+            extra = {"pixel_patches": torch.randn(16, 12, generator=g), "image_grid": (4, 4)}
+        elif kind == "video":
+            toks = [3] + [VID] * 4 + [9, 10, 11]
+            extra = {"video_patches": torch.randn(16, 24, generator=g), "video_grid": (2, 4, 2)}
+        else:
+            toks, extra = [3, 4, 5, 6, 7, 8], {}
+        m = torch.zeros(len(toks))
+        m[-4:-1] = 1
+        return dict(tokens=torch.tensor(toks), loss_mask=m, **extra)
+
+    batch = [sample("image"), sample("video"), sample("text"), sample("image")]
+    losses = [e.finetune_step(batch)["lm_loss"] for _ in range(6)]
+    assert losses[-1] < losses[0] - 0.2, losses
+    lp = e.compute_log_probs(batch)
+    assert all(torch.isfinite(s["logprobs"]).all() for s in lp)

@@ -168,6 +168,8 @@ class ReportConfig(MappingMixin):
     log_dir: str = "./logs"
     log_interval: int = 1
     use_verl_metric_names: bool = False
+    debug_log_shards: bool = False      # one DEBUG log file per process under <task dir>/debug
+    redirect_engine_log: bool = False   # stdout / stderr of the rollout phase go to <task dir>/infer_engine_log
     profile: ProfileConfig = field(default_factory=ProfileConfig)
 
 

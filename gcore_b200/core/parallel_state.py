@@ -163,6 +163,48 @@ def initialize_model_parallel(tp: int = 1, pp: int = 1, cp: int = 1, ep: int = 1
     return st
 
 
+def offload_process_groups() -> int:
+    """Destroys the model-parallel communicators of the default backend (their device buffers return to the
+    allocator while the rollout engine owns the GPU; ``policy.offload_process_group``,
+    gpatch_v4/utils/reloadable_process_group.py:116-287).  Collective.  The gloo side groups and the default group
+    stay.  Returns the number of groups destroyed."""
+    st = _STATE
+    assert st.initialized
+    n = 0
+    for name, g in list(st.groups.items()):
+        if name == "world" or g is None:
+            continue
+        same = st.gloo_groups.get(name) is g
+        dist.destroy_process_group(g)
+        st.groups[name] = None
+        if same:
+            st.gloo_groups[name] = None
+        n += 1
+    st.offloaded = True
+    return n
+
+
+def reload_process_groups(timeout_minutes: int = 30) -> int:
+    """Re-creates what ``offload_process_groups`` destroyed: every rank walks the same group plan in the same order
+    (``dist.new_group`` is collective over the default group)."""
+    st = _STATE
+    if not getattr(st, "offloaded", False):
+        return 0
+    fam, _, _ = plan_groups(st.world_size, st.tp, st.pp, st.cp, st.ep, st.etp)
+    timeout = datetime.timedelta(minutes=timeout_minutes)
+    n = 0
+    for name, lists in fam.items():
+        for ranks in lists:
+            g = dist.new_group(ranks, timeout=timeout) if len(ranks) > 1 else None
+            if st.rank in ranks and g is not None:
+                st.groups[name] = g
+                if st.gloo_groups.get(name) is None:
+                    st.gloo_groups[name] = g
+                n += 1
+    st.offloaded = False
+    return n
+
+
 def destroy_model_parallel():
     global _STATE
     _STATE = ParallelState()

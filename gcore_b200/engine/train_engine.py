@@ -810,6 +810,26 @@ class TrainingEngine:
         for sw in getattr(self, "_model_swaps", None) or []:
             sw.onload()
 
+    def offload_process_groups(self):
+        """Releases the model-parallel communicators for the duration of a rollout (not with peer-memory buffers: those
+        are rendezvoused over their group once and stay mapped on the peers)."""
+        assert not any(b.peer for b in (self.ddp.buffers if self.ddp is not None else [])), \
+            "communicators that back peer-memory buffers cannot be released: set GCORE_FUSED_DP=0"
+        return ps.offload_process_groups()
+
+    def reload_process_groups(self):
+        n = ps.reload_process_groups(self.policy_cfg.dist_config.torch_dist_timeout_minutes)
+        if n and self.ddp is not None:
+            dense = ps.get_data_parallel_group(with_context_parallel=True)
+            expert = ps.get_expert_data_parallel_group()
+            for buf in self.ddp.buffers:   # reduction domains fetch their new communicators
+                buf.group = expert if any(getattr(p, "is_expert", False) for p in buf.params) else dense
+        if self._dcp is not None:
+            from ..parallel.dynamic_cp import build_block_groups
+            self._dcp = {"pool": ps.get_data_parallel_group(with_context_parallel=True),
+                         "groups": build_block_groups(ps.get_data_parallel_group(with_context_parallel=True))}
+        return n
+
     def offload_optimizer(self):
         if self.optimizer is not None:
             self.optimizer.offload()

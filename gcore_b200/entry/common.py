@@ -35,7 +35,8 @@ def init_runtime(config):
         ps.apply_deterministic_mode()
     ps.set_seed(config.training.seed)
     rank = dist.get_rank() if dist.is_initialized() else 0
-    setup_logging(config.report.log_dir, config.report.run_name or "run", role="train", rank=rank)
+    setup_logging(config.report.log_dir, config.report.run_name or "run", role="train", rank=rank,
+                  debug_shards=config.report.debug_log_shards)
     return rank
 
 

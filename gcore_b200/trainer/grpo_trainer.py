@@ -140,6 +140,10 @@ class GrpoTrainer:
         parameters for this call (evaluation passes its own temperature / length)."""
         t = self.cfg.training
         n = int(n or t.sampling_repeat_n)
+        release_pg = (self.cfg.policy.offload_process_group and dist.is_initialized() and ps.get_state().initialized
+                      and self.engine.tp == 1 and self.engine.ep_group is None)
+        if release_pg:   # the trainer's communicators hold device memory the KV cache can use
+            self.policy.offload_process_groups()
         self.engine.wake_up(("kv_cache",))
         sp = SamplingParams(**{**self.sampling.__dict__, **(sampling or {}),
                                "seed": self.sampling.seed + self.ppo_step * 1000003})
@@ -160,8 +164,12 @@ class GrpoTrainer:
                     patches = torch.as_tensor(im["pixel_patches"], dtype=torch.float32).to(self.policy.device)
                     embeds.append(model.vision(patches.to(next(model.vision.parameters()).dtype), grids))
             vl_kw = dict(image_embeds=embeds, image_token_id=model.image_token_id)
-        reqs = self.engine.generate(prompts, sp, n=n, **vl_kw)
+        from ..utils.logging_utils import redirect_engine_output
+        with redirect_engine_output(self.ppo_step, enabled=bool(getattr(self.cfg.report, "redirect_engine_log", False))):
+            reqs = self.engine.generate(prompts, sp, n=n, **vl_kw)
         self.engine.sleep(("kv_cache", "weights") if self.release_rollout_weights else ("kv_cache",))
+        if release_pg:
+            self.policy.reload_process_groups()
         samples = []
         dp_rank = ps.get_data_parallel_rank()
         for k, r in enumerate(reqs):

@@ -90,3 +90,15 @@ def test_grpo_update_runs_on_balanced_token_counts(tmp_path):
     assert abs(r0["before"] - r1["before"]) > abs(r0["after"] - r1["after"]), (r0, r1)
     assert r0["before"] + r1["before"] == r0["after"] + r1["after"]
     assert r0["grad_norm"] == r1["grad_norm"] and r0["grad_norm"] > 0
+
+
+def test_training_continues_after_process_groups_are_offloaded_and_reloaded(tmp_path):
+    import parallel_worker as pw
+    from gcore_b200.models.config import get_preset
+    out = tmp_path / "pg.json"
+    _spawn("pg_offload", out, port="29575")
+    got = json.load(open(out))["losses"]
+    e = pw.engine(get_preset("tiny_llama", dtype="float32", qkv_bias=True), 1)
+    ref = [e.finetune_step(pw.samples(8, 230 + s))["lm_loss"] for s in range(3)]
+    for a, b in zip(ref, got):
+        assert abs(a - b) < 5e-4, (ref, got)

@@ -1,5 +1,5 @@
 """gloo worker for the parallelism parity tests: mode = tp | ep | ep_rollout | ep_grpo | cp | pp | vpp | fsdp |
-ep_dynmbs | aux_dp | tp_topk | nodistopt | dyncp | dp_grpo_balance."""
+ep_dynmbs | aux_dp | tp_topk | nodistopt | dyncp | dp_grpo_balance | pg_offload."""
 import json
 import os
 import sys
@@ -245,6 +245,20 @@ def main():
         allres = [None, None]
         dist.all_gather_object(allres, res)
         res = {"ranks": allres}
+    elif mode == "pg_offload":
+        # data-parallel SFT steps with the communicators destroyed and re-created in between (what a rollout phase
+        # does under policy.offload_process_group): the run equals one without the cycle
+        ps.initialize_model_parallel(tp=1)
+        mcfg = get_preset("tiny_llama", dtype="float32", qkv_bias=True)
+        e = engine(mcfg, 1)
+        losses = []
+        for s_ in range(3):
+            losses.append(e.finetune_step(samples(8, 230 + s_)[rank::world])["lm_loss"])
+            if s_ == 0:
+                n = e.offload_process_groups()
+                assert n >= 1 and ps.get_data_parallel_group() is None
+                assert e.reload_process_groups() >= 1 and ps.get_data_parallel_group() is not None
+        res = {"losses": losses}
     elif mode == "nodistopt":
         ps.initialize_model_parallel(tp=1)
         mcfg = get_preset("tiny_llama", dtype="float32", qkv_bias=True)

@@ -120,6 +120,11 @@ def _declare_kernels(lib: ctypes.CDLL):
     P, I, L, F = c_void_p, c_int, c_ll, c_float
     d("gk_gemm_bf16", [P, L, L, I, P, L, L, I, P, L, I, I, I, P, I, I, F, I, I, I, I, I, I, I, P, I, L, I, P, P, P, P])
     d("gk_gemm_wide", [P, L, L, I, P, L, L, I, P, L, I, I, P, I, F, I, I, I, P, P])
+    d("gk_dsv4_indexer_fwd", [P, P, P, P, P, P, I, I, I, I, F, P])
+    d("gk_dsv4_indexer_bwd", [P, P, P, P, P, P, P, P, I, I, I, I, I, F, P])
+    d("gk_dsv4_sparse_mqa_fwd", [P, P, P, P, P, P, I, I, I, I, I, F, P])
+    d("gk_dsv4_sparse_mqa_bwd", [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, P])
+    d("gk_hadamard", [P, P, L, I, P])
     d("gk_rope_table", [P, P, P, I, I, I, I, L, I, I, P])
     d("gk_gemm_2cta", [P, L, L, I, P, L, L, I, P, L, I, I, P, I, F, I, I, I, P, P])
     d("gk_gemm_set_decode_smem_cap", [I], None)

@@ -531,3 +531,86 @@ def test_gemm_cta_pair_kernel(M, N, K, a_mn, b_mn):
         G.TWO_CTA["enabled"] = True
     two = G.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
     _close(two, one, rtol=1e-4, atol=1e-3)
+
+
+def test_dsv4_sparse_mqa_and_indexer_kernels():
+    """Gather attention (shared key / value rows, sinks, -1 entries, rows without any entry), its backward, the
+    indexer scores with per-row bounds and the gradient through selected entries."""
+    from gcore_b200.ops import dsv4 as K4
+    torch.manual_seed(5)
+    S, T, H, D, K = 200, 333, 6, 128, 40
+    q = _rand(S, H, D, scale=0.5).requires_grad_(True)
+    kv = _rand(T, D, scale=0.5).requires_grad_(True)
+    sinks = torch.randn(H, device=DEV).requires_grad_(True)
+    idx = torch.randint(0, T, (S, K), device=DEV, dtype=torch.int32)
+    idx[torch.rand(S, K, device=DEV) < 0.3] = -1
+    idx[7] = -1
+    out = K4.sparse_mqa(q, kv, sinks, idx, D ** -0.5)
+    do = _rand(S, H, D)
+    out.backward(do)
+    qr, kr, sr = (t.detach().float().requires_grad_(True) for t in (q, kv, sinks))
+    ref, _ = K4.sparse_mqa_ref(qr, kr, sr, idx, D ** -0.5)
+    ref.backward(do.float())
+    _close(out, ref, rtol=2e-2, atol=1e-2)
+    _close(q.grad, qr.grad, rtol=3e-2, atol=2e-2)
+    _close(kv.grad, kr.grad, rtol=3e-2, atol=3e-2)
+    _close(sinks.grad, sr.grad, rtol=3e-2, atol=3e-2)
+    assert (out[7] == 0).all()
+
+    Hi, Di = 8, 64
+    qi, ki = _rand(S, Hi, Di, scale=0.5), _rand(T, Di, scale=0.5)
+    w = torch.rand(S, Hi, device=DEV)
+    ks = torch.randint(0, T // 2, (S,), device=DEV, dtype=torch.int32)
+    ke = ks + torch.randint(0, T // 2, (S,), device=DEV, dtype=torch.int32)
+    sc = K4.indexer_scores(qi, ki, w, ks, ke, Di ** -0.5)
+    rf = K4.indexer_scores_ref(qi, ki, w, ks, ke, Di ** -0.5)
+    assert torch.equal(torch.isinf(sc), torch.isinf(rf))
+    fin = torch.isfinite(rf)
+    _close(sc[fin], rf[fin], rtol=1e-2, atol=1e-2)
+    sel_idx = torch.randint(-1, T, (S, 12), device=DEV, dtype=torch.int32)
+    qg, kg, wg = qi.clone().requires_grad_(True), ki.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    sel = K4.indexer_selected_scores(qg, kg, wg, sel_idx, Di ** -0.5)
+    gs = torch.randn_like(sel)
+    sel.backward(gs)
+    q2, k2, w2 = (t.detach().float().requires_grad_(True) for t in (qi, ki, w))
+    K4._selected_ref(q2, k2, w2, sel_idx, Di ** -0.5).backward(gs)
+    _close(qg.grad, q2.grad, rtol=3e-2, atol=2e-2)
+    _close(kg.grad, k2.grad, rtol=3e-2, atol=3e-2)
+    _close(wg.grad, w2.grad, rtol=3e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("n", [16, 128, 512, 2048])
+def test_hadamard_rotation(n):
+    from gcore_b200.ops import dsv4 as K4
+    torch.manual_seed(6)
+    x = _rand(37, 3, n)
+    y = K4.rotate_activation(x)
+    _close(y, K4.hadamard_ref(x.float()), rtol=1e-2, atol=1e-2)
+    _close(K4.rotate_activation(y), x, rtol=2e-2, atol=2e-2)
+
+
+def test_dsv4_model_step_on_gpu():
+    from gcore_b200.models.deepseek_v4 import DSV4Config, DeepseekV4Model, causal_lm_loss
+    torch.manual_seed(0)
+    cfg = DSV4Config(dtype="bfloat16", head_dim=64, index_head_dim=32)
+    m = DeepseekV4Model(cfg, device=DEV)
+    data = torch.randint(0, 64, (160,), device=DEV)
+    from gcore_b200.ops import dsv4 as K4
+    before = K4.LAUNCHES["dsv4"]
+    loss = causal_lm_loss(m, data, [0, 64, 160])
+    loss.backward()
+    assert K4.LAUNCHES["dsv4"] > before and torch.isfinite(loss)
+    assert m.layers[1].self_attn.compressor.compress.kv_proj.weight.grad.abs().sum() > 0
+
+
+def test_rope_table_kernel_matches_reference():
+    from gcore_b200.ops import fused
+    torch.manual_seed(7)
+    T, Hh, D = 300, 5, 128
+    x = _rand(T, Hh, D)
+    pos3 = torch.randint(0, 500, (T, 3), device=DEV)
+    tab = fused.mrope_tables(pos3, 1e6, D, (24, 20, 20), True)
+    y = fused.rope_inplace(x.clone(), tab, 1e6, D, False, False)
+    _close(y, fused.rope_ref(x.float(), tab, 1e6, D), rtol=1e-2, atol=1e-2)
+    back = fused.rope_inplace(y.clone(), tab, 1e6, D, False, True)
+    _close(back, x, rtol=2e-2, atol=2e-2)

@@ -52,6 +52,9 @@ def kernels() -> ctypes.CDLL:
                 "to eager PyTorch)")
         lib = ctypes.CDLL(str(path))
         _declare_kernels(lib)
+        st2 = os.environ.get("GCORE_2CTA_STAGES")
+        if st2 is not None and hasattr(lib, "gk_gemm_2cta_set_stages"):
+            lib.gk_gemm_2cta_set_stages(int(st2))
         cap = os.environ.get("GCORE_DECODE_SMEM_KB")   # shared-memory budget of decode GEMM CTAs (0 = full ring)
         if cap is not None and hasattr(lib, "gk_gemm_set_decode_smem_cap"):
             lib.gk_gemm_set_decode_smem_cap(int(cap) * 1024)

@@ -34,8 +34,12 @@ constexpr int TM = 256, TN = 256;
 constexpr int BK = 64, UMMA_K = 16;
 constexpr int THREADS = 192;
 constexpr int A_BYTES = BMH * BK * 2, B_BYTES = BNH * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int STAGES = 6;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int MAX_STAGES = 7;
+constexpr int SMEM_BYTES = MAX_STAGES * STAGE_BYTES + 1024 + 256;
+inline int& stages_setting() {
+  static int n = 6;
+  return n;
+}
 constexpr int TMEM_COLS = 512;  // two 256-column accumulators
 
 struct P2 {
@@ -47,6 +51,7 @@ struct P2 {
   int bias_fp32;
   float alpha;
   int* err;
+  int stages;
 };
 
 __device__ __forceinline__ uint32_t cta_rank() {
@@ -157,9 +162,10 @@ __global__ void __launch_bounds__(THREADS, 1)
 gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, P2 p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int STAGES = p.stages;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
-  uint64_t* empty = full + STAGES;
-  uint64_t* tfull = empty + STAGES;
+  uint64_t* empty = full + MAX_STAGES;
+  uint64_t* tfull = empty + MAX_STAGES;
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tempty + 2);
 
@@ -318,7 +324,9 @@ int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const P2& p, cudaStr
   auto* fn = gemm_2cta_kernel<A_MN, B_MN>;
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(THREADS, 1, 1);
-  cfg.dynamicSmemBytes = SMEM_BYTES;
+  P2 q = p;
+  q.stages = stages_setting() < 2 ? 2 : (stages_setting() > MAX_STAGES ? MAX_STAGES : stages_setting());
+  cfg.dynamicSmemBytes = q.stages * STAGE_BYTES + 1024 + 256;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -331,17 +339,19 @@ int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const P2& p, cudaStr
     if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
       return static_cast<int>(cudaGetLastError());
     cfg.gridDim = dim3(2 * (gk::sm_count() / 2), 1, 1);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
     int n = 0;
     if (cudaOccupancyMaxActiveClusters(&n, fn, &cfg) != cudaSuccess || n < 1) {
       cudaGetLastError();
       n = gk::sm_count() / 2 - 2;
     }
     max_clusters = n;
+    cfg.dynamicSmemBytes = q.stages * STAGE_BYTES + 1024 + 256;
   }
   const long long tiles = static_cast<long long>((p.M + TM - 1) / TM) * ((p.N + TN - 1) / TN);
   const int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
   cfg.gridDim = dim3(2 * clusters, 1, 1);
-  if (cudaLaunchKernelEx(&cfg, fn, tmA, tmB, p) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, fn, tmA, tmB, q) != cudaSuccess) {
     const int e = gk::launch_status();
     return e ? e : -7;
   }
@@ -349,6 +359,9 @@ int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const P2& p, cudaStr
 }
 
 }  // namespace gk2
+
+// Shared-memory ring depth of the pair kernel (2..7 stages of 32 KB per CTA).
+GK_EXPORT void gk_gemm_2cta_set_stages(int n) { gk2::stages_setting() = n; }
 
 // C[M,N] (ldc) = alpha * A . B^T (+ bias[N]) (+ C when accumulate); see the header comment.  a_rows / b_rows are the
 // outer extents of the operand tensors as stored.  Returns 0, a negative argument error or a positive cudaError_t.

@@ -45,6 +45,12 @@ __device__ __forceinline__ float4 ld_peer(const float* p) {
   return v;
 }
 
+constexpr int MAX_GRID = 4096;
+// per-CTA partial sums of squares and the ticket that elects the CTA which adds them up (launches that ask for the
+// norm are ordered on one stream per device)
+__device__ float g_ss_part[MAX_GRID];
+__device__ unsigned int g_ss_ticket;
+
 __global__ void __launch_bounds__(THREADS) zero1_kernel(Z1Params p) {
   __shared__ float red[THREADS / 32];
   const long long nvec = p.n >> 3;
@@ -126,6 +132,8 @@ __global__ void __launch_bounds__(THREADS) zero1_kernel(Z1Params p) {
     }
   }
   if (p.sumsq && p.mode != 2) {
+    // fixed-order reduction: shuffle tree inside a warp, warps in index order, CTAs in index order by whichever
+    // CTA finishes last; the result does not depend on scheduling, so every run of the same grid gives the same norm
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffff, ss, o);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
@@ -133,7 +141,16 @@ __global__ void __launch_bounds__(THREADS) zero1_kernel(Z1Params p) {
     if (threadIdx.x == 0) {
       float t = 0.f;
       for (int w = 0; w < THREADS / 32; ++w) t += red[w];
-      atomicAdd(p.sumsq, t);
+      g_ss_part[blockIdx.x] = t;
+      __threadfence();
+      const unsigned int ticket = atomicAdd(&g_ss_ticket, 1u);
+      if (ticket == gridDim.x - 1) {
+        __threadfence();
+        float tot = 0.f;
+        for (unsigned int b = 0; b < gridDim.x; ++b) tot += __ldcg(&g_ss_part[b]);
+        *p.sumsq += tot;
+        g_ss_ticket = 0;
+      }
     }
   }
 }
@@ -186,7 +203,8 @@ GK_EXPORT int gk_zero1_step(int mode, const unsigned long long* ptrs, int rank, 
   p.bc1 = 1.f - powf(b1, static_cast<float>(step));
   p.bc2 = 1.f - powf(b2, static_cast<float>(step));
   long long want = (n / 8 + THREADS - 1) / THREADS;
-  const int cap = ctas > 0 ? ctas : 4 * gk::sm_count();
+  int cap = ctas > 0 ? ctas : 4 * gk::sm_count();
+  if (cap > MAX_GRID) cap = MAX_GRID;
   const int grid = static_cast<int>(want < cap ? want : cap);
   zero1_kernel<<<grid, THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
   return gk::launch_status();

@@ -5,21 +5,47 @@
 linear_ce_kernels.py:159-1644): ``logp[t] = log softmax(h_t W^T / temperature)[target_t]`` plus the entropy of that
 distribution, with ``weight`` optionally sharded over the vocabulary across a tensor-parallel group.
 
-Implementation: tokens are processed in chunks; per chunk the logits tile is produced by the tcgen05 GEMM, reduced
-by one kernel pass to (max, sum-exp, sum p*z, target logit), and discarded.  With TP the per-rank partials are
-all-gathered once (``[T,4]`` floats) and merged.  Backward recomputes each chunk's logits, overwrites them with
-d(logits) in place and feeds the dgrad / wgrad GEMMs.
+Forward: one kernel (``csrc/linear_ce.cu``) runs the vocabulary GEMM on the tensor cores and folds every finished
+256-column tile into per-row (max, sum-exp, sum p*z, target logit) in its epilogue; only ``[splits, T, 4]`` floats
+reach memory, and a merge kernel turns them (and, with TP, the all-gathered partials of every rank) into log-prob,
+entropy and log-sum-exp.  ``GCORE_FUSED_LINEAR_CE=0`` selects the older chunked form (logits of 4096 tokens at a
+time through the plain GEMM, one reduction pass, discard).  Backward recomputes each chunk's logits, overwrites them
+with d(logits) in place and feeds the dgrad / wgrad GEMMs.
 """
 from __future__ import annotations
 
 import torch
 import torch.distributed as dist
 
+import os
+
 from . import _lib
 from .gemm import gemm, linear_dgrad, linear_forward, linear_wgrad
 
 LAUNCHES = {"vocab": 0}
 CHUNK_TOKENS = 4096
+FUSED_FWD = {"enabled": os.environ.get("GCORE_FUSED_LINEAR_CE", "1") != "0"}
+
+
+def _fused_ok(hidden, weight):
+    return (FUSED_FWD["enabled"] and hasattr(_lib.kernels(), "gk_linear_ce_fwd") and weight.dtype == torch.bfloat16
+            and hidden.stride(1) == 1 and weight.stride(1) == 1 and hidden.stride(0) % 8 == 0
+            and weight.stride(0) % 8 == 0 and hidden.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def fused_linear_stats(hidden, weight, targets, inv_temp, vocab_start):
+    """Partials ``[splits, T, 4]`` = (max, sum exp, sum exp * z, target z or -FLT_MAX) of ``hidden @ weight.T *
+    inv_temp`` per row and vocabulary split, without the logits."""
+    T, K = hidden.shape
+    V = weight.shape[0]
+    lib = _lib.kernels()
+    splits = lib.gk_linear_ce_splits(T, V)
+    part = torch.empty(splits, T, 4, dtype=torch.float32, device=hidden.device)
+    LAUNCHES["vocab"] += 1
+    _lib.check(lib.gk_linear_ce_fwd(_lib.ptr(hidden), hidden.stride(0), _lib.ptr(weight), weight.stride(0),
+                                    _lib.ptr(targets), inv_temp, vocab_start, T, V, K, splits, _lib.ptr(part),
+                                    _lib.ptr(_lib.err_flag(hidden.device)), _lib.stream_ptr()), "linear_ce_fwd")
+    return part
 
 
 def logprob_entropy_ref(logits, targets, temperature=1.0):
@@ -73,7 +99,15 @@ class _LinearLogprobFn(torch.autograd.Function):
         logp = torch.empty(T, dtype=torch.float32, device=hidden.device)
         ent = torch.empty(T, dtype=torch.float32, device=hidden.device)
         lse = torch.empty(T, dtype=torch.float32, device=hidden.device)
-        for s in range(0, T, CHUNK_TOKENS):
+        fused = _fused_ok(hidden, weight)
+        if fused:
+            part = fused_linear_stats(hidden, weight, targets, inv_temp, vocab_start)
+            if tp > 1:
+                allp = torch.empty(tp * part.shape[0], T, 4, dtype=torch.float32, device=hidden.device)
+                dist.all_gather_into_tensor(allp, part, group=tp_group)
+                part = allp
+            logp, ent, lse = _combine(part, T)
+        for s in range(0, T if not fused else 0, CHUNK_TOKENS):
             e = min(T, s + CHUNK_TOKENS)
             logits = linear_forward(hidden[s:e], weight)
             if tp > 1:

@@ -376,6 +376,31 @@ def cmd_decode_chain(argv=None):
         return linear_forward(fused.swiglu(linear_forward(h2, c)), d2)
 
     res["layer_chain_us"] = round(graph_time([lambda i=i: layer(i) for i in range(12)]), 2)
+    # the tail of a step: final norm, vocabulary projection (fp32 logits), sampling, state advance
+    from gcore_b200.ops.vocab import sample
+    V = 152064 // tp
+    heads = [(torch.randn(V, H, device=dev) * 0.02).bfloat16() for _ in range(2)]
+    seeds = torch.arange(T, device=dev, dtype=torch.int64)
+    steps = torch.zeros(T, dtype=torch.int32, device=dev)
+    toks = torch.zeros(T, dtype=torch.int64, device=dev)
+    ring = torch.zeros(64, T, dtype=torch.int64, device=dev)
+    ring_idx = torch.zeros(1, dtype=torch.int64, device=dev)
+    res["lm_head_fp32"] = round(graph_time(
+        [lambda i=i: linear_forward(x, heads[i % 2], out_dtype=torch.float32) for i in range(8)]), 2)
+    res["lm_head_torch_bf16"] = round(graph_time([lambda i=i: torch.matmul(x, heads[i % 2].t()) for i in range(8)]), 2)
+    logits = linear_forward(x, heads[0], out_dtype=torch.float32)
+    res["sample"] = round(graph_time([lambda: sample(logits, 1.0, seeds, steps) for _ in range(8)]), 2)
+
+    def tail(i):
+        hl, _ = fused.rmsnorm(x, g, 1e-6, r)
+        tok, lp = sample(linear_forward(hl, heads[i % 2], out_dtype=torch.float32), 1.0, seeds, steps)
+        toks.copy_(tok)
+        ring.index_copy_(0, ring_idx % 64, tok[None])
+        steps.add_(1)
+        ring_idx.add_(1)
+
+    res["step_tail_us"] = round(graph_time([lambda i=i: tail(i) for i in range(8)]), 2)
+    res["lm_head_MB"] = round(V * H * 2 / 1e6, 1)
     _lib.check_device_errors()
     print(json.dumps(res, indent=1))
     if args.json:

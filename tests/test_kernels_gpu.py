@@ -208,6 +208,31 @@ def test_linear_logprob_entropy_fwd_bwd():
         vocab.CHUNK_TOKENS = old
 
 
+@pytest.mark.parametrize("T,H,V,vs", [(300, 256, 5000, 0), (1024, 512, 33000, 0), (130, 192, 777, 1000)])
+def test_fused_linear_stats_never_writes_logits(T, H, V, vs):
+    """The vocabulary GEMM with the softmax statistics in its epilogue against the fp32 definition, including a
+    vocabulary that is not a multiple of the tile, rows that are not a multiple of 128 and targets outside the
+    local vocabulary shard."""
+    from gcore_b200.ops import _lib, vocab
+    torch.manual_seed(17)
+    h = _rand(T, H, scale=1.0)
+    w = _rand(V, H, scale=0.1)
+    tg = torch.randint(vs - 50 if vs else 0, vs + V + (50 if vs else 0), (T,), device=DEV).clamp_min(0)
+    part = vocab.fused_linear_stats(h, w, tg, 1.0 / 0.7, vs)
+    _lib.check_device_errors()
+    assert part.shape[1:] == (T, 4)
+    z = (h.float() @ w.float().t()) / 0.7
+    lp, en, lse = vocab._combine(part, T)
+    lse_ref = torch.logsumexp(z, -1)
+    _close(lse, lse_ref, atol=2e-3)
+    _close(en, lse_ref - (torch.softmax(z, -1) * z).sum(-1), atol=5e-3)
+    local = tg - vs
+    mine = (local >= 0) & (local < V)
+    zt_ref = z.gather(-1, local.clamp(0, V - 1)[:, None]).squeeze(-1)
+    _close(lp[mine], (zt_ref - lse_ref)[mine], atol=5e-3)
+    assert (part[:, :, 3].max(0).values[~mine] < -1e30).all()        # no split claims a target it does not own
+
+
 def test_sampling_distribution_and_logprob():
     from gcore_b200.ops.vocab import sample
     torch.manual_seed(8)

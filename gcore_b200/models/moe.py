@@ -65,34 +65,11 @@ class Router(nn.Module):
         if self.lora is not None:
             logits = logits + self.lora(x.float())
         replay = RouterReplay.get(self.layer_idx) if RouterReplay.mode == "replay" else None
-        if cfg.moe_router_type == "softmax":
-            probs = torch.softmax(logits, dim=-1)
-            if replay is not None:
-                idx = replay.to(x.device)
-                w = probs.gather(-1, idx)
-            else:
-                w, idx = torch.topk(probs, K, dim=-1)
-            if cfg.moe_norm_topk_prob:
-                w = w / w.sum(-1, keepdim=True).clamp_min(1e-20)
-            scores_for_aux = probs
-        else:
-            scores = torch.sigmoid(logits)
-            sel = scores + self.expert_bias if self.expert_bias is not None else scores
-            if replay is not None:
-                idx = replay.to(x.device)
-            else:
-                G = cfg.moe_n_group
-                if G > 1:
-                    grp = sel.view(-1, G, E // G).topk(2, dim=-1).values.sum(-1)  # [T, G]
-                    gidx = grp.topk(cfg.moe_topk_group, dim=-1).indices
-                    gmask = torch.zeros_like(grp).scatter_(1, gidx, 1.0)
-                    sel = sel.masked_fill(gmask[:, :, None].expand(-1, G, E // G).reshape(-1, E) == 0, float("-inf"))
-                idx = sel.topk(K, dim=-1).indices
-            w = scores.gather(-1, idx)
-            if cfg.moe_norm_topk_prob:
-                w = w / w.sum(-1, keepdim=True).clamp_min(1e-20)
-            w = w * cfg.moe_routed_scaling_factor
-            scores_for_aux = scores / scores.sum(-1, keepdim=True).clamp_min(1e-20)
+        from ..ops.router import route
+        sigmoid = cfg.moe_router_type != "softmax"
+        idx, w = route(logits, self.expert_bias if sigmoid else None, replay, K, cfg.moe_n_group if sigmoid else 1,
+                       cfg.moe_topk_group if sigmoid else 1, sigmoid, cfg.moe_norm_topk_prob,
+                       cfg.moe_routed_scaling_factor if sigmoid else 1.0)
         if RouterReplay.mode == "record":
             RouterReplay.put(self.layer_idx, idx.detach())
         if self.tokens_per_expert is not None and self.training and torch.is_grad_enabled():
@@ -108,7 +85,11 @@ class Router(nn.Module):
                 f = torch.zeros(E, dtype=torch.float32, device=x.device)
                 f.scatter_add_(0, idx.reshape(-1), torch.ones(idx.numel(), dtype=torch.float32, device=x.device))
                 f = f * (E / (K * max(T, 1)))
-                P = scores_for_aux.mean(0)
+                if sigmoid:
+                    scores = torch.sigmoid(logits)
+                    P = (scores / scores.sum(-1, keepdim=True).clamp_min(1e-20)).mean(0)
+                else:
+                    P = torch.softmax(logits, dim=-1).mean(0)
                 aux = aux + cfg.moe_aux_loss_coef * (f * P).sum()
             if cfg.moe_z_loss_coef > 0:
                 aux = aux + cfg.moe_z_loss_coef * torch.logsumexp(logits, -1).pow(2).mean()

@@ -161,6 +161,8 @@ def _declare_kernels(lib: ctypes.CDLL):
     d("gk_axpy_cast", [P, I, P, I, L, F, I, P])
     d("gk_logprob_entropy_fwd", [P, I, L, P, F, I, I, L, P, P, P, P, P])
     d("gk_logprob_entropy_combine", [P, I, L, P, P, P, P])
+    d("gk_router_fwd", [P, P, P, P, P, L, I, I, I, I, I, I, F, P])
+    d("gk_router_bwd", [P, P, P, P, L, I, I, I, I, F, P])
     d("gk_linear_ce_splits", [I, I])
     d("gk_linear_ce_fwd", [P, L, P, L, P, F, I, I, I, I, I, P, P, P])
     d("gk_logprob_entropy_bwd", [P, I, L, P, P, P, P, P, F, I, I, L, P])

@@ -233,6 +233,34 @@ def test_fused_linear_stats_never_writes_logits(T, H, V, vs):
     assert (part[:, :, 3].max(0).values[~mine] < -1e30).all()        # no split claims a target it does not own
 
 
+@pytest.mark.parametrize("E,K,G,TG,sigmoid,norm,scale,use_bias", [
+    (128, 8, 1, 1, False, True, 1.0, False), (64, 4, 1, 1, False, False, 1.0, False),
+    (256, 8, 8, 4, True, True, 2.5, True), (32, 2, 4, 2, True, False, 1.0, True), (512, 16, 1, 1, True, True, 1.0, False)])
+def test_router_kernel_matches_reference(E, K, G, TG, sigmoid, norm, scale, use_bias):
+    from gcore_b200.ops.router import route, route_ref
+    torch.manual_seed(21)
+    T = 777
+    logits = torch.randn(T, E, device=DEV, dtype=torch.float32, requires_grad=True)
+    bias = torch.randn(E, device=DEV) * 0.3 if use_bias else None
+    idx, w = route(logits, bias, None, K, G, TG, sigmoid, norm, scale)
+    lr = logits.detach().clone().requires_grad_(True)
+    idx_r, w_r = route_ref(lr, bias, None, K, G, TG, sigmoid, norm, scale)
+    assert torch.equal(idx.sort(-1).values, idx_r.sort(-1).values)
+    # same experts, possibly listed in another order: compare weights per expert
+    dense = torch.zeros(T, E, device=DEV).scatter(1, idx, w)
+    dense_r = torch.zeros(T, E, device=DEV).scatter(1, idx_r, w_r)
+    assert torch.allclose(dense, dense_r, atol=1e-5, rtol=1e-4)
+    coef = torch.randn(T, E, device=DEV)
+    (dense * coef).sum().backward()
+    (dense_r * coef).sum().backward()
+    assert torch.allclose(logits.grad, lr.grad, atol=1e-5, rtol=1e-3), (logits.grad - lr.grad).abs().max()
+    # forced expert ids (routing replay) give the reference's weights for those ids
+    forced = torch.stack([torch.randperm(E, device=DEV)[:K] for _ in range(T)])
+    idx_f, w_f = route(logits.detach(), bias, forced, K, G, TG, sigmoid, norm, scale)
+    _, w_fr = route_ref(logits.detach(), bias, forced, K, G, TG, sigmoid, norm, scale)
+    assert torch.equal(idx_f, forced) and torch.allclose(w_f, w_fr, atol=1e-5, rtol=1e-4)
+
+
 def test_sampling_distribution_and_logprob():
     from gcore_b200.ops.vocab import sample
     torch.manual_seed(8)

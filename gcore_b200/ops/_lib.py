@@ -168,6 +168,7 @@ def _declare_kernels(lib: ctypes.CDLL):
     d("gk_logprob_entropy_bwd", [P, I, L, P, P, P, P, P, F, I, I, L, P])
     d("gk_sample", [P, I, L, I, I, F, I, P, P, P, P, P, I, P])
     d("gk_sample_combine", [P, I, I, P, P, P])
+    d("gk_sample_filtered", [P, I, L, I, F, I, F, F, I, P, P, P, P, P, I, P])
     d("gk_grpo_loss", [P, P, P, P, P, L, F, F, F, F, F, F, P, P, P, P])
     d("gk_gae", [P, P, P, P, P, I, I, F, F, P])
     d("gk_kv_append_rope", [P, P, P, P, P, I, I, I, I, I, I, F, I, P])

@@ -255,6 +255,28 @@ def sample(logits, temperature, seeds, steps, greedy=False, tp_group=None, vocab
     return tokens, logp
 
 
+def sample_filtered(logits, temperature, top_k, top_p, min_p, seeds, steps, greedy=False, return_kept=False):
+    """Top-k / top-p / min-p sampling over whole-vocabulary ``logits`` [B, V]: one kernel finds the cut by radix
+    selection over counts and probability mass (no sort) and draws with the sampler's counter-based random stream.
+    Returns ``(tokens, logp)`` with ``logp`` under the renormalised filtered distribution (the definition:
+    ``sample(apply_top_k_top_p(logits / temperature, ...), 1.0, ...)``)."""
+    B, V = logits.shape
+    if not (_lib.use_native(logits) and logits.dtype in (torch.bfloat16, torch.float32) and logits.stride(1) == 1
+            and hasattr(_lib.kernels(), "gk_sample_filtered")):
+        z = apply_top_k_top_p(logits / max(float(temperature), 1e-6), top_k, top_p, min_p)
+        out = sample(z.contiguous(), 1.0, seeds, steps, greedy)
+        return (*out, torch.isfinite(z).sum(-1).int()) if return_kept else out
+    tokens = torch.empty(B, dtype=torch.int64, device=logits.device)
+    logp = torch.empty(B, dtype=torch.float32, device=logits.device)
+    kept = torch.empty(B, dtype=torch.int32, device=logits.device) if return_kept else None
+    LAUNCHES["vocab"] += 1
+    _lib.check(_lib.kernels().gk_sample_filtered(
+        _lib.ptr(logits), int(logits.dtype == torch.float32), logits.stride(0), V, 1.0 / max(float(temperature), 1e-6),
+        int(top_k or 0), float(top_p), float(min_p), int(greedy), _lib.ptr(seeds), _lib.ptr(steps), _lib.ptr(tokens),
+        _lib.ptr(logp), _lib.ptr(kept), B, _lib.stream_ptr()), "sample_filtered")
+    return (tokens, logp, kept) if return_kept else (tokens, logp)
+
+
 def apply_top_k_top_p(logits, top_k=0, top_p=1.0, min_p=0.0):
     """Masks logits outside the top-k / nucleus / min-p set with -inf (sort based; only used when a request asks
     for it, the default rollout configuration samples from the full distribution)."""

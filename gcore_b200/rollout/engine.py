@@ -34,7 +34,7 @@ from ..models.config import ModelConfig
 from ..ops import _lib, fused
 from ..ops.attention import flash_attn_varlen, kv_append_rope, paged_decode
 from ..ops.gemm import linear_forward
-from ..ops.vocab import apply_top_k_top_p, sample
+from ..ops.vocab import apply_top_k_top_p, sample, sample_filtered
 from ..utils import io_counters
 
 
@@ -618,8 +618,8 @@ class InferEngine:
                 dist.all_gather(parts, logits.contiguous(), group=self.tp_group)
                 logits = torch.cat(parts, dim=1)
                 tp_group, vocab_start = None, 0
-            logits = apply_top_k_top_p(logits / max(sp["temperature"], 1e-6), sp["top_k"], sp["top_p"], sp["min_p"])
-            tok, lp = sample(logits.contiguous(), 1.0, st["seeds"], st["steps"], sp["greedy"], tp_group, vocab_start)
+            tok, lp = sample_filtered(logits.contiguous(), sp["temperature"], sp["top_k"], sp["top_p"], sp["min_p"],
+                                      st["seeds"], st["steps"], sp["greedy"])
         else:
             tok, lp = sample(logits, sp["temperature"], st["seeds"], st["steps"], sp["greedy"],
                              self.tp_group if self.tp > 1 else None, self.vocab_start)

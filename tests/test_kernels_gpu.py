@@ -261,6 +261,33 @@ def test_router_kernel_matches_reference(E, K, G, TG, sigmoid, norm, scale, use_
     assert torch.equal(idx_f, forced) and torch.allclose(w_f, w_fr, atol=1e-5, rtol=1e-4)
 
 
+@pytest.mark.parametrize("top_k,top_p,min_p", [(50, 1.0, 0.0), (0, 0.9, 0.0), (200, 0.8, 0.0), (0, 1.0, 0.05),
+                                                (1000, 0.95, 0.01)])
+def test_filtered_sampling_matches_sort_based_definition(top_k, top_p, min_p):
+    from gcore_b200.ops.vocab import apply_top_k_top_p, sample_filtered
+    torch.manual_seed(23)
+    B, V, temp = 48, 50000, 0.8
+    logits = (torch.randn(B, V, device=DEV) * 2.5).contiguous()
+    seeds = torch.arange(B, device=DEV, dtype=torch.int64)
+    steps = torch.full((B,), 3, device=DEV, dtype=torch.int32)
+    tok, lp, kept = sample_filtered(logits, temp, top_k, top_p, min_p, seeds, steps, return_kept=True)
+    z = apply_top_k_top_p(logits / temp, top_k, top_p, min_p)
+    kept_ref = torch.isfinite(z).sum(-1)
+    # keys quantise the logits to 2.4e-6: the kept sets may differ by elements that close to the cut
+    assert (kept.long() - kept_ref).abs().max() <= 1, (kept, kept_ref)
+    assert torch.isfinite(z.gather(-1, tok[:, None])).all()          # every drawn token is inside the reference set
+    lp_ref = torch.log_softmax(z, -1).gather(-1, tok[:, None]).squeeze(-1)
+    assert torch.allclose(lp, lp_ref, atol=2e-3), (lp - lp_ref).abs().max()
+    # the draw is Gumbel-max with the sampler's random stream: same token as the unfiltered sampler run on the
+    # masked logits
+    from gcore_b200.ops.vocab import sample
+    tok_ref, _ = sample(z.contiguous(), 1.0, seeds, steps)
+    same = (kept.long() == kept_ref)
+    assert torch.equal(tok[same], tok_ref[same])
+    tok_g, _ = sample_filtered(logits, temp, top_k, top_p, min_p, seeds, steps, greedy=True)
+    assert torch.equal(tok_g, logits.argmax(-1))
+
+
 def test_sampling_distribution_and_logprob():
     from gcore_b200.ops.vocab import sample
     torch.manual_seed(8)

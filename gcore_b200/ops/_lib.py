@@ -149,6 +149,7 @@ def _declare_kernels(lib: ctypes.CDLL):
     d("gk_set_peer_wait_budget", [L], None)
     d("gk_peer_rows", [P, L, I, P, P])
     d("gk_allreduce_oneshot", [P, P, L, I, I, L, P, P, P, P])
+    d("gk_allreduce_rmsnorm", [P, P, P, P, P, I, I, F, I, I, L, P, P, P, P])
     d("gk_gemm_splitk_scratch", [I, I, I, I, ctypes.POINTER(L), ctypes.POINTER(L)], None)
     d("gk_rmsnorm_fwd", [P, P, P, P, P, P, I, I, F, P])
     d("gk_rmsnorm_bwd_parts", [I])

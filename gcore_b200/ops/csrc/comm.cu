@@ -133,6 +133,153 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_oneshot_kernel(ArParams 
   }
 }
 
+// ---- all-reduce + residual add + RMSNorm in one kernel (tensor-parallel decode: the partial sums of a row-parallel
+// projection go straight into the next norm).  Same exchange as above, but a CTA owns whole rows: it pushes its rows'
+// partials to every peer, waits for the peers' partials of the same rows, and then per row
+//   a   = bf16(sum over ranks, fixed order)            (what the separate all-reduce would have stored)
+//   res = bf16(a + residual)                           -> res_out      (a alone when there is no residual)
+//   y   = bf16(res * rsqrt(mean(res^2) + eps) * gamma) -> y
+// i.e. bit-identical to all-reduce followed by the RMSNorm kernel of elementwise.cu, on every rank.
+struct ArNormParams {
+  ArParams ar;                  // in = partial [rows, H]; out unused; n = rows * H
+  const __nv_bfloat16* res_in;  // may be null
+  const __nv_bfloat16* gamma;   // [H]
+  __nv_bfloat16* res_out;       // [rows, H]
+  __nv_bfloat16* y;             // [rows, H]
+  int rows, H;
+  float eps;
+};
+
+__device__ __forceinline__ void unpack_bf16x8(const uint4& w, float (&f)[8]) {
+  const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    f[2 * q] = __uint_as_float((ww[q] & 0xFFFFu) << 16);
+    f[2 * q + 1] = __uint_as_float(ww[q] & 0xFFFF0000u);
+  }
+}
+__device__ __forceinline__ uint4 pack_bf16x8(const float (&f)[8]) {
+  uint4 o;
+  __nv_bfloat162 t2;
+  t2 = __floats2bfloat162_rn(f[0], f[1]); o.x = *reinterpret_cast<uint32_t*>(&t2);
+  t2 = __floats2bfloat162_rn(f[2], f[3]); o.y = *reinterpret_cast<uint32_t*>(&t2);
+  t2 = __floats2bfloat162_rn(f[4], f[5]); o.z = *reinterpret_cast<uint32_t*>(&t2);
+  t2 = __floats2bfloat162_rn(f[6], f[7]); o.w = *reinterpret_cast<uint32_t*>(&t2);
+  return o;
+}
+
+constexpr int ARN_MAXV = 4;  // vectors of 8 per thread and row: H <= 256 * 8 * 4 = 8192
+
+__global__ void __launch_bounds__(AR_THREADS) allreduce_rmsnorm_kernel(ArNormParams q) {
+  __shared__ int s_ok;
+  __shared__ float red[AR_THREADS / 32];
+  const ArParams& p = q.ar;
+  gk::pdl_launch_dependents();
+  gk::pdl_wait();
+  const unsigned int calls = *reinterpret_cast<volatile unsigned int*>(p.state);
+  const int parity = calls & 1;
+  const uint32_t epoch = (calls >> 1) + 1;
+  const int hv = q.H >> 3;
+  const int rpc = (q.rows + gridDim.x - 1) / gridDim.x;
+  int r0 = blockIdx.x * rpc, r1 = r0 + rpc;
+  if (r0 > q.rows) r0 = q.rows;
+  if (r1 > q.rows) r1 = q.rows;
+  const long long v0 = static_cast<long long>(r0) * hv, v1 = static_cast<long long>(r1) * hv;
+  const uint4* in = reinterpret_cast<const uint4*>(p.in);
+  const long long slot_vec = p.slot_elems >> 3;
+  for (int pr = 1; pr < p.nranks; ++pr) {
+    const int peer = (p.rank + pr) % p.nranks;
+    uint4* dst = reinterpret_cast<uint4*>(p.inbox[peer]) + (static_cast<long long>(parity) * p.nranks + p.rank) * slot_vec;
+    for (long long i = v0 + threadIdx.x; i < v1; i += AR_THREADS) dst[i] = in[i];
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    for (int pr = 1; pr < p.nranks; ++pr) {
+      const int peer = (p.rank + pr) % p.nranks;
+      st_release_sys(p.flags[peer] + (parity * p.nranks + p.rank) * AR_CTAS + blockIdx.x, epoch);
+    }
+    int ok = 1;
+    const long long t0 = clock64();
+    for (int pr = 1; pr < p.nranks && ok; ++pr) {
+      const int src = (p.rank + pr) % p.nranks;
+      const uint32_t* f = p.flags[p.rank] + (parity * p.nranks + src) * AR_CTAS + blockIdx.x;
+      int spins = 0;
+      while (static_cast<int32_t>(ld_acquire_sys(f) - epoch) < 0) {
+        if ((++spins & 63) == 0 && (clock64() - t0 > WAIT_CYCLES || *reinterpret_cast<volatile int*>(p.err) != 0)) {
+          atomicCAS(p.err, 0, 5);
+          ok = 0;
+          break;
+        }
+      }
+    }
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (s_ok) {
+    const uint4* mine = reinterpret_cast<const uint4*>(p.inbox[p.rank]) + static_cast<long long>(parity) * p.nranks * slot_vec;
+    const uint4* gv = reinterpret_cast<const uint4*>(q.gamma);
+    for (int row = r0; row < r1; ++row) {
+      const long long rb = static_cast<long long>(row) * hv;
+      float f[ARN_MAXV][8];
+      float ss = 0.f;
+#pragma unroll
+      for (int u = 0; u < ARN_MAXV; ++u) {
+        const int c = threadIdx.x + u * AR_THREADS;
+        if (c < hv) {
+          float tot[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int r = 0; r < p.nranks; ++r) {
+            const uint4 w = r == p.rank ? in[rb + c] : __ldcg(mine + static_cast<long long>(r) * slot_vec + rb + c);
+            add8(tot, w);
+          }
+          unpack_bf16x8(pack_bf16x8(tot), f[u]);  // the value a stand-alone all-reduce would have stored
+          if (q.res_in) {
+            float g[8];
+            unpack_bf16x8(reinterpret_cast<const uint4*>(q.res_in)[rb + c], g);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[u][j] += g[j];
+          }
+          const uint4 stored = pack_bf16x8(f[u]);
+          reinterpret_cast<uint4*>(q.res_out)[rb + c] = stored;
+          unpack_bf16x8(stored, f[u]);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ss += f[u][j] * f[u][j];
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      __syncthreads();
+      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+      __syncthreads();
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < AR_THREADS / 32; ++w) t += red[w];
+      const float rstd = rsqrtf(t / q.H + q.eps);
+#pragma unroll
+      for (int u = 0; u < ARN_MAXV; ++u) {
+        const int c = threadIdx.x + u * AR_THREADS;
+        if (c < hv) {
+          float g[8], o[8];
+          unpack_bf16x8(gv[c], g);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = f[u][j] * rstd * g[j];
+          reinterpret_cast<uint4*>(q.y)[rb + c] = pack_bf16x8(o);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int ticket = atomicAdd(p.state + 1, 1u);
+    if (ticket == gridDim.x - 1) {
+      p.state[1] = 0;
+      __threadfence();
+      p.state[0] = calls + 1;
+    }
+  }
+}
+
 // Segment gather / reduce over peer memory for context parallelism: out[i] = sum over the segments that cover i of
 // seg.src[i - seg.start], in segment order (fp32 accumulation, bf16 in and out).  With disjoint segments this is the
 // pull of the K/V rows a rank needs from the ranks that own them; with overlapping segments it is the return of the
@@ -251,5 +398,33 @@ GK_EXPORT int gk_allreduce_oneshot(const void* in, void* out, long long n, int r
   p.state = state;
   p.err = err;
   gk::launch_k(allreduce_oneshot_kernel, dim3(AR_CTAS), dim3(AR_THREADS), 0, reinterpret_cast<cudaStream_t>(stream), p);
+  return gk::launch_status();
+}
+
+// partial [rows, H] bf16 (this rank's partial sums) -> res_out = all-reduce(partial) + res_in, y = RMSNorm(res_out) * gamma.
+// Shares inboxes, flags and the call counter with gk_allreduce_oneshot (same ptrs / state).  H % 8 == 0, H <= 8192,
+// rows * H <= slot_elems.  res_in may be null and may alias res_out.
+GK_EXPORT int gk_allreduce_rmsnorm(const void* partial, const void* res_in, const void* gamma, void* res_out, void* y,
+                                   int rows, int H, float eps, int rank, int nranks, long long slot_elems,
+                                   const unsigned long long* ptrs, unsigned int* state, int* err, void* stream) {
+  const long long n = static_cast<long long>(rows) * H;
+  if (H % 8 || H > AR_THREADS * 8 * ARN_MAXV || n > slot_elems || nranks < 1 || nranks > MAX_RANKS) return -1;
+  if (rows == 0) return 0;
+  ArNormParams q;
+  q.ar.in = reinterpret_cast<const __nv_bfloat16*>(partial);
+  q.ar.out = nullptr;
+  q.ar.n = n; q.ar.rank = rank; q.ar.nranks = nranks; q.ar.slot_elems = slot_elems;
+  for (int r = 0; r < nranks; ++r) {
+    q.ar.inbox[r] = reinterpret_cast<__nv_bfloat16*>(ptrs[r]);
+    q.ar.flags[r] = reinterpret_cast<uint32_t*>(ptrs[nranks + r]);
+  }
+  q.ar.state = state;
+  q.ar.err = err;
+  q.res_in = reinterpret_cast<const __nv_bfloat16*>(res_in);
+  q.gamma = reinterpret_cast<const __nv_bfloat16*>(gamma);
+  q.res_out = reinterpret_cast<__nv_bfloat16*>(res_out);
+  q.y = reinterpret_cast<__nv_bfloat16*>(y);
+  q.rows = rows; q.H = H; q.eps = eps;
+  gk::launch_k(allreduce_rmsnorm_kernel, dim3(AR_CTAS), dim3(AR_THREADS), 0, reinterpret_cast<cudaStream_t>(stream), q);
   return gk::launch_status();
 }

@@ -217,6 +217,26 @@ class PeerAllReduce:
         return x
 
 
+    def all_reduce_rmsnorm(self, partial: torch.Tensor, residual, gamma: torch.Tensor, eps: float):
+        """``(y, new_residual)`` with ``new_residual = all_reduce(partial) + residual`` and ``y = RMSNorm(new_residual)
+        * gamma``, one kernel; ``None`` when the shape is outside the kernel's limits (the caller then runs the two
+        steps separately)."""
+        rows, H = partial.shape
+        if (rows * H > self.slot or H % 8 or H > 8192 or partial.dtype != torch.bfloat16 or not partial.is_contiguous()
+                or gamma.dtype != torch.bfloat16 or (residual is not None and not residual.is_contiguous())
+                or not hasattr(_lib.kernels(), "gk_allreduce_rmsnorm")):
+            return None
+        y = torch.empty_like(partial)
+        res_out = torch.empty_like(partial)
+        LAUNCHES["fused_comm"] += 1
+        rc = _lib.kernels().gk_allreduce_rmsnorm(_lib.ptr(partial), _lib.ptr(residual), _lib.ptr(gamma), _lib.ptr(res_out),
+                                                 _lib.ptr(y), rows, H, float(eps), self.rank, self.tp, self.slot,
+                                                 self.ptrs, _lib.ptr(self.state), _lib.ptr(_lib.err_flag(partial.device)),
+                                                 _lib.stream_ptr())
+        _lib.check(rc, "gk_allreduce_rmsnorm")
+        return y, res_out
+
+
 _FUSED: dict = {}
 
 

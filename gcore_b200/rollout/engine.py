@@ -417,27 +417,47 @@ class InferEngine:
         return linear_forward(h, getattr(lw, name), bias)
 
     # ------------------------------------------------------------------ model math (no autograd)
+    def _ensure_peer_ar(self, x):
+        if self._peer_ar is None and self.device.type == "cuda" and not _lib.force_eager() \
+                and x.dtype == torch.bfloat16 and os.environ.get("GCORE_PEER_ALLREDUCE", "1") != "0":
+            from ..parallel.symm import PeerAllReduce
+            self._peer_ar = PeerAllReduce(self.tp_group, self.max_running * self.cfg.hidden_size, self.device)
+
     def _allreduce(self, x):
         if self.tp > 1:
-            if self._peer_ar is None and self.device.type == "cuda" and not _lib.force_eager() \
-                    and x.dtype == torch.bfloat16 and os.environ.get("GCORE_PEER_ALLREDUCE", "1") != "0":
-                from ..parallel.symm import PeerAllReduce
-                self._peer_ar = PeerAllReduce(self.tp_group, self.max_running * self.cfg.hidden_size, self.device)
+            self._ensure_peer_ar(x)
             if self._peer_ar is not None and x.numel() <= self._peer_ar.slot and x.is_contiguous():
                 return self._peer_ar.all_reduce(x)  # one-shot push over NVLink peer memory (decode-sized tensors)
             dist.all_reduce(x, group=self.tp_group)
         return x
 
-    def _mlp(self, lw: LayerWeights, h):
+    def _reduce_norm(self, partial, gamma, res, pending: bool):
+        """``RMSNorm(all_reduce(partial) + res)`` and the new residual.  ``pending``: ``partial`` still holds this
+        rank's partial sums; on the peer-memory path the all-reduce, the residual add and the norm are then one
+        kernel that reads the peers' partials (tensor-parallel decode), otherwise all-reduce and norm run one after
+        the other."""
+        if pending and self.tp > 1:
+            self._ensure_peer_ar(partial)
+            if self._peer_ar is not None and os.environ.get("GCORE_FUSED_AR_NORM", "1") != "0":
+                out = self._peer_ar.all_reduce_rmsnorm(partial, res, gamma, self.cfg.rms_norm_eps)
+                if out is not None:
+                    return out
+            partial = self._allreduce(partial)
+        return fused.rmsnorm(partial, gamma, self.cfg.rms_norm_eps, res)
+
+    def _mlp(self, lw: LayerWeights, h, reduce: bool = True):
+        """Feed-forward block; with ``reduce=False`` a dense block returns this rank's partial sums (second value
+        True) and leaves the all-reduce to the caller."""
         if lw.moe is not None:
             was = lw.moe.training
             lw.moe.eval()
             y, _ = lw.moe(h)
             if was:
                 lw.moe.train()
-            return y
+            return y if reduce else (y, False)
         g = self._lin(h, lw, "fc1_w")
-        return self._allreduce(self._lin(fused.swiglu(g), lw, "fc2_w"))
+        y = self._lin(fused.swiglu(g), lw, "fc2_w")
+        return self._allreduce(y) if reduce else (y, self.tp > 1)
 
     def _embed(self, tokens):
         if self.tp == 1:
@@ -524,13 +544,13 @@ class InferEngine:
             lat_mask = p_all[None, :] < ctx[:, None]
             sink = (self.k_cache[0].shape[0] - 1) * self.bs
             lat_slots = torch.where(slots >= 0, slots, torch.full_like(slots, sink)).long()
+        pending = False   # x still holds this rank's partial sums of the previous block's row-parallel projection
         for li, lw in enumerate(self.w.layers):
-            h, res = fused.rmsnorm(x, lw.ln1, cfg.rms_norm_eps, res)
+            h, res = self._reduce_norm(x, lw.ln1, res, pending)
             if lw.mla is not None:
                 o = self._mla_decode(lw.mla, h, pos, self.k_cache[li], lat_slots, lat_idx, lat_mask)
-                a = self._allreduce(lw.mla.linear_proj(o))
-                h, res = fused.rmsnorm(a, lw.ln2, cfg.rms_norm_eps, res)
-                x = self._mlp(lw, h)
+                h, res = self._reduce_norm(lw.mla.linear_proj(o), lw.ln2, res, self.tp > 1)
+                x, pending = self._mlp(lw, h, reduce=False)
                 continue
             qkv = self._lin(h, lw, "qkv_w", lw.qkv_b)
             qkv = self._qk_norm(lw, qkv, B)
@@ -539,10 +559,9 @@ class InferEngine:
             q = qkv.view(B, self.hq + 2 * self.hk, self.D)[:, :self.hq]
             o = paged_decode(q, self.k_cache[li], self.v_cache[li], st["block_table"], ctx, self.max_model_len,
                              window=lw.window, sinks=lw.sinks)
-            a = self._allreduce(self._lin(o.view(B, self.hq * self.D), lw, "o_w"))
-            h, res = fused.rmsnorm(a, lw.ln2, cfg.rms_norm_eps, res)
-            x = self._mlp(lw, h)
-        hl, _ = fused.rmsnorm(x, self.w.final_ln, cfg.rms_norm_eps, res)
+            h, res = self._reduce_norm(self._lin(o.view(B, self.hq * self.D), lw, "o_w"), lw.ln2, res, self.tp > 1)
+            x, pending = self._mlp(lw, h, reduce=False)
+        hl, _ = self._reduce_norm(x, self.w.final_ln, res, pending)
         self._sample_into(hl, st)
         # state advance
         st["pos"].add_(st["active"].to(pos.dtype))

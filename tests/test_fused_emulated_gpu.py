@@ -187,6 +187,40 @@ def test_allreduce_oneshot_rank0_of_2():
     assert state[:2].tolist() == [1, 0]                              # call counter advanced, ticket reset
 
 
+@pytest.mark.parametrize("with_res", [True, False])
+def test_allreduce_residual_rmsnorm_rank0_of_2(with_res):
+    """One kernel = all-reduce, residual add and RMSNorm; bit-identical to the three steps done one after the other."""
+    lib = _lib()
+    from gcore_b200.ops import fused
+    torch.manual_seed(7)
+    k = lib.kernels()
+    ctas = k.gk_allreduce_ctas()
+    rows, H, tp = 100, 3584, 2                        # 100 rows over 32 CTAs: uneven, some CTAs own no row
+    slot = 128 * H
+    x0, x1 = _bf(rows, H), _bf(rows, H)
+    res = _bf(rows, H) if with_res else None
+    gamma = (1 + 0.1 * torch.randn(H, device="cuda")).bfloat16()
+    inbox = torch.zeros(2, tp, slot, dtype=torch.bfloat16, device="cuda")
+    inbox[0, 1, :rows * H] = x1.reshape(-1)
+    flags = torch.zeros(2, tp, ctas, dtype=torch.int32, device="cuda")
+    flags[0, 1] = 1
+    peer_inbox, peer_flags = torch.zeros_like(inbox), torch.zeros_like(flags)
+    state = torch.zeros(4, dtype=torch.int32, device="cuda")
+    y, res_out = torch.empty_like(x0), torch.empty_like(x0)
+    lib.check(k.gk_allreduce_rmsnorm(lib.ptr(x0), lib.ptr(res), lib.ptr(gamma), lib.ptr(res_out), lib.ptr(y), rows, H,
+                                     1e-6, 0, tp, slot, _ptrs(inbox, peer_inbox, flags, peer_flags), lib.ptr(state),
+                                     _err(), lib.stream_ptr()), "allreduce_rmsnorm")
+    torch.cuda.synchronize()
+    lib.check_device_errors()
+    summed = (x0.float() + x1.float()).bfloat16()
+    y_ref, res_ref = fused.rmsnorm(summed, gamma, 1e-6, res)
+    assert torch.equal(res_out, res_ref if with_res else summed)
+    assert torch.equal(y, y_ref)
+    assert torch.equal(peer_inbox[0, 0, :rows * H], x0.reshape(-1))
+    assert peer_flags[0, 0].tolist() == [1] * ctas                   # CTAs without rows still publish their flag
+    assert state[:2].tolist() == [1, 0]
+
+
 def test_expert_dispatch_combine_two_ranks_sequential():
     """ep_plan / ep_push / ep_pull of both ranks of an expert-parallel pair, run in an order in which no kernel has to
     wait: rank 1's counts are placed in rank 0's table before rank 0 plans; rank 0's plan publishes its counts to

@@ -157,29 +157,89 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm), "source": "nvidia-smi"}
 
 
+# The benchmark recipes: GRPO on the 7B dense model (the headline), GRPO on the 30B-A3B MoE with expert parallelism,
+# long-context SFT with context x tensor parallelism, block-fp8 GRPO with LoRA on the 12-layer DeepSeek-V3 shape.
+CONFIGS = {
+    "grpo7b": dict(kind="grpo", model="qwen2.5-7b", prompts_per_gpu=8, samples=8, prompt_len=256, max_response=1024),
+    "moe30b": dict(kind="grpo", model="qwen3-30b-a3b", prompts_per_gpu=4, samples=16, prompt_len=256, max_response=2048,
+                   mb_tokens=8192, recompute="full"),
+    "longctx": dict(kind="sft", model="llama3-8b-swa", seq_len=65536, sequences=8, recompute="full"),
+    "dsv3fp8": dict(kind="grpo", model="deepseek-v3-12l", prompts_per_gpu=4, samples=8, prompt_len=512,
+                    max_response=1024, mb_tokens=8192, recompute="full"),
+}
+
+
+def parallelism(config: str, world: int):
+    """(tp, cp, ep) of a recipe at ``world`` GPUs (the named layouts at 8, the closest smaller ones below)."""
+    if config == "grpo7b":
+        return (1 if world == 1 else 2), 1, 1
+    if config in ("moe30b", "dsv3fp8"):
+        return 1, 1, world
+    tp = 2 if world >= 2 else 1
+    return tp, max(1, min(4, world // tp)), 1
+
+
 def build_config(args, world):
     from gcore_b200.configs.base import from_dict
     from gcore_b200.configs.config import RlConfig
-    tp = 1 if world == 1 else 2
-    dp = world // tp
+    tp, cp, ep = parallelism(args.config, world)
+    dp = world // (tp * cp)
     prompts_per_dp = args.prompts_per_gpu * tp
     n = args.samples
+    dist_cfg = {"tensor_model_parallel_size": tp, "sequence_parallel": tp > 1, "context_parallel_size": cp,
+                "expert_model_parallel_size": ep}
+    policy = {"model_arch": args.model, "recompute": args.recompute, "recompute_num_layers": args.recompute_layers,
+              "share_rollout_weights": True, "dist_config": dist_cfg, "dynamic_mbs_target_seqlen": args.mb_tokens}
+    ppo = {"ppo_ratio_eps": 0.2, "grpo_kl_loss_beta": 0.001, "advantage_type": "grpo", "loss_func": "grpo"}
+    opt = {"lr": 1e-6, "lr_decay_style": "constant", "weight_decay": 0.01, "max_grad_norm": 1.0}
+    if args.config == "dsv3fp8":
+        policy.update(fp8=True, lora={"rank": 64, "alpha": 128, "type": "lora",
+                                      "target_modules": ["linear_q_down_proj", "linear_q_up_proj", "linear_kv_down_proj",
+                                                         "linear_kv_up_proj", "linear_proj"]})
+        ppo["grpo_kl_loss_beta"] = 0.0
+        opt.update(lr=2e-5, weight_decay=0.0)
+    if args.config == "longctx":
+        cfg = from_dict(RlConfig, {
+            "training": {"train_gbs": args.sequences, "train_mbs": 1, "seq_length": args.seq_len, "seed": 1234,
+                         "total_ppo_step": 1000, "per_token_loss": True},
+            "policy": policy, "optimizer": {"lr": 1e-5, "lr_decay_style": "constant", "weight_decay": 0.1,
+                                            "max_grad_norm": 1.0}})
+        return cfg, tp, dp, 0
     cfg = from_dict(RlConfig, {
         "training": {"rollout_gbs": prompts_per_dp * dp, "sampling_repeat_n": n, "train_gbs": prompts_per_dp * dp * n,
                      "train_mbs": 1, "seed": 1234, "total_ppo_step": 1000},
-        "policy": {"model_arch": args.model, "recompute": args.recompute,
-                   "recompute_num_layers": args.recompute_layers, "share_rollout_weights": True,
-                   "dist_config": {"tensor_model_parallel_size": tp, "sequence_parallel": tp > 1},
-                   "dynamic_mbs_target_seqlen": args.mb_tokens},
-        "optimizer": {"lr": 1e-6, "lr_decay_style": "constant", "weight_decay": 0.01, "max_grad_norm": 1.0},
+        "policy": policy, "optimizer": opt,
         "sampler": {"infer_engine_configs": [{"generate_max_tokens": args.max_response, "temperature": 1.0,
                                                "max_model_len": args.prompt_len + args.max_response,
                                                "kv_block_size": 16, "seed": 42,
                                                "dist_config": {"tensor_model_parallel_size": tp}}]},
         "data": {"max_prompt_length": args.prompt_len},
-        "ppo": {"ppo_ratio_eps": 0.2, "grpo_kl_loss_beta": 0.001, "advantage_type": "grpo", "loss_func": "grpo"},
+        "ppo": ppo,
     })
     return cfg, tp, dp, prompts_per_dp
+
+
+def long_context_batch(step: int, dp_rank: int, sequences: int, seq_len: int):
+    """``sequences`` packed streams of ``seq_len`` tokens, each a run of documents whose lengths are
+    lognormal(mu=7, sigma=1.2) clipped to [64, 32768]; token ids uniform in [100, 128000); loss on every token.
+    Returned as one sample per document (the engine packs them back into ``seq_len``-token micro-batches), in pinned
+    host memory."""
+    import torch
+    g = torch.Generator().manual_seed(7919 * step + dp_rank)
+    samples = []
+    for _ in range(sequences):
+        left = seq_len
+        while left > 0:
+            n = int(torch.empty(1).log_normal_(7.0, 1.2, generator=g).clamp_(64, 32768).item())
+            n = min(n, left)
+            if left - n < 64:
+                n = left
+            toks = torch.randint(100, 128000, (n,), generator=g, dtype=torch.int64).pin_memory()
+            m = torch.ones(n, dtype=torch.float32)
+            m[-1] = 0.0
+            samples.append({"tokens": toks, "loss_mask": m, "prompt_length": 0})
+            left -= n
+    return samples
 
 
 def main():
@@ -188,12 +248,16 @@ def main():
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference", "nccl_eager"])
-    ap.add_argument("--model", default="qwen2.5-7b")
+    ap.add_argument("--config", default="grpo7b", choices=sorted(CONFIGS),
+                    help="benchmark recipe; the headline (and the default) is grpo7b")
+    ap.add_argument("--model", default=None)
     ap.add_argument("--layers", type=int, default=None, help="debug only: truncating the model invalidates the number")
-    ap.add_argument("--prompts-per-gpu", type=int, default=8)
-    ap.add_argument("--samples", type=int, default=8)
-    ap.add_argument("--prompt-len", type=int, default=256)
-    ap.add_argument("--max-response", type=int, default=1024)
+    ap.add_argument("--prompts-per-gpu", type=int, default=None)
+    ap.add_argument("--samples", type=int, default=None)
+    ap.add_argument("--prompt-len", type=int, default=None)
+    ap.add_argument("--max-response", type=int, default=None)
+    ap.add_argument("--seq-len", type=int, default=None, help="longctx: tokens per packed sequence")
+    ap.add_argument("--sequences", type=int, default=None, help="longctx: sequences per global batch")
     ap.add_argument("--mb-tokens", type=int, default=None,
                     help="token budget of a packed micro-batch; default 8192 on one GPU (activations share the GPU with "
                     "the optimizer state of the whole model), 16384 when tensor parallelism halves the state")
@@ -202,6 +266,12 @@ def main():
     ap.add_argument("--recompute-layers", type=int, default=None,
                     help="with --recompute full: recompute only the first N layers")
     args = ap.parse_args()
+    for k, v in CONFIGS[args.config].items():
+        if k != "kind" and getattr(args, k, None) is None:
+            setattr(args, k, v)
+    args.kind = CONFIGS[args.config]["kind"]
+    if args.kind == "sft":
+        args.mb_tokens = args.mb_tokens or args.seq_len
     if args.mb_tokens is None:
         args.mb_tokens = 8192 if args.gpus == 1 else 16384
     if args.recompute is None:
@@ -228,8 +298,9 @@ def main():
     if world > 1:
         ps.init_distributed("nccl")
     cfg, tp, dp, prompts_per_dp = build_config(args, world)
+    _, cp, ep = parallelism(args.config, world)
     if world > 1:
-        ps.initialize_model_parallel(tp=tp)
+        ps.initialize_model_parallel(tp=tp, cp=cp, ep=ep)
     if args.impl == "nccl_eager":
         # library build of the same step: cuBLAS GEMMs, the library's fused attention, PyTorch elementwise ops, NCCL
         # collectives at the call sites of the fused kernels, a CUDA-graph decode loop over library ops, and a weight
@@ -242,19 +313,38 @@ def main():
             os.environ[k] = "0"
     over = {"num_layers": args.layers} if args.layers else {}
     mcfg = get_preset(args.model, **over)
-    trainer = GrpoTrainer(cfg, model_cfg=mcfg, reward_fn=synthetic_reward).setup()
-    dp_rank = ps.get_data_parallel_rank()
-
-    # synthetic prompts live in pinned host memory; every step copies its prompts to the device inside the timed region
-    g = torch.Generator().manual_seed(1000 + dp_rank)
     total_steps = args.warmup + args.steps
-    host_prompts = torch.randint(100, 150000, (total_steps, prompts_per_dp, args.prompt_len), generator=g,
-                                 dtype=torch.int64).pin_memory()
     from gcore_b200.utils import io_counters
+    if args.kind == "sft":
+        from gcore_b200.engine import get_training_engine
+        cfg.policy.without_ref = True
+        engine = get_training_engine(cfg.policy, cfg.optimizer, cfg.training, None, model_cfg=mcfg, total_steps=1000)
+        engine.setup_model_and_get_optimizer()
+        dp_rank = ps.get_data_parallel_rank()
+        per_dp = max(args.sequences // dp, 1)
+        # every step's documents are generated ahead of the timed region, in pinned host memory
+        batches = [long_context_batch(i, dp_rank, per_dp, args.seq_len) for i in range(total_steps)]
+        trainer = None
 
-    def run_step(i):
-        # the engine uploads the prompt tokens (pinned host -> device) when it prefills them
-        return trainer.step(host_prompts[i])
+        def run_step(i):
+            t0 = time.perf_counter()
+            m = engine.finetune_step(batches[i])          # uploads the tokens, returns the loss to the host
+            dt = time.perf_counter() - t0
+            m.update({"time_perf/step": dt, "time_perf/train_step": dt,
+                      "rollout-metrics/total_tokens": float(per_dp * dp * args.seq_len)})
+            return m
+    else:
+        trainer = GrpoTrainer(cfg, model_cfg=mcfg, reward_fn=synthetic_reward).setup()
+        dp_rank = ps.get_data_parallel_rank()
+        # synthetic prompts live in pinned host memory; every step copies its prompts to the device inside the timed
+        # region
+        g = torch.Generator().manual_seed(1000 + dp_rank)
+        host_prompts = torch.randint(100, 150000, (total_steps, prompts_per_dp, args.prompt_len), generator=g,
+                                     dtype=torch.int64).pin_memory()
+
+        def run_step(i):
+            # the engine uploads the prompt tokens (pinned host -> device) when it prefills them
+            return trainer.step(host_prompts[i])
 
     def barrier():
         if world > 1:
@@ -269,8 +359,8 @@ def main():
             sampler.start()
         m = run_step(i)
         if rank == 0:
-            print(f"[warmup {i}] step {m['time_perf/step']:.2f}s rollout {m['time_perf/rollout']:.2f}s "
-                  f"logps {m['time_perf/compute_logps']:.2f}s train {m['time_perf/train_step']:.2f}s "
+            print(f"[warmup {i}] step {m['time_perf/step']:.2f}s rollout {m.get('time_perf/rollout', 0.0):.2f}s "
+                  f"logps {m.get('time_perf/compute_logps', 0.0):.2f}s train {m['time_perf/train_step']:.2f}s "
                   f"tokens {m['rollout-metrics/total_tokens']:.0f}", file=sys.stderr, flush=True)
     _lib.check_device_errors()
     # the model, engine and optimizer objects built so far are permanent: keep the cyclic collector from walking them
@@ -310,21 +400,15 @@ def main():
     if rank == 0:
         value = tokens / dev_s
         out = {
-            "metric": "grpo_rollout_plus_train_tokens_per_s", "value": round(value, 1), "unit": "tokens/s",
+            "metric": ("grpo_rollout_plus_train_tokens_per_s" if args.kind == "grpo" else "sft_train_tokens_per_s"),
+            "value": round(value, 1), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_s / args.steps * 1e3, 1),
             "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": vs_baseline(args, world, value), "dtype": "bf16", "data": "synthetic",
+            "vs_baseline": vs_baseline(args, world, value),
+            "dtype": "bf16 (frozen base projections block-scaled e4m3)" if args.config == "dsv3fp8" else "bf16",
+            "data": "synthetic", "recipe": args.config,
             "impl": args.impl,
-            "config": {"model": args.model + (f"-{args.layers}layers-DEBUG" if args.layers else ""),
-                       "global_batch": int(cfg.training.rollout_gbs * args.samples),
-                       "seq_len": args.prompt_len + args.max_response,
-                       "parallelism": f"tp{tp}dp{dp}", "prompts": int(cfg.training.rollout_gbs),
-                       "samples_per_prompt": args.samples, "weights": "random-init",
-                       "resync": ("zero-copy shared parameter storage (trainer and rollout engine, same TP layout)"
-                                  if cfg.policy.share_rollout_weights else
-                                  "bucketed copy into a separate rollout copy (rebuilt every step, freed after rollout)"),
-                       "l2": "inputs (15 GB of weights per pass) are larger than L2", "recompute": args.recompute, "recompute_layers": args.recompute_layers,
-                       "micro_batch_tokens": args.mb_tokens},
+            "config": bench_config_record(args, cfg, tp, cp, ep, dp),
             "clocks": clocks,
             "e2e": {"value": round(tokens / wall, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d / args.steps),
                     "d2h_bytes_per_step": int(d2h / args.steps)},
@@ -333,7 +417,8 @@ def main():
             "resync_ms": round(phase.get("time_perf/update_weights", 0.0) * 1e3, 3),
             "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1),
             "peak_reserved_gb": round(torch.cuda.max_memory_reserved() / 2**30, 1),
-            "reward_mean": round(m["rollout-rewards/mean"], 4),
+            **({"reward_mean": round(m["rollout-rewards/mean"], 4)} if args.kind == "grpo"
+               else {"lm_loss": round(float(m["lm_loss"]), 4)}),
         }
         print(json.dumps(out), flush=True)
     if world > 1:
@@ -342,11 +427,28 @@ def main():
     return 0
 
 
+def bench_config_record(args, cfg, tp, cp, ep, dp):
+    par = f"tp{tp}" + (f"cp{cp}" if cp > 1 else "") + (f"ep{ep}" if ep > 1 else "") + f"dp{dp}"
+    rec = {"model": args.model + (f"-{args.layers}layers-DEBUG" if args.layers else ""), "parallelism": par,
+           "weights": "random-init", "recompute": args.recompute, "recompute_layers": args.recompute_layers,
+           "micro_batch_tokens": args.mb_tokens, "l2": "inputs (weights of every pass) are larger than L2"}
+    if args.kind == "sft":
+        rec.update(global_batch=int(args.sequences), seq_len=int(args.seq_len),
+                   documents="lognormal(7, 1.2) clipped to [64, 32768], packed")
+        return rec
+    rec.update(global_batch=int(cfg.training.rollout_gbs * args.samples), seq_len=args.prompt_len + args.max_response,
+               prompts=int(cfg.training.rollout_gbs), samples_per_prompt=args.samples,
+               resync=("zero-copy shared parameter storage (trainer and rollout engine, same layout)"
+                       if cfg.policy.share_rollout_weights else
+                       "bucketed copy into a separate rollout copy (rebuilt every step, freed after rollout)"))
+    return rec
+
+
 def vs_baseline(args, world, value):
     """value / the library (``nccl_eager``) build's measured value of the same config at the same GPU count, from the
     committed ``baseline/measured_baselines.json``; None when that row has not been measured.  (The reference
     publishes no number for this metric, and cannot run here: the library build is its stand-in.)"""
-    if args.impl != "native" or args.layers:
+    if args.impl != "native" or args.layers or args.config != "grpo7b":
         return None
     try:
         rows = json.load(open(os.path.join(ROOT, "baseline", "measured_baselines.json")))["nccl_eager"]
@@ -358,7 +460,11 @@ def vs_baseline(args, world, value):
 
 def trainer_launches(trainer) -> int:
     from gcore_b200.ops import attention, fused, gemm, optim, rl, vocab
-    eager = sum(sum(m.LAUNCHES.values()) for m in (attention, fused, gemm, optim, rl, vocab))
+    from gcore_b200.ops import router
+    from gcore_b200.parallel import ep_fused, symm
+    eager = sum(sum(m.LAUNCHES.values()) for m in (attention, fused, gemm, optim, rl, vocab, router, ep_fused, symm))
+    if trainer is None:
+        return eager
     eng = trainer.engine
     return eager + eng.stats["graph_replays"] * getattr(eng, "graph_launches", 0)
 

@@ -55,6 +55,9 @@ def kernels() -> ctypes.CDLL:
         st2 = os.environ.get("GCORE_2CTA_STAGES")
         if st2 is not None and hasattr(lib, "gk_gemm_2cta_set_stages"):
             lib.gk_gemm_2cta_set_stages(int(st2))
+        gm = os.environ.get("GCORE_GEMM_GROUP_M")      # tile rows per band of the dense GEMMs' tile order (0 = row-fastest)
+        if gm is not None and hasattr(lib, "gk_gemm_set_raster"):
+            lib.gk_gemm_set_raster(int(gm))
         cap = os.environ.get("GCORE_DECODE_SMEM_KB")   # shared-memory budget of decode GEMM CTAs (0 = full ring)
         if cap is not None and hasattr(lib, "gk_gemm_set_decode_smem_cap"):
             lib.gk_gemm_set_decode_smem_cap(int(cap) * 1024)
@@ -131,6 +134,7 @@ def _declare_kernels(lib: ctypes.CDLL):
     d("gk_rope_table", [P, P, P, I, I, I, I, L, I, I, P])
     d("gk_gemm_2cta", [P, L, L, I, P, L, L, I, P, L, I, I, P, I, F, I, I, I, P, P])
     d("gk_gemm_set_decode_smem_cap", [I], None)
+    d("gk_gemm_set_raster", [I], None)
     d("gk_gemm_skinny", [P, L, P, L, P, L, I, P, I, I, I, I, I, I, P, P])
     d("gk_gemm_skinny_max_clusters", [I, I, I])
     d("gk_gemm_comm", [I, P, L, P, L, L, I, P, L, P, I, I, I, I, I, I, I, ctypes.c_uint, P, L, P, P])
@@ -167,7 +171,7 @@ def _declare_kernels(lib: ctypes.CDLL):
     d("gk_linear_ce_splits", [I, I])
     d("gk_linear_ce_fwd", [P, L, P, L, P, F, I, I, I, I, I, P, P, P])
     d("gk_logprob_entropy_bwd", [P, I, L, P, P, P, P, P, F, I, I, L, P])
-    d("gk_sample", [P, I, L, I, I, F, I, P, P, P, P, P, I, P])
+    d("gk_sample", [P, I, L, I, I, F, I, P, P, P, P, P, I, I, P])
     d("gk_sample_combine", [P, I, I, P, P, P])
     d("gk_sample_filtered", [P, I, L, I, F, I, F, F, I, P, P, P, P, P, I, P])
     d("gk_grpo_loss", [P, P, P, P, P, L, F, F, F, F, F, F, P, P, P, P])

@@ -52,6 +52,7 @@ struct P2 {
   float alpha;
   int* err;
   int stages;
+  int group_m;
 };
 
 __device__ __forceinline__ uint32_t cta_rank() {
@@ -206,8 +207,10 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t ph = 0;
     bool ok = true;
     for (int tile = cluster_id; tile < ntiles && ok; tile += n_clusters) {
-      const int m0 = (tile % mt) * TM + static_cast<int>(rank) * BMH;
-      const int n0 = (tile / mt) * TN + static_cast<int>(rank) * BNH;
+      int mi, ni;
+      raster_tile(tile, mt, nt, p.group_m, mi, ni);
+      const int m0 = mi * TM + static_cast<int>(rank) * BMH;
+      const int n0 = ni * TN + static_cast<int>(rank) * BNH;
       for (int kb = 0; kb < kblocks; ++kb) {
         ok = mbar_wait(&empty[s], ph ^ 1, p.err, ERR_WAIT_EMPTY);
         if (!ok) break;
@@ -288,8 +291,10 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       ok = mbar_wait(&tfull[acc], pacc, p.err, ERR_WAIT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
-      const int row = (tile % mt) * TM + static_cast<int>(rank) * BMH + row_in_half;
-      const int col0 = (tile / mt) * TN;
+      int mi, ni;
+      raster_tile(tile, mt, nt, p.group_m, mi, ni);
+      const int row = mi * TM + static_cast<int>(rank) * BMH + row_in_half;
+      const int col0 = ni * TN;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * TN;
 #pragma unroll 1
       for (int c = 0; c < TN / 32; ++c) {
@@ -325,6 +330,7 @@ int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const P2& p, cudaStr
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(THREADS, 1, 1);
   P2 q = p;
+  q.group_m = gk::raster_group_m();
   q.stages = stages_setting() < 2 ? 2 : (stages_setting() > MAX_STAGES ? MAX_STAGES : stages_setting());
   cfg.dynamicSmemBytes = q.stages * STAGE_BYTES + 1024 + 256;
   cfg.stream = st;

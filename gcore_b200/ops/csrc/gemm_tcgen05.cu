@@ -56,6 +56,7 @@ struct GemmParams {
   int* counters;
   int* err;
   int stages;   // shared-memory ring depth actually used (<= Cfg::STAGES)
+  int group_m;  // tile order of dense problems (host_utils.h: raster_tile)
   int a_early;  // operand A does not depend on the kernel before this one (decode: A is the weight): its first
                 // tiles are requested before the programmatic-dependency wait, while the predecessor still runs
 };
@@ -131,8 +132,10 @@ __device__ __forceinline__ Tile decode_tile(const GemmParams& p, const int* s_pr
     const int mt = (p.M + BM - 1) / BM;
     t.ks = tile % p.ksplit;
     const int r = tile / p.ksplit;
-    t.m0 = (r % mt) * BM;
-    t.n0 = (r / mt) * BN;
+    int mi, ni;
+    raster_tile(r, mt, nt, p.group_m, mi, ni);
+    t.m0 = mi * BM;
+    t.n0 = ni * BN;
     const int kb_total = (p.K + BK - 1) / BK;
     const int per = (kb_total + p.ksplit - 1) / p.ksplit;
     const int kb0 = t.ks * per;
@@ -504,6 +507,7 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams
   GemmParams q = p;
   q.stages = C::STAGES;
   q.a_early = 0;
+  q.group_m = gk::raster_group_m();
   if constexpr (!A_MN && !B_MN && BN <= 128) {
     if (p.transposed && p.group_mode == 0) {
       // decode (swap-AB): A is the weight, which no earlier kernel of the chain writes: its first tiles are requested
@@ -527,6 +531,9 @@ using namespace gk;
 
 // Shared-memory budget of decode-shaped (swap-AB) launches; 0 restores the full-depth ring and the late A loads.
 GK_EXPORT void gk_gemm_set_decode_smem_cap(int bytes) { gk::decode_smem_cap() = bytes; }
+
+// Tile rows per band of the dense GEMMs' tile order (host_utils.h: raster_group_m); 0 or 1 = row-fastest order.
+GK_EXPORT void gk_gemm_set_raster(int group_m) { gk::raster_group_m() = group_m; }
 
 // Scratch requirement of split-K for a given problem: floats of workspace and ints of counters.
 GK_EXPORT void gk_gemm_splitk_scratch(int M, int N, int bn, int ksplit, long long* ws_floats, long long* counters) {

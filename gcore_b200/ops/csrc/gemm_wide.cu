@@ -33,6 +33,7 @@ struct WParams {
   int bias_fp32;
   float alpha;
   int* err;
+  int group_m;
 };
 
 // 32 consecutive accumulator columns of one output row
@@ -137,7 +138,9 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t ph = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-      const int m0 = (tile % mt) * BMW, n0 = (tile / mt) * BN;
+      int mi, ni;
+      raster_tile(tile, mt, nt, p.group_m, mi, ni);
+      const int m0 = mi * BMW, n0 = ni * BN;
       for (int kb = 0; kb < kblocks; ++kb) {
         ok = mbar_wait(&empty[s], ph ^ 1, p.err, ERR_WAIT_EMPTY);
         if (!ok) break;
@@ -211,7 +214,9 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t pt = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-      const int m0 = (tile % mt) * BMW, n0 = (tile / mt) * BN;
+      int mi, ni;
+      raster_tile(tile, mt, nt, p.group_m, mi, ni);
+      const int m0 = mi * BMW, n0 = ni * BN;
       if (kblocks > 0) {
         ok = mbar_wait(tfull, pt, p.err, ERR_WAIT_TMEM_FULL);
         if (!ok) break;
@@ -280,6 +285,7 @@ GK_EXPORT int gk_gemm_wide(const void* A, long long lda, long long a_rows, int a
   WParams p;
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32; p.accumulate = accumulate;
   p.bias = bias; p.bias_fp32 = bias_fp32; p.alpha = alpha; p.err = err;
+  p.group_m = gk::raster_group_m();
   const long long tiles = static_cast<long long>((M + BMW - 1) / BMW) * ((N + BN - 1) / BN);
   const int grid = static_cast<int>(tiles < gk::sm_count() ? tiles : gk::sm_count());
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);

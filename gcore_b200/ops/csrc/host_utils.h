@@ -105,6 +105,32 @@ inline int& decode_smem_cap() {
   return cap;
 }
 
+// ---- output-tile order of the persistent dense GEMMs.  Tiles are handed out in bands of `raster_group_m()` tile rows:
+// inside a band the row index runs fastest, so the CTAs that run at the same time cover a patch of about group_m
+// tile rows x (CTAs / group_m) tile columns.  Every operand tile is then wanted by a handful of CTAs at a time (and
+// is re-read from L2 while it is still hot) instead of one B tile by every CTA of the wave at once, which
+// concentrates the requests on the few L2 slices that hold it.  0 or 1 = plain row-fastest order.
+inline int& raster_group_m() {
+  static int g = 8;
+  return g;
+}
+#ifdef __CUDACC__
+__device__ __forceinline__ void raster_tile(int tile, int mt, int nt, int group_m, int& mi, int& ni) {
+  if (group_m <= 1) {
+    mi = tile % mt;
+    ni = tile / mt;
+    return;
+  }
+  const int per_band = group_m * nt;
+  const int band = tile / per_band;
+  const int first = band * group_m;
+  const int rows = mt - first < group_m ? mt - first : group_m;
+  const int r = tile - band * per_band;
+  mi = first + r % rows;
+  ni = r / rows;
+}
+#endif
+
 // ---- programmatic dependent launch: a kernel launched through launch_k may start its prologue while the previous
 // kernel of the stream is still draining; it must call pdl_wait() before it touches global memory, and it calls
 // pdl_launch_dependents() first so that its own successor may be scheduled early.  Both instructions are no-ops in a

@@ -182,7 +182,11 @@ __global__ void __launch_bounds__(256) sample_kernel(const void* __restrict__ lo
   int bidx = 0;
   const unsigned long long seed = static_cast<unsigned long long>(seeds ? seeds[row] : 0);
   const unsigned long long step = static_cast<unsigned long long>(steps ? steps[row] : 0);
-  for (int j = threadIdx.x; j < V; j += blockDim.x) {
+  // gridDim.y CTAs share a row: each takes a contiguous slice of the vocabulary and writes a partial
+  const int per = (V + gridDim.y - 1) / gridDim.y;
+  const int j0 = blockIdx.y * per;
+  const int j1 = j0 + per < V ? j0 + per : V;
+  for (int j = j0 + threadIdx.x; j < j1; j += blockDim.x) {
     const float z = load_logit(logits, is_fp32, base + j) * inv_temp;
     online_add(o, z);
     float score = z;
@@ -208,7 +212,7 @@ __global__ void __launch_bounds__(256) sample_kernel(const void* __restrict__ lo
     for (int i = 1; i < nw; ++i)
       if (s_best[i] > best || (s_best[i] == best && s_idx[i] < bidx)) { best = s_best[i]; bidx = s_idx[i]; bz = s_bz[i]; }
     if (partial_out) {
-      float* p = partial_out + row * 6;
+      float* p = partial_out + (static_cast<long long>(blockIdx.y) * gridDim.x + row) * 6;
       p[0] = o.m; p[1] = o.s; p[2] = o.sz; p[3] = best; p[4] = __int_as_float(bidx); p[5] = bz;
     } else {
       tokens[row] = bidx;
@@ -359,12 +363,15 @@ GK_EXPORT int gk_logprob_entropy_bwd(void* logits, int is_fp32, long long ld, co
   return launch_status();
 }
 
+// slices > 1: every row is shared by `slices` CTAs and `partial` receives [slices, B, 6] (merged by gk_sample_combine
+// with R = slices, or R = ranks x slices after an all-gather); the draw does not depend on the slicing.
 GK_EXPORT int gk_sample(const void* logits, int is_fp32, long long ld, int V, int vocab_start, float inv_temp,
                         int greedy, const long long* seeds, const int* steps, long long* tokens, float* logp,
-                        float* partial, int B, void* stream) {
+                        float* partial, int B, int slices, void* stream) {
   if (B == 0) return 0;
-  sample_kernel<<<B, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(logits, is_fp32, ld, V, vocab_start, inv_temp,
-                                                                       greedy, seeds, steps, tokens, logp, partial);
+  if (slices < 1 || (slices > 1 && !partial)) return -1;
+  sample_kernel<<<dim3(B, slices), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      logits, is_fp32, ld, V, vocab_start, inv_temp, greedy, seeds, steps, tokens, logp, partial);
   return launch_status();
 }
 

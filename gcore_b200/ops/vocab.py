@@ -237,21 +237,26 @@ def sample(logits, temperature, seeds, steps, greedy=False, tp_group=None, vocab
     logp = torch.empty(B, dtype=torch.float32, device=logits.device)
     lib = _lib.kernels()
     tp = dist.get_world_size(tp_group) if tp_group is not None else 1
+    # a row of a large vocabulary is shared by several CTAs (the random stream is evaluated per element: one CTA per
+    # row leaves most of the GPU idle at decode batch sizes); their partials merge like tensor-parallel shards
+    slices = max(1, min(8, 592 // max(B, 1))) if V >= 16384 else 1
     LAUNCHES["vocab"] += 1
-    if tp == 1:
+    if tp == 1 and slices == 1:
         _lib.check(lib.gk_sample(_lib.ptr(logits), int(logits.dtype == torch.float32), logits.stride(0), V, vocab_start,
                                  inv_temp, int(greedy), _lib.ptr(seeds), _lib.ptr(steps), _lib.ptr(tokens),
-                                 _lib.ptr(logp), None, B, _lib.stream_ptr()), "sample")
+                                 _lib.ptr(logp), None, B, 1, _lib.stream_ptr()), "sample")
         return tokens, logp
-    part = torch.empty(B, 6, dtype=torch.float32, device=logits.device)
+    part = torch.empty(slices, B, 6, dtype=torch.float32, device=logits.device)
     _lib.check(lib.gk_sample(_lib.ptr(logits), int(logits.dtype == torch.float32), logits.stride(0), V, vocab_start,
                              inv_temp, int(greedy), _lib.ptr(seeds), _lib.ptr(steps), None, None, _lib.ptr(part), B,
-                             _lib.stream_ptr()), "sample")
-    allp = torch.empty(tp, B, 6, dtype=torch.float32, device=logits.device)
-    dist.all_gather_into_tensor(allp, part, group=tp_group)
+                             slices, _lib.stream_ptr()), "sample")
+    if tp > 1:
+        allp = torch.empty(tp * slices, B, 6, dtype=torch.float32, device=logits.device)
+        dist.all_gather_into_tensor(allp, part, group=tp_group)
+        part = allp
     LAUNCHES["vocab"] += 1
-    _lib.check(lib.gk_sample_combine(_lib.ptr(allp), tp, B, _lib.ptr(tokens), _lib.ptr(logp), _lib.stream_ptr()),
-               "sample_combine")
+    _lib.check(lib.gk_sample_combine(_lib.ptr(part), part.shape[0], B, _lib.ptr(tokens), _lib.ptr(logp),
+                                     _lib.stream_ptr()), "sample_combine")
     return tokens, logp
 
 

@@ -288,6 +288,26 @@ def test_filtered_sampling_matches_sort_based_definition(top_k, top_p, min_p):
     assert torch.equal(tok_g, logits.argmax(-1))
 
 
+def test_sampling_is_independent_of_row_slicing():
+    """Large vocabularies are sampled by several CTAs per row; the draw and its log-prob equal the one-CTA result."""
+    from gcore_b200.ops import _lib
+    from gcore_b200.ops.vocab import sample
+    torch.manual_seed(29)
+    B, V = 24, 40000
+    logits = (torch.randn(B, V, device=DEV) * 3).contiguous()
+    seeds = torch.arange(B, device=DEV, dtype=torch.int64) + 5
+    steps = torch.full((B,), 11, device=DEV, dtype=torch.int32)
+    tok, lp = sample(logits, 0.9, seeds, steps)
+    tok1 = torch.empty(B, dtype=torch.int64, device=DEV)
+    lp1 = torch.empty(B, dtype=torch.float32, device=DEV)
+    _lib.check(_lib.kernels().gk_sample(_lib.ptr(logits), 1, V, V, 0, 1.0 / 0.9, 0, _lib.ptr(seeds), _lib.ptr(steps),
+                                        _lib.ptr(tok1), _lib.ptr(lp1), None, B, 1, _lib.stream_ptr()), "sample")
+    assert torch.equal(tok, tok1)
+    assert torch.allclose(lp, lp1, atol=1e-4)
+    ref = torch.log_softmax(logits / 0.9, -1).gather(-1, tok[:, None]).squeeze(-1)
+    assert torch.allclose(lp, ref, atol=1e-3)
+
+
 def test_sampling_distribution_and_logprob():
     from gcore_b200.ops.vocab import sample
     torch.manual_seed(8)

@@ -221,9 +221,15 @@ class TrainingEngine:
         if kind is None:
             return
         from ..models.gpt import ParallelLinear
+        from ..models.moe import Experts
         for name, mod in self.model.named_modules():
             if isinstance(mod, ParallelLinear) and "decoder.layers" in name and mod.in_local % 128 == 0 \
                     and mod.out_local > 1:
+                mod.precision = kind
+                self.lowp_modules.append(name)
+            elif isinstance(mod, Experts) and kind == "fp8":
+                # grouped expert projections on the grouped block-fp8 GEMM (shapes that are not multiples of 128
+                # stay bf16 inside grouped_linear)
                 mod.precision = kind
                 self.lowp_modules.append(name)
 

@@ -168,9 +168,51 @@ class _GroupedLinearFn(torch.autograd.Function):
         return dx, dw, None, None
 
 
-def grouped_linear(x, w, offsets):
-    """``y[seg_g] = x[seg_g] @ w[g]^T`` with autograd; ``w`` [G, N, K]."""
+class _GroupedFp8LinearFn(torch.autograd.Function):
+    """Grouped expert projection in block-scaled e4m3 (activations 1x128 per token, weights 128x128, cached until the
+    parameter changes); like the dense fp8 linear, the backward runs in bf16 against the dequantised weight, and the
+    weight gradient is skipped for a frozen base (the reference's grouped fp8 linear:
+    gpatch_v4/models/deepseek_v4/fp8.py:181-394)."""
+
+    @staticmethod
+    def forward(ctx, x, w, offsets, main_grad, cache):
+        from ..ops import quant
+        G, N, K = w.shape
+        ver = (w._version, w.data_ptr())
+        if cache.get("ver") != ver:
+            q, s = quant.quant_weight_128x128(w.detach().to(torch.bfloat16).reshape(G * N, K).contiguous())
+            cache.update(ver=ver, q=q, s=s)
+        aq, as_ = quant.quant_act_1x128(x.to(torch.bfloat16).contiguous())
+        y = quant.gemm_fp8_grouped(aq, as_, cache["q"], cache["s"], offsets, G, out_dtype=x.dtype
+                                   if x.dtype in (torch.bfloat16, torch.float32) else torch.bfloat16)
+        ctx.save_for_backward(x if w.requires_grad else x.new_empty(0), w, offsets)
+        ctx.cache, ctx.main_grad = cache, main_grad
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops import quant
+        x, w, offsets = ctx.saved_tensors
+        G, N, K = w.shape
+        dy = dy.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            w_dq = quant.dequant_128x128(ctx.cache["q"], ctx.cache["s"])[:G * N, :K].to(dy.dtype).view(G, N, K)
+            dx = grouped_gemm(dy, w_dq.contiguous(), offsets, b_mn=True)
+        if ctx.needs_input_grad[1]:
+            if ctx.main_grad is not None:
+                grouped_wgrad(dy, x, offsets, G, out=ctx.main_grad, accumulate=True)
+            else:
+                dw = grouped_wgrad(dy, x, offsets, G).to(w.dtype)
+        return dx, dw, None, None, None
+
+
+def grouped_linear(x, w, offsets, precision=None, cache=None):
+    """``y[seg_g] = x[seg_g] @ w[g]^T`` with autograd; ``w`` [G, N, K].  ``precision="fp8"`` runs the product on the
+    grouped block-fp8 GEMM (N and K multiples of 128)."""
     mg = getattr(w, "main_grad", None) if w.requires_grad else None
+    if precision == "fp8" and w.shape[1] % 128 == 0 and w.shape[2] % 128 == 0:
+        return _GroupedFp8LinearFn.apply(x, w, offsets, mg, cache if cache is not None else {})
     return _GroupedLinearFn.apply(x, w, offsets, mg)
 
 
@@ -188,13 +230,15 @@ class Experts(nn.Module):
         self.linear_fc1.weight.is_expert = True
         self.linear_fc2.weight.is_expert = True
         self.lora_fc1 = self.lora_fc2 = None   # models/lora.py::ExpertLoRA when the experts are adapted
+        self.precision = None                  # None (bf16) | "fp8": grouped block-fp8 GEMM (policy.fp8)
+        self._fp8_cache = ({}, {})
 
     def forward(self, x_perm, offsets):
-        h = grouped_linear(x_perm, self.linear_fc1.weight, offsets)
+        h = grouped_linear(x_perm, self.linear_fc1.weight, offsets, self.precision, self._fp8_cache[0])
         if self.lora_fc1 is not None:
             h = h + self.lora_fc1(x_perm, offsets).to(h.dtype)
         h = fused.swiglu(h)
-        y = grouped_linear(h, self.linear_fc2.weight, offsets)
+        y = grouped_linear(h, self.linear_fc2.weight, offsets, self.precision, self._fp8_cache[1])
         if self.lora_fc2 is not None:
             y = y + self.lora_fc2(h, offsets).to(y.dtype)
         return y

@@ -142,6 +142,7 @@ def _declare_kernels(lib: ctypes.CDLL):
     d("gk_weight_quant_128x128", [P, P, P, P, I, I, I, P])
     d("gk_fp4_quant_1x32", [P, P, P, P, P, L, P])
     d("gk_gemm_fp8_blockscaled", [P, L, P, L, P, P, P, L, I, I, I, I, P, P])
+    d("gk_gemm_fp8_grouped", [P, L, P, L, P, P, P, L, I, I, I, I, P, I, P, P])
     d("gk_zero1_step", [I, P, I, I, L, L, P, P, P, P, F, P, P, F, F, F, F, F, I, I, P])
     d("gk_peer_barrier", [P, I, I, I, ctypes.c_uint, P, P])
     d("gk_ep_plan", [P, P, I, I, I, I, I, ctypes.c_uint, P, P, P, P, P])

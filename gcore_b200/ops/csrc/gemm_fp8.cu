@@ -31,7 +31,23 @@ struct P8 {
   long long ldc;
   int out_fp32;
   int* err;
+  // ragged-M groups (experts): rows [offsets[g], offsets[g+1]) of A multiply group g's weight, stored at rows
+  // [g * N, (g + 1) * N) of B with its scales at rows [g * ceil(N / 128), ...) of sB.  Offsets are multiples of 128
+  // (device array, G + 1 entries); M is the capacity of A, tiles at or beyond offsets[G] are skipped.
+  const int* group_offsets;
+  int num_groups;
 };
+
+// group of the 128-row tile starting at row m0, or -1 when the tile lies beyond the last group
+__device__ __forceinline__ int group_of(const P8& p, int m0) {
+  if (m0 >= p.group_offsets[p.num_groups]) return -1;
+  int lo = 0, hi = p.num_groups;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (p.group_offsets[mid] <= m0) lo = mid; else hi = mid;
+  }
+  return lo;
+}
 
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, P8 p) {
@@ -68,6 +84,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     long long it = 0;
     for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
       const int m0 = (tile % mt) * BM, n0 = (tile / mt) * BN;
+      int b_row = n0;
+      if (p.group_offsets) {
+        const int g = group_of(p, m0);
+        if (g < 0) continue;
+        b_row += g * p.N;
+      }
       for (int kb = 0; kb < KB && ok; ++kb, ++it) {
         const int s = static_cast<int>(it % STAGES);
         const uint32_t ph = static_cast<uint32_t>(it / STAGES) & 1;
@@ -77,7 +99,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           uint8_t* sa = smem + s * STAGE_BYTES;
           mbar_expect_tx(&full[s], STAGE_BYTES);
           tma_load_2d(sa, &tmA, &full[s], kb * BK, m0);
-          tma_load_2d(sa + BM * BK, &tmB, &full[s], kb * BK, n0);
+          tma_load_2d(sa + BM * BK, &tmB, &full[s], kb * BK, b_row);
         }
         __syncwarp();
       }
@@ -85,8 +107,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   } else if (warp == 1) {
     constexpr uint32_t idesc = make_idesc(BM, BN, 0, 0, 0, 0);  // e4m3 x e4m3 -> f32
     bool ok = true;
-    const long long total = static_cast<long long>((ntiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
-                                                   static_cast<int>(gridDim.x)) * KB;
+    long long live = 0;  // tiles of this CTA that carry rows (all of them for a dense problem)
+    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x)
+      live += (!p.group_offsets || (tile % mt) * BM < p.group_offsets[p.num_groups]) ? 1 : 0;
+    const long long total = live * KB;
     for (long long it = 0; it < total && ok; ++it) {
       const int s = static_cast<int>(it % STAGES), a = static_cast<int>(it % NBUF);
       ok = mbar_wait(&tempty[a], (static_cast<uint32_t>(it / NBUF) & 1) ^ 1, p.err, ERR_WAIT_TMEM_EMPTY);
@@ -114,10 +138,15 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
     const int m0 = (tile % mt) * BM, n0 = (tile / mt) * BN;
     const int row = m0 + quad * 32 + lane;
+    int nb = n0 / 128;
+    if (p.group_offsets) {
+      const int g = group_of(p, m0);
+      if (g < 0) continue;
+      nb += g * ((p.N + 127) / 128);
+    }
     float acc[HALF];
 #pragma unroll
     for (int j = 0; j < HALF; ++j) acc[j] = 0.f;
-    const int nb = n0 / 128;
     const float* sa_row = p.sA + static_cast<long long>(row < p.M ? row : 0) * KB;
     const float* sb_row = p.sB + static_cast<long long>(nb) * KB;
     float sc_next = (row < p.M ? sa_row[0] : 0.f) * sb_row[0];
@@ -195,6 +224,7 @@ GK_EXPORT int gk_gemm_fp8_blockscaled(const void* A, long long lda, const void* 
   }
   P8 p;
   p.M = M; p.N = N; p.K = K; p.sA = sA; p.sB = sB; p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32; p.err = err;
+  p.group_offsets = nullptr; p.num_groups = 0;
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   static int sms = 0;
   if (sms == 0) {
@@ -203,6 +233,32 @@ GK_EXPORT int gk_gemm_fp8_blockscaled(const void* A, long long lda, const void* 
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (sms <= 0) sms = 148;
   }
+  gemm_fp8_kernel<<<tiles < sms ? tiles : sms, THREADS, SMEM_BYTES, reinterpret_cast<cudaStream_t>(stream)>>>(tmA, tmB, p);
+  return gk::launch_status();
+}
+
+// Ragged-M grouped form (experts): A [M_cap, K] e4m3 with expert-sorted rows, group g = rows [offsets[g],
+// offsets[g+1]) (multiples of 128, device array of G + 1 ints); B [G * N, K] e4m3, sB [G * ceil(N/128), ceil(K/128)].
+// C [M_cap, N]: rows of group g hold A_g . B_g^T; rows beyond offsets[G] are not written.
+GK_EXPORT int gk_gemm_fp8_grouped(const void* A, long long lda, const void* B, long long ldb, const float* sA,
+                                  const float* sB, void* C, long long ldc, int out_fp32, int M_cap, int N, int K,
+                                  const int* offsets, int num_groups, int* err, void* stream) {
+  if ((lda & 15) || (ldb & 15) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -1;
+  if (num_groups < 1 || !offsets || M_cap % BM) return -5;
+  CUtensorMap tmA, tmB;
+  if (gk::make_tmap_2d(&tmA, A, 1, M_cap, K, lda, BM, BK, true)) return -2;
+  if (gk::make_tmap_2d(&tmB, B, 1, static_cast<uint64_t>(num_groups) * N, K, ldb, BN, BK, true)) return -3;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+      return -4;
+    configured = true;
+  }
+  P8 p;
+  p.M = M_cap; p.N = N; p.K = K; p.sA = sA; p.sB = sB; p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32; p.err = err;
+  p.group_offsets = offsets; p.num_groups = num_groups;
+  const int tiles = (M_cap / BM) * ((N + BN - 1) / BN);
+  const int sms = gk::sm_count();
   gemm_fp8_kernel<<<tiles < sms ? tiles : sms, THREADS, SMEM_BYTES, reinterpret_cast<cudaStream_t>(stream)>>>(tmA, tmB, p);
   return gk::launch_status();
 }

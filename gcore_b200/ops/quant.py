@@ -168,6 +168,34 @@ def gemm_fp8_blockscaled(a_q, a_s, b_q, b_s, out_dtype=torch.bfloat16):
     return out
 
 
+def gemm_fp8_grouped(a_q, a_s, b_q, b_s, offsets, num_groups: int, out_dtype=torch.bfloat16):
+    """Ragged-M grouped block-fp8 GEMM (experts): rows ``offsets[g]:offsets[g+1]`` of ``a_q`` [R, K] (multiples of
+    128; scales ``a_s`` [R, K/128]) multiply group g's weight ``b_q[g * N:(g + 1) * N]`` ([G * N, K] e4m3, 128x128
+    scales ``b_s`` [G * N / 128, K / 128]; N a multiple of 128 so that no scale block spans two experts).  Rows of the
+    output beyond ``offsets[G]`` are zero."""
+    R, K = a_q.shape
+    N = b_q.shape[0] // num_groups
+    assert N % 128 == 0 and R % 128 == 0, (N, R)
+    if not _lib.use_native(a_q) or not hasattr(_lib.kernels(), "gk_gemm_fp8_grouped"):
+        a = dequant_1x128(a_q, a_s)
+        b = dequant_128x128(b_q, b_s)[:num_groups * N, :K].view(num_groups, N, K)
+        out = torch.zeros(R, N, dtype=torch.float32, device=a_q.device)
+        off = offsets.tolist()
+        for g in range(num_groups):
+            if off[g + 1] > off[g]:
+                out[off[g]:off[g + 1]] = a[off[g]:off[g + 1]].float() @ b[g].float().t()
+        return out.to(out_dtype)
+    out = torch.zeros(R, N, dtype=out_dtype, device=a_q.device)
+    LAUNCHES["quant"] += 1
+    rc = _lib.kernels().gk_gemm_fp8_grouped(_lib.ptr(a_q), a_q.stride(0), _lib.ptr(b_q), b_q.stride(0),
+                                            _lib.ptr(a_s.contiguous()), _lib.ptr(b_s.contiguous()), _lib.ptr(out),
+                                            out.stride(0), int(out_dtype == torch.float32), R, N, K,
+                                            _lib.ptr(offsets.int().contiguous()), num_groups,
+                                            _lib.ptr(_lib.err_flag(a_q.device)), _lib.stream_ptr())
+    _lib.check(rc, "gemm_fp8_grouped")
+    return out
+
+
 class Fp8Linear(torch.nn.Module):
     """Frozen block-fp8 base weight (e4m3 + 128x128 fp32 scales); activations are quantised 1x128 on the fly.  Used
     for the fp8 rollout path and as the frozen base under LoRA."""

@@ -787,3 +787,23 @@ def test_async_controller_hands_a_batched_sampler_all_groups_of_a_round_at_once(
     assert [s["group_id"] for s in batch] == [0] * 3 + [1] * 3 + [2] * 3 + [3] * 3
     assert [s["tokens"][-1] for s in batch[:3]] == [0, 1, 2]
     c.shutdown()
+
+
+def test_grouped_fp8_expert_projection_cpu_definition():
+    """``policy.fp8`` reaches the grouped expert projections: forward through quantise -> grouped product (here the
+    PyTorch definition of the kernel), backward in the compute dtype; close to the unquantised projection."""
+    import torch
+    from gcore_b200.models.moe import grouped_linear
+    torch.manual_seed(0)
+    G, N, K = 3, 128, 256
+    offs = torch.tensor([0, 128, 256, 384], dtype=torch.int32)
+    x = torch.randn(384, K).requires_grad_(True)
+    w = (torch.randn(G, N, K) * 0.05).requires_grad_(True)
+    y = grouped_linear(x, w, offs, "fp8", {})
+    x2, w2 = x.detach().clone().requires_grad_(True), w.detach().clone().requires_grad_(True)
+    y2 = grouped_linear(x2, w2, offs)
+    assert (y - y2).abs().max() / y2.abs().max() < 0.08
+    y.sum().backward()
+    y2.sum().backward()
+    assert (x.grad - x2.grad).abs().max() / x2.grad.abs().max() < 0.08
+    assert torch.allclose(w.grad, w2.grad, atol=1e-4)

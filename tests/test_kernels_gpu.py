@@ -522,6 +522,52 @@ def test_gemm_fp8_blockscaled(M, N, K):
     assert (out.float() - full).abs().max() / full.abs().max() < 0.1
 
 
+@pytest.mark.parametrize("G,N,K,rows", [(4, 256, 512, [128, 0, 384, 256]), (8, 4096, 7168, [256, 128, 0, 0, 512, 128, 128, 384]),
+                                        (3, 7168, 2048, [128, 128, 128])])
+def test_gemm_fp8_grouped_matches_dequantised_reference(G, N, K, rows):
+    """Ragged-M grouped block-fp8 GEMM (experts): every segment against its own expert's dequantised weight; an
+    empty expert, spare capacity behind the last segment."""
+    from gcore_b200.ops import _lib, quant
+    torch.manual_seed(31)
+    offs = [0]
+    for r in rows:
+        offs.append(offs[-1] + r)
+    cap = offs[-1] + 256                                     # spare rows beyond the last group stay zero
+    a = _rand(cap, K, scale=1.0)
+    a[offs[-1]:] = 0
+    w = _rand(G, N, K, scale=0.05)
+    aq, as_ = quant.quant_act_1x128(a)
+    bq, bs = quant.quant_weight_128x128(w.reshape(G * N, K).contiguous())
+    offsets = torch.tensor(offs, dtype=torch.int32, device=DEV)
+    out = quant.gemm_fp8_grouped(aq, as_, bq, bs, offsets, G)
+    _lib.check_device_errors()
+    a_dq = quant.dequant_1x128(aq, as_).float()
+    w_dq = quant.dequant_128x128(bq, bs)[:G * N, :K].float().view(G, N, K)
+    for g in range(G):
+        if rows[g]:
+            ref = a_dq[offs[g]:offs[g + 1]] @ w_dq[g].t()
+            _close(out[offs[g]:offs[g + 1]], ref, rtol=1e-2, atol=1e-2)
+    assert not out[offs[-1]:].any()
+
+
+def test_grouped_fp8_expert_projection_forward_backward():
+    from gcore_b200.models.moe import grouped_linear
+    torch.manual_seed(32)
+    G, N, K = 4, 256, 384
+    offs = torch.tensor([0, 128, 128, 384, 512], dtype=torch.int32, device=DEV)
+    x = _rand(512, K, scale=1.0).requires_grad_(True)
+    w = _rand(G, N, K, scale=0.05).requires_grad_(True)
+    y = grouped_linear(x, w, offs, "fp8", {})
+    x2, w2 = x.detach().clone().requires_grad_(True), w.detach().clone().requires_grad_(True)
+    y2 = grouped_linear(x2, w2, offs)
+    assert (y.float() - y2.float()).abs().max() / y2.float().abs().max() < 0.08
+    g = torch.randn_like(y)
+    y.backward(g)
+    y2.backward(g)
+    assert (x.grad.float() - x2.grad.float()).abs().max() / x2.grad.float().abs().max() < 0.08
+    _close(w.grad, w2.grad, rtol=2e-2, atol=2e-2)            # wgrad runs in bf16 on the same operands
+
+
 @pytest.mark.parametrize("T,N,K,bias,fp32", [(1, 512, 256, False, False), (8, 4608, 3584, True, False),
                                               (64, 3584, 18944, False, False), (100, 1000, 1792, True, True),
                                               (128, 2304, 3584, True, False), (128, 3584, 9472, False, True),

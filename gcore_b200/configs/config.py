@@ -616,6 +616,9 @@ class PretrainConfig(FinetuneConfig):
 @dataclass
 class RlConfig(BaseTopConfig):
     placement_type: str = "colocate"
+    # disaggregated placement: ranks [0, disaggregated_train_gpus) train, the others run rollout engines
+    # (default: half of the job each)
+    disaggregated_train_gpus: Optional[int] = None
     critic: Optional[CriticConfig] = None
     teacher: Optional[PolicyConfig] = None  # frozen teacher for on-policy distillation (advantage_type on_policy_distill)
     sampler: SamplerConfig = field(default_factory=SamplerConfig)

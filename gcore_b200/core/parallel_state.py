@@ -130,37 +130,69 @@ def plan_groups(world_size: int, tp: int = 1, pp: int = 1, cp: int = 1, ep: int 
 
 
 def initialize_model_parallel(tp: int = 1, pp: int = 1, cp: int = 1, ep: int = 1, etp: Optional[int] = None,
-                              create_gloo: bool = True, timeout_minutes: int = 30) -> ParallelState:
+                              create_gloo: bool = True, timeout_minutes: int = 30,
+                              ranks: Optional[List[int]] = None) -> ParallelState:
+    """``ranks``: the ranks of the default group that form this role's world (disaggregated placement: trainer ranks
+    and rollout ranks each lay out their own parallel groups inside their slice).  Every rank of the default group must
+    make the call, with the same arguments, because group creation is collective; a rank outside ``ranks`` takes part
+    in the creation and keeps the state it had."""
     global _STATE
     assert dist.is_initialized(), "call init_distributed() first"
-    world, rank = dist.get_world_size(), dist.get_rank()
+    rank = dist.get_rank()
+    world_ranks = list(ranks) if ranks is not None else list(range(dist.get_world_size()))
+    world = len(world_ranks)
+    member = rank in world_ranks
     fam, dense, expert = plan_groups(world, tp, pp, cp, ep, etp)
+    local = world_ranks.index(rank) if member else 0
     st = ParallelState(world_size=world, rank=rank, tp=tp, cp=cp, dp=dense["dp"], pp=pp, ep=ep,
                        etp=expert["etp"], edp=expert["edp"])
-    st.coords = rank_coords(rank, dense, ["tp", "cp", "dp", "pp"])
-    st.coords.update(rank_coords(rank, expert, ["etp", "ep", "edp", "pp"]))
+    st.coords = rank_coords(local, dense, ["tp", "cp", "dp", "pp"])
+    st.coords.update(rank_coords(local, expert, ["etp", "ep", "edp", "pp"]))
     timeout = datetime.timedelta(minutes=timeout_minutes)
     backend_is_nccl = dist.get_backend() == "nccl"
     for name, lists in fam.items():
-        for ranks in lists:
+        for idx in lists:
+            grp = [world_ranks[i] for i in idx]
             # every rank must create every group, in the same order
-            g = dist.new_group(ranks, timeout=timeout) if len(ranks) > 1 else None
+            g = dist.new_group(grp, timeout=timeout) if len(grp) > 1 else None
             gg = None
-            if create_gloo and backend_is_nccl and name in ("dp", "mp", "mp_cp", "dp_cp", "tp") and len(ranks) > 1:
-                gg = dist.new_group(ranks, backend="gloo", timeout=timeout)
-            if rank in ranks:
+            if create_gloo and backend_is_nccl and name in ("dp", "mp", "mp_cp", "dp_cp", "tp") and len(grp) > 1:
+                gg = dist.new_group(grp, backend="gloo", timeout=timeout)
+            if member and rank in grp:
                 st.groups[name] = g
-                st.group_ranks[name] = ranks
+                st.group_ranks[name] = grp
                 st.gloo_groups[name] = gg if gg is not None else g
-    st.groups["world"] = dist.group.WORLD
-    st.group_ranks["world"] = list(range(world))
-    if create_gloo and backend_is_nccl:
-        st.gloo_groups["world"] = dist.new_group(list(range(world)), backend="gloo", timeout=timeout)
+    if ranks is None:
+        st.groups["world"] = dist.group.WORLD
     else:
-        st.gloo_groups["world"] = dist.group.WORLD
+        st.groups["world"] = dist.new_group(world_ranks, timeout=timeout)   # also for a one-rank role: passing no
+        # group to a collective would address the default group, i.e. both roles
+    st.group_ranks["world"] = world_ranks
+    if create_gloo and backend_is_nccl:
+        st.gloo_groups["world"] = dist.new_group(world_ranks, backend="gloo", timeout=timeout)
+    else:
+        st.gloo_groups["world"] = st.groups["world"]
+    if not member:
+        return _STATE
     st.initialized = True
+    st.sub_world = ranks is not None
     _STATE = st
     return st
+
+
+def get_world_group():
+    """The group of all ranks of this role (the default group unless the job runs disaggregated roles)."""
+    st = _STATE
+    if st.initialized and getattr(st, "sub_world", False):
+        return st.groups["world"]
+    return dist.group.WORLD if dist.is_initialized() else None
+
+
+def get_world_size() -> int:
+    st = _STATE
+    if st.initialized:
+        return st.world_size
+    return dist.get_world_size() if dist.is_initialized() else 1
 
 
 def offload_process_groups() -> int:
@@ -192,11 +224,14 @@ def reload_process_groups(timeout_minutes: int = 30) -> int:
         return 0
     fam, _, _ = plan_groups(st.world_size, st.tp, st.pp, st.cp, st.ep, st.etp)
     timeout = datetime.timedelta(minutes=timeout_minutes)
+    world_ranks = st.group_ranks["world"]
+    me = st.rank
     n = 0
     for name, lists in fam.items():
-        for ranks in lists:
+        for idx in lists:
+            ranks = [world_ranks[i] for i in idx]
             g = dist.new_group(ranks, timeout=timeout) if len(ranks) > 1 else None
-            if st.rank in ranks and g is not None:
+            if me in ranks and g is not None:
                 st.groups[name] = g
                 if st.gloo_groups.get(name) is None:
                     st.gloo_groups[name] = g
@@ -333,7 +368,13 @@ def is_mp_cp_head() -> bool:
 
 
 def is_last_rank() -> bool:
-    return (not dist.is_initialized()) or dist.get_rank() == dist.get_world_size() - 1
+    """Last rank of this role's world (the reporting rank)."""
+    if not dist.is_initialized():
+        return True
+    st = _STATE
+    if st.initialized and st.group_ranks.get("world"):
+        return dist.get_rank() == st.group_ranks["world"][-1]
+    return dist.get_rank() == dist.get_world_size() - 1
 
 
 def cpu_barrier(name: str = "world"):

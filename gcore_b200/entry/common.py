@@ -44,7 +44,7 @@ def finalize():
     from ..checkpoint.torch_dist import wait_for_async_save
     wait_for_async_save()   # an asynchronous save still in flight is completed and published before the job ends
     if dist.is_initialized():
-        dist.barrier()
+        dist.barrier(group=ps.get_world_group())
         dist.destroy_process_group()
 
 

@@ -111,7 +111,7 @@ inline int& decode_smem_cap() {
 // is re-read from L2 while it is still hot) instead of one B tile by every CTA of the wave at once, which
 // concentrates the requests on the few L2 slices that hold it.  0 or 1 = plain row-fastest order.
 inline int& raster_group_m() {
-  static int g = 8;
+  static int g = 16;
   return g;
 }
 #ifdef __CUDACC__

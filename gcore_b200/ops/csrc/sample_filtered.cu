@@ -36,9 +36,14 @@ __device__ __forceinline__ float hash_uniform(unsigned long long seed, unsigned 
   x ^= x >> 31;
   return (static_cast<float>(x >> 40) + 0.5f) * (1.0f / 16777216.0f);
 }
-// key of a scaled logit; 0xFFFFFFFF = outside the window
+// Scaled logit and its key; 0xFFFFFFFF = outside the window.  Explicitly rounded operations: the same element must map
+// to the same key in every pass, so the compiler may not contract the scaling, the subtraction and the multiply into
+// fused multiply-adds differently from one call site to the next.
+__device__ __forceinline__ float scaled(const void* p, int is_fp32, long long i, float inv_temp) {
+  return __fmul_rn(load_logit(p, is_fp32, i), inv_temp);
+}
 __device__ __forceinline__ unsigned int key_of(float z, float zmax) {
-  const float q = (zmax - z) * (16777216.f / WINDOW);
+  const float q = __fmul_rn(__fsub_rn(zmax, z), 16777216.f / WINDOW);
   return q < 16777215.5f ? static_cast<unsigned int>(q) : 0xFFFFFFFFu;
 }
 
@@ -60,7 +65,7 @@ __device__ Sel radix_select(const void* logits, int is_fp32, long long base, int
     for (int i = threadIdx.x; i < 256; i += blockDim.x) { hist_c[i] = 0.f; hist_m[i] = 0.f; }
     __syncthreads();
     for (int j = threadIdx.x; j < V; j += blockDim.x) {
-      const float z = load_logit(logits, is_fp32, base + j) * inv_temp;
+      const float z = scaled(logits, is_fp32, base + j, inv_temp);
       const unsigned int u = key_of(z, zmax);
       if (u > limit) continue;
       if (level > 0 && (u >> (shift + 8)) != prefix) continue;
@@ -128,7 +133,7 @@ __global__ void __launch_bounds__(THREADS) sample_filtered_kernel(
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
   // ---- row maximum
   float zmax = -FLT_MAX;
-  for (int j = threadIdx.x; j < V; j += blockDim.x) zmax = fmaxf(zmax, load_logit(logits, is_fp32, base + j) * inv_temp);
+  for (int j = threadIdx.x; j < V; j += blockDim.x) zmax = fmaxf(zmax, scaled(logits, is_fp32, base + j, inv_temp));
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) zmax = fmaxf(zmax, __shfl_xor_sync(0xffffffffu, zmax, o));
   if (lane == 0) s_red[w] = zmax;
@@ -147,7 +152,7 @@ __global__ void __launch_bounds__(THREADS) sample_filtered_kernel(
     // mass of what is left after top-k / min-p
     float m = 0.f;
     for (int j = threadIdx.x; j < V; j += blockDim.x) {
-      const float z = load_logit(logits, is_fp32, base + j) * inv_temp;
+      const float z = scaled(logits, is_fp32, base + j, inv_temp);
       if (key_of(z, zmax) <= limit) m += __expf(z - zmax);
     }
 #pragma unroll
@@ -171,7 +176,7 @@ __global__ void __launch_bounds__(THREADS) sample_filtered_kernel(
   float best = -FLT_MAX, bz = 0.f, mass = 0.f;
   int bidx = 0, kept = 0;
   for (int j = threadIdx.x; j < V; j += blockDim.x) {
-    const float z = load_logit(logits, is_fp32, base + j) * inv_temp;
+    const float z = scaled(logits, is_fp32, base + j, inv_temp);
     if (key_of(z, zmax) > limit) continue;
     mass += __expf(z - zmax);
     ++kept;

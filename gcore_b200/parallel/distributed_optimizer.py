@@ -369,9 +369,10 @@ class DistributedOptimizer:
         total = self._local_sumsq(skip_peer)
         if extra is not None:
             total += extra
-        if dist.is_initialized() and dist.get_world_size() > 1:
+        if dist.is_initialized() and ps.get_world_size() > 1:
             # shards partition the DP x CP group, model-parallel ranks hold different parameters: sum over everyone
-            dist.all_reduce(total)
+            # (of this role: with disaggregated placement the rollout ranks are not part of it)
+            dist.all_reduce(total, group=ps.get_world_group())
         return total.sqrt()
 
     # ------------------------------------------------------------------ step

@@ -23,9 +23,9 @@ from .grpo_trainer import GrpoTrainer
 
 
 class RlLoop:
-    def __init__(self, config, model_cfg=None, tokenizer=None, reward_fn=None):
+    def __init__(self, config, model_cfg=None, tokenizer=None, reward_fn=None, trainer=None):
         self.cfg, self.tokenizer = config, tokenizer
-        self.trainer = GrpoTrainer(config, model_cfg=model_cfg, reward_fn=reward_fn)
+        self.trainer = trainer if trainer is not None else GrpoTrainer(config, model_cfg=model_cfg, reward_fn=reward_fn)
         self.log = get_logger("rl")
         self.rank = dist.get_rank() if dist.is_initialized() else 0
         self.injector = FaultInjector(config.debug.fault_injection, self.rank, int(os.environ.get("GCORE_ATTEMPT", "0")))

@@ -10,6 +10,11 @@ import torch
 import torch.distributed as dist
 
 
+def _world_group():
+    from ..core import parallel_state as ps
+    return ps.get_world_group()
+
+
 class _Timer:
     def __init__(self, device_timing: bool):
         self.device = device_timing and torch.cuda.is_available()
@@ -21,7 +26,7 @@ class _Timer:
 
     def start(self, barrier=False):
         if barrier and dist.is_initialized():
-            dist.barrier()
+            dist.barrier(group=_world_group())
         if self.device:
             self._ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
             self._ev[0].record()

@@ -653,7 +653,16 @@ def test_gemm_cta_pair_kernel(M, N, K, a_mn, b_mn):
     from gcore_b200.ops import gemm as G
     if (a_mn and M % 8) or (b_mn and N % 8):
         pytest.skip("MN-major operands need a 16-byte aligned leading dimension")
-    assert G.TWO_CTA["enabled"] and G._use_two_cta(M, N, K)
+    was = G.TWO_CTA["enabled"]
+    G.TWO_CTA["enabled"] = True                 # opt-in kernel: switched on for this test
+    try:
+        _check_cta_pair(G, M, N, K, a_mn, b_mn)
+    finally:
+        G.TWO_CTA["enabled"] = was
+
+
+def _check_cta_pair(G, M, N, K, a_mn, b_mn):
+    assert G._use_two_cta(M, N, K)
     torch.manual_seed(3)
     A, B = _rand(M, K, scale=0.5), _rand(N, K, scale=0.5)
     a = A.t().contiguous() if a_mn else A

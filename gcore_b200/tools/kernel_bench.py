@@ -8,6 +8,8 @@ against the measured roofline denominators in ``MEASURED_PEAKS.json`` when prese
 ``python -m gcore_b200.tools.kernel_bench decode_chain [--tokens 64] [--tp 1] [--json out.json]``   per-kernel cost
                                                                  of one decoder layer under CUDA-graph replay
 ``python -m gcore_b200.tools.kernel_bench train_step --model qwen2.5-7b --layers 8 --tokens 8192 --seqlen 1280``
+``python -m gcore_b200.tools.kernel_bench ce --tokens 8192 --vocab 152064 --k 3584 [--fused-only]``   vocabulary
+                                                                 GEMM with softmax statistics vs the chunked form
 
 The single-shape sub-commands launch one kernel a few times, which also makes them the small cases profilers are
 pointed at.
@@ -154,7 +156,7 @@ def cmd_gemm(argv=None):
     ap.add_argument("--k", "--K", type=int, default=3584)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--layout", default="fwd")
-    ap.add_argument("--two-cta", type=int, default=1, help="0: keep the one-CTA kernels (A/B comparison)")
+    ap.add_argument("--two-cta", type=int, default=0, help="1: route large problems to the CTA-pair kernel (A/B)")
     args = ap.parse_args(argv)
     from gcore_b200.ops import _lib
     from gcore_b200.ops import gemm as gemm_mod
@@ -484,6 +486,66 @@ def cmd_train_step(argv=None):
 
 COMMANDS = {"table": cmd_table, "gemm": cmd_gemm, "attn": cmd_attn, "paged": cmd_paged,
             "decode_chain": cmd_decode_chain, "train_step": cmd_train_step}
+
+
+def cmd_ce(argv=None):
+    """Log-prob / entropy over the vocabulary: the GEMM with the softmax statistics in its epilogue against the chunked
+    form (logits of 4096 tokens through the plain GEMM, one reduction pass) and against the plain GEMM alone."""
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--vocab", type=int, default=152064)
+    ap.add_argument("--k", type=int, default=3584)
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--fused-only", action="store_true", help="run only the fused kernel (for ncu captures)")
+    args = ap.parse_args(argv)
+    from gcore_b200.ops import _lib, vocab
+    from gcore_b200.ops.gemm import linear_forward
+    T, V, K = args.tokens, args.vocab, args.k
+    h = torch.randn(T, K, device="cuda").bfloat16()
+    w = (torch.randn(V, K, device="cuda") * 0.02).bfloat16()
+    tg = torch.randint(0, V, (T,), device="cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def timed(fn):
+        ts = []
+        for _ in range(args.iters):
+            flush.zero_()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn()
+            e.record()
+            torch.cuda.synchronize()
+            ts.append(s.elapsed_time(e))
+        return sorted(ts)[len(ts) // 2]
+
+    def fused():
+        with torch.no_grad():
+            vocab.FUSED_FWD["enabled"] = True
+            return vocab.linear_logprob_entropy(h, w, tg, 1.0)
+
+    def chunked():
+        with torch.no_grad():
+            vocab.FUSED_FWD["enabled"] = False
+            try:
+                return vocab.linear_logprob_entropy(h, w, tg, 1.0)
+            finally:
+                vocab.FUSED_FWD["enabled"] = True
+
+    res = {"T": T, "V": V, "K": K, "fused_ms": round(timed(fused), 4)}
+    if not args.fused_only:
+        res["chunked_ms"] = round(timed(chunked), 4)
+        res["plain_gemm_bf16_logits_ms"] = round(timed(lambda: linear_forward(h, w)), 4)
+        res["torch_matmul_ms"] = round(timed(lambda: torch.matmul(h, w.t())), 4)
+        a, b = fused(), chunked()
+        res["max_abs_diff_logp"] = float((a[0] - b[0]).abs().max())
+    fl = 2.0 * T * V * K
+    res["fused_tflops"] = round(fl / res["fused_ms"] / 1e9, 1)
+    res["partials_bytes"] = int(_lib.kernels().gk_linear_ce_splits(T, V)) * T * 16
+    _lib.check_device_errors()
+    print(json.dumps(res))
+
+
+COMMANDS["ce"] = cmd_ce
 
 
 def main(argv=None):

@@ -107,9 +107,23 @@ class _Base:
     def total_steps(self):
         return self.cfg.training.total_training_step
 
+    def generation_validation(self) -> Dict[str, float]:
+        """Every ``training.eval_interval`` steps, when ``data.eval_data_path`` names validation cases: generate them
+        with the current weights and score caption / image similarity (``validation/runner.py``)."""
+        path = getattr(self.cfg.data, "eval_data_path", None)
+        ev = self.cfg.training.eval_interval
+        if not (path and ev and (self.step + 1) % ev == 0 and callable(getattr(self.pipe, "__call__", None))):
+            return {}
+        if getattr(self, "_val_runner", None) is None:
+            from ..validation import ValidationRunner
+            root = os.path.join(self.cfg.checkpoint.save_ckpt_path or self.cfg.report.log_dir or ".", "val_results")
+            self._val_runner = ValidationRunner(self.pipe, data_path=path, save_dir=root)
+        return self._val_runner.run(self.step + 1)[0]
+
     def run(self):
         while self.step < self.total_steps():
             m = self.train_one_step()
+            m.update(self.generation_validation())
             self.step += 1
             self.history.append(m)
             if _dp()[0] == 0:

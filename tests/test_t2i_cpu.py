@@ -145,3 +145,38 @@ def test_t2i_entry_points(tmp_path):
     for mod in (train_t2i_grpo, train_t2i_dpo, train_t2i_edit_sft, train_bagel, train_bagel_t2i_grpo):
         hist = mod.main(["--config", str(p)] + small)
         assert len(hist) == 1, mod.__name__
+
+
+def test_generation_validation_runs_inside_the_training_loop(tmp_path):
+    """Validation cases are generated with the live weights every ``eval_interval`` steps; images, ``metrics.json``
+    and the aggregated similarities land below ``val_results/step_*``; module modes are restored afterwards."""
+    import json
+    import os
+    from gcore_b200.trainer.t2i_trainers import T2iGrpoTrainer
+    from gcore_b200.validation import EmbeddingMetrics, restore_modes, snapshot_modes
+    cases = tmp_path / "val.jsonl"
+    with open(cases, "w") as f:
+        for p in ("a red square", "a blue square", "a green square"):
+            f.write(json.dumps({"prompt": p, "task_type": "t2i"}) + "\n")
+    cfg = _cfg(training={"total_ppo_step": 2, "eval_interval": 2}, data={"eval_data_path": str(cases)},
+               report={"log_dir": str(tmp_path)})
+    tr = T2iGrpoTrainer(cfg).setup()
+    tr.pipe.model.train()
+    hist = tr.run()
+    assert tr.pipe.model.training
+    assert "val/train/t2i/text_image" not in hist[0]
+    m = hist[1]
+    assert m["val/train/t2i/cases"] == 3 and -1.0 <= m["val/train/t2i/text_image"] <= 1.0
+    root = os.path.join(str(tmp_path), "val_results", "step_0000002")
+    assert json.load(open(os.path.join(root, "metrics.json")))["val/train/t2i/cases"] == 3
+    assert len([n for n in os.listdir(os.path.join(root, "train")) if n.endswith(".pt")]) == 3
+    # the scorer: an image is most similar to itself; mode snapshot / restore is exact
+    em = EmbeddingMetrics()
+    a, b = torch.rand(3, 16, 16), torch.rand(3, 16, 16)
+    assert em.image_image_score(a, a) > 0.999 > em.image_image_score(a, b)
+    mod = torch.nn.Sequential(torch.nn.Linear(2, 2), torch.nn.Dropout())
+    mod[1].eval()
+    snap = snapshot_modes(mod)
+    mod.eval()
+    restore_modes(mod, snap)
+    assert mod.training and mod[0].training and not mod[1].training

@@ -548,6 +548,160 @@ def cmd_ce(argv=None):
 COMMANDS["ce"] = cmd_ce
 
 
+def cmd_fused(argv=None):
+    """The fused compute + collective kernels of rank 0 of 2 on ONE GPU: the peer's buffers and flags are stand-ins in
+    local memory, pre-filled at the call epoch, so a single launch runs to completion alone.  Times the kernel at a
+    training-sized shape (the bytes that would cross NVLink stay on this GPU: the numbers show the kernel's compute
+    and memory behaviour, not link bandwidth) and is the small case profilers are pointed at."""
+    import ctypes
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", default="ag", choices=["ag", "rs", "zero1", "ar_norm", "ep", "peer_copy"])
+    ap.add_argument("--rows", type=int, default=4096, help="rows per rank (ag / rs) or tokens (ep)")
+    ap.add_argument("--n", type=int, default=4608)
+    ap.add_argument("--k", type=int, default=3584)
+    ap.add_argument("--iters", type=int, default=5)
+    args = ap.parse_args(argv)
+    from gcore_b200.ops import _lib
+    lib = _lib.kernels()
+    dev = "cuda"
+    err = _lib.ptr(_lib.err_flag(torch.device(dev)))
+
+    def ptrs(*ts):
+        return (ctypes.c_ulonglong * len(ts))(*[t.data_ptr() for t in ts])
+
+    def bf(*shape, scale=1.0):
+        return (torch.randn(*shape, device=dev) * scale).bfloat16()
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    res = {"kernel": args.kernel}
+    state = {"epoch": 0}
+    if args.kernel in ("ag", "rs"):
+        Tl, N, K, tp = args.rows, args.n, args.k, 2
+        w = bf(N, K, scale=0.02)
+        if args.kernel == "ag":
+            mine = bf(tp * Tl, K)
+            peer = torch.zeros_like(mine)
+            flags = [torch.zeros(1 << 14, dtype=torch.int32, device=dev) for _ in range(2)]
+            flags[0].fill_(1 << 30)                       # the peer's rows "have arrived" for every epoch to come
+            y = torch.empty(tp * Tl, N, dtype=torch.bfloat16, device=dev)
+
+            def launch():
+                state["epoch"] += 1
+                _lib.check(lib.gk_gemm_comm(1, _lib.ptr(mine), K, _lib.ptr(w), K, N, 0, _lib.ptr(y), N, None, tp * Tl, N,
+                                            K, 0, tp, Tl, 16, state["epoch"], ptrs(mine, peer, flags[0], flags[1]), K, err,
+                                            _lib.stream_ptr()), "ag")
+            res.update(flops=2.0 * tp * Tl * N * K, nvlink_bytes=Tl * K * 2)
+        else:
+            a = bf(tp * Tl, K)
+            inbox = torch.zeros(tp, Tl, N, dtype=torch.bfloat16, device=dev)
+            peer_inbox = torch.zeros_like(inbox)
+            flags = [torch.zeros(1 << 14, dtype=torch.int32, device=dev) for _ in range(2)]
+            flags[0].fill_(1 << 30)
+            y = torch.empty(Tl, N, dtype=torch.bfloat16, device=dev)
+
+            def launch():
+                state["epoch"] += 1
+                _lib.check(lib.gk_gemm_comm(2, _lib.ptr(a), K, _lib.ptr(w), K, N, 0, _lib.ptr(y), N, None, tp * Tl, N, K, 0,
+                                            tp, Tl, 0, state["epoch"], ptrs(inbox, peer_inbox, flags[0], flags[1]), N, err,
+                                            _lib.stream_ptr()), "rs")
+            res.update(flops=2.0 * tp * Tl * N * K, nvlink_bytes=Tl * N * 2)
+    elif args.kernel == "zero1":
+        n = 1 << 28                                            # 268 M parameters in this rank's shard pair
+        shard = n // 2
+        grads = [torch.randn(n, device=dev) for _ in range(2)]
+        params = [torch.zeros(n, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        master, m, v = (torch.zeros(shard, device=dev) for _ in range(3))
+        F = ctypes.c_float
+
+        def launch():
+            _lib.check(lib.gk_zero1_step(3, ptrs(*grads, *params), 0, 2, 0, shard, None, _lib.ptr(master), _lib.ptr(m),
+                                         _lib.ptr(v), F(0.5), None, None, F(1e-4), F(0.9), F(0.95), F(1e-8), F(0.01), 2, 0,
+                                         _lib.stream_ptr()), "zero1")
+        # per element: 2 x 4 B gradients read, 12 B state read + 12 B written, 2 x 2 B parameters written
+        res.update(bytes=shard * (8 + 24 + 4), nvlink_bytes=shard * (4 + 2))
+    elif args.kernel == "ar_norm":
+        rows, H = 128, args.k
+        slot = rows * H
+        x0, res_in, gamma = bf(rows, H), bf(rows, H), bf(H)
+        ctas = lib.gk_allreduce_ctas()
+        inbox = torch.zeros(2, 2, slot, dtype=torch.bfloat16, device=dev)
+        flags = torch.full((2, 2, ctas), 1 << 30, dtype=torch.int32, device=dev)   # every epoch already "arrived"
+        peer_inbox, peer_flags = torch.zeros_like(inbox), torch.zeros_like(flags)
+        st = torch.zeros(4, dtype=torch.int32, device=dev)
+        y, ro = torch.empty_like(x0), torch.empty_like(x0)
+
+        def launch():
+            _lib.check(lib.gk_allreduce_rmsnorm(_lib.ptr(x0), _lib.ptr(res_in), _lib.ptr(gamma), _lib.ptr(ro), _lib.ptr(y),
+                                                rows, H, 1e-6, 0, 2, slot, ptrs(inbox, peer_inbox, flags, peer_flags),
+                                                _lib.ptr(st), err, _lib.stream_ptr()), "ar_norm")
+        res.update(bytes=rows * H * 2 * 5, nvlink_bytes=rows * H * 2)
+    elif args.kernel == "peer_copy":
+        rows, cols = 37888, 3584
+        src = bf(rows, cols)
+        dst = torch.empty(rows, cols // 2, dtype=torch.bfloat16, device=dev)
+
+        def launch():
+            _lib.check(lib.gk_peer_copy_2d(_lib.ptr(dst), cols // 2, _lib.ptr(src), cols, rows, cols // 2,
+                                           _lib.stream_ptr()), "peer_copy")
+        res.update(bytes=rows * cols * 2, nvlink_bytes=rows * cols)
+    else:   # ep: push of T x K rows to two "ranks", pull back
+        from gcore_b200.parallel.ep_fused import SEG
+        T, K, H, E, ep = args.rows, 8, 2048, 128, 2
+        El = E // ep
+        R_max = T * K + El * SEG
+        idx = torch.stack([torch.randperm(E, device=dev)[:K] for _ in range(T)])
+        x = bf(T, H)
+        flat = idx.reshape(-1)
+        cnt = torch.bincount(flat, minlength=E).int()
+        order = torch.argsort(flat, stable=True)
+        starts = cnt.long().cumsum(0) - cnt.long()
+        pos = torch.empty_like(flat)
+        pos[order] = torch.arange(flat.numel(), device=dev) - starts[flat[order]]
+        tables = [torch.zeros(2, ep, E, dtype=torch.int32, device=dev) for _ in range(ep)]
+        fl = [torch.zeros(2, ep, dtype=torch.int32, device=dev) for _ in range(ep)]
+        tables[0][0, 1] = 0
+        fl[0][0, 1] = 1
+        recv = [torch.zeros(R_max, H, dtype=torch.bfloat16, device=dev) for _ in range(ep)]
+        sb = torch.empty(E, dtype=torch.int32, device=dev)
+        offs = torch.zeros(El + 1, dtype=torch.int32, device=dev)
+        tot = torch.zeros(El, dtype=torch.int32, device=dev)
+        dst_row = torch.empty(T * K, dtype=torch.int32, device=dev)
+        _lib.check(lib.gk_ep_plan(_lib.ptr(cnt), ptrs(*tables, *fl), 0, ep, E, SEG, R_max, 0, _lib.ptr(sb), _lib.ptr(offs),
+                                  _lib.ptr(tot), err, _lib.stream_ptr()), "ep_plan")
+        wgt = torch.rand(T * K, device=dev)
+        y = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+
+        def launch():
+            _lib.check(lib.gk_ep_push(_lib.ptr(x), None, _lib.ptr(flat.int()), _lib.ptr(pos.int()), _lib.ptr(sb),
+                                      _lib.ptr(offs), _lib.ptr(tot), ptrs(*recv), _lib.ptr(dst_row), 0, ep, El, SEG, R_max,
+                                      K, H, T, _lib.stream_ptr()), "ep_push")
+            _lib.check(lib.gk_ep_pull(ptrs(*recv), _lib.ptr(dst_row), _lib.ptr(wgt), _lib.ptr(y), None, ep, K, H, R_max, T,
+                                      _lib.stream_ptr()), "ep_pull")
+        res.update(bytes=T * K * H * 2 * 4, nvlink_bytes=T * K * H * 2)
+    ts = []
+    for _ in range(args.iters):
+        flush.zero_()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        launch()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    _lib.check_device_errors()
+    ms = sorted(ts)[len(ts) // 2]
+    res["ms"] = round(ms, 4)
+    if "flops" in res:
+        res["tflops"] = round(res.pop("flops") / ms / 1e9, 1)
+    if "bytes" in res:
+        res["local_gbs"] = round(res.pop("bytes") / ms / 1e6, 1)
+    res["nvlink_ms_at_770GBs"] = round(res.pop("nvlink_bytes") / 770e6, 4)
+    print(json.dumps(res))
+
+
+COMMANDS["fused"] = cmd_fused
+
+
 def main(argv=None):
     argv = list(sys.argv[1:] if argv is None else argv)
     if argv and argv[0] in COMMANDS:

@@ -143,6 +143,22 @@ def test_every_recipe_yaml_loads_and_names_a_known_model():
             assert cfg.policy.fp8 and cfg.policy.lora.enabled and "linear_kv_up_proj" in cfg.policy.lora.target_modules
 
 
+def test_image_generation_and_vision_language_recipes_load():
+    import glob
+    from gcore_b200.configs.base import load_config
+    from gcore_b200.configs.config import FinetuneConfig, T2iConfig
+    from gcore_b200.models.dit import DiTConfig
+    files = sorted(glob.glob(os.path.join(ROOT, "tasks", "t2i", "yaml", "*.yaml")))
+    assert len(files) >= 4
+    for f in files:
+        cfg = load_config(T2iConfig, f, [])
+        assert cfg.model.pipeline in ("flux", "qwen_image_edit", "flux_kontext", "bagel")
+        if cfg.model.transformer:
+            DiTConfig(**cfg.model.transformer)          # rotary axes sum to the head size, etc.
+    cfg = load_config(FinetuneConfig, os.path.join(ROOT, "tasks", "vlm_sft", "yaml", "sft_vlm_images.yaml"), [])
+    assert cfg.policy.vision_config["patch_size"] == 14 and cfg.data.py_path.endswith("dataset.py")
+
+
 def test_reference_spellings_of_ppo_fields_are_accepted():
     from gcore_b200.configs.base import ConfigError, from_dict
     from gcore_b200.configs.config import PpoConfig

@@ -58,6 +58,9 @@ def kernels() -> ctypes.CDLL:
         gm = os.environ.get("GCORE_GEMM_GROUP_M")      # tile rows per band of the dense GEMMs' tile order (0 = row-fastest)
         if gm is not None and hasattr(lib, "gk_gemm_set_raster"):
             lib.gk_gemm_set_raster(int(gm))
+        stg = os.environ.get("GCORE_WIDE_STAGED")       # 0: the wide GEMM's epilogue stores rows per thread
+        if stg is not None and hasattr(lib, "gk_gemm_wide_set_staged"):
+            lib.gk_gemm_wide_set_staged(int(stg))
         cap = os.environ.get("GCORE_DECODE_SMEM_KB")   # shared-memory budget of decode GEMM CTAs (0 = full ring)
         if cap is not None and hasattr(lib, "gk_gemm_set_decode_smem_cap"):
             lib.gk_gemm_set_decode_smem_cap(int(cap) * 1024)
@@ -135,6 +138,7 @@ def _declare_kernels(lib: ctypes.CDLL):
     d("gk_gemm_2cta", [P, L, L, I, P, L, L, I, P, L, I, I, P, I, F, I, I, I, P, P])
     d("gk_gemm_set_decode_smem_cap", [I], None)
     d("gk_gemm_set_raster", [I], None)
+    d("gk_gemm_wide_set_staged", [I], None)
     d("gk_gemm_skinny", [P, L, P, L, P, L, I, P, I, I, I, I, I, I, P, P])
     d("gk_gemm_skinny_max_clusters", [I, I, I])
     d("gk_gemm_comm", [I, P, L, P, L, L, I, P, L, P, I, I, I, I, I, I, I, ctypes.c_uint, P, L, P, P])

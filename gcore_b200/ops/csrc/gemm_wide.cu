@@ -22,7 +22,15 @@ constexpr int BMW = 256, BN = 256, BK = 64, UMMA_K = 16;
 constexpr int THREADS = 192;
 constexpr int STAGES = 3;
 constexpr int A_BYTES = BMW * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+// Epilogue staging: every epilogue warp owns 32 rows x 128 bytes (64 bf16 or 32 fp32 columns of its TMEM lane
+// quarter).  Values go from TMEM registers into that area row by row (16-byte units, XOR-swizzled by row so that the
+// 32 lanes of a store hit 32 different banks groups) and leave it as whole 128-byte row segments, four rows per
+// warp-wide store: every global store instruction then writes complete 128-byte lines instead of 32 separate
+// 16-byte fragments.  The accumulators of this kernel are not double-buffered, so the time the epilogue needs to
+// drain the first half of a tile is time the tensor cores wait.
+constexpr int STAGE_ROW_BYTES = 128;
+constexpr int EPI_STAGE_BYTES = 4 * 32 * STAGE_ROW_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_STAGE_BYTES + 1024 + 256;
 
 struct WParams {
   int M, N, K;
@@ -34,6 +42,7 @@ struct WParams {
   float alpha;
   int* err;
   int group_m;
+  int staged;   // C rows are 16-byte aligned (and no bf16 read-modify-write): the epilogue stores through shared memory
 };
 
 // 32 consecutive accumulator columns of one output row
@@ -105,7 +114,8 @@ __global__ void __launch_bounds__(THREADS, 1)
 gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, WParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint8_t* epi_stage = smem + STAGES * STAGE_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES + EPI_STAGE_BYTES);
   uint64_t* empty = full + STAGES;
   uint64_t* tfull = empty + STAGES;   // 1: both halves are complete
   uint64_t* tempty = tfull + 1;       // 2: upper / lower half drained (128 arrivals each)
@@ -226,20 +236,104 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int half = 0; half < 2; ++half) {
         const int row = m0 + half * 128 + quad * 32 + lane;
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + half * BN;
+        if (p.staged) {
+          uint8_t* st = epi_stage + quad * (32 * STAGE_ROW_BYTES);
+          const int esz = p.out_fp32 ? 4 : 2;
+          const int group_cols = STAGE_ROW_BYTES / esz;          // 32 fp32 or 64 bf16 columns per pass
+          const int row0 = m0 + half * 128 + quad * 32;           // first row of this warp
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          float v[32];
-          if (kblocks > 0) {
-            uint32_t r[32];
-            tmem_ld32(taddr + c * 32, r);
-            tmem_ld_wait();
+          for (int g0 = 0; g0 < BN; g0 += group_cols) {
+#pragma unroll 1
+            for (int c = g0 / 32; c < (g0 + group_cols) / 32; ++c) {
+              float v[32];
+              if (kblocks > 0) {
+                uint32_t r[32];
+                tmem_ld32(taddr + c * 32, r);
+                tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-          } else {
+                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+              } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = 0.f;
+                for (int j = 0; j < 32; ++j) v[j] = 0.f;
+              }
+              const int col0 = n0 + c * 32;
+              if (p.bias) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  if (col0 + j < p.N)
+                    v[j] += p.bias_fp32 ? reinterpret_cast<const float*>(p.bias)[col0 + j]
+                                        : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[col0 + j]);
+                }
+              }
+              if (p.out_fp32) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  *reinterpret_cast<float4*>(st + lane * STAGE_ROW_BYTES + ((j ^ (lane & 7)) << 4)) =
+                      make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              } else {
+                const int ubase = (c & 1) * 4;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  uint4 o;
+                  o.x = pack_bf16x2(v[8 * j + 0], v[8 * j + 1]);
+                  o.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
+                  o.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]);
+                  o.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
+                  *reinterpret_cast<uint4*>(st + lane * STAGE_ROW_BYTES + (((ubase + j) ^ (lane & 7)) << 4)) = o;
+                }
+              }
+            }
+            __syncwarp();
+            // drain: lane -> (row 4 i + lane / 8, unit lane % 8); one instruction = four rows x 128 bytes
+            const int unit = lane & 7;
+            const int ucols = 16 / esz;
+            const int col = n0 + g0 + unit * ucols;
+#pragma unroll 4
+            for (int i = 0; i < 8; ++i) {
+              const int rr = 4 * i + (lane >> 3);
+              const int grow = row0 + rr;
+              const uint4 w = *reinterpret_cast<const uint4*>(st + rr * STAGE_ROW_BYTES + ((unit ^ (rr & 7)) << 4));
+              if (grow >= p.M || col >= p.N) continue;
+              uint8_t* dst = reinterpret_cast<uint8_t*>(p.C) + (static_cast<long long>(grow) * p.ldc + col) * esz;
+              if (col + ucols <= p.N) {
+                if (p.out_fp32 && p.accumulate) {
+                  const float4 c4 = *reinterpret_cast<const float4*>(dst);
+                  float4 o = *reinterpret_cast<const float4*>(&w);
+                  o.x += c4.x; o.y += c4.y; o.z += c4.z; o.w += c4.w;
+                  *reinterpret_cast<float4*>(dst) = o;
+                } else {
+                  *reinterpret_cast<uint4*>(dst) = w;
+                }
+              } else if (p.out_fp32) {
+                const float* e = reinterpret_cast<const float*>(&w);
+                float* d = reinterpret_cast<float*>(dst);
+                for (int j = 0; j < ucols; ++j)
+                  if (col + j < p.N) d[j] = p.accumulate ? d[j] + e[j] : e[j];
+              } else {
+                const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&w);
+                __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(dst);
+                for (int j = 0; j < ucols; ++j)
+                  if (col + j < p.N) d[j] = e[j];
+              }
+            }
+            __syncwarp();   // the staging rows are free for the next pass
           }
-          store32(p, v, row, n0 + c * 32);
+        } else {
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            float v[32];
+            if (kblocks > 0) {
+              uint32_t r[32];
+              tmem_ld32(taddr + c * 32, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = 0.f;
+            }
+            store32(p, v, row, n0 + c * 32);
+          }
         }
         tc_fence_before();
         mbar_arrive(&tempty[half]);
@@ -269,6 +363,9 @@ int launch_wide(const CUtensorMap& tmA, const CUtensorMap& tmB, const WParams& p
 
 using namespace gkw;
 
+// 0: per-thread row stores (A/B switch for the staged epilogue)
+GK_EXPORT void gk_gemm_wide_set_staged(int on) { gk::wide_staged_epilogue() = on; }
+
 // C[M,N] (+)= alpha * A . B^T (+ bias over N).  a_mn: A is [K, M] (M contiguous); b_mn: B is [K, N].
 GK_EXPORT int gk_gemm_wide(const void* A, long long lda, long long a_rows, int a_mn, const void* B, long long ldb,
                            long long b_rows, int b_mn, void* C, long long ldc, int out_fp32, int accumulate,
@@ -286,6 +383,9 @@ GK_EXPORT int gk_gemm_wide(const void* A, long long lda, long long a_rows, int a
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32; p.accumulate = accumulate;
   p.bias = bias; p.bias_fp32 = bias_fp32; p.alpha = alpha; p.err = err;
   p.group_m = gk::raster_group_m();
+  const int esz = out_fp32 ? 4 : 2;
+  p.staged = ((reinterpret_cast<uintptr_t>(C) & 15) == 0 && (ldc * esz) % 16 == 0 && (out_fp32 || !accumulate) &&
+              gk::wide_staged_epilogue()) ? 1 : 0;
   const long long tiles = static_cast<long long>((M + BMW - 1) / BMW) * ((N + BN - 1) / BN);
   const int grid = static_cast<int>(tiles < gk::sm_count() ? tiles : gk::sm_count());
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);

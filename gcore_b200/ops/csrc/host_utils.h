@@ -114,6 +114,10 @@ inline int& raster_group_m() {
   static int g = 16;
   return g;
 }
+inline int& wide_staged_epilogue() {
+  static int on = 1;
+  return on;
+}
 #ifdef __CUDACC__
 __device__ __forceinline__ void raster_tile(int tile, int mt, int nt, int group_m, int& mi, int& ni) {
   if (group_m <= 1) {

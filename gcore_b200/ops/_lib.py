@@ -58,6 +58,9 @@ def kernels() -> ctypes.CDLL:
         gm = os.environ.get("GCORE_GEMM_GROUP_M")      # tile rows per band of the dense GEMMs' tile order (0 = row-fastest)
         if gm is not None and hasattr(lib, "gk_gemm_set_raster"):
             lib.gk_gemm_set_raster(int(gm))
+        tsp = os.environ.get("GCORE_WIDE_TAIL_SPLIT")   # 0: the wide GEMM's partial last wave is not split along K
+        if tsp is not None and hasattr(lib, "gk_gemm_wide_set_tail_split"):
+            lib.gk_gemm_wide_set_tail_split(int(tsp))
         stg = os.environ.get("GCORE_WIDE_STAGED")       # 0: the wide GEMM's epilogue stores rows per thread
         if stg is not None and hasattr(lib, "gk_gemm_wide_set_staged"):
             lib.gk_gemm_wide_set_staged(int(stg))
@@ -128,7 +131,8 @@ def _declare_kernels(lib: ctypes.CDLL):
 
     P, I, L, F = c_void_p, c_int, c_ll, c_float
     d("gk_gemm_bf16", [P, L, L, I, P, L, L, I, P, L, I, I, I, P, I, I, F, I, I, I, I, I, I, I, P, I, L, I, P, P, P, P])
-    d("gk_gemm_wide", [P, L, L, I, P, L, L, I, P, L, I, I, P, I, F, I, I, I, P, P])
+    d("gk_gemm_wide", [P, L, L, I, P, L, L, I, P, L, I, I, P, I, F, I, I, I, P, L, P, I, P, P])
+    d("gk_gemm_wide_set_tail_split", [I], None)
     d("gk_dsv4_indexer_fwd", [P, P, P, P, P, P, I, I, I, I, F, P])
     d("gk_dsv4_indexer_bwd", [P, P, P, P, P, P, P, P, I, I, I, I, I, F, P])
     d("gk_dsv4_sparse_mqa_fwd", [P, P, P, P, P, P, I, I, I, I, I, F, P])

@@ -43,7 +43,34 @@ struct WParams {
   int* err;
   int group_m;
   int staged;   // C rows are 16-byte aligned (and no bf16 read-modify-write): the epilogue stores through shared memory
+  // Tail split: a problem whose tile count is a little more than a whole number of waves would leave most SMs idle
+  // during the last wave (448 tiles on 148 SMs: 3 waves and 4 tiles).  The tiles of that partial wave are cut along K
+  // into `tail_ks` slices of `tail_per` k-blocks, each slice is a work item of its own, the slices leave fp32
+  // partials in `ws` and the CTA that finishes a tile's last slice adds them up and stores the tile.
+  int full_tiles;   // tiles [0, full_tiles) are whole work items; the others are split
+  int tail_ks, tail_per;
+  float* ws;        // [tail tiles][tail_ks][256 x 256] fp32
+  int* counters;    // [tail tiles], zero between launches
 };
+
+struct Item {
+  int tile, kb0, kb1, slice;
+  bool split;
+};
+__device__ __forceinline__ Item work_item(const WParams& p, int w, int kblocks) {
+  Item it;
+  if (w < p.full_tiles) {
+    it.tile = w; it.kb0 = 0; it.kb1 = kblocks; it.slice = 0; it.split = false;
+  } else {
+    const int r = w - p.full_tiles;
+    it.tile = p.full_tiles + r / p.tail_ks;
+    it.slice = r % p.tail_ks;
+    it.kb0 = it.slice * p.tail_per;
+    it.kb1 = it.kb0 + p.tail_per < kblocks ? it.kb0 + p.tail_per : kblocks;
+    it.split = true;
+  }
+  return it;
+}
 
 // 32 consecutive accumulator columns of one output row
 __device__ __forceinline__ void store32(const WParams& p, float (&v)[32], int row, int col0) {
@@ -120,6 +147,7 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* tfull = empty + STAGES;   // 1: both halves are complete
   uint64_t* tempty = tfull + 1;       // 2: upper / lower half drained (128 arrivals each)
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tempty + 2);
+  int* s_last = reinterpret_cast<int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   pdl_launch_dependents();
@@ -142,16 +170,18 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int mt = (p.M + BMW - 1) / BMW, nt = (p.N + BN - 1) / BN;
   const int ntiles = mt * nt;
   const int kblocks = (p.K + BK - 1) / BK;
+  const int nitems = p.full_tiles + (ntiles - p.full_tiles) * p.tail_ks;
 
   if (warp == 0) {
     int s = 0;
     uint32_t ph = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+    for (int w = blockIdx.x; w < nitems && ok; w += gridDim.x) {
+      const Item it = work_item(p, w, kblocks);
       int mi, ni;
-      raster_tile(tile, mt, nt, p.group_m, mi, ni);
+      raster_tile(it.tile, mt, nt, p.group_m, mi, ni);
       const int m0 = mi * BMW, n0 = ni * BN;
-      for (int kb = 0; kb < kblocks; ++kb) {
+      for (int kb = it.kb0; kb < it.kb1; ++kb) {
         ok = mbar_wait(&empty[s], ph ^ 1, p.err, ERR_WAIT_EMPTY);
         if (!ok) break;
         if (lane == 0) {
@@ -181,8 +211,9 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int s = 0;
     uint32_t ph = 0, pt = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-      for (int kb = 0; kb < kblocks && ok; ++kb) {
+    for (int w = blockIdx.x; w < nitems && ok; w += gridDim.x) {
+      const Item it = work_item(p, w, kblocks);
+      for (int kb = it.kb0; kb < it.kb1 && ok; ++kb) {
         ok = mbar_wait(&full[s], ph, p.err, ERR_WAIT_FULL);
         if (!ok) break;
         tc_fence_after();
@@ -190,7 +221,7 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const uint32_t b_base = a_base + A_BYTES;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-          if (kb == 0) {  // the previous tile's accumulator half must have been read out
+          if (kb == it.kb0) {  // the previous item's accumulator half must have been read out
             ok = mbar_wait(&tempty[half], pt ^ 1, p.err, ERR_WAIT_TMEM_EMPTY);
             if (!ok) break;
             tc_fence_after();
@@ -204,7 +235,7 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                           : make_smem_desc_sw128(ah + k4 * (UMMA_K * 2), 16, 1024);
               const uint64_t bdesc = B_MN ? make_smem_desc_sw128(b_base + k4 * (UMMA_K * 128), 8192, 1024)
                                           : make_smem_desc_sw128(b_base + k4 * (UMMA_K * 2), 16, 1024);
-              umma_f16(tmem_base + half * BN, adesc, bdesc, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+              umma_f16(tmem_base + half * BN, adesc, bdesc, idesc, (kb > it.kb0 || k4 > 0) ? 1u : 0u);
             }
           }
           __syncwarp();
@@ -212,7 +243,7 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!ok) break;
         if (lane == 0) {
           umma_commit(&empty[s]);
-          if (kb == kblocks - 1) umma_commit(tfull);
+          if (kb == it.kb1 - 1) umma_commit(tfull);
         }
         __syncwarp();
         if (++s == STAGES) { s = 0; ph ^= 1; }
@@ -223,14 +254,65 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int quad = warp & 3;
     uint32_t pt = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+    for (int w = blockIdx.x; w < nitems && ok; w += gridDim.x) {
+      const Item it = work_item(p, w, kblocks);
       int mi, ni;
-      raster_tile(tile, mt, nt, p.group_m, mi, ni);
+      raster_tile(it.tile, mt, nt, p.group_m, mi, ni);
       const int m0 = mi * BMW, n0 = ni * BN;
       if (kblocks > 0) {
         ok = mbar_wait(tfull, pt, p.err, ERR_WAIT_TMEM_FULL);
         if (!ok) break;
         tc_fence_after();
+      }
+      if (it.split) {
+        // ---- a K-slice of a tail tile: park the fp32 partial (column-major inside the tile: lanes hold consecutive
+        // rows, so every store is one 128-byte line), release the accumulators, and let the CTA that brings the last
+        // slice add everything up and store the tile
+        const int tslot = it.tile - p.full_tiles;
+        float* part = p.ws + (static_cast<long long>(tslot) * p.tail_ks + it.slice) * (BMW * BN);
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + half * BN;
+          const int rin = half * 128 + quad * 32 + lane;
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld32(taddr + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) __stcg(part + static_cast<long long>(c * 32 + j) * BMW + rin, __uint_as_float(r[j]));
+          }
+          tc_fence_before();
+          mbar_arrive(&tempty[half]);
+        }
+        pt ^= 1;
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) *s_last = atomicAdd(&p.counters[tslot], 1) == p.tail_ks - 1 ? 1 : 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*s_last) {
+          __threadfence();
+          const float* base = p.ws + static_cast<long long>(tslot) * p.tail_ks * (BMW * BN);
+#pragma unroll 1
+          for (int half = 0; half < 2; ++half) {
+            const int rin = half * 128 + quad * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+              float v[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = 0.f;
+              for (int sl = 0; sl < p.tail_ks; ++sl) {
+                const float* src = base + static_cast<long long>(sl) * (BMW * BN) + static_cast<long long>(c * 32) * BMW + rin;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] += __ldcg(src + j * BMW);
+              }
+              store32(p, v, m0 + rin, n0 + c * 32);
+            }
+          }
+          if (threadIdx.x == 64) p.counters[tslot] = 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        continue;
       }
 #pragma unroll 1
       for (int half = 0; half < 2; ++half) {
@@ -367,9 +449,14 @@ using namespace gkw;
 GK_EXPORT void gk_gemm_wide_set_staged(int on) { gk::wide_staged_epilogue() = on; }
 
 // C[M,N] (+)= alpha * A . B^T (+ bias over N).  a_mn: A is [K, M] (M contiguous); b_mn: B is [K, N].
+// 0: no K-split of the partial last wave (A/B switch)
+GK_EXPORT void gk_gemm_wide_set_tail_split(int on) { gk::wide_tail_split() = on; }
+
+// ws / counters (optional): scratch for the tail split, `ws_floats` floats and `counter_ints` zero-initialised ints.
 GK_EXPORT int gk_gemm_wide(const void* A, long long lda, long long a_rows, int a_mn, const void* B, long long ldb,
                            long long b_rows, int b_mn, void* C, long long ldc, int out_fp32, int accumulate,
-                           const void* bias, int bias_fp32, float alpha, int M, int N, int K, int* err, void* stream) {
+                           const void* bias, int bias_fp32, float alpha, int M, int N, int K, float* ws,
+                           long long ws_floats, int* counters, int counter_ints, int* err, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return -10;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7)) return -15;
   CUtensorMap tmA, tmB;
@@ -387,7 +474,25 @@ GK_EXPORT int gk_gemm_wide(const void* A, long long lda, long long a_rows, int a
   p.staged = ((reinterpret_cast<uintptr_t>(C) & 15) == 0 && (ldc * esz) % 16 == 0 && (out_fp32 || !accumulate) &&
               gk::wide_staged_epilogue()) ? 1 : 0;
   const long long tiles = static_cast<long long>((M + BMW - 1) / BMW) * ((N + BN - 1) / BN);
-  const int grid = static_cast<int>(tiles < gk::sm_count() ? tiles : gk::sm_count());
+  const int sms = gk::sm_count();
+  int grid = static_cast<int>(tiles < sms ? tiles : sms);
+  p.full_tiles = static_cast<int>(tiles); p.tail_ks = 1; p.tail_per = 0; p.ws = ws; p.counters = counters;
+  const int kblocks = (K + BK - 1) / BK;
+  const int tail = static_cast<int>(tiles % sms);
+  if (ws && counters && gk::wide_tail_split() && tail > 0 && tail * 2 <= sms && kblocks >= 8) {
+    // as many slices as fill the idle SMs of the partial wave, at least four k-blocks each
+    int ks = sms / tail;
+    if (ks > kblocks / 4) ks = kblocks / 4;
+    if (ks > 16) ks = 16;
+    const long long need = static_cast<long long>(tail) * ks * BMW * BN;
+    if (ks >= 2 && need <= ws_floats && tail <= counter_ints) {
+      const int per = (kblocks + ks - 1) / ks;
+      p.tail_per = per;
+      p.tail_ks = (kblocks + per - 1) / per;   // no empty slice
+      p.full_tiles = static_cast<int>(tiles) - tail;
+      if (tiles < sms) grid = static_cast<int>(tiles - tail + tail * p.tail_ks < sms ? tiles - tail + tail * p.tail_ks : sms);
+    }
+  }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (!a_mn && !b_mn) return launch_wide<false, false>(tmA, tmB, p, grid, st);
   if (a_mn && !b_mn) return launch_wide<true, false>(tmA, tmB, p, grid, st);

@@ -114,6 +114,10 @@ inline int& raster_group_m() {
   static int g = 16;
   return g;
 }
+inline int& wide_tail_split() {
+  static int on = 1;
+  return on;
+}
 inline int& wide_staged_epilogue() {
   static int on = 1;
   return on;

@@ -45,7 +45,8 @@ def _pick_bn(n: int, m: int = 0, b_mn: bool = False) -> int:
     return 256  # 192 / 224 wide tiles exist in the kernel but did not pay off on B200 (the kernel is L2-bound)
 
 
-WIDE = {"enabled": os.environ.get("GCORE_WIDE_GEMM", "1") != "0", "gain": 1.05}
+WIDE = {"enabled": os.environ.get("GCORE_WIDE_GEMM", "1") != "0", "gain": 1.05,
+        "tail_split": os.environ.get("GCORE_WIDE_TAIL_SPLIT", "1") != "0"}
 
 
 def _use_wide(M: int, N: int, K: int) -> bool:
@@ -56,9 +57,23 @@ def _use_wide(M: int, N: int, K: int) -> bool:
     nt = (N + 255) // 256
     tw = ((M + 255) // 256) * nt
     tg = ((M + 127) // 128) * nt
-    eff_w = tw / (((tw + 147) // 148) * 148)
+    eff_w = tw / _wide_waves(tw, (K + 63) // 64) / 148
     eff_g = tg / (((tg + 147) // 148) * 148)
     return eff_w * WIDE["gain"] > eff_g
+
+
+def _wide_waves(tiles: int, kblocks: int) -> float:
+    """Waves the 256 x 256 kernel needs on 148 SMs.  A partial last wave of at most half the SMs is cut along K into
+    slices (the kernel's tail split): it then costs the share of a tile one slice is, plus the partial-sum pass."""
+    full, tail = divmod(tiles, 148)
+    if tail == 0:
+        return float(full)
+    if WIDE["tail_split"] and tail * 2 <= 148 and kblocks >= 8:
+        ks = min(148 // tail, kblocks // 4, 16)
+        if ks >= 2:
+            per = -(-kblocks // ks)
+            return full + per / kblocks + 0.06
+    return float(full + 1)
 
 
 # The CTA-pair kernel is numerically verified but measures 5-10 % behind the one-CTA 256 x 256 kernel on the training
@@ -130,10 +145,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if (bn is None and ksplit == 1 and not transposed and not bias_along_m and _use_wide(M, N, K)
             and out.dtype in (torch.bfloat16, torch.float32) and hasattr(lib, "gk_gemm_wide")):
         LAUNCHES["gemm"] += 1
+        ws, cnt = _scratch(a.device, 16 << 20, 4096)     # 64 MB: K-split partials of the partial last wave
         rc = lib.gk_gemm_wide(_lib.ptr(a), a.stride(0), a.shape[0], int(a_mn), _lib.ptr(b), b.stride(0), b.shape[0],
                               int(b_mn), _lib.ptr(out), out.stride(0), int(out.dtype == torch.float32), int(accumulate),
                               _lib.ptr(bias), int(bias is not None and bias.dtype == torch.float32), float(alpha),
-                              M, N, K, _lib.ptr(_lib.err_flag(a.device)), _lib.stream_ptr())
+                              M, N, K, _lib.ptr(ws), ws.numel(), _lib.ptr(cnt), cnt.numel(),
+                              _lib.ptr(_lib.err_flag(a.device)), _lib.stream_ptr())
         _lib.check(rc, "gk_gemm_wide")
         return out
     if bn is None:

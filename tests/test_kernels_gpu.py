@@ -628,10 +628,13 @@ def test_gemm_wide_tiles(M, N, K, a_mn, b_mn):
     ref = (a.float().t() if a_mn else a.float()) @ (b.float() if b_mn else b.float().t())
     lib = _lib.kernels()
 
+    ws, cnt = G._scratch(a.device, 16 << 20, 4096)
+
     def run(out, accumulate, bias_t, alpha):
         rc = lib.gk_gemm_wide(_lib.ptr(a), a.stride(0), a.shape[0], int(a_mn), _lib.ptr(b), b.stride(0), b.shape[0],
                               int(b_mn), _lib.ptr(out), out.stride(0), int(out.dtype == torch.float32), int(accumulate),
-                              _lib.ptr(bias_t), 0, alpha, M, N, K, _lib.ptr(_lib.err_flag(a.device)), _lib.stream_ptr())
+                              _lib.ptr(bias_t), 0, alpha, M, N, K, _lib.ptr(ws), ws.numel(), _lib.ptr(cnt), cnt.numel(),
+                              _lib.ptr(_lib.err_flag(a.device)), _lib.stream_ptr())
         assert rc == 0
         _lib.check_device_errors()
 

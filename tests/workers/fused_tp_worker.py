@@ -99,6 +99,23 @@ def main():
         graph.replay()
     torch.cuda.synchronize()
     res["peer_allreduce"] = dict(eager=ok_ar, graph=close(buf, ref, 1e-2)[0])
+    # all-reduce + residual + RMSNorm in one kernel: bit-identical to the three steps, with and without a residual,
+    # row counts that do and do not divide over the kernel's CTAs, interleaved with plain all-reduces (shared epoch)
+    from gcore_b200.ops import fused as fused_ops
+    ok_arn = True
+    for it, rows in enumerate((64, 100, 128, 7)):
+        torch.manual_seed(500 + 10 * it + rank)
+        part = torch.randn(rows, 3584, device=dev).bfloat16()
+        torch.manual_seed(600 + it)                       # residual and gain are replicated over the ranks
+        resid = torch.randn(rows, 3584, device=dev).bfloat16() if it % 2 == 0 else None
+        gamma = (1 + 0.1 * torch.randn(3584, device=dev)).bfloat16()
+        summed = part.clone()
+        par.all_reduce(summed)
+        y_ref, r_ref = fused_ops.rmsnorm(summed, gamma, 1e-6, resid)
+        out = par.all_reduce_rmsnorm(part, resid, gamma, 1e-6)
+        ok_arn = ok_arn and out is not None and torch.equal(out[0], y_ref) and \
+            torch.equal(out[1], r_ref if resid is not None else summed)
+    res["peer_allreduce"]["fused_norm"] = bool(ok_arn)
     if bench:
         x64 = torch.randn(64, 3584, device=dev).bfloat16()
         row = {}

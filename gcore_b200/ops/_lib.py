@@ -153,6 +153,8 @@ def _declare_kernels(lib: ctypes.CDLL):
     d("gk_gemm_fp8_grouped", [P, L, P, L, P, P, P, L, I, I, I, I, P, I, P, P])
     d("gk_zero1_step", [I, P, I, I, L, L, P, P, P, P, F, P, P, F, F, F, F, F, I, I, P])
     d("gk_peer_barrier", [P, I, I, I, ctypes.c_uint, P, P])
+    d("gk_peer_barrier_dev", [P, I, I, I, P, P, P])
+    d("gk_ep_plan_dev", [P, P, I, I, I, I, I, P, P, P, P, P, P])
     d("gk_ep_plan", [P, P, I, I, I, I, I, ctypes.c_uint, P, P, P, P, P])
     d("gk_ep_push", [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, L, P])
     d("gk_ep_copy_rows", [P, P, P, I, P])

@@ -32,6 +32,7 @@ struct PlanParams {
   uint32_t* flags[MAX_RANKS];   // every rank's flags [2 parity][ep]
   int rank, ep, E, E_local, seg, R_max, parity;
   uint32_t epoch;
+  unsigned int* calls_dev;      // optional: calls so far, kept on the device (parity / epoch derive from it)
   int* send_base;               // [E]   first row of my tokens for expert g inside its owner's buffer
   int* offsets;                 // [E_local + 1] padded segment starts of my own buffer
   int* tot_local;               // [E_local] real rows per local expert
@@ -54,6 +55,13 @@ __global__ void __launch_bounds__(256) ep_plan_kernel(PlanParams p) {
   __shared__ int s_tot[MAX_EXPERTS], s_before[MAX_EXPERTS], s_pad[MAX_EXPERTS];
   __shared__ int s_ok;
   const int tid = threadIdx.x;
+  if (p.calls_dev) {   // replayable form: the call number comes from device memory and is advanced at the end
+    const unsigned int calls = *reinterpret_cast<volatile unsigned int*>(p.calls_dev);
+    p.parity = calls & 1;
+    p.epoch = (calls >> 1) + 1;
+    __syncthreads();
+    if (tid == 0) *p.calls_dev = calls + 1;
+  }
   for (int g = tid; g < p.E; g += blockDim.x) {
     const int c = p.cnt[g];
     for (int r = 0; r < p.ep; ++r) p.cnt_all[r][(p.parity * p.ep + p.rank) * p.E + g] = c;
@@ -231,10 +239,12 @@ GK_EXPORT int gk_ep_copy_rows(const void* src, void* dst, const int* n_rows, int
 }
 
 // ptrs: [0..ep) count tables, [ep..2ep) flag arrays of every rank.
-GK_EXPORT int gk_ep_plan(const int* cnt, const unsigned long long* ptrs, int rank, int ep, int E, int seg, int R_max,
-                         unsigned int calls, int* send_base, int* offsets, int* tot_local, int* err, void* stream) {
+static int ep_plan_launch(const int* cnt, const unsigned long long* ptrs, int rank, int ep, int E, int seg, int R_max,
+                          unsigned int calls, unsigned int* calls_dev, int* send_base, int* offsets, int* tot_local,
+                          int* err, void* stream) {
   if (ep < 1 || ep > MAX_RANKS || E > MAX_EXPERTS || E % ep) return -1;
   PlanParams p;
+  p.calls_dev = calls_dev;
   p.cnt = cnt;
   for (int r = 0; r < MAX_RANKS; ++r) {
     p.cnt_all[r] = r < ep ? reinterpret_cast<int*>(ptrs[r]) : nullptr;
@@ -245,6 +255,20 @@ GK_EXPORT int gk_ep_plan(const int* cnt, const unsigned long long* ptrs, int ran
   p.send_base = send_base; p.offsets = offsets; p.tot_local = tot_local; p.err = err;
   ep_plan_kernel<<<1, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
   return gk::launch_status();
+}
+
+GK_EXPORT int gk_ep_plan(const int* cnt, const unsigned long long* ptrs, int rank, int ep, int E, int seg, int R_max,
+                         unsigned int calls, int* send_base, int* offsets, int* tot_local, int* err, void* stream) {
+  return ep_plan_launch(cnt, ptrs, rank, ep, E, seg, R_max, calls, nullptr, send_base, offsets, tot_local, err, stream);
+}
+
+// The call number (which selects the table parity and the flag epoch) is read from `calls_dev` and advanced by the
+// kernel: the launch can be captured in a CUDA graph.
+GK_EXPORT int gk_ep_plan_dev(const int* cnt, const unsigned long long* ptrs, int rank, int ep, int E, int seg, int R_max,
+                             unsigned int* calls_dev, int* send_base, int* offsets, int* tot_local, int* err,
+                             void* stream) {
+  if (!calls_dev) return -1;
+  return ep_plan_launch(cnt, ptrs, rank, ep, E, seg, R_max, 0u, calls_dev, send_base, offsets, tot_local, err, stream);
 }
 
 // recv_ptrs: receive buffer [R_max, H] of every rank.

@@ -158,9 +158,15 @@ __global__ void __launch_bounds__(THREADS) zero1_kernel(Z1Params p) {
 // Barrier across the ranks of a group: publish `epoch` into slot [slot][rank] of every peer's flag array, then wait
 // until every peer's epoch shows up in the own array.  One CTA, one thread per peer; waits are bounded.
 __global__ void peer_barrier_kernel(uint32_t* const* flags_by_rank, int rank, int nranks, int slot, uint32_t epoch,
-                                    int* err, long long budget) {
+                                    int* err, long long budget, unsigned int* epoch_dev) {
   __threadfence_system();
   const int t = threadIdx.x;
+  if (epoch_dev) {
+    // the epoch lives on the device (the launch can be replayed from a CUDA graph with frozen arguments): every
+    // thread reads the count of barriers done so far, the last statement of the kernel advances it
+    epoch = *reinterpret_cast<volatile unsigned int*>(epoch_dev) + 1;
+    __syncwarp();
+  }
   if (t < nranks && t != rank) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags_by_rank[t] + slot * MAX_RANKS + rank), "r"(epoch)
                  : "memory");
@@ -176,6 +182,10 @@ __global__ void peer_barrier_kernel(uint32_t* const* flags_by_rank, int rank, in
         break;
       }
     }
+  }
+  if (epoch_dev) {
+    __syncwarp();
+    if (t == 0) *epoch_dev = epoch;
   }
 }
 
@@ -215,7 +225,17 @@ GK_EXPORT int gk_peer_barrier(const void* flags_dev, int rank, int nranks, int s
                               void* stream) {
   if (nranks < 1 || nranks > MAX_RANKS) return -1;
   peer_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<uint32_t* const*>(flags_dev), rank, nranks, slot, epoch, err, gkz::g_barrier_budget);
+      reinterpret_cast<uint32_t* const*>(flags_dev), rank, nranks, slot, epoch, err, gkz::g_barrier_budget, nullptr);
+  return gk::launch_status();
+}
+
+// The same barrier with the epoch kept in device memory (`epoch_dev`: barriers completed so far on this slot, advanced
+// by the kernel), so that the launch can be captured in a CUDA graph and replayed.
+GK_EXPORT int gk_peer_barrier_dev(const void* flags_dev, int rank, int nranks, int slot, unsigned int* epoch_dev,
+                                  int* err, void* stream) {
+  if (nranks < 1 || nranks > MAX_RANKS || !epoch_dev) return -1;
+  peer_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<uint32_t* const*>(flags_dev), rank, nranks, slot, 0u, err, gkz::g_barrier_budget, epoch_dev);
   return gk::launch_status();
 }
 

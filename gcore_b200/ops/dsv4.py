@@ -35,9 +35,12 @@ def indexer_scores(q, k, w, ks, ke, scale):
         return indexer_scores_ref(q, k, w, ks, ke, scale)
     out = torch.empty(S, T, dtype=torch.float32, device=q.device)
     LAUNCHES["dsv4"] += 1
-    _lib.check(_lib.kernels().gk_dsv4_indexer_fwd(_lib.ptr(q.contiguous()), _lib.ptr(k.contiguous()),
-                                                  _lib.ptr(w.float().contiguous()), _lib.ptr(ks.int().contiguous()),
-                                                  _lib.ptr(ke.int().contiguous()), _lib.ptr(out), S, T, H, D,
+    # converted / compacted copies get names: a temporary inside the call expression is released as soon as its pointer
+    # has been taken, and the next temporary may be given the same block before the asynchronous kernel has read it
+    q, k, w, ks, ke = q.contiguous(), k.contiguous(), w.float().contiguous(), ks.int().contiguous(), ke.int().contiguous()
+    _lib.check(_lib.kernels().gk_dsv4_indexer_fwd(_lib.ptr(q), _lib.ptr(k),
+                                                  _lib.ptr(w), _lib.ptr(ks),
+                                                  _lib.ptr(ke), _lib.ptr(out), S, T, H, D,
                                                   float(scale), _lib.stream_ptr()), "dsv4_indexer_fwd")
     return out
 
@@ -67,9 +70,11 @@ class _IndexerSelected(torch.autograd.Function):
         dk = torch.zeros(T, D, dtype=torch.float32, device=q.device)
         dw = torch.empty(S, H, dtype=torch.float32, device=q.device)
         LAUNCHES["dsv4"] += 1
+        qc, kc, wc, ic, dsc = (q.contiguous(), k.contiguous(), w.float().contiguous(), idx.int().contiguous(),
+                               ds.float().contiguous())   # named: they must outlive the asynchronous launch
         _lib.check(_lib.kernels().gk_dsv4_indexer_bwd(
-            _lib.ptr(q.contiguous()), _lib.ptr(k.contiguous()), _lib.ptr(w.float().contiguous()),
-            _lib.ptr(idx.int().contiguous()), _lib.ptr(ds.float().contiguous()), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dw),
+            _lib.ptr(qc), _lib.ptr(kc), _lib.ptr(wc),
+            _lib.ptr(ic), _lib.ptr(dsc), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dw),
             S, T, H, D, K, float(ctx.scale), _lib.stream_ptr()), "dsv4_indexer_bwd")
         return dq.to(q.dtype), dk.to(k.dtype), dw.to(w.dtype), None, None
 
@@ -128,9 +133,10 @@ class _SparseMqa(torch.autograd.Function):
         dkv = torch.zeros(T, D, dtype=torch.float32, device=q.device)
         dsk = torch.zeros(H, dtype=torch.float32, device=q.device)
         LAUNCHES["dsv4"] += 1
+        do = do.contiguous()
         _lib.check(_lib.kernels().gk_dsv4_sparse_mqa_bwd(
             _lib.ptr(q), _lib.ptr(kv), _lib.ptr(sk if ctx.has_sinks else None), _lib.ptr(idx), _lib.ptr(out),
-            _lib.ptr(lse), _lib.ptr(do.contiguous()), _lib.ptr(dq), _lib.ptr(dkv), _lib.ptr(dsk), S, T, H, D, K,
+            _lib.ptr(lse), _lib.ptr(do), _lib.ptr(dq), _lib.ptr(dkv), _lib.ptr(dsk), S, T, H, D, K,
             float(ctx.scale), _lib.stream_ptr()), "dsv4_sparse_mqa_bwd")
         return dq.to(q.dtype), dkv.to(kv.dtype), (dsk.to(ctx.sink_dtype) if ctx.has_sinks else None), None, None
 

@@ -160,8 +160,9 @@ def gemm_fp8_blockscaled(a_q, a_s, b_q, b_s, out_dtype=torch.bfloat16):
         return (dequant_1x128(a_q, a_s) @ dequant_128x128(b_q, b_s).t()).to(out_dtype)
     out = torch.empty(M, N, dtype=out_dtype, device=a_q.device)
     LAUNCHES["quant"] += 1
+    a_s, b_s = a_s.contiguous(), b_s.contiguous()   # named: a temporary must outlive the asynchronous launch
     rc = _lib.kernels().gk_gemm_fp8_blockscaled(_lib.ptr(a_q), a_q.stride(0), _lib.ptr(b_q), b_q.stride(0),
-                                                _lib.ptr(a_s.contiguous()), _lib.ptr(b_s.contiguous()), _lib.ptr(out),
+                                                _lib.ptr(a_s), _lib.ptr(b_s), _lib.ptr(out),
                                                 out.stride(0), int(out_dtype == torch.float32), M, N, K,
                                                 _lib.ptr(_lib.err_flag(a_q.device)), _lib.stream_ptr())
     _lib.check(rc, "gemm_fp8_blockscaled")
@@ -187,10 +188,11 @@ def gemm_fp8_grouped(a_q, a_s, b_q, b_s, offsets, num_groups: int, out_dtype=tor
         return out.to(out_dtype)
     out = torch.zeros(R, N, dtype=out_dtype, device=a_q.device)
     LAUNCHES["quant"] += 1
+    a_s, b_s, offs = a_s.contiguous(), b_s.contiguous(), offsets.int().contiguous()   # named: they must outlive the launch
     rc = _lib.kernels().gk_gemm_fp8_grouped(_lib.ptr(a_q), a_q.stride(0), _lib.ptr(b_q), b_q.stride(0),
-                                            _lib.ptr(a_s.contiguous()), _lib.ptr(b_s.contiguous()), _lib.ptr(out),
+                                            _lib.ptr(a_s), _lib.ptr(b_s), _lib.ptr(out),
                                             out.stride(0), int(out_dtype == torch.float32), R, N, K,
-                                            _lib.ptr(offsets.int().contiguous()), num_groups,
+                                            _lib.ptr(offs), num_groups,
                                             _lib.ptr(_lib.err_flag(a_q.device)), _lib.stream_ptr())
     _lib.check(rc, "gemm_fp8_grouped")
     return out

@@ -43,9 +43,12 @@ class _Route(torch.autograd.Function):
         idx = torch.empty(T, K, dtype=torch.int64, device=logits.device)
         w = torch.empty(T, K, dtype=torch.float32, device=logits.device)
         LAUNCHES["router"] += 1
+        # named copies: a temporary inside the call expression would be released before the asynchronous launch reads it
+        bias_f = bias.float().contiguous() if bias is not None else None
+        replay_l = replay.to(device=logits.device, dtype=torch.int64).contiguous() if replay is not None else None
         _lib.check(_lib.kernels().gk_router_fwd(
-            _lib.ptr(logits), _lib.ptr(bias.float().contiguous() if bias is not None else None),
-            _lib.ptr(replay.to(device=logits.device, dtype=torch.int64).contiguous() if replay is not None else None),
+            _lib.ptr(logits), _lib.ptr(bias_f),
+            _lib.ptr(replay_l),
             _lib.ptr(idx), _lib.ptr(w), T, E, K, n_group, topk_group, int(sigmoid), int(norm), float(scale),
             _lib.stream_ptr()), "router_fwd")
         ctx.save_for_backward(logits, idx)
@@ -60,7 +63,8 @@ class _Route(torch.autograd.Function):
         T, E = logits.shape
         dl = torch.empty_like(logits)
         LAUNCHES["router"] += 1
-        _lib.check(_lib.kernels().gk_router_bwd(_lib.ptr(logits), _lib.ptr(idx), _lib.ptr(g_w.float().contiguous()),
+        g_w = g_w.float().contiguous()
+        _lib.check(_lib.kernels().gk_router_bwd(_lib.ptr(logits), _lib.ptr(idx), _lib.ptr(g_w),
                                                 _lib.ptr(dl), T, E, K, sigmoid, norm, scale, _lib.stream_ptr()),
                    "router_bwd")
         return dl, None, None, None, None, None, None, None, None

@@ -55,6 +55,11 @@ class FusedEP:
         self.bflag_ptrs = torch.tensor(self.bflags.ptrs, dtype=torch.int64, device=self.device)
         self.plan_calls = 0
         self.barrier_epoch = 0
+        # call / epoch counters on the device ([0] plans, [1] barriers), advanced by the kernels themselves: the whole
+        # dispatch -> experts -> combine sequence can then be captured in a CUDA graph and replayed (decode steps of
+        # an expert-parallel rollout engine)
+        self.dev_ctr = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self.dev_epochs = hasattr(_lib.kernels(), "gk_ep_plan_dev") and hasattr(_lib.kernels(), "gk_peer_barrier_dev")
         torch.cuda.synchronize()
         dist.barrier(group=group)
 
@@ -64,6 +69,11 @@ class FusedEP:
     def barrier(self):
         self.barrier_epoch += 1
         LAUNCHES["ep"] += 1
+        if self.dev_epochs:
+            _lib.check(_lib.kernels().gk_peer_barrier_dev(_lib.ptr(self.bflag_ptrs), self.rank, self.ep, 0,
+                                                          _lib.ptr(self.dev_ctr[1:]), self._err(), _lib.stream_ptr()),
+                       "ep_barrier")
+            return
         _lib.check(_lib.kernels().gk_peer_barrier(_lib.ptr(self.bflag_ptrs), self.rank, self.ep, 0, self.barrier_epoch,
                                                   self._err(), _lib.stream_ptr()), "ep_barrier")
 
@@ -74,7 +84,8 @@ class FusedEP:
             raise RuntimeError(f"expert-parallel buffers were sized for {self.max_tokens} tokens per micro-batch, got "
                                f"{T}; set GCORE_EP_MAX_TOKENS")
         flat = idx.reshape(-1)
-        cnt = torch.bincount(flat, minlength=self.E)
+        # histogram without a host synchronisation (bincount sizes its output on the host)
+        cnt = torch.zeros(self.E, dtype=torch.int64, device=flat.device).scatter_add_(0, flat, torch.ones_like(flat))
         order = torch.argsort(flat, stable=True)
         starts = cnt.cumsum(0) - cnt
         pos = torch.empty_like(flat)
@@ -85,10 +96,16 @@ class FusedEP:
                   tot_local=torch.zeros(self.E_local, dtype=torch.int32, device=self.device),
                   dst_row=torch.empty(T * K, dtype=torch.int32, device=self.device))
         LAUNCHES["ep"] += 1
-        _lib.check(_lib.kernels().gk_ep_plan(_lib.ptr(st["cnt"]), self.plan_ptrs, self.rank, self.ep, self.E, SEG,
-                                             self.R_max, self.plan_calls, _lib.ptr(st["send_base"]),
-                                             _lib.ptr(st["offsets"]), _lib.ptr(st["tot_local"]), self._err(),
-                                             _lib.stream_ptr()), "ep_plan")
+        if self.dev_epochs:
+            _lib.check(_lib.kernels().gk_ep_plan_dev(_lib.ptr(st["cnt"]), self.plan_ptrs, self.rank, self.ep, self.E, SEG,
+                                                     self.R_max, _lib.ptr(self.dev_ctr), _lib.ptr(st["send_base"]),
+                                                     _lib.ptr(st["offsets"]), _lib.ptr(st["tot_local"]), self._err(),
+                                                     _lib.stream_ptr()), "ep_plan")
+        else:
+            _lib.check(_lib.kernels().gk_ep_plan(_lib.ptr(st["cnt"]), self.plan_ptrs, self.rank, self.ep, self.E, SEG,
+                                                 self.R_max, self.plan_calls, _lib.ptr(st["send_base"]),
+                                                 _lib.ptr(st["offsets"]), _lib.ptr(st["tot_local"]), self._err(),
+                                                 _lib.stream_ptr()), "ep_plan")
         self.plan_calls += 1
         return st
 

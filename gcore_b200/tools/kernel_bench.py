@@ -670,9 +670,12 @@ def cmd_fused(argv=None):
                                   _lib.ptr(tot), err, _lib.stream_ptr()), "ep_plan")
         wgt = torch.rand(T * K, device=dev)
         y = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+        # int32 copies made once and kept alive: a temporary created inside the call expression would be released (and
+        # its block handed to the next temporary) before the asynchronous kernel reads it
+        flat_i, pos_i = flat.int().contiguous(), pos.int().contiguous()
 
         def launch():
-            _lib.check(lib.gk_ep_push(_lib.ptr(x), None, _lib.ptr(flat.int()), _lib.ptr(pos.int()), _lib.ptr(sb),
+            _lib.check(lib.gk_ep_push(_lib.ptr(x), None, _lib.ptr(flat_i), _lib.ptr(pos_i), _lib.ptr(sb),
                                       _lib.ptr(offs), _lib.ptr(tot), ptrs(*recv), _lib.ptr(dst_row), 0, ep, El, SEG, R_max,
                                       K, H, T, _lib.stream_ptr()), "ep_push")
             _lib.check(lib.gk_ep_pull(ptrs(*recv), _lib.ptr(dst_row), _lib.ptr(wgt), _lib.ptr(y), None, ep, K, H, R_max, T,

@@ -19,7 +19,9 @@ namespace gkw {
 using namespace gk;
 
 constexpr int BMW = 256, BN = 256, BK = 64, UMMA_K = 16;
-constexpr int THREADS = 192;
+constexpr int EPI_WARPS = 8;       // two per TMEM lane quarter: each drains one 128-column half of an accumulator
+constexpr int EPI_THREADS = EPI_WARPS * 32;
+constexpr int THREADS = 64 + EPI_THREADS;
 constexpr int STAGES = 3;
 constexpr int A_BYTES = BMW * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 // Epilogue staging: every epilogue warp owns 32 rows x 128 bytes (64 bf16 or 32 fp32 columns of its TMEM lane
@@ -28,8 +30,9 @@ constexpr int A_BYTES = BMW * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYT
 // warp-wide store: every global store instruction then writes complete 128-byte lines instead of 32 separate
 // 16-byte fragments.  The accumulators of this kernel are not double-buffered, so the time the epilogue needs to
 // drain the first half of a tile is time the tensor cores wait.
+constexpr int MAX_TAIL_KS = 4;      // K-slices of a tail tile (their partials are summed by one CTA)
 constexpr int STAGE_ROW_BYTES = 128;
-constexpr int EPI_STAGE_BYTES = 4 * 32 * STAGE_ROW_BYTES;
+constexpr int EPI_STAGE_BYTES = EPI_WARPS * 32 * STAGE_ROW_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_STAGE_BYTES + 1024 + 256;
 
 struct WParams {
@@ -154,8 +157,8 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     mbar_init(tfull, 1);
-    mbar_init(&tempty[0], 128);
-    mbar_init(&tempty[1], 128);
+    mbar_init(&tempty[0], EPI_THREADS);
+    mbar_init(&tempty[1], EPI_THREADS);
     fence_barrier_init();
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
@@ -251,7 +254,8 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       pt ^= 1;
     }
   } else {
-    const int quad = warp & 3;
+    const int quad = warp & 3;            // the TMEM lane quarter a warp may read is fixed by its index
+    const int chalf = (warp - 2) >> 2;    // which 128 columns of the 256
     uint32_t pt = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < nitems && ok; w += gridDim.x) {
@@ -275,7 +279,7 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + half * BN;
           const int rin = half * 128 + quad * 32 + lane;
 #pragma unroll 1
-          for (int c = 0; c < BN / 32; ++c) {
+          for (int c = chalf * 4; c < chalf * 4 + 4; ++c) {
             uint32_t r[32];
             tmem_ld32(taddr + c * 32, r);
             tmem_ld_wait();
@@ -287,9 +291,9 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         pt ^= 1;
         __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
         if (threadIdx.x == 64) *s_last = atomicAdd(&p.counters[tslot], 1) == p.tail_ks - 1 ? 1 : 0;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
         if (*s_last) {
           __threadfence();
           const float* base = p.ws + static_cast<long long>(tslot) * p.tail_ks * (BMW * BN);
@@ -297,21 +301,33 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int half = 0; half < 2; ++half) {
             const int rin = half * 128 + quad * 32 + lane;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = chalf * 4; c < chalf * 4 + 4; ++c) {
+              // all slices' loads of a chunk are in flight together (at most MAX_TAIL_KS x 32 per thread): the pass
+              // costs one trip to L2 per chunk, not one per slice
+              float part[MAX_TAIL_KS][32];
+#pragma unroll
+              for (int sl = 0; sl < MAX_TAIL_KS; ++sl) {
+                const int s2 = sl < p.tail_ks ? sl : 0;   // a repeated slice is loaded but not added
+                const float* src = base + static_cast<long long>(s2) * (BMW * BN) + static_cast<long long>(c * 32) * BMW + rin;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) part[sl][j] = __ldcg(src + j * BMW);
+              }
               float v[32];
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = 0.f;
-              for (int sl = 0; sl < p.tail_ks; ++sl) {
-                const float* src = base + static_cast<long long>(sl) * (BMW * BN) + static_cast<long long>(c * 32) * BMW + rin;
+              for (int j = 0; j < 32; ++j) v[j] = part[0][j];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] += __ldcg(src + j * BMW);
+              for (int sl = 1; sl < MAX_TAIL_KS; ++sl) {
+                if (sl < p.tail_ks) {
+#pragma unroll
+                  for (int j = 0; j < 32; ++j) v[j] += part[sl][j];
+                }
               }
               store32(p, v, m0 + rin, n0 + c * 32);
             }
           }
           if (threadIdx.x == 64) p.counters[tslot] = 0;
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
         continue;
       }
 #pragma unroll 1
@@ -319,12 +335,12 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int row = m0 + half * 128 + quad * 32 + lane;
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + half * BN;
         if (p.staged) {
-          uint8_t* st = epi_stage + quad * (32 * STAGE_ROW_BYTES);
+          uint8_t* st = epi_stage + (warp - 2) * (32 * STAGE_ROW_BYTES);
           const int esz = p.out_fp32 ? 4 : 2;
           const int group_cols = STAGE_ROW_BYTES / esz;          // 32 fp32 or 64 bf16 columns per pass
           const int row0 = m0 + half * 128 + quad * 32;           // first row of this warp
 #pragma unroll 1
-          for (int g0 = 0; g0 < BN; g0 += group_cols) {
+          for (int g0 = chalf * 128; g0 < chalf * 128 + 128; g0 += group_cols) {
 #pragma unroll 1
             for (int c = g0 / 32; c < (g0 + group_cols) / 32; ++c) {
               float v[32];
@@ -402,7 +418,7 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         } else {
 #pragma unroll 1
-          for (int c = 0; c < BN / 32; ++c) {
+          for (int c = chalf * 4; c < chalf * 4 + 4; ++c) {
             float v[32];
             if (kblocks > 0) {
               uint32_t r[32];
@@ -483,7 +499,7 @@ GK_EXPORT int gk_gemm_wide(const void* A, long long lda, long long a_rows, int a
     // as many slices as fill the idle SMs of the partial wave, at least four k-blocks each
     int ks = sms / tail;
     if (ks > kblocks / 4) ks = kblocks / 4;
-    if (ks > 16) ks = 16;
+    if (ks > MAX_TAIL_KS) ks = MAX_TAIL_KS;
     const long long need = static_cast<long long>(tail) * ks * BMW * BN;
     if (ks >= 2 && need <= ws_floats && tail <= counter_ints) {
       const int per = (kblocks + ks - 1) / ks;

@@ -69,10 +69,10 @@ def _wide_waves(tiles: int, kblocks: int) -> float:
     if tail == 0:
         return float(full)
     if WIDE["tail_split"] and tail * 2 <= 148 and kblocks >= 8:
-        ks = min(148 // tail, kblocks // 4, 16)
+        ks = min(148 // tail, kblocks // 4, 4)
         if ks >= 2:
             per = -(-kblocks // ks)
-            return full + per / kblocks + 0.06
+            return full + per / kblocks + 0.08
     return float(full + 1)
 
 

@@ -250,10 +250,18 @@ class InferEngine:
         self.use_graph = use_cuda_graph and self.device.type == "cuda" and not _lib.force_eager()
         self.ep_group = None  # set when experts are parallel: engines of the group then run their passes in lockstep
         if any(getattr(lw.moe, "ep_size", 1) > 1 for lw in weights.layers if lw.moe is not None):
-            # expert-parallel dispatch sizes its exchanges on the host (and the peer-memory path numbers its epochs
-            # there), so a decode step cannot be replayed from a captured graph
-            self.use_graph = False
             self.ep_group = ps.get_expert_model_parallel_group()
+            # The NCCL dispatch sizes its exchanges on the host, so a decode step over it cannot be replayed from a
+            # captured graph.  The peer-memory dispatch plans on the device and keeps its call / barrier epochs in
+            # device memory (parallel/ep_fused.py), so its decode steps are captured like the dense ones; the
+            # engines of the group replay in lockstep (same number of steps between two host agreements).
+            fused_ep = (self.device.type == "cuda" and not _lib.force_eager()
+                        and os.environ.get("GCORE_FUSED_EP", "1") != "0"
+                        and os.environ.get("GCORE_EP_DECODE_GRAPH", "1") != "0"
+                        and hasattr(_lib.kernels(), "gk_ep_plan_dev") and dist.get_world_size(self.ep_group) <= 8
+                        and cfg.hidden_size % 8 == 0)
+            if not fused_ep:
+                self.use_graph = False
         # decode steps between two host synchronisations: ``sync_interval`` while requests wait for a slot (a finished
         # request should hand its slot over soon), up to ``max_sync_interval`` when nothing waits (then only the
         # discarded tokens after an early stop are at stake, and every synchronisation costs the GPU an idle gap)

@@ -64,6 +64,9 @@ def kernels() -> ctypes.CDLL:
         stg = os.environ.get("GCORE_WIDE_STAGED")       # 0: the wide GEMM's epilogue stores rows per thread
         if stg is not None and hasattr(lib, "gk_gemm_wide_set_staged"):
             lib.gk_gemm_wide_set_staged(int(stg))
+        pt = os.environ.get("GCORE_PAGED_TARGET_CTAS")  # CTAs the paged decode kernel sizes its KV splits for (444)
+        if pt is not None and hasattr(lib, "gk_paged_set_target_ctas"):
+            lib.gk_paged_set_target_ctas(int(pt))
         cap = os.environ.get("GCORE_DECODE_SMEM_KB")   # shared-memory budget of decode GEMM CTAs (0 = full ring)
         if cap is not None and hasattr(lib, "gk_gemm_set_decode_smem_cap"):
             lib.gk_gemm_set_decode_smem_cap(int(cap) * 1024)
@@ -190,5 +193,6 @@ def _declare_kernels(lib: ctypes.CDLL):
     d("gk_kv_append_rope", [P, P, P, P, P, I, I, I, I, I, I, F, I, P])
     d("gk_paged_decode", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P])
     d("gk_paged_decode_scratch", [I, I, I, I, ctypes.POINTER(L)], None)
+    d("gk_paged_set_target_ctas", [I], None)
     d("gk_attn_fwd", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P])
     d("gk_attn_bwd", [P, P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P])

@@ -13,7 +13,11 @@ namespace gk {
 constexpr int PD_THREADS = 128;
 constexpr int PD_TILE = 32;     // tokens per shared-memory tile
 constexpr int PD_MAX_GROUP = 16;
-constexpr int PD_SPLIT = 128;   // tokens per KV split
+constexpr int PD_SPLIT = 128;   // tokens per KV split (the finest; the tensor-core kernel uses multiples)
+inline int& paged_target_ctas() {
+  static int n = 444;
+  return n;
+}
 
 // qkv: [T, (Hq + 2*Hk) * D] as produced by the fused QKV projection ([q | k | v] per token).
 // Rotates q and k in place (rotate-half pairing) and writes k, v to cache slot `slots[t]`
@@ -219,7 +223,8 @@ __global__ void __launch_bounds__(PD2_WARPS * 32, 3) paged_decode_mma_kernel(
     const __nv_bfloat16* __restrict__ q, long long q_stride, const __nv_bfloat16* __restrict__ kc,
     const __nv_bfloat16* __restrict__ vc, const int* __restrict__ block_table, int max_blocks,
     const int* __restrict__ ctx_len, const float* __restrict__ sinks, __nv_bfloat16* __restrict__ out,
-    float* __restrict__ scratch, int Hq, int Hk, int block_size, int window, float scale, int nsplit) {
+    float* __restrict__ scratch, int Hq, int Hk, int block_size, int window, float scale, int nsplit,
+    int split_tokens) {
   constexpr int D = 128;
   __shared__ __align__(16) uint8_t sq[16 * 256];  // Q tile, 16 rows (heads, zero padded) x 256 B, chunk-swizzled
   __shared__ long long slot_buf[PD2_WARPS][32];
@@ -235,30 +240,34 @@ __global__ void __launch_bounds__(PD2_WARPS * 32, 3) paged_decode_mma_kernel(
   const int len = ctx_len[b];
   int start = 0;
   if (window > 0 && len > window) start = len - window;
-  // splits beyond this request's context have nothing to do (the combine kernel only reads the live ones)
-  if (split > 0 && start + split * PD_SPLIT >= len) return;
+  // A CTA owns `split_tokens` consecutive tokens of the request (the host sizes the splits so that the grid about
+  // fills the GPU once: with many requests a CTA walks a request's whole context, and the per-CTA costs - context
+  // length, block table, Q staging, merge, partial write - are paid once per request instead of once per 128 tokens).
+  // Splits beyond this request's context have nothing to do (the combine kernel only reads the live ones).
+  const int s0 = start + split * split_tokens;
+  if (split > 0 && s0 >= len) return;
+  int s1 = s0 + split_tokens;
+  if (s1 > len) s1 = len;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int w0 = start + split * PD_SPLIT + warp * PD2_TOK_PER_WARP;
-  int w1 = w0 + PD2_TOK_PER_WARP;
-  if (w1 > len) w1 = len;
-  const int nt = w1 > w0 ? w1 - w0 : 0;
+  const int ntiles = s1 > s0 ? (s1 - s0 + 31) / 32 : 0;
 
-  // ---- request this warp's K / V tile first (one memory round trip per warp), then stage Q while it is in flight
   uint8_t* kt = k_tile + warp * (32 * 256);
   uint8_t* vt = v_tile + warp * (32 * 256);
-  {
-    long long slot = 0;
-    if (lane < nt) {
-      const int tok = w0 + lane;
-      slot = static_cast<long long>(block_table[static_cast<long long>(b) * max_blocks + tok / block_size]) *
-                 block_size + tok % block_size;
-    }
-    slot_buf[warp][lane] = slot;
-  }
-  __syncwarp();
-  if (nt > 0) {
-    const uint32_t kts = static_cast<uint32_t>(__cvta_generic_to_shared(kt));
-    const uint32_t vts = static_cast<uint32_t>(__cvta_generic_to_shared(vt));
+  const uint32_t kts = static_cast<uint32_t>(__cvta_generic_to_shared(kt));
+  const uint32_t vts = static_cast<uint32_t>(__cvta_generic_to_shared(vt));
+
+  // this warp's tiles are warp, warp + 4, ...: request the first one, stage Q while it is in flight
+  auto tile_slot = [&](int t) -> long long {
+    const int tok = s0 + t * 32 + lane;
+    if (t >= ntiles || tok >= s1) return 0;
+    return static_cast<long long>(block_table[static_cast<long long>(b) * max_blocks + tok / block_size]) * block_size +
+           tok % block_size;
+  };
+  auto request_tile = [&](int t, long long slot_lane) {
+    const int base_tok = s0 + t * 32;
+    const int nt = s1 - base_tok < 32 ? s1 - base_tok : 32;
+    slot_buf[warp][lane] = slot_lane;
+    __syncwarp();
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       const int idx = i * 32 + lane;
@@ -272,7 +281,8 @@ __global__ void __launch_bounds__(PD2_WARPS * 32, 3) paged_decode_mma_kernel(
                    "l"(vc + (slot * Hk + kvh) * D + ch * 8), "r"(nbytes) : "memory");
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
-  }
+  };
+  if (warp < ntiles) request_tile(warp, tile_slot(warp));
   for (int i = tid; i < 16 * 16; i += PD2_WARPS * 32) {
     const int g = i >> 4, c = i & 15;
     uint4 v = make_uint4(0, 0, 0, 0);
@@ -288,7 +298,7 @@ __global__ void __launch_bounds__(PD2_WARPS * 32, 3) paged_decode_mma_kernel(
 #pragma unroll
   for (int j = 0; j < 16; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
 
-  if (nt > 0) {
+  if (warp < ntiles) {
     // Q as A fragments for the 8 k-steps (16 dims each)
     uint32_t qa[8][4];
     const uint32_t sqs = static_cast<uint32_t>(__cvta_generic_to_shared(sq));
@@ -298,63 +308,75 @@ __global__ void __launch_bounds__(PD2_WARPS * 32, 3) paged_decode_mma_kernel(
       const int ch = ks * 2 + (lane >> 4);
       ldsm_x4(qa[ks], sqs + row * 256 + ((ch ^ (row & 15)) << 4));
     }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncwarp();
-    const uint32_t kts = static_cast<uint32_t>(__cvta_generic_to_shared(kt));
-    const uint32_t vts = static_cast<uint32_t>(__cvta_generic_to_shared(vt));
-    // ---- S = Q K^T : 4 token tiles of 8
-    float s[4][4];
+#pragma unroll 1
+    for (int t = warp; t < ntiles; t += PD2_WARPS) {
+      const int base_tok = s0 + t * 32;
+      const int nt = s1 - base_tok < 32 ? s1 - base_tok : 32;
+      // the block-table entries of this warp's next tile are fetched while the current tile's K / V arrive
+      const long long next_slot = tile_slot(t + PD2_WARPS);
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      __syncwarp();
+      // ---- S = Q K^T : 4 token tiles of 8
+      float sc[4][4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+      for (int j = 0; j < 4; ++j) { sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f; }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < 4; ++j) {
 #pragma unroll
-      for (int kp = 0; kp < 4; ++kp) {  // pairs of k-steps
-        uint32_t kb[4];
-        const int row = j * 8 + (lane & 7);
-        const int ch = kp * 4 + (lane >> 3);
-        ldsm_x4(kb, kts + row * 256 + ((ch ^ (row & 15)) << 4));
-        mma_bf16_16816(s[j], qa[2 * kp], kb[0], kb[1]);
-        mma_bf16_16816(s[j], qa[2 * kp + 1], kb[2], kb[3]);
+        for (int kp = 0; kp < 4; ++kp) {  // pairs of k-steps
+          uint32_t kb[4];
+          const int row = j * 8 + (lane & 7);
+          const int ch = kp * 4 + (lane >> 3);
+          ldsm_x4(kb, kts + row * 256 + ((ch ^ (row & 15)) << 4));
+          mma_bf16_16816(sc[j], qa[2 * kp], kb[0], kb[1]);
+          mma_bf16_16816(sc[j], qa[2 * kp + 1], kb[2], kb[3]);
+        }
       }
-    }
-    // ---- softmax over this tile for row r0 (rows 8..15 are padding)
-    float mx = -FLT_MAX;
+      // ---- online softmax over this tile for row r0 (rows 8..15 are padding)
+      float mx = -FLT_MAX;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < 4; ++j) {
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int ti = j * 8 + cq + e;
-        const float v = ti < nt ? s[j][e] * scale : -FLT_MAX;
-        s[j][e] = v;
-        mx = fmaxf(mx, v);
+        for (int e = 0; e < 2; ++e) {
+          const int ti = j * 8 + cq + e;
+          const float v = ti < nt ? sc[j][e] * scale : -FLT_MAX;
+          sc[j][e] = v;
+          mx = fmaxf(mx, v);
+        }
       }
-    }
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffff, mx, 1));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffff, mx, 2));
-    m_run = mx;
-    uint32_t pa[2][4];
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffff, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffff, mx, 2));
+      const float m_new = fmaxf(m_run, mx);
+      const float resc = m_run == -FLT_MAX ? 0.f : __expf(m_run - m_new);
+      m_run = m_new;
+      l_run *= resc;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float p0 = s[j][0] == -FLT_MAX ? 0.f : __expf(s[j][0] - mx);
-      const float p1 = s[j][1] == -FLT_MAX ? 0.f : __expf(s[j][1] - mx);
-      l_run += p0 + p1;
-      // A fragment of k-step j/2: regs {rows lo cols lo, rows hi cols lo, rows lo cols hi, rows hi cols hi}
-      pa[j >> 1][(j & 1) * 2] = pack2_bf16(p0, p1);
-      pa[j >> 1][(j & 1) * 2 + 1] = 0u;  // padding rows
-    }
-    // ---- O = P V : 2 k-steps of 16 tokens, 16 dim tiles of 8
+      for (int j = 0; j < 16; ++j) { o[j][0] *= resc; o[j][1] *= resc; }
+      uint32_t pa[2][4];
 #pragma unroll
-    for (int kk = 0; kk < 2; ++kk) {
-#pragma unroll
-      for (int np = 0; np < 8; ++np) {  // pairs of dim tiles
-        uint32_t vb[4];
-        const int row = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-        const int ch = np * 2 + (lane >> 4);
-        ldsm_x4_trans(vb, vts + row * 256 + ((ch ^ (row & 15)) << 4));
-        mma_bf16_16816(o[2 * np], pa[kk], vb[0], vb[1]);
-        mma_bf16_16816(o[2 * np + 1], pa[kk], vb[2], vb[3]);
+      for (int j = 0; j < 4; ++j) {
+        const float p0 = sc[j][0] == -FLT_MAX ? 0.f : __expf(sc[j][0] - m_new);
+        const float p1 = sc[j][1] == -FLT_MAX ? 0.f : __expf(sc[j][1] - m_new);
+        l_run += p0 + p1;
+        // A fragment of k-step j/2: regs {rows lo cols lo, rows hi cols lo, rows lo cols hi, rows hi cols hi}
+        pa[j >> 1][(j & 1) * 2] = pack2_bf16(p0, p1);
+        pa[j >> 1][(j & 1) * 2 + 1] = 0u;  // padding rows
       }
+      // ---- O += P V : 2 k-steps of 16 tokens, 16 dim tiles of 8
+#pragma unroll
+      for (int kk = 0; kk < 2; ++kk) {
+#pragma unroll
+        for (int np = 0; np < 8; ++np) {  // pairs of dim tiles
+          uint32_t vb[4];
+          const int row = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+          const int ch = np * 2 + (lane >> 4);
+          ldsm_x4_trans(vb, vts + row * 256 + ((ch ^ (row & 15)) << 4));
+          mma_bf16_16816(o[2 * np], pa[kk], vb[0], vb[1]);
+          mma_bf16_16816(o[2 * np + 1], pa[kk], vb[2], vb[3]);
+        }
+      }
+      __syncwarp();   // every lane is done with the tile before its storage is refilled
+      if (t + PD2_WARPS < ntiles) request_tile(t + PD2_WARPS, next_slot);
     }
   }
   // ---- merge the four warps (K tiles are dead after the barrier: their storage carries the partial outputs)
@@ -395,14 +417,15 @@ __global__ void __launch_bounds__(PD2_WARPS * 32, 3) paged_decode_mma_kernel(
 template <int D>
 __global__ void paged_decode_combine_kernel(const float* __restrict__ scratch, const float* __restrict__ sinks,
                                             const int* __restrict__ ctx_len, int window,
-                                            __nv_bfloat16* __restrict__ out, int Hq, int nsplit_total) {
+                                            __nv_bfloat16* __restrict__ out, int Hq, int nsplit_total,
+                                            int split_tokens) {
   pdl_launch_dependents();
   pdl_wait();
   const int b = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
   const float* base = scratch + (static_cast<long long>(b) * Hq + h) * nsplit_total * (D + 2);
   int span = ctx_len[b];
   if (window > 0 && span > window) span = window;
-  int nsplit = (span + PD_SPLIT - 1) / PD_SPLIT;  // live splits: the others were never written
+  int nsplit = (span + split_tokens - 1) / split_tokens;  // live splits: the others were never written
   if (nsplit < 1) nsplit = 1;
   if (nsplit > nsplit_total) nsplit = nsplit_total;
   float m = -FLT_MAX;
@@ -434,6 +457,9 @@ GK_EXPORT int gk_kv_append_rope(void* qkv, const int* pos, const int* slots, voi
   return launch_status();
 }
 
+// CTAs the tensor-core decode kernel aims for (three fit an SM); the host derives the split size from it
+GK_EXPORT void gk_paged_set_target_ctas(int n) { paged_target_ctas() = n > 0 ? n : 444; }
+
 GK_EXPORT void gk_paged_decode_scratch(int B, int Hq, int D, int max_ctx, long long* floats) {
   const long long ns = (max_ctx + PD_SPLIT - 1) / PD_SPLIT;
   *floats = static_cast<long long>(B) * Hq * ns * (D + 2);
@@ -449,9 +475,21 @@ GK_EXPORT int gk_paged_decode(const void* q, const void* kc, const void* vc, con
   if (B == 0) return 0;
   int span = max_ctx;
   if (window > 0 && window < span) span = window;
-  const int nsplit = (span + PD_SPLIT - 1) / PD_SPLIT > 0 ? (span + PD_SPLIT - 1) / PD_SPLIT : 1;
-  if (nsplit > 1 && !scratch) return -2;
+  const int nsplit_max = (span + PD_SPLIT - 1) / PD_SPLIT > 0 ? (span + PD_SPLIT - 1) / PD_SPLIT : 1;
+  int nsplit = nsplit_max, split_tokens = PD_SPLIT;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (Hq / Hk <= PD2_G) {
+    // as many splits as give the GPU about one wave of CTAs (three fit an SM), never finer than 128 tokens
+    const int pairs = B * Hk;
+    int want = paged_target_ctas() / pairs;
+    if (want < 1) want = 1;
+    if (want < nsplit) nsplit = want;
+    split_tokens = ((span + nsplit - 1) / nsplit + 31) / 32 * 32;
+    if (split_tokens < PD_SPLIT) split_tokens = PD_SPLIT;
+    nsplit = (span + split_tokens - 1) / split_tokens;
+    if (nsplit < 1) nsplit = 1;
+  }
+  if (nsplit > 1 && !scratch) return -2;
   dim3 grid(B, Hk, nsplit);
   if (Hq / Hk <= PD2_G) {
     constexpr int PD2_SMEM = 2 * PD2_WARPS * 32 * 128 * 2;
@@ -463,7 +501,7 @@ GK_EXPORT int gk_paged_decode(const void* q, const void* kc, const void* vc, con
     launch_k(paged_decode_mma_kernel, grid, dim3(PD2_WARPS * 32), PD2_SMEM, st,
         reinterpret_cast<const __nv_bfloat16*>(q), q_stride, reinterpret_cast<const __nv_bfloat16*>(kc),
         reinterpret_cast<const __nv_bfloat16*>(vc), block_table, max_blocks, ctx_len, sinks,
-        reinterpret_cast<__nv_bfloat16*>(out), scratch, Hq, Hk, block_size, window, scale, nsplit);
+        reinterpret_cast<__nv_bfloat16*>(out), scratch, Hq, Hk, block_size, window, scale, nsplit, split_tokens);
   } else
   paged_decode_kernel<128><<<grid, PD_THREADS, 0, st>>>(
       reinterpret_cast<const __nv_bfloat16*>(q), q_stride, reinterpret_cast<const __nv_bfloat16*>(kc),
@@ -471,7 +509,8 @@ GK_EXPORT int gk_paged_decode(const void* q, const void* kc, const void* vc, con
       reinterpret_cast<__nv_bfloat16*>(out), scratch, Hq, Hk, block_size, window, scale, nsplit);
   if (nsplit > 1) {
     launch_k(paged_decode_combine_kernel<128>, dim3(B, Hq), dim3(128), 0, st, scratch, sinks, ctx_len, window,
-                                                                  reinterpret_cast<__nv_bfloat16*>(out), Hq, nsplit);
+                                                                  reinterpret_cast<__nv_bfloat16*>(out), Hq, nsplit,
+                                                                  split_tokens);
   }
   return launch_status();
 }

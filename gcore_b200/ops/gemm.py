@@ -243,6 +243,8 @@ _SKINNY = [__import__("os").environ.get("GCORE_SKINNY_GEMM", "1") != "0"]
 
 
 _SKINNY_PLANS: dict = {}
+# output tiles (of 128 features) up to which the cluster kernel is tried: 37 x 4 CTAs fill the 148 SMs in one wave
+SKINNY_MAX_TILES = [int(os.environ.get("GCORE_SKINNY_MAX_TILES", "37"))]
 
 
 def _skinny_plan(T: int, tiles: int, kb: int, K: int):
@@ -279,7 +281,7 @@ def linear_forward(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None =
         kb = (K + 63) // 64
         # measured on B200 under graph replay: the cluster kernel wins for few tiles and moderate K (projections of a
         # tensor-parallel shard); the persistent kernel's global split-K wins for more tiles or very long K
-        if (tiles <= 32 and kb <= 160 and _SKINNY[0] and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+        if (tiles <= SKINNY_MAX_TILES[0] and kb <= 160 and _SKINNY[0] and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
                 and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
                 and hasattr(_lib.kernels(), "gk_gemm_skinny")):
             # few output tiles: cluster split-K with the reduction in distributed shared memory

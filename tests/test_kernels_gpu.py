@@ -405,6 +405,17 @@ def test_paged_decode_and_kv_append(window, use_sinks):
     ref = paged_decode(q.cpu(), kc.cpu(), vc.cpu(), perm.cpu(), ctx.cpu(), max(lens), window=window,
                        sinks=sinks.cpu() if use_sinks else None)
     _close(out, ref.to(DEV), atol=2e-2)
+    # the split size follows the number of CTAs the launch aims for: one CTA per (request, kv head) walking the whole
+    # context tile by tile (what large batches get), and two splits of several tiles each
+    from gcore_b200.ops import _lib
+    try:
+        for target in (1, 40):
+            _lib.kernels().gk_paged_set_target_ctas(target)
+            out_t = paged_decode(q, kc, vc, perm, ctx, max(lens), window=window, sinks=sinks)
+            _close(out_t, ref.to(DEV), atol=2e-2)
+    finally:
+        _lib.kernels().gk_paged_set_target_ctas(444)
+    _lib.check_device_errors()
 
 
 @pytest.mark.parametrize("D", [128, 64])

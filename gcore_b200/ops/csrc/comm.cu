@@ -139,7 +139,8 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_oneshot_kernel(ArParams 
 //   a   = bf16(sum over ranks, fixed order)            (what the separate all-reduce would have stored)
 //   res = bf16(a + residual)                           -> res_out      (a alone when there is no residual)
 //   y   = bf16(res * rsqrt(mean(res^2) + eps) * gamma) -> y
-// i.e. bit-identical to all-reduce followed by the RMSNorm kernel of elementwise.cu, on every rank.
+// The new residual is bit-identical to all-reduce followed by the RMSNorm kernel of elementwise.cu; the normalised
+// output agrees to rounding (the sum of squares is added up in another order) and is identical on every rank.
 struct ArNormParams {
   ArParams ar;                  // in = partial [rows, H]; out unused; n = rows * H
   const __nv_bfloat16* res_in;  // may be null
@@ -168,11 +169,9 @@ __device__ __forceinline__ uint4 pack_bf16x8(const float (&f)[8]) {
   return o;
 }
 
-constexpr int ARN_MAXV = 4;  // vectors of 8 per thread and row: H <= 256 * 8 * 4 = 8192
 
 __global__ void __launch_bounds__(AR_THREADS) allreduce_rmsnorm_kernel(ArNormParams q) {
   __shared__ int s_ok;
-  __shared__ float red[AR_THREADS / 32];
   const ArParams& p = q.ar;
   gk::pdl_launch_dependents();
   gk::pdl_wait();
@@ -217,54 +216,45 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_rmsnorm_kernel(ArNormPar
   }
   __syncthreads();
   if (s_ok) {
+    // one warp per row (the rows of a CTA run side by side, no block-wide barrier): pass 1 sums the ranks' partials in
+    // rank order, adds the residual, stores the new residual and accumulates the sum of squares; pass 2 re-reads the
+    // row it just wrote (L1 / L2) and writes the normalised output
     const uint4* mine = reinterpret_cast<const uint4*>(p.inbox[p.rank]) + static_cast<long long>(parity) * p.nranks * slot_vec;
     const uint4* gv = reinterpret_cast<const uint4*>(q.gamma);
-    for (int row = r0; row < r1; ++row) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int row = r0 + warp; row < r1; row += AR_THREADS / 32) {
       const long long rb = static_cast<long long>(row) * hv;
-      float f[ARN_MAXV][8];
       float ss = 0.f;
-#pragma unroll
-      for (int u = 0; u < ARN_MAXV; ++u) {
-        const int c = threadIdx.x + u * AR_THREADS;
-        if (c < hv) {
-          float tot[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          for (int r = 0; r < p.nranks; ++r) {
-            const uint4 w = r == p.rank ? in[rb + c] : __ldcg(mine + static_cast<long long>(r) * slot_vec + rb + c);
-            add8(tot, w);
-          }
-          unpack_bf16x8(pack_bf16x8(tot), f[u]);  // the value a stand-alone all-reduce would have stored
-          if (q.res_in) {
-            float g[8];
-            unpack_bf16x8(reinterpret_cast<const uint4*>(q.res_in)[rb + c], g);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) f[u][j] += g[j];
-          }
-          const uint4 stored = pack_bf16x8(f[u]);
-          reinterpret_cast<uint4*>(q.res_out)[rb + c] = stored;
-          unpack_bf16x8(stored, f[u]);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) ss += f[u][j] * f[u][j];
+      for (int c = lane; c < hv; c += 32) {
+        float tot[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int r = 0; r < p.nranks; ++r) {
+          const uint4 w = r == p.rank ? in[rb + c] : __ldcg(mine + static_cast<long long>(r) * slot_vec + rb + c);
+          add8(tot, w);
         }
+        float f[8];
+        unpack_bf16x8(pack_bf16x8(tot), f);  // the value a stand-alone all-reduce would have stored
+        if (q.res_in) {
+          float g[8];
+          unpack_bf16x8(reinterpret_cast<const uint4*>(q.res_in)[rb + c], g);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] += g[j];
+        }
+        const uint4 stored = pack_bf16x8(f);
+        reinterpret_cast<uint4*>(q.res_out)[rb + c] = stored;
+        unpack_bf16x8(stored, f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
       }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      __syncthreads();
-      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-      __syncthreads();
-      float t = 0.f;
+      const float rstd = rsqrtf(ss / q.H + q.eps);
+      for (int c = lane; c < hv; c += 32) {
+        float f[8], g[8], o[8];
+        unpack_bf16x8(reinterpret_cast<const uint4*>(q.res_out)[rb + c], f);   // this lane's own store
+        unpack_bf16x8(gv[c], g);
 #pragma unroll
-      for (int w = 0; w < AR_THREADS / 32; ++w) t += red[w];
-      const float rstd = rsqrtf(t / q.H + q.eps);
-#pragma unroll
-      for (int u = 0; u < ARN_MAXV; ++u) {
-        const int c = threadIdx.x + u * AR_THREADS;
-        if (c < hv) {
-          float g[8], o[8];
-          unpack_bf16x8(gv[c], g);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] = f[u][j] * rstd * g[j];
-          reinterpret_cast<uint4*>(q.y)[rb + c] = pack_bf16x8(o);
-        }
+        for (int j = 0; j < 8; ++j) o[j] = f[j] * rstd * g[j];
+        reinterpret_cast<uint4*>(q.y)[rb + c] = pack_bf16x8(o);
       }
     }
   }
@@ -408,7 +398,7 @@ GK_EXPORT int gk_allreduce_rmsnorm(const void* partial, const void* res_in, cons
                                    int rows, int H, float eps, int rank, int nranks, long long slot_elems,
                                    const unsigned long long* ptrs, unsigned int* state, int* err, void* stream) {
   const long long n = static_cast<long long>(rows) * H;
-  if (H % 8 || H > AR_THREADS * 8 * ARN_MAXV || n > slot_elems || nranks < 1 || nranks > MAX_RANKS) return -1;
+  if (H % 8 || n > slot_elems || nranks < 1 || nranks > MAX_RANKS) return -1;
   if (rows == 0) return 0;
   ArNormParams q;
   q.ar.in = reinterpret_cast<const __nv_bfloat16*>(partial);

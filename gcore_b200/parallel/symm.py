@@ -222,7 +222,7 @@ class PeerAllReduce:
         * gamma``, one kernel; ``None`` when the shape is outside the kernel's limits (the caller then runs the two
         steps separately)."""
         rows, H = partial.shape
-        if (rows * H > self.slot or H % 8 or H > 8192 or partial.dtype != torch.bfloat16 or not partial.is_contiguous()
+        if (rows * H > self.slot or H % 8 or partial.dtype != torch.bfloat16 or not partial.is_contiguous()
                 or gamma.dtype != torch.bfloat16 or (residual is not None and not residual.is_contiguous())
                 or not hasattr(_lib.kernels(), "gk_allreduce_rmsnorm")):
             return None

@@ -189,7 +189,8 @@ def test_allreduce_oneshot_rank0_of_2():
 
 @pytest.mark.parametrize("with_res", [True, False])
 def test_allreduce_residual_rmsnorm_rank0_of_2(with_res):
-    """One kernel = all-reduce, residual add and RMSNorm; bit-identical to the three steps done one after the other."""
+    """One kernel = all-reduce, residual add and RMSNorm: the residual stream bit-identical to the three steps done one
+    after the other, the normalised output to rounding."""
     lib = _lib()
     from gcore_b200.ops import fused
     torch.manual_seed(7)
@@ -215,7 +216,7 @@ def test_allreduce_residual_rmsnorm_rank0_of_2(with_res):
     summed = (x0.float() + x1.float()).bfloat16()
     y_ref, res_ref = fused.rmsnorm(summed, gamma, 1e-6, res)
     assert torch.equal(res_out, res_ref if with_res else summed)
-    assert torch.equal(y, y_ref)
+    assert torch.allclose(y.float(), y_ref.float(), atol=2e-2, rtol=1e-2)   # sum of squares added in another order
     assert torch.equal(peer_inbox[0, 0, :rows * H], x0.reshape(-1))
     assert peer_flags[0, 0].tolist() == [1] * ctas                   # CTAs without rows still publish their flag
     assert state[:2].tolist() == [1, 0]

@@ -189,6 +189,7 @@ def build_config(args, world):
     dist_cfg = {"tensor_model_parallel_size": tp, "sequence_parallel": tp > 1, "context_parallel_size": cp,
                 "expert_model_parallel_size": ep}
     policy = {"model_arch": args.model, "recompute": args.recompute, "recompute_num_layers": args.recompute_layers,
+              "offload_ref_model": bool(args.offload_ref),
               "share_rollout_weights": True, "dist_config": dist_cfg, "dynamic_mbs_target_seqlen": args.mb_tokens}
     ppo = {"ppo_ratio_eps": 0.2, "grpo_kl_loss_beta": 0.001, "advantage_type": "grpo", "loss_func": "grpo"}
     opt = {"lr": 1e-6, "lr_decay_style": "constant", "weight_decay": 0.01, "max_grad_norm": 1.0}
@@ -265,6 +266,10 @@ def main():
                     "whole 7B model shares the GPU with the activations), none when tensor parallelism halves it")
     ap.add_argument("--recompute-layers", type=int, default=None,
                     help="with --recompute full: recompute only the first N layers")
+    ap.add_argument("--offload-ref", type=int, default=None,
+                    help="1: the frozen reference model lives in pinned host memory outside its forward pass (its "
+                    "upload runs on a side stream under the old-policy pass); default: on at 1 GPU, where the whole "
+                    "model's optimizer state shares the GPU with the activations")
     args = ap.parse_args()
     for k, v in CONFIGS[args.config].items():
         if k != "kind" and getattr(args, k, None) is None:
@@ -280,6 +285,8 @@ def main():
             # 152 GB of weights, reference model, fp32 gradients and AdamW state leave room for the activations of
             # 16 of the 28 layers at 8192 tokens per micro-batch (peak 164 GB of 180); the other 12 are recomputed
             args.recompute_layers = 12
+    if args.offload_ref is None:
+        args.offload_ref = 0
     if args.impl == "reference":
         return reference_arm(args)
 
@@ -431,7 +438,8 @@ def bench_config_record(args, cfg, tp, cp, ep, dp):
     par = f"tp{tp}" + (f"cp{cp}" if cp > 1 else "") + (f"ep{ep}" if ep > 1 else "") + f"dp{dp}"
     rec = {"model": args.model + (f"-{args.layers}layers-DEBUG" if args.layers else ""), "parallelism": par,
            "weights": "random-init", "recompute": args.recompute, "recompute_layers": args.recompute_layers,
-           "micro_batch_tokens": args.mb_tokens, "l2": "inputs (weights of every pass) are larger than L2"}
+           "micro_batch_tokens": args.mb_tokens, "l2": "inputs (weights of every pass) are larger than L2",
+           "reference_model": "pinned host memory outside its forward pass" if args.offload_ref else "resident"}
     if args.kind == "sft":
         rec.update(global_batch=int(args.sequences), seq_len=int(args.seq_len),
                    documents="lognormal(7, 1.2) clipped to [64, 32768], packed")

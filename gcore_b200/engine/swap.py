@@ -44,6 +44,7 @@ class ModuleSwap:
         self.device = ts[0].device
         cuda = self.device.type == "cuda"
         self.bytes = 0
+        copied = False
         for t in ts:
             h = self.host.get(id(t))
             if h is None or not self.frozen:
@@ -51,13 +52,16 @@ class ModuleSwap:
                     h = torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=cuda)
                     self.host[id(t)] = h
                 h.copy_(t.data, non_blocking=cuda)
+                copied = True
             self.bytes += h.numel() * h.element_size()
-        if cuda:
+        if cuda and copied:
             torch.cuda.current_stream().synchronize()
         for t in ts:
             t.data = torch.empty(0, dtype=t.dtype, device=self.device)
         self.on_device = False
-        if cuda:
+        if cuda and copied:
+            # the first offload returns the segments to the driver; later ones of a frozen module leave the blocks
+            # in the current stream's pool, where the next phase's activations reuse them without a cudaMalloc
             torch.cuda.empty_cache()
 
     def prefetch(self):
@@ -73,21 +77,21 @@ class ModuleSwap:
             return
         if self._stream is None:
             self._stream = torch.cuda.Stream(device=self.device)
+        # the destination blocks come from the consumer stream's pool (so that freeing them later hands them back to
+        # that pool); the side stream starts after everything the consumer stream has queued so far, which covers any
+        # earlier use of those blocks
+        dst = [torch.empty(self.host[id(t)].shape, dtype=t.dtype, device=self.device) for t in ts]
         self._stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(self._stream):
-            for t in ts:
-                d = torch.empty(self.host[id(t)].shape, dtype=t.dtype, device=self.device)
+            for t, d in zip(ts, dst):
                 d.copy_(self.host[id(t)], non_blocking=True)
-                d.record_stream(torch.cuda.current_stream())
                 t.data = d
             self._event = torch.cuda.Event()
             self._event.record(self._stream)
 
     def wait(self):
         if self._event is not None:
-            torch.cuda.current_stream().wait_event(self._event)
-            for t in self._tensors():   # the consumer stream owns the tensors from here on
-                t.data.record_stream(torch.cuda.current_stream())
+            torch.cuda.current_stream().wait_event(self._event)   # the side stream's last use precedes this point
             self._event = None
             self.on_device = True
 

@@ -89,3 +89,29 @@ def test_grpo_step_fp8_base_lora_mla_moe_on_gpu():
         assert gap < 0.35 and m["policy/grad_norm"] > 0, (gap, m["policy/grad_norm"])
     from gcore_b200.ops import _lib
     _lib.check_device_errors()
+
+
+@pytest.mark.gpu
+def test_frozen_module_swap_round_trips_under_allocator_reuse():
+    """A frozen module goes to pinned host memory and back several times while other tensors take and return the
+    freed blocks in between: the weights read back bit-identical, and nothing stays allocated while it is away."""
+    from gcore_b200.engine.swap import ModuleSwap
+    torch.manual_seed(0)
+    dev = torch.device("cuda:0")
+    mod = torch.nn.Sequential(*[torch.nn.Linear(512, 512) for _ in range(6)]).to(dev, torch.bfloat16)
+    want = [p.detach().clone() for p in mod.parameters()]
+    x = torch.randn(64, 512, device=dev, dtype=torch.bfloat16)
+    y0 = mod(x)
+    sw = ModuleSwap(mod, frozen=True)
+    for it in range(4):
+        sw.offload()
+        assert all(p.numel() == 0 for p in mod.parameters())
+        junk = [torch.full((512, 512), float(it), device=dev, dtype=torch.bfloat16) for _ in range(8)]
+        busy = torch.randn(2048, 2048, device=dev) @ torch.randn(2048, 2048, device=dev)
+        del junk
+        sw.prefetch()
+        busy = busy @ busy   # work queued on the consumer stream while the copies run
+        sw.wait()
+        for p, w in zip(mod.parameters(), want):
+            assert torch.equal(p, w)
+        assert torch.equal(mod(x), y0)

@@ -14,6 +14,7 @@ The forward returns the final hidden states; the vocabulary projection is fused 
 from __future__ import annotations
 
 import math
+import os
 import re
 from typing import Optional
 
@@ -225,7 +226,7 @@ class MLAttention(nn.Module):
         k_rope = fused.rope(k_rope.reshape(T, 1, dr).contiguous(), pos, cfg.rope_theta, dr, cfg.rope_interleaved)
         return q_nope, q_rope, c_kv, k_rope.reshape(T, dr)
 
-    def attend(self, q_nope, q_rope, c_kv, k_rope, cu_seqlens):
+    def attend(self, q_nope, q_rope, c_kv, k_rope, cu_seqlens, max_seqlen=None):
         """Causal attention over packed sequences with the latent expanded to per-head keys and values."""
         cfg = self.cfg
         T, h = q_nope.shape[0], self.h
@@ -234,13 +235,22 @@ class MLAttention(nn.Module):
         k_nope, v = kvu.split([dn, dv], dim=-1)
         qf = torch.cat([q_nope, q_rope], -1)
         kf = torch.cat([k_nope, k_rope.reshape(T, 1, dr).expand(T, h, dr)], -1)
+        from ..ops import _lib
+        if (dn + dr, dv) == (192, 128) and qf.is_cuda and qf.dtype == torch.bfloat16 and not _lib.force_eager() \
+                and os.environ.get("GCORE_MLA_FLASH", "1") != "0":
+            # 192-wide keys / 128-wide values: the tcgen05 flash kernel's wide-key instance over the whole packed batch
+            from ..ops.attention import flash_attn_varlen
+            if max_seqlen is None:
+                max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
+            o = flash_attn_varlen(qf, kf, v.contiguous(), cu_seqlens, cu_seqlens, max_seqlen, max_seqlen, causal=True,
+                                  scale=1.0 / math.sqrt(dn + dr))
+            return o.reshape(T, h * dv)
         # pad v to the qk head dim so one attention call serves both (extra columns are zero and sliced away)
         vpad = torch.nn.functional.pad(v, (0, dn + dr - dv))
         scale = 1.0 / math.sqrt(dn + dr)
-        from ..ops import _lib
         if qf.is_cuda and qf.dtype in (torch.bfloat16, torch.float16) and not _lib.force_eager():
-            # 192-wide keys / 128-wide values do not fit the tcgen05 flash kernel (128 x 128 head dims); until it does,
-            # the library's fused attention runs one sequence at a time (memory linear in the sequence length)
+            # other latent geometries: the library's fused attention, one sequence at a time (memory linear in the
+            # sequence length)
             bounds = cu_seqlens.tolist()
             outs = []
             for a, b in zip(bounds[:-1], bounds[1:]):
@@ -257,7 +267,7 @@ class MLAttention(nn.Module):
         return o[..., :dv].reshape(T, h * dv)
 
     def forward(self, x, pos, cu_seqlens, max_seqlen):
-        return self.linear_proj(self.attend(*self.project(x, pos), cu_seqlens))
+        return self.linear_proj(self.attend(*self.project(x, pos), cu_seqlens, max_seqlen))
 
 
 class MLP(nn.Module):

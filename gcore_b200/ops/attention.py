@@ -5,12 +5,14 @@
   (``csrc/attention_fwd.cu``); backward runs ``csrc/attention_bwd.cu`` when built, else a recompute through the
   PyTorch reference.  Same call contract as ``myfa_varlen_sw_sinks`` (gfused/myfa_varlen_sw_sinks.py:704).
 * ``paged_decode`` / ``kv_append_rope`` - rollout decoder (``csrc/paged_attention.cu``).
+* ``mla_paged_decode`` - rollout decoder of latent-attention models on the paged latent cache (``csrc/mla_decode.cu``).
 * ``attn_varlen_ref`` - the fp32 PyTorch oracle (mirrors tests/test_gfused/test_myfa_varlen_sw_sinks.py:33-98).
 """
 from __future__ import annotations
 
 import ctypes
 import math
+import os
 
 import torch
 
@@ -63,7 +65,8 @@ def attn_varlen_ref(q, k, v, cu_q, cu_k, causal=True, window=0, sinks=None, scal
 def _native_fwd(q, k, v, cu_q, cu_k, max_q, causal, window, sinks, scale):
     Tq, Hq, D = q.shape
     Tk, Hk, _ = k.shape
-    out = torch.empty(Tq, Hq, D, dtype=q.dtype, device=q.device)
+    Dv = v.shape[-1]
+    out = torch.empty(Tq, Hq, Dv, dtype=q.dtype, device=q.device)
     lse = torch.empty(Hq, Tq, dtype=torch.float32, device=q.device)
     B = cu_q.numel() - 1
     strides = (ctypes.c_longlong * 4)(q.stride(0), k.stride(0), v.stride(0), out.stride(0))
@@ -71,17 +74,18 @@ def _native_fwd(q, k, v, cu_q, cu_k, max_q, causal, window, sinks, scale):
     LAUNCHES["attention"] += 1
     rc = _lib.kernels().gk_attn_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(lse),
                                     _lib.ptr(cu_q), _lib.ptr(cu_k), _lib.ptr(sinks), B, Tq, Tk, Hq, Hk, D,
-                                    int(max_q), int(causal), float(scale), int(window or 0), 0,
+                                    int(max_q), int(causal), float(scale), int(window or 0), Dv,
                                     ctypes.cast(strides, ctypes.c_void_p), ctypes.cast(se, ctypes.c_void_p))
     _lib.check(rc, "gk_attn_fwd")
     return out, lse
 
 
 def _native_ok(q, k, v):
-    D = q.shape[-1]
-    return (q.dtype == torch.bfloat16 and _lib.use_native(q) and D in (64, 128) and v.shape[-1] == D
+    D, Dv = q.shape[-1], v.shape[-1]
+    # equal head dims, or the 192 / 128 geometry of latent attention expanded to per-head keys (forward kernel only)
+    return (q.dtype == torch.bfloat16 and _lib.use_native(q) and ((D in (64, 128) and Dv == D) or (D, Dv) == (192, 128))
             and q.stride(2) == 1 and q.stride(1) == D and k.stride(2) == 1 and k.stride(1) == D
-            and v.stride(2) == 1 and v.stride(1) == D and q.stride(0) % 8 == 0 and k.stride(0) % 8 == 0
+            and v.stride(2) == 1 and v.stride(1) == Dv and q.stride(0) % 8 == 0 and k.stride(0) % 8 == 0
             and v.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and k.data_ptr() % 16 == 0
             and v.data_ptr() % 16 == 0)
 
@@ -109,14 +113,66 @@ class _FlashAttnFn(torch.autograd.Function):
         return dq, dk, dv, dsinks, None, None, None, None, None, None, None
 
 
+class _FlashAttnWideKeyFn(torch.autograd.Function):
+    """Causal self-attention with 192-wide queries / keys and 128-wide values: the forward is the tcgen05 kernel; the
+    backward kernels are built for equal head dims, so the gradient comes from the library's flash backward on the
+    saved output and log-sum-exp (values, output and its gradient zero-padded to the key width, which that routine
+    wants equal), or, where that entry point is missing or refuses the operands, from a per-sequence recompute through
+    the library's fused attention under autograd."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, cu, max_s, scale):
+        out, lse = _native_fwd(q, k, v, cu, cu, max_s, True, 0, None, scale)
+        ctx.save_for_backward(q, k, v, out, lse, cu)
+        ctx.cfg = (max_s, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, out, lse, cu = ctx.saved_tensors
+        max_s, scale = ctx.cfg
+        D, Dv = q.shape[-1], v.shape[-1]
+        pad = (0, D - Dv)
+        try:
+            if os.environ.get("GCORE_WIDE_KEY_BWD", "flash") != "flash":
+                raise NotImplementedError
+            F = torch.nn.functional
+            dq, dk, dvp = torch.ops.aten._flash_attention_backward(
+                F.pad(do, pad).contiguous(), q.contiguous(), k.contiguous(), F.pad(v, pad).contiguous(),
+                F.pad(out, pad).contiguous(), lse.contiguous(), cu, cu, int(max_s), int(max_s), 0.0, True,
+                torch.zeros(2, dtype=torch.int64, device=q.device), torch.empty(0, device=q.device), scale=scale)
+            return dq, dk, dvp[..., :Dv].contiguous(), None, None, None
+        except (RuntimeError, NotImplementedError, AttributeError):
+            pass
+        bounds = cu.tolist()
+        dq, dk, dv = torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v)
+        for a, b in zip(bounds[:-1], bounds[1:]):
+            if b <= a:
+                continue
+            with torch.enable_grad():
+                qs, ks, vs = (t[a:b].detach().requires_grad_(True) for t in (q, k, v))
+                o = torch.nn.functional.scaled_dot_product_attention(
+                    qs.transpose(0, 1)[None], ks.transpose(0, 1)[None],
+                    torch.nn.functional.pad(vs, pad).transpose(0, 1)[None], is_causal=True, scale=scale)
+                o = o[0].transpose(0, 1)[..., :Dv]
+                gq, gk, gv = torch.autograd.grad(o, (qs, ks, vs), do[a:b])
+            dq[a:b], dk[a:b], dv[a:b] = gq, gk, gv
+        return dq, dk, dv, None, None, None
+
+
 def flash_attn_varlen(q, k, v, cu_q, cu_k, max_q, max_k, causal=True, window=0, sinks=None, scale=None):
-    """Packed varlen attention; returns ``[Tq, Hq, D]``."""
+    """Packed varlen attention; returns ``[Tq, Hq, Dv]``."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     if _native_ok(q, k, v):
         cu_q = cu_q if cu_q.dtype == torch.int32 else cu_q.to(torch.int32)
         cu_k = cu_k if cu_k.dtype == torch.int32 else cu_k.to(torch.int32)
-        if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad or
-                                        (sinks is not None and sinks.requires_grad)):
+        needs_grad = torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad or
+                                                  (sinks is not None and sinks.requires_grad))
+        if needs_grad and v.shape[-1] != q.shape[-1]:
+            assert causal and not window and sinks is None, \
+                "the wide-key geometry is differentiable for causal self-attention only"
+            return _FlashAttnWideKeyFn.apply(q, k, v, cu_q, max_q, scale)
+        if needs_grad:
             return _FlashAttnFn.apply(q, k, v, sinks, cu_q, cu_k, max_q, max_k, causal, window, scale)
         return _native_fwd(q, k, v, cu_q, cu_k, max_q, causal, window, sinks, scale)[0]
     if q.is_cuda and q.dtype in (torch.bfloat16, torch.float16) and sinks is None and causal \
@@ -240,6 +296,65 @@ def paged_decode(q, k_cache, v_cache, block_table, ctx_len, max_ctx, scale=None,
             l = torch.logsumexp(s, -1)
         p = torch.exp(s - l[:, None])
         out[b] = torch.einsum("hn,nhd->hd", p, vv).to(out.dtype)
+    return out
+
+
+def mla_decode_supported(q_lat, q_rope) -> bool:
+    """True when the latent decode kernel serves these operands (bf16 on a GPU, a built geometry)."""
+    if not (_lib.use_native(q_lat) and q_lat.dtype == torch.bfloat16 and q_rope.dtype == torch.bfloat16):
+        return False
+    lib = _lib.kernels()
+    return hasattr(lib, "gk_mla_paged_decode") and bool(lib.gk_mla_decode_supported(q_lat.shape[-1], q_rope.shape[-1]))
+
+
+def mla_paged_decode_ref(q_lat, q_rope, cache, block_table, ctx_len, scale):
+    """fp32 reference of ``mla_paged_decode``: per request, softmax over its cached rows of
+    ``q_lat . row[:C] + q_rope . row[C:]``, output = weighted sum of ``row[:C]``; a request without rows gives zeros."""
+    B, H, C = q_lat.shape
+    bs = cache.shape[1]
+    flat = cache.reshape(-1, cache.shape[-1]).float()
+    out = torch.zeros(B, H, C, dtype=torch.float32, device=q_lat.device)
+    for b in range(B):
+        n = int(ctx_len[b])
+        if n == 0:
+            continue
+        toks = torch.arange(n, device=q_lat.device)
+        rows = flat[block_table[b, toks // bs].long() * bs + toks % bs]          # [n, C + dr]
+        s = (q_lat[b].float() @ rows[:, :C].T + q_rope[b].float() @ rows[:, C:].T) * scale
+        out[b] = torch.softmax(s, -1) @ rows[:, :C]
+    return out
+
+
+def mla_paged_decode(q_lat, q_rope, cache, block_table, ctx_len, max_ctx, scale, out=None):
+    """One query token per request of absorbed multi-head latent attention.  q_lat: [B, H, C] (query times the key
+    up-projection), q_rope: [B, H, dr], cache: [blocks, block_size, C + dr] latent rows shared by all heads,
+    block_table: [B, max_blocks] int32, ctx_len: [B] int32.  Returns [B, H, C] in q_lat's dtype (``out`` may be any
+    strided view whose last dimension is contiguous: the kernel writes through batch / head strides)."""
+    B, H, C = q_lat.shape
+    dr = q_rope.shape[-1]
+    if out is None:
+        out = torch.empty(B, H, C, dtype=q_lat.dtype, device=q_lat.device)
+    if not mla_decode_supported(q_lat, q_rope):
+        if q_lat.is_cuda and not _lib.force_eager() and q_lat.dtype == torch.bfloat16:
+            raise RuntimeError(f"mla_paged_decode: no kernel for kv_lora_rank={C}, rope dim={dr}")
+        out.copy_(mla_paged_decode_ref(q_lat, q_rope, cache, block_table, ctx_len, scale).to(out.dtype))
+        return out
+    assert q_lat.stride(2) == 1 and q_rope.stride(2) == 1 and out.stride(2) == 1 and cache.is_contiguous()
+    assert cache.dtype == torch.bfloat16 and cache.shape[-1] == C + dr
+    lib = _lib.kernels()
+    need = ctypes.c_longlong()
+    lib.gk_mla_decode_scratch(B, H, C, int(max_ctx), ctypes.byref(need))
+    key = ("mla", q_lat.device.index)
+    sc = _PD_SCRATCH.get(key)
+    if sc is None or sc.numel() < need.value:
+        sc = torch.empty(max(need.value, 1), dtype=torch.float32, device=q_lat.device)
+        _PD_SCRATCH[key] = sc
+    LAUNCHES["attention"] += 1
+    _lib.check(lib.gk_mla_paged_decode(_lib.ptr(q_lat), q_lat.stride(0), q_lat.stride(1), _lib.ptr(q_rope),
+                                       q_rope.stride(0), q_rope.stride(1), _lib.ptr(cache), _lib.ptr(block_table),
+                                       _lib.ptr(ctx_len), _lib.ptr(out), out.stride(0), out.stride(1), _lib.ptr(sc),
+                                       B, H, C, dr, cache.shape[1], block_table.shape[1], int(max_ctx), float(scale),
+                                       _lib.stream_ptr()), "mla_paged_decode")
     return out
 
 

@@ -38,13 +38,17 @@ struct FaParams {
   int* err;
 };
 
-template <int D>
+// DQK = head dim of queries and keys, DV = head dim of values and of the output (equal except for multi-head latent
+// attention expanded to per-head keys: 128 + 64 rotary dims against 128-wide values).
+template <int DQK, int DV>
 __global__ void __launch_bounds__(FA_THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, FaParams p) {
-  constexpr int NCH = D / 64;              // 64-element (128-byte) chunks along the head dim
-  constexpr int TILE_BYTES = 128 * D * 2;      // the Q tile
-  constexpr int KV_BYTES = FA_BN * D * 2;      // one K or V tile
+  constexpr int NCH = DQK / 64;            // 64-element (128-byte) chunks along the query / key head dim
+  constexpr int NCHV = DV / 64;
+  constexpr int TILE_BYTES = 128 * DQK * 2;    // the Q tile
+  constexpr int K_BYTES = FA_BN * DQK * 2;     // one K tile
+  constexpr int V_BYTES = FA_BN * DV * 2;      // one V tile
   constexpr int KV_CHUNK = FA_BN * 128;        // one 64-dim (128-byte) chunk of a K / V tile
   constexpr int P_BYTES = 128 * FA_BN * 2;
   // no alignment slack: two CTAs must fit in one SM.  The dynamic segment starts on a 1024-byte boundary when the
@@ -53,8 +57,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint8_t* smem = smem_raw;
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + TILE_BYTES;    // 2 stages
-  uint8_t* sV = sK + 2 * KV_BYTES;  // 2 stages
-  uint8_t* sP = sV + 2 * KV_BYTES;
+  uint8_t* sV = sK + 2 * K_BYTES;   // 2 stages
+  uint8_t* sP = sV + 2 * V_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
   uint64_t* q_full = bars;         // 1
   uint64_t* k_full = bars + 1;     // 2
@@ -135,12 +139,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!ok) break;
         if (lane == 0) {
           const int krow = k_beg + (j_beg + it) * FA_BN;
-          mbar_expect_tx(&k_full[s], KV_BYTES);
+          mbar_expect_tx(&k_full[s], K_BYTES);
 #pragma unroll
-          for (int c = 0; c < NCH; ++c) tma_load_3d(sK + s * KV_BYTES + c * KV_CHUNK, &tmK, &k_full[s], c * 64, hk, krow);
-          mbar_expect_tx(&v_full[s], KV_BYTES);
+          for (int c = 0; c < NCH; ++c) tma_load_3d(sK + s * K_BYTES + c * KV_CHUNK, &tmK, &k_full[s], c * 64, hk, krow);
+          mbar_expect_tx(&v_full[s], V_BYTES);
 #pragma unroll
-          for (int c = 0; c < NCH; ++c) tma_load_3d(sV + s * KV_BYTES + c * KV_CHUNK, &tmV, &v_full[s], c * 64, hk, krow);
+          for (int c = 0; c < NCHV; ++c) tma_load_3d(sV + s * V_BYTES + c * KV_CHUNK, &tmV, &v_full[s], c * 64, hk, krow);
         }
         __syncwarp();
       }
@@ -148,7 +152,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   } else if (warp == 5) {
     // ------------------------------------------------------------------ MMA issuer
     constexpr uint32_t idesc_s = make_idesc(FA_BM, FA_BN, 1, 1, 0, 0);
-    constexpr uint32_t idesc_pv = make_idesc(FA_BM, D, 1, 1, 0, 1);
+    constexpr uint32_t idesc_pv = make_idesc(FA_BM, DV, 1, 1, 0, 1);
     bool ok = ntiles > 0;
     if (ok) ok = mbar_wait(q_full, 0, p.err, ERR_WAIT_FULL);
     auto issue_s = [&](int it) -> bool {
@@ -157,9 +161,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (it >= 2 && !mbar_wait(&s_empty[s], ((it - 2) >> 1) & 1, p.err, ERR_WAIT_TMEM_EMPTY)) return false;
       tc_fence_after();
       if (lane == 0) {
-        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + s * KV_BYTES);
+        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + s * K_BYTES);
 #pragma unroll
-        for (int k4 = 0; k4 < D / 16; ++k4) {
+        for (int k4 = 0; k4 < DQK / 16; ++k4) {
           const uint32_t oq = (k4 >> 2) * 16384 + (k4 & 3) * 32;     // Q chunks are 128 rows x 128 B apart
           const uint32_t okk = (k4 >> 2) * KV_CHUNK + (k4 & 3) * 32;  // K chunks FA_BN rows x 128 B
           umma_f16(tmem_base + s * FA_BN, make_smem_desc_sw128(qa + oq, 16, 1024),
@@ -183,7 +187,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (!ok) break;
       tc_fence_after();
       if (lane == 0) {
-        const uint32_t pa = smem_u32(sP), va = smem_u32(sV + s * KV_BYTES);
+        const uint32_t pa = smem_u32(sP), va = smem_u32(sV + s * V_BYTES);
 #pragma unroll
         for (int k4 = 0; k4 < FA_BN / 16; ++k4) {
           const uint64_t adesc = make_smem_desc_sw128(pa + (k4 >> 2) * 16384 + (k4 & 3) * 32, 16, 1024);
@@ -265,7 +269,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_fence_after();
         if (__any_sync(0xffffffff, changed)) {
 #pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
+          for (int c = 0; c < DV / 32; ++c) {
             uint32_t r[32];
             tmem_ld32(tmem_o + lane_addr + c * 32, r);
             tmem_ld_wait();
@@ -304,9 +308,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (p.sinks) l += exp2f(p.sinks[h] * 1.4426950408889634f - m_use);
       const float inv = l > 0.f ? 1.f / l : 0.f;
       const bool valid = qi < lq;
-      __nv_bfloat16* orow = p.out + static_cast<long long>(q_beg + qi) * p.o_stride_t + static_cast<long long>(h) * D;
+      __nv_bfloat16* orow = p.out + static_cast<long long>(q_beg + qi) * p.o_stride_t + static_cast<long long>(h) * DV;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < DV / 32; ++c) {
         uint32_t r[32];
         if (ntiles > 0) {
           tmem_ld32(tmem_o + lane_addr + c * 32, r);
@@ -342,20 +346,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
-template <int D>
+template <int DQK, int DV>
 int launch_fa(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& p, dim3 grid,
               cudaStream_t st) {
-  constexpr int SMEM = 128 * D * 2 + 4 * FA_BN * D * 2 + 128 * FA_BN * 2 + 256;
+  // 112 KB at 128 / 128 (two CTAs per SM), 144 KB at 192 / 128 (one)
+  constexpr int SMEM = 128 * DQK * 2 + 2 * FA_BN * DQK * 2 + 2 * FA_BN * DV * 2 + 128 * FA_BN * 2 + 256;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<DQK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return static_cast<int>(e);
     // the whole L1 / shared array as shared memory, so that two CTAs fit
-    cudaFuncSetAttribute(attn_fwd_kernel<D>, cudaFuncAttributePreferredSharedMemoryCarveout,
+    cudaFuncSetAttribute(attn_fwd_kernel<DQK, DV>, cudaFuncAttributePreferredSharedMemoryCarveout,
                          cudaSharedmemCarveoutMaxShared);
     configured = true;
   }
-  attn_fwd_kernel<D><<<grid, FA_THREADS, SMEM, st>>>(tq, tk, tv, p);
+  attn_fwd_kernel<DQK, DV><<<grid, FA_THREADS, SMEM, st>>>(tq, tk, tv, p);
   return launch_status();
 }
 
@@ -363,22 +368,23 @@ int launch_fa(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& t
 
 using namespace gk;
 
-// q: [Tq, Hq, D], k/v: [Tk, Hk, D] (token strides in elements, heads contiguous), out: [Tq, Hq, D].
+// q: [Tq, Hq, D], k: [Tk, Hk, D], v: [Tk, Hk, Dv] (token strides in elements, heads contiguous), out: [Tq, Hq, Dv].
+// Dv = 0 means Dv = D; built geometries: 64 / 64, 128 / 128 and 192 / 128.
 // cu_q / cu_k: int32 [B + 1] on device.  max_q bounds every sequence's query length (fixes the grid).
 GK_EXPORT int gk_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* cu_q,
                           const int* cu_k, const float* sinks, int B, int Tq, int Tk, int Hq, int Hk, int D,
-                          int max_q, int causal, float scale, int window, int strides_packed, void* strides,
+                          int max_q, int causal, float scale, int window, int Dv, void* strides,
                           void* stream_err) {
   // strides: long long[4] = {q_stride_t, k_stride_t, v_stride_t, o_stride_t}; stream_err: void*[2] = {stream, err}
-  (void)strides_packed;
   const long long* sd = reinterpret_cast<const long long*>(strides);
   void** se = reinterpret_cast<void**>(stream_err);
-  if (D != 64 && D != 128) return -1;
+  if (Dv == 0) Dv = D;
+  if (!((D == 64 && Dv == 64) || (D == 128 && Dv == 128) || (D == 192 && Dv == 128))) return -1;
   if (Hq % Hk) return -2;
   CUtensorMap tq, tk, tv;
   if (make_tmap_3d(&tq, q, 2, Tq, Hq, D, sd[0], D, 128, 1, 64, true)) return -3;
   if (make_tmap_3d(&tk, k, 2, Tk, Hk, D, sd[1], D, FA_BN, 1, 64, true)) return -4;
-  if (make_tmap_3d(&tv, v, 2, Tk, Hk, D, sd[2], D, FA_BN, 1, 64, true)) return -5;
+  if (make_tmap_3d(&tv, v, 2, Tk, Hk, Dv, sd[2], Dv, FA_BN, 1, 64, true)) return -5;
   FaParams p;
   p.cu_q = cu_q; p.cu_k = cu_k; p.sinks = sinks;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
@@ -388,6 +394,7 @@ GK_EXPORT int gk_attn_fwd(const void* q, const void* k, const void* v, void* out
   p.err = reinterpret_cast<int*>(se[1]);
   dim3 grid((max_q + FA_BM - 1) / FA_BM, Hq, B);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(se[0]);
-  if (D == 128) return launch_fa<128>(tq, tk, tv, p, grid, st);
-  return launch_fa<64>(tq, tk, tv, p, grid, st);
+  if (D == 192) return launch_fa<192, 128>(tq, tk, tv, p, grid, st);
+  if (D == 128) return launch_fa<128, 128>(tq, tk, tv, p, grid, st);
+  return launch_fa<64, 64>(tq, tk, tv, p, grid, st);
 }

@@ -32,7 +32,7 @@ import torch.distributed as dist
 from ..core import parallel_state as ps
 from ..models.config import ModelConfig
 from ..ops import _lib, fused
-from ..ops.attention import flash_attn_varlen, kv_append_rope, paged_decode
+from ..ops.attention import flash_attn_varlen, kv_append_rope, mla_paged_decode, paged_decode
 from ..ops.gemm import linear_forward
 from ..ops.vocab import apply_top_k_top_p, sample, sample_filtered
 from ..utils import io_counters
@@ -503,7 +503,7 @@ class InferEngine:
                 self.k_cache[li].view(-1, self.mla_dim).index_copy_(
                     0, torch.where(slots >= 0, slots, torch.full_like(slots, sink)).long(),
                     torch.cat([self._mla_cached_latent(lw.mla, c_kv), k_rope], -1))
-                a = self._allreduce(lw.mla.linear_proj(lw.mla.attend(q_nope, q_rope, c_kv, k_rope, cu)))
+                a = self._allreduce(lw.mla.linear_proj(lw.mla.attend(q_nope, q_rope, c_kv, k_rope, cu, max_len)))
                 h, res = fused.rmsnorm(a, lw.ln2, cfg.rms_norm_eps, res)
                 x = self._mlp(lw, h)
                 continue
@@ -546,17 +546,20 @@ class InferEngine:
         x = self._embed(st["tokens"])
         res = None
         if self.mla_dim:
-            # latent rows of every request, gathered once per step for all layers' index arithmetic
-            p_all = torch.arange(self.max_model_len, device=pos.device)
-            lat_idx = (st["block_table"].long()[:, p_all // self.bs] * self.bs + p_all % self.bs)  # [B, Lmax]
-            lat_mask = p_all[None, :] < ctx[:, None]
             sink = (self.k_cache[0].shape[0] - 1) * self.bs
             lat_slots = torch.where(slots >= 0, slots, torch.full_like(slots, sink)).long()
+            lat_idx = lat_mask = None
+            if not self._mla_native():
+                # eager form: latent rows of every request, gathered once per step for all layers' index arithmetic
+                p_all = torch.arange(self.max_model_len, device=pos.device)
+                lat_idx = (st["block_table"].long()[:, p_all // self.bs] * self.bs + p_all % self.bs)  # [B, Lmax]
+                lat_mask = p_all[None, :] < ctx[:, None]
         pending = False   # x still holds this rank's partial sums of the previous block's row-parallel projection
         for li, lw in enumerate(self.w.layers):
             h, res = self._reduce_norm(x, lw.ln1, res, pending)
             if lw.mla is not None:
-                o = self._mla_decode(lw.mla, h, pos, self.k_cache[li], lat_slots, lat_idx, lat_mask)
+                o = self._mla_decode(lw.mla, h, pos, self.k_cache[li], lat_slots, lat_idx, lat_mask,
+                                     paged=(st["block_table"], ctx))
                 h, res = self._reduce_norm(lw.mla.linear_proj(o), lw.ln2, res, self.tp > 1)
                 x, pending = self._mlp(lw, h, reduce=False)
                 continue
@@ -605,7 +608,18 @@ class InferEngine:
             w = quant.dequant_128x128(q, sc)[:w.shape[0], :w.shape[1]].to(up.weight.dtype)
         return w
 
-    def _mla_decode(self, mla, h, pos, cache, slots, lat_idx, lat_mask):
+    def _mla_native(self) -> bool:
+        """Whether the decode step runs the latent-attention kernel (bf16 cache on a GPU, a built geometry)."""
+        cfg = self.cfg
+        if self.device.type != "cuda" or _lib.force_eager() or os.environ.get("GCORE_MLA_DECODE", "1") == "0":
+            return False
+        if self.k_cache is None or self.k_cache[0].dtype != torch.bfloat16:
+            return False
+        lib = _lib.kernels()
+        return hasattr(lib, "gk_mla_decode_supported") and \
+            bool(lib.gk_mla_decode_supported(cfg.kv_lora_rank, cfg.qk_rope_head_dim))
+
+    def _mla_decode(self, mla, h, pos, cache, slots, lat_idx, lat_mask, paged=None):
         """One token per request of multi-head latent attention on the latent cache, in the absorbed form: the key
         up-projection is folded into the query and the value up-projection is applied after the weighted sum, so a
         step reads ``kv_lora + rope`` values per cached token instead of per-head keys and values
@@ -616,11 +630,21 @@ class InferEngine:
         q_nope, q_rope, c_kv, k_rope = mla.project(h, pos)
         flat = cache.view(-1, self.mla_dim)
         flat.index_copy_(0, slots, torch.cat([self._mla_cached_latent(mla, c_kv), k_rope], -1))
-        lat = flat[lat_idx]                                            # [B, Lmax, C + dr]
         w_up = self._mla_up_weight(mla).view(mla.h, dn + dv, C)
         up_lora = getattr(mla.linear_kv_up_proj, "lora", None)
         if up_lora is not None:  # adapters on the up-projection: fold their delta into the absorbed matrices
             w_up = w_up + up_lora.delta_weight().view(mla.h, dn + dv, C).to(w_up.dtype)
+        if lat_idx is None:
+            # latent decode kernel straight on the paged cache: the two absorbed projections are head-batched GEMMs
+            # in head-major layout, which the kernel reads and writes through strides
+            block_table, ctx = paged
+            q_lat = torch.bmm(q_nope.transpose(0, 1), w_up[:, :dn])                   # [h, B, C]
+            o_lat = torch.empty_like(q_lat)
+            mla_paged_decode(q_lat.transpose(0, 1), q_rope, cache.view(-1, self.bs, self.mla_dim), block_table, ctx,
+                             self.max_model_len, 1.0 / math.sqrt(dn + dr), out=o_lat.transpose(0, 1))
+            o = torch.bmm(o_lat, w_up[:, dn:].transpose(1, 2))                        # [h, B, dv]
+            return o.transpose(0, 1).reshape(B, mla.h * dv)
+        lat = flat[lat_idx]                                            # [B, Lmax, C + dr]
         q_abs = torch.einsum("bhd,hdc->bhc", q_nope.float(), w_up[:, :dn].float())
         s = torch.einsum("bhc,blc->bhl", q_abs, lat[..., :C].float())
         s = s + torch.einsum("bhr,blr->bhl", q_rope.float(), lat[..., C:].float())

@@ -18,6 +18,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import sys
 import time
@@ -273,6 +274,71 @@ def cmd_paged(argv=None):
     _lib.check_device_errors()
     print(f"paged decode T={T} H={hq}/{hk} ctx={a.ctx} max={a.max_ctx}: {us:.2f} us per call, {mb:.0f} MB of K/V "
           f"-> {mb / us:.2f} TB/s")
+
+
+def cmd_mla_decode(argv=None):
+    """Times the latent-attention decode kernel on one shape against the eager absorbed form (gather of every
+    request's rows + fp32 einsums), reports the share of the measured copy bandwidth the cache rows are read at and
+    the tensor throughput of the two contractions."""
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=64)
+    ap.add_argument("--heads", type=int, default=128)
+    ap.add_argument("--kv-lora", type=int, default=512)
+    ap.add_argument("--rope", type=int, default=64)
+    ap.add_argument("--ctx", type=int, default=2048)
+    ap.add_argument("--block-size", type=int, default=16)
+    ap.add_argument("--iters", type=int, default=8)
+    ap.add_argument("--eager", type=int, default=1)
+    a = ap.parse_args(argv)
+    from gcore_b200.ops import _lib
+    from gcore_b200.ops.attention import mla_paged_decode
+    dev = torch.device("cuda")
+    B, H, C, dr, bs = a.tokens, a.heads, a.kv_lora, a.rope, a.block_size
+    per = (a.ctx + bs - 1) // bs
+    copies = 3
+    caches = [torch.randn(B * per, bs, C + dr, device=dev).bfloat16() * 0.5 for _ in range(copies)]
+    bt = torch.arange(B * per, device=dev, dtype=torch.int32).view(B, per)
+    ctx = torch.full((B,), a.ctx, dtype=torch.int32, device=dev)
+    q_lat = (torch.randn(B, H, C, device=dev) * 0.3).bfloat16()
+    q_rope = (torch.randn(B, H, dr, device=dev) * 0.3).bfloat16()
+    scale = 1.0 / math.sqrt(192)
+    out = torch.empty(B, H, C, device=dev, dtype=torch.bfloat16)
+
+    def timed(fn):
+        ts = []
+        for i in range(a.iters):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn(i)
+            e.record()
+            torch.cuda.synchronize()
+            ts.append(s.elapsed_time(e) * 1e3)
+        return min(ts[1:]) if len(ts) > 1 else ts[0]
+
+    us = timed(lambda i: mla_paged_decode(q_lat, q_rope, caches[i % copies], bt, ctx, a.ctx, scale, out=out))
+    _lib.check_device_errors()
+    mb = B * a.ctx * (C + dr) * 2 / 1e6
+    gf = 2.0 * B * H * a.ctx * (2 * C + dr) / 1e9
+    _, hbm, which = _peaks()
+    line = (f"mla decode B={B} H={H} C={C}+{dr} ctx={a.ctx}: {us:.1f} us, {mb:.0f} MB of latent rows -> "
+            f"{mb / us:.2f} TB/s ({mb / us * 1e3 / hbm:.2f} of {which} copy), {gf / us * 1e3:.0f} TFLOP/s")
+    if a.eager:
+        p_all = torch.arange(a.ctx, device=dev)
+        idx = bt.long()[:, p_all // bs] * bs + p_all % bs
+
+        def eager(i):
+            lat = caches[i % copies].view(-1, C + dr)[idx]
+            s = torch.einsum("bhc,blc->bhl", q_lat.float(), lat[..., :C].float())
+            s = (s + torch.einsum("bhr,blr->bhl", q_rope.float(), lat[..., C:].float())) * scale
+            return torch.einsum("bhl,blc->bhc", torch.softmax(s, -1), lat[..., :C].float())
+        ue = timed(eager)
+        ref = eager(0)
+        got = mla_paged_decode(q_lat, q_rope, caches[0], bt, ctx, a.ctx, scale, out=out).float()
+        line += f"; eager absorbed form {ue:.1f} us ({ue / us:.1f}x), max |diff| {float((got - ref).abs().max()):.3e}"
+    print(line)
+
+
+COMMANDS_LATE = {"mla_decode": cmd_mla_decode}
 
 
 def graph_time(fn_list, reps=5):
@@ -703,6 +769,7 @@ def cmd_fused(argv=None):
 
 
 COMMANDS["fused"] = cmd_fused
+COMMANDS.update(COMMANDS_LATE)
 
 
 def main(argv=None):

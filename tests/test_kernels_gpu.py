@@ -373,6 +373,68 @@ def test_adam_and_sumsq():
     assert abs(s.item() - g.float().pow(2).sum().item()) / s.item() < 1e-3
 
 
+def test_flash_attention_wide_keys_forward_and_backward():
+    """192-wide queries / keys with 128-wide values (latent attention expanded to per-head keys): the forward kernel
+    and the gradient path behind it against the fp32 reference under autograd."""
+    from gcore_b200.ops.attention import attn_varlen_ref, flash_attn_varlen
+    torch.manual_seed(3)
+    lens = [5, 300, 129, 64, 1000]
+    T, H = sum(lens), 6
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device=DEV, dtype=torch.int32)
+    q = _rand(T, H, 192, scale=0.5).requires_grad_(True)
+    k = _rand(T, H, 192, scale=0.5).requires_grad_(True)
+    v = _rand(T, H, 128, scale=0.5).requires_grad_(True)
+    scale = 1.0 / math.sqrt(192)
+    with torch.no_grad():
+        out_ng = flash_attn_varlen(q, k, v, cu, cu, max(lens), max(lens), causal=True, scale=scale)
+    qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    ref = attn_varlen_ref(qr, kr, vr, cu, cu, True, 0, None, scale)
+    assert out_ng.shape == (T, H, 128)
+    _close(out_ng, ref.detach())
+    out = flash_attn_varlen(q, k, v, cu, cu, max(lens), max(lens), causal=True, scale=scale)
+    do = _rand(T, H, 128, scale=0.5)
+    out.backward(do)
+    ref.backward(do.float())
+    _close(q.grad, qr.grad, atol=1e-2)
+    _close(k.grad, kr.grad, atol=1e-2)
+    _close(v.grad, vr.grad, atol=1e-2)
+
+
+@pytest.mark.parametrize("H,C,dr,lens,head_major", [
+    (20, 128, 32, [0, 5, 700, 33], False),      # ragged head group (20 = 16 + 4), an empty request, partial tiles
+    (128, 512, 64, [2048, 130], True),          # the 512 + 64 geometry, several KV splits, strided operands
+    (16, 256, 64, [1, 257, 64, 31, 1000], False),
+])
+def test_mla_paged_decode(H, C, dr, lens, head_major):
+    """Latent attention decode on the paged cache vs fp32 PyTorch: as one KV split per request and with the splits
+    the launch plan picks."""
+    from gcore_b200.ops import _lib
+    from gcore_b200.ops.attention import mla_paged_decode, mla_paged_decode_ref
+    torch.manual_seed(5)
+    B, bs = len(lens), 16
+    max_blocks = (max(lens) + bs - 1) // bs + 1
+    nblocks = B * max_blocks + 3
+    cache = _rand(nblocks, bs, C + dr, scale=0.5)
+    table = torch.randperm(nblocks, device=DEV)[:B * max_blocks].view(B, max_blocks).to(torch.int32)
+    ctx = torch.tensor(lens, device=DEV, dtype=torch.int32)
+    if head_major:   # [H, B, *] storage seen as [B, H, *]: what the head-batched projections around the kernel produce
+        q_lat = _rand(H, B, C, scale=0.3).transpose(0, 1)
+        q_rope = _rand(H, B, dr, scale=0.3).transpose(0, 1)
+        out = torch.empty(H, B, C, device=DEV, dtype=torch.bfloat16).transpose(0, 1)
+    else:
+        q_lat, q_rope, out = _rand(B, H, C, scale=0.3), _rand(B, H, dr, scale=0.3), None
+    scale = 1.0 / math.sqrt(C // 4 + dr)
+    ref = mla_paged_decode_ref(q_lat, q_rope, cache, table, ctx, scale)
+    try:
+        for target in (1, 296):
+            _lib.kernels().gk_mla_set_target_ctas(target)
+            got = mla_paged_decode(q_lat, q_rope, cache, table, ctx, max(lens), scale, out=out)
+            _close(got, ref, atol=1e-2)
+            assert got[ctx == 0].abs().max().item() == 0 if (ctx == 0).any() else True
+    finally:
+        _lib.kernels().gk_mla_set_target_ctas(296)
+
+
 @pytest.mark.parametrize("window,use_sinks", [(0, False), (96, True)])
 def test_paged_decode_and_kv_append(window, use_sinks):
     from gcore_b200.ops.attention import kv_append_rope, paged_decode

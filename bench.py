@@ -392,6 +392,10 @@ def main():
         for k, v in m.items():
             if k.startswith("time_perf/"):
                 phase[k] = phase.get(k, 0.0) + v / args.steps
+        if rank == 0 and "time_perf/step" in m:
+            print(f"[step {i}] step {m['time_perf/step']:.2f}s rollout {m.get('time_perf/rollout', 0.0):.2f}s "
+                  f"logps {m.get('time_perf/compute_logps', 0.0):.2f}s train {m.get('time_perf/train_step', 0.0):.2f}s",
+                  file=sys.stderr, flush=True)
     ev1.record()
     barrier()
     wall = time.perf_counter() - t0
@@ -424,6 +428,7 @@ def main():
             "resync_ms": round(phase.get("time_perf/update_weights", 0.0) * 1e3, 3),
             "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1),
             "peak_reserved_gb": round(torch.cuda.max_memory_reserved() / 2**30, 1),
+            "alloc_retries": int(torch.cuda.memory_stats().get("num_alloc_retries", 0)),
             **({"reward_mean": round(m["rollout-rewards/mean"], 4)} if args.kind == "grpo"
                else {"lm_loss": round(float(m["lm_loss"]), 4)}),
         }

@@ -170,6 +170,25 @@ def hf_name_map(cfg) -> Dict[str, str]:
     return m
 
 
+_MTP_RE = re.compile(r"mtp\.layers\.(\d+)\.(.*)")
+_MTP_OWN = {"enorm.weight": "enorm.weight", "hnorm.weight": "hnorm.weight", "eh_proj.weight": "eh_proj.weight",
+            "final_layernorm.weight": "shared_head.norm.weight"}
+
+
+def _mtp_alias(name: str, cfg):
+    """Multi-token-prediction blocks are stored the DeepSeek-V3 way, as layers behind the last decoder layer:
+    block k's transformer layer under ``model.layers.{L + k}.*`` with the usual names, its own tensors as
+    ``enorm`` / ``hnorm`` / ``eh_proj`` / ``shared_head.norm`` of that layer.  Returns ``(name as a decoder-layer
+    parameter, None)`` or ``(None, HF key)`` for the block's own tensors; ``(name, None)`` for anything else."""
+    m = _MTP_RE.match(name)
+    if not m:
+        return name, None
+    li, rest = cfg.num_layers + int(m.group(1)), m.group(2)
+    if rest.startswith("transformer_layer."):
+        return f"decoder.layers.{li}." + rest[len("transformer_layer."):], None
+    return None, f"model.layers.{li}.{_MTP_OWN[rest]}"
+
+
 def _gather_tp(t: torch.Tensor, dim: int, group) -> torch.Tensor:
     n = dist.get_world_size(group) if group is not None else 1
     if n == 1:
@@ -184,6 +203,10 @@ def full_hf_tensors(name: str, t: torch.Tensor, cfg, tp_mode: str, tp_group, ep_
     """Gathers one local parameter over TP (and EP for experts) and yields its HF-named full tensors."""
     tp = dist.get_world_size(tp_group) if tp_group is not None else 1
     D = cfg.head_dim
+    name, own = _mtp_alias(name, cfg)
+    if own is not None:
+        yield own, t
+        return
     m = _LAYER_RE.match(name)
     li = int(m.group(1)) if m else None
     rest = m.group(2) if m else name
@@ -251,6 +274,10 @@ def load_hf_weights(model, hf_tensors: Dict[str, torch.Tensor], tp_rank: int = 0
     with torch.no_grad():
         for name, p in model.named_parameters():
             if getattr(p, "is_lora", False):
+                continue
+            name, own = _mtp_alias(name, cfg)
+            if own is not None:
+                p.copy_(hf_tensors[own])
                 continue
             m = _LAYER_RE.match(name)
             li = int(m.group(1)) if m else None

@@ -505,6 +505,9 @@ class TrainingConfig(MappingMixin):
     loss_func: str = "cross_entropy"
     cross_entropy_loss_fusion: bool = True
     per_token_loss: bool = True
+    # RL / distillation: also train the multi-token-prediction blocks (model_config.mtp_num_layers) with a next-token
+    # cross-entropy on the sampled responses; the trunk receives no gradient from it
+    online_mtp_sft: bool = False
     sort_batched: bool = False
     manual_gc: bool = False
     manual_gc_interval: int = 1

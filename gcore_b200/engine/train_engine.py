@@ -374,6 +374,36 @@ class TrainingEngine:
         return linear_logprob_entropy(hidden, w, targets, self.temperature, tp_group, model.vocab_start(), mg,
                                       want_entropy)
 
+    def _mtp_loss(self, model: GPTModel, mb: PackedBatch, hidden, per_token: bool, denom, detach_trunk: bool):
+        """Scaled cross-entropy of the multi-token-prediction blocks on one micro-batch: depth k reads the trunk's
+        hidden state at t and the embedding of token t + k and is scored on token t + k + 1 under the loss mask of
+        that position; positions whose k-step look-ahead leaves their sequence are dropped.  Weighted like the main
+        loss (same normaliser), averaged over depths and scaled by ``mtp_loss_scaling_factor``.  Returns
+        ``(loss, [sum of masked nll, mask count])`` (Megatron's multi-token-prediction loss; label / mask shifting as in
+        gpatch_v4/extended_model/mtp_mixin.py:44-80)."""
+        assert mb.cp_ctx is None, "multi-token prediction with context-parallel shards is not supported"
+        cfg = self.model_cfg
+        seq_ids = mb.seq_ids.long()
+        outs, aux = model.mtp_hidden(hidden.detach() if detach_trunk else hidden, mb.tokens, mb.position_ids,
+                                     mb.cu_seqlens, mb.max_seqlen, seq_ids)
+        T = mb.tokens.shape[0]
+        ar = torch.arange(T, device=mb.tokens.device)
+        total, stat = None, torch.zeros(2, device=hidden.device)
+        for k, (h, valid) in enumerate(outs, start=1):
+            src = (ar + k).clamp_max(T - 1)
+            mask = mb.loss_mask[src] * valid.to(mb.loss_mask.dtype)
+            targets = mb.targets[src]
+            lp, _ = self._logprob_entropy(model, h, targets, False, mask)
+            w = PL.aggregation_weights(mask, mb.seq_ids, mb.num_seqs + 1, per_token, denom)
+            term = -(lp * w).sum()
+            total = term if total is None else total + term
+            with torch.no_grad():
+                stat += torch.stack([-(lp.detach() * mask).sum(), mask.sum()])
+        loss = total * (cfg.mtp_loss_scaling_factor / len(outs))
+        if aux is not None:
+            loss = loss + aux * self._aux_scale(1)
+        return loss, stat
+
     def _tp_pad(self):
         return ps.get_tensor_model_parallel_world_size() if (self.model is not None and self.model.sequence_parallel) \
             else 1
@@ -615,6 +645,10 @@ class TrainingEngine:
                     loss = loss + aux * aux_scale
                 with torch.no_grad():
                     acc["lm_loss"] += torch.stack([-(lp.detach() * mb.loss_mask).sum(), mb.loss_mask.sum()])
+                if hasattr(self.model, "mtp"):
+                    ml, st = self._mtp_loss(self.model, mb, hidden, per_token, denom, detach_trunk=False)
+                    loss = loss + ml
+                    acc.setdefault("mtp_loss", torch.zeros(2, device=self.device)).add_(st)
                 return loss
 
             self._for_each_microbatch(self.model, samples, batches, (), step)
@@ -659,6 +693,7 @@ class TrainingEngine:
                 and cfg.loss_func_py_path is None and not cfg.entropy_regularization_type)
         loss_fn = None if fast else self._resolve_loss()
         acc: Dict[str, torch.Tensor] = {}
+        online_mtp = bool(getattr(self.train_cfg, "online_mtp_sft", False)) and hasattr(self.model, "mtp")
 
         def add(k, v):
             acc[k] = acc[k] + v if k in acc else v.clone()
@@ -713,6 +748,10 @@ class TrainingEngine:
                         add("policy/entropy", torch.stack([(ent.detach() * mb.loss_mask).sum(), mb.loss_mask.sum()]))
                 if aux is not None:
                     loss = loss + aux * aux_scale
+                if online_mtp:
+                    ml, st = self._mtp_loss(self.model, mb, hidden, per_token, denom, detach_trunk=True)
+                    loss = loss + ml
+                    add("ppo-metrics/mtp_loss", st)
                 return loss
 
             if self._dcp is not None:

@@ -61,6 +61,10 @@ class ModelConfig:
     mrope_interleaved: bool = True
     dtype: str = "bfloat16"
     init_std: float = 0.02
+    # multi-token prediction: extra depth-k blocks behind the trunk that predict token t + k + 1 from the hidden state
+    # at t and the embedding of token t + k; trained with a scaled cross-entropy beside the main objective
+    mtp_num_layers: int = 0
+    mtp_loss_scaling_factor: float = 0.1
     fp8_base_weights: bool = False  # frozen e4m3 base with 128x128 block scales
 
     def __post_init__(self):

@@ -349,6 +349,22 @@ def _layer_forward_fused(self, x, residual, pos, cu_seqlens, max_seqlen):
 TransformerLayer._forward_fused = _layer_forward_fused
 
 
+class MTPBlock(nn.Module):
+    """One depth of multi-token prediction: ``h' = layer(W [norm_e(emb(token t+k)) ; norm_h(h_t)])`` followed by its
+    own final norm; the vocabulary projection is the trunk's (the multi-token-prediction layers the reference trains
+    through Megatron and its online-MTP data preparation, gpatch_v4/extended_model/mtp_mixin.py:11-80)."""
+
+    def __init__(self, cfg: ModelConfig, depth: int, tp_size: int, ep_size: int, device=None):
+        super().__init__()
+        self.enorm = RMSNormWeight(cfg.hidden_size, cfg, device)
+        self.hnorm = RMSNormWeight(cfg.hidden_size, cfg, device)
+        # replicated, applied to the sequence-parallel token shard: its gradient is summed over the TP group
+        self.eh_proj = ParallelLinear(2 * cfg.hidden_size, cfg.hidden_size, "none", cfg, device=device)
+        self.eh_proj.weight.sequence_parallel = True
+        self.transformer_layer = TransformerLayer(cfg, cfg.num_layers + depth, tp_size, ep_size, device)
+        self.final_layernorm = RMSNormWeight(cfg.hidden_size, cfg, device)
+
+
 class GPTModel(nn.Module):
     """One pipeline stage worth of layers (all of them when PP = 1)."""
 
@@ -398,6 +414,12 @@ class GPTModel(nn.Module):
                 self.output_layer.weight = nn.Parameter(
                     torch.empty(self.vocab_local, cfg.hidden_size, dtype=dt, device=device))
                 self.output_layer.weight.tp_mode = "column"
+        if cfg.mtp_num_layers > 0 and not value_head:
+            assert pre_process and post_process and len(ranges) == 1, \
+                "multi-token prediction needs the embedding and the head on one stage (pipeline size 1)"
+            self.mtp = nn.Module()
+            self.mtp.layers = nn.ModuleList([MTPBlock(cfg, k, tp_size, ep_size, device)
+                                             for k in range(cfg.mtp_num_layers)])
         self.reset_parameters()
 
     # ------------------------------------------------------------------ init
@@ -446,7 +468,8 @@ class GPTModel(nn.Module):
                         full = torch.randn(p.shape[0], p.shape[1] * self.tp_size, generator=g) * mod_std
                         p.copy_(full.chunk(self.tp_size, 1)[tp_rank])
                 elif p.is_cuda and p.numel() > (1 << 22):
-                    g = torch.Generator(device=p.device).manual_seed((key + 7919 * tp_rank) & 0x7FFFFFFF)
+                    g = torch.Generator(device=p.device).manual_seed(
+                        (key + (7919 * tp_rank if mode in ("column", "row") else 0)) & 0x7FFFFFFF)
                     p.copy_(torch.randn(p.shape, generator=g, device=p.device, dtype=torch.float32) * mod_std)
                 else:
                     g = torch.Generator(device="cpu").manual_seed(
@@ -529,6 +552,39 @@ class GPTModel(nn.Module):
         if self.value_head:
             return self.output_layer(h).squeeze(-1).float(), aux_total
         return h, aux_total
+
+    def mtp_hidden(self, hidden, input_ids, position_ids, cu_seqlens, max_seqlen, seq_ids):
+        """Final-normed hidden states of every prediction depth, ``[(h_k, valid_k)]``: ``h_k[t]`` predicts token
+        ``t + k + 1`` (k = 1 .. depth) and ``valid_k[t]`` says whether tokens ``t + 1 .. t + k`` belong to the same
+        packed sequence as ``t``.  ``hidden`` is the trunk's final-normed output (gathered over sequence parallel),
+        ``seq_ids`` [T] the sequence index of every position.  Returns ``([...], aux_loss)``."""
+        tp_group = ps.get_tensor_model_parallel_group() if self.tp_size > 1 else None
+        sp, cfg = self.sequence_parallel, self.cfg
+        T = input_ids.shape[0]
+        pos32 = position_ids.to(torch.int32) if position_ids.dtype != torch.int32 else position_ids
+        outs, aux_total, h_prev = [], None, hidden
+        ar = torch.arange(T, device=input_ids.device)
+        for k, blk in enumerate(self.mtp.layers, start=1):
+            src = (ar + k).clamp_max(T - 1)
+            valid = (ar + k < T) & (seq_ids[src] == seq_ids)
+            e = tp_ops.vocab_parallel_embedding(input_ids[src], self.embedding.word_embeddings.weight,
+                                                self.vocab_start(), tp_group)
+            hp = h_prev
+            if sp:
+                e = tp_ops.scatter_to_sequence_parallel(e, tp_group)
+                hp = tp_ops.scatter_to_sequence_parallel(hp, tp_group)
+            e = fused.rmsnorm(e, blk.enorm.weight, cfg.rms_norm_eps)[0]
+            hp = fused.rmsnorm(hp, blk.hnorm.weight, cfg.rms_norm_eps)[0]
+            x = blk.eh_proj(torch.cat([e, hp], dim=-1))
+            x, residual, aux = blk.transformer_layer(x, None, pos32, cu_seqlens, max_seqlen, tp_group, sp)
+            if aux is not None:
+                aux_total = aux if aux_total is None else aux_total + aux
+            h, _ = fused.rmsnorm(x, blk.final_layernorm.weight, cfg.rms_norm_eps, residual)
+            if sp:
+                h = tp_ops.gather_from_sequence_parallel(h, tp_group)
+            outs.append((h, valid))
+            h_prev = h
+        return outs, aux_total
 
     def logits(self, hidden):
         """Materialised (local-vocab) logits; only for small debugging / generation on CPU."""

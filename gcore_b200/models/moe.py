@@ -170,8 +170,8 @@ class _GroupedLinearFn(torch.autograd.Function):
 
 class _GroupedFp8LinearFn(torch.autograd.Function):
     """Grouped expert projection in block-scaled e4m3 (activations 1x128 per token, weights 128x128, cached until the
-    parameter changes); like the dense fp8 linear, the backward runs in bf16 against the dequantised weight, and the
-    weight gradient is skipped for a frozen base (the reference's grouped fp8 linear:
+    parameter changes); like the dense fp8 linear, the data gradient runs on the same grouped GEMM against the
+    transposed e4m3 cache, the weight gradient in bf16, skipped for a frozen base (the reference's grouped fp8 linear:
     gpatch_v4/models/deepseek_v4/fp8.py:181-394)."""
 
     @staticmethod
@@ -197,8 +197,12 @@ class _GroupedFp8LinearFn(torch.autograd.Function):
         dy = dy.contiguous()
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            w_dq = quant.dequant_128x128(ctx.cache["q"], ctx.cache["s"])[:G * N, :K].to(dy.dtype).view(G, N, K)
-            dx = grouped_gemm(dy, w_dq.contiguous(), offsets, b_mn=True)
+            from ..ops.lowp_linear import fp8_dgrad_enabled
+            if fp8_dgrad_enabled() and dy.shape[0] % 128 == 0:
+                dx = quant.fp8_dgrad(dy, ctx.cache, dy.dtype, offsets=offsets, groups=G)
+            else:
+                w_dq = quant.dequant_128x128(ctx.cache["q"], ctx.cache["s"])[:G * N, :K].to(dy.dtype).view(G, N, K)
+                dx = grouped_gemm(dy, w_dq.contiguous(), offsets, b_mn=True)
         if ctx.needs_input_grad[1]:
             if ctx.main_grad is not None:
                 grouped_wgrad(dy, x, offsets, G, out=ctx.main_grad, accumulate=True)

@@ -1,8 +1,11 @@
 """Low-precision variants of the linear layer, selected per module by ``ParallelLinear.precision``:
 
 * ``fp8``      - block-scaled e4m3 compute: activations quantised 1x128 per token on the fly, the weight 128x128
-  (cached until the parameter changes), product on the fp8 tensor-core GEMM; the backward pass runs in bf16 against
-  the dequantised weight (dgrad) and the saved bf16 activations (wgrad, skipped for a frozen base under LoRA).
+  (cached until the parameter changes), product on the fp8 tensor-core GEMM.  The data gradient runs on the same
+  GEMM (dY quantised 1x128 along the output features, the cached e4m3 weight transposed once per version;
+  ``GCORE_FP8_DGRAD=0`` falls back to bf16 against the dequantised weight); the weight gradient (skipped for a
+  frozen base under LoRA) runs in bf16 from the saved activations, or with ``GCORE_FP8_WGRAD=1`` on the fp8 GEMM
+  with both operands quantised along the token axis.
 * ``fp8_qat`` / ``fp4_qat`` - quantisation-aware training: the bf16 GEMM sees the weight after a quantise ->
   dequantise round trip (128x128 e4m3 blocks, or 1x32 e2m1 groups with power-of-two scales); gradients pass straight
   through to the bf16 parameter.
@@ -10,6 +13,8 @@
 (The reference's fp8 training path and fp8 / fp4 QAT: gpatch_v4/models/deepseek_v4/fp8.py, kernel/quantize/qat.py.)
 """
 from __future__ import annotations
+
+import os
 
 import torch
 
@@ -62,6 +67,14 @@ class _Ste(torch.autograd.Function):
         return g, None
 
 
+def fp8_dgrad_enabled() -> bool:
+    return os.environ.get("GCORE_FP8_DGRAD", "1") != "0"
+
+
+def fp8_wgrad_enabled() -> bool:
+    return os.environ.get("GCORE_FP8_WGRAD", "0") == "1"
+
+
 class _Fp8LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x2, w, bias, main_grad, cache):
@@ -84,10 +97,19 @@ class _Fp8LinearFn(torch.autograd.Function):
         dy2 = dy.contiguous()
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
-            w_dq = quant.dequant_128x128(ctx.cache["q"], ctx.cache["s"]).to(dy2.dtype)
-            dx = linear_dgrad(dy2, w_dq[:w.shape[0], :w.shape[1]].contiguous())
+            if fp8_dgrad_enabled() and w.shape[0] % 128 == 0 and w.shape[1] % 128 == 0:
+                dx = quant.fp8_dgrad(dy2, ctx.cache, dy2.dtype)
+            else:
+                w_dq = quant.dequant_128x128(ctx.cache["q"], ctx.cache["s"]).to(dy2.dtype)
+                dx = linear_dgrad(dy2, w_dq[:w.shape[0], :w.shape[1]].contiguous())
         if ctx.needs_input_grad[1]:
-            if ctx.main_grad is not None:
+            if fp8_wgrad_enabled() and w.shape[0] % 128 == 0 and w.shape[1] % 128 == 0:
+                g = quant.fp8_wgrad(dy2, x2)
+                if ctx.main_grad is not None:
+                    ctx.main_grad.add_(g)
+                else:
+                    dw = g.to(w.dtype)
+            elif ctx.main_grad is not None:
                 linear_wgrad(dy2, x2, out=ctx.main_grad, accumulate=True)
             else:
                 dw = linear_wgrad(dy2, x2, out_dtype=torch.float32).to(w.dtype)

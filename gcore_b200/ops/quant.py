@@ -169,6 +169,44 @@ def gemm_fp8_blockscaled(a_q, a_s, b_q, b_s, out_dtype=torch.bfloat16):
     return out
 
 
+def transpose_weight_128x128(q: torch.Tensor, s: torch.Tensor, groups: int = 1):
+    """Transposed copy of a 128x128-block-scaled e4m3 weight (``[G * N, K]`` -> ``[G * K, N]``, scales alike): a
+    square scale block is its own transpose, so the codes move and no value is re-quantised.  This is the B operand
+    of the fp8 data-gradient GEMM ``dX = dY W``."""
+    GN, K = q.shape
+    N = GN // groups
+    assert N % 128 == 0 and K % 128 == 0, (N, K)
+    qt = q.view(torch.uint8).view(groups, N, K).transpose(1, 2).contiguous().view(groups * K, N).view(q.dtype)
+    st = s.view(groups, N // 128, K // 128).transpose(1, 2).contiguous().view(groups * (K // 128), N // 128)
+    return qt, st
+
+
+def fp8_dgrad(dy: torch.Tensor, cache: dict, out_dtype, offsets=None, groups: int = 1):
+    """``dX = dY W`` on the block-fp8 GEMM: dY quantised 1x128 along the output features (the contraction), W taken
+    from the forward's e4m3 cache in transposed form (built once per weight version).  With ``offsets`` the grouped
+    (per-expert) form."""
+    if cache.get("t_ver") != cache["ver"]:
+        qt, st = transpose_weight_128x128(cache["q"], cache["s"], groups)
+        cache.update(t_ver=cache["ver"], qt=qt, st=st)
+    gq, gs = quant_act_1x128(dy.to(torch.bfloat16).contiguous())
+    od = out_dtype if out_dtype in (torch.bfloat16, torch.float32) else torch.bfloat16
+    if offsets is None:
+        return gemm_fp8_blockscaled(gq, gs, cache["qt"], cache["st"], out_dtype=od)
+    return gemm_fp8_grouped(gq, gs, cache["qt"], cache["st"], offsets, groups, out_dtype=od)
+
+
+def fp8_wgrad(dy: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """``dW = dY^T X`` (fp32 [N, K]) on the block-fp8 GEMM: the contraction runs over tokens, so dY^T is quantised
+    1x128 along tokens and X^T in 128x128 blocks; token counts are padded to a multiple of 128 with zero rows."""
+    M = dy.shape[0]
+    pad = (-M) % 128
+    dyt = torch.nn.functional.pad(dy.to(torch.bfloat16), (0, 0, 0, pad)).t().contiguous()   # [N, M']
+    xt = torch.nn.functional.pad(x.to(torch.bfloat16), (0, 0, 0, pad)).t().contiguous()     # [K, M']
+    aq, as_ = quant_act_1x128(dyt)
+    bq, bs = quant_weight_128x128(xt)
+    return gemm_fp8_blockscaled(aq, as_, bq, bs, out_dtype=torch.float32)
+
+
 def gemm_fp8_grouped(a_q, a_s, b_q, b_s, offsets, num_groups: int, out_dtype=torch.bfloat16):
     """Ragged-M grouped block-fp8 GEMM (experts): rows ``offsets[g]:offsets[g+1]`` of ``a_q`` [R, K] (multiples of
     128; scales ``a_s`` [R, K/128]) multiply group g's weight ``b_q[g * N:(g + 1) * N]`` ([G * N, K] e4m3, 128x128

@@ -807,3 +807,44 @@ def test_grouped_fp8_expert_projection_cpu_definition():
     y2.sum().backward()
     assert (x.grad - x2.grad).abs().max() / x2.grad.abs().max() < 0.08
     assert torch.allclose(w.grad, w2.grad, atol=1e-4)
+
+
+def test_fp8_data_and_weight_gradients_follow_the_bf16_ones(monkeypatch):
+    """The fp8 linear's backward on the block-fp8 product: the data gradient from the transposed e4m3 weight cache
+    (codes moved, not re-quantised), and, when switched on, the weight gradient with both operands quantised along
+    the token axis; dense and grouped (per-expert) forms, against the unquantised gradients."""
+    import torch
+    from gcore_b200.models.moe import grouped_linear
+    from gcore_b200.ops import quant
+    from gcore_b200.ops.lowp_linear import fp8_linear
+    torch.manual_seed(1)
+    # the transposed cache holds exactly the transposed values
+    w = torch.randn(2 * 256, 128) * 0.05
+    q, s = quant.quant_weight_128x128(w.bfloat16())
+    qt, st = quant.transpose_weight_128x128(q, s, groups=2)
+    full = quant.dequant_128x128(q, s).view(2, 256, 128)
+    assert torch.equal(quant.dequant_128x128(qt, st).view(2, 128, 256), full.transpose(1, 2))
+
+    def grads(env_d, env_w):
+        monkeypatch.setenv("GCORE_FP8_DGRAD", env_d)
+        monkeypatch.setenv("GCORE_FP8_WGRAD", env_w)
+        x = (torch.randn(200, 256, generator=torch.Generator().manual_seed(2))).requires_grad_(True)
+        wt = (torch.randn(384, 256, generator=torch.Generator().manual_seed(3)) * 0.05).requires_grad_(True)
+        y = fp8_linear(x, wt, None, None, {})
+        y.backward(torch.randn(200, 384, generator=torch.Generator().manual_seed(4)))
+        return x.grad, wt.grad
+    dx0, dw0 = grads("0", "0")
+    dx1, dw1 = grads("1", "1")
+    assert not torch.equal(dx0, dx1) and (dx0 - dx1).abs().max() / dx0.abs().max() < 0.08
+    assert not torch.equal(dw0, dw1) and (dw0 - dw1).abs().max() / dw0.abs().max() < 0.08
+
+    offs = torch.tensor([0, 128, 128, 384], dtype=torch.int32)    # the middle expert has no rows
+    outs = []
+    for flag in ("0", "1"):
+        monkeypatch.setenv("GCORE_FP8_DGRAD", flag)
+        x = torch.randn(384, 256, generator=torch.Generator().manual_seed(5)).requires_grad_(True)
+        wg = (torch.randn(3, 128, 256, generator=torch.Generator().manual_seed(6)) * 0.05).requires_grad_(True)
+        grouped_linear(x, wg, offs, "fp8", {}).backward(
+            torch.randn(384, 128, generator=torch.Generator().manual_seed(7)))
+        outs.append(x.grad)
+    assert not torch.equal(outs[0], outs[1]) and (outs[0] - outs[1]).abs().max() / outs[0].abs().max() < 0.08

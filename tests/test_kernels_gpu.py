@@ -641,6 +641,38 @@ def test_grouped_fp8_expert_projection_forward_backward():
     _close(w.grad, w2.grad, rtol=2e-2, atol=2e-2)            # wgrad runs in bf16 on the same operands
 
 
+def test_fp8_data_and_weight_gradient_products():
+    """dX = dY W and dW = dY^T X on the block-fp8 GEMM against the products of the same quantised operands in fp32
+    (dense and grouped data gradient), and against the unquantised gradients to fp8 accuracy."""
+    from gcore_b200.ops import _lib, quant
+    torch.manual_seed(33)
+    M, N, K = 300, 384, 512
+    dy, x, w = _rand(M, N, scale=1.0), _rand(M, K, scale=1.0), _rand(N, K, scale=0.05)
+    q, s = quant.quant_weight_128x128(w)
+    cache = {"ver": 1, "q": q, "s": s}
+    dx = quant.fp8_dgrad(dy, cache, torch.bfloat16)
+    gq, gs = quant.quant_act_1x128(dy)
+    ref = quant.dequant_1x128(gq, gs).float() @ quant.dequant_128x128(q, s)[:N, :K].float()
+    _close(dx, ref, rtol=1e-2, atol=1e-2)
+    assert (dx.float() - dy.float() @ w.float()).abs().max() / (dy.float() @ w.float()).abs().max() < 0.08
+    dw = quant.fp8_wgrad(dy, x)
+    full = dy.float().t() @ x.float()
+    assert dw.dtype == torch.float32 and dw.shape == (N, K)
+    assert (dw - full).abs().max() / full.abs().max() < 0.08
+    # grouped: experts 0 and 2 have rows, expert 1 none
+    G, offs = 3, torch.tensor([0, 128, 128, 384], dtype=torch.int32, device=DEV)
+    wg = _rand(G, 256, K, scale=0.05)
+    qg, sg = quant.quant_weight_128x128(wg.reshape(G * 256, K).contiguous())
+    dyg = _rand(384, 256, scale=1.0)
+    dxg = quant.fp8_dgrad(dyg, {"ver": 1, "q": qg, "s": sg}, torch.bfloat16, offsets=offs, groups=G)
+    gq, gs = quant.quant_act_1x128(dyg)
+    wdq = quant.dequant_128x128(qg, sg)[:G * 256, :K].float().view(G, 256, K)
+    a = quant.dequant_1x128(gq, gs).float()
+    _close(dxg[:128], a[:128] @ wdq[0], rtol=1e-2, atol=1e-2)
+    _close(dxg[128:384], a[128:384] @ wdq[2], rtol=1e-2, atol=1e-2)
+    _lib.check_device_errors()
+
+
 @pytest.mark.parametrize("T,N,K,bias,fp32", [(1, 512, 256, False, False), (8, 4608, 3584, True, False),
                                               (64, 3584, 18944, False, False), (100, 1000, 1792, True, True),
                                               (128, 2304, 3584, True, False), (128, 3584, 9472, False, True),

@@ -164,9 +164,22 @@ def from_dict(cls, data: dict, path: str = ""):
         raise ConfigError(f"{path or cls.__name__}: {e}") from e
 
 
-def load_yaml(path: str) -> dict:
+def load_yaml(path: str, _seen: tuple = ()) -> dict:
+    """Reads a YAML file.  A top-level ``base: other.yaml`` (relative to the file, or a list of them) is loaded first
+    and this file's keys are merged over it, so a recipe variant only spells what it changes."""
+    import os
+    real = os.path.realpath(path)
+    if real in _seen:
+        raise ConfigError(f"recipe files include each other in a cycle: {' -> '.join(_seen + (real,))}")
     with open(path) as f:
-        return yaml.safe_load(f) or {}
+        tree = yaml.safe_load(f) or {}
+    bases = tree.pop("base", None)
+    if not bases:
+        return tree
+    merged: dict = {}
+    for b in ([bases] if isinstance(bases, str) else list(bases)):
+        _deep_update(merged, load_yaml(os.path.join(os.path.dirname(path), b), _seen + (real,)))
+    return _deep_update(merged, tree)
 
 
 def load_config(cls, yaml_path: str | None = None, overrides: list[str] | None = None, base: dict | None = None):

@@ -28,7 +28,7 @@ def off_policy_loop(trainer: GrpoTrainer, prompt_batches, steps: int, log):
                       max_running_requests=ie.max_running_requests or cfg.training.rollout_gbs,
                       max_model_len=ie.max_model_len or (cfg.data.max_prompt_length + ie.generate_max_tokens),
                       kv_block_size=ie.kv_block_size, use_cuda_graph=not ie.disable_cuda_graph, device=teacher.device)
-    sp = SamplingParams(temperature=ie.temperature, top_k=ie.top_k, top_p=ie.top_p, min_p=ie.min_p,
+    sp = SamplingParams(temperature=ie.temperature, top_k=ie.top_k, top_p=ie.top_p, min_p=ie.min_p, repetition_penalty=ie.repetition_penalty,
                         max_new_tokens=ie.generate_max_tokens, seed=ie.seed)
     history = []
     for step, prompts in zip(range(steps), prompt_batches):

@@ -31,7 +31,7 @@ class DisaggGrpoTrainer(GrpoTrainer):
         self.release_rollout_weights = False
         self.serve_fp8 = False
         self.engine = None
-        self.sampling = SamplingParams(temperature=ie.temperature, top_k=ie.top_k, top_p=ie.top_p, min_p=ie.min_p,
+        self.sampling = SamplingParams(temperature=ie.temperature, top_k=ie.top_k, top_p=ie.top_p, min_p=ie.min_p, repetition_penalty=ie.repetition_penalty,
                                        max_new_tokens=ie.generate_max_tokens, seed=ie.seed,
                                        stop_token_ids=tuple(ie.generate_params.get("stop_token_ids", ())))
         if getattr(cfg.policy, "offload_ref_model", False):

@@ -117,7 +117,7 @@ class GrpoTrainer:
             kv_block_size=ie.kv_block_size, num_kv_blocks=ie.num_kv_blocks,
             gpu_memory_utilization=ie.gpu_memory_utilization, max_prefill_tokens=ie.max_prefill_tokens,
             use_cuda_graph=not ie.disable_cuda_graph, device=self.policy.device)
-        self.sampling = SamplingParams(temperature=ie.temperature, top_k=ie.top_k, top_p=ie.top_p, min_p=ie.min_p,
+        self.sampling = SamplingParams(temperature=ie.temperature, top_k=ie.top_k, top_p=ie.top_p, min_p=ie.min_p, repetition_penalty=ie.repetition_penalty,
                                        max_new_tokens=ie.generate_max_tokens, seed=ie.seed,
                                        stop_token_ids=tuple(ie.generate_params.get("stop_token_ids", ())))
         # fp8 serving: asked for by the engine config, and implied by an fp8 policy so that trainer and rollout

@@ -131,16 +131,65 @@ def test_every_recipe_yaml_loads_and_names_a_known_model():
     from gcore_b200.configs.base import load_config
     from gcore_b200.configs.config import FinetuneConfig, RlConfig
     from gcore_b200.models.config import PRESETS
+    from gcore_b200.configs.base import load_yaml
     files = sorted(glob.glob(os.path.join(ROOT, "tasks", "math_rl", "yaml", "*.yaml")))
-    assert len(files) >= 7
+    assert len(files) >= 35
     for f in files:
-        raw = yaml.safe_load(open(f))
+        raw = load_yaml(f)                    # variants name a ``base:`` recipe and spell only what they change
         cfg = load_config(RlConfig if "sampler" in raw else FinetuneConfig, f, [])
         assert cfg.policy.model_arch in PRESETS, f
         if "teacher" in raw:
             assert cfg.teacher.model_arch in PRESETS and cfg.ppo.advantage_type == "on_policy_distill"
         if raw["policy"].get("fp8"):
             assert cfg.policy.fp8 and cfg.policy.lora.enabled and "linear_kv_up_proj" in cfg.policy.lora.target_modules
+
+
+def test_recipe_variants_change_what_they_say_and_plug_ins_resolve():
+    from gcore_b200.configs.base import ConfigError, import_from_path, load_config, load_yaml
+    from gcore_b200.configs.config import FinetuneConfig, RlConfig
+    y = lambda n: os.path.join(ROOT, "tasks", "math_rl", "yaml", n)
+    base = load_config(RlConfig, y("grpo_qwen2.5_7b.yaml"), [])
+    want = {"rl_cispo.yaml": lambda c: c.ppo.loss_func == "cispo" and c.ppo.ppo_clip_ratio_high == 0.28,
+            "rl_gspo.yaml": lambda c: c.ppo.loss_func == "gspo" and not c.ppo.per_token_loss,
+            "rl_icepop.yaml": lambda c: c.ppo.offpolicy_correction == "icepop" and c.ppo.offpolicy_correction_lower == 0.5,
+            "rl_clip_cov.yaml": lambda c: c.ppo.entropy_regularization_type == "clip-cov",
+            "rl_dynamic_sampling.yaml": lambda c: c.training.dynamic_sampling.enable and c.policy.without_ref,
+            "rl_async.yaml": lambda c: c.training.async_rollout and c.training.rollout_max_staleness == 1,
+            "rl_online_mtp.yaml": lambda c: c.training.online_mtp_sft and c.policy.model_config["mtp_num_layers"] == 1,
+            "rl_disaggregated.yaml": lambda c: c.placement_type == "disaggregated" and c.disaggregated_train_gpus == 4,
+            "rl_sampling_filters.yaml": lambda c: c.sampler.infer_engine_configs[0].repetition_penalty == 1.1,
+            "rl_dynamic_cp.yaml": lambda c: c.policy.dist_config.dynamic_context_parallel
+            and c.policy.dist_config.context_parallel_size == 4,
+            "rl_gdpo.yaml": lambda c: c.ppo.advantage_type == "gdpo" and c.ppo.gdpo_reward_weights["format"] == 0.2}
+    for name, check in want.items():
+        c = load_config(RlConfig, y(name), [])
+        assert check(c), name
+        # everything the variant does not mention is the base recipe's
+        assert c.policy.model_arch == base.policy.model_arch and c.training.rollout_gbs == base.training.rollout_gbs
+        assert c.report.run_name == name[:-5]
+    s = load_config(FinetuneConfig, y("sft_fsdp2.yaml"), [])
+    assert s.training.training_backend == "fsdp2" and s.policy.dist_config.tensor_model_parallel_size == 1
+    assert load_config(FinetuneConfig, y("sft_with_mtp.yaml"), []).policy.model_config["mtp_num_layers"] == 1
+    assert load_config(FinetuneConfig, y("sft_muon.yaml"), []).optimizer.optimizer_type == "muon"
+    c = load_config(RlConfig, y("rl_custom_advantage.yaml"), [])
+    fn = import_from_path(os.path.join(ROOT, c.ppo.advantage_py_path), c.ppo.advantage_fn_name)
+    import torch
+    smp = [{"group_id": 0, "rewards": torch.tensor(r), "mask": torch.tensor([0.0, 1.0, 1.0])} for r in (1.0, 0.0, 0.0)]
+    out = fn(smp, c.ppo)
+    assert out[0]["advantages"].tolist() == [0.0, 1.0, 1.0] and out[1]["advantages"].tolist() == [0.0, -0.5, -0.5]
+
+
+def test_recipe_includes_merge_in_order_and_reject_cycles(tmp_path):
+    from gcore_b200.configs.base import ConfigError, load_yaml
+    (tmp_path / "a.yaml").write_text("x: {p: 1, q: 2}\ny: 1\n")
+    (tmp_path / "b.yaml").write_text("base: a.yaml\nx: {q: 3}\nz: 5\n")
+    (tmp_path / "c.yaml").write_text("base: [a.yaml, b.yaml]\ny: 9\n")
+    assert load_yaml(str(tmp_path / "b.yaml")) == {"x": {"p": 1, "q": 3}, "y": 1, "z": 5}
+    assert load_yaml(str(tmp_path / "c.yaml")) == {"x": {"p": 1, "q": 3}, "y": 9, "z": 5}
+    (tmp_path / "d.yaml").write_text("base: e.yaml\n")
+    (tmp_path / "e.yaml").write_text("base: d.yaml\n")
+    with pytest.raises(ConfigError):
+        load_yaml(str(tmp_path / "d.yaml"))
 
 
 def test_image_generation_and_vision_language_recipes_load():

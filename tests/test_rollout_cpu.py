@@ -261,3 +261,33 @@ def test_block_manager_accounting_fork_and_exhaustion():
     # exhaustion: a request that cannot fit is refused at add time, the cache stays consistent
     assert s.add(9, 100, 50) != 0
     assert s.stats()["free_blocks"] == 12 and s.stats()["waiting"] == 0
+
+
+def test_repetition_penalty_follows_the_definition_across_slot_reuse():
+    """Greedy decode with a repetition penalty = a full recompute that divides (positive) / multiplies (negative) the
+    logits of every token of the prompt and of the output so far; more requests than slots, so slots are re-used and
+    their tables of seen tokens restart."""
+    cfg, model = build()
+    pen = 1.7
+    eng = InferEngine(cfg, RolloutWeights.from_model(model), max_running_requests=2, max_model_len=64,
+                      kv_block_size=4, sync_interval=3, use_cuda_graph=False)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(3, 1024, (l,), generator=g).tolist() for l in (6, 11, 4, 9, 7)]
+    reqs = eng.generate(prompts, SamplingParams(max_new_tokens=8, greedy=True, repetition_penalty=pen))
+    plain = eng.generate(prompts, SamplingParams(max_new_tokens=8, greedy=True))
+    assert any(a.out_tokens != b.out_tokens for a, b in zip(reqs, plain))     # the penalty changes something
+    for r, p in zip(reqs, prompts):
+        toks = list(p)
+        for want, want_lp in zip(r.out_tokens, r.out_logprobs):
+            t = torch.tensor(toks)
+            with torch.no_grad():
+                h, _ = model(t, torch.arange(len(toks), dtype=torch.int32), torch.tensor([0, len(toks)], dtype=torch.int32),
+                             len(toks))
+                z = model.logits(h[-1:]).float()[0]
+            seen = torch.zeros_like(z, dtype=torch.bool)
+            seen[t] = True
+            z = torch.where(seen, torch.where(z > 0, z / pen, z * pen), z)
+            lp = torch.log_softmax(z, -1)
+            assert int(lp.argmax()) == want
+            assert abs(float(lp[want]) - want_lp) < 1e-3
+            toks.append(want)

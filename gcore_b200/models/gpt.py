@@ -238,7 +238,8 @@ class MLAttention(nn.Module):
         from ..ops import _lib
         if (dn + dr, dv) == (192, 128) and qf.is_cuda and qf.dtype == torch.bfloat16 and not _lib.force_eager() \
                 and os.environ.get("GCORE_MLA_FLASH", "1") != "0":
-            # 192-wide keys / 128-wide values: the tcgen05 flash kernel's wide-key instance over the whole packed batch
+            # 192-wide keys / 128-wide values: the tcgen05 flash kernels' wide-key instances (forward and backward)
+            # over the whole packed batch
             from ..ops.attention import flash_attn_varlen
             if max_seqlen is None:
                 max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max())

@@ -200,3 +200,4 @@ def _declare_kernels(lib: ctypes.CDLL):
     d("gk_mla_set_target_ctas", [I], None)
     d("gk_attn_fwd", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P])
     d("gk_attn_bwd", [P, P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P])
+    d("gk_attn_bwd_dv", [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P, P])

@@ -91,7 +91,7 @@ def _native_ok(q, k, v):
 
 
 def _have_native_bwd():
-    return getattr(_lib.kernels(), "gk_attn_bwd", None) is not None
+    return getattr(_lib.kernels(), "gk_attn_bwd_dv", None) is not None
 
 
 class _FlashAttnFn(torch.autograd.Function):
@@ -114,11 +114,10 @@ class _FlashAttnFn(torch.autograd.Function):
 
 
 class _FlashAttnWideKeyFn(torch.autograd.Function):
-    """Causal self-attention with 192-wide queries / keys and 128-wide values: the forward is the tcgen05 kernel; the
-    backward kernels are built for equal head dims, so the gradient comes from the library's flash backward on the
-    saved output and log-sum-exp (values, output and its gradient zero-padded to the key width, which that routine
-    wants equal), or, where that entry point is missing or refuses the operands, from a per-sequence recompute through
-    the library's fused attention under autograd."""
+    """Causal self-attention with 192-wide queries / keys and 128-wide values: forward and backward are the tcgen05
+    kernels' 192 / 128 instances.  ``GCORE_WIDE_KEY_BWD=flash`` takes the gradient from the library's flash backward
+    on the saved output and log-sum-exp instead (values, output and its gradient zero-padded to the key width, which
+    that routine wants equal), ``=recompute`` from a per-sequence recompute through the library's fused attention."""
 
     @staticmethod
     def forward(ctx, q, k, v, cu, max_s, scale):
@@ -133,17 +132,21 @@ class _FlashAttnWideKeyFn(torch.autograd.Function):
         max_s, scale = ctx.cfg
         D, Dv = q.shape[-1], v.shape[-1]
         pad = (0, D - Dv)
-        try:
-            if os.environ.get("GCORE_WIDE_KEY_BWD", "flash") != "flash":
-                raise NotImplementedError
-            F = torch.nn.functional
-            dq, dk, dvp = torch.ops.aten._flash_attention_backward(
-                F.pad(do, pad).contiguous(), q.contiguous(), k.contiguous(), F.pad(v, pad).contiguous(),
-                F.pad(out, pad).contiguous(), lse.contiguous(), cu, cu, int(max_s), int(max_s), 0.0, True,
-                torch.zeros(2, dtype=torch.int64, device=q.device), torch.empty(0, device=q.device), scale=scale)
-            return dq, dk, dvp[..., :Dv].contiguous(), None, None, None
-        except (RuntimeError, NotImplementedError, AttributeError):
-            pass
+        how = os.environ.get("GCORE_WIDE_KEY_BWD", "native")
+        if how == "native" and _have_native_bwd():
+            from .attention_bwd import attn_bwd
+            dq, dk, dv, _ = attn_bwd(do.contiguous(), q, k, v, out, lse, None, cu, cu, max_s, max_s, True, 0, scale)
+            return dq, dk, dv, None, None, None
+        if how in ("native", "flash"):
+            try:
+                F = torch.nn.functional
+                dq, dk, dvp = torch.ops.aten._flash_attention_backward(
+                    F.pad(do, pad).contiguous(), q.contiguous(), k.contiguous(), F.pad(v, pad).contiguous(),
+                    F.pad(out, pad).contiguous(), lse.contiguous(), cu, cu, int(max_s), int(max_s), 0.0, True,
+                    torch.zeros(2, dtype=torch.int64, device=q.device), torch.empty(0, device=q.device), scale=scale)
+                return dq, dk, dvp[..., :Dv].contiguous(), None, None, None
+            except (RuntimeError, NotImplementedError, AttributeError):
+                pass
         bounds = cu.tolist()
         dq, dk, dv = torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v)
         for a, b in zip(bounds[:-1], bounds[1:]):

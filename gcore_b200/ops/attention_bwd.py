@@ -51,31 +51,31 @@ def _recompute_bwd(do, q, k, v, sinks, cu_q, cu_k, causal, window, scale):
 
 def attn_bwd(do, q, k, v, out, lse, sinks, cu_q, cu_k, max_q, max_k, causal, window, scale):
     lib = _lib.kernels() if _lib.use_native(q) else None
-    fn = getattr(lib, "gk_attn_bwd", None) if lib is not None else None
+    fn = getattr(lib, "gk_attn_bwd_dv", None) if lib is not None else None
     if fn is None:
         return _recompute_bwd(do, q, k, v, sinks, cu_q, cu_k, causal, window, scale)
     Tq, Hq, D = q.shape
     Tk, Hk, _ = k.shape
+    Dv = v.shape[-1]       # equal to D, or 128 beside 192-wide queries / keys (expanded latent attention)
     B = cu_q.numel() - 1
     g = Hq // Hk
     dq = torch.empty_like(q)
     # per-query-head dK/dV, reduced over the GQA group afterwards (deterministic, no atomics)
     dk_h = torch.empty(Tk, Hq, D, dtype=q.dtype, device=q.device)
-    dv_h = torch.empty(Tk, Hq, D, dtype=q.dtype, device=q.device)
+    dv_h = torch.empty(Tk, Hq, Dv, dtype=q.dtype, device=q.device)
     delta = torch.empty(Hq, Tq, dtype=torch.float32, device=q.device)
-    dsink_part = torch.zeros(Hq, dtype=torch.float32, device=q.device) if sinks is not None else None
     strides = (ctypes.c_longlong * 4)(q.stride(0), k.stride(0), v.stride(0), out.stride(0))
     se = (ctypes.c_void_p * 2)(torch.cuda.current_stream().cuda_stream, _lib.err_flag(q.device).data_ptr())
     rc = fn(_lib.ptr(do), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(lse), _lib.ptr(delta),
-            _lib.ptr(dq), _lib.ptr(dk_h), _lib.ptr(dv_h), _lib.ptr(cu_q), _lib.ptr(cu_k), _lib.ptr(sinks),
-            _lib.ptr(dsink_part), B, Tq, Tk, Hq, Hk, D, int(max_q), int(max_k), float(scale), int(causal),
-            int(window or 0), ctypes.cast(strides, ctypes.c_void_p), ctypes.cast(se, ctypes.c_void_p))
+            _lib.ptr(dq), _lib.ptr(dk_h), _lib.ptr(dv_h), _lib.ptr(cu_q), _lib.ptr(cu_k), B, Tq, Tk, Hq, Hk, D, Dv,
+            int(max_q), int(max_k), float(scale), int(causal), int(window or 0),
+            ctypes.cast(strides, ctypes.c_void_p), ctypes.cast(se, ctypes.c_void_p))
     _lib.check(rc, "gk_attn_bwd")
     if g == 1:
         dk, dv = dk_h, dv_h
     else:
         dk = dk_h.view(Tk, Hk, g, D).float().sum(2).to(q.dtype)
-        dv = dv_h.view(Tk, Hk, g, D).float().sum(2).to(q.dtype)
+        dv = dv_h.view(Tk, Hk, g, Dv).float().sum(2).to(q.dtype)
     ds = None
     if sinks is not None:
         # d sink_h = -sum_t exp(sink_h - lse[h, t]) * delta[h, t]   (rows without any visible key carry lse = -max)

@@ -79,22 +79,30 @@ __device__ __forceinline__ void store_row_chunk_sw128(uint8_t* tile, int row, in
 
 // ---------------------------------------------------------------------------------------------------------------
 // dK / dV.  Stationary: K, V tile of 128 keys.  Streamed: Q, dO tiles of 64 query rows (2 stages).
-// TMEM columns: S^T buffers [0,64) [64,128), dP^T buffers [128,192) [192,256), dV [256, 256+D), dK [384, 384+D).
-template <int D>
+// DQK = head dim of Q / K / dK, DV = head dim of V / dO / dV.
+// TMEM columns with equal head dims (<= 128): S^T buffers [0,64) [64,128), dP^T buffers [128,192) [192,256),
+// dV [256, 256+DV), dK [384, 384+DQK).  The 192 / 128 instance has one S^T and one dP^T buffer (NT = 1), which is
+// what fits beside a 192-column dK: S^T [0,64), dP^T [64,128), dV [128,256), dK [256,448); the scores of tile i+1
+// are then issued once the threads have read tile i, and still overlap tile i's accumulate MMAs.
+template <int DQK, int DV>
 __global__ void __launch_bounds__(FB_THREADS, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, FbParams p) {
-  constexpr int NCH = D / 64;
-  constexpr int KV_BYTES = 128 * D * 2;  // stationary tile
-  constexpr int Q_BYTES = 64 * D * 2;    // streamed tile (64 rows): chunks of 8 KB
-  constexpr int PS_BYTES = 128 * 64 * 2; // P^T / dS^T tile: 128 rows x 128 B
+  constexpr int NCH = DQK / 64;
+  constexpr int NCHV = DV / 64;
+  constexpr int NT = (256 + DV + DQK <= 512) ? 2 : 1;   // S^T / dP^T buffers in tensor memory
+  constexpr int K_BYTES = 128 * DQK * 2;  // stationary tiles
+  constexpr int V_BYTES = 128 * DV * 2;
+  constexpr int Q_BYTES = 64 * DQK * 2;   // streamed tiles (64 rows): chunks of 8 KB
+  constexpr int DO_BYTES = 64 * DV * 2;
+  constexpr int PS_BYTES = 128 * 64 * 2;  // P^T / dS^T tile: 128 rows x 128 B
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
-  uint8_t* sV = sK + KV_BYTES;
-  uint8_t* sQ = sV + KV_BYTES;           // 2 stages
+  uint8_t* sV = sK + K_BYTES;
+  uint8_t* sQ = sV + V_BYTES;            // 2 stages
   uint8_t* sDO = sQ + 2 * Q_BYTES;       // 2 stages
-  uint8_t* sP = sDO + 2 * Q_BYTES;       // 2 buffers
+  uint8_t* sP = sDO + 2 * DO_BYTES;      // 2 buffers
   uint8_t* sDS = sP + 2 * PS_BYTES;      // 2 buffers
   float* s_lse = reinterpret_cast<float*>(sDS + 2 * PS_BYTES);  // [2][64]
   float* s_delta = s_lse + 128;                                  // [2][64]
@@ -151,18 +159,18 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
-  const uint32_t tmem_dv = tmem_base + 256, tmem_dk = tmem_base + 384;
+  const uint32_t tmem_dp = tmem_base + NT * 64;
+  const uint32_t tmem_dv = tmem_base + 2 * NT * 64, tmem_dk = tmem_dv + DV;
 
   if (warp == 4) {
     // ------------------------------------------------------------------ TMA producer
     if (ntiles > 0) {
       if (lane == 0) {
-        mbar_expect_tx(kv_full, 2 * KV_BYTES);
+        mbar_expect_tx(kv_full, K_BYTES + V_BYTES);
 #pragma unroll
-        for (int c = 0; c < NCH; ++c) {
-          tma_load_3d(sK + c * 16384, &tmK, kv_full, c * 64, hk, k_beg + k0);
-          tma_load_3d(sV + c * 16384, &tmV, kv_full, c * 64, hk, k_beg + k0);
-        }
+        for (int c = 0; c < NCH; ++c) tma_load_3d(sK + c * 16384, &tmK, kv_full, c * 64, hk, k_beg + k0);
+#pragma unroll
+        for (int c = 0; c < NCHV; ++c) tma_load_3d(sV + c * 16384, &tmV, kv_full, c * 64, hk, k_beg + k0);
       }
       __syncwarp();
       bool ok = true;
@@ -172,12 +180,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         if (!ok) break;
         if (lane == 0) {
           const int qrow = q_beg + (i_beg + it) * 64;
-          mbar_expect_tx(&qd_full[s], 2 * Q_BYTES);
+          mbar_expect_tx(&qd_full[s], Q_BYTES + DO_BYTES);
 #pragma unroll
-          for (int c = 0; c < NCH; ++c) {
-            tma_load_3d(sQ + s * Q_BYTES + c * 8192, &tmQ, &qd_full[s], c * 64, h, qrow);
-            tma_load_3d(sDO + s * Q_BYTES + c * 8192, &tmDO, &qd_full[s], c * 64, h, qrow);
-          }
+          for (int c = 0; c < NCH; ++c) tma_load_3d(sQ + s * Q_BYTES + c * 8192, &tmQ, &qd_full[s], c * 64, h, qrow);
+#pragma unroll
+          for (int c = 0; c < NCHV; ++c)
+            tma_load_3d(sDO + s * DO_BYTES + c * 8192, &tmDO, &qd_full[s], c * 64, h, qrow);
         }
         __syncwarp();
       }
@@ -185,32 +193,33 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   } else if (warp == 5) {
     // ------------------------------------------------------------------ MMA issuer
     constexpr uint32_t idesc_st = make_idesc(128, 64, 1, 1, 0, 0);  // [keys x q] = K-major x K-major
-    constexpr uint32_t idesc_acc = make_idesc(128, D, 1, 1, 0, 1);  // [keys x D] = A(K-major over q) x B(MN-major)
+    constexpr uint32_t idesc_dv = make_idesc(128, DV, 1, 1, 0, 1);   // [keys x DV] = A(K-major over q) x B(MN-major)
+    constexpr uint32_t idesc_dk = make_idesc(128, DQK, 1, 1, 0, 1);
     bool ok = ntiles > 0;
     if (ok) ok = mbar_wait(kv_full, 0, p.err, ERR_WAIT_FULL);
     auto issue_scores = [&](int it) -> bool {
-      const int s = it & 1;
+      const int s = it & 1, ts = it % NT;
       if (!mbar_wait(&qd_full[s], (it >> 1) & 1, p.err, ERR_WAIT_FULL)) return false;
-      if (it >= 2 && !mbar_wait(&s_free[s], ((it - 2) >> 1) & 1, p.err, ERR_WAIT_TMEM_EMPTY)) return false;
+      if (it >= NT && !mbar_wait(&s_free[ts], ((it - NT) / NT) & 1, p.err, ERR_WAIT_TMEM_EMPTY)) return false;
       tc_fence_after();
       if (lane == 0) {
         const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
-        const uint32_t qa = smem_u32(sQ + s * Q_BYTES), da = smem_u32(sDO + s * Q_BYTES);
+        const uint32_t qa = smem_u32(sQ + s * Q_BYTES), da = smem_u32(sDO + s * DO_BYTES);
 #pragma unroll
-        for (int k4 = 0; k4 < D / 16; ++k4) {
+        for (int k4 = 0; k4 < DQK / 16; ++k4) {
           const uint32_t oa = (k4 >> 2) * 16384 + (k4 & 3) * 32;  // stationary tiles: 128-row chunks
           const uint32_t ob = (k4 >> 2) * 8192 + (k4 & 3) * 32;   // streamed tiles: 64-row chunks
-          umma_f16(tmem_base + s * 64, make_smem_desc_sw128(ka + oa, 16, 1024),
+          umma_f16(tmem_base + ts * 64, make_smem_desc_sw128(ka + oa, 16, 1024),
                    make_smem_desc_sw128(qa + ob, 16, 1024), idesc_st, k4 > 0 ? 1u : 0u);
         }
 #pragma unroll
-        for (int k4 = 0; k4 < D / 16; ++k4) {
+        for (int k4 = 0; k4 < DV / 16; ++k4) {
           const uint32_t oa = (k4 >> 2) * 16384 + (k4 & 3) * 32;
           const uint32_t ob = (k4 >> 2) * 8192 + (k4 & 3) * 32;
-          umma_f16(tmem_base + 128 + s * 64, make_smem_desc_sw128(va + oa, 16, 1024),
+          umma_f16(tmem_dp + ts * 64, make_smem_desc_sw128(va + oa, 16, 1024),
                    make_smem_desc_sw128(da + ob, 16, 1024), idesc_st, k4 > 0 ? 1u : 0u);
         }
-        umma_commit(&s_full[s]);
+        umma_commit(&s_full[ts]);
       }
       __syncwarp();
       return true;
@@ -227,16 +236,16 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tc_fence_after();
       if (lane == 0) {
         const uint32_t pa = smem_u32(sP + s * PS_BYTES), dsa = smem_u32(sDS + s * PS_BYTES);
-        const uint32_t qa = smem_u32(sQ + s * Q_BYTES), da = smem_u32(sDO + s * Q_BYTES);
+        const uint32_t qa = smem_u32(sQ + s * Q_BYTES), da = smem_u32(sDO + s * DO_BYTES);
 #pragma unroll
         for (int k4 = 0; k4 < 64 / 16; ++k4) {  // contraction over the 64 query rows
           umma_f16(tmem_dv, make_smem_desc_sw128(pa + k4 * 32, 16, 1024),
-                   make_smem_desc_sw128(da + k4 * 2048, 8192, 1024), idesc_acc, (it > 0 || k4 > 0) ? 1u : 0u);
+                   make_smem_desc_sw128(da + k4 * 2048, 8192, 1024), idesc_dv, (it > 0 || k4 > 0) ? 1u : 0u);
         }
 #pragma unroll
         for (int k4 = 0; k4 < 64 / 16; ++k4) {
           umma_f16(tmem_dk, make_smem_desc_sw128(dsa + k4 * 32, 16, 1024),
-                   make_smem_desc_sw128(qa + k4 * 2048, 8192, 1024), idesc_acc, (it > 0 || k4 > 0) ? 1u : 0u);
+                   make_smem_desc_sw128(qa + k4 * 2048, 8192, 1024), idesc_dk, (it > 0 || k4 > 0) ? 1u : 0u);
         }
         umma_commit(&acc_done[s]);
       }
@@ -271,7 +280,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
       ok = mbar_wait(&lse_full[s], (it >> 1) & 1, p.err, ERR_WAIT_MISC);
       if (!ok) break;
-      ok = mbar_wait(&s_full[s], (it >> 1) & 1, p.err, ERR_WAIT_TMEM_FULL);
+      const int ts = it % NT;
+      ok = mbar_wait(&s_full[ts], (it / NT) & 1, p.err, ERR_WAIT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
       // interior tile for this warp's 32 keys: every (query, key) pair is visible, no mask arithmetic needed
@@ -281,8 +291,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t rs[32], rp[32];
-        tmem_ld32(tmem_base + lane_addr + s * 64 + c * 32, rs);
-        tmem_ld32(tmem_base + lane_addr + 128 + s * 64 + c * 32, rp);
+        tmem_ld32(tmem_base + lane_addr + ts * 64 + c * 32, rs);
+        tmem_ld32(tmem_dp + lane_addr + ts * 64 + c * 32, rp);
         tmem_ld_wait();
         float pv[32], dsv[32];
         const float4* l4 = reinterpret_cast<const float4*>(s_lse + s * 64 + c * 32);
@@ -319,7 +329,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         store_row_chunk_sw128(sDS + s * PS_BYTES, row, c * 32, dsv);
       }
       tc_fence_before();
-      mbar_arrive(&s_free[s]);
+      mbar_arrive(&s_free[ts]);
       fence_proxy_async();
       mbar_arrive(&pds_full[s]);
     }
@@ -329,14 +339,14 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
     if (ok) {
       const bool valid = kj < lk;
-      const long long orow = (static_cast<long long>(k_beg + kj) * p.Hq + h) * D;
+      const long long orow = static_cast<long long>(k_beg + kj) * p.Hq + h;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
-        __nv_bfloat16* dst = (which == 0 ? p.dv : p.dk) + orow;
+        __nv_bfloat16* dst = which == 0 ? p.dv + orow * DV : p.dk + orow * DQK;
         const uint32_t tbase = (which == 0 ? tmem_dv : tmem_dk) + lane_addr;
         const float mul = which == 0 ? 1.f : p.scale;
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = 0; c < (which == 0 ? DV : DQK) / 32; ++c) {
           uint32_t r[32];
           if (ntiles > 0) {
             tmem_ld32(tbase + c * 32, r);
@@ -370,22 +380,25 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
 // ---------------------------------------------------------------------------------------------------------------
 // dQ.  Stationary: Q, dO tile of 128 query rows.  Streamed: K, V tiles of 64 keys (2 stages).
-// TMEM columns: S buffers [0,64) [64,128), dP buffers [128,192) [192,256), dQ [256, 256+D).
-template <int D>
+// TMEM columns: S buffers [0,64) [64,128), dP buffers [128,192) [192,256), dQ [256, 256+DQK).
+template <int DQK, int DV>
 __global__ void __launch_bounds__(FB_THREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, FbParams p) {
-  constexpr int NCH = D / 64;
-  constexpr int Q_BYTES = 128 * D * 2;
-  constexpr int KV_BYTES = 64 * D * 2;
+  constexpr int NCH = DQK / 64;
+  constexpr int NCHV = DV / 64;
+  constexpr int Q_BYTES = 128 * DQK * 2;
+  constexpr int DO_BYTES = 128 * DV * 2;
+  constexpr int K_BYTES = 64 * DQK * 2;
+  constexpr int V_BYTES = 64 * DV * 2;
   constexpr int DS_BYTES = 128 * 64 * 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sDO = sQ + Q_BYTES;
-  uint8_t* sK = sDO + Q_BYTES;         // 2 stages
-  uint8_t* sV = sK + 2 * KV_BYTES;     // 2 stages
-  uint8_t* sDS = sV + 2 * KV_BYTES;    // 2 buffers
+  uint8_t* sK = sDO + DO_BYTES;        // 2 stages
+  uint8_t* sV = sK + 2 * K_BYTES;      // 2 stages
+  uint8_t* sDS = sV + 2 * V_BYTES;     // 2 buffers
   uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + 2 * DS_BYTES);
   uint64_t* q_full = bars;         // 1
   uint64_t* kv_full = bars + 1;    // 2
@@ -442,12 +455,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (warp == 4) {
     if (ntiles > 0) {
       if (lane == 0) {
-        mbar_expect_tx(q_full, 2 * Q_BYTES);
+        mbar_expect_tx(q_full, Q_BYTES + DO_BYTES);
 #pragma unroll
-        for (int c = 0; c < NCH; ++c) {
-          tma_load_3d(sQ + c * 16384, &tmQ, q_full, c * 64, h, q_beg + q0);
-          tma_load_3d(sDO + c * 16384, &tmDO, q_full, c * 64, h, q_beg + q0);
-        }
+        for (int c = 0; c < NCH; ++c) tma_load_3d(sQ + c * 16384, &tmQ, q_full, c * 64, h, q_beg + q0);
+#pragma unroll
+        for (int c = 0; c < NCHV; ++c) tma_load_3d(sDO + c * 16384, &tmDO, q_full, c * 64, h, q_beg + q0);
       }
       __syncwarp();
       bool ok = true;
@@ -457,19 +469,18 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (!ok) break;
         if (lane == 0) {
           const int krow = k_beg + (j_beg + it) * 64;
-          mbar_expect_tx(&kv_full[s], 2 * KV_BYTES);
+          mbar_expect_tx(&kv_full[s], K_BYTES + V_BYTES);
 #pragma unroll
-          for (int c = 0; c < NCH; ++c) {
-            tma_load_3d(sK + s * KV_BYTES + c * 8192, &tmK, &kv_full[s], c * 64, hk, krow);
-            tma_load_3d(sV + s * KV_BYTES + c * 8192, &tmV, &kv_full[s], c * 64, hk, krow);
-          }
+          for (int c = 0; c < NCH; ++c) tma_load_3d(sK + s * K_BYTES + c * 8192, &tmK, &kv_full[s], c * 64, hk, krow);
+#pragma unroll
+          for (int c = 0; c < NCHV; ++c) tma_load_3d(sV + s * V_BYTES + c * 8192, &tmV, &kv_full[s], c * 64, hk, krow);
         }
         __syncwarp();
       }
     }
   } else if (warp == 5) {
     constexpr uint32_t idesc_s = make_idesc(128, 64, 1, 1, 0, 0);
-    constexpr uint32_t idesc_dq = make_idesc(128, D, 1, 1, 0, 1);
+    constexpr uint32_t idesc_dq = make_idesc(128, DQK, 1, 1, 0, 1);
     bool ok = ntiles > 0;
     if (ok) ok = mbar_wait(q_full, 0, p.err, ERR_WAIT_FULL);
     auto issue_scores = [&](int it) -> bool {
@@ -479,16 +490,16 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tc_fence_after();
       if (lane == 0) {
         const uint32_t qa = smem_u32(sQ), da = smem_u32(sDO);
-        const uint32_t ka = smem_u32(sK + s * KV_BYTES), va = smem_u32(sV + s * KV_BYTES);
+        const uint32_t ka = smem_u32(sK + s * K_BYTES), va = smem_u32(sV + s * V_BYTES);
 #pragma unroll
-        for (int k4 = 0; k4 < D / 16; ++k4) {
+        for (int k4 = 0; k4 < DQK / 16; ++k4) {
           const uint32_t oa = (k4 >> 2) * 16384 + (k4 & 3) * 32;
           const uint32_t ob = (k4 >> 2) * 8192 + (k4 & 3) * 32;
           umma_f16(tmem_base + s * 64, make_smem_desc_sw128(qa + oa, 16, 1024),
                    make_smem_desc_sw128(ka + ob, 16, 1024), idesc_s, k4 > 0 ? 1u : 0u);
         }
 #pragma unroll
-        for (int k4 = 0; k4 < D / 16; ++k4) {
+        for (int k4 = 0; k4 < DV / 16; ++k4) {
           const uint32_t oa = (k4 >> 2) * 16384 + (k4 & 3) * 32;
           const uint32_t ob = (k4 >> 2) * 8192 + (k4 & 3) * 32;
           umma_f16(tmem_base + 128 + s * 64, make_smem_desc_sw128(da + oa, 16, 1024),
@@ -510,7 +521,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (!ok) break;
       tc_fence_after();
       if (lane == 0) {
-        const uint32_t dsa = smem_u32(sDS + s * DS_BYTES), ka = smem_u32(sK + s * KV_BYTES);
+        const uint32_t dsa = smem_u32(sDS + s * DS_BYTES), ka = smem_u32(sK + s * K_BYTES);
 #pragma unroll
         for (int k4 = 0; k4 < 64 / 16; ++k4) {  // contraction over the 64 keys
           umma_f16(tmem_dq, make_smem_desc_sw128(dsa + k4 * 32, 16, 1024),
@@ -580,9 +591,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (ok) tc_fence_after();
     }
     if (ok) {
-      __nv_bfloat16* dst = p.dq + (static_cast<long long>(q_beg + qi) * p.Hq + h) * D;
+      __nv_bfloat16* dst = p.dq + (static_cast<long long>(q_beg + qi) * p.Hq + h) * DQK;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < DQK / 32; ++c) {
         uint32_t r[32];
         if (ntiles > 0) {
           tmem_ld32(tmem_dq + lane_addr + c * 32, r);
@@ -613,24 +624,28 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   }
 }
 
-template <int D>
+template <int DQK, int DV>
 int launch_bwd(const CUtensorMap& q128, const CUtensorMap& q64, const CUtensorMap& k128, const CUtensorMap& k64,
                const CUtensorMap& v128, const CUtensorMap& v64, const CUtensorMap& do128, const CUtensorMap& do64,
                const FbParams& p, int B, int max_q, int max_k, cudaStream_t st) {
-  constexpr int SMEM1 = 2 * 128 * D * 2 + 4 * 64 * D * 2 + 4 * 128 * 64 * 2 + 1024 + 1024 + 256;
-  constexpr int SMEM2 = 2 * 128 * D * 2 + 4 * 64 * D * 2 + 2 * 128 * 64 * 2 + 1024 + 256;
+  // stationary + 2 streamed stages of each operand, P^T / dS^T buffers, lse / delta slots, alignment slack, barriers:
+  // 226.25 KB for 192 / 128 (of 227 KB), 194.25 KB for 128 / 128
+  constexpr int SMEM1 = (128 + 2 * 64) * (DQK + DV) * 2 + 4 * 128 * 64 * 2 + 1024 + 1024 + 256;
+  constexpr int SMEM2 = (128 + 2 * 64) * (DQK + DV) * 2 + 2 * 128 * 64 * 2 + 1024 + 256;
+  static_assert(SMEM1 <= 232448, "dK/dV kernel exceeds the shared memory of an SM");
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_bwd_dkdv_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM1);
+    cudaError_t e =
+        cudaFuncSetAttribute(attn_bwd_dkdv_kernel<DQK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM1);
     if (e != cudaSuccess) return static_cast<int>(e);
-    e = cudaFuncSetAttribute(attn_bwd_dq_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2);
+    e = cudaFuncSetAttribute(attn_bwd_dq_kernel<DQK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
   dim3 g1((max_k + 127) / 128, p.Hq, B);
-  attn_bwd_dkdv_kernel<D><<<g1, FB_THREADS, SMEM1, st>>>(q64, k128, v128, do64, p);
+  attn_bwd_dkdv_kernel<DQK, DV><<<g1, FB_THREADS, SMEM1, st>>>(q64, k128, v128, do64, p);
   dim3 g2((max_q + 127) / 128, p.Hq, B);
-  attn_bwd_dq_kernel<D><<<g2, FB_THREADS, SMEM2, st>>>(q128, k64, v64, do128, p);
+  attn_bwd_dq_kernel<DQK, DV><<<g2, FB_THREADS, SMEM2, st>>>(q128, k64, v64, do128, p);
   return launch_status();
 }
 
@@ -638,19 +653,19 @@ int launch_bwd(const CUtensorMap& q128, const CUtensorMap& q64, const CUtensorMa
 
 using namespace gk;
 
-// do/q/k/v/out: [T, H, D] with token strides given in `strides` = {q, k, v, out} (elements); `d_o` is contiguous
-// ([Tq, Hq, D]).  dq [Tq, Hq, D], dk_h / dv_h [Tk, Hq, D] contiguous outputs; delta [Hq, Tq] scratch.
+// q / k: [T, H, D], v / out: [T, H, Dv] with token strides given in `strides` = {q, k, v, out} (elements); `d_o` is
+// contiguous ([Tq, Hq, Dv]).  dq [Tq, Hq, D], dk_h [Tk, Hq, D], dv_h [Tk, Hq, Dv] contiguous outputs; delta [Hq, Tq]
+// scratch.  Dv = 0 means Dv = D; built geometries: 64 / 64, 128 / 128, 192 / 128.
 // dsink is not computed here: it is -sum_t exp(sink_h - lse[h, t]) * delta[h, t], a reduction of the two arrays this
 // call leaves behind.
-GK_EXPORT int gk_attn_bwd(const void* d_o, const void* q, const void* k, const void* v, const void* out,
-                          const float* lse, float* delta, void* dq, void* dk_h, void* dv_h, const int* cu_q,
-                          const int* cu_k, const float* sinks, float* dsink, int B, int Tq, int Tk, int Hq, int Hk,
-                          int D, int max_q, int max_k, float scale, int causal, int window, void* strides,
-                          void* stream_err) {
-  (void)sinks; (void)dsink;
+GK_EXPORT int gk_attn_bwd_dv(const void* d_o, const void* q, const void* k, const void* v, const void* out,
+                             const float* lse, float* delta, void* dq, void* dk_h, void* dv_h, const int* cu_q,
+                             const int* cu_k, int B, int Tq, int Tk, int Hq, int Hk, int D, int Dv, int max_q,
+                             int max_k, float scale, int causal, int window, void* strides, void* stream_err) {
   const long long* sd = reinterpret_cast<const long long*>(strides);
   void** se = reinterpret_cast<void**>(stream_err);
-  if (D != 64 && D != 128) return -1;
+  if (Dv == 0) Dv = D;
+  if (!((D == 64 && Dv == 64) || (D == 128 && Dv == 128) || (D == 192 && Dv == 128))) return -1;
   if (Hq % Hk) return -2;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(se[0]);
   {
@@ -659,18 +674,18 @@ GK_EXPORT int gk_attn_bwd(const void* d_o, const void* q, const void* k, const v
     if (blocks > 0)
       attn_delta_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(
           reinterpret_cast<const __nv_bfloat16*>(out), sd[3], reinterpret_cast<const __nv_bfloat16*>(d_o),
-          static_cast<long long>(Hq) * D, delta, Tq, Hq, D);
+          static_cast<long long>(Hq) * Dv, delta, Tq, Hq, Dv);
   }
   CUtensorMap q128, q64, k128, k64, v128, v64, do128, do64;
-  const long long dos = static_cast<long long>(Hq) * D;
+  const long long dos = static_cast<long long>(Hq) * Dv;
   if (make_tmap_3d(&q128, q, 2, Tq, Hq, D, sd[0], D, 128, 1, 64, true)) return -3;
   if (make_tmap_3d(&q64, q, 2, Tq, Hq, D, sd[0], D, 64, 1, 64, true)) return -3;
   if (make_tmap_3d(&k128, k, 2, Tk, Hk, D, sd[1], D, 128, 1, 64, true)) return -4;
   if (make_tmap_3d(&k64, k, 2, Tk, Hk, D, sd[1], D, 64, 1, 64, true)) return -4;
-  if (make_tmap_3d(&v128, v, 2, Tk, Hk, D, sd[2], D, 128, 1, 64, true)) return -5;
-  if (make_tmap_3d(&v64, v, 2, Tk, Hk, D, sd[2], D, 64, 1, 64, true)) return -5;
-  if (make_tmap_3d(&do128, d_o, 2, Tq, Hq, D, dos, D, 128, 1, 64, true)) return -6;
-  if (make_tmap_3d(&do64, d_o, 2, Tq, Hq, D, dos, D, 64, 1, 64, true)) return -6;
+  if (make_tmap_3d(&v128, v, 2, Tk, Hk, Dv, sd[2], Dv, 128, 1, 64, true)) return -5;
+  if (make_tmap_3d(&v64, v, 2, Tk, Hk, Dv, sd[2], Dv, 64, 1, 64, true)) return -5;
+  if (make_tmap_3d(&do128, d_o, 2, Tq, Hq, Dv, dos, Dv, 128, 1, 64, true)) return -6;
+  if (make_tmap_3d(&do64, d_o, 2, Tq, Hq, Dv, dos, Dv, 64, 1, 64, true)) return -6;
   FbParams p;
   p.cu_q = cu_q; p.cu_k = cu_k; p.lse = lse; p.delta = delta;
   p.dq = reinterpret_cast<__nv_bfloat16*>(dq);
@@ -678,6 +693,17 @@ GK_EXPORT int gk_attn_bwd(const void* d_o, const void* q, const void* k, const v
   p.dv = reinterpret_cast<__nv_bfloat16*>(dv_h);
   p.tq_total = Tq; p.Hq = Hq; p.Hk = Hk; p.causal = causal; p.window = window; p.scale = scale;
   p.err = reinterpret_cast<int*>(se[1]);
-  if (D == 128) return launch_bwd<128>(q128, q64, k128, k64, v128, v64, do128, do64, p, B, max_q, max_k, st);
-  return launch_bwd<64>(q128, q64, k128, k64, v128, v64, do128, do64, p, B, max_q, max_k, st);
+  if (D == 192) return launch_bwd<192, 128>(q128, q64, k128, k64, v128, v64, do128, do64, p, B, max_q, max_k, st);
+  if (D == 128) return launch_bwd<128, 128>(q128, q64, k128, k64, v128, v64, do128, do64, p, B, max_q, max_k, st);
+  return launch_bwd<64, 64>(q128, q64, k128, k64, v128, v64, do128, do64, p, B, max_q, max_k, st);
+}
+
+GK_EXPORT int gk_attn_bwd(const void* d_o, const void* q, const void* k, const void* v, const void* out,
+                          const float* lse, float* delta, void* dq, void* dk_h, void* dv_h, const int* cu_q,
+                          const int* cu_k, const float* sinks, float* dsink, int B, int Tq, int Tk, int Hq, int Hk,
+                          int D, int max_q, int max_k, float scale, int causal, int window, void* strides,
+                          void* stream_err) {
+  (void)sinks; (void)dsink;
+  return gk_attn_bwd_dv(d_o, q, k, v, out, lse, delta, dq, dk_h, dv_h, cu_q, cu_k, B, Tq, Tk, Hq, Hk, D, 0, max_q, max_k,
+                        scale, causal, window, strides, stream_err);
 }

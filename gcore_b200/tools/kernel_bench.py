@@ -191,6 +191,7 @@ def cmd_attn(argv=None):
     ap.add_argument("--heads", type=int, default=8)
     ap.add_argument("--kv-heads", type=int, default=2)
     ap.add_argument("--dim", type=int, default=128)
+    ap.add_argument("--v-dim", type=int, default=0, help="value head dim when it differs from --dim (192 / 128)")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--bwd", action="store_true")
     ap.add_argument("--sdpa", action="store_true", help="time torch SDPA on the same shape instead")
@@ -199,21 +200,23 @@ def cmd_attn(argv=None):
     from gcore_b200.ops.attention import flash_attn_varlen
     B, L, H, Hk, D = a.batch, a.seq, a.heads, a.kv_heads, a.dim
     T = B * L
+    Dv = a.v_dim or D
     q = torch.randn(T, H, D, device="cuda").bfloat16().requires_grad_(a.bwd)
     k = torch.randn(T, Hk, D, device="cuda").bfloat16().requires_grad_(a.bwd)
-    v = torch.randn(T, Hk, D, device="cuda").bfloat16().requires_grad_(a.bwd)
-    do = torch.randn(T, H, D, device="cuda").bfloat16()
+    v = torch.randn(T, Hk, Dv, device="cuda").bfloat16().requires_grad_(a.bwd)
+    do = torch.randn(T, H, Dv, device="cuda").bfloat16()
     cu = torch.arange(0, T + 1, L, dtype=torch.int32, device="cuda")
-    flops = 4.0 * B * H * L * L * D / 2 * (3.5 if a.bwd else 1.0)
+    # causal: half of (Q K^T + P V) forward; backward adds dP, dV (value width) and dQ, dK (key width) + the recompute
+    flops = B * H * L * L * ((D + Dv) + ((2 * D + Dv) + (D + Dv) if a.bwd else 0))
 
     def run():
         if a.sdpa:
             qq = q.view(B, L, H, D).transpose(1, 2)
             kk = k.view(B, L, Hk, D).transpose(1, 2).repeat_interleave(H // Hk, 1)
-            vv = v.view(B, L, Hk, D).transpose(1, 2).repeat_interleave(H // Hk, 1)
+            vv = torch.nn.functional.pad(v, (0, D - Dv)).view(B, L, Hk, D).transpose(1, 2).repeat_interleave(H // Hk, 1)
             o = torch.nn.functional.scaled_dot_product_attention(qq, kk, vv, is_causal=True)
             if a.bwd:
-                o.backward(do.view(B, L, H, D).transpose(1, 2))
+                o.backward(torch.nn.functional.pad(do, (0, D - Dv)).view(B, L, H, D).transpose(1, 2))
             return
         o = flash_attn_varlen(q, k, v, cu, cu, L, L, causal=True)
         if a.bwd:

@@ -373,10 +373,14 @@ def test_adam_and_sumsq():
     assert abs(s.item() - g.float().pow(2).sum().item()) / s.item() < 1e-3
 
 
-def test_flash_attention_wide_keys_forward_and_backward():
+@pytest.mark.parametrize("bwd", ["native", "flash", "recompute"])
+def test_flash_attention_wide_keys_forward_and_backward(bwd, monkeypatch):
     """192-wide queries / keys with 128-wide values (latent attention expanded to per-head keys): the forward kernel
-    and the gradient path behind it against the fp32 reference under autograd."""
+    and each gradient path behind it (the backward kernels' 192 / 128 instance, the library's flash backward on the
+    saved output, per-sequence recompute) against the fp32 reference under autograd."""
+    from gcore_b200.ops import _lib
     from gcore_b200.ops.attention import attn_varlen_ref, flash_attn_varlen
+    monkeypatch.setenv("GCORE_WIDE_KEY_BWD", bwd)
     torch.manual_seed(3)
     lens = [5, 300, 129, 64, 1000]
     T, H = sum(lens), 6
@@ -398,6 +402,7 @@ def test_flash_attention_wide_keys_forward_and_backward():
     _close(q.grad, qr.grad, atol=1e-2)
     _close(k.grad, kr.grad, atol=1e-2)
     _close(v.grad, vr.grad, atol=1e-2)
+    _lib.check_device_errors()
 
 
 @pytest.mark.parametrize("H,C,dr,lens,head_major", [

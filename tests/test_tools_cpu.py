@@ -1,5 +1,5 @@
-"""DeepSeek-V4 checkpoint format tool: published (fp4 experts, power-of-two scales) <-> fp8 serving layout <-> bf16,
-on a miniature checkpoint written by the test."""
+"""Checkpoint-format and dump tools: the DeepSeek-V4 layouts (published fp4 experts with power-of-two scales <-> fp8
+serving layout <-> bf16) on a miniature checkpoint written by the test, and the per-token dump alignment / comparison."""
 import json
 import os
 import subprocess
@@ -125,3 +125,23 @@ def test_two_ranks_split_the_shards_and_rank0_merges_the_index(tmp_path):
     idx = json.load(open(os.path.join(out, "model.safetensors.index.json")))
     assert len(set(idx["weight_map"].values())) == 2 and not [f for f in os.listdir(out) if f.startswith(".index")]
     assert T.compare_dirs(pub, out)["equal"]
+
+
+def test_token_dump_alignment_and_comparison(tmp_path):
+    """The per-token dump tool: fields brought to the trainer's lengths; two dumps compared field by field."""
+    from gcore_b200.tools import align_dumps as A
+    row = {"prompt_length": 2, "group_id": 0, "reward": 1.0, "tokens": [5, 6, 7, 8, 9],
+           "mask": [0, 1, 1, 1, 0], "logprobs": [0.0, -1.0, -2.0, -3.0, 0.0], "advantages": [0.0, 0.5, 0.5, 0.5, 0.0]}
+    al = A.align_sample(row, pad_multiple=4)
+    assert al["padded_seqlen"] == 8 and al["tokens"] == [5, 6, 7, 8, 9, 0, 0, 0]
+    assert len(al["mask"]) == len(al["logprobs"]) == 7 and al["logprobs"][:4] == [0.0, -1.0, -2.0, -3.0]
+    other = json.loads(json.dumps(row))
+    other["logprobs"][2] = -2.25
+    fa, fb = tmp_path / "a.jsonl", tmp_path / "b.jsonl"
+    fa.write_text(json.dumps(row) + "\n" + json.dumps(row) + "\n")
+    fb.write_text(json.dumps(row) + "\n" + json.dumps(other) + "\n")
+    rep = A.compare_dumps(A.read_dump(str(fa)), A.read_dump(str(fb)))
+    assert not rep["equal"] and rep["logprobs"]["first_difference"] == {"sample": 1, "position": 2, "a": -2.0, "b": -2.25}
+    assert rep["logprobs"]["max_abs_diff"] == 0.25 and rep["advantages"]["first_difference"] is None
+    assert A.compare_dumps(A.read_dump(str(fa)), A.read_dump(str(fa)))["equal"]
+    assert A.main(["compare", "--a", str(fa), "--b", str(fb)]) == 1

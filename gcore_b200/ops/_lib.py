@@ -193,6 +193,7 @@ def _declare_kernels(lib: ctypes.CDLL):
     d("gk_kv_append_rope", [P, P, P, P, P, I, I, I, I, I, I, F, I, P])
     d("gk_paged_decode", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P])
     d("gk_paged_decode_scratch", [I, I, I, I, ctypes.POINTER(L)], None)
+    d("gk_paged_decode_append", [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, F, P])
     d("gk_paged_set_target_ctas", [I], None)
     d("gk_mla_paged_decode", [P, L, L, P, L, L, P, P, P, P, L, L, P, I, I, I, I, I, I, I, F, P])
     d("gk_mla_decode_scratch", [I, I, I, I, ctypes.POINTER(L)], None)

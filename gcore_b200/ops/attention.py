@@ -302,6 +302,44 @@ def paged_decode(q, k_cache, v_cache, block_table, ctx_len, max_ctx, scale=None,
     return out
 
 
+def paged_decode_append_supported(qkv, Hq, Hk, D, rot) -> bool:
+    """True when rotary embedding, cache append and decode attention run as one kernel for these operands."""
+    return (_lib.use_native(qkv) and qkv.dtype == torch.bfloat16 and D == 128 and Hq % Hk == 0 and Hq // Hk <= 8
+            and 0 < rot <= D and rot % 16 == 0 and os.environ.get("GCORE_FUSED_KV_APPEND", "1") != "0"
+            and hasattr(_lib.kernels(), "gk_paged_decode_append"))
+
+
+def paged_decode_append(qkv, pos, slots, k_cache, v_cache, block_table, ctx_len, max_ctx, Hq, Hk, D, theta, rot=None,
+                        scale=None, window=0, sinks=None):
+    """``kv_append_rope`` followed by ``paged_decode`` on the packed ``[T, (Hq + 2 Hk) * D]`` rows of the QKV
+    projection.  One launch where the tensor-core decode kernel serves the shape (the rotation and the append happen
+    inside it: the packed rows are then left unrotated), otherwise the two kernels one after the other."""
+    T = qkv.shape[0]
+    rot = rot or D
+    if paged_decode_append_supported(qkv, Hq, Hk, D, rot):
+        scale = scale if scale is not None else 1.0 / math.sqrt(D)
+        out = torch.empty(T, Hq, D, dtype=qkv.dtype, device=qkv.device)
+        lib = _lib.kernels()
+        need = ctypes.c_longlong()
+        lib.gk_paged_decode_scratch(T, Hq, D, int(max_ctx), ctypes.byref(need))
+        key = qkv.device.index
+        sc = _PD_SCRATCH.get(key)
+        if sc is None or sc.numel() < need.value:
+            sc = torch.empty(max(need.value, 1), dtype=torch.float32, device=qkv.device)
+            _PD_SCRATCH[key] = sc
+        LAUNCHES["attention"] += 1
+        _lib.check(lib.gk_paged_decode_append(_lib.ptr(qkv), _lib.ptr(k_cache), _lib.ptr(v_cache),
+                                              _lib.ptr(block_table), _lib.ptr(ctx_len), _lib.ptr(slots),
+                                              _lib.ptr(sinks), _lib.ptr(out), _lib.ptr(sc), T, Hq, Hk, D,
+                                              k_cache.shape[1], block_table.shape[1], int(max_ctx), float(scale),
+                                              int(window or 0), qkv.stride(0), int(rot), float(theta),
+                                              _lib.stream_ptr()), "paged_decode_append")
+        return out
+    kv_append_rope(qkv, pos, slots, k_cache, v_cache, Hq, Hk, D, theta, rot)
+    q = qkv.view(T, Hq + 2 * Hk, D)[:, :Hq]
+    return paged_decode(q, k_cache, v_cache, block_table, ctx_len, max_ctx, scale=scale, window=window, sinks=sinks)
+
+
 def mla_decode_supported(q_lat, q_rope) -> bool:
     """True when the latent decode kernel serves these operands (bf16 on a GPU, a built geometry)."""
     if not (_lib.use_native(q_lat) and q_lat.dtype == torch.bfloat16 and q_rope.dtype == torch.bfloat16):

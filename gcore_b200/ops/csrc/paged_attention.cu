@@ -224,9 +224,16 @@ __global__ void __launch_bounds__(PD2_WARPS * 32, 3) paged_decode_mma_kernel(
     const __nv_bfloat16* __restrict__ vc, const int* __restrict__ block_table, int max_blocks,
     const int* __restrict__ ctx_len, const float* __restrict__ sinks, __nv_bfloat16* __restrict__ out,
     float* __restrict__ scratch, int Hq, int Hk, int block_size, int window, float scale, int nsplit,
-    int split_tokens) {
+    int split_tokens, int rot, float theta, const int* __restrict__ new_slots, __nv_bfloat16* __restrict__ kc_w,
+    __nv_bfloat16* __restrict__ vc_w) {
+  // rot > 0: q is the query part of packed [q | k | v] rows (row stride q_stride) that have not been rotated yet.
+  // The kernel then does what kv_append_rope_kernel does for its (request, kv head): rotary embedding of the query
+  // heads while they are staged, and, in the CTA whose split ends at the request's newest position, rotation of the
+  // new key, its and the new value's store to cache slot new_slots[b], and their use from shared memory in this step
+  // (the cache row the tile copy fetched for that position is stale and is overwritten in the tile).
   constexpr int D = 128;
   __shared__ __align__(16) uint8_t sq[16 * 256];  // Q tile, 16 rows (heads, zero padded) x 256 B, chunk-swizzled
+  __shared__ float rope_s[64], rope_c[64];
   __shared__ long long slot_buf[PD2_WARPS][32];
   __shared__ float m_all[PD2_WARPS][PD2_G], l_all[PD2_WARPS][PD2_G];
   extern __shared__ __align__(16) uint8_t pd3_dyn[];  // K tiles | V tiles: 32 rows x 256 B per warp
@@ -283,13 +290,49 @@ __global__ void __launch_bounds__(PD2_WARPS * 32, 3) paged_decode_mma_kernel(
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
   if (warp < ntiles) request_tile(warp, tile_slot(warp));
+  const int half = rot >> 1;
+  if (rot > 0) {
+    if (tid < half) {
+      const float inv = __powf(theta, -2.f * tid / rot);
+      sincosf((len - 1) * inv, &rope_s[tid], &rope_c[tid]);
+    }
+    __syncthreads();
+  }
+  // rotate-half pairing on 16-byte chunks: chunk c < half / 8 holds dims 8c .. 8c + 7, its partners sit half / 8
+  // chunks further; dims at or beyond rot pass through
+  auto rotate_pair = [&](uint4& lo, uint4& hi, int c) {
+    __nv_bfloat16* a = reinterpret_cast<__nv_bfloat16*>(&lo);
+    __nv_bfloat16* bb = reinterpret_cast<__nv_bfloat16*>(&hi);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float sn = rope_s[c * 8 + e], cs = rope_c[c * 8 + e];
+      const float x = __bfloat162float(a[e]), y = __bfloat162float(bb[e]);
+      a[e] = __float2bfloat16(x * cs - y * sn);
+      bb[e] = __float2bfloat16(y * cs + x * sn);
+    }
+  };
+  const int hc = half >> 3;   // chunks per rotated half (0 without fused rotation)
   for (int i = tid; i < 16 * 16; i += PD2_WARPS * 32) {
     const int g = i >> 4, c = i & 15;
+    if (rot > 0 && c >= hc && c < 2 * hc) continue;   // written together with its partner chunk
+    const uint4* src = reinterpret_cast<const uint4*>(q + b * q_stride + static_cast<long long>(kvh * G + g) * D);
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (g < G) v = reinterpret_cast<const uint4*>(q + b * q_stride + static_cast<long long>(kvh * G + g) * D)[c];
+    if (rot > 0 && c < hc) {
+      uint4 w = make_uint4(0, 0, 0, 0);
+      if (g < G) {
+        v = src[c];
+        w = src[c + hc];
+        rotate_pair(v, w, c);
+      }
+      *reinterpret_cast<uint4*>(sq + g * 256 + (((c + hc) ^ (g & 15)) << 4)) = w;
+    } else if (g < G) {
+      v = src[c];
+    }
     *reinterpret_cast<uint4*>(sq + g * 256 + ((c ^ (g & 15)) << 4)) = v;
   }
   __syncthreads();
+  // the newest position of the request lies in the last tile of the split that ends at `len`
+  const bool appends = rot > 0 && s1 == len && ntiles > 0;
 
   const int r0 = lane >> 2;        // this thread's accumulator row = head index inside the group
   const int cq = (lane & 3) * 2;   // first of its two columns inside an 8-wide tile
@@ -316,6 +359,33 @@ __global__ void __launch_bounds__(PD2_WARPS * 32, 3) paged_decode_mma_kernel(
       const long long next_slot = tile_slot(t + PD2_WARPS);
       asm volatile("cp.async.wait_group 0;" ::: "memory");
       __syncwarp();
+      if (appends && t == ntiles - 1) {
+        const int row = len - 1 - base_tok;
+        const long long slot = new_slots[b];
+        const __nv_bfloat16* krow = q + b * q_stride + static_cast<long long>(Hq + kvh) * D;
+        const __nv_bfloat16* vrow = q + b * q_stride + static_cast<long long>(Hq + Hk + kvh) * D;
+        if (lane < 16) {          // the key: lanes below hc rotate a chunk pair, lanes of unrotated chunks copy
+          const int c = lane;
+          const bool lead = c < hc, partner = c >= hc && c < 2 * hc;
+          if (!partner) {
+            uint4 v = reinterpret_cast<const uint4*>(krow)[c];
+            if (lead) {
+              uint4 w = reinterpret_cast<const uint4*>(krow)[c + hc];
+              rotate_pair(v, w, c);
+              *reinterpret_cast<uint4*>(kt + row * 256 + (((c + hc) ^ (row & 15)) << 4)) = w;
+              if (slot >= 0) reinterpret_cast<uint4*>(kc_w + (slot * Hk + kvh) * D)[c + hc] = w;
+            }
+            *reinterpret_cast<uint4*>(kt + row * 256 + ((c ^ (row & 15)) << 4)) = v;
+            if (slot >= 0) reinterpret_cast<uint4*>(kc_w + (slot * Hk + kvh) * D)[c] = v;
+          }
+        } else {                  // the value
+          const int c = lane - 16;
+          const uint4 v = reinterpret_cast<const uint4*>(vrow)[c];
+          *reinterpret_cast<uint4*>(vt + row * 256 + ((c ^ (row & 15)) << 4)) = v;
+          if (slot >= 0) reinterpret_cast<uint4*>(vc_w + (slot * Hk + kvh) * D)[c] = v;
+        }
+        __syncwarp();
+      }
       // ---- S = Q K^T : 4 token tiles of 8
       float sc[4][4];
 #pragma unroll
@@ -467,11 +537,12 @@ GK_EXPORT void gk_paged_decode_scratch(int B, int Hq, int D, int max_ctx, long l
 
 // max_ctx bounds every ctx_len[b] (after windowing); it fixes the number of KV splits so the launch shape does
 // not depend on device data (CUDA-graph friendly).
-GK_EXPORT int gk_paged_decode(const void* q, const void* kc, const void* vc, const int* block_table,
-                              const int* ctx_len, const float* sinks, void* out, float* scratch, int B, int Hq,
-                              int Hk, int D, int block_size, int max_blocks, int max_ctx, float scale, int window,
-                              int q_stride, void* stream) {
+static int paged_decode_impl(const void* q, const void* kc, const void* vc, const int* block_table,
+                             const int* ctx_len, const float* sinks, void* out, float* scratch, int B, int Hq,
+                             int Hk, int D, int block_size, int max_blocks, int max_ctx, float scale, int window,
+                             int q_stride, int rot, float theta, const int* new_slots, void* stream) {
   if (D != 128 || Hq % Hk || Hq / Hk > PD_MAX_GROUP) return -1;
+  if (rot > 0 && (Hq / Hk > PD2_G || rot > D || rot % 16 || !new_slots)) return -4;
   if (B == 0) return 0;
   int span = max_ctx;
   if (window > 0 && window < span) span = window;
@@ -501,7 +572,9 @@ GK_EXPORT int gk_paged_decode(const void* q, const void* kc, const void* vc, con
     launch_k(paged_decode_mma_kernel, grid, dim3(PD2_WARPS * 32), PD2_SMEM, st,
         reinterpret_cast<const __nv_bfloat16*>(q), q_stride, reinterpret_cast<const __nv_bfloat16*>(kc),
         reinterpret_cast<const __nv_bfloat16*>(vc), block_table, max_blocks, ctx_len, sinks,
-        reinterpret_cast<__nv_bfloat16*>(out), scratch, Hq, Hk, block_size, window, scale, nsplit, split_tokens);
+        reinterpret_cast<__nv_bfloat16*>(out), scratch, Hq, Hk, block_size, window, scale, nsplit, split_tokens,
+        rot, theta, new_slots, reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(kc)),
+        reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(vc)));
   } else
   paged_decode_kernel<128><<<grid, PD_THREADS, 0, st>>>(
       reinterpret_cast<const __nv_bfloat16*>(q), q_stride, reinterpret_cast<const __nv_bfloat16*>(kc),
@@ -513,4 +586,24 @@ GK_EXPORT int gk_paged_decode(const void* q, const void* kc, const void* vc, con
                                                                   split_tokens);
   }
   return launch_status();
+}
+
+GK_EXPORT int gk_paged_decode(const void* q, const void* kc, const void* vc, const int* block_table,
+                              const int* ctx_len, const float* sinks, void* out, float* scratch, int B, int Hq,
+                              int Hk, int D, int block_size, int max_blocks, int max_ctx, float scale, int window,
+                              int q_stride, void* stream) {
+  return paged_decode_impl(q, kc, vc, block_table, ctx_len, sinks, out, scratch, B, Hq, Hk, D, block_size, max_blocks,
+                           max_ctx, scale, window, q_stride, 0, 0.f, nullptr, stream);
+}
+
+// Decode attention straight on the packed, not yet rotated [q | k | v] rows of the QKV projection: rotary embedding,
+// the append of the new key / value to the cache (slot new_slots[b], negative = no store) and the attention in one
+// launch.  Tensor-core kernel only (GQA groups of up to 8 heads); rot = rotated dims (a multiple of 16, <= D).
+GK_EXPORT int gk_paged_decode_append(void* qkv, void* kc, void* vc, const int* block_table, const int* ctx_len,
+                                     const int* new_slots, const float* sinks, void* out, float* scratch, int B,
+                                     int Hq, int Hk, int D, int block_size, int max_blocks, int max_ctx, float scale,
+                                     int window, int q_stride, int rot, float theta, void* stream) {
+  if (rot <= 0) return -4;
+  return paged_decode_impl(qkv, kc, vc, block_table, ctx_len, sinks, out, scratch, B, Hq, Hk, D, block_size,
+                           max_blocks, max_ctx, scale, window, q_stride, rot, theta, new_slots, stream);
 }

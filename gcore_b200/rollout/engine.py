@@ -32,7 +32,7 @@ import torch.distributed as dist
 from ..core import parallel_state as ps
 from ..models.config import ModelConfig
 from ..ops import _lib, fused
-from ..ops.attention import flash_attn_varlen, kv_append_rope, mla_paged_decode, paged_decode
+from ..ops.attention import flash_attn_varlen, kv_append_rope, mla_paged_decode, paged_decode_append
 from ..ops.gemm import linear_forward
 from ..ops.vocab import apply_top_k_top_p, sample, sample_filtered
 from ..utils import io_counters
@@ -569,11 +569,11 @@ class InferEngine:
                 continue
             qkv = self._lin(h, lw, "qkv_w", lw.qkv_b)
             qkv = self._qk_norm(lw, qkv, B)
-            kv_append_rope(qkv, pos, slots, self.k_cache[li], self.v_cache[li], self.hq, self.hk, self.D,
-                           cfg.rope_theta, cfg.rotary_dim)
-            q = qkv.view(B, self.hq + 2 * self.hk, self.D)[:, :self.hq]
-            o = paged_decode(q, self.k_cache[li], self.v_cache[li], st["block_table"], ctx, self.max_model_len,
-                             window=lw.window, sinks=lw.sinks)
+            # rotary embedding, cache append and attention: one kernel where the tensor-core decode kernel serves
+            # the shape, else the two kernels in sequence
+            o = paged_decode_append(qkv, pos, slots, self.k_cache[li], self.v_cache[li], st["block_table"], ctx,
+                                    self.max_model_len, self.hq, self.hk, self.D, cfg.rope_theta, cfg.rotary_dim,
+                                    window=lw.window, sinks=lw.sinks)
             h, res = self._reduce_norm(self._lin(o.view(B, self.hq * self.D), lw, "o_w"), lw.ln2, res, self.tp > 1)
             x, pending = self._mlp(lw, h, reduce=False)
         hl, _ = self._reduce_norm(x, self.w.final_ln, res, pending)

@@ -378,7 +378,7 @@ def cmd_decode_chain(argv=None):
     ap.add_argument("--pdl", type=int, default=0, help="launch the native kernels with programmatic dependent launch")
     args = ap.parse_args(argv)
     from gcore_b200.ops import _lib, fused
-    from gcore_b200.ops.attention import kv_append_rope, paged_decode
+    from gcore_b200.ops.attention import kv_append_rope, paged_decode, paged_decode_append
     from gcore_b200.ops.gemm import gemm, linear_forward
     dev = torch.device("cuda")
     if args.pdl:
@@ -428,6 +428,10 @@ def cmd_decode_chain(argv=None):
     slots = (bt[:, (ctx_len - 1) // bs] * bs + (ctx_len - 1) % bs).to(torch.int32)
     res["kv_append_rope"] = round(graph_time(
         [lambda: kv_append_rope(qkv, pos, slots, kc[0], vc[0], hq, hk, D, 1e6) for _ in range(24)]), 2)
+    # rotation + append + attention in one launch (GCORE_FUSED_KV_APPEND=0: the two kernels above in sequence)
+    res["paged_decode_append_ctx768"] = round(graph_time(
+        [lambda i=i: paged_decode_append(qkv, pos, slots, kc[i % 4], vc[i % 4], bt, ctx, max_len, hq, hk, D, 1e6)
+         for i in range(24)]), 2)
     # one decoder layer as the rollout engine chains it (without the all-reduces)
     Hd = H
     wq = (torch.randn((hq + 2 * hk) * D, Hd, device=dev) * 0.02).bfloat16()
@@ -440,8 +444,7 @@ def cmd_decode_chain(argv=None):
         a, b, c, d2 = layers[i % 6]
         h, r2 = fused.rmsnorm(x, g, 1e-6, r)
         qkv2 = linear_forward(h, a)
-        kv_append_rope(qkv2, pos, slots, kc[i % 4], vc[i % 4], hq, hk, D, 1e6)
-        o = paged_decode(qkv2.view(T, hq + 2 * hk, D)[:, :hq], kc[i % 4], vc[i % 4], bt, ctx, max_len)
+        o = paged_decode_append(qkv2, pos, slots, kc[i % 4], vc[i % 4], bt, ctx, max_len, hq, hk, D, 1e6)
         y = linear_forward(o.view(T, hq * D), b)
         h2, _ = fused.rmsnorm(y, g, 1e-6, r2)
         return linear_forward(fused.swiglu(linear_forward(h2, c)), d2)

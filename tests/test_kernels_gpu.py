@@ -440,6 +440,48 @@ def test_mla_paged_decode(H, C, dr, lens, head_major):
         _lib.kernels().gk_mla_set_target_ctas(296)
 
 
+@pytest.mark.parametrize("rot,window,use_sinks", [(128, 0, False), (64, 96, True)])
+def test_paged_decode_with_fused_rotation_and_append(rot, window, use_sinks):
+    """Rotary embedding + cache append + decode attention in one launch against the two kernels in sequence: same
+    attention output, same cache rows, for one KV split per request and for several (the newest position is handled
+    by the split that ends at the context length); full and partial rotary width."""
+    from gcore_b200.ops import _lib
+    from gcore_b200.ops.attention import kv_append_rope, paged_decode, paged_decode_append, paged_decode_append_supported
+    torch.manual_seed(12)
+    B, Hq, Hk, D, bs = 6, 28, 4, 128, 16
+    lens = [1, 17, 300, 513, 64, 0]                    # context including the new token; the last request is inactive
+    max_blocks, nblocks = 40, 320
+    kc = _rand(nblocks, bs, Hk, D, scale=0.5)
+    vc = _rand(nblocks, bs, Hk, D, scale=0.5)
+    table = torch.randperm(nblocks, device=DEV)[:B * max_blocks].view(B, max_blocks).to(torch.int32)
+    ctx = torch.tensor(lens, device=DEV, dtype=torch.int32)
+    pos = (ctx - 1).clamp_min(0)
+    slots = torch.where(ctx > 0, table.gather(1, (pos // bs).long()[:, None]).squeeze(1) * bs + pos % bs,
+                        torch.full_like(pos, -1)).to(torch.int32)
+    qkv = _rand(B, (Hq + 2 * Hk) * D, scale=0.5)
+    sinks = torch.randn(Hq, device=DEV) if use_sinks else None
+    assert paged_decode_append_supported(qkv, Hq, Hk, D, rot)
+    # reference: the two kernels on copies
+    qkv_r, kc_r, vc_r = qkv.clone(), kc.clone(), vc.clone()
+    kv_append_rope(qkv_r, pos, slots, kc_r, vc_r, Hq, Hk, D, 1e6, rot)
+    want = paged_decode(qkv_r.view(B, Hq + 2 * Hk, D)[:, :Hq], kc_r, vc_r, table, ctx, max(lens), window=window,
+                        sinks=sinks)
+    try:
+        for target in (1, 444, 4000):
+            _lib.kernels().gk_paged_set_target_ctas(target)
+            kc_f, vc_f, qkv_f = kc.clone(), vc.clone(), qkv.clone()
+            got = paged_decode_append(qkv_f, pos, slots, kc_f, vc_f, table, ctx, max(lens), Hq, Hk, D, 1e6, rot,
+                                      window=window, sinks=sinks)
+            _close(got[:5], want[:5], atol=2e-2)
+            assert torch.equal(vc_f, vc_r)                                  # same rows appended, nothing else touched
+            assert (kc_f != kc).any(-1).any(-1).flatten().sum() == 5         # one key row per active request
+            _close(kc_f, kc_r, atol=1e-2)                                    # rotated keys: equal up to fp contraction
+            assert torch.equal(qkv_f, qkv)                                   # the packed rows stay unrotated
+    finally:
+        _lib.kernels().gk_paged_set_target_ctas(444)
+    _lib.check_device_errors()
+
+
 @pytest.mark.parametrize("window,use_sinks", [(0, False), (96, True)])
 def test_paged_decode_and_kv_append(window, use_sinks):
     from gcore_b200.ops.attention import kv_append_rope, paged_decode

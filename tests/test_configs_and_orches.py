@@ -177,6 +177,19 @@ def test_recipe_variants_change_what_they_say_and_plug_ins_resolve():
     smp = [{"group_id": 0, "rewards": torch.tensor(r), "mask": torch.tensor([0.0, 1.0, 1.0])} for r in (1.0, 0.0, 0.0)]
     out = fn(smp, c.ppo)
     assert out[0]["advantages"].tolist() == [0.0, 1.0, 1.0] and out[1]["advantages"].tolist() == [0.0, -0.5, -0.5]
+    # policy-loss plug-in: uncertain tokens with a positive advantage get the wider upper clip
+    from gcore_b200.loss.policy_loss import LossInput
+    c = load_config(RlConfig, y("rl_custom_loss.yaml"), [])
+    loss = import_from_path(os.path.join(ROOT, c.ppo.loss_func_py_path), c.ppo.loss_func_fn_name)
+    lp = torch.tensor([-3.0, -0.5, -3.0], requires_grad=True)
+    lo = loss(c.ppo, LossInput(lp, torch.tensor([-3.5, -0.9, -3.5]), None, None, torch.tensor([1.0, 1.0, -1.0]),
+                               torch.ones(3), torch.zeros(3, dtype=torch.int32), 1))
+    assert torch.allclose(lo.token_loss, torch.tensor([-1.4, -1.2, 1.6487]), atol=1e-4)
+    assert lo.metrics["widened_clip_frac"].tolist() == [1.0, 3.0]
+    gen = import_from_path(os.path.join(ROOT, "tasks", "math_rl", "gen_rm_reward.py"), "parse_verdict")
+    prompt = import_from_path(os.path.join(ROOT, "tasks", "math_rl", "gen_rm_reward.py"), "build_judge_prompt")
+    assert gen("Verdict: wrong. On reflection, Verdict: Correct") == 1.0 and gen("unsure") == 0.0
+    assert "Reference answer: 42" in prompt({"prompt_text": "6 x 7?", "response_text": "42", "answer": "42"})
 
 
 def test_recipe_includes_merge_in_order_and_reject_cycles(tmp_path):

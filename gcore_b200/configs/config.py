@@ -502,6 +502,8 @@ class TrainingConfig(MappingMixin):
     use_linear_ce: bool = True
     linear_ce_backend: str = "separate"
     ce_compaction: bool = False
+    # supervised objective: cross_entropy | square_averaging_cross_entropy (a token of a sample with N answer tokens
+    # weighs 1 / sqrt(N), normalised by the global sum of sqrt(N))
     loss_func: str = "cross_entropy"
     cross_entropy_loss_fusion: bool = True
     per_token_loss: bool = True
@@ -561,6 +563,9 @@ class TrainingConfig(MappingMixin):
             self.training_backend = "native"   # the Megatron-style ZeRO-1 / TP / PP / CP / EP engine of this package
         if self.training_backend not in ("native", "nccl_eager", "fsdp2"):
             raise ConfigError(f"unknown training_backend {self.training_backend}")
+        if self.loss_func not in ("cross_entropy", "square_averaging_cross_entropy"):
+            raise ConfigError(f"training.loss_func must be cross_entropy|square_averaging_cross_entropy, "
+                              f"got {self.loss_func}")
         if self.sampling_keep_n is None:
             self.sampling_keep_n = self.sampling_repeat_n
         if self.sampling_keep_n > self.sampling_repeat_n:

@@ -551,8 +551,10 @@ class TrainingEngine:
         return samples
 
     # ------------------------------------------------------------------ shared step machinery
-    def _global_counts(self, samples, per_token: bool) -> float:
-        if per_token:
+    def _global_counts(self, samples, per_token: bool, sqrt_lengths: bool = False) -> float:
+        if sqrt_lengths:   # square-averaging normaliser: sum over sequences of sqrt(answer tokens)
+            n = sum(float(torch.as_tensor(s["mask"] if "mask" in s else s["loss_mask"]).sum()) ** 0.5 for s in samples)
+        elif per_token:
             n = sum(float(torch.as_tensor(s["mask"] if "mask" in s else s["loss_mask"]).sum()) for s in samples)
         else:
             n = float(len(samples))
@@ -628,10 +630,12 @@ class TrainingEngine:
             if "mask" not in s and "loss_mask" not in s:
                 from ..core.packing import response_mask
                 s["mask"] = response_mask(int(s.get("prompt_length", 0)), len(s["tokens"]))
-        denom = self._global_counts(samples, per_token)
+        square_avg = getattr(self.train_cfg, "loss_func", "cross_entropy") == "square_averaging_cross_entropy"
+        denom = self._global_counts(samples, per_token, sqrt_lengths=square_avg)
         acc = {"lm_loss": torch.zeros(2, device=self.device)}
         with backend_scope(self.backend):
             if self._dcp is not None:
+                assert not square_avg, "square-averaging weights need whole sequences on a rank (no dynamic CP)"
                 samples, batches = self._dynamic_cp_plan(samples, forward_only=False)
             else:
                 batches = self._microbatches(samples)
@@ -639,7 +643,11 @@ class TrainingEngine:
 
             def step(mb, hidden, aux):
                 lp, _ = self._logprob_entropy(self.model, hidden, mb.targets, False, mb.loss_mask)
-                w = PL.aggregation_weights(mb.loss_mask, mb.seq_ids, mb.num_seqs + 1, per_token, denom)
+                if square_avg:
+                    assert mb.cp_ctx is None, "square-averaging weights need whole sequences on a rank"
+                    w = PL.square_averaging_weights(mb.loss_mask, mb.seq_ids, mb.num_seqs + 1, denom)
+                else:
+                    w = PL.aggregation_weights(mb.loss_mask, mb.seq_ids, mb.num_seqs + 1, per_token, denom)
                 loss = -(lp * w).sum()
                 if aux is not None:
                     loss = loss + aux * aux_scale

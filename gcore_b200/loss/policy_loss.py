@@ -408,6 +408,14 @@ def aggregation_weights(mask, seq_ids, num_seqs, per_token: bool, denom: float):
     return mask / lens[seq_ids.long()] / max(denom, 1.0)
 
 
+def square_averaging_weights(mask, seq_ids, num_seqs, denom: float):
+    """Weights of the square-averaging cross-entropy: a token of a sequence with N answer tokens counts 1 / sqrt(N),
+    normalised by the global sum of sqrt(N) over sequences (``denom``), so that short answers are not drowned by
+    long ones (gpatch_v4/training_backend/loss_factory.py:3199-3290)."""
+    lens = _seg_sum(mask, seq_ids, num_seqs).clamp_min(1.0)
+    return mask / lens.sqrt()[seq_ids.long()] / max(denom, 1.0)
+
+
 def value_loss(values, old_values, returns, mask_w, clip: Optional[float]):
     """0.5 * max((clip(V) - R)^2, (V - R)^2) (gpatch_v4/training_backend/loss_factory.py:3355-3371)."""
     l1 = (values - returns) ** 2

@@ -136,3 +136,47 @@ def test_checkpoint_stage_converters(tmp_path):
     back = CheckpointReader(str(tmp_path / "back" / "iter_0000000"))
     for key in ("embedding.word_embeddings.weight", "decoder.layers.self_attention.linear_qkv.weight", k):
         assert torch.equal(back.full_tensor(key), src.full_tensor(key)), key
+
+
+def test_square_averaging_cross_entropy_weights_and_gradient():
+    """``training.loss_func: square_averaging_cross_entropy``: the gradient equals that of
+    sum_i sum_t nll_it / sqrt(N_i) / sum_i sqrt(N_i), whatever the micro-batching."""
+    from gcore_b200.configs.config import OptimizerConfig, PolicyConfig, TrainingConfig
+    from gcore_b200.engine.train_engine import TrainingEngine
+    from gcore_b200.loss import policy_loss as PL
+    from gcore_b200.models.config import get_preset
+    mask = torch.tensor([1.0, 1, 1, 1, 0, 1, 0, 0])
+    seq = torch.tensor([0, 0, 0, 0, 0, 1, 1, 2], dtype=torch.int32)
+    w = PL.square_averaging_weights(mask, seq, 3, denom=3.0)          # sqrt(4) + sqrt(1) = 3
+    assert torch.allclose(w, torch.tensor([1 / 6, 1 / 6, 1 / 6, 1 / 6, 0, 1 / 3, 0, 0]))
+    g = torch.Generator().manual_seed(0)
+    samples = []
+    for n_ans in (4, 64, 16, 1):
+        t = torch.randint(3, 1024, (80,), generator=g)
+        m = torch.zeros(80)
+        m[10:10 + n_ans] = 1.0
+        samples.append({"tokens": t, "loss_mask": m})
+    grads = []
+    for mbs in (4, 1):
+        pc = PolicyConfig(recompute="none", without_ref=True)
+        oc = OptimizerConfig(lr=0.0, lr_decay_style="constant", weight_decay=0.0, max_grad_norm=0.0)
+        tc = TrainingConfig(train_mbs=mbs, train_gbs=4, loss_func="square_averaging_cross_entropy")
+        eng = TrainingEngine(pc, oc, tc, model_cfg=get_preset("tiny_llama", dtype="float32"))
+        eng.setup_model_and_get_optimizer(seed=7)
+        eng.finetune_step([dict(s) for s in samples])
+        grads.append(dict((n, p.main_grad.clone()) for n, p in eng.model.named_parameters()))
+        model = eng.model
+    name = "decoder.layers.0.mlp.linear_fc1.weight"
+    assert torch.allclose(grads[0][name], grads[1][name], atol=1e-6)
+    # direct definition on the same (unchanged, lr = 0) model
+    eng.ddp.zero_grad_buffer()      # autograd hooks route every gradient into the fp32 main_grad buffers
+    total, norm = 0.0, sum(float(s["loss_mask"].sum()) ** 0.5 for s in samples)
+    for s in samples:
+        n = s["tokens"].numel()
+        h, _ = model(s["tokens"], torch.arange(n, dtype=torch.int32), torch.tensor([0, n], dtype=torch.int32), n)
+        lp = torch.log_softmax(model.logits(h).float(), -1)[:-1].gather(-1, s["tokens"][1:, None]).squeeze(-1)
+        m = s["loss_mask"][:-1]
+        total = total - (lp * m).sum() / m.sum().sqrt() / norm
+    total.backward()
+    ref = dict(model.named_parameters())[name].main_grad
+    assert torch.allclose(grads[0][name], ref, atol=2e-5), float((grads[0][name] - ref).abs().max())

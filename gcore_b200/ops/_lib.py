@@ -161,6 +161,7 @@ def _declare_kernels(lib: ctypes.CDLL):
     d("gk_ep_plan", [P, P, I, I, I, I, I, ctypes.c_uint, P, P, P, P, P])
     d("gk_ep_push", [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, L, P])
     d("gk_ep_copy_rows", [P, P, P, I, P])
+    d("gk_ep_local_plan", [P, I, I, I, P, P, P, P, P, P])
     d("gk_ep_pull", [P, P, P, P, P, I, I, I, I, L, P])
     d("gk_peer_copy_2d", [P, L, P, L, L, I, P])
     d("gk_set_pdl", [I], None)

@@ -227,9 +227,51 @@ __global__ void __launch_bounds__(256) copy_rows_bounded_kernel(const uint4* __r
     dst[i] = src[i];
 }
 
+// Routing bookkeeping of one rank for a small batch (decode steps): per expert the number of (token, k) pairs that
+// chose it, and for every pair its rank among the pairs of the same expert in (token, k) order - what a stable sort
+// by expert plus a histogram would give, in one launch instead of a dozen.  One CTA; thread e walks the n choices in
+// shared memory for expert e (n <= LOCAL_PLAN_MAX: a few hundred pairs in a decode step), so every position is
+// written by exactly one thread and the order is the input order.  Also clears the per-call outputs of the
+// cross-rank plan (offsets, tot_local) so that the caller needs no memset.
+constexpr int LOCAL_PLAN_MAX = 8192;
+__global__ void ep_local_plan_kernel(const long long* __restrict__ idx, int n, int E, int* __restrict__ idx32,
+                                     int* __restrict__ pos, int* __restrict__ cnt, int* __restrict__ offsets,
+                                     int* __restrict__ tot_local, int E_local) {
+  __shared__ short s_e[LOCAL_PLAN_MAX];
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = static_cast<int>(idx[i]);
+    s_e[i] = static_cast<short>(e);
+    idx32[i] = e;
+  }
+  for (int i = threadIdx.x; i <= E_local; i += blockDim.x) {
+    offsets[i] = 0;
+    if (i < E_local) tot_local[i] = 0;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int c = 0;
+    for (int i = 0; i < n; ++i) {
+      if (s_e[i] == e) pos[i] = c++;
+    }
+    cnt[e] = c;
+  }
+}
+
 }  // namespace gke
 
 using namespace gke;
+
+// idx: int64 [n] expert of every (token, k) pair.  Outputs: idx32 [n], pos [n], cnt [E] (int32), and zeroed
+// offsets [E_local + 1] / tot_local [E_local].  n <= 8192, E <= 1024.
+GK_EXPORT int gk_ep_local_plan(const long long* idx, int n, int E, int E_local, int* idx32, int* pos, int* cnt,
+                               int* offsets, int* tot_local, void* stream) {
+  if (n > LOCAL_PLAN_MAX || E > 32767 || n < 0) return -1;
+  int threads = 32;
+  while (threads < E && threads < 1024) threads <<= 1;
+  ep_local_plan_kernel<<<1, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(idx, n, E, idx32, pos, cnt, offsets,
+                                                                                  tot_local, E_local);
+  return gk::launch_status();
+}
 
 GK_EXPORT int gk_ep_copy_rows(const void* src, void* dst, const int* n_rows, int H, void* stream) {
   if (H % 8) return -1;

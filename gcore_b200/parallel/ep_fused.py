@@ -10,6 +10,7 @@ of each is the other's kernel (scaled push / unweighted pull).  No host synchron
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import os
 from typing import Optional
@@ -84,17 +85,32 @@ class FusedEP:
             raise RuntimeError(f"expert-parallel buffers were sized for {self.max_tokens} tokens per micro-batch, got "
                                f"{T}; set GCORE_EP_MAX_TOKENS")
         flat = idx.reshape(-1)
-        # histogram without a host synchronisation (bincount sizes its output on the host)
-        cnt = torch.zeros(self.E, dtype=torch.int64, device=flat.device).scatter_add_(0, flat, torch.ones_like(flat))
-        order = torch.argsort(flat, stable=True)
-        starts = cnt.cumsum(0) - cnt
-        pos = torch.empty_like(flat)
-        pos[order] = torch.arange(flat.numel(), device=flat.device) - starts[flat[order]]
-        st = dict(T=T, K=K, idx=flat.to(torch.int32), pos=pos.to(torch.int32), cnt=cnt.to(torch.int32),
-                  send_base=torch.empty(self.E, dtype=torch.int32, device=self.device),
-                  offsets=torch.zeros(self.E_local + 1, dtype=torch.int32, device=self.device),
-                  tot_local=torch.zeros(self.E_local, dtype=torch.int32, device=self.device),
-                  dst_row=torch.empty(T * K, dtype=torch.int32, device=self.device))
+        n = flat.numel()
+        if n <= LOCAL_PLAN_MAX and flat.dtype == torch.int64 and hasattr(_lib.kernels(), "gk_ep_local_plan"):
+            # small batches (decode steps): histogram, in-expert positions and the cleared per-call outputs from one
+            # single-CTA kernel; all per-call int32 arrays are slices of one allocation
+            flat = flat.contiguous()
+            buf = torch.empty(3 * n + 2 * self.E + 2 * self.E_local + 1, dtype=torch.int32, device=self.device)
+            o = [0, n, 2 * n, 3 * n, 3 * n + self.E, 3 * n + 2 * self.E, 3 * n + 2 * self.E + self.E_local + 1]
+            idx32, pos, dst_row, cnt, send_base, offsets, tot_local = (buf[a:b] for a, b in zip(o, o[1:] + [buf.numel()]))
+            LAUNCHES["ep"] += 1
+            _lib.check(_lib.kernels().gk_ep_local_plan(_lib.ptr(flat), n, self.E, self.E_local, _lib.ptr(idx32),
+                                                       _lib.ptr(pos), _lib.ptr(cnt), _lib.ptr(offsets),
+                                                       _lib.ptr(tot_local), _lib.stream_ptr()), "ep_local_plan")
+            st = dict(T=T, K=K, idx=idx32, pos=pos, cnt=cnt, send_base=send_base, offsets=offsets, tot_local=tot_local,
+                      dst_row=dst_row, _keep=(flat, buf))
+        else:
+            # histogram without a host synchronisation (bincount sizes its output on the host)
+            cnt = torch.zeros(self.E, dtype=torch.int64, device=flat.device).scatter_add_(0, flat, torch.ones_like(flat))
+            order = torch.argsort(flat, stable=True)
+            starts = cnt.cumsum(0) - cnt
+            pos = torch.empty_like(flat)
+            pos[order] = torch.arange(flat.numel(), device=flat.device) - starts[flat[order]]
+            st = dict(T=T, K=K, idx=flat.to(torch.int32), pos=pos.to(torch.int32), cnt=cnt.to(torch.int32),
+                      send_base=torch.empty(self.E, dtype=torch.int32, device=self.device),
+                      offsets=torch.zeros(self.E_local + 1, dtype=torch.int32, device=self.device),
+                      tot_local=torch.zeros(self.E_local, dtype=torch.int32, device=self.device),
+                      dst_row=torch.empty(T * K, dtype=torch.int32, device=self.device))
         LAUNCHES["ep"] += 1
         if self.dev_epochs:
             _lib.check(_lib.kernels().gk_ep_plan_dev(_lib.ptr(st["cnt"]), self.plan_ptrs, self.rank, self.ep, self.E, SEG,
@@ -182,6 +198,26 @@ class _Combine(torch.autograd.Function):
 _INSTANCES = {}
 
 
+LOCAL_PLAN_MAX = 8192      # (token, k) pairs up to which the single-kernel local plan is used
+_SMALL = {"tokens": 0}
+
+
+@contextlib.contextmanager
+def small_batch(tokens: int):
+    """Inside this context expert-parallel layers with at most ``tokens`` tokens per rank use an instance whose peer
+    buffers (and with them the row capacity the grouped expert GEMMs and the activation between them run over) are
+    sized for ``tokens`` tokens in the worst case of every rank sending all its pairs to one rank, instead of for a
+    training micro-batch.  The rollout engine's decode steps enter it with their static batch size, which is the
+    same on every rank of the group; a decode step then moves a few thousand rows of capacity per layer, not a few
+    hundred thousand."""
+    prev = _SMALL["tokens"]
+    _SMALL["tokens"] = int(tokens)
+    try:
+        yield
+    finally:
+        _SMALL["tokens"] = prev
+
+
 def get_fused_ep(group, hidden: int, num_experts: int, top_k: int, tokens: int, x: torch.Tensor) -> Optional[FusedEP]:
     """The per-group instance, created on first use (a collective over the group).  The choice between this path and
     the NCCL one depends only on values that are equal on every rank."""
@@ -191,10 +227,15 @@ def get_fused_ep(group, hidden: int, num_experts: int, top_k: int, tokens: int, 
         return None
     if not hasattr(_lib.kernels(), "gk_ep_plan"):
         return None
-    key = (id(group), hidden, num_experts, top_k)
+    small = _SMALL["tokens"] if 0 < tokens <= _SMALL["tokens"] else 0
+    key = (id(group), hidden, num_experts, top_k, small)
     if key not in _INSTANCES:
-        max_tokens = int(os.environ.get("GCORE_EP_MAX_TOKENS", "0")) or max(16384, 2 * tokens)
-        _INSTANCES[key] = FusedEP(group, hidden, num_experts, top_k, max_tokens, device=x.device)
+        if small:
+            _INSTANCES[key] = FusedEP(group, hidden, num_experts, top_k, small, device=x.device,
+                                      capacity_factor=float(dist.get_world_size(group)))
+        else:
+            max_tokens = int(os.environ.get("GCORE_EP_MAX_TOKENS", "0")) or max(16384, 2 * tokens)
+            _INSTANCES[key] = FusedEP(group, hidden, num_experts, top_k, max_tokens, device=x.device)
     return _INSTANCES[key]
 
 

@@ -535,7 +535,14 @@ class InferEngine:
         if pdl:
             _lib.kernels().gk_set_pdl(1)
         try:
-            self._decode_layers(st)
+            if self.ep_group is not None:
+                # expert-parallel layers of a decode step run on peer buffers sized for the (static, rank-uniform)
+                # decode batch instead of a training micro-batch
+                from ..parallel.ep_fused import small_batch
+                with small_batch(st["tokens"].numel()):
+                    self._decode_layers(st)
+            else:
+                self._decode_layers(st)
         finally:
             if pdl:
                 _lib.kernels().gk_set_pdl(0)

@@ -924,3 +924,27 @@ def test_rope_table_kernel_matches_reference():
     _close(y, fused.rope_ref(x.float(), tab, 1e6, D), rtol=1e-2, atol=1e-2)
     back = fused.rope_inplace(y.clone(), tab, 1e6, D, False, True)
     _close(back, x, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("T,K,E,ep", [(64, 8, 128, 8), (1, 2, 8, 2), (500, 6, 256, 4), (1024, 8, 64, 2)])
+def test_expert_parallel_local_plan_kernel_matches_sort_and_histogram(T, K, E, ep):
+    """The single-kernel routing bookkeeping of small batches: per-expert counts and, for every (token, k) pair, its
+    rank among the pairs of the same expert in input order = what a stable sort by expert gives."""
+    from gcore_b200.ops import _lib
+    torch.manual_seed(40)
+    flat = torch.randint(0, E, (T * K,), device=DEV, dtype=torch.int64)
+    n, El = T * K, E // ep
+    idx32 = torch.empty(n, dtype=torch.int32, device=DEV)
+    pos = torch.full((n,), -1, dtype=torch.int32, device=DEV)
+    cnt = torch.full((E,), -1, dtype=torch.int32, device=DEV)
+    offsets = torch.full((El + 1,), 7, dtype=torch.int32, device=DEV)
+    tot = torch.full((El,), 7, dtype=torch.int32, device=DEV)
+    _lib.check(_lib.kernels().gk_ep_local_plan(_lib.ptr(flat), n, E, El, _lib.ptr(idx32), _lib.ptr(pos), _lib.ptr(cnt),
+                                               _lib.ptr(offsets), _lib.ptr(tot), _lib.stream_ptr()), "local_plan")
+    want_cnt = torch.bincount(flat, minlength=E)
+    order = torch.argsort(flat, stable=True)
+    starts = want_cnt.cumsum(0) - want_cnt
+    want_pos = torch.empty_like(flat)
+    want_pos[order] = torch.arange(n, device=DEV) - starts[flat[order]]
+    assert torch.equal(cnt.long(), want_cnt) and torch.equal(pos.long(), want_pos) and torch.equal(idx32.long(), flat)
+    assert not offsets.any() and not tot.any()

@@ -241,7 +241,8 @@ class Experts(nn.Module):
         h = grouped_linear(x_perm, self.linear_fc1.weight, offsets, self.precision, self._fp8_cache[0])
         if self.lora_fc1 is not None:
             h = h + self.lora_fc1(x_perm, offsets).to(h.dtype)
-        h = fused.swiglu(h)
+        # offsets[-1] = rows in use (the buffer is sized for the worst case): without autograd only those are activated
+        h = fused.swiglu(h, n_rows=offsets[-1:] if offsets.dtype == torch.int32 else None)
         y = grouped_linear(h, self.linear_fc2.weight, offsets, self.precision, self._fp8_cache[1])
         if self.lora_fc2 is not None:
             y = y + self.lora_fc2(h, offsets).to(y.dtype)

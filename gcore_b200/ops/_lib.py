@@ -174,7 +174,9 @@ def _declare_kernels(lib: ctypes.CDLL):
     d("gk_rmsnorm_bwd_parts", [I])
     d("gk_rmsnorm_bwd", [P, P, P, P, P, P, P, P, I, I, I, P])
     d("gk_rope", [P, P, I, I, I, I, L, F, I, I, P])
+    d("gk_qk_headnorm", [P, P, P, L, I, I, I, L, F, P])
     d("gk_swiglu_fwd", [P, P, L, I, P])
+    d("gk_swiglu_fwd_rows", [P, P, L, I, P, P])
     d("gk_swiglu_bwd", [P, P, P, L, I, P])
     d("gk_adam", [P, P, P, P, I, P, L, F, F, F, F, F, I, P, F, P])
     d("gk_sumsq", [P, I, L, P, P])

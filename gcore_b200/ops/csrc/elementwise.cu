@@ -241,16 +241,38 @@ __global__ void rope_table_kernel(__nv_bfloat16* __restrict__ x, const float* __
 
 // ------------------------------------------------------------------------------------------ SwiGLU
 // in [T, 2F] = [gate | up]; out [T, F] = silu(gate) * up
+// A thread's (row, 8-wide column vector) pair advances by the grid stride without a division per element: one 64-bit
+// division at entry, then carries (a division per element made the kernel issue-bound: 99 us for 9216 x 1536 outputs).
+struct RowColIter {
+  long long t;
+  int i, di, nv;
+  long long dt;
+  __device__ RowColIter(int nv_) : nv(nv_) {
+    const long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    const long long step = static_cast<long long>(gridDim.x) * blockDim.x;
+    t = idx / nv;
+    i = static_cast<int>(idx - t * nv);
+    dt = step / nv;
+    di = static_cast<int>(step - dt * nv);
+  }
+  __device__ void next() {
+    t += dt;
+    i += di;
+    if (i >= nv) { i -= nv; ++t; }
+  }
+};
+
+// n_rows (device, optional): rows at or beyond *n_rows are left untouched (expert-sorted buffers sized for the worst
+// case carry a device-side count of the rows in use).
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, long long T,
-                                  int F) {
+                                  int F, const int* __restrict__ n_rows) {
   pdl_launch_dependents();
   pdl_wait();
   const int nv = F >> 3;
-  const long long total = T * nv;
-  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
-       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long t = idx / nv;
-    const int i = static_cast<int>(idx - t * nv);
+  if (n_rows && *n_rows < T) T = *n_rows;
+  for (RowColIter it(nv); it.t < T; it.next()) {
+    const long long t = it.t;
+    const int i = it.i;
     const bf16x8* row = reinterpret_cast<const bf16x8*>(in + t * 2 * F);
     float g[8], u[8];
     unpack8(row[i], g);
@@ -263,11 +285,9 @@ __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfl
 __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ in,
                                   __nv_bfloat16* __restrict__ din, long long T, int F) {
   const int nv = F >> 3;
-  const long long total = T * nv;
-  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
-       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long t = idx / nv;
-    const int i = static_cast<int>(idx - t * nv);
+  for (RowColIter it(nv); it.t < T; it.next()) {
+    const long long t = it.t;
+    const int i = it.i;
     const bf16x8* row = reinterpret_cast<const bf16x8*>(in + t * 2 * F);
     float g[8], u[8], d[8], dg[8], du[8];
     unpack8(row[i], g);
@@ -365,6 +385,55 @@ GK_EXPORT int gk_rmsnorm_fwd(const void* x, const void* res, const void* w, void
   return launch_status();
 }
 
+// Per-head RMSNorm of the query and key heads of packed [q | k | v] rows, in place (decode / prefill of models with
+// q / k layer norms): one warp per (token, head), D <= 256.  Replaces two norm launches over reshaped copies and the
+// copies back into the packed rows.
+__global__ void qk_headnorm_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ wq,
+                                   const __nv_bfloat16* __restrict__ wk, long long T, int Hq, int Hk, int D,
+                                   long long stride_t, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const long long warp = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const int heads = Hq + Hk;
+  const int nv = D >> 3;
+  for (long long w = warp; w < T * heads; w += nwarps) {
+    const long long t = w / heads;
+    const int h = static_cast<int>(w - t * heads);
+    bf16x8* row = reinterpret_cast<bf16x8*>(qkv + t * stride_t + static_cast<long long>(h) * D);
+    const bf16x8* g = reinterpret_cast<const bf16x8*>(h < Hq ? wq : wk);
+    float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float ss = 0.f;
+    if (lane < nv) {
+      unpack8(row[lane], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffff, ss, off);
+    const float rstd = rsqrtf(ss / D + eps);
+    if (lane < nv) {
+      float gw[8];
+      unpack8(g[lane], gw);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = f[j] * rstd * gw[j];
+      row[lane] = pack8(f);
+    }
+  }
+}
+
+GK_EXPORT int gk_qk_headnorm(void* qkv, const void* wq, const void* wk, long long T, int Hq, int Hk, int D,
+                             long long stride_t, float eps, void* stream) {
+  if (D % 8 || D > 256 || stride_t % 8) return -1;
+  if (T == 0) return 0;
+  launch_k(qk_headnorm_kernel, dim3(grid_for(T * (Hq + Hk) * 32, 256)), dim3(256), 0,
+           reinterpret_cast<cudaStream_t>(stream), reinterpret_cast<__nv_bfloat16*>(qkv),
+           reinterpret_cast<const __nv_bfloat16*>(wq), reinterpret_cast<const __nv_bfloat16*>(wk), T, Hq, Hk, D, stride_t,
+           eps);
+  return launch_status();
+}
+
 GK_EXPORT int gk_rmsnorm_bwd_parts(int T) {
   const int cap = sm_count() * 2;
   return T < cap ? (T > 0 ? T : 1) : cap;
@@ -405,12 +474,21 @@ GK_EXPORT int gk_rope_table(void* x, const float* cs, const float* sn, int T, in
   return launch_status();
 }
 
-GK_EXPORT int gk_swiglu_fwd(const void* in, void* out, long long T, int F, void* stream) {
+static int swiglu_fwd_launch(const void* in, void* out, long long T, int F, const int* n_rows, void* stream) {
   if (F % 8) return -1;
   if (T == 0) return 0;
   launch_k(swiglu_fwd_kernel, dim3(grid_for(T * (F / 8), 256)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
-      reinterpret_cast<const __nv_bfloat16*>(in), reinterpret_cast<__nv_bfloat16*>(out), T, F);
+      reinterpret_cast<const __nv_bfloat16*>(in), reinterpret_cast<__nv_bfloat16*>(out), T, F, n_rows);
   return launch_status();
+}
+
+GK_EXPORT int gk_swiglu_fwd(const void* in, void* out, long long T, int F, void* stream) {
+  return swiglu_fwd_launch(in, out, T, F, nullptr, stream);
+}
+
+// rows at or beyond *n_rows (device) are not computed
+GK_EXPORT int gk_swiglu_fwd_rows(const void* in, void* out, long long T, int F, const int* n_rows, void* stream) {
+  return swiglu_fwd_launch(in, out, T, F, n_rows, stream);
 }
 
 GK_EXPORT int gk_swiglu_bwd(const void* dout, const void* in, void* din, long long T, int F, void* stream) {

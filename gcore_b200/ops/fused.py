@@ -164,6 +164,22 @@ def rope(x, pos, theta, rot=None, interleaved=False):
 
 
 # ------------------------------------------------------------------------------------------------ SwiGLU
+def qk_headnorm_(qkv: torch.Tensor, wq: torch.Tensor, wk: torch.Tensor, Hq: int, Hk: int, D: int, eps: float):
+    """In-place per-head RMSNorm of the query and key heads of packed ``[T, (Hq + 2 Hk) * D]`` rows (inference: no
+    autograd).  One kernel on a GPU; the same arithmetic through ``rmsnorm`` elsewhere."""
+    T = qkv.shape[0]
+    if (qkv.dtype == torch.bfloat16 and _lib.use_native(qkv) and D % 8 == 0 and D <= 256 and qkv.stride(1) == 1
+            and wq.dtype == torch.bfloat16 and hasattr(_lib.kernels(), "gk_qk_headnorm")):
+        LAUNCHES["elementwise"] += 1
+        _lib.check(_lib.kernels().gk_qk_headnorm(_lib.ptr(qkv), _lib.ptr(wq), _lib.ptr(wk), T, Hq, Hk, D,
+                                                 qkv.stride(0), float(eps), _lib.stream_ptr()), "qk_headnorm")
+        return qkv
+    v = qkv.view(T, Hq + 2 * Hk, D)
+    v[:, :Hq] = rmsnorm(v[:, :Hq].reshape(-1, D), wq, eps)[0].view(T, Hq, D)
+    v[:, Hq:Hq + Hk] = rmsnorm(v[:, Hq:Hq + Hk].reshape(-1, D), wk, eps)[0].view(T, Hk, D)
+    return qkv
+
+
 def swiglu_ref(x):
     g, u = x.float().chunk(2, dim=-1)
     return (torch.nn.functional.silu(g) * u).to(x.dtype)
@@ -194,10 +210,20 @@ class _SwigluFn(torch.autograd.Function):
         return din.reshape(ctx.shape)
 
 
-def swiglu(x: torch.Tensor) -> torch.Tensor:
-    """``silu(x[..., :F]) * x[..., F:]`` for ``x = [gate | up]``."""
+def swiglu(x: torch.Tensor, n_rows: torch.Tensor = None) -> torch.Tensor:
+    """``silu(x[..., :F]) * x[..., F:]`` for ``x = [gate | up]``.  ``n_rows`` (one int32 on the device, inference only):
+    rows of the 2-D ``x`` at or beyond it are not computed and their output is undefined - for expert-sorted buffers
+    that are sized for the worst case and carry the count of rows in use on the device."""
     if x.dtype == torch.bfloat16 and _lib.use_native(x) and (x.shape[-1] // 2) % 8 == 0:
         if not x.is_contiguous():
             x = x.contiguous()
+        if n_rows is not None and x.dim() == 2 and not (torch.is_grad_enabled() and x.requires_grad) \
+                and n_rows.dtype == torch.int32 and hasattr(_lib.kernels(), "gk_swiglu_fwd_rows"):
+            F = x.shape[1] // 2
+            out = torch.empty(x.shape[0], F, dtype=x.dtype, device=x.device)
+            LAUNCHES["elementwise"] += 1
+            _lib.check(_lib.kernels().gk_swiglu_fwd_rows(_lib.ptr(x), _lib.ptr(out), x.shape[0], F, _lib.ptr(n_rows),
+                                                         _lib.stream_ptr()), "swiglu_fwd_rows")
+            return out
         return _SwigluFn.apply(x)
     return swiglu_ref(x)

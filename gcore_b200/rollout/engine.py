@@ -482,12 +482,7 @@ class InferEngine:
     def _qk_norm(self, lw, qkv, T):
         if lw.q_ln is None:
             return qkv
-        v = qkv.view(T, self.hq + 2 * self.hk, self.D)
-        q = fused.rmsnorm(v[:, :self.hq].reshape(-1, self.D), lw.q_ln, self.cfg.rms_norm_eps)[0]
-        k = fused.rmsnorm(v[:, self.hq:self.hq + self.hk].reshape(-1, self.D), lw.k_ln, self.cfg.rms_norm_eps)[0]
-        v[:, :self.hq] = q.view(T, self.hq, self.D)
-        v[:, self.hq:self.hq + self.hk] = k.view(T, self.hk, self.D)
-        return qkv
+        return fused.qk_headnorm_(qkv, lw.q_ln, lw.k_ln, self.hq, self.hk, self.D, self.cfg.rms_norm_eps)
 
     @torch.no_grad()
     def _prefill(self, tokens, pos, cu, max_len, slots, embed_rows=None):

@@ -948,3 +948,47 @@ def test_expert_parallel_local_plan_kernel_matches_sort_and_histogram(T, K, E, e
     want_pos[order] = torch.arange(n, device=DEV) - starts[flat[order]]
     assert torch.equal(cnt.long(), want_cnt) and torch.equal(pos.long(), want_pos) and torch.equal(idx32.long(), flat)
     assert not offsets.any() and not tot.any()
+
+
+def test_swiglu_shapes_and_row_bound():
+    """SwiGLU forward / backward on shapes whose row length does not divide the grid stride (the index carries of the
+    division-free iteration), and the forward that stops at a device-side row count."""
+    from gcore_b200.ops import fused
+    torch.manual_seed(41)
+    for T, F in ((9216, 1536), (64, 18944), (777, 104), (3, 8)):
+        x = _rand(T, 2 * F, scale=1.5).requires_grad_(True)
+        y = fused.swiglu(x)
+        xr = x.detach().float().requires_grad_(True)
+        g, u = xr.chunk(2, -1)
+        ref = torch.nn.functional.silu(g) * u
+        _close(y, ref.detach())
+        dy = _rand(T, F)
+        y.backward(dy)
+        ref.backward(dy.float())
+        _close(x.grad, xr.grad)
+    x = _rand(1024, 512, scale=1.5)
+    n = torch.tensor([300], dtype=torch.int32, device=DEV)
+    with torch.no_grad():
+        y = fused.swiglu(x, n_rows=n)
+    g, u = x.float().chunk(2, -1)
+    _close(y[:300], (torch.nn.functional.silu(g) * u)[:300])
+
+
+def test_qk_headnorm_in_place():
+    """Per-head RMSNorm of the q and k heads of packed rows in one launch = the two norms over reshaped copies; the
+    value heads and the row padding stay untouched."""
+    from gcore_b200.ops import fused
+    torch.manual_seed(42)
+    T, Hq, Hk, D = 70, 32, 4, 128
+    buf = _rand(T, (Hq + 2 * Hk) * D + 64, scale=2.0)          # rows with a pitch larger than their width
+    qkv = buf[:, :(Hq + 2 * Hk) * D]
+    wq, wk = _rand(D, scale=1.0) + 1.0, _rand(D, scale=1.0) + 1.0
+    want = qkv.clone().float().view(T, Hq + 2 * Hk, D)
+    for sl, w in ((slice(0, Hq), wq), (slice(Hq, Hq + Hk), wk)):
+        x = want[:, sl]
+        want[:, sl] = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + 1e-6) * w.float()
+    before = buf.clone()
+    fused.qk_headnorm_(qkv, wq, wk, Hq, Hk, D, 1e-6)
+    _close(qkv.reshape(T, Hq + 2 * Hk, D), want)
+    assert torch.equal(qkv.reshape(T, Hq + 2 * Hk, D)[:, Hq + Hk:], before[:, :(Hq + 2 * Hk) * D].view(T, -1, D)[:, Hq + Hk:])
+    assert torch.equal(buf[:, (Hq + 2 * Hk) * D:], before[:, (Hq + 2 * Hk) * D:])

@@ -346,7 +346,10 @@ def main():
         # synthetic prompts live in pinned host memory; every step copies its prompts to the device inside the timed
         # region
         g = torch.Generator().manual_seed(1000 + dp_rank)
-        host_prompts = torch.randint(100, 150000, (total_steps, prompts_per_dp, args.prompt_len), generator=g,
+        # token ids uniform in [100, 150000) as the recipe says, capped by the model's vocabulary (129 280 for the
+        # DeepSeek-V3 shape: ids beyond it would index outside the embedding table)
+        hi = min(150000, mcfg.vocab_size)
+        host_prompts = torch.randint(100, hi, (total_steps, prompts_per_dp, args.prompt_len), generator=g,
                                      dtype=torch.int64).pin_memory()
 
         def run_step(i):

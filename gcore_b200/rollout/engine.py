@@ -763,6 +763,11 @@ class InferEngine:
         reqs: List[Request] = []
         if isinstance(prompts, torch.Tensor):
             prompts = prompts.tolist()
+        vocab = self.cfg.vocab_size
+        for i, p in enumerate(prompts):
+            if len(p) and not (0 <= min(p) and max(p) < vocab):
+                # checked on the host: an id outside the embedding table would otherwise trip a device-side assert
+                raise ValueError(f"prompt {i} holds token ids outside [0, {vocab})")
         for i, p in enumerate(prompts):
             for j in range(n):
                 rid = self._next_rid

@@ -291,3 +291,15 @@ def test_repetition_penalty_follows_the_definition_across_slot_reuse():
             assert int(lp.argmax()) == want
             assert abs(float(lp[want]) - want_lp) < 1e-3
             toks.append(want)
+
+
+def test_prompt_ids_outside_the_vocabulary_are_refused_on_the_host():
+    import pytest
+    cfg, model = build()
+    eng = InferEngine(cfg, RolloutWeights.from_model(model), max_running_requests=2, max_model_len=32,
+                      kv_block_size=4, use_cuda_graph=False)
+    with pytest.raises(ValueError, match="outside"):
+        eng.generate([[5, 6, cfg.vocab_size]], SamplingParams(max_new_tokens=2, greedy=True))
+    with pytest.raises(ValueError, match="outside"):
+        eng.generate([[5, -1]], SamplingParams(max_new_tokens=2, greedy=True))
+    assert len(eng.generate([[5, 6, cfg.vocab_size - 1]], SamplingParams(max_new_tokens=2, greedy=True))) == 1

@@ -245,6 +245,7 @@ class InferEngine:
         self.hk = cfg.num_kv_heads // tp_size
         self.D = cfg.head_dim
         self.mla_dim = (cfg.kv_lora_rank + cfg.qk_rope_head_dim) if getattr(cfg, "use_mla", False) else 0
+        self._mla_abs: Dict[int, list] = {}   # id(attention module) -> [absorbed up-projection, stale]
         self.vocab_local = weights.head.shape[0]
         self.vocab_start = self.vocab_local * (dist.get_rank(tp_group) if (tp_group is not None and tp_size > 1) else 0)
         # the library (eager) backend launches its decode ops one by one (its GPU path has no host synchronisation, so
@@ -374,6 +375,7 @@ class InferEngine:
         self.owns_weights = True
         self.asleep["weights"] = False
         self._graphs.clear()
+        self._mla_abs.clear()   # the latent-attention modules of the new copy get fresh absorbed matrices
         if self.device.type == "cuda":
             torch.cuda.current_stream().synchronize()
         return moved
@@ -399,6 +401,8 @@ class InferEngine:
                 self._graphs.clear()
         if getattr(self, "fp8_enabled", False):
             self.quantize_weights_fp8()
+        for ent in self._mla_abs.values():
+            ent[1] = True
         if self.device.type == "cuda":
             torch.cuda.current_stream().synchronize()
 
@@ -614,6 +618,27 @@ class InferEngine:
             w = quant.dequant_128x128(q, sc)[:w.shape[0], :w.shape[1]].to(up.weight.dtype)
         return w
 
+    def _mla_absorbed(self, mla):
+        """The kv up-projection as ``[heads, nope + v, kv_lora]`` with adapters folded in (and, for block-fp8 layers,
+        after the quantise -> dequantise round trip): what the absorbed decode multiplies the query and the latent
+        output with.  Derived once per weight version, not per decode step: ``update_weights`` marks the copies stale
+        and ``generate`` rewrites them in place before it decodes (captured graphs keep reading the same storage)."""
+        cfg = self.cfg
+        dn, dv, C = cfg.qk_nope_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
+        ent = self._mla_abs.get(id(mla))
+        if ent is None or ent[1]:
+            w_up = self._mla_up_weight(mla).view(mla.h, dn + dv, C)
+            up_lora = getattr(mla.linear_kv_up_proj, "lora", None)
+            if up_lora is not None:  # adapters on the up-projection: fold their delta into the absorbed matrices
+                w_up = w_up + up_lora.delta_weight().view(mla.h, dn + dv, C).to(w_up.dtype)
+            if ent is None:
+                ent = [w_up.contiguous().clone(), False]
+                self._mla_abs[id(mla)] = ent
+            else:
+                ent[0].copy_(w_up)
+                ent[1] = False
+        return ent[0]
+
     def _mla_native(self) -> bool:
         """Whether the decode step runs the latent-attention kernel (bf16 cache on a GPU, a built geometry)."""
         cfg = self.cfg
@@ -636,10 +661,7 @@ class InferEngine:
         q_nope, q_rope, c_kv, k_rope = mla.project(h, pos)
         flat = cache.view(-1, self.mla_dim)
         flat.index_copy_(0, slots, torch.cat([self._mla_cached_latent(mla, c_kv), k_rope], -1))
-        w_up = self._mla_up_weight(mla).view(mla.h, dn + dv, C)
-        up_lora = getattr(mla.linear_kv_up_proj, "lora", None)
-        if up_lora is not None:  # adapters on the up-projection: fold their delta into the absorbed matrices
-            w_up = w_up + up_lora.delta_weight().view(mla.h, dn + dv, C).to(w_up.dtype)
+        w_up = self._mla_absorbed(mla)
         if lat_idx is None:
             # latent decode kernel straight on the paged cache: the two absorbed projections are head-batched GEMMs
             # in head-major layout, which the kernel reads and writes through strides
@@ -759,6 +781,10 @@ class InferEngine:
         placeholder embeddings in the prefill, decoding is unchanged."""
         if self.asleep["kv_cache"]:
             self.wake_up(("kv_cache",))
+        if self.mla_dim:
+            for lw in self.w.layers:   # re-derive stale absorbed matrices here, outside any graph capture
+                if lw.mla is not None:
+                    self._mla_absorbed(lw.mla)
         dev = self.device
         reqs: List[Request] = []
         if isinstance(prompts, torch.Tensor):

@@ -69,7 +69,7 @@ class BtRmReward:
 
 
 class GenRmReward:
-    """Generative reward model: builds a judging prompt per response, samples ``repeat_n`` verdicts, parses yes / no
+    """Generative reward model: builds a grading prompt per response, samples ``repeat_n`` verdicts, parses yes / no
     into +-1 and averages."""
 
     def __init__(self, engine, build_prompt: Callable, parse: Callable, sampling, repeat_n: int = 1):

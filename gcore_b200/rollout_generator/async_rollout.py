@@ -74,7 +74,7 @@ class RolloutController:
         return g
 
     def _run_groups(self, groups: List[RolloutGroup], sampler) -> List[RolloutGroup]:
-        """All groups handed to one sampler in this round, as ONE engine call: a continuous-batching engine decodes
+        """All groups handed to one sampler in this dispatch, as ONE engine call: a continuous-batching engine decodes
         ``len(groups) * repeat_n`` sequences per step instead of ``repeat_n``."""
         outs = sampler.generate_groups([g.prompt for g in groups], self.repeat_n, self.params)
         assert len(outs) == len(groups) * self.repeat_n, "a batched sampler returns repeat_n samples per prompt, in order"

@@ -187,7 +187,7 @@ def test_recipe_variants_change_what_they_say_and_plug_ins_resolve():
     assert torch.allclose(lo.token_loss, torch.tensor([-1.4, -1.2, 1.6487]), atol=1e-4)
     assert lo.metrics["widened_clip_frac"].tolist() == [1.0, 3.0]
     gen = import_from_path(os.path.join(ROOT, "tasks", "math_rl", "gen_rm_reward.py"), "parse_verdict")
-    prompt = import_from_path(os.path.join(ROOT, "tasks", "math_rl", "gen_rm_reward.py"), "build_judge_prompt")
+    prompt = import_from_path(os.path.join(ROOT, "tasks", "math_rl", "gen_rm_reward.py"), "build_grader_prompt")
     assert gen("Verdict: wrong. On reflection, Verdict: Correct") == 1.0 and gen("unsure") == 0.0
     assert "Reference answer: 42" in prompt({"prompt_text": "6 x 7?", "response_text": "42", "answer": "42"})
 

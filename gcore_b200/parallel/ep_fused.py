@@ -136,6 +136,10 @@ class FusedEP:
                                              self.rank, self.ep, self.E_local, SEG, self.R_max, st["K"], self.H,
                                              st["T"], _lib.stream_ptr()), "ep_push")
         self.barrier()
+        if st.get("forward_only"):
+            # forward-only passes read the receive buffer in place: a peer overwrites it with the next layer's rows
+            # only after the group barrier of this layer's combine, which this rank reaches after its expert GEMMs
+            return self.recv.t[:self.R_max * self.H].view(self.R_max, self.H)
         out = torch.empty(self.R_max, self.H, dtype=torch.bfloat16, device=self.device)
         self._copy_rows(self.recv.t, out, st)
         return out
@@ -241,6 +245,8 @@ def get_fused_ep(group, hidden: int, num_experts: int, top_k: int, tokens: int, 
 
 def fused_ep_moe_forward(fe: FusedEP, layer, x, idx, w):
     st = fe.plan(idx)
+    # read here: an autograd function always runs its forward with grad mode off
+    st["forward_only"] = not torch.is_grad_enabled() and os.environ.get("GCORE_EP_RECV_INPLACE", "1") != "0"
     rows = _Dispatch.apply(x, fe, st)
     y_rows = layer.experts(rows, st["offsets"])
     return _Combine.apply(y_rows, w, fe, st)

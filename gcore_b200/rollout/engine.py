@@ -169,6 +169,24 @@ class RolloutWeights:
         self.layers: List[LayerWeights] = []
         self.embed = self.final_ln = self.head = None
 
+    @staticmethod
+    def _serving_module(module, clone: bool):
+        """The trainer's module itself (shared storage) or, for a separate rollout copy, a deep copy whose parameters
+        are plain tensors of their own (no gradient buffers, no optimizer hooks)."""
+        if not clone:
+            return module
+        if any(getattr(p, "is_lora", False) for p in module.parameters()):
+            raise NotImplementedError("a separate rollout copy of a latent-attention or MoE module that carries LoRA "
+                                      "adapters is not supported: use policy.share_rollout_weights=true")
+        import copy
+        own = copy.deepcopy(module)
+        for p in own.parameters():
+            p.requires_grad_(False)
+            for attr in ("main_grad", "grad"):
+                if getattr(p, attr, None) is not None:
+                    setattr(p, attr, None)
+        return own
+
     @classmethod
     def from_model(cls, model, clone: bool = False):
         f = (lambda t: t.detach().clone()) if clone else (lambda t: t.detach())
@@ -186,13 +204,12 @@ class RolloutWeights:
             if hasattr(a, "linear_kv_down_proj"):
                 # multi-head latent attention: the module itself serves (its projections carry LoRA adapters and
                 # fp8 wrappers as they are); the cache holds the latent and the shared rotated key
-                import copy
-                lw.mla = copy.deepcopy(a) if clone else a
+                lw.mla = cls._serving_module(a, clone)
                 lw.qkv_w = lw.qkv_b = lw.o_w = lw.q_ln = lw.k_ln = lw.sinks = None
                 lw.window = 0
                 lw.ln2 = f(layer.pre_mlp_layernorm.weight)
                 if layer.is_moe:
-                    lw.moe = layer.mlp
+                    lw.moe = cls._serving_module(layer.mlp, clone)
                     lw.fc1_w = lw.fc2_w = None
                 else:
                     lw.moe = None
@@ -209,7 +226,8 @@ class RolloutWeights:
             lw.sinks = f(a.sinks) if getattr(a, "sinks", None) is not None else None
             lw.window = a.window
             if layer.is_moe:
-                lw.moe = layer.mlp  # module reference: router + experts are used as they are
+                # the module serves as it is (router + experts); a separate rollout copy owns a deep copy of it
+                lw.moe = cls._serving_module(layer.mlp, clone)
                 lw.fc1_w = lw.fc2_w = None
             else:
                 lw.moe = None

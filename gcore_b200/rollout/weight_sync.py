@@ -257,7 +257,7 @@ def detach_lora_targets(policy_engine, weights) -> List[str]:
 
     class _W:  # minimal stand-in so that _engine_tensor_map can be reused before an engine exists
         w = weights
-    tmap = _engine_tensor_map(_W, policy_engine.model)
+    tmap = _engine_tensor_map(_W, policy_engine.model, modules=False)
     attr = {"self_attention.linear_qkv.weight": "qkv_w", "self_attention.linear_proj.weight": "o_w",
             "mlp.linear_fc1.weight": "fc1_w", "mlp.linear_fc2.weight": "fc2_w"}
     done = []
@@ -279,7 +279,7 @@ def sync_lora_deltas(policy_engine, infer_engine) -> Dict[str, float]:
     gpatch_v4/training_backend/megatron_backend/checkpoint.py:520-700, BASELINE config 5 "only LoRA deltas are
     resynced")."""
     targets = _lora_targets(policy_engine)
-    dst = _engine_tensor_map(infer_engine, policy_engine.model)
+    dst = _engine_tensor_map(infer_engine, policy_engine.model, modules=False)
     params = dict(policy_engine.model.named_parameters())
     moved = factors = 0
     with torch.no_grad():
@@ -322,8 +322,9 @@ def _peer_sync(policy_engine, tp_src, tp_dst, max_bucket_mb, src, dst) -> Option
     return _PEER_SYNC[key]
 
 
-def _engine_tensor_map(infer_engine, model) -> Dict[str, torch.Tensor]:
-    """Rollout-side tensors keyed by the trainer's parameter names."""
+def _engine_tensor_map(infer_engine, model, modules: bool = True) -> Dict[str, torch.Tensor]:
+    """Rollout-side tensors keyed by the trainer's parameter names.  ``modules=False`` leaves out the tensors of
+    latent-attention and MoE modules, which serve as modules (adapters included) rather than as plain weights."""
     w = infer_engine.w
     out = {"embedding.word_embeddings.weight": w.embed, "decoder.final_layernorm.weight": w.final_ln}
     if hasattr(model, "output_layer"):
@@ -331,10 +332,20 @@ def _engine_tensor_map(infer_engine, model) -> Dict[str, torch.Tensor]:
     for i, lw in enumerate(w.layers):
         p = f"decoder.layers.{i}."
         out[p + "input_layernorm.weight"] = lw.ln1
-        out[p + "self_attention.linear_qkv.weight"] = lw.qkv_w
-        if lw.qkv_b is not None:
-            out[p + "self_attention.linear_qkv.bias"] = lw.qkv_b
-        out[p + "self_attention.linear_proj.weight"] = lw.o_w
+        if lw.mla is not None:
+            # latent-attention module (owned copy or the trainer's own): its projections and norms by parameter name
+            for n, t in (lw.mla.named_parameters() if modules else ()):
+                if not getattr(t, "is_lora", False):
+                    out[p + "self_attention." + n] = t
+        else:
+            out[p + "self_attention.linear_qkv.weight"] = lw.qkv_w
+            if lw.qkv_b is not None:
+                out[p + "self_attention.linear_qkv.bias"] = lw.qkv_b
+            out[p + "self_attention.linear_proj.weight"] = lw.o_w
+        if lw.moe is not None and modules:
+            for n, t in lw.moe.named_parameters():   # router, (grouped) expert and shared-expert weights
+                if not getattr(t, "is_lora", False):
+                    out[p + "mlp." + n] = t
         out[p + "pre_mlp_layernorm.weight"] = lw.ln2
         if lw.fc1_w is not None:
             out[p + "mlp.linear_fc1.weight"] = lw.fc1_w

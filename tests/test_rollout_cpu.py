@@ -303,3 +303,43 @@ def test_prompt_ids_outside_the_vocabulary_are_refused_on_the_host():
     with pytest.raises(ValueError, match="outside"):
         eng.generate([[5, -1]], SamplingParams(max_new_tokens=2, greedy=True))
     assert len(eng.generate([[5, 6, cfg.vocab_size - 1]], SamplingParams(max_new_tokens=2, greedy=True))) == 1
+
+
+def test_separate_rollout_copy_owns_its_moe_and_latent_attention_weights():
+    """``share_rollout_weights=false`` with an MoE + latent-attention model: the engine's copy is really separate
+    (trainer updates do not show through), ``verify`` sees the stale expert / router / latent tensors, ``sync_weights``
+    brings them over and the engine then reproduces the trainer's log-probs."""
+    from gcore_b200.configs.config import OptimizerConfig, PolicyConfig, TrainingConfig
+    from gcore_b200.engine.train_engine import TrainingEngine
+    from gcore_b200.models.config import ModelConfig
+    from gcore_b200.rollout.weight_sync import sync_weights, verify
+    mcfg = ModelConfig(arch="deepseek_v3", num_layers=2, hidden_size=64, num_attention_heads=4, num_kv_heads=4,
+                       ffn_hidden_size=128, vocab_size=256, use_mla=True, q_lora_rank=32, kv_lora_rank=32,
+                       qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16, head_dim=24, num_experts=8, moe_top_k=2,
+                       moe_ffn_hidden_size=32, moe_shared_expert_ffn=32, moe_router_type="sigmoid_group", moe_n_group=4,
+                       moe_topk_group=2, first_k_dense=1, moe_router_bias=True, dtype="float32")
+    eng = TrainingEngine(PolicyConfig(recompute="none", without_ref=True), OptimizerConfig(lr=1e-2), TrainingConfig(),
+                         model_cfg=mcfg)
+    eng.setup_model_and_get_optimizer(seed=1, with_ref=False)
+    ie = InferEngine(mcfg, RolloutWeights.from_model(eng.model, clone=True), num_kv_blocks=64, kv_block_size=4,
+                     max_model_len=48, use_cuda_graph=False)
+    moe = eng.model.decoder.layers[1].mlp
+    assert ie.w.layers[1].moe is not moe
+    assert ie.w.layers[1].moe.experts.linear_fc1.weight.data_ptr() != moe.experts.linear_fc1.weight.data_ptr()
+    assert ie.w.layers[0].mla is not eng.model.decoder.layers[0].self_attention
+    assert verify(eng, ie) == []
+    prompt = [5, 9, 200, 31, 7]
+    before = ie.generate([prompt], SamplingParams(max_new_tokens=6, greedy=True))[0]
+    with torch.no_grad():
+        for p in eng.model.parameters():
+            p.add_(torch.randn_like(p) * 0.05)
+    stale = verify(eng, ie)
+    assert any("experts.linear_fc1" in n for n in stale) and any("router" in n for n in stale)
+    assert any("linear_kv_up_proj" in n for n in stale)
+    again = ie.generate([prompt], SamplingParams(max_new_tokens=6, greedy=True))[0]
+    assert again.out_tokens == before.out_tokens            # the trainer's update does not show through
+    sync_weights(eng, ie, max_bucket_mb=1)
+    assert verify(eng, ie) == []
+    ref_t, ref_lp = naive_greedy(eng.model.eval(), prompt, 6)
+    after = ie.generate([prompt], SamplingParams(max_new_tokens=6, greedy=True))[0]
+    assert after.out_tokens == ref_t and max(abs(a - b) for a, b in zip(after.out_logprobs, ref_lp)) < 1e-3

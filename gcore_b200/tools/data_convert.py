@@ -5,8 +5,10 @@ the datasets read, tokenising once offline.
     python -m gcore_b200.tools.data_convert prompts  --src q.jsonl    --dst prompts.jsonl --tokenizer tok_dir
     python -m gcore_b200.tools.data_convert pretrain --src text.jsonl --dst tokens.jsonl --tokenizer tok_dir
 
-``sft``: ``{"messages": [{"role", "content"}, ...]}`` or ``{"prompt", "response"}`` -> ``{"prompt": ids, "response":
-ids}``; ``prompts``: ``{"prompt" | "question", "answer"}`` -> ``{"prompt": ids, "answer": ...}``; ``pretrain``:
+``sft``: ``{"messages": [{"role", "content"}, ...]}``, the ShareGPT (``conversations``) and Alpaca (``instruction`` /
+``input`` / ``output``) layouts of LLaMA-Factory datasets, or ``{"prompt", "response"}`` -> ``{"prompt": ids,
+"response": ids}``; ``dpo``: preference records in the same layouts (``chosen`` / ``rejected``) -> ``{"prompt",
+"chosen", "rejected"}`` ids; ``prompts``: ``{"prompt" | "question", "answer"}`` -> ``{"prompt": ids, "answer": ...}``; ``pretrain``:
 ``{"text"}`` -> ``{"tokens": ids}``.  Without ``--tokenizer`` a byte-level encoding (id = byte + 3) is used, which
 keeps the tools usable in tests and for smoke runs.  The offset index (``.idx``) is written next to the output."""
 from __future__ import annotations
@@ -28,13 +30,57 @@ def load_tokenizer(path: str | None) -> Callable[[str], List[int]]:
     return lambda s: tok.encode(s, add_special_tokens=False)
 
 
-def _chat_to_pair(rec: dict) -> tuple:
+_SHAREGPT_ROLES = {"human": "user", "user": "user", "gpt": "assistant", "assistant": "assistant", "system": "system",
+                   "observation": "tool", "function_call": "assistant"}
+
+
+def _messages(rec: dict) -> list:
+    """Chat turns of a record in any of the accepted layouts: ``messages`` (role / content), the ShareGPT layout of
+    LLaMA-Factory (``conversations`` of ``from`` / ``value``, optional ``system``), or the Alpaca layout
+    (``instruction`` [+ ``input``] -> ``output``, optional ``system`` and ``history`` of [user, assistant] pairs)."""
     if "messages" in rec:
-        msgs = rec["messages"]
+        return rec["messages"]
+    if "conversations" in rec:
+        msgs = [{"role": "system", "content": rec["system"]}] if rec.get("system") else []
+        for t in rec["conversations"]:
+            role = _SHAREGPT_ROLES.get(t.get("from", t.get("role")), "user")
+            msgs.append({"role": role, "content": t.get("value", t.get("content", ""))})
+        return msgs
+    if "instruction" in rec:
+        msgs = [{"role": "system", "content": rec["system"]}] if rec.get("system") else []
+        for u, a in rec.get("history") or []:
+            msgs += [{"role": "user", "content": u}, {"role": "assistant", "content": a}]
+        q = rec["instruction"] + ("\n" + rec["input"] if rec.get("input") else "")
+        msgs.append({"role": "user", "content": q})
+        if "output" in rec and not isinstance(rec["output"], (list, tuple)):
+            msgs.append({"role": "assistant", "content": rec["output"]})
+        return msgs
+    return None
+
+
+def _render(msgs: list) -> str:
+    return "".join(f"<|{m['role']}|>\n{m['content']}\n" for m in msgs) + "<|assistant|>\n"
+
+
+def _chat_to_pair(rec: dict) -> tuple:
+    msgs = _messages(rec)
+    if msgs is not None:
         last = max(i for i, m in enumerate(msgs) if m["role"] == "assistant")
-        prompt = "".join(f"<|{m['role']}|>\n{m['content']}\n" for m in msgs[:last]) + "<|assistant|>\n"
-        return prompt, msgs[last]["content"]
+        return _render(msgs[:last]), msgs[last]["content"]
     return rec["prompt"], rec["response"]
+
+
+def _preference_triple(rec: dict) -> tuple:
+    """(prompt, chosen, rejected) of a preference record: explicit ``prompt`` / ``chosen`` / ``rejected`` strings,
+    ShareGPT / ``messages`` context with ``chosen`` / ``rejected`` turns ({"value" | "content"}), or the Alpaca layout
+    with ``output = [chosen, rejected]``."""
+    def text(x):
+        return x if isinstance(x, str) else x.get("value", x.get("content", ""))
+    if "instruction" in rec and isinstance(rec.get("output"), (list, tuple)):
+        return _render(_messages(rec)), rec["output"][0], rec["output"][1]
+    msgs = _messages(rec)
+    prompt = _render(msgs) if msgs is not None else rec["prompt"]
+    return prompt, text(rec["chosen"]), text(rec["rejected"])
 
 
 def convert(kind: str, src: str, dst: str, encode: Callable[[str], List[int]], max_len: int | None = None) -> int:
@@ -53,6 +99,11 @@ def convert(kind: str, src: str, dst: str, encode: Callable[[str], List[int]], m
                 out = {"prompt": encode(rec.get("prompt") or rec["question"]), "answer": rec.get("answer")}
                 if max_len and len(out["prompt"]) > max_len:
                     continue
+            elif kind == "dpo":
+                p, c, r = _preference_triple(rec)
+                out = {"prompt": encode(p), "chosen": encode(c), "rejected": encode(r)}
+                if max_len and len(out["prompt"]) + max(len(out["chosen"]), len(out["rejected"])) > max_len:
+                    continue
             elif kind == "pretrain":
                 out = {"tokens": encode(rec["text"])}
             else:
@@ -66,7 +117,7 @@ def convert(kind: str, src: str, dst: str, encode: Callable[[str], List[int]], m
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("kind", choices=["sft", "prompts", "pretrain"])
+    ap.add_argument("kind", choices=["sft", "prompts", "pretrain", "dpo"])
     ap.add_argument("--src", required=True)
     ap.add_argument("--dst", required=True)
     ap.add_argument("--tokenizer", default=None)

@@ -528,6 +528,31 @@ def test_data_convert_tools(tmp_path):
     q.write_text(json.dumps({"question": "1+1", "answer": "2"}) + "\n")
     assert data_convert.main(["prompts", "--src", str(q), "--dst", str(tmp_path / "p.jsonl")]) == 1
     assert IndexedJsonlDataset(str(tmp_path / "p.jsonl"))[0]["answer"] == "2"
+    # LLaMA-Factory layouts: ShareGPT conversations, Alpaca instructions (with history), and preference pairs
+    lf = tmp_path / "lf.jsonl"
+    lf.write_text(
+        json.dumps({"system": "be brief", "conversations": [{"from": "human", "value": "2+2?"},
+                                                             {"from": "gpt", "value": "4"},
+                                                             {"from": "human", "value": "and 3+3?"},
+                                                             {"from": "gpt", "value": "6"}]}) + "\n" +
+        json.dumps({"instruction": "Add.", "input": "1 1", "output": "2", "history": [["Add. 0 0", "0"]]}) + "\n")
+    assert data_convert.main(["sft", "--src", str(lf), "--dst", str(tmp_path / "lf_sft.jsonl")]) == 2
+    ds = IndexedJsonlDataset(str(tmp_path / "lf_sft.jsonl"))
+    dec = lambda ids: bytes(t - 3 for t in ids).decode()
+    assert dec(ds[0]["response"]) == "6" and dec(ds[0]["prompt"]).startswith("<|system|>\nbe brief\n<|user|>\n2+2?")
+    assert dec(ds[0]["prompt"]).endswith("<|user|>\nand 3+3?\n<|assistant|>\n")
+    assert dec(ds[1]["response"]) == "2" and "<|assistant|>\n0\n<|user|>\nAdd.\n1 1\n" in dec(ds[1]["prompt"])
+    pref = tmp_path / "pref.jsonl"
+    pref.write_text(
+        json.dumps({"conversations": [{"from": "human", "value": "capital of France?"}],
+                    "chosen": {"from": "gpt", "value": "Paris"}, "rejected": {"from": "gpt", "value": "Rome"}}) + "\n" +
+        json.dumps({"instruction": "Say hi", "output": ["hi", "bye"]}) + "\n" +
+        json.dumps({"prompt": "x", "chosen": "good", "rejected": "bad"}) + "\n")
+    assert data_convert.main(["dpo", "--src", str(pref), "--dst", str(tmp_path / "dpo.jsonl")]) == 3
+    dp = IndexedJsonlDataset(str(tmp_path / "dpo.jsonl"))
+    assert [dec(dp[i]["chosen"]) for i in range(3)] == ["Paris", "hi", "good"]
+    assert [dec(dp[i]["rejected"]) for i in range(3)] == ["Rome", "bye", "bad"]
+    assert dec(dp[1]["prompt"]) == "<|user|>\nSay hi\n<|assistant|>\n" and dec(dp[2]["prompt"]) == "x"
     rep = gpu_check.main([])       # no GPU here: the report says so instead of failing
     assert rep["cuda_available"] is False and rep["ok"] is False
 

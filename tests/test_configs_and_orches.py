@@ -192,6 +192,18 @@ def test_recipe_variants_change_what_they_say_and_plug_ins_resolve():
     assert "Reference answer: 42" in prompt({"prompt_text": "6 x 7?", "response_text": "42", "answer": "42"})
 
 
+def test_preference_recipes_load():
+    from gcore_b200.configs.base import load_config
+    from gcore_b200.configs.config import DpoConfig, RewardTrainConfig
+    y = lambda n: os.path.join(ROOT, "tasks", "preference", "yaml", n)
+    d = load_config(DpoConfig, y("dpo_qwen2.5_7b.yaml"), [])
+    assert d.dpo_beta == 0.1 and d.dpo_sft_loss_coef == 0.05 and not d.reference_free
+    r = load_config(DpoConfig, y("dpo_reference_free_lora.yaml"), [])
+    assert r.reference_free and r.policy.lora.rank == 32 and r.policy.model_arch == d.policy.model_arch
+    m = load_config(RewardTrainConfig, y("reward_model_bt.yaml"), [])
+    assert m.rm_loss == "bt" and m.policy.without_ref
+
+
 def test_recipe_includes_merge_in_order_and_reject_cycles(tmp_path):
     from gcore_b200.configs.base import ConfigError, load_yaml
     (tmp_path / "a.yaml").write_text("x: {p: 1, q: 2}\ny: 1\n")

@@ -88,7 +88,10 @@ def rank_coords(rank: int, sizes: Dict[str, int], order: List[str]) -> Dict[str,
 def plan_groups(world_size: int, tp: int = 1, pp: int = 1, cp: int = 1, ep: int = 1, etp: Optional[int] = None):
     """Pure function (no process groups): returns ``{name: [rank lists]}`` for every group family.  Used by
     ``initialize_model_parallel`` and directly by the placement / planning tests."""
-    etp = etp if etp is not None else tp
+    # experts are never tensor-sharded in this package: every TP rank holds whole experts and routes the tokens of its
+    # own sequence-parallel shard, so by default the TP ranks belong to the expert-data-parallel group (their expert
+    # gradients are summed like those of data-parallel replicas)
+    etp = etp if etp is not None else 1
     if world_size % (tp * pp * cp):
         raise ValueError(f"world_size {world_size} not divisible by tp*pp*cp = {tp * pp * cp}")
     dp = world_size // (tp * pp * cp)

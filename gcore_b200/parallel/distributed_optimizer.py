@@ -251,8 +251,14 @@ class DistributedDataParallel:
             b.release_grads()
 
     def finish_grad_sync(self, extra_scale: float = 1.0):
-        """Averages over the reduction group (and applies ``extra_scale``, e.g. 1/num_tokens for per-token losses
-        summed over micro-batches) and reduces every bucket."""
+        """Reduces every bucket: the sum over the buffer's reduction group times ``extra_scale`` / (dense data-parallel
+        size), i.e. the average over the data-parallel replicas for ``extra_scale = 1`` and the plain sum for
+        ``extra_scale = dense DP size`` (losses already normalised by global counts).  The divisor is the *dense* group
+        size for every buffer: an expert buffer reduces over its own group (whose size differs: expert parallelism
+        removes ranks from it, tensor-parallel ranks holding whole experts join it), but every token still
+        contributes exactly once to an expert's gradient, so the normalisation is that of the batch, not of the group.
+        (Dividing by the expert group's own size scaled expert gradients by the expert-parallel size.)"""
+        dense_dp = ps.get_data_parallel_world_size(with_context_parallel=True)
         tp_group = ps.get_tensor_model_parallel_group()
         if ps.get_tensor_model_parallel_world_size() > 1 and getattr(self.model, "sequence_parallel", False):
             # gains / router weights that act on sequence-parallel activations see only this rank's tokens
@@ -267,7 +273,7 @@ class DistributedDataParallel:
                     o += g.numel()
         handles = []
         for buf in self.buffers:
-            scale = extra_scale / buf.dp
+            scale = extra_scale / max(dense_dp, 1)
             if buf.peer:
                 # reduce-scatter happens inside the optimizer kernels (peer pulls); only order the ranks here
                 buf.pending_scale = scale

@@ -83,6 +83,26 @@ def test_ep2_matches_single_process(tmp_path):
     ref = [e.finetune_step(pw.samples(8, 70 + s, vocab=512))["lm_loss"] for s in range(3)]
     for a, b in zip(ref, got["losses"]):
         assert abs(a - b) < 2e-3, (ref, got)
+    # the gradient norm pins the scale of the expert gradients (a factor of the expert-parallel size on them moves it
+    # by 3 % here, while Adam hides such a factor from the losses)
+    assert abs(float(e.optimizer.last_grad_norm) - got["grad_norm"]) < 5e-3, (float(e.optimizer.last_grad_norm), got)
+
+
+def test_tp2_with_unsplit_experts_matches_single_process(tmp_path):
+    """MoE under tensor parallelism without expert parallelism: the TP ranks hold whole experts and see different
+    tokens, so their expert gradients are reduced over a group that contains both (losses, gradient norm and the
+    updated expert weights equal the single-process run; the two ranks' expert weights stay identical)."""
+    import parallel_worker as pw
+    out = tmp_path / "tpmoe.json"
+    _spawn("tp_moe", out, port="29561")
+    got = json.load(open(out))
+    e = pw.engine(pw.MOE_CFG, 1)
+    ref = [e.finetune_step(pw.samples(8, 70 + s, vocab=512))["lm_loss"] for s in range(4)]
+    for a, b in zip(ref, got["losses"]):
+        assert abs(a - b) < 2e-3, (ref, got["losses"])
+    assert got["expert_weights_equal"]
+    # the gradient norm pins the scale of the expert gradients (summed over the two ranks, not averaged)
+    assert abs(float(e.optimizer.last_grad_norm) - got["grad_norm"]) < 5e-3
 
 
 def test_cp2_matches_single_process(tmp_path):

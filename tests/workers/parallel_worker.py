@@ -1,4 +1,4 @@
-"""gloo worker for the parallelism parity tests: mode = tp | ep | ep_rollout | ep_grpo | cp | pp | vpp | fsdp |
+"""gloo worker for the parallelism parity tests: mode = tp | tp_moe | ep | ep_rollout | ep_grpo | cp | pp | vpp | fsdp |
 ep_dynmbs | aux_dp | tp_topk | nodistopt | dyncp | dp_grpo_balance | pg_offload."""
 import json
 import os
@@ -62,6 +62,19 @@ def main():
             from gcore_b200.checkpoint.torch_dist import save_checkpoint
             save_checkpoint(e, os.path.join(sys.argv[3], "ckpt"), 4)
             save_hf(e, os.path.join(sys.argv[3], "hf"))
+    elif mode == "tp_moe":
+        # tensor parallel 2 with an MoE model whose experts are not split (expert parallel 1): every TP rank routes the
+        # tokens of its own sequence-parallel shard through whole experts, so the expert gradients of the two ranks
+        # have to be summed - the TP ranks are data-parallel replicas as far as the experts are concerned
+        ps.initialize_model_parallel(tp=2)
+        e = engine(MOE_CFG, 2)
+        losses = [e.finetune_step(samples(8, 70 + s, vocab=512))["lm_loss"] for s in range(4)]
+        w = e.model.decoder.layers[1].mlp.experts.linear_fc1.weight.detach()
+        parts = [torch.empty_like(w) for _ in range(world)]
+        dist.all_gather(parts, w.contiguous())
+        res = {"losses": losses, "grad_norm": float(e.optimizer.last_grad_norm),
+               "expert_weights_equal": bool(torch.equal(parts[0], parts[1])),
+               "fc1_sum": float(w.double().sum())}
     elif mode == "ep":
         ps.initialize_model_parallel(tp=1, ep=2)
         mcfg = ModelConfig(arch="qwen3_moe", num_layers=2, hidden_size=128, num_attention_heads=4, num_kv_heads=2,
@@ -72,7 +85,7 @@ def main():
         for s in range(3):
             batch = samples(8, 70 + s, vocab=512)
             losses.append(e.finetune_step(batch[rank::world])["lm_loss"])  # EP ranks are also DP ranks
-        res = {"losses": losses}
+        res = {"losses": losses, "grad_norm": float(e.optimizer.last_grad_norm)}
     elif mode == "ep_rollout":
         # two engines whose experts are split over both ranks serve different workloads (3 prompts x 9 tokens against
         # 1 prompt x 3 tokens): the engine that finishes first has to keep its experts in the others' all-to-alls

@@ -13,11 +13,11 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, os.path.join(ROOT, "tests", "workers"))
 
 
-def _spawn(mode, out, extra=(), port="29541"):
+def _spawn(mode, out, extra=(), port="29541", world=2):
     env = dict(os.environ, PYTHONPATH=ROOT, MASTER_ADDR="127.0.0.1", MASTER_PORT=port, OMP_NUM_THREADS="2")
     procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "workers", "parallel_worker.py"), mode,
-                               str(out), *extra], env=dict(env, RANK=str(r), WORLD_SIZE="2", LOCAL_RANK=str(r)))
-             for r in range(2)]
+                               str(out), *extra], env=dict(env, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r)))
+             for r in range(world)]
     for p in procs:
         assert p.wait(timeout=900) == 0
 
@@ -103,6 +103,23 @@ def test_tp2_with_unsplit_experts_matches_single_process(tmp_path):
     assert got["expert_weights_equal"]
     # the gradient norm pins the scale of the expert gradients (summed over the two ranks, not averaged)
     assert abs(float(e.optimizer.last_grad_norm) - got["grad_norm"]) < 5e-3
+
+
+@pytest.mark.parametrize("mode,port", [("tp2ep2", "29563"), ("ep2dp4", "29565")])
+def test_four_rank_expert_layouts_match_single_process(tmp_path, mode, port):
+    """Experts split over two ranks and replicated over two more, under tensor parallelism 2 x data parallelism 2 and
+    under data parallelism 4: losses and the global gradient norm of the single-process run (the norm pins the scale
+    of the expert gradients across the expert-data-parallel replicas)."""
+    import parallel_worker as pw
+    out = tmp_path / f"{mode}.json"
+    _spawn(mode, out, port=port, world=4)
+    got = json.load(open(out))
+    assert got["edp"] == 2
+    e = pw.engine(pw.MOE_CFG, 1)
+    ref = [e.finetune_step(pw.samples(8, 70 + s, vocab=512))["lm_loss"] for s in range(2)]
+    for a, b in zip(ref, got["losses"]):
+        assert abs(a - b) < 2e-3, (ref, got["losses"])
+    assert abs(float(e.optimizer.last_grad_norm) - got["grad_norm"]) < 5e-3, (float(e.optimizer.last_grad_norm), got)
 
 
 def test_cp2_matches_single_process(tmp_path):

@@ -1,4 +1,4 @@
-"""gloo worker for the parallelism parity tests: mode = tp | tp_moe | ep | ep_rollout | ep_grpo | cp | pp | vpp | fsdp |
+"""gloo worker for the parallelism parity tests: mode = tp | tp_moe | tp2ep2 | ep2dp4 | ep | ep_rollout | ep_grpo | cp | pp | vpp | fsdp |
 ep_dynmbs | aux_dp | tp_topk | nodistopt | dyncp | dp_grpo_balance | pg_offload."""
 import json
 import os
@@ -75,6 +75,19 @@ def main():
         res = {"losses": losses, "grad_norm": float(e.optimizer.last_grad_norm),
                "expert_weights_equal": bool(torch.equal(parts[0], parts[1])),
                "fc1_sum": float(w.double().sum())}
+    elif mode in ("tp2ep2", "ep2dp4"):
+        # four ranks: tensor parallel 2 x data parallel 2 with the experts split 2 ways and replicated 2 ways, or pure
+        # data parallel 4 with the experts split 2 ways and replicated 2 ways
+        if mode == "tp2ep2":
+            ps.initialize_model_parallel(tp=2, ep=2, etp=1)
+            e = engine(MOE_CFG, 2)
+        else:
+            ps.initialize_model_parallel(tp=1, ep=2)
+            e = engine(MOE_CFG, 1)
+        dpr, dpw = ps.get_data_parallel_rank(), ps.get_data_parallel_world_size()
+        losses = [e.finetune_step(samples(8, 70 + s, vocab=512)[dpr::dpw])["lm_loss"] for s in range(2)]
+        res = {"losses": losses, "grad_norm": float(e.optimizer.last_grad_norm),
+               "edp": dist.get_world_size(ps.get_expert_data_parallel_group())}
     elif mode == "ep":
         ps.initialize_model_parallel(tp=1, ep=2)
         mcfg = ModelConfig(arch="qwen3_moe", num_layers=2, hidden_size=128, num_attention_heads=4, num_kv_heads=2,

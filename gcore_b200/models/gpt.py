@@ -572,8 +572,10 @@ class GPTModel(nn.Module):
                                                 self.vocab_start(), tp_group)
             hp = h_prev
             if sp:
+                # the embedding rows were computed in full on every rank; the hidden state came out of a
+                # sequence-parallel gather, whose backward sums the ranks' gradients: hand back this rank's share only
                 e = tp_ops.scatter_to_sequence_parallel(e, tp_group)
-                hp = tp_ops.scatter_to_sequence_parallel(hp, tp_group)
+                hp = tp_ops.slice_of_gathered(hp, tp_group)
             e = fused.rmsnorm(e, blk.enorm.weight, cfg.rms_norm_eps)[0]
             hp = fused.rmsnorm(hp, blk.hnorm.weight, cfg.rms_norm_eps)[0]
             x = blk.eh_proj(torch.cat([e, hp], dim=-1))

@@ -108,6 +108,33 @@ class _ScatterToSP(torch.autograd.Function):
         return all_gather_dim0(g, ctx.group), None
 
 
+class _SliceOfGathered(torch.autograd.Function):
+    """fwd: this rank's token slice of a tensor that came out of ``gather_from_sequence_parallel``; bwd: the gradient
+    in that slice, zeros elsewhere.  The gather's own backward sums the ranks' gradients (reduce-scatter), so a branch
+    that re-shards its output must hand back only its own share; ``scatter_to_sequence_parallel`` (all-gather in the
+    backward) is for tensors that every rank computed in full, such as the output of the vocabulary-parallel
+    embedding."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        n = _ws(group)
+        r = dist.get_rank(group)
+        c = x.shape[0] // n
+        ctx.meta = (r * c, c, x.shape[0])
+        return x[r * c:(r + 1) * c].contiguous()
+
+    @staticmethod
+    def backward(ctx, g):
+        lo, c, total = ctx.meta
+        full = g.new_zeros((total,) + tuple(g.shape[1:]))
+        full[lo:lo + c] = g
+        return full, None
+
+
+def slice_of_gathered(x, group):
+    return _SliceOfGathered.apply(x, group) if _ws(group) > 1 else x
+
+
 def gather_from_sequence_parallel(x, group):
     return _GatherFromSP.apply(x, group) if _ws(group) > 1 else x
 

@@ -88,6 +88,22 @@ def test_ep2_matches_single_process(tmp_path):
     assert abs(float(e.optimizer.last_grad_norm) - got["grad_norm"]) < 5e-3, (float(e.optimizer.last_grad_norm), got)
 
 
+def test_tp2_multi_token_prediction_matches_single_process(tmp_path):
+    import dataclasses
+    import parallel_worker as pw
+    from gcore_b200.models.config import get_preset
+    out = tmp_path / "tpmtp.json"
+    _spawn("tp_mtp", out, port="29567")
+    got = json.load(open(out))
+    mcfg = dataclasses.replace(get_preset("tiny_llama", dtype="float32", qkv_bias=True), mtp_num_layers=2,
+                               mtp_loss_scaling_factor=0.3)
+    e = pw.engine(mcfg, 1)
+    ref = [e.finetune_step(pw.samples(8, 50 + s)) for s in range(3)]
+    for r, a, b in zip(ref, got["losses"], got["mtp"]):
+        assert abs(r["lm_loss"] - a) < 5e-4 and abs(r["mtp_loss"] - b) < 5e-4, (ref, got)
+    assert abs(float(e.optimizer.last_grad_norm) - got["grad_norm"]) < 5e-3
+
+
 def test_tp2_with_unsplit_experts_matches_single_process(tmp_path):
     """MoE under tensor parallelism without expert parallelism: the TP ranks hold whole experts and see different
     tokens, so their expert gradients are reduced over a group that contains both (losses, gradient norm and the

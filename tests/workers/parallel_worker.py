@@ -1,4 +1,4 @@
-"""gloo worker for the parallelism parity tests: mode = tp | tp_moe | tp2ep2 | ep2dp4 | ep | ep_rollout | ep_grpo | cp | pp | vpp | fsdp |
+"""gloo worker for the parallelism parity tests: mode = tp | tp_mtp | tp_moe | tp2ep2 | ep2dp4 | ep | ep_rollout | ep_grpo | cp | pp | vpp | fsdp |
 ep_dynmbs | aux_dp | tp_topk | nodistopt | dyncp | dp_grpo_balance | pg_offload."""
 import json
 import os
@@ -62,6 +62,17 @@ def main():
             from gcore_b200.checkpoint.torch_dist import save_checkpoint
             save_checkpoint(e, os.path.join(sys.argv[3], "ckpt"), 4)
             save_hf(e, os.path.join(sys.argv[3], "hf"))
+    elif mode == "tp_mtp":
+        # multi-token-prediction blocks under tensor + sequence parallelism: their branch re-shards the gathered trunk
+        # output, whose backward must hand back each rank's own share only
+        import dataclasses
+        ps.initialize_model_parallel(tp=2)
+        mcfg = dataclasses.replace(get_preset("tiny_llama", dtype="float32", qkv_bias=True), mtp_num_layers=2,
+                                   mtp_loss_scaling_factor=0.3)
+        e = engine(mcfg, 2)
+        outs = [e.finetune_step(samples(8, 50 + s)) for s in range(3)]
+        res = {"losses": [o["lm_loss"] for o in outs], "mtp": [o["mtp_loss"] for o in outs],
+               "grad_norm": float(e.optimizer.last_grad_norm)}
     elif mode == "tp_moe":
         # tensor parallel 2 with an MoE model whose experts are not split (expert parallel 1): every TP rank routes the
         # tokens of its own sequence-parallel shard through whole experts, so the expert gradients of the two ranks

@@ -84,6 +84,9 @@ class ExpertLoRA(nn.Module):
             p.tp_mode = "none" if shared else "expert"
             if not shared:
                 p.is_expert = True
+            else:
+                # acts on the tokens of this rank's sequence-parallel shard, like the norm gains and the router
+                p.sequence_parallel = True
 
     def forward(self, x_perm, offsets):
         x_perm = x_perm.to(self.lora_A.dtype)
@@ -142,6 +145,12 @@ def apply_lora(model: nn.Module, lora_cfg, seed: int = 0) -> Dict[str, LoRAAdapt
         ad.lora_A.tp_mode = "row" if mod.mode == "row" else "none"
         for b in ad.lora_B:
             b.tp_mode = "column" if mod.mode == "column" else "none"
+        if mod.tp_size > 1 and mod.mode in ("column", "row"):
+            # the replicated half of an adapter on a sharded projection (A of a column-parallel layer, B of a
+            # row-parallel one) receives from every TP rank only the part of its gradient that flows through that
+            # rank's shard of the other half: the parts are summed over the TP group with the gradient reduction
+            for q in ([ad.lora_A] if mod.mode == "column" else list(ad.lora_B)):
+                q.tp_partial_grad = True
         mod.lora = ad
         adapters[name] = ad
     # grouped expert projections: `linear_fc1` / `linear_fc2` among the targets also adapt the experts, with one
@@ -169,8 +178,10 @@ def apply_lora(model: nn.Module, lora_cfg, seed: int = 0) -> Dict[str, LoRAAdapt
                                  w.device, lora_cfg.lora_A_init_method, lora_cfg.lora_B_init_method,
                                  seed=(seed + zlib.crc32(name.encode())) & 0x7FFFFFFF)
                 ad.lora_A.tp_mode = "none"
+                ad.lora_A.sequence_parallel = True     # sees the tokens of this rank's sequence-parallel shard
                 for b in ad.lora_B:
                     b.tp_mode = "none"
+                    b.sequence_parallel = True
                 mod.lora = ad
                 adapters[name] = ad
     if lora_cfg.check_lora_all_coverage:

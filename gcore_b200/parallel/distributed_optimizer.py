@@ -260,10 +260,12 @@ class DistributedDataParallel:
         (Dividing by the expert group's own size scaled expert gradients by the expert-parallel size.)"""
         dense_dp = ps.get_data_parallel_world_size(with_context_parallel=True)
         tp_group = ps.get_tensor_model_parallel_group()
-        if ps.get_tensor_model_parallel_world_size() > 1 and getattr(self.model, "sequence_parallel", False):
-            # gains / router weights that act on sequence-parallel activations see only this rank's tokens
-            sp_grads = [p.main_grad for buf in self.buffers for p in buf.params
-                        if getattr(p, "sequence_parallel", False) and p.main_grad is not None]
+        if ps.get_tensor_model_parallel_world_size() > 1:
+            # gains / router weights that act on sequence-parallel activations see only this rank's tokens; replicated
+            # adapter halves on sharded projections see only this rank's shard of the other half
+            sp = getattr(self.model, "sequence_parallel", False)
+            sp_grads = [p.main_grad for buf in self.buffers for p in buf.params if p.main_grad is not None
+                        and ((sp and getattr(p, "sequence_parallel", False)) or getattr(p, "tp_partial_grad", False))]
             if sp_grads:
                 flat = torch.cat([g.reshape(-1) for g in sp_grads])
                 dist.all_reduce(flat, group=tp_group)

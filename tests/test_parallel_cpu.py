@@ -88,6 +88,29 @@ def test_ep2_matches_single_process(tmp_path):
     assert abs(float(e.optimizer.last_grad_norm) - got["grad_norm"]) < 5e-3, (float(e.optimizer.last_grad_norm), got)
 
 
+@pytest.mark.parametrize("mode,port", [("tp_lora", "29569"), ("tp_lora_moe", "29571")])
+def test_tp2_lora_matches_single_process(tmp_path, mode, port):
+    """LoRA under tensor + sequence parallelism (dense model; MoE model with adapters on the router and a shared
+    adapter on the experts): losses, gradient norm, and the replicated adapter halves stay identical on both ranks."""
+    import dataclasses
+    import parallel_worker as pw
+    from gcore_b200.models.config import get_preset
+    out = tmp_path / f"{mode}.json"
+    _spawn(mode, out, port=port)
+    got = json.load(open(out))
+    if mode == "tp_lora":
+        e, vocab = pw.lora_engine(get_preset("tiny_llama", dtype="float32", qkv_bias=True), 1), 1024
+    else:
+        e = pw.lora_engine(dataclasses.replace(pw.MOE_CFG, moe_aux_loss_coef=0.0), 1,
+                           ["linear_qkv", "linear_proj", "linear_fc1", "linear_fc2", "router"])
+        vocab = 512
+    ref = [e.finetune_step(pw.samples(8, 50 + s, vocab=vocab))["lm_loss"] for s in range(3)]
+    for a, b in zip(ref, got["losses"]):
+        assert abs(a - b) < 5e-4, (ref, got["losses"])
+    assert abs(float(e.optimizer.last_grad_norm) - got["grad_norm"]) < 2e-3, (float(e.optimizer.last_grad_norm), got)
+    assert got["replicated_halves_equal"]
+
+
 def test_tp2_multi_token_prediction_matches_single_process(tmp_path):
     import dataclasses
     import parallel_worker as pw

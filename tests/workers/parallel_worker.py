@@ -1,4 +1,4 @@
-"""gloo worker for the parallelism parity tests: mode = tp | tp_mtp | tp_moe | tp2ep2 | ep2dp4 | ep | ep_rollout | ep_grpo | cp | pp | vpp | fsdp |
+"""gloo worker for the parallelism parity tests: mode = tp | tp_lora | tp_lora_moe | tp_mtp | tp_moe | tp2ep2 | ep2dp4 | ep | ep_rollout | ep_grpo | cp | pp | vpp | fsdp |
 ep_dynmbs | aux_dp | tp_topk | nodistopt | dyncp | dp_grpo_balance | pg_offload."""
 import json
 import os
@@ -44,6 +44,40 @@ def engine(mcfg, tp, sp=True, lr=1e-3, vpp=None):
     return e
 
 
+def lora_engine(mcfg, tp, targets=None):
+    """Engine with rank-8 adapters whose two halves are both non-zero and drawn from the full (unsharded) tensors, so
+    that a TP = 2 run and a single-process run hold the same effective adapters."""
+    import zlib
+    pc = PolicyConfig(recompute="none", without_ref=True)
+    pc.dist_config.tensor_model_parallel_size = tp
+    pc.dist_config.sequence_parallel = tp > 1
+    pc.lora.rank, pc.lora.alpha = 8, 16
+    if targets:
+        pc.lora.target_modules = list(targets)
+    oc = OptimizerConfig(lr=1e-3, lr_decay_style="constant", weight_decay=0.0, max_grad_norm=1.0)
+    e = TrainingEngine(pc, oc, TrainingConfig(train_mbs=2, train_gbs=8), model_cfg=mcfg)
+    e.setup_model_and_get_optimizer(seed=11)
+    r = ps.get_tensor_model_parallel_rank() if tp > 1 else 0
+    with torch.no_grad():
+        for n, p in sorted(e.model.named_parameters()):
+            if not getattr(p, "is_lora", False):
+                continue
+            mode = getattr(p, "tp_mode", "none")
+            shape = list(p.shape)
+            if tp > 1 and mode == "column":
+                shape[0] *= tp
+            if tp > 1 and mode == "row":
+                shape[-1] *= tp
+            g = torch.Generator().manual_seed(zlib.crc32(n.encode()) & 0x7FFFFFFF)
+            full = torch.randn(*shape, generator=g) * 0.05
+            if tp > 1 and mode == "column":
+                full = full.chunk(tp, 0)[r]
+            if tp > 1 and mode == "row":
+                full = full.chunk(tp, -1)[r]
+            p.copy_(full)
+    return e
+
+
 def main():
     mode, out = sys.argv[1], sys.argv[2]
     ps.init_distributed(os.environ.get("GCORE_TEST_BACKEND", "gloo"))  # nccl: the same parity check on GPUs
@@ -62,6 +96,24 @@ def main():
             from gcore_b200.checkpoint.torch_dist import save_checkpoint
             save_checkpoint(e, os.path.join(sys.argv[3], "ckpt"), 4)
             save_hf(e, os.path.join(sys.argv[3], "hf"))
+    elif mode in ("tp_lora", "tp_lora_moe"):
+        # adapters under tensor + sequence parallelism: the replicated half of an adapter on a sharded projection gets
+        # partial gradients per rank, router / shared-expert adapters see one token shard per rank
+        import dataclasses
+        ps.initialize_model_parallel(tp=2)
+        if mode == "tp_lora":
+            e = lora_engine(get_preset("tiny_llama", dtype="float32", qkv_bias=True), 2)
+            vocab = 1024
+        else:
+            e = lora_engine(dataclasses.replace(MOE_CFG, moe_aux_loss_coef=0.0), 2,
+                            ["linear_qkv", "linear_proj", "linear_fc1", "linear_fc2", "router"])
+            vocab = 512
+        losses = [e.finetune_step(samples(8, 50 + s, vocab=vocab))["lm_loss"] for s in range(3)]
+        from gcore_b200.models.lora import verify_lora_weight_consistency
+        same = verify_lora_weight_consistency({k: v for k, v in e.adapters.items() if hasattr(v, "lora_B")
+                                               and isinstance(v.lora_B, torch.nn.ParameterList)},
+                                              ps.get_tensor_model_parallel_group())
+        res = {"losses": losses, "grad_norm": float(e.optimizer.last_grad_norm), "replicated_halves_equal": bool(same)}
     elif mode == "tp_mtp":
         # multi-token-prediction blocks under tensor + sequence parallelism: their branch re-shards the gathered trunk
         # output, whose backward must hand back each rank's own share only

@@ -204,6 +204,13 @@ class MLAttention(nn.Module):
         self.kv_layernorm = RMSNormWeight(cfg.kv_lora_rank, cfg, device)
         self.linear_kv_up_proj = ParallelLinear(cfg.kv_lora_rank, cfg.num_attention_heads * (dn + dv), "column", cfg,
                                                 tp_size=tp_size, device=device)
+        if tp_size > 1:
+            # the down-projections (and the shared rotary key inside the kv one) are replicated while the heads behind
+            # them are sharded: every TP rank sends back the part of their gradient that flows through its heads, and
+            # the parts are summed over the TP group with the gradient reduction (their norm gains already are)
+            for lin in (getattr(self, "linear_q_down_proj", None), self.linear_kv_down_proj):
+                if lin is not None:
+                    lin.weight.tp_partial_grad = True
         self.linear_proj = ParallelLinear(cfg.num_attention_heads * dv, H, "row", cfg, tp_size=tp_size,
                                           init_std=cfg.init_std / math.sqrt(2 * cfg.num_layers), device=device)
 

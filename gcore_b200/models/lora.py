@@ -151,6 +151,11 @@ def apply_lora(model: nn.Module, lora_cfg, seed: int = 0) -> Dict[str, LoRAAdapt
             # rank's shard of the other half: the parts are summed over the TP group with the gradient reduction
             for q in ([ad.lora_A] if mod.mode == "column" else list(ad.lora_B)):
                 q.tp_partial_grad = True
+        elif getattr(w, "tp_partial_grad", False):
+            # a replicated projection in front of sharded heads (latent-attention down-projections): both halves of
+            # its adapter get per-rank partial gradients, like the weight itself
+            for q in [ad.lora_A] + list(ad.lora_B):
+                q.tp_partial_grad = True
         mod.lora = ad
         adapters[name] = ad
     # grouped expert projections: `linear_fc1` / `linear_fc2` among the targets also adapt the experts, with one

@@ -111,6 +111,25 @@ def test_tp2_lora_matches_single_process(tmp_path, mode, port):
     assert got["replicated_halves_equal"]
 
 
+@pytest.mark.parametrize("mode,port", [("tp_mla", "29573"), ("tp_mla_lora", "29575")])
+def test_tp2_latent_attention_matches_single_process(tmp_path, mode, port):
+    """Latent attention under tensor parallelism, plain and with adapters on all five projections: the replicated
+    down-projections (and their adapters) collect their gradient from both ranks' heads."""
+    import parallel_worker as pw
+    out = tmp_path / f"{mode}.json"
+    _spawn(mode, out, port=port)
+    got = json.load(open(out))
+    if mode == "tp_mla":
+        e = pw.engine(pw.MLA_CFG, 1)
+    else:
+        e = pw.lora_engine(pw.MLA_CFG, 1, ["linear_q_down_proj", "linear_q_up_proj", "linear_kv_down_proj",
+                                           "linear_kv_up_proj", "linear_proj"])
+    ref = [e.finetune_step(pw.samples(8, 50 + s, vocab=512))["lm_loss"] for s in range(3)]
+    for a, b in zip(ref, got["losses"]):
+        assert abs(a - b) < 5e-4, (ref, got["losses"])
+    assert abs(float(e.optimizer.last_grad_norm) - got["grad_norm"]) < 2e-3, (float(e.optimizer.last_grad_norm), got)
+
+
 def test_tp2_multi_token_prediction_matches_single_process(tmp_path):
     import dataclasses
     import parallel_worker as pw

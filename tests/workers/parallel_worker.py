@@ -1,4 +1,4 @@
-"""gloo worker for the parallelism parity tests: mode = tp | tp_lora | tp_lora_moe | tp_mtp | tp_moe | tp2ep2 | ep2dp4 | ep | ep_rollout | ep_grpo | cp | pp | vpp | fsdp |
+"""gloo worker for the parallelism parity tests: mode = tp | tp_mla | tp_mla_lora | tp_lora | tp_lora_moe | tp_mtp | tp_moe | tp2ep2 | ep2dp4 | ep | ep_rollout | ep_grpo | cp | pp | vpp | fsdp |
 ep_dynmbs | aux_dp | tp_topk | nodistopt | dyncp | dp_grpo_balance | pg_offload."""
 import json
 import os
@@ -30,6 +30,11 @@ def samples(n, seed, L=48, vocab=1024):
 MOE_CFG = ModelConfig(arch="qwen3_moe", num_layers=2, hidden_size=128, num_attention_heads=4, num_kv_heads=2,
                       ffn_hidden_size=256, vocab_size=512, num_experts=8, moe_top_k=2, moe_ffn_hidden_size=64,
                       moe_aux_loss_coef=1e-2, dtype="float32", qk_layernorm=True)
+
+
+MLA_CFG = ModelConfig(arch="deepseek_v3", num_layers=2, hidden_size=128, num_attention_heads=4, num_kv_heads=4,
+                      ffn_hidden_size=256, vocab_size=512, use_mla=True, q_lora_rank=64, kv_lora_rank=32,
+                      qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16, head_dim=24, dtype="float32")
 
 
 def engine(mcfg, tp, sp=True, lr=1e-3, vpp=None):
@@ -96,6 +101,16 @@ def main():
             from gcore_b200.checkpoint.torch_dist import save_checkpoint
             save_checkpoint(e, os.path.join(sys.argv[3], "ckpt"), 4)
             save_hf(e, os.path.join(sys.argv[3], "hf"))
+    elif mode in ("tp_mla", "tp_mla_lora"):
+        # latent attention under tensor parallelism: replicated down-projections in front of sharded heads
+        ps.initialize_model_parallel(tp=2)
+        if mode == "tp_mla":
+            e = engine(MLA_CFG, 2)
+        else:
+            e = lora_engine(MLA_CFG, 2, ["linear_q_down_proj", "linear_q_up_proj", "linear_kv_down_proj",
+                                         "linear_kv_up_proj", "linear_proj"])
+        losses = [e.finetune_step(samples(8, 50 + s, vocab=512))["lm_loss"] for s in range(3)]
+        res = {"losses": losses, "grad_norm": float(e.optimizer.last_grad_norm)}
     elif mode in ("tp_lora", "tp_lora_moe"):
         # adapters under tensor + sequence parallelism: the replicated half of an adapter on a sharded projection gets
         # partial gradients per rank, router / shared-expert adapters see one token shard per rank

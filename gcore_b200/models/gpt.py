@@ -558,6 +558,8 @@ class GPTModel(nn.Module):
         if sp:
             h = tp_ops.gather_from_sequence_parallel(h, tp_group)
         if self.value_head:
+            if sp:   # the scalar head is replicated: every TP rank back-propagates the whole value loss
+                h = tp_ops.replicated_consumer_of_gathered(h, tp_group)
             return self.output_layer(h).squeeze(-1).float(), aux_total
         return h, aux_total
 

@@ -131,6 +131,25 @@ class _SliceOfGathered(torch.autograd.Function):
         return full, None
 
 
+class _ScaleGrad(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, factor):
+        ctx.factor = factor
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g * ctx.factor, None
+
+
+def replicated_consumer_of_gathered(x, group):
+    """Marks a tensor that came out of ``gather_from_sequence_parallel`` as the input of a computation every TP rank
+    repeats in full (a replicated head): each rank then sends back the whole gradient, and the gather's backward would
+    add the copies up, so each copy is scaled by 1 / TP size."""
+    n = _ws(group)
+    return _ScaleGrad.apply(x, 1.0 / n) if n > 1 else x
+
+
 def slice_of_gathered(x, group):
     return _SliceOfGathered.apply(x, group) if _ws(group) > 1 else x
 

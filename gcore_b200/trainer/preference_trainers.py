@@ -110,6 +110,12 @@ def _pooled(engine: TrainingEngine, samples: Sequence[dict], grad: bool, pooling
         for idx in engine._microbatches(samples, forward_only=not grad):
             mb = engine._pack(samples, idx)
             h, _ = engine._hidden(engine.model, mb)
+            if grad and getattr(engine.model, "sequence_parallel", False):
+                # pooling and the contrastive loss are repeated in full on every TP rank, so every rank back-propagates
+                # the whole gradient into the gathered hidden states
+                from ..core import parallel_state as ps
+                from ..parallel.tp_ops import replicated_consumer_of_gathered
+                h = replicated_consumer_of_gathered(h, ps.get_tensor_model_parallel_group())
             if pooling == "mean":
                 n = mb.num_seqs + 1
                 seg = torch.zeros(n, h.shape[1], dtype=torch.float32, device=h.device).index_add(

@@ -130,6 +130,18 @@ def test_tp2_latent_attention_matches_single_process(tmp_path, mode, port):
     assert abs(float(e.optimizer.last_grad_norm) - got["grad_norm"]) < 2e-3, (float(e.optimizer.last_grad_norm), got)
 
 
+def test_tp2_critic_matches_single_process(tmp_path):
+    """Value head under tensor parallelism: same loss and gradient norm as one process (the replicated head's
+    gradient into the gathered hidden states is not added up over the TP ranks)."""
+    import parallel_worker as pw
+    out = tmp_path / "tpvalue.json"
+    _spawn("tp_value", out, port="29577")
+    got = json.load(open(out))
+    ref = pw.value_engine(1).rl_train_value(pw.value_samples())
+    assert abs(ref["value/loss"] - got["value/loss"]) < 1e-5
+    assert abs(ref["value/grad_norm"] - got["value/grad_norm"]) < 2e-3, (ref, got)
+
+
 def test_tp2_multi_token_prediction_matches_single_process(tmp_path):
     import dataclasses
     import parallel_worker as pw

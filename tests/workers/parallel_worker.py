@@ -1,4 +1,4 @@
-"""gloo worker for the parallelism parity tests: mode = tp | tp_mla | tp_mla_lora | tp_lora | tp_lora_moe | tp_mtp | tp_moe | tp2ep2 | ep2dp4 | ep | ep_rollout | ep_grpo | cp | pp | vpp | fsdp |
+"""gloo worker for the parallelism parity tests: mode = tp | tp_value | tp_mla | tp_mla_lora | tp_lora | tp_lora_moe | tp_mtp | tp_moe | tp2ep2 | ep2dp4 | ep | ep_rollout | ep_grpo | cp | pp | vpp | fsdp |
 ep_dynmbs | aux_dp | tp_topk | nodistopt | dyncp | dp_grpo_balance | pg_offload."""
 import json
 import os
@@ -47,6 +47,28 @@ def engine(mcfg, tp, sp=True, lr=1e-3, vpp=None):
     e = TrainingEngine(pc, oc, tc, model_cfg=mcfg)
     e.setup_model_and_get_optimizer(seed=11)
     return e
+
+
+def value_engine(tp):
+    from gcore_b200.configs.config import PpoConfig
+    pc = PolicyConfig(recompute="none", without_ref=True)
+    pc.dist_config.tensor_model_parallel_size = tp
+    pc.dist_config.sequence_parallel = tp > 1
+    oc = OptimizerConfig(lr=1e-3, lr_decay_style="constant", weight_decay=0.0, max_grad_norm=1.0)
+    e = TrainingEngine(pc, oc, TrainingConfig(train_mbs=2, train_gbs=8), ppo_cfg=PpoConfig(),
+                       model_cfg=get_preset("tiny_llama", dtype="float32", qkv_bias=True), value_head=True)
+    e.setup_model_and_get_optimizer(seed=11)
+    return e
+
+
+def value_samples():
+    smp = samples(8, 60)
+    g = torch.Generator().manual_seed(9)
+    for s in smp:
+        n = s["tokens"].numel()
+        s["mask"] = s["loss_mask"]
+        s["returns"], s["values"] = torch.randn(n, generator=g), torch.randn(n, generator=g)
+    return smp
 
 
 def lora_engine(mcfg, tp, targets=None):
@@ -101,6 +123,12 @@ def main():
             from gcore_b200.checkpoint.torch_dist import save_checkpoint
             save_checkpoint(e, os.path.join(sys.argv[3], "ckpt"), 4)
             save_hf(e, os.path.join(sys.argv[3], "hf"))
+    elif mode == "tp_value":
+        # critic under tensor parallelism: the scalar head is replicated, every rank back-propagates the whole loss
+        from gcore_b200.configs.config import PpoConfig
+        ps.initialize_model_parallel(tp=2)
+        e = value_engine(2)
+        res = e.rl_train_value(value_samples())
     elif mode in ("tp_mla", "tp_mla_lora"):
         # latent attention under tensor parallelism: replicated down-projections in front of sharded heads
         ps.initialize_model_parallel(tp=2)

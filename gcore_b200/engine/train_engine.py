@@ -316,10 +316,18 @@ class TrainingEngine:
                 packed[i] = self._pack(samples, batches[i], keys)
             return packed[i]
 
+        aux_scale = self._aux_scale(len(batches))
+
         def forward_step(i, hidden_in, chunk=None):
             mb = get(i)
-            return model(mb.tokens, mb.position_ids, mb.cp_ctx if mb.cp_ctx is not None else mb.cu_seqlens,
-                         mb.max_seqlen, hidden_in=hidden_in, chunk=chunk)
+            out, aux = model(mb.tokens, mb.position_ids, mb.cp_ctx if mb.cp_ctx is not None else mb.cu_seqlens,
+                             mb.max_seqlen, hidden_in=hidden_in, chunk=chunk)
+            ends_here = ps.is_pipeline_last_stage() and (chunk is None or chunk == n_chunks - 1)
+            if aux is not None and not ends_here:
+                # a stage (or model chunk) that does not evaluate the loss back-propagates its own auxiliary loss with
+                # a unit gradient: give it the weight the loss-side adds it with
+                aux = aux * aux_scale
+            return out, aux
 
         def loss_step(i, hidden, aux):
             r = step_fn(get(i), hidden, aux)

@@ -130,6 +130,21 @@ def test_tp2_latent_attention_matches_single_process(tmp_path, mode, port):
     assert abs(float(e.optimizer.last_grad_norm) - got["grad_norm"]) < 2e-3, (float(e.optimizer.last_grad_norm), got)
 
 
+def test_pp2_with_moe_layers_on_both_stages_matches_single_process(tmp_path):
+    """The load-balance loss of MoE layers on a stage that does not evaluate the loss enters the backward with the
+    weight the last stage gives its own (1 / (micro-batches x data-parallel size))."""
+    import dataclasses
+    import parallel_worker as pw
+    out = tmp_path / "ppmoe.json"
+    _spawn("pp_moe", out, port="29579")
+    got = json.load(open(out))
+    e = pw.engine(dataclasses.replace(pw.MOE_CFG, num_layers=4), 1)
+    ref = [e.finetune_step(pw.samples(8, 130 + s, vocab=512))["lm_loss"] for s in range(3)]
+    for a, b in zip(ref, got["losses"]):
+        assert abs(a - b) < 3e-4, (ref, got["losses"])
+    assert abs(float(e.optimizer.last_grad_norm) - got["grad_norm"]) < 3e-4, (float(e.optimizer.last_grad_norm), got)
+
+
 def test_tp2_critic_matches_single_process(tmp_path):
     """Value head under tensor parallelism: same loss and gradient norm as one process (the replicated head's
     gradient into the gathered hidden states is not added up over the TP ranks)."""

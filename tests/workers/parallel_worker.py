@@ -1,4 +1,4 @@
-"""gloo worker for the parallelism parity tests: mode = tp | tp_value | tp_mla | tp_mla_lora | tp_lora | tp_lora_moe | tp_mtp | tp_moe | tp2ep2 | ep2dp4 | ep | ep_rollout | ep_grpo | cp | pp | vpp | fsdp |
+"""gloo worker for the parallelism parity tests: mode = tp | tp_value | tp_mla | tp_mla_lora | tp_lora | tp_lora_moe | tp_mtp | tp_moe | tp2ep2 | ep2dp4 | ep | ep_rollout | ep_grpo | cp | pp | pp_moe | vpp | fsdp |
 ep_dynmbs | aux_dp | tp_topk | nodistopt | dyncp | dp_grpo_balance | pg_offload."""
 import json
 import os
@@ -266,6 +266,13 @@ def main():
         lp = e.compute_log_probs(samples(3, 99))
         res = {"losses": losses, "grad_norm": float(e.optimizer.last_grad_norm),
                "logprobs": [x["logprobs"].tolist() for x in lp]}
+    elif mode == "pp_moe":
+        # MoE layers on both pipeline stages: the first stage back-propagates its own load-balance loss
+        import dataclasses
+        ps.initialize_model_parallel(tp=1, pp=2)
+        e = engine(dataclasses.replace(MOE_CFG, num_layers=4), 1)
+        losses = [e.finetune_step(samples(8, 130 + s, vocab=512))["lm_loss"] for s in range(3)]
+        res = {"losses": losses, "grad_norm": float(e.optimizer.last_grad_norm)}
     elif mode in ("pp", "vpp"):
         ps.initialize_model_parallel(tp=1, pp=2)
         mcfg = get_preset("tiny_llama", dtype="float32", qkv_bias=True, num_layers=4)

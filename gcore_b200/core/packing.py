@@ -34,6 +34,9 @@ class PackedBatch:
     # vision-language batches: (patches [sum(h*w), patch_dim], [(h, w), ...]), or with videos a dict of
     # image_patches / image_grid / video_patches / video_grid
     vision: Optional[object] = None
+    # context-parallel shards of models with multi-token prediction: the tokens / targets / loss_mask / seq_ids of the
+    # first positions behind this rank's chunk (seq_ids -1 past the end of the stream)
+    halo: Optional[Dict[str, torch.Tensor]] = None
 
     def _vision_to(self, kw):
         v = self.vision
@@ -53,7 +56,8 @@ class PackedBatch:
                            self.max_seqlen, self.targets.to(**kw), self.loss_mask.to(**kw), self.seq_ids.to(**kw),
                            self.sample_index, {k: v.to(**kw) for k, v in self.fields.items()}, self.pad_tokens,
                            self.cp_ctx,
-                           self._vision_to(kw))
+                           self._vision_to(kw),
+                           None if self.halo is None else {k: v.to(**kw) for k, v in self.halo.items()})
 
 
 def response_mask(prompt_len: int, seq_len: int) -> torch.Tensor:

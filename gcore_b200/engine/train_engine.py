@@ -389,18 +389,23 @@ class TrainingEngine:
         loss (same normaliser), averaged over depths and scaled by ``mtp_loss_scaling_factor``.  Returns
         ``(loss, [sum of masked nll, mask count])`` (Megatron's multi-token-prediction loss; label / mask shifting as in
         gpatch_v4/extended_model/mtp_mixin.py:44-80)."""
-        assert mb.cp_ctx is None, "multi-token prediction with context-parallel shards is not supported"
         cfg = self.model_cfg
         seq_ids = mb.seq_ids.long()
+        halo = mb.halo if mb.cp_ctx is not None else None
+        assert mb.cp_ctx is None or halo is not None, "context-parallel shard without its look-ahead positions"
         outs, aux = model.mtp_hidden(hidden.detach() if detach_trunk else hidden, mb.tokens, mb.position_ids,
-                                     mb.cu_seqlens, mb.max_seqlen, seq_ids)
+                                     mb.cp_ctx if mb.cp_ctx is not None else mb.cu_seqlens, mb.max_seqlen, seq_ids,
+                                     halo=halo)
         T = mb.tokens.shape[0]
         ar = torch.arange(T, device=mb.tokens.device)
+        # under context parallelism the look-ahead of the last positions lives on the next rank: read it from the halo
+        loss_mask = mb.loss_mask if halo is None else torch.cat([mb.loss_mask, halo["loss_mask"]])
+        all_targets = mb.targets if halo is None else torch.cat([mb.targets, halo["targets"]])
         total, stat = None, torch.zeros(2, device=hidden.device)
         for k, (h, valid) in enumerate(outs, start=1):
-            src = (ar + k).clamp_max(T - 1)
-            mask = mb.loss_mask[src] * valid.to(mb.loss_mask.dtype)
-            targets = mb.targets[src]
+            src = (ar + k).clamp_max(loss_mask.shape[0] - 1)
+            mask = loss_mask[src] * valid.to(loss_mask.dtype)
+            targets = all_targets[src]
             lp, _ = self._logprob_entropy(model, h, targets, False, mask)
             w = PL.aggregation_weights(mask, mb.seq_ids, mb.num_seqs + 1, per_token, denom)
             term = -(lp * w).sum()
@@ -439,7 +444,7 @@ class TrainingEngine:
         if cpg is not None:
             from ..parallel.cp import shard_packed_batch
             PL.set_context_parallel_group(cpg)
-            mb = shard_packed_batch(mb, cpg, self.device)
+            mb = shard_packed_batch(mb, cpg, self.device, halo=int(getattr(self.model_cfg, "mtp_num_layers", 0) or 0))
         io_counters.add_h2d(io_counters.tensor_bytes(mb.tokens, mb.position_ids, mb.cu_seqlens, mb.targets, mb.loss_mask,
                                                      mb.seq_ids, *mb.fields.values()))
         return mb.to(self.device)

@@ -112,6 +112,9 @@ class SelfAttention(nn.Module):
         if cfg.qk_layernorm:
             self.q_layernorm = RMSNormWeight(D, cfg, device)
             self.k_layernorm = RMSNormWeight(D, cfg, device)
+            if tp_size > 1:   # one gain for all heads, but every TP rank sees only its own heads
+                self.q_layernorm.weight.tp_partial_grad = True
+                self.k_layernorm.weight.tp_partial_grad = True
         self.window = cfg.layer_window(layer_idx)
         if cfg.attention_sinks:
             self.sinks = nn.Parameter(torch.zeros(self.hq, dtype=torch.float32, device=device))
@@ -211,6 +214,9 @@ class MLAttention(nn.Module):
             for lin in (getattr(self, "linear_q_down_proj", None), self.linear_kv_down_proj):
                 if lin is not None:
                     lin.weight.tp_partial_grad = True
+            for nm in (getattr(self, "q_layernorm", None), self.kv_layernorm):
+                if nm is not None:
+                    nm.weight.tp_partial_grad = True
         self.linear_proj = ParallelLinear(cfg.num_attention_heads * dv, H, "row", cfg, tp_size=tp_size,
                                           init_std=cfg.init_std / math.sqrt(2 * cfg.num_layers), device=device)
 
@@ -238,25 +244,40 @@ class MLAttention(nn.Module):
         cfg = self.cfg
         T, h = q_nope.shape[0], self.h
         dn, dr, dv = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim
-        kvu = self.linear_kv_up_proj(c_kv).view(T, h, dn + dv)
+        cu_q = cu_k = cu_seqlens
+        max_q = max_k = max_seqlen
+        cp_on = isinstance(cu_seqlens, CPContext)
+        if cp_on:
+            # context parallel: what crosses the ranks is the compressed latent and the shared rotary key
+            # (kv_lora + dr numbers a token, not heads x (dn + dr + dv)); each rank expands the document prefixes its
+            # queries need.  The gather's backward sums the ranks' gradient parts back onto the owning rows.
+            from ..parallel.cp import gather_from_cp
+            cpx = cu_seqlens
+            plan = cpx.plan(0)
+            cu_q, cu_k = cpx.cu_tensors(0)
+            max_q, max_k = plan.max_q, plan.max_k
+            lat = gather_from_cp(torch.cat([c_kv, k_rope], -1).contiguous(), cpx.group)[plan.k0:plan.k0 + plan.rows]
+            c_kv, k_rope = lat[:, :cfg.kv_lora_rank].contiguous(), lat[:, cfg.kv_lora_rank:]
+        Tk = c_kv.shape[0]
+        kvu = self.linear_kv_up_proj(c_kv).view(Tk, h, dn + dv)
         k_nope, v = kvu.split([dn, dv], dim=-1)
         qf = torch.cat([q_nope, q_rope], -1)
-        kf = torch.cat([k_nope, k_rope.reshape(T, 1, dr).expand(T, h, dr)], -1)
+        kf = torch.cat([k_nope, k_rope.reshape(Tk, 1, dr).expand(Tk, h, dr)], -1)
         from ..ops import _lib
         if (dn + dr, dv) == (192, 128) and qf.is_cuda and qf.dtype == torch.bfloat16 and not _lib.force_eager() \
                 and os.environ.get("GCORE_MLA_FLASH", "1") != "0":
             # 192-wide keys / 128-wide values: the tcgen05 flash kernels' wide-key instances (forward and backward)
             # over the whole packed batch
             from ..ops.attention import flash_attn_varlen
-            if max_seqlen is None:
-                max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
-            o = flash_attn_varlen(qf, kf, v.contiguous(), cu_seqlens, cu_seqlens, max_seqlen, max_seqlen, causal=True,
+            if max_q is None:
+                max_q = max_k = int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
+            o = flash_attn_varlen(qf, kf, v.contiguous(), cu_q, cu_k, max_q, max_k, causal=True,
                                   scale=1.0 / math.sqrt(dn + dr))
             return o.reshape(T, h * dv)
         # pad v to the qk head dim so one attention call serves both (extra columns are zero and sliced away)
         vpad = torch.nn.functional.pad(v, (0, dn + dr - dv))
         scale = 1.0 / math.sqrt(dn + dr)
-        if qf.is_cuda and qf.dtype in (torch.bfloat16, torch.float16) and not _lib.force_eager():
+        if qf.is_cuda and qf.dtype in (torch.bfloat16, torch.float16) and not _lib.force_eager() and not cp_on:
             # other latent geometries: the library's fused attention, one sequence at a time (memory linear in the
             # sequence length)
             bounds = cu_seqlens.tolist()
@@ -271,7 +292,7 @@ class MLAttention(nn.Module):
             o = torch.cat(outs, 0)
         else:
             from ..ops.attention import attn_varlen_ref
-            o = attn_varlen_ref(qf, kf, vpad, cu_seqlens, cu_seqlens, True, 0, None, scale)
+            o = attn_varlen_ref(qf, kf, vpad, cu_q, cu_k, True, 0, None, scale)
         return o[..., :dv].reshape(T, h * dv)
 
     def forward(self, x, pos, cu_seqlens, max_seqlen):
@@ -383,6 +404,10 @@ class GPTModel(nn.Module):
         self.cfg = cfg
         self.tp_size, self.ep_size = tp_size, ep_size
         self.sequence_parallel = sequence_parallel and tp_size > 1
+        if tp_size > 1 and not self.sequence_parallel and cfg.num_experts:
+            # without the token shard every TP rank would route (and back-propagate) the same tokens through the same
+            # unsplit experts (Megatron-LM makes the same demand of MoE models under tensor parallelism)
+            raise ValueError("mixture-of-experts layers under tensor parallelism need sequence_parallel=True")
         self.pre_process, self.post_process = pre_process, post_process
         self.recompute = recompute
         dt = _dtype(cfg)
@@ -557,27 +582,38 @@ class GPTModel(nn.Module):
         h, _ = fused.rmsnorm(x, self.decoder.final_layernorm.weight, self.cfg.rms_norm_eps, residual)
         if sp:
             h = tp_ops.gather_from_sequence_parallel(h, tp_group)
+        elif tp_group is not None and not self.value_head:
+            # every TP rank holds the whole hidden state; the vocabulary-parallel head behind it sends back only the
+            # part of the gradient that flows through its own vocabulary shard
+            h = tp_ops.copy_to_tensor_parallel(h, tp_group)
         if self.value_head:
             if sp:   # the scalar head is replicated: every TP rank back-propagates the whole value loss
                 h = tp_ops.replicated_consumer_of_gathered(h, tp_group)
             return self.output_layer(h).squeeze(-1).float(), aux_total
         return h, aux_total
 
-    def mtp_hidden(self, hidden, input_ids, position_ids, cu_seqlens, max_seqlen, seq_ids):
+    def mtp_hidden(self, hidden, input_ids, position_ids, cu_seqlens, max_seqlen, seq_ids, halo=None):
         """Final-normed hidden states of every prediction depth, ``[(h_k, valid_k)]``: ``h_k[t]`` predicts token
         ``t + k + 1`` (k = 1 .. depth) and ``valid_k[t]`` says whether tokens ``t + 1 .. t + k`` belong to the same
         packed sequence as ``t``.  ``hidden`` is the trunk's final-normed output (gathered over sequence parallel),
-        ``seq_ids`` [T] the sequence index of every position.  Returns ``([...], aux_loss)``."""
+        ``seq_ids`` [T] the sequence index of every position.  On a context-parallel shard ``halo`` carries the
+        ``tokens`` / ``seq_ids`` of the positions behind this rank's chunk (the look-ahead of its last positions) and
+        ``cu_seqlens`` is the shard's ``CPContext``.  Returns ``([...], aux_loss)``."""
         tp_group = ps.get_tensor_model_parallel_group() if self.tp_size > 1 else None
         sp, cfg = self.sequence_parallel, self.cfg
         T = input_ids.shape[0]
         pos32 = position_ids.to(torch.int32) if position_ids.dtype != torch.int32 else position_ids
         outs, aux_total, h_prev = [], None, hidden
         ar = torch.arange(T, device=input_ids.device)
+        ids_ext, seq_ext = input_ids, seq_ids
+        if halo is not None:
+            ids_ext = torch.cat([input_ids, halo["tokens"].to(input_ids.dtype)])
+            seq_ext = torch.cat([seq_ids, halo["seq_ids"].to(seq_ids.dtype)])
+        Te = ids_ext.shape[0]
         for k, blk in enumerate(self.mtp.layers, start=1):
-            src = (ar + k).clamp_max(T - 1)
-            valid = (ar + k < T) & (seq_ids[src] == seq_ids)
-            e = tp_ops.vocab_parallel_embedding(input_ids[src], self.embedding.word_embeddings.weight,
+            src = (ar + k).clamp_max(Te - 1)
+            valid = (ar + k < Te) & (seq_ext[src] == seq_ids)
+            e = tp_ops.vocab_parallel_embedding(ids_ext[src], self.embedding.word_embeddings.weight,
                                                 self.vocab_start(), tp_group)
             hp = h_prev
             if sp:
@@ -585,6 +621,10 @@ class GPTModel(nn.Module):
                 # sequence-parallel gather, whose backward sums the ranks' gradients: hand back this rank's share only
                 e = tp_ops.scatter_to_sequence_parallel(e, tp_group)
                 hp = tp_ops.slice_of_gathered(hp, tp_group)
+            elif tp_group is not None and k == 1:
+                # without sequence parallelism the trunk's output sums the gradients of all TP ranks, and this
+                # (replicated) branch computes the same full gradient on every one of them
+                hp = tp_ops.replicated_consumer_of_gathered(hp, tp_group)
             e = fused.rmsnorm(e, blk.enorm.weight, cfg.rms_norm_eps)[0]
             hp = fused.rmsnorm(hp, blk.hnorm.weight, cfg.rms_norm_eps)[0]
             x = blk.eh_proj(torch.cat([e, hp], dim=-1))
@@ -594,8 +634,10 @@ class GPTModel(nn.Module):
             h, _ = fused.rmsnorm(x, blk.final_layernorm.weight, cfg.rms_norm_eps, residual)
             if sp:
                 h = tp_ops.gather_from_sequence_parallel(h, tp_group)
-            outs.append((h, valid))
             h_prev = h
+            if not sp and tp_group is not None:
+                h = tp_ops.copy_to_tensor_parallel(h, tp_group)   # in front of the vocabulary-parallel head
+            outs.append((h, valid))
         return outs, aux_total
 
     def logits(self, hidden):

@@ -119,9 +119,11 @@ class CPContext:
         return self._tensors[w]
 
 
-def shard_packed_batch(mb, group, device):
+def shard_packed_batch(mb, group, device, halo: int = 0):
     """Slices every per-token tensor of a host-side ``PackedBatch`` to this rank's contiguous chunk and attaches the
-    ``CPContext``.  The batch must already be padded to a multiple of the group size."""
+    ``CPContext``.  The batch must already be padded to a multiple of the group size.  ``halo`` > 0 also keeps the
+    ids, targets, mask and sequence index of that many positions behind the chunk (look-ahead of the multi-token
+    prediction blocks; sequence index -1 past the end of the stream)."""
     from dataclasses import replace
     cp, rank = dist.get_world_size(group), dist.get_rank(group)
     T = mb.tokens.numel()
@@ -133,6 +135,14 @@ def shard_packed_batch(mb, group, device):
                   loss_mask=mb.loss_mask[sl], seq_ids=mb.seq_ids[sl],
                   fields={k: v[sl] for k, v in mb.fields.items()})
     out.cp_ctx = ctx
+    if halo > 0:
+        lo, hi = (rank + 1) * s, min((rank + 1) * s + halo, T)
+
+        def behind(x, fill):
+            pad = x.new_full((halo - (hi - lo),), fill)
+            return torch.cat([x[lo:hi], pad])
+        out.halo = {"tokens": behind(mb.tokens, 0), "targets": behind(mb.targets, 0),
+                    "loss_mask": behind(mb.loss_mask, 0), "seq_ids": behind(mb.seq_ids, -1)}
     return out
 
 

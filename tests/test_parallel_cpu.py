@@ -145,6 +145,52 @@ def test_pp2_with_moe_layers_on_both_stages_matches_single_process(tmp_path):
     assert abs(float(e.optimizer.last_grad_norm) - got["grad_norm"]) < 3e-4, (float(e.optimizer.last_grad_norm), got)
 
 
+def test_cp2_latent_attention_matches_single_process(tmp_path):
+    import parallel_worker as pw
+    out = tmp_path / "cpmla.json"
+    _spawn("cp_mla", out, port="29581")
+    got = json.load(open(out))
+    e = pw.engine(pw.MLA_CFG, 1)
+    ref = [e.finetune_step(pw.samples(8, 170 + s, vocab=512))["lm_loss"] for s in range(3)]
+    for a, b in zip(ref, got["losses"]):
+        assert abs(a - b) < 3e-4, (ref, got["losses"])
+    assert abs(float(e.optimizer.last_grad_norm) - got["grad_norm"]) < 3e-4, (float(e.optimizer.last_grad_norm), got)
+
+
+def test_cp2_multi_token_prediction_matches_single_process(tmp_path):
+    import parallel_worker as pw
+    out = tmp_path / "cpmtp.json"
+    _spawn("cp_mtp", out, port="29582")
+    got = json.load(open(out))
+    e = pw.engine(pw.NOSP_CFG, 1)
+    ref = [e.finetune_step(pw.samples(8, 180 + s))["lm_loss"] for s in range(3)]
+    for a, b in zip(ref, got["losses"]):
+        assert abs(a - b) < 3e-4, (ref, got["losses"])
+    assert abs(float(e.optimizer.last_grad_norm) - got["grad_norm"]) < 3e-4, (float(e.optimizer.last_grad_norm), got)
+
+
+def test_tp2_without_sequence_parallel_matches_single_process(tmp_path):
+    """Every TP rank holds all tokens: the hidden state in front of the vocabulary-parallel head sums the ranks'
+    gradient parts, the per-head q/k gains sum theirs, and the replicated multi-token-prediction branch hands the
+    trunk its gradient once."""
+    import parallel_worker as pw
+    out = tmp_path / "nosp.json"
+    _spawn("tp_nosp", out, port="29580")
+    got = json.load(open(out))
+    e = pw.engine(pw.NOSP_CFG, 1)
+    ref = [e.finetune_step(pw.samples(8, 150 + s))["lm_loss"] for s in range(3)]
+    for a, b in zip(ref, got["losses"]):
+        assert abs(a - b) < 3e-4, (ref, got["losses"])
+    assert abs(float(e.optimizer.last_grad_norm) - got["grad_norm"]) < 3e-4, (float(e.optimizer.last_grad_norm), got)
+
+
+def test_moe_under_tensor_parallelism_demands_sequence_parallel():
+    from gcore_b200.models.gpt import GPTModel
+    import parallel_worker as pw
+    with pytest.raises(ValueError, match="sequence_parallel"):
+        GPTModel(pw.MOE_CFG, tp_size=2, sequence_parallel=False, device="meta")
+
+
 def test_tp2_critic_matches_single_process(tmp_path):
     """Value head under tensor parallelism: same loss and gradient norm as one process (the replicated head's
     gradient into the gathered hidden states is not added up over the TP ranks)."""

@@ -1,4 +1,4 @@
-"""gloo worker for the parallelism parity tests: mode = tp | tp_value | tp_mla | tp_mla_lora | tp_lora | tp_lora_moe | tp_mtp | tp_moe | tp2ep2 | ep2dp4 | ep | ep_rollout | ep_grpo | cp | pp | pp_moe | vpp | fsdp |
+"""gloo worker for the parallelism parity tests: mode = tp | tp_value | tp_mla | tp_mla_lora | tp_lora | tp_lora_moe | tp_mtp | tp_moe | tp2ep2 | ep2dp4 | ep | ep_rollout | ep_grpo | cp | cp_mla | cp_mtp | pp | pp_moe | tp_nosp | vpp | fsdp |
 ep_dynmbs | aux_dp | tp_topk | nodistopt | dyncp | dp_grpo_balance | pg_offload."""
 import json
 import os
@@ -13,6 +13,10 @@ from gcore_b200.configs.config import OptimizerConfig, PolicyConfig, TrainingCon
 from gcore_b200.core import parallel_state as ps  # noqa: E402
 from gcore_b200.engine.train_engine import TrainingEngine  # noqa: E402
 from gcore_b200.models.config import ModelConfig, get_preset  # noqa: E402
+
+
+NOSP_CFG = get_preset("tiny_llama", dtype="float32", qk_layernorm=True, mtp_num_layers=1,
+                      mtp_loss_scaling_factor=0.3)
 
 
 def samples(n, seed, L=48, vocab=1024):
@@ -266,6 +270,26 @@ def main():
         lp = e.compute_log_probs(samples(3, 99))
         res = {"losses": losses, "grad_norm": float(e.optimizer.last_grad_norm),
                "logprobs": [x["logprobs"].tolist() for x in lp]}
+    elif mode == "cp_mla":
+        # latent attention under context parallelism: the compressed latent crosses the ranks, not the expanded heads
+        ps.initialize_model_parallel(tp=1, cp=2)
+        e = engine(MLA_CFG, 1)
+        losses = [e.finetune_step(samples(8, 170 + s, vocab=512))["lm_loss"] for s in range(3)]
+        res = {"losses": losses, "grad_norm": float(e.optimizer.last_grad_norm)}
+    elif mode == "cp_mtp":
+        # multi-token prediction on context-parallel shards: the look-ahead of a chunk's last positions is its halo
+        ps.initialize_model_parallel(tp=1, cp=2)
+        e = engine(NOSP_CFG, 1)
+        losses = [e.finetune_step(samples(8, 180 + s))["lm_loss"] for s in range(3)]
+        res = {"losses": losses, "grad_norm": float(e.optimizer.last_grad_norm)}
+    elif mode == "tp_nosp":
+        # tensor parallelism without the sequence-parallel token shard: per-head q/k gains, multi-token prediction
+        import dataclasses
+        ps.initialize_model_parallel(tp=2)
+        e = engine(NOSP_CFG, 2, sp=False)
+        assert not e.model.sequence_parallel
+        losses = [e.finetune_step(samples(8, 150 + s))["lm_loss"] for s in range(3)]
+        res = {"losses": losses, "grad_norm": float(e.optimizer.last_grad_norm)}
     elif mode == "pp_moe":
         # MoE layers on both pipeline stages: the first stage back-propagates its own load-balance loss
         import dataclasses

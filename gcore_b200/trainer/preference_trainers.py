@@ -19,6 +19,16 @@ from ..engine.train_engine import TrainingEngine, backend_scope
 from ..loss import policy_loss as PL
 
 
+def _whole_stream(x: torch.Tensor, mb) -> torch.Tensor:
+    """Per-token outputs of a context-parallel shard -> the whole packed stream on every rank of the group (sequence
+    ends and pooled means index global positions).  Every rank then computes the same loss; the gather's backward adds
+    the ranks' copies up, which the gradient reduction's division by the group size undoes."""
+    if mb.cp_ctx is None:
+        return x
+    from ..parallel.cp import gather_from_cp
+    return gather_from_cp(x.contiguous(), mb.cp_ctx.group)
+
+
 def _seq_logps(engine: TrainingEngine, model, samples: Sequence[dict], grad: bool) -> torch.Tensor:
     """Sum of masked token log-probs per sample, differentiable when ``grad``."""
     out = []
@@ -30,6 +40,11 @@ def _seq_logps(engine: TrainingEngine, model, samples: Sequence[dict], grad: boo
             lp, _ = engine._logprob_entropy(model, hidden, mb.targets, False, mb.loss_mask)
             seg = torch.zeros(mb.num_seqs + 1, dtype=lp.dtype, device=lp.device).index_add(0, mb.seq_ids.long(),
                                                                                            lp * mb.loss_mask)
+            if mb.cp_ctx is not None:
+                # a sequence's tokens are spread over the context-parallel ranks: every rank needs the whole sum for the
+                # (non-linear) preference loss, and sends gradient back only into its own tokens
+                from ..parallel.cp import all_reduce_cp
+                seg = all_reduce_cp(seg, mb.cp_ctx.group)
             out.append((idx, seg[:len(idx)]))
     res = [None] * len(samples)
     for idx, seg in out:
@@ -58,13 +73,24 @@ def dpo_step(engine: TrainingEngine, chosen: List[dict], rejected: List[dict], b
                 return float(torch.as_tensor(m).sum())
             return float(len(s["tokens"]) - int(s.get("prompt_length", 0)))
         ntok = sum(resp_tokens(s) for s in chosen)
+        dpw = ps.get_data_parallel_world_size()
+        if dpw > 1:
+            # token mean over the global batch: (sum of all replicas' tokens) / dp is what the gradient average needs
+            t = torch.tensor([ntok], dtype=torch.float64, device=engine.device)
+            dist.all_reduce(t, group=ps.get_data_parallel_group())
+            ntok = float(t) / dpw
         loss = loss - sft_coef * pol[:n].sum() / max(ntok, 1.0)
-    dp = ps.get_data_parallel_world_size(with_context_parallel=True)
-    (loss / 1.0).backward()
-    engine.ddp.finish_grad_sync(extra_scale=1.0)
+    loss.backward()
+    # the loss is the mean over this data-parallel rank's pairs (averaged over the replicas by the reduction); the
+    # context-parallel ranks of one replica hold parts of the same gradient, which add up
+    engine.ddp.finish_grad_sync(extra_scale=float(ps.get_context_parallel_world_size()))
     lr = engine.optimizer.step()
     engine.step += 1
-    out = {"dpo/loss": float(loss.detach()), "lr": lr, "grad_norm": float(engine.optimizer.last_grad_norm)}
+    shown = loss.detach().clone()
+    if ps.get_data_parallel_world_size() > 1:
+        dist.all_reduce(shown, group=ps.get_data_parallel_group())
+        shown /= ps.get_data_parallel_world_size()
+    out = {"dpo/loss": float(shown), "lr": lr, "grad_norm": float(engine.optimizer.last_grad_norm)}
     out.update({k: float(v) for k, v in m.items()})
     return out
 
@@ -80,6 +106,7 @@ def rm_step(engine: TrainingEngine, chosen: List[dict], rejected: List[dict], ma
         for idx in engine._microbatches(allc):
             mb = engine._pack(allc, idx)
             v, _ = engine._hidden(engine.model, mb)
+            v = _whole_stream(v, mb)
             last = (mb.cu_seqlens[1:len(idx) + 1] - 1).long()
             scores.append((idx, v[last]))
     s = [None] * len(allc)
@@ -110,6 +137,7 @@ def _pooled(engine: TrainingEngine, samples: Sequence[dict], grad: bool, pooling
         for idx in engine._microbatches(samples, forward_only=not grad):
             mb = engine._pack(samples, idx)
             h, _ = engine._hidden(engine.model, mb)
+            h = _whole_stream(h, mb)
             if grad and getattr(engine.model, "sequence_parallel", False):
                 # pooling and the contrastive loss are repeated in full on every TP rank, so every rank back-propagates
                 # the whole gradient into the gathered hidden states
@@ -118,10 +146,11 @@ def _pooled(engine: TrainingEngine, samples: Sequence[dict], grad: bool, pooling
                 h = replicated_consumer_of_gathered(h, ps.get_tensor_model_parallel_group())
             if pooling == "mean":
                 n = mb.num_seqs + 1
+                sid = _whole_stream(mb.seq_ids, mb).long()
                 seg = torch.zeros(n, h.shape[1], dtype=torch.float32, device=h.device).index_add(
-                    0, mb.seq_ids.long(), h.float())
+                    0, sid, h.float())
                 cnt = torch.zeros(n, dtype=torch.float32, device=h.device).index_add(
-                    0, mb.seq_ids.long(), torch.ones(h.shape[0], device=h.device))
+                    0, sid, torch.ones(h.shape[0], device=h.device))
                 vec = seg[:len(idx)] / cnt[:len(idx), None].clamp_min(1.0)
             else:
                 vec = h[(mb.cu_seqlens[1:len(idx) + 1] - 1).long()].float()

@@ -169,6 +169,33 @@ def test_cp2_multi_token_prediction_matches_single_process(tmp_path):
     assert abs(float(e.optimizer.last_grad_norm) - got["grad_norm"]) < 3e-4, (float(e.optimizer.last_grad_norm), got)
 
 
+@pytest.mark.parametrize("mode", ["dpo_cp", "dpo_dp", "dpo_tp"])
+def test_two_rank_dpo_matches_single_process(tmp_path, mode):
+    import parallel_worker as pw
+    from gcore_b200.models.config import get_preset
+    from gcore_b200.trainer.preference_trainers import dpo_step
+    out = tmp_path / f"{mode}.json"
+    _spawn(mode, out, port="29583")
+    got = json.load(open(out))
+    e = pw.engine(get_preset("tiny_llama", dtype="float32", qkv_bias=True), 1)
+    ref = [dpo_step(e, pw.samples(4, 200 + s), pw.samples(4, 300 + s), beta=0.5, reference_free=True, sft_coef=0.1)
+           for s in range(2)]
+    for r, a, b in zip(ref, got["losses"], got["grad_norms"]):
+        assert abs(r["dpo/loss"] - a) < 1e-3 * abs(r["dpo/loss"]), (ref, got)
+        assert abs(r["grad_norm"] - b) < 1e-3 * r["grad_norm"], (ref, got)
+
+
+def test_cp2_reward_model_and_embedding_steps_match_single_process(tmp_path):
+    import parallel_worker as pw
+    out = tmp_path / "rmcp.json"
+    _spawn("rm_cp", out, port="29584")
+    got = json.load(open(out))["runs"]
+    ref = pw.preference_run()["runs"]
+    for (l0, g0), (l1, g1) in zip(ref, got):
+        assert abs(l0 - l1) < 1e-3 * max(abs(l0), 1e-2), (ref, got)
+        assert abs(g0 - g1) < 1e-3 * max(g0, 1e-2), (ref, got)
+
+
 def test_tp2_without_sequence_parallel_matches_single_process(tmp_path):
     """Every TP rank holds all tokens: the hidden state in front of the vocabulary-parallel head sums the ranks'
     gradient parts, the per-head q/k gains sum theirs, and the replicated multi-token-prediction branch hands the

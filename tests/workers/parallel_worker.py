@@ -1,4 +1,4 @@
-"""gloo worker for the parallelism parity tests: mode = tp | tp_value | tp_mla | tp_mla_lora | tp_lora | tp_lora_moe | tp_mtp | tp_moe | tp2ep2 | ep2dp4 | ep | ep_rollout | ep_grpo | cp | cp_mla | cp_mtp | pp | pp_moe | tp_nosp | vpp | fsdp |
+"""gloo worker for the parallelism parity tests: mode = tp | tp_value | tp_mla | tp_mla_lora | tp_lora | tp_lora_moe | tp_mtp | tp_moe | tp2ep2 | ep2dp4 | ep | ep_rollout | ep_grpo | cp | cp_mla | cp_mtp | dpo_cp | dpo_dp | dpo_tp | rm_cp | pp | pp_moe | tp_nosp | vpp | fsdp |
 ep_dynmbs | aux_dp | tp_topk | nodistopt | dyncp | dp_grpo_balance | pg_offload."""
 import json
 import os
@@ -73,6 +73,21 @@ def value_samples():
         s["mask"] = s["loss_mask"]
         s["returns"], s["values"] = torch.randn(n, generator=g), torch.randn(n, generator=g)
     return smp
+
+
+def preference_run():
+    """Two reward-model steps and one contrastive step per pooling mode: (loss, gradient norm) of each."""
+    from gcore_b200.trainer.preference_trainers import embedding_step, rm_step
+    e = value_engine(1)
+    out = []
+    for s in range(2):
+        o = rm_step(e, samples(4, 200 + s), samples(4, 300 + s))
+        out.append([o["rm/loss"], float(e.optimizer.last_grad_norm)])
+    e2 = engine(get_preset("tiny_llama", dtype="float32", qkv_bias=True), 1)
+    for pooling in ("last", "mean"):
+        o = embedding_step(e2, samples(4, 400), samples(4, 500), pooling=pooling)
+        out.append([o["embedding/loss"], o["grad_norm"]])
+    return {"runs": out}
 
 
 def lora_engine(mcfg, tp, targets=None):
@@ -282,6 +297,22 @@ def main():
         e = engine(NOSP_CFG, 1)
         losses = [e.finetune_step(samples(8, 180 + s))["lm_loss"] for s in range(3)]
         res = {"losses": losses, "grad_norm": float(e.optimizer.last_grad_norm)}
+    elif mode in ("dpo_cp", "dpo_dp", "dpo_tp"):
+        # preference pairs: sequence log-probs cross context-parallel ranks; the token-mean SFT term is global
+        from gcore_b200.trainer.preference_trainers import dpo_step
+        ps.initialize_model_parallel(tp=2 if mode == "dpo_tp" else 1, cp=2 if mode == "dpo_cp" else 1)
+        e = engine(get_preset("tiny_llama", dtype="float32", qkv_bias=True), 2 if mode == "dpo_tp" else 1)
+        dpr, dpw = ps.get_data_parallel_rank(), ps.get_data_parallel_world_size()
+        outs = []
+        for s in range(2):
+            ch, rj = samples(4, 200 + s), samples(4, 300 + s)
+            outs.append(dpo_step(e, ch[dpr::dpw], rj[dpr::dpw], beta=0.5, reference_free=True, sft_coef=0.1))
+        res = {"losses": [o["dpo/loss"] for o in outs], "grad_norms": [o["grad_norm"] for o in outs]}
+    elif mode == "rm_cp":
+        # sequence-end scores and pooled embeddings index the whole stream, which lives on two context-parallel ranks
+        from gcore_b200.trainer.preference_trainers import embedding_step, rm_step
+        ps.initialize_model_parallel(tp=1, cp=2)
+        res = preference_run()
     elif mode == "tp_nosp":
         # tensor parallelism without the sequence-parallel token shard: per-head q/k gains, multi-token prediction
         import dataclasses

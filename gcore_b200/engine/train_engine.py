@@ -552,15 +552,22 @@ class TrainingEngine:
         assert self.value_head
         self.model.eval()
         with backend_scope(self.backend):
-            for idx in self._microbatches(samples, forward_only=True):
-                mb = self._pack(samples, idx)
-                v, _ = self._hidden(self.model, mb)
+            batches = self._microbatches(samples, forward_only=True)
+            results = self._for_each_microbatch(self.model, samples, batches, (),
+                                                lambda mb, v, aux: self._gather_cp(v.float()), forward_only=True)
+            for bi, idx in enumerate(batches):
                 if isinstance(idx, FillerBatch):
                     continue
-                vc = self._gather_cp(v.float()).cpu()
-                cu = mb.cu_seqlens.tolist()
-                for j, i in enumerate(idx):
-                    samples[i]["values"] = vc[cu[j]:cu[j + 1]].clone()
+                lens = [len(samples[i]["tokens"]) for i in idx]
+                pad_mult = self._pad_multiple("static")
+                total_padded = (sum(lens) + pad_mult - 1) // pad_mult * pad_mult
+                # with pipeline stages the last one holds the values: every stage receives them
+                v = self._from_last_stage(results[bi] if results else None, (total_padded,), torch.float32)
+                vc = v.cpu()
+                o = 0
+                for i, ln in zip(idx, lens):
+                    samples[i]["values"] = vc[o:o + ln].clone()
+                    o += ln
         return samples
 
     # ------------------------------------------------------------------ shared step machinery
@@ -808,13 +815,15 @@ class TrainingEngine:
         for s in samples:
             s.setdefault("loss_mask", s["mask"])
         with backend_scope(self.backend):
-            for idx in self._microbatches(samples):
-                mb = self._pack(samples, idx, ["returns", "values"])
-                v, _ = self._hidden(self.model, mb)
+            def step(mb, v, aux):
                 w = mb.loss_mask / denom
                 loss = PL.value_loss(v, mb.fields["values"], mb.fields["returns"], w, cfg.ppo_value_clip)
-                loss.backward()
                 acc["value/loss"] += torch.stack([loss.detach() * denom, mb.loss_mask.sum()])
+                return loss
+
+            # through the micro-batch driver, so that a critic split over pipeline stages runs the same schedule as
+            # the policy
+            self._for_each_microbatch(self.model, samples, self._microbatches(samples), ["returns", "values"], step)
             lr, gn = self._finish_step()
         out = self._reduce_metrics(acc)
         out.update({"value/lr": lr, "value/grad_norm": gn})

@@ -196,6 +196,16 @@ def test_cp2_reward_model_and_embedding_steps_match_single_process(tmp_path):
         assert abs(g0 - g1) < 1e-3 * max(g0, 1e-2), (ref, got)
 
 
+def test_pp2_critic_trains_and_scores_like_a_single_process(tmp_path):
+    import parallel_worker as pw
+    out = tmp_path / "ppvalue.json"
+    _spawn("pp_value", out, port="29585")
+    got = json.load(open(out))
+    ref = pw.value_run()
+    for k in ref:
+        assert abs(ref[k] - got[k]) < 1e-3 * max(abs(ref[k]), 1e-1), (k, ref, got)
+
+
 def test_tp2_without_sequence_parallel_matches_single_process(tmp_path):
     """Every TP rank holds all tokens: the hidden state in front of the vocabulary-parallel head sums the ranks'
     gradient parts, the per-head q/k gains sum theirs, and the replicated multi-token-prediction branch hands the

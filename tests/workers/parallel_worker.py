@@ -1,4 +1,4 @@
-"""gloo worker for the parallelism parity tests: mode = tp | tp_value | tp_mla | tp_mla_lora | tp_lora | tp_lora_moe | tp_mtp | tp_moe | tp2ep2 | ep2dp4 | ep | ep_rollout | ep_grpo | cp | cp_mla | cp_mtp | dpo_cp | dpo_dp | dpo_tp | rm_cp | pp | pp_moe | tp_nosp | vpp | fsdp |
+"""gloo worker for the parallelism parity tests: mode = tp | tp_value | tp_mla | tp_mla_lora | tp_lora | tp_lora_moe | tp_mtp | tp_moe | tp2ep2 | ep2dp4 | ep | ep_rollout | ep_grpo | cp | cp_mla | cp_mtp | dpo_cp | dpo_dp | dpo_tp | rm_cp | pp_value | pp | pp_moe | tp_nosp | vpp | fsdp |
 ep_dynmbs | aux_dp | tp_topk | nodistopt | dyncp | dp_grpo_balance | pg_offload."""
 import json
 import os
@@ -73,6 +73,17 @@ def value_samples():
         s["mask"] = s["loss_mask"]
         s["returns"], s["values"] = torch.randn(n, generator=g), torch.randn(n, generator=g)
     return smp
+
+
+def value_run():
+    e = value_engine(1)
+    out = e.rl_train_value(value_samples())
+    smp = value_samples()
+    for s in smp:
+        s.pop("values")
+    e.compute_values(smp)
+    return {"loss": out["value/loss"], "grad_norm": out["value/grad_norm"],
+            "values_sum": float(sum(s["values"].double().sum() for s in smp)), "value_3_5": float(smp[3]["values"][5])}
 
 
 def preference_run():
@@ -313,6 +324,10 @@ def main():
         from gcore_b200.trainer.preference_trainers import embedding_step, rm_step
         ps.initialize_model_parallel(tp=1, cp=2)
         res = preference_run()
+    elif mode == "pp_value":
+        # a critic split over two pipeline stages trains and scores through the same schedule as the policy
+        ps.initialize_model_parallel(tp=1, pp=2)
+        res = value_run()
     elif mode == "tp_nosp":
         # tensor parallelism without the sequence-parallel token shard: per-head q/k gains, multi-token prediction
         import dataclasses

@@ -593,7 +593,9 @@ class TrainingEngine:
         the effective ``moe_aux_loss_coef`` is then the configured one whatever the parallel layout or the packing
         (Megatron scales by 1 / num_microbatches and averages over data parallel)."""
         dp = ps.get_data_parallel_world_size(with_context_parallel=True)
-        return 1.0 / (max(n_microbatches, 1) * max(dp, 1))
+        # under sequence parallelism every TP rank evaluates the term on its own token shard and the router gradients
+        # of the ranks are summed: each rank's term is one of TP equal shares
+        return 1.0 / (max(n_microbatches, 1) * max(dp, 1) * max(self._tp_pad(), 1))
 
     def _finish_step(self, lr=None):
         dp = ps.get_data_parallel_world_size(with_context_parallel=True)
